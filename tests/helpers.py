@@ -1,0 +1,115 @@
+"""Shared by the tests: two tiny OPT configurations that differ in every size and option, model
+folders with seeded random weights (made in a temporary folder), the plain implementation's
+logits, trace builders and the comparison with its tolerances."""
+from __future__ import annotations
+
+import io
+import json
+import os
+import tempfile
+
+import numpy as np
+import torch
+
+from plain import opt_plain
+from transformers_neuronx_b200.config import OPTConfig
+from transformers_neuronx_b200.models import opt as opt_arch
+from transformers_neuronx_b200.models.decoder import DecoderModel
+from transformers_neuronx_b200.weights import load_tensors, write_model_folder
+
+CONFIG_A = dict(vocab_size=512, hidden_size=64, num_hidden_layers=2, num_attention_heads=4, ffn_dim=256,
+                max_position_embeddings=128, word_embed_proj_dim=64, do_layer_norm_before=True,
+                enable_bias=True, layer_norm_elementwise_affine=True, layer_norm_eps=1e-5,
+                activation_function="relu", init_std=0.02, architectures=["OPTForCausalLM"], model_type="opt")
+CONFIG_B = dict(vocab_size=1000, hidden_size=96, num_hidden_layers=3, num_attention_heads=3, ffn_dim=320,
+                max_position_embeddings=256, word_embed_proj_dim=48, do_layer_norm_before=False,
+                enable_bias=False, layer_norm_elementwise_affine=False, layer_norm_eps=1e-6,
+                activation_function="relu", init_std=0.05, architectures=["OPTForCausalLM"], model_type="opt")
+CONFIGS = {"A": CONFIG_A, "B": CONFIG_B}
+
+# Largest allowed |engine - plain| as a fraction of the largest |plain logit| of the compared rows.
+# float32: both sides compute in 32-bit and differ by the order of additions only.
+# bfloat16: activations are rounded to 8 bits of mantissa between kernels (relative step 2^-8).
+TOLERANCE = {"float32": 2e-5, "bfloat16": 4e-2}
+
+
+class TinyModel:
+    """A model folder with random weights plus what the tests need to know about it."""
+
+    def __init__(self, name: str, seed: int = 0, root: str = None):
+        self.name = name
+        self.cfg_dict = dict(CONFIGS[name])
+        self.cfg = OPTConfig.from_dict(self.cfg_dict)
+        self._tmp = tempfile.TemporaryDirectory(prefix=f"tnx_tiny_{name}_", dir=root)
+        self.folder = self._tmp.name
+        specs = DecoderModel(opt_arch.build_spec(self.cfg)).tensor_specs()
+        write_model_folder(self.folder, self.cfg, specs, seed)
+        self.tensors = {k: v.clone() for k, v in load_tensors(self.folder, specs).items()}
+        self._plain_cache = {}
+
+    def plain_logits(self, ids) -> torch.Tensor:
+        key = tuple(int(i) for i in ids)
+        if key not in self._plain_cache:
+            self._plain_cache[key] = opt_plain.forward_logits(list(key), self.tensors, self.cfg.to_dict())
+        return self._plain_cache[key]
+
+    def random_ids(self, n: int, seed: int):
+        g = torch.Generator().manual_seed(seed)
+        ids = torch.randint(3, self.cfg.vocab_size, (n,), generator=g).tolist()
+        ids[0] = self.cfg.bos_token_id
+        return ids
+
+
+def trace_lines(steps) -> list:
+    return [json.dumps(s) for s in steps]
+
+
+def run_trace_inprocess(folder: str, dtype: str, steps, max_tokens: int):
+    """Runs the replay program's own function in this process; returns {step: array [wanted, vocab]}."""
+    from transformers_neuronx_b200.engine.replay import replay
+    out_dir = tempfile.mkdtemp(prefix="tnx_trace_out_")
+    sink = io.StringIO()
+    rc = replay(folder, dtype, out_dir, max_tokens, lines=trace_lines(steps), out=sink)
+    assert rc == 0
+    done = [l for l in sink.getvalue().splitlines() if l.startswith("done ")]
+    assert [int(l.split()[1]) for l in done] == [s["step"] for s in steps]
+    res = {}
+    for s in steps:
+        p = os.path.join(out_dir, f"{s['step']}.f32")
+        n_want = sum(len(e.get("want", [])) for e in s["entries"])
+        if n_want:
+            arr = np.fromfile(p, dtype="<f4")
+            res[s["step"]] = arr.reshape(n_want, -1)
+        else:
+            assert not os.path.exists(p)
+    return res
+
+
+def live_tokens_rounded(counts, unit=64):
+    return sum(-(-c // unit) * unit for c in counts)
+
+
+def compare_trace(model: TinyModel, requests: dict, steps, results, dtype: str):
+    """requests: {id: full token list}.  Checks every wanted row against the plain logits of its
+    request at its position; returns the largest relative error seen."""
+    pos = {rid: 0 for rid in requests}
+    worst = 0.0
+    for s in steps:
+        row = 0
+        for e in s["entries"]:
+            rid, n = e["id"], len(e["tokens"])
+            assert list(e["tokens"]) == list(requests[rid][pos[rid]:pos[rid] + n]), "trace builder bug"
+            plain = model.plain_logits(requests[rid]) if e.get("want") else None
+            for w in e.get("want", []):
+                got = torch.from_numpy(results[s["step"]][row].copy())
+                want = plain[pos[rid] + w]
+                scale = float(want.abs().max())
+                err = float((got - want).abs().max()) / scale
+                worst = max(worst, err)
+                assert err <= TOLERANCE[dtype], (
+                    f"{dtype} step {s['step']} request {rid} position {pos[rid] + w}: "
+                    f"relative error {err:.3e} > {TOLERANCE[dtype]:.1e} "
+                    f"(first wrong place: argmax got {int(got.argmax())}, plain {int(want.argmax())})")
+                row += 1
+            pos[rid] += n
+    return worst

@@ -1,0 +1,140 @@
+"""Trace replay against the plain implementation, in 32-bit and in bfloat16: each request alone and
+whole; most of it in one step and the last 32 tokens one by one; in portions of changing size down
+to two tokens; and mixed, up to four live requests with so few pages that they are used again."""
+import json
+import os
+import subprocess
+import sys
+import tempfile
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import (TOLERANCE, TinyModel, compare_trace, live_tokens_rounded, run_trace_inprocess,
+                     trace_lines)
+
+pytestmark = pytest.mark.gpu
+DTYPES = ["float32", "bfloat16"]
+LENGTHS = {"A": [5, 17, 33, 64, 120], "B": [1, 40, 120, 250]}
+
+
+@pytest.fixture(scope="module", params=["A", "B"])
+def tiny(request):
+    return TinyModel(request.param, seed=11)
+
+
+def _requests(tiny, lengths=None):
+    lengths = lengths or LENGTHS[tiny.name]
+    return {f"r{i}": tiny.random_ids(n, seed=100 + i) for i, n in enumerate(lengths)}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_whole(tiny, dtype):
+    reqs = _requests(tiny)
+    steps = [{"step": i, "entries": [{"id": rid, "tokens": ids, "want": list(range(len(ids)))}], "end": [rid]}
+             for i, (rid, ids) in enumerate(reqs.items())]
+    res = run_trace_inprocess(tiny.folder, dtype, steps, live_tokens_rounded([max(len(v) for v in reqs.values())]))
+    compare_trace(tiny, reqs, steps, res, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_prefix_then_one_by_one(tiny, dtype):
+    reqs = _requests(tiny, [n for n in LENGTHS[tiny.name] if n > 33])
+    steps, k = [], 0
+    for rid, ids in reqs.items():
+        cut = len(ids) - 32
+        steps.append({"step": k, "entries": [{"id": rid, "tokens": ids[:cut], "want": [cut - 1]}], "end": []})
+        k += 1
+        for j in range(cut, len(ids)):
+            steps.append({"step": k, "entries": [{"id": rid, "tokens": [ids[j]], "want": [0]}],
+                          "end": [rid] if j == len(ids) - 1 else []})
+            k += 1
+    res = run_trace_inprocess(tiny.folder, dtype, steps, live_tokens_rounded([max(len(v) for v in reqs.values())]))
+    compare_trace(tiny, reqs, steps, res, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_portions_of_changing_size(tiny, dtype):
+    reqs = _requests(tiny, [n for n in LENGTHS[tiny.name] if n >= 17])
+    sizes = [2, 3, 16, 2, 7, 17, 5, 2, 31, 4, 15, 33]
+    steps, k = [], 0
+    for rid, ids in reqs.items():
+        p, j = 0, 0
+        while p < len(ids):
+            n = min(sizes[j % len(sizes)], len(ids) - p)
+            if len(ids) - p - n == 1:      # never leave a single token: portions go down to two
+                n += 1
+            steps.append({"step": k, "entries": [{"id": rid, "tokens": ids[p:p + n], "want": [0, n - 1]}],
+                          "end": [rid] if p + n == len(ids) else []})
+            p += n; j += 1; k += 1
+    res = run_trace_inprocess(tiny.folder, dtype, steps, live_tokens_rounded([max(len(v) for v in reqs.values())]))
+    compare_trace(tiny, reqs, steps, res, dtype)
+
+
+def mixed_steps(reqs, chunk_sizes=(7, 16, 2, 21, 5), decode_tail=12, max_live=4):
+    """Up to `max_live` requests live: portions of some prompts beside single decoded tokens of others;
+    a request ends, its pages go back, and the next waiting request takes them."""
+    waiting = list(reqs.items())
+    live = {}          # rid -> position reached
+    steps, k, j = [], 0, 0
+    peak = 0
+    while waiting or live:
+        while waiting and len(live) < max_live:
+            rid, ids = waiting.pop(0)
+            live[rid] = 0
+        entries, end = [], []
+        for rid in list(live):
+            ids, p = reqs[rid], live[rid]
+            prompt_end = max(1, len(ids) - decode_tail)
+            if p < prompt_end:
+                n = min(chunk_sizes[j % len(chunk_sizes)], prompt_end - p)
+                j += 1
+                if k % 3 == 2 and len(entries) >= 2:
+                    continue                 # a request may be left out of a step and go on later
+                want = [n - 1]
+            else:
+                n, want = 1, [0]
+            entries.append({"id": rid, "tokens": ids[p:p + n], "want": want})
+            live[rid] = p + n
+            if live[rid] == len(ids):
+                end.append(rid)
+        peak = max(peak, live_tokens_rounded([live[r] for r in live]))
+        steps.append({"step": k, "entries": entries, "end": end})
+        for rid in end:
+            del live[rid]
+        k += 1
+    return steps, peak
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_mixed_with_page_reuse(tiny, dtype):
+    lens = {"A": [40, 90, 17, 64, 120, 33, 75, 50], "B": [120, 30, 200, 64, 250, 90, 45, 160]}[tiny.name]
+    reqs = _requests(tiny, lens)
+    steps, peak = mixed_steps(reqs)
+    assert sum(-(-n // 64) * 64 for n in lens) > peak, "the pool must be too small for all requests at once"
+    res = run_trace_inprocess(tiny.folder, dtype, steps, peak)
+    compare_trace(tiny, reqs, steps, res, dtype)
+
+
+def test_program_in_a_subprocess():
+    """bin/trace_run itself, as a user calls it: steps on stdin, `done` lines, files, exit code 0."""
+    tiny = TinyModel("A", seed=3)
+    ids = tiny.random_ids(40, seed=5)
+    steps = [{"step": 0, "entries": [{"id": "x", "tokens": ids[:30], "want": [29]}], "end": []},
+             {"step": 1, "entries": [{"id": "x", "tokens": ids[30:], "want": [0, 9]}], "end": ["x"]},
+             {"step": 2, "entries": [{"id": "y", "tokens": ids[:8], "want": []}], "end": ["y"]}]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = tempfile.mkdtemp(prefix="tnx_trace_sub_")
+    proc = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", tiny.folder,
+                           "--dtype", "float32", "--out", out, "--max-tokens", "64"],
+                          input="\n".join(trace_lines(steps)) + "\n", capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2"]
+    assert not os.path.exists(os.path.join(out, "2.f32"))
+    plain = tiny.plain_logits(ids)
+    got0 = np.fromfile(os.path.join(out, "0.f32"), dtype="<f4").reshape(1, -1)
+    got1 = np.fromfile(os.path.join(out, "1.f32"), dtype="<f4").reshape(2, -1)
+    for got, p in ((got0[0], 29), (got1[0], 30), (got1[1], 39)):
+        err = float(np.abs(got - plain[p].numpy()).max()) / float(plain[p].abs().max())
+        assert err <= TOLERANCE["float32"]

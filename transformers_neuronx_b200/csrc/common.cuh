@@ -1,0 +1,65 @@
+// Helpers shared by every kernel file of the engine.  Each .cu file is built into a shared
+// library of its own with plain C entry points (no torch headers): the Python side loads it with
+// ctypes, passes device pointers and the current CUDA stream, and checks the returned code.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define TNX_EXPORT extern "C" __attribute__((visibility("default")))
+
+// Entry points return 0 on success, a CUDA error code (>0) if a launch failed, or a negative
+// code of their own for an argument they refuse.
+#define TNX_ERR_BAD_ARG (-1)
+#define TNX_ERR_UNSUPPORTED (-2)
+#define TNX_ERR_TIMEOUT (-3)
+
+static inline int tnx_launch_status() {
+    cudaError_t e = cudaGetLastError();
+    return (int)e;
+}
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_float<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a thread block; `scratch` holds at least 32 floats of shared memory.  Every thread
+// receives the result.  The order of the additions is fixed by the block size alone.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float r = (lane < nwarps) ? scratch[lane] : 0.f;
+    r = warp_sum(r);
+    return r;
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float r = (lane < nwarps) ? scratch[lane] : -INFINITY;
+    r = warp_max(r);
+    return r;
+}

@@ -1,0 +1,63 @@
+// Token embedding gather + learned position embedding.
+//
+//   x[n, :] = (tok_table ? tok_table[ids[n], :] : pre[n, :]) + (pos_table ? pos_table[positions[n] + offset, :] : 0)
+//
+// written as the 32-bit residual stream and, when asked, also in the activation type for a block
+// that reads its input un-normalised.  `pre` is the 32-bit output of project_in when the embedding
+// width differs from the hidden width.  gather_rows copies table rows in the activation type (the
+// input of project_in).
+#include "common.cuh"
+
+template <typename TT, typename TA>
+__global__ void embed_kernel(const TT* __restrict__ tok_table, const float* __restrict__ pre,
+                             const int* __restrict__ ids, const TT* __restrict__ pos_table,
+                             const int* __restrict__ positions, int pos_offset,
+                             float* __restrict__ out_f32, TA* __restrict__ out_act, int H) {
+    const int n = blockIdx.x;
+    const TT* trow = tok_table ? tok_table + (size_t)ids[n] * H : nullptr;
+    const TT* prow = pos_table ? pos_table + (size_t)(positions[n] + pos_offset) * H : nullptr;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float v = trow ? to_float(trow[c]) : pre[(size_t)n * H + c];
+        if (prow) v += to_float(prow[c]);
+        if (out_f32) out_f32[(size_t)n * H + c] = v;
+        if (out_act) out_act[(size_t)n * H + c] = from_float<TA>(v);
+    }
+}
+
+template <typename TT, typename TA>
+__global__ void gather_rows_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
+                                   TA* __restrict__ out, int E) {
+    const int n = blockIdx.x;
+    const TT* row = table + (size_t)ids[n] * E;
+    for (int c = threadIdx.x; c < E; c += blockDim.x) out[(size_t)n * E + c] = from_float<TA>(to_float(row[c]));
+}
+
+// table_bf16 / act_bf16: 1 when the tables / the activation output are bfloat16, 0 for float.
+TNX_EXPORT int tnx_embed(const void* tok_table, const float* pre, const int* ids, const void* pos_table,
+                         const int* positions, int pos_offset, float* out_f32, void* out_act,
+                         int N, int H, int table_bf16, int act_bf16, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (H <= 0 || (!tok_table && !pre)) return TNX_ERR_BAD_ARG;
+    const int threads = H >= 1024 ? 256 : 128;
+#define LAUNCH(TT, TA)                                                                            \
+    embed_kernel<TT, TA><<<N, threads, 0, stream>>>((const TT*)tok_table, pre, ids, (const TT*)pos_table, \
+                                                    positions, pos_offset, out_f32, (TA*)out_act, H)
+    if (table_bf16 && act_bf16) LAUNCH(bf16, bf16);
+    else if (table_bf16 && !act_bf16) LAUNCH(bf16, float);
+    else if (!table_bf16 && act_bf16) LAUNCH(float, bf16);
+    else LAUNCH(float, float);
+#undef LAUNCH
+    return tnx_launch_status();
+}
+
+TNX_EXPORT int tnx_gather_rows(const void* table, const int* ids, void* out, int N, int E,
+                               int table_bf16, int act_bf16, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (E <= 0) return TNX_ERR_BAD_ARG;
+    const int threads = E >= 1024 ? 256 : 128;
+    if (table_bf16 && act_bf16) gather_rows_kernel<bf16, bf16><<<N, threads, 0, stream>>>((const bf16*)table, ids, (bf16*)out, E);
+    else if (table_bf16) gather_rows_kernel<bf16, float><<<N, threads, 0, stream>>>((const bf16*)table, ids, (float*)out, E);
+    else if (act_bf16) gather_rows_kernel<float, bf16><<<N, threads, 0, stream>>>((const float*)table, ids, (bf16*)out, E);
+    else gather_rows_kernel<float, float><<<N, threads, 0, stream>>>((const float*)table, ids, (float*)out, E);
+    return tnx_launch_status();
+}

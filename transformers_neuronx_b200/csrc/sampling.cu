@@ -1,0 +1,225 @@
+// Next-token choice from 32-bit logits, one thread block per row.
+//
+//   temperature <= 0 : argmax, the lowest index winning a tie.
+//   temperature  > 0 : s_i = logit_i / temperature (the suppressed id, if any, at -inf);
+//                      top-k: keep the k largest s_i; top-p: of those, keep the most likely tokens
+//                      until their probability reaches top_p (a token is kept when the mass
+//                      before it is < top_p); then draw from softmax over the kept tokens by
+//                      inverse CDF in index order with one Philox uniform per (seed, counter).
+//
+// Everything that decides the outcome is integer arithmetic: the thresholds are found by radix
+// selection on order-preserving integer keys, and probability masses are summed as 2^-40
+// fixed-point integers, so a draw depends on (logits, parameters, seed, counter) alone and not
+// on the order in which threads run.  Tokens tied with the k-th largest are all kept.
+#include "common.cuh"
+
+namespace {
+
+constexpr int THREADS = 1024;
+constexpr double FX_ONE = 1099511627776.0;   // 2^40
+
+__device__ __forceinline__ uint32_t ordered_key(float v) {
+    uint32_t u = __float_as_uint(v);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+__device__ __forceinline__ void philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3,
+                                              uint32_t k0, uint32_t k1, uint32_t out[4]) {
+    const uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u, W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
+#pragma unroll
+    for (int r = 0; r < 10; ++r) {
+        const uint32_t hi0 = __umulhi(M0, c0), lo0 = M0 * c0;
+        const uint32_t hi1 = __umulhi(M1, c2), lo1 = M1 * c2;
+        const uint32_t n0 = hi1 ^ c1 ^ k0, n1 = lo1, n2 = hi0 ^ c3 ^ k1, n3 = lo0;
+        c0 = n0; c1 = n1; c2 = n2; c3 = n3;
+        k0 += W0; k1 += W1;
+    }
+    out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
+}
+
+struct ArgMax { float v; int i; };
+__device__ __forceinline__ ArgMax better(ArgMax a, ArgMax b) {
+    if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
+    return a;
+}
+
+__global__ void __launch_bounds__(THREADS)
+sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __restrict__ temperature,
+              const int* __restrict__ top_k, const float* __restrict__ top_p,
+              const unsigned long long* __restrict__ seeds, const unsigned long long* __restrict__ counters,
+              int suppress_id, int* __restrict__ out) {
+    __shared__ float fscratch[32];
+    __shared__ ArgMax ascratch[32];
+    __shared__ unsigned int chist[256];
+    __shared__ unsigned long long mhist[256];
+    __shared__ unsigned long long sums[THREADS];
+    __shared__ unsigned int sh_prefix, sh_remaining;
+    __shared__ unsigned long long sh_above, sh_total;
+    __shared__ int sh_owner;
+
+    const int r = blockIdx.x, tid = threadIdx.x;
+    const float* row = logits + (size_t)r * ld;
+    const float T = temperature ? temperature[r] : 0.f;
+
+    if (!(T > 0.f)) {
+        ArgMax best{-INFINITY, 0x7fffffff};
+        for (int i = tid; i < V; i += THREADS) best = better(best, ArgMax{row[i], i});
+        for (int o = 16; o > 0; o >>= 1) {
+            ArgMax other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+            best = better(best, other);
+        }
+        if ((tid & 31) == 0) ascratch[tid >> 5] = best;
+        __syncthreads();
+        if (tid < 32) {
+            best = ascratch[tid];
+            for (int o = 16; o > 0; o >>= 1) {
+                ArgMax other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+                best = better(best, other);
+            }
+            if (tid == 0) out[r] = best.i == 0x7fffffff ? 0 : best.i;
+        }
+        return;
+    }
+
+#define SCORE(i) (((i) == suppress_id) ? -INFINITY : row[(i)] / T)
+    float mx = -INFINITY;
+    for (int i = tid; i < V; i += THREADS) mx = fmaxf(mx, SCORE(i));
+    mx = block_max(mx, fscratch);
+
+    // ---- top-k: the key of the k-th largest score (0 keeps everything) ----------------------
+    uint32_t thr = 0;
+    const int k = top_k ? top_k[r] : 0;
+    if (k > 0 && k < V) {
+        if (tid == 0) { sh_prefix = 0; sh_remaining = (unsigned)k; }
+        uint32_t mask = 0;
+        for (int shift = 24; shift >= 0; shift -= 8) {
+            if (tid < 256) chist[tid] = 0;
+            __syncthreads();
+            const uint32_t prefix = sh_prefix;
+            for (int i = tid; i < V; i += THREADS) {
+                const uint32_t key = ordered_key(SCORE(i));
+                if ((key & mask) == prefix) atomicAdd(&chist[(key >> shift) & 255u], 1u);
+            }
+            __syncthreads();
+            if (tid == 0) {
+                unsigned cum = 0, remaining = sh_remaining;
+                int b = 255;
+                for (; b > 0; --b) {
+                    if (cum + chist[b] >= remaining) break;
+                    cum += chist[b];
+                }
+                sh_remaining = remaining - cum;
+                sh_prefix = prefix | ((uint32_t)b << shift);
+            }
+            mask |= 255u << shift;
+            __syncthreads();
+        }
+        thr = sh_prefix;
+    }
+
+    // ---- top-p over the tokens that top-k kept -------------------------------------------------
+    const float P = top_p ? top_p[r] : 1.f;
+    if (P < 1.f) {
+        unsigned long long local = 0;
+        for (int i = tid; i < V; i += THREADS) {
+            const float s = SCORE(i);
+            if (ordered_key(s) >= thr) local += (unsigned long long)((double)expf(s - mx) * FX_ONE);
+        }
+        if (tid == 0) sh_total = 0;
+        __syncthreads();
+        atomicAdd(&sh_total, local);
+        __syncthreads();
+        unsigned long long limit = (unsigned long long)((double)P * (double)sh_total);
+        if (limit < 1) limit = 1;                      // the most likely token is always kept
+        if (tid == 0) { sh_prefix = 0; sh_above = 0; }
+        uint32_t mask = 0;
+        for (int shift = 24; shift >= 0; shift -= 8) {
+            if (tid < 256) mhist[tid] = 0;
+            __syncthreads();
+            const uint32_t prefix = sh_prefix;
+            for (int i = tid; i < V; i += THREADS) {
+                const float s = SCORE(i);
+                const uint32_t key = ordered_key(s);
+                if (key >= thr && (key & mask) == prefix)
+                    atomicAdd(&mhist[(key >> shift) & 255u], (unsigned long long)((double)expf(s - mx) * FX_ONE));
+            }
+            __syncthreads();
+            if (tid == 0) {
+                unsigned long long cum = sh_above, chosen_above = sh_above;
+                int chosen = 255;
+                for (int b = 255; b >= 0; --b) {       // lowest digit whose tokens may still be kept
+                    if (cum < limit || b == 255) { chosen = b; chosen_above = cum; } else break;
+                    cum += mhist[b];
+                }
+                sh_above = chosen_above;
+                sh_prefix = prefix | ((uint32_t)chosen << shift);
+            }
+            mask |= 255u << shift;
+            __syncthreads();
+        }
+        if (sh_prefix > thr) thr = sh_prefix;
+    }
+
+    // ---- inverse CDF in index order over the kept tokens --------------------------------------
+    const int chunk = (V + THREADS - 1) / THREADS;
+    const int lo = tid * chunk, hi = min(V, lo + chunk);
+    unsigned long long local = 0;
+    for (int i = lo; i < hi; ++i) {
+        const float s = SCORE(i);
+        if (ordered_key(s) >= thr) local += (unsigned long long)((double)expf(s - mx) * FX_ONE);
+    }
+    sums[tid] = local;
+    __syncthreads();
+    if (tid < 32) {                                   // exclusive scan of 1024 partial sums
+        unsigned long long run = 0;
+        const int base = tid * 32;
+        for (int j = 0; j < 32; ++j) { unsigned long long v = sums[base + j]; sums[base + j] = run; run += v; }
+        unsigned long long incl = run;
+        for (int o = 1; o < 32; o <<= 1) {
+            unsigned long long nb = __shfl_up_sync(0xffffffffu, incl, o);
+            if (tid >= o) incl += nb;
+        }
+        const unsigned long long excl = incl - run;
+        for (int j = 0; j < 32; ++j) sums[base + j] += excl;
+        if (tid == 31) sh_total = incl;
+    }
+    if (tid == 0) sh_owner = -1;
+    __syncthreads();
+    const unsigned long long total = sh_total;
+    uint32_t rnd[4];
+    const unsigned long long seed = seeds ? seeds[r] : 0ull, ctr = counters ? counters[r] : 0ull;
+    philox4x32_10((uint32_t)ctr, (uint32_t)(ctr >> 32), 0u, 0u, (uint32_t)seed, (uint32_t)(seed >> 32), rnd);
+    // target = floor(total * u), u = rnd / 2^32 in [0, 1)
+    const unsigned long long target = __umul64hi(total, (unsigned long long)rnd[0] << 32);
+    const unsigned long long mine = sums[tid];
+    if (local > 0 && target >= mine && target < mine + local) {
+        unsigned long long run = mine;
+        int pick = lo;
+        for (int i = lo; i < hi; ++i) {
+            const float s = SCORE(i);
+            if (ordered_key(s) >= thr) {
+                run += (unsigned long long)((double)expf(s - mx) * FX_ONE);
+                pick = i;
+                if (run > target) break;
+            }
+        }
+        out[r] = pick;
+        sh_owner = tid;
+    }
+    __syncthreads();
+    if (tid == 0 && sh_owner < 0) {                   // total == 0: every score was -inf or NaN
+        out[r] = 0;
+    }
+#undef SCORE
+}
+}  // namespace
+
+TNX_EXPORT int tnx_sample(const float* logits, int ld, int n_rows, int V, const float* temperature,
+                          const int* top_k, const float* top_p, const unsigned long long* seeds,
+                          const unsigned long long* counters, int suppress_id, int* out, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (V <= 0 || ld < V) return TNX_ERR_BAD_ARG;
+    sample_kernel<<<n_rows, THREADS, 0, stream>>>(logits, ld, V, temperature, top_k, top_p, seeds, counters,
+                                                  suppress_id, out);
+    return tnx_launch_status();
+}

@@ -1,0 +1,49 @@
+"""From a model folder (config.json, model.safetensors) to a model on the GPU."""
+from __future__ import annotations
+
+import sys
+import time
+
+import torch
+
+from ..config import canonical_dtype, load_config
+from ..kernels import build as kbuild
+from ..models.decoder import DecoderModel
+from ..weights import load_tensors
+
+_TORCH_DTYPE = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def require_cuda(device="cuda:0") -> torch.device:
+    if not torch.cuda.is_available():
+        raise RuntimeError("no CUDA device: this engine runs on a GPU only (sm_100a); there is no CPU path")
+    dev = torch.device(device)
+    major, minor = torch.cuda.get_device_capability(dev)
+    if major != 10:
+        raise RuntimeError(f"the kernels are built for sm_100a (B200); device {dev} is sm_{major}{minor}")
+    return dev
+
+
+def build_model(spec, tensors, dtype: str, device="cuda:0", verbose=True) -> DecoderModel:
+    """A ModelSpec and its {name: tensor} -> a DecoderModel on the device, kernels compiled."""
+    dev = require_cuda(device)
+    torch.cuda.set_device(dev)
+    model = DecoderModel(spec)
+    kbuild.build_many(model.libraries(), verbose=verbose)
+    model.load(tensors, dev, _TORCH_DTYPE[canonical_dtype(dtype)])
+    return model
+
+
+def load_model(folder: str, dtype: str = "bfloat16", device="cuda:0", verbose=True):
+    """Returns (model, typed config).  The model class is chosen by config.json."""
+    arch, cfg = load_config(folder)
+    spec = arch.build_spec(cfg)
+    probe = DecoderModel(spec)                       # host-only: lists the tensors the model reads
+    t0 = time.time()
+    tensors = load_tensors(folder, probe.tensor_specs())
+    model = build_model(spec, tensors, dtype, device, verbose)
+    if verbose:
+        print(f"[tnx-b200] {arch.name} loaded from {folder} as {canonical_dtype(dtype)} in "
+              f"{time.time() - t0:.1f} s ({model.parameter_bytes() / 1e9:.2f} GB of weights)",
+              file=sys.stderr, flush=True)
+    return model, cfg

@@ -1,0 +1,3 @@
+from . import build, ops
+from .build import KernelBuildError, build_all, build_many
+from .ops import KernelError

@@ -1,0 +1,155 @@
+"""Builds the CUDA sources of csrc/ into shared libraries and loads them with ctypes.
+
+Each .cu file becomes one library with plain C entry points, compiled for sm_100a by nvcc when it
+is first needed (a model builds what its parts need, nothing else) and kept under csrc/_build/,
+named by a hash of the source, the headers and the flags.  When that folder cannot be written,
+a per-user folder under the system's temporary directory is used.  There is no fallback: a
+library that cannot be built or loaded raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from concurrent.futures import ThreadPoolExecutor
+from typing import Dict, Iterable, List, Optional
+
+CSRC = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "csrc")
+CSRC = os.path.normpath(CSRC)
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
+]
+
+# library name -> source file (relative to csrc/)
+SOURCES: Dict[str, str] = {
+    "embedding": "embedding.cu",
+    "layernorm": "layernorm.cu",
+    "gemm_simt": "gemm_simt.cu",
+    "kv_cache": "kv_cache.cu",
+    "attention_simt": "attention_simt.cu",
+    "sampling": "sampling.cu",
+}
+
+_loaded: Dict[str, ctypes.CDLL] = {}
+_lock = threading.Lock()
+_build_locks: Dict[str, threading.Lock] = {}
+
+
+class KernelBuildError(RuntimeError):
+    pass
+
+
+def register_source(name: str, filename: str) -> None:
+    SOURCES[name] = filename
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.isfile(cand):
+            return cand
+    raise KernelBuildError("nvcc not found: the engine's kernels are compiled from source at first use")
+
+
+def _headers() -> List[str]:
+    return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h")))
+
+
+def _digest(src: str) -> str:
+    h = hashlib.sha256()
+    h.update(" ".join(NVCC_FLAGS).encode())
+    for p in [src] + _headers():
+        with open(p, "rb") as fp:
+            h.update(fp.read())
+    return h.hexdigest()[:16]
+
+
+def _build_dir() -> str:
+    first = os.path.join(CSRC, "_build")
+    try:
+        os.makedirs(first, exist_ok=True)
+        probe = os.path.join(first, f".w{os.getpid()}")
+        with open(probe, "w"):
+            pass
+        os.remove(probe)
+        return first
+    except OSError:
+        alt = os.path.join(tempfile.gettempdir(), f"tnx_b200_build_{os.getuid()}")
+        os.makedirs(alt, exist_ok=True)
+        return alt
+
+
+def library_path(name: str) -> str:
+    src = os.path.join(CSRC, SOURCES[name])
+    return os.path.join(_build_dir(), f"{name}.{_digest(src)}.so")
+
+
+def _say(msg: str) -> None:
+    print(f"[tnx-b200 build] {msg}", file=sys.stderr, flush=True)
+
+
+def build(name: str, verbose: bool = True) -> str:
+    """Compiles one library if its up-to-date binary is not there yet; returns its path."""
+    if name not in SOURCES:
+        raise KernelBuildError(f"no kernel source registered under {name!r}")
+    with _lock:
+        lk = _build_locks.setdefault(name, threading.Lock())
+    with lk:
+        src = os.path.join(CSRC, SOURCES[name])
+        out = library_path(name)
+        if os.path.isfile(out):
+            return out
+        tmp = f"{out}.{os.getpid()}.{threading.get_ident()}.tmp"
+        cmd = [_nvcc()] + NVCC_FLAGS + ["-I", CSRC, "-o", tmp, src]
+        if verbose:
+            _say(f"compiling {SOURCES[name]} for sm_100a ...")
+        t0 = time.time()
+        proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+        while True:                      # a line now and then while a long compile runs
+            try:
+                log, _ = proc.communicate(timeout=20)
+                break
+            except subprocess.TimeoutExpired:
+                if verbose:
+                    _say(f"  still compiling {SOURCES[name]} ({time.time() - t0:.0f} s)")
+        if proc.returncode != 0:
+            if os.path.exists(tmp):
+                os.remove(tmp)
+            raise KernelBuildError(f"nvcc failed on {src}:\n{log}")
+        os.replace(tmp, out)
+        if verbose:
+            _say(f"built {os.path.basename(out)} in {time.time() - t0:.1f} s")
+        return out
+
+
+def build_many(names: Iterable[str], verbose: bool = True) -> None:
+    names = [n for n in dict.fromkeys(names) if n not in _loaded]
+    todo = [n for n in names if not os.path.isfile(library_path(n))]
+    if not todo:
+        return
+    with ThreadPoolExecutor(max_workers=min(len(todo), os.cpu_count() or 4)) as ex:
+        list(ex.map(lambda n: build(n, verbose), todo))
+
+
+def build_all(verbose: bool = True) -> None:
+    build_many(list(SOURCES), verbose)
+
+
+def load(name: str) -> ctypes.CDLL:
+    lib = _loaded.get(name)
+    if lib is not None:
+        return lib
+    path = build(name)
+    try:
+        lib = ctypes.CDLL(path)
+    except OSError as e:
+        raise KernelBuildError(f"cannot load {path}: {e}") from e
+    _loaded[name] = lib
+    return lib

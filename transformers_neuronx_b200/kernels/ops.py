@@ -1,0 +1,243 @@
+"""Python faces of the CUDA entry points: they check devices, types, shapes and strides, then pass
+raw pointers and the current CUDA stream.  Nothing here computes; there is no fallback: on a tensor
+that is not on a CUDA device every function raises."""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+from typing import Optional
+
+import torch
+
+from . import build as _build
+
+_ERRORS = {-1: "bad argument", -2: "unsupported size", -3: "a bounded wait inside the kernel ran out"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code < 0:
+        raise KernelError(f"{what}: {_ERRORS.get(code, 'error')} (code {code})")
+    raise KernelError(f"{what}: CUDA error {code} at launch")
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _p(t: Optional[torch.Tensor]) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _need(t: torch.Tensor, name: str, dtype=None, ndim=None, contiguous=True) -> None:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor: the engine has no CPU path")
+    if dtype is not None:
+        ok = t.dtype in dtype if isinstance(dtype, (tuple, list)) else t.dtype == dtype
+        if not ok:
+            raise KernelError(f"{name} has dtype {t.dtype}, expected {dtype}")
+    if ndim is not None and t.dim() != ndim:
+        raise KernelError(f"{name} has {t.dim()} dimensions, expected {ndim}")
+    if contiguous and not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+
+
+_FLOATS = (torch.float32, torch.bfloat16)
+
+
+def _is_bf16(t: torch.Tensor) -> int:
+    return 1 if t.dtype == torch.bfloat16 else 0
+
+
+def _rows_2d(t: torch.Tensor, name: str):
+    """A 2-D tensor whose rows are contiguous (a column slice of a wider buffer is allowed)."""
+    if t.dim() != 2 or (t.shape[1] > 1 and t.stride(1) != 1):
+        raise KernelError(f"{name} must be 2-D with contiguous rows")
+    return t.shape[0], t.shape[1], t.stride(0)
+
+
+# ---------------------------------------------------------------------------------------------
+def embed(tok_table, pre, ids, pos_table, positions, pos_offset, out_f32, out_act):
+    """out[n] = (tok_table[ids[n]] or pre[n]) + pos_table[positions[n] + pos_offset]."""
+    lib = _build.load("embedding")
+    N = ids.shape[0]
+    _need(ids, "ids", torch.int32, 1)
+    ref = out_f32 if out_f32 is not None else out_act
+    H = ref.shape[1]
+    table_bf16 = 0
+    if tok_table is not None:
+        _need(tok_table, "tok_table", _FLOATS, 2)
+        if tok_table.shape[1] != H:
+            raise KernelError("tok_table width differs from the output width")
+        table_bf16 = _is_bf16(tok_table)
+    else:
+        _need(pre, "pre", torch.float32, 2)
+    if pos_table is not None:
+        _need(pos_table, "pos_table", _FLOATS, 2)
+        _need(positions, "positions", torch.int32, 1)
+        if tok_table is not None and pos_table.dtype != tok_table.dtype:
+            raise KernelError("token and position tables must have one dtype")
+        table_bf16 = _is_bf16(pos_table)
+        if pos_table.shape[1] != H:
+            raise KernelError("pos_table width differs from the output width")
+    if out_f32 is not None:
+        _need(out_f32, "out_f32", torch.float32, 2)
+    act_bf16 = 0
+    if out_act is not None:
+        _need(out_act, "out_act", _FLOATS, 2)
+        act_bf16 = _is_bf16(out_act)
+    _check(lib.tnx_embed(_p(tok_table), _p(pre), _p(ids), _p(pos_table), _p(positions), c_int(pos_offset),
+                         _p(out_f32), _p(out_act), c_int(N), c_int(H), c_int(table_bf16), c_int(act_bf16),
+                         _stream()), "embed")
+
+
+def gather_rows(table, ids, out):
+    lib = _build.load("embedding")
+    _need(table, "table", _FLOATS, 2)
+    _need(ids, "ids", torch.int32, 1)
+    _need(out, "out", _FLOATS, 2)
+    _check(lib.tnx_gather_rows(_p(table), _p(ids), _p(out), c_int(ids.shape[0]), c_int(table.shape[1]),
+                               c_int(_is_bf16(table)), c_int(_is_bf16(out)), _stream()), "gather_rows")
+
+
+def layer_norm(x, gamma, beta, eps, out_f32=None, out_act=None, rows=None):
+    """Rows of the 32-bit x normalised; `rows` (int32) picks input rows."""
+    lib = _build.load("layernorm")
+    _need(x, "x", torch.float32, 2)
+    H = x.shape[1]
+    n_rows = rows.shape[0] if rows is not None else x.shape[0]
+    if rows is not None:
+        _need(rows, "rows", torch.int32, 1)
+    for t, nm in ((gamma, "gamma"), (beta, "beta")):
+        if t is not None:
+            _need(t, nm, torch.float32, 1)
+            if t.shape[0] != H:
+                raise KernelError(f"{nm} has {t.shape[0]} elements, the rows have {H}")
+    act_bf16 = 0
+    for t, nm in ((out_f32, "out_f32"), (out_act, "out_act")):
+        if t is not None:
+            _need(t, nm, torch.float32 if nm == "out_f32" else _FLOATS, 2)
+            if t.shape[0] < n_rows or t.shape[1] != H:
+                raise KernelError(f"{nm} has shape {tuple(t.shape)}, needs [{n_rows}, {H}]")
+    if out_act is not None:
+        act_bf16 = _is_bf16(out_act)
+    _check(lib.tnx_layer_norm(_p(x), _p(rows), _p(gamma), _p(beta), c_float(eps), _p(out_f32), _p(out_act),
+                              c_int(n_rows), c_int(H), c_int(act_bf16), _stream()), "layer_norm")
+
+
+def pick_rows(x, rows, out_f32=None, out_act=None):
+    lib = _build.load("layernorm")
+    _need(x, "x", torch.float32, 2)
+    n_rows = rows.shape[0] if rows is not None else x.shape[0]
+    act_bf16 = _is_bf16(out_act) if out_act is not None else 0
+    _check(lib.tnx_pick_rows(_p(x), _p(rows), _p(out_f32), _p(out_act), c_int(n_rows), c_int(x.shape[1]),
+                             c_int(act_bf16), _stream()), "pick_rows")
+
+
+def gemm_simt(a, w, out, bias=None, residual=None, relu=False):
+    """out = epilogue(a @ w^T) on CUDA cores with 32-bit FMA; a [M, K], w [N, K], out [M, N]."""
+    lib = _build.load("gemm_simt")
+    _need(a, "a", _FLOATS, None, contiguous=False)
+    _need(w, "w", _FLOATS, None, contiguous=False)
+    _need(out, "out", _FLOATS, None, contiguous=False)
+    M, K, lda = _rows_2d(a, "a")
+    N, Kw, ldw = _rows_2d(w, "w")
+    Mo, No, ldc = _rows_2d(out, "out")
+    if Kw != K or Mo != M or No != N:
+        raise KernelError(f"gemm shapes do not fit: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if bias is not None:
+        _need(bias, "bias", torch.float32, 1)
+        if bias.shape[0] != N:
+            raise KernelError("bias length differs from the output width")
+    if residual is not None:
+        _need(residual, "residual", torch.float32, None, contiguous=False)
+        if tuple(residual.shape) != (M, N) or _rows_2d(residual, "residual")[2] != ldc or out.dtype != torch.float32:
+            raise KernelError("residual must be float32 with the shape and row stride of a float32 out")
+    _check(lib.tnx_gemm_simt(_p(a), _p(w), _p(bias), _p(residual), _p(out), c_int(M), c_int(N), c_int(K),
+                             c_int(lda), c_int(ldw), c_int(ldc), c_int(1 if relu else 0), c_int(_is_bf16(a)),
+                             c_int(_is_bf16(w)), c_int(_is_bf16(out)), _stream()), "gemm_simt")
+
+
+def kv_append(k_src, v_src, slot_mapping, cache, page_size):
+    """k_src, v_src: [N, n_kv_heads * head_dim] views (rows contiguous, one row stride);
+    cache: [pages, 2, n_kv_heads, page_size, head_dim]."""
+    lib = _build.load("kv_cache")
+    _need(cache, "cache", _FLOATS, 5)
+    _need(slot_mapping, "slot_mapping", torch.int32, 1)
+    N, width, stride = _rows_2d(k_src, "k_src")
+    if _rows_2d(v_src, "v_src") != (N, width, stride) or k_src.dtype != cache.dtype or v_src.dtype != cache.dtype:
+        raise KernelError("k_src and v_src must agree in shape, stride and dtype with the cache")
+    _, two, n_kv, ps, d = cache.shape
+    if two != 2 or ps != page_size or n_kv * d != width:
+        raise KernelError(f"cache shape {tuple(cache.shape)} does not fit rows of width {width}")
+    _check(lib.tnx_kv_append(_p(k_src), _p(v_src), c_int(stride), _p(slot_mapping), _p(cache), c_int(N),
+                             c_int(n_kv), c_int(d), c_int(ps), c_int(_is_bf16(cache)), _stream()), "kv_append")
+
+
+def attention_simt(q, cache, block_tables, token_request, positions, out, n_heads, scale, window=0):
+    """q: [N, n_heads * head_dim] view; out likewise; cache as in kv_append."""
+    lib = _build.load("attention_simt")
+    _need(cache, "cache", _FLOATS, 5)
+    N, width, q_stride = _rows_2d(q, "q")
+    No, wo, out_stride = _rows_2d(out, "out")
+    _, _, n_kv, ps, d = cache.shape
+    if width != n_heads * d or (No, wo) != (N, width) or q.dtype != cache.dtype or out.dtype != cache.dtype:
+        raise KernelError("q/out do not fit the cache's head size or dtype")
+    _need(block_tables, "block_tables", torch.int32, 2)
+    _need(token_request, "token_request", torch.int32, 1)
+    _need(positions, "positions", torch.int32, 1)
+    _check(lib.tnx_attention_simt(_p(q), c_int(q_stride), _p(cache), _p(block_tables), c_int(block_tables.stride(0)),
+                                  _p(token_request), _p(positions), _p(out), c_int(out_stride), c_int(N),
+                                  c_int(n_heads), c_int(n_kv), c_int(d), c_int(ps), c_int(window or 0),
+                                  c_float(scale), c_int(_is_bf16(cache)), _stream()), "attention_simt")
+
+
+def sample(logits, out, temperature=None, top_k=None, top_p=None, seeds=None, counters=None, suppress_id=-1):
+    """out[r] = next token of row r; per-row float32 temperature (<= 0: greedy), int32 top_k
+    (0: off), float32 top_p (1: off), int64 seeds and counters for the Philox draw."""
+    lib = _build.load("sampling")
+    _need(logits, "logits", torch.float32, None, contiguous=False)
+    R, V, ld = _rows_2d(logits, "logits")
+    _need(out, "out", torch.int32, 1)
+    for t, nm, dt in ((temperature, "temperature", torch.float32), (top_k, "top_k", torch.int32),
+                      (top_p, "top_p", torch.float32), (seeds, "seeds", torch.int64),
+                      (counters, "counters", torch.int64)):
+        if t is not None:
+            _need(t, nm, dt, 1)
+            if t.shape[0] < R:
+                raise KernelError(f"{nm} has fewer entries than there are rows")
+    _check(lib.tnx_sample(_p(logits), c_int(ld), c_int(R), c_int(V), _p(temperature), _p(top_k), _p(top_p),
+                          _p(seeds), _p(counters), c_int(suppress_id), _p(out), _stream()), "sample")
+
+
+# ---------------------------------------------------------------------------------------------
+# Tensor-core kernels (bfloat16).  Registered by their own modules when they are built.
+_gemm_tc_impl = None
+_attention_impls = {}
+
+
+def has_gemm_tc() -> bool:
+    return _gemm_tc_impl is not None
+
+
+def gemm_tc(a, w, out, bias=None, residual=None, relu=False):
+    if _gemm_tc_impl is None:
+        raise KernelError("the tensor-core matrix product is not available")
+    _gemm_tc_impl(a, w, out, bias, residual, relu)
+
+
+def attention(ctx, group, q, cache, out, n_heads, scale, window=0):
+    """Attention of this step's queries over the cache of the running schedule entry.  32-bit
+    caches, and head sizes or windows that the bfloat16 kernels do not take, run on the CUDA-core
+    kernel; bfloat16 runs the prefill kernel for requests with several rows and the split
+    decode kernel for requests with one."""
+    impl = _attention_impls.get("bf16") if cache.dtype == torch.bfloat16 else None
+    if impl is not None and impl(ctx, group, q, cache, out, n_heads, scale, window):
+        return
+    attention_simt(q, cache, ctx.block_tables[group], ctx.token_request, ctx.positions, out, n_heads, scale,
+                   window)

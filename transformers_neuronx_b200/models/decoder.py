@@ -1,0 +1,103 @@
+"""A decoder put together from parts according to a ModelSpec: embedding, the scheduled layers,
+head.  It knows no architecture: models/opt.py (or a test) supplies the specification."""
+from __future__ import annotations
+
+from typing import Dict, List
+
+import torch
+
+from ..kernels import build as kbuild
+from ..kernels import ops
+from ..parts import Embedding, Head, build_block, build_part
+from ..parts.spec import ModelSpec
+from ..weights.loader import TensorSpec
+
+
+class DecoderModel:
+    def __init__(self, spec: ModelSpec):
+        self.spec = spec
+        self.embedding = Embedding(spec.embedding)
+        self.blocks = []
+        for ls in spec.layers:
+            self.blocks.append(build_block(ls.block, build_part("norm", ls.norm1), build_part("mixer", ls.mixer),
+                                           build_part("norm", ls.norm2),
+                                           build_part("feed_forward", ls.feed_forward)))
+        self.head = Head(spec.head)
+        for e in spec.schedule:
+            if not (0 <= e.layer < len(self.blocks)):
+                raise ValueError(f"schedule names layer {e.layer}, the model has {len(self.blocks)}")
+        self.device = None
+        self.act_dtype = None
+
+    # ---- parts, tensors, kernels --------------------------------------------------------------
+    def all_parts(self):
+        out = [self.embedding]
+        for b in self.blocks:
+            out += b.parts()
+        out.append(self.head)
+        return out
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        seen, out = set(), []
+        for p in self.all_parts():
+            for s in p.tensor_specs():
+                if s.name not in seen:
+                    seen.add(s.name)
+                    out.append(s)
+        return out
+
+    def libraries(self) -> List[str]:
+        libs = []
+        for p in self.all_parts():
+            libs += [l for l in p.libraries if l in kbuild.SOURCES]
+        return list(dict.fromkeys(libs))
+
+    def cache_needs(self) -> Dict[int, object]:
+        """{cache id -> what the mixer(s) using it keep}; entries sharing a cache must agree."""
+        needs: Dict[int, object] = {}
+        for e in self.spec.schedule:
+            need = self.blocks[e.layer].mixer.cache_need()
+            if e.cache in needs and needs[e.cache] != need:
+                raise ValueError(f"cache {e.cache} is shared by mixers with different needs: "
+                                 f"{needs[e.cache]} and {need}")
+            needs[e.cache] = need
+        return needs
+
+    def load(self, tensors: Dict[str, torch.Tensor], device, act_dtype) -> None:
+        self.device, self.act_dtype = device, act_dtype
+        self.embedding.load(tensors, device, act_dtype)
+        for b in self.blocks:
+            for p in b.parts():
+                p.load(tensors, device, act_dtype)
+        self.head.load(tensors, device, act_dtype, shared={self.spec.embedding.table: self.embedding.table})
+
+    def parameter_bytes(self) -> int:
+        """Bytes of every weight one step reads once (a tied table counted once)."""
+        n, seen = 0, set()
+        for p in self.all_parts():
+            n += p.parameter_bytes()
+        if self.head.weight is self.embedding.table:
+            n -= self.head.weight.numel() * self.head.weight.element_size()
+        return n
+
+    # ---- one step -------------------------------------------------------------------------------
+    def forward(self, ctx) -> torch.Tensor:
+        """Runs the tokens of ctx through the scheduled layers; returns 32-bit logits of ctx.logit_rows
+        ([0, vocab] when none is wanted)."""
+        N, H = ctx.n_tokens, self.spec.hidden_size
+        x = ctx.empty(N, H, torch.float32)
+        first = self.blocks[self.spec.schedule[0].layer] if self.spec.schedule else None
+        want_act = any(self.blocks[e.layer].needs_act_input for e in self.spec.schedule)
+        x_act = ctx.empty(N, H) if want_act else None
+        self.embedding.forward(ctx, x, x_act if (first is not None and first.needs_act_input) else None)
+        act_current = first is not None and first.needs_act_input
+        for e in self.spec.schedule:
+            block = self.blocks[e.layer]
+            if block.needs_act_input and not act_current:
+                ops.pick_rows(x, None, out_act=x_act)
+            ctx.cache_id = e.cache
+            block.forward(ctx, x, x_act)
+            act_current = block.keeps_act_current
+        if ctx.logit_rows is None or ctx.logit_rows.shape[0] == 0:
+            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=ctx.device)
+        return self.head.forward(ctx, x, ctx.logit_rows)

@@ -1,0 +1,110 @@
+"""Interfaces of the parts a decoder is put together from, and what a part sees of a step.
+
+Hidden state travels between parts as two tensors of shape [tokens, hidden]: the 32-bit residual
+stream, and (where a part reads its input un-normalised) a copy in the activation type.
+
+    Norm.forward(ctx, x, out_f32=None, out_act=None, rows=None)
+    Mixer.forward(ctx, h, residual)          residual += mix(h), using and updating its cache
+    FeedForward.forward(ctx, h, residual)    residual += ff(h)
+    PositionEncoding.table_for_embedding()   a (table, offset) added where tokens are embedded, or None
+    PositionEncoding.embed(ctx, x)           any other change of the hidden state at that place
+    PositionEncoding.rotate(ctx, q, k)       a change of queries and keys inside a mixer
+    Block.forward(ctx, x, x_act)             one layer: its norms, mixer and feed-forward in its order
+
+Every part lists the tensors it reads (``tensor_specs``), takes them in ``load`` and names the
+kernel libraries it needs (``libraries``), so that a model compiles only what it uses.  A mixer
+says what it keeps between steps with ``cache_need`` (cache/manager.py): paged keys and values,
+state of fixed size per request, or nothing.  No part knows which model it is in.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..weights.loader import TensorSpec
+
+
+class StepContext:
+    """The running step, as parts see it.  All index tensors are int32 on the device."""
+
+    def __init__(self, device, act_dtype):
+        self.device = device
+        self.act_dtype = act_dtype            # torch.bfloat16 or torch.float32
+        self.n_tokens = 0
+        self.n_requests = 0
+        self.token_ids = None                 # [N]
+        self.positions = None                 # [N] position of each token in its request
+        self.token_request = None             # [N] index of the token's request in this batch
+        self.q_start = None                   # [R] first row of each request
+        self.q_len = None                     # [R] rows of each request
+        self.ctx_len = None                   # [R] tokens the request had in the cache before this step
+        self.logit_rows = None                # [W] rows whose logits are wanted
+        self.state_slots = None               # [R] slot of each request (state of fixed size)
+        self.block_tables: List[torch.Tensor] = []   # per paged group: [R, blocks]
+        self.slot_mapping: List[torch.Tensor] = []   # per paged group: [N] page * page_size + row
+        self.host = None                      # the same numbers as Python lists (engine/step.py: HostBatch)
+        self.storage = None                   # cache/storage.py: CacheStorage
+        self.cache_id = -1                    # set by the model before each mixer runs
+        self.page_size = 0
+        self.decode_only = False              # every request has exactly one row
+        self.max_ctx = 0                      # longest context (after this step) in the batch
+
+    def empty(self, rows, cols, dtype=None) -> torch.Tensor:
+        return torch.empty((rows, cols), dtype=dtype or self.act_dtype, device=self.device)
+
+    # what the mixer of the running schedule entry owns
+    def cache(self) -> torch.Tensor:
+        return self.storage.tensor(self.cache_id)
+
+    def cache_group(self) -> int:
+        return self.storage.group_of(self.cache_id)
+
+
+class Part:
+    libraries: Sequence[str] = ()
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        return []
+
+    def load(self, tensors: Dict[str, torch.Tensor], device, act_dtype) -> None:
+        pass
+
+    def parameter_bytes(self) -> int:
+        return 0
+
+
+class Norm(Part):
+    def forward(self, ctx, x, out_f32=None, out_act=None, rows=None):
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    def cache_need(self):
+        return None
+
+    def forward(self, ctx, h, residual):
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, ctx, h, residual):
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def table_for_embedding(self):
+        return None
+
+    def embed(self, ctx, x):
+        return None
+
+    def rotate(self, ctx, q, k):
+        return None
+
+
+def to_device(t: torch.Tensor, device, dtype=None) -> torch.Tensor:
+    """Host tensor (possibly a view of a memory-mapped file) -> device, optionally converted."""
+    if dtype is not None and t.dtype != dtype:
+        t = t.to(dtype)
+    return t.contiguous().to(device, non_blocking=False)
