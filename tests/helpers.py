@@ -44,7 +44,7 @@ class TinyModel:
         self.folder = self._tmp.name
         specs = DecoderModel(opt_arch.build_spec(self.cfg)).tensor_specs()
         write_model_folder(self.folder, self.cfg, specs, seed)
-        self.tensors = {k: v.clone() for k, v in load_tensors(self.folder, specs).items()}
+        self.tensors = load_tensors(self.folder, specs)
         self._plain_cache = {}
 
     def plain_logits(self, ids) -> torch.Tensor:

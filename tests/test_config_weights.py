@@ -1,0 +1,148 @@
+"""Configuration, registry and weight loading (no GPU)."""
+import json
+import os
+
+import pytest
+import torch
+
+from helpers import CONFIG_A, CONFIG_B, TinyModel
+from transformers_neuronx_b200.config import (ConfigError, EngineConfig, OPTConfig, canonical_dtype, load_config,
+                                              resolve_architecture)
+from transformers_neuronx_b200.models import opt as opt_arch
+from transformers_neuronx_b200.models.decoder import DecoderModel
+from transformers_neuronx_b200.weights import (TensorSpec, WeightError, load_tensors, match_tensors,
+                                               random_tensors, save_safetensors, SafetensorsFile)
+
+
+def test_config_reads_its_keys():
+    cfg = OPTConfig.from_dict(dict(CONFIG_B, some_unknown_key=3))
+    assert (cfg.hidden_size, cfg.num_attention_heads, cfg.head_dim) == (96, 3, 32)
+    assert cfg.word_embed_proj_dim == 48 and cfg.has_projection
+    assert not cfg.do_layer_norm_before and not cfg.has_final_layer_norm
+    assert cfg.layer_norm_eps == 1e-6 and not cfg.enable_bias
+    a = OPTConfig.from_dict({k: v for k, v in CONFIG_A.items() if k != "word_embed_proj_dim"})
+    assert a.word_embed_proj_dim == a.hidden_size and not a.has_projection and a.has_final_layer_norm
+
+
+def test_config_errors():
+    with pytest.raises(ConfigError, match="ffn_dim"):
+        OPTConfig.from_dict({k: v for k, v in CONFIG_A.items() if k != "ffn_dim"})
+    with pytest.raises(ConfigError, match="multiple"):
+        OPTConfig.from_dict(dict(CONFIG_A, num_attention_heads=5))
+    with pytest.raises(ConfigError):
+        OPTConfig.from_dict(dict(CONFIG_A, vocab_size=-1))
+
+
+def test_registry():
+    assert resolve_architecture({"architectures": ["OPTForCausalLM"]}).name == "OPTForCausalLM"
+    assert resolve_architecture({"model_type": "opt"}).name == "OPTForCausalLM"
+    with pytest.raises(KeyError, match="OPTForCausalLM"):
+        resolve_architecture({"architectures": ["LlamaForCausalLM"], "model_type": "llama"})
+
+
+def test_dtype_names():
+    assert canonical_dtype("f32") == "float32" and canonical_dtype("bf16") == "bfloat16"
+    assert canonical_dtype(torch.bfloat16) == "bfloat16"
+    with pytest.raises(ValueError, match="bfloat16"):
+        canonical_dtype("f16")
+    with pytest.raises(ValueError):
+        EngineConfig(page_size=24)
+
+
+def test_spec_follows_config():
+    for c in (CONFIG_A, CONFIG_B):
+        cfg = OPTConfig.from_dict(c)
+        spec = opt_arch.build_spec(cfg)
+        assert len(spec.layers) == cfg.num_hidden_layers == len(spec.schedule)
+        l0 = spec.layers[0]
+        assert l0.block == ("pre_norm" if cfg.do_layer_norm_before else "post_norm")
+        assert l0.mixer.n_heads == cfg.num_attention_heads and l0.mixer.head_dim == cfg.head_dim
+        assert l0.norm1.eps == cfg.layer_norm_eps
+        assert (l0.mixer.q.bias is not None) == cfg.enable_bias
+        assert (l0.norm1.weight is not None) == cfg.layer_norm_elementwise_affine
+        assert (spec.embedding.project_in is not None) == cfg.has_projection
+        assert (spec.head.final_norm is not None) == cfg.has_final_layer_norm
+        assert spec.embedding.position.rows == cfg.max_position_embeddings + 2
+        names = [s.name for s in DecoderModel(spec).tensor_specs()]
+        assert len(names) == len(set(names))
+        assert ("model.decoder.project_in.weight" in names) == cfg.has_projection
+
+
+def test_random_weights_are_seeded_and_roundtrip(tmp_path):
+    m1, m2, m3 = TinyModel("A", seed=5), TinyModel("A", seed=5), TinyModel("A", seed=6)
+    k = "model.decoder.layers.1.fc1.weight"
+    assert torch.equal(m1.tensors[k], m2.tensors[k]) and not torch.equal(m1.tensors[k], m3.tensors[k])
+    assert m1.tensors[k].dtype == torch.bfloat16
+    assert m1.tensors["model.decoder.layers.0.final_layer_norm.weight"].dtype == torch.float32   # stays 32-bit
+    assert m1.tensors["lm_head.weight"] is m1.tensors["model.decoder.embed_tokens.weight"]        # tied
+    arch, cfg = load_config(m1.folder)
+    assert arch.name == "OPTForCausalLM" and cfg == m1.cfg
+    assert sorted(os.listdir(m1.folder)) == ["config.json", "model.safetensors"]
+
+
+def _specs():
+    return [TensorSpec("model.a.weight", (4, 3)), TensorSpec("model.a.bias", (4,), "bias"),
+            TensorSpec("head.weight", (4, 3), tied_to="model.a.weight")]
+
+
+def test_one_error_lists_everything():
+    avail = {"model.a.weight": (torch.bfloat16, (4, 5)), "stray": (torch.float32, (1,)),
+             "other.stray": (torch.float32, (2,))}
+    with pytest.raises(WeightError) as ei:
+        match_tensors(_specs() + [TensorSpec("model.b.weight", (2, 2))], avail, "mem")
+    e = ei.value
+    assert set(e.missing) == {"model.a.bias", "model.b.weight"}
+    assert set(e.unexpected) == {"stray", "other.stray"}
+    assert [w[0] for w in e.wrong_shape][:1] == ["model.a.weight"]
+    msg = str(e)
+    for word in ("missing", "unexpected", "wrong shape", "model.b.weight", "stray", "[4, 5]"):
+        assert word in msg
+
+
+def test_prefix_and_tie(tmp_path):
+    # a checkpoint of the bare decoder lacks 'model.'; the tied head is absent
+    t = {"a.weight": torch.randn(4, 3).bfloat16(), "a.bias": torch.randn(4).half()}
+    save_safetensors(t, str(tmp_path / "model.safetensors"))
+    (tmp_path / "config.json").write_text("{}")
+    out = load_tensors(str(tmp_path), _specs())
+    assert out["head.weight"] is out["model.a.weight"]
+    assert out["model.a.bias"].dtype == torch.bfloat16           # float16 becomes bfloat16
+    # a stored head that differs from the table it is tied to is an error
+    t["head.weight"] = torch.randn(4, 3).bfloat16()
+    save_safetensors(t, str(tmp_path / "model.safetensors"))
+    with pytest.raises(WeightError, match="tied"):
+        load_tensors(str(tmp_path), _specs())
+    t["head.weight"] = t["a.weight"].clone()
+    save_safetensors(t, str(tmp_path / "model.safetensors"))
+    assert torch.equal(load_tensors(str(tmp_path), _specs())["head.weight"], t["a.weight"])
+
+
+def test_dtypes_kept(tmp_path):
+    t = {"w32": torch.randn(3, 3), "wb": torch.randn(3, 3).bfloat16(), "i64": torch.arange(4), "i32": torch.arange(4, dtype=torch.int32)}
+    save_safetensors(t, str(tmp_path / "model.safetensors"))
+    specs = [TensorSpec("w32", (3, 3)), TensorSpec("wb", (3, 3)), TensorSpec("i64", (4,), "int_table"), TensorSpec("i32", (4,), "int_table")]
+    out = load_tensors(str(tmp_path), specs)
+    assert out["w32"].dtype == torch.float32 and torch.equal(out["w32"], t["w32"])
+    assert out["wb"].dtype == torch.bfloat16
+    assert out["i64"].dtype == torch.int32 and out["i32"].dtype == torch.int32
+
+
+def test_missing_files(tmp_path):
+    with pytest.raises(FileNotFoundError, match="safetensors"):
+        load_tensors(str(tmp_path), _specs())
+    with pytest.raises(FileNotFoundError, match="config.json"):
+        load_config(str(tmp_path))
+    (tmp_path / "model.safetensors").write_bytes(b"\x00\x01")
+    with pytest.raises(ValueError):
+        SafetensorsFile(str(tmp_path / "model.safetensors"))
+
+
+def test_sharded_index(tmp_path):
+    a = {"model.a.weight": torch.randn(4, 3).bfloat16()}
+    b = {"model.a.bias": torch.randn(4)}
+    save_safetensors(a, str(tmp_path / "s1.safetensors"))
+    save_safetensors(b, str(tmp_path / "s2.safetensors"))
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps(
+        {"weight_map": {"model.a.weight": "s1.safetensors", "model.a.bias": "s2.safetensors"}}))
+    out = load_tensors(str(tmp_path), _specs())
+    assert torch.equal(out["model.a.bias"], b["model.a.bias"])

@@ -1,0 +1,81 @@
+"""The plain implementation checked against itself and against torch's own primitives, so that
+the oracle of all other tests is not trusted blindly."""
+import math
+
+import pytest
+import torch
+
+from helpers import TinyModel
+from plain import opt_plain as P
+
+
+def test_layer_norm_matches_torch():
+    x = torch.randn(7, 96)
+    w, b = torch.randn(96), torch.randn(96)
+    assert torch.allclose(P.layer_norm(x, w, b, 1e-6), torch.nn.functional.layer_norm(x, (96,), w, b, 1e-6), atol=1e-5)
+    assert torch.allclose(P.layer_norm(x, None, None, 1e-5), torch.nn.functional.layer_norm(x, (96,), None, None, 1e-5), atol=1e-5)
+
+
+def test_attention_matches_torch_sdpa():
+    T, H, d = 19, 3, 32
+    q, k, v = torch.randn(H, T, d), torch.randn(H, T, d), torch.randn(H, T, d)
+    s = P.attention_scores(q, k, d)
+    c = P.attention_context(P.masked_softmax(s, P.causal_mask(T, T)[None]), v)
+    ref = torch.nn.functional.scaled_dot_product_attention(q[None], k[None], v[None], is_causal=True)[0]
+    assert torch.allclose(c, ref, atol=1e-5)
+
+
+def test_causal_mask_and_window():
+    m = P.causal_mask(3, 5, first_query_position=2)
+    assert m.tolist() == [[True, True, True, False, False], [True, True, True, True, False], [True] * 5]
+    m = P.causal_mask(4, 4, window=2)
+    assert m.tolist() == [[True, False, False, False], [True, True, False, False], [False, True, True, False], [False, False, True, True]]
+
+
+def test_position_offset_is_two():
+    table = torch.arange(10.0)[:, None].repeat(1, 4)
+    assert P.learned_position_embedding(torch.tensor([0, 3]), table)[:, 0].tolist() == [2.0, 5.0]
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_causality_and_determinism(name):
+    m = TinyModel(name, seed=1)
+    ids = m.random_ids(24, seed=2)
+    full = m.plain_logits(ids)
+    part = P.forward_logits(ids[:10], m.tensors, m.cfg.to_dict())
+    assert full.shape == (24, m.cfg.vocab_size)
+    assert torch.allclose(full[:10], part, atol=1e-5)          # later tokens do not change earlier logits
+    f64 = P.forward_logits(ids, m.tensors, m.cfg.to_dict(), dtype=torch.float64)
+    assert float((full.double() - f64).abs().max()) < 1e-4 * float(f64.abs().max())
+
+
+def test_options_matter():
+    """Every option of configuration B changes the logits: none is silently ignored."""
+    m = TinyModel("B", seed=1)
+    ids = m.random_ids(12, seed=3)
+    base = m.plain_logits(ids)
+    for key, val in (("do_layer_norm_before", True), ("layer_norm_eps", 1e-1), ("num_attention_heads", 6)):
+        cfg = dict(m.cfg.to_dict(), **{key: val})
+        other = P.forward_logits(ids, m.tensors, cfg)
+        assert float((other - base).abs().max()) > 1e-4, key
+
+
+def test_sampling_filters():
+    logits = torch.tensor([[2.0, 1.0, 0.5, 0.0, -1.0]])
+    p = P.sampling_distribution(logits, temperature=1.0, top_k=2)
+    assert (p[0] > 0).tolist() == [True, True, False, False, False] and abs(float(p.sum()) - 1) < 1e-6
+    probs = torch.softmax(logits, -1)[0]
+    top_p = float(probs[0] + probs[1] / 2)                      # reached inside the second token
+    p = P.sampling_distribution(logits, top_p=top_p)
+    assert (p[0] > 0).tolist() == [True, True, False, False, False]
+    p = P.sampling_distribution(logits, top_p=float(probs[0]) - 1e-3)
+    assert (p[0] > 0).tolist() == [True, False, False, False, False]
+    p = P.sampling_distribution(logits, temperature=0.5, suppress=[0])
+    assert p[0, 0] == 0 and torch.allclose(p[0, 1:], torch.softmax(logits[0, 1:] / 0.5, -1))
+    assert int(P.greedy_token(torch.tensor([1.0, 3.0, 3.0]))) == 1
+
+
+def test_greedy_generate():
+    m = TinyModel("A", seed=4)
+    out = P.greedy_generate(m.random_ids(6, seed=1), 5, m.tensors, m.cfg.to_dict())
+    assert len(out) == 5 and all(0 <= t < m.cfg.vocab_size for t in out)

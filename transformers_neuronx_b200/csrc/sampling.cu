@@ -63,7 +63,7 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
 
     if (!(T > 0.f)) {
         ArgMax best{-INFINITY, 0x7fffffff};
-        for (int i = tid; i < V; i += THREADS) best = better(best, ArgMax{row[i], i});
+        for (int i = tid; i < V; i += THREADS) best = better(best, ArgMax{i == suppress_id ? -INFINITY : row[i], i});
         for (int o = 16; o > 0; o >>= 1) {
             ArgMax other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
             best = better(best, other);

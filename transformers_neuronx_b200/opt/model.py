@@ -1,0 +1,149 @@
+"""The Python entry point in the reference's manner:
+
+    model = OPTForSampling.from_pretrained(path, batch_size=4, amp='bf16', n_positions=2048)
+    model.to_neuron()
+    tokens = model.sample(input_ids, sequence_length=2048)
+
+Names and meanings follow src/transformers_neuronx/opt/model.py:34-192: ``sequence_length`` is the
+total length (prompt included); ``sample`` draws from the top_k (default 50) most likely tokens and
+never draws the end-of-sequence token (sampling.py:26-30, :131-180); ``top_k=1`` is greedy, as in
+the reference's own validation (testing/validation.py:68-101); ``forward(input_ids, cache_ids,
+start_ids)`` returns the 32-bit logits [batch, vocab] of each row's last token; ``start_ids`` marks
+left padding.  ``tp_degree``, ``unroll``, ``context_length_estimate`` and ``neuron_config`` have no
+meaning on one GPU and are accepted and ignored with a warning.  ``to_neuron`` loads the weights
+onto the GPU and compiles the kernels that the model needs.
+"""
+from __future__ import annotations
+
+import os
+import warnings
+from typing import List, Optional
+
+import torch
+
+from ..config import EngineConfig, OPTConfig, canonical_dtype, load_config
+from ..engine import LLMEngine, SamplingParams, StepEntry, load_model
+
+
+class OPTForSampling:
+    def __init__(self, folder: str, config: OPTConfig, batch_size=1, amp=None, tp_degree=None, n_positions=2048,
+                 unroll=None, context_length_estimate=None, context_unroll=None, neuron_config=None, **kwargs):
+        for name, val in (("tp_degree", tp_degree), ("unroll", unroll), ("context_unroll", context_unroll),
+                          ("context_length_estimate", context_length_estimate), ("neuron_config", neuron_config)):
+            if val is not None:
+                warnings.warn(f"{name}={val!r} has no meaning for the one-GPU engine and is ignored")
+        if kwargs:
+            raise KeyError(f"unknown argument(s): {sorted(kwargs)}")
+        if amp is None:
+            amp = "bf16" if str(config.torch_dtype).replace("torch.", "") in ("float16", "bfloat16") else "f32"
+        self.amp = amp
+        self.dtype = canonical_dtype(amp)
+        max_bucket = max(n_positions) if isinstance(n_positions, (list, tuple)) else n_positions
+        if max_bucket > config.max_position_embeddings:     # opt/model.py:51-57
+            raise ValueError(f"Sequence length ({max_bucket}) cannot be larger than position embedding's "
+                             f"context size ({config.max_position_embeddings})!")
+        self.folder = folder
+        self.config = config
+        self.batch_size = max(batch_size) if isinstance(batch_size, (list, tuple)) else int(batch_size)
+        self.n_positions = int(max_bucket)
+        self.engine: Optional[LLMEngine] = None
+        self.model = None
+        self._rows: List[str] = []
+
+    # ---- loading ------------------------------------------------------------------------------------
+    @classmethod
+    def from_pretrained(cls, pretrained_model_path, *model_args, **kwargs):
+        if not os.path.isdir(pretrained_model_path):
+            raise FileNotFoundError(f"{pretrained_model_path!r} is not a folder; there is no network here to "
+                                    "fetch a model by name")
+        arch, config = load_config(pretrained_model_path)
+        if arch.name != "OPTForCausalLM":
+            raise ValueError(f"{pretrained_model_path} holds a {arch.name}, not an OPT model")
+        return cls(pretrained_model_path, config, *model_args, **kwargs)
+
+    def to_neuron(self):
+        """Weights to the GPU, kernels compiled, cache made.  Kept under the reference's name."""
+        if self.engine is not None:
+            return self
+        self.model, _ = load_model(self.folder, self.dtype)
+        ec = EngineConfig(dtype=self.dtype, max_num_seqs=max(self.batch_size, 1), max_model_len=self.n_positions,
+                          max_tokens=self.batch_size * (-(-self.n_positions // 16) * 16),
+                          max_batch_tokens=max(2048, self.batch_size))
+        self.engine = LLMEngine(self.model, ec, eos_token_id=self.config.eos_token_id)
+        return self
+
+    to_gpu = to_neuron
+
+    def _ready(self):
+        if self.engine is None:
+            self.to_neuron()
+
+    # ---- generation ---------------------------------------------------------------------------------
+    def sample(self, input_ids, sequence_length, start_ids=None, top_k=50, streamer=None, temperature=1.0,
+               top_p=1.0, seed=0):
+        """[batch, prompt] ids -> [batch, sequence_length] ids (prompt included)."""
+        self._ready()
+        input_ids = torch.as_tensor(input_ids)
+        B, T0 = input_ids.shape
+        if B > self.batch_size:
+            raise ValueError(f"batch of {B} rows; the model was made for batch_size={self.batch_size}")
+        if sequence_length > self.n_positions:
+            raise ValueError(f"sequence_length {sequence_length} exceeds n_positions {self.n_positions}")
+        starts = [0] * B if start_ids is None else [int(s) for s in torch.as_tensor(start_ids).tolist()]
+        rows = input_ids.tolist()
+        prompts = [rows[b][starts[b]:] for b in range(B)]
+        n_new = sequence_length - T0
+        if n_new <= 0:
+            return input_ids[:, :sequence_length]
+        greedy = top_k == 1
+        params = [SamplingParams(temperature=0.0 if greedy else float(temperature), top_k=0 if greedy else int(top_k or 0),
+                                 top_p=float(top_p), seed=int(seed) + b, suppress_eos=True) for b in range(B)]
+        outs = self.engine.generate(prompts, n_new, params, stop_on_eos=False)
+        result = torch.cat([input_ids, torch.as_tensor(outs, dtype=input_ids.dtype)], dim=1)
+        if streamer is not None:
+            for t in range(T0, sequence_length):
+                streamer.put(result[:, t:t + 1])
+            streamer.end()
+        return result
+
+    # ---- the static-batch forward of the reference ---------------------------------------------------------
+    def reset(self):
+        if self.engine is not None:
+            for rid in self._rows:
+                if rid in self.engine.runner.cache:
+                    self.engine.runner.finish(rid)
+        self._rows = []
+
+    def forward(self, input_ids, cache_ids=None, start_ids=None):
+        """cache_ids None: the rows are whole prompts (a new batch).  Otherwise input_ids holds the
+        next token(s) of every row at positions cache_ids.  Returns 32-bit logits [batch, vocab] of
+        the last token of each row, on the host."""
+        self._ready()
+        input_ids = torch.as_tensor(input_ids)
+        B, T = input_ids.shape
+        runner = self.engine.runner
+        starts = [0] * B if start_ids is None else [int(s) for s in torch.as_tensor(start_ids).tolist()]
+        if cache_ids is None:
+            self.reset()
+            self._rows = [f"row{b}" for b in range(B)]
+            for rid in self._rows:
+                runner.add_request(rid)
+            toks = [input_ids[b, starts[b]:].tolist() for b in range(B)]
+        else:
+            first = int(torch.as_tensor(cache_ids).flatten()[0])
+            toks = [input_ids[b].tolist() for b in range(B)]
+            for b, rid in enumerate(self._rows):
+                have = runner.cache.length(rid)
+                if have != first - starts[b]:
+                    raise ValueError(f"row {b} holds {have} tokens; cache_ids says {first - starts[b]}")
+        entries = [StepEntry(rid, t, [len(t) - 1]) for rid, t in zip(self._rows, toks)]
+        return runner.step(entries).to("cpu", torch.float32)
+
+    __call__ = forward
+
+
+class OPTForGreedySearch(OPTForSampling):
+    """Greedy search with the choice made on the device (opt/model.py:534-570)."""
+
+    def sample(self, input_ids, sequence_length, start_ids=None, **_):
+        return super().sample(input_ids, sequence_length, start_ids=start_ids, top_k=1)

@@ -114,14 +114,18 @@ def load_tensors(folder: str, specs: Sequence[TensorSpec]) -> Dict[str, torch.Te
     out, other = {}, []
     by_name = {s.name: s for s in specs}
     for name, src in resolved.items():
+        if by_name[name].tied_to is not None and resolved.get(by_name[name].tied_to) == src:
+            continue                          # filled from its tie below
         out[name] = _convert(owner[src].tensor(src), name, other)
     # A file that stores a tied tensor under both names must store the same values.
     for s in specs:
-        if s.tied_to is not None and resolved.get(s.name) != resolved.get(s.tied_to):
+        if s.tied_to is None:
+            continue
+        if resolved.get(s.name) != resolved.get(s.tied_to):
             a, b = out[s.name], out[s.tied_to]
             if a.shape == b.shape and not torch.equal(a.float(), b.float()):
                 other.append(f"{s.name} differs from {s.tied_to}, to which it is tied")
-            out[s.name] = out[s.tied_to]
+        out[s.name] = out[s.tied_to]          # one tensor under both names
     if other:
         raise WeightError(folder, [], [], [], other)
     for f in files:
