@@ -1,0 +1,510 @@
+// bfloat16 matrix product on the 5th-generation tensor cores (tcgen05), operands brought into
+// shared memory by TMA, 32-bit accumulators in tensor memory.
+//
+//   C[m, n] = epilogue( sum_k A[m, k] * W[n, k] )        A: [M, K] bf16, W: [N, K] bf16, row-major
+//   epilogue: + bias[n] (32-bit); ReLU; + residual[m, n] (32-bit); stored as bfloat16 or float.
+//
+// One CTA computes one 128 x BN tile of D = P Q^T over a range of K.  Two forms:
+//   normal (many tokens): P = A (128 tokens), Q = W (BN = 128 features)
+//   swapped (few tokens): P = W (128 features), Q = A (BN = 16/32/64 tokens): the weight matrix,
+//     which is what a decode step has to stream from HBM, fills the 128-row operand and nothing
+//     is wasted on padding tokens.  Few output tiles -> K is split over several CTAs; each writes
+//     its 32-bit partial tile to scratch memory and the CTA that finishes last adds the partials in
+//     split order (a fixed order) and applies the epilogue.
+//
+// Warp roles: warp 0 issues TMA loads, warp 1 allocates tensor memory and issues the MMAs (one
+// elected lane), warps 2-5 read the accumulators (tcgen05.ld, one 32-lane quadrant each) and write
+// the result.  Shared-memory stages are handed over with mbarriers; every wait is bounded and
+// reports through an error word instead of hanging.
+//
+// TMA: every CTA loads its own tiles (no multicast); the innermost coordinate is a multiple of 64
+// elements, so every copy starts on a 128-byte boundary.  K must be a multiple of 8 (row pitch a
+// multiple of 16 bytes); K, M and N tails are zero-filled by TMA and masked at the store.
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BLOCK_K = 64;          // 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int TILE_P = 128;          // rows of the 128-row operand = TMEM lanes
+constexpr int NUM_THREADS = 192;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // 2 s
+
+// ---- PTX wrappers ----------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait: false (and *err set) when the phase did not complete within the limit.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    for (;;) {
+        for (int i = 0; i < 256; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (global_ns() - t0 > WAIT_LIMIT_NS) {
+            atomicExch(err, code);
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"((unsigned long long)map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzled
+// (what TMA writes with CU_TENSOR_MAP_SWIZZLE_128B): groups of 8 rows are 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);            // start address, bits [0,14)
+    d |= (uint64_t)1 << 16;                              // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;                    // stride byte offset, bits [32,46)
+    d |= (uint64_t)1 << 46;                              // descriptor version for sm_100
+    d |= (uint64_t)2 << 61;                              // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor: D = f32, A = B = bf16, both K-major, M = 128, N = n.
+__host__ __device__ constexpr uint32_t instr_desc(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TILE_P >> 4) << 24);
+}
+
+struct Params {
+    int rows_p, rows_q;          // extents of the P (lane) and Q (column) axes
+    int K;
+    int kb_per_split;            // K blocks per split
+    int splits;
+    int ldc;
+    int relu;
+    int c_is_bf16;
+    const float* bias;           // indexed by feature
+    const float* residual;       // [M, ldc] 32-bit, may alias C
+    void* C;
+    float* partials;             // [splits][rows_p_padded][rows_q_padded] when splits > 1
+    int* counters;               // one per output tile, zero between calls
+    int* err;
+};
+
+template <int BN, bool SWAP>
+__device__ __forceinline__ void store_tile_row(const Params& p, int lane_row, int col0, const float (&v)[32], int ncols) {
+    // lane_row: index on the P axis; col0..col0+ncols: indices on the Q axis.
+    if (lane_row >= p.rows_p) return;
+    if (SWAP) {
+        // P axis = feature n, Q axis = token m: lanes of a warp write consecutive n.
+        const int n = lane_row;
+        const float b = p.bias ? p.bias[n] : 0.f;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const int m = col0 + j;
+            if (j < ncols && m < p.rows_q) {
+                float x = v[j] + b;
+                if (p.relu) x = fmaxf(x, 0.f);
+                const size_t o = (size_t)m * p.ldc + n;
+                if (p.residual) x += p.residual[o];
+                if (p.c_is_bf16) ((bf16*)p.C)[o] = __float2bfloat16_rn(x);
+                else ((float*)p.C)[o] = x;
+            }
+        }
+    } else {
+        // P axis = token m, Q axis = feature n: a thread writes a run of its own row.
+        const int m = lane_row;
+        const size_t rowo = (size_t)m * p.ldc;
+        const bool full = (col0 + 32 <= p.rows_q) && ncols == 32 && (p.ldc % 8 == 0);
+        float x[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const int n = col0 + j;
+            float t = v[j];
+            if (n < p.rows_q) {
+                if (p.bias) t += __ldg(p.bias + n);
+                if (p.relu) t = fmaxf(t, 0.f);
+                if (p.residual) t += p.residual[rowo + n];
+            }
+            x[j] = t;
+        }
+        if (full) {
+            if (p.c_is_bf16) {
+                uint4* dst = (uint4*)((bf16*)p.C + rowo + col0);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    __nv_bfloat162 h0 = __floats2bfloat162_rn(x[8 * q + 0], x[8 * q + 1]);
+                    __nv_bfloat162 h1 = __floats2bfloat162_rn(x[8 * q + 2], x[8 * q + 3]);
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(x[8 * q + 4], x[8 * q + 5]);
+                    __nv_bfloat162 h3 = __floats2bfloat162_rn(x[8 * q + 6], x[8 * q + 7]);
+                    uint4 u;
+                    u.x = *(uint32_t*)&h0; u.y = *(uint32_t*)&h1; u.z = *(uint32_t*)&h2; u.w = *(uint32_t*)&h3;
+                    dst[q] = u;
+                }
+            } else {
+                float4* dst = (float4*)((float*)p.C + rowo + col0);
+#pragma unroll
+                for (int q = 0; q < 8; ++q) dst[q] = make_float4(x[4 * q], x[4 * q + 1], x[4 * q + 2], x[4 * q + 3]);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const int n = col0 + j;
+                if (j < ncols && n < p.rows_q) {
+                    if (p.c_is_bf16) ((bf16*)p.C)[rowo + n] = __float2bfloat16_rn(x[j]);
+                    else ((float*)p.C)[rowo + n] = x[j];
+                }
+            }
+        }
+    }
+}
+
+template <int BN, int STAGES, bool SWAP>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, const Params p) {
+    constexpr int A_BYTES = TILE_P * BLOCK_K * 2;            // 16 KB
+    constexpr int B_BYTES = BN * BLOCK_K * 2;
+    constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+    constexpr int LD_COLS = BN < 32 ? 16 : 32;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], tmem_full_bar;
+    __shared__ uint32_t tmem_base_smem;
+    __shared__ int last_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile_p = blockIdx.x, tile_q = blockIdx.y, split = blockIdx.z;
+    const int num_kb_total = (p.K + BLOCK_K - 1) / BLOCK_K;
+    const int kb_begin = split * p.kb_per_split;
+    const int kb_end = min(num_kb_total, kb_begin + p.kb_per_split);
+    const int num_kb = max(0, kb_end - kb_begin);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        mbar_init(&tmem_full_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(&tmem_base_smem, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_smem;
+    bool ok = true;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int i = 0; i < num_kb && ok; ++i) {
+                const int s = i % STAGES;
+                const uint32_t ph = (i / STAGES) & 1;
+                ok = mbar_wait(&empty_bar[s], ph ^ 1, p.err, 1);
+                if (!ok) break;
+                mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+                uint8_t* a_dst = smem + (size_t)s * STAGE_BYTES;
+                uint8_t* b_dst = a_dst + A_BYTES;
+                const int kx = (kb_begin + i) * BLOCK_K;
+                tma_load_2d(a_dst, &map_p, &full_bar[s], kx, tile_p * TILE_P);
+                tma_load_2d(b_dst, &map_q, &full_bar[s], kx, tile_q * BN);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc(BN);
+            for (int i = 0; i < num_kb && ok; ++i) {
+                const int s = i % STAGES;
+                const uint32_t ph = (i / STAGES) & 1;
+                ok = mbar_wait(&full_bar[s], ph, p.err, 2);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(smem + (size_t)s * STAGE_BYTES);
+                const uint32_t b_addr = a_addr + A_BYTES;
+                const uint64_t adesc = smem_desc_sw128(a_addr);
+                const uint64_t bdesc = smem_desc_sw128(b_addr);
+#pragma unroll
+                for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                    // advancing 16 elements along K = 32 bytes = 2 units of the address field
+                    umma_bf16(tmem_base, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
+                              (i > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(&empty_bar[s]);          // the stage is free once these MMAs have read it
+            }
+            umma_commit(&tmem_full_bar);             // accumulators complete
+        }
+    } else {
+        // Epilogue warps 2..5: TMEM lane quadrant = warp % 4.
+        const int quad = warp & 3;
+        const int row_in_tile = quad * 32 + lane;
+        ok = mbar_wait(&tmem_full_bar, 0, p.err, 3);
+        tc_fence_after();
+        const int lane_row = tile_p * TILE_P + row_in_tile;
+        if (ok) {
+            if (p.splits == 1) {
+#pragma unroll 1
+                for (int c = 0; c < BN; c += LD_COLS) {
+                    uint32_t r[32];
+                    const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c;
+                    if (LD_COLS == 32) tmem_ld32(taddr, r); else tmem_ld16(taddr, r);
+                    tmem_ld_wait();
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = (j < LD_COLS && num_kb > 0) ? __uint_as_float(r[j]) : 0.f;
+                    store_tile_row<BN, SWAP>(p, lane_row, tile_q * BN + c, v, LD_COLS);
+                }
+            } else {
+                // 32-bit partial tile -> scratch: [split][tile_p][tile_q][row 0..127][col 0..BN)
+                const size_t tiles = (size_t)gridDim.x * gridDim.y;
+                const size_t tile_id = (size_t)tile_p * gridDim.y + tile_q;
+                float* dst = p.partials + (((size_t)split * tiles + tile_id) * TILE_P + row_in_tile) * BN;
+#pragma unroll 1
+                for (int c = 0; c < BN; c += LD_COLS) {
+                    uint32_t r[32];
+                    const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c;
+                    if (LD_COLS == 32) tmem_ld32(taddr, r); else tmem_ld16(taddr, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < LD_COLS; j += 4) {
+                        float4 f = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                               __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                        if (num_kb == 0) f = make_float4(0.f, 0.f, 0.f, 0.f);
+                        *(float4*)(dst + c + j) = f;
+                    }
+                }
+            }
+        }
+    }
+
+    // ---- split-K: the CTA that finishes last adds the partial tiles in split order -------------
+    if (p.splits > 1) {
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const int tile_id = tile_p * gridDim.y + tile_q;
+            const int prev = atomicAdd(&p.counters[tile_id], 1);
+            last_flag = (prev == p.splits - 1);
+            if (last_flag) p.counters[tile_id] = 0;           // ready for the next call
+        }
+        __syncthreads();
+        if (last_flag && warp >= 2) {
+            __threadfence();
+            const int quad = warp & 3;
+            const int row_in_tile = quad * 32 + lane;
+            const int lane_row = tile_p * TILE_P + row_in_tile;
+            const size_t tiles = (size_t)gridDim.x * gridDim.y;
+            const size_t tile_id = (size_t)tile_p * gridDim.y + tile_q;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += LD_COLS) {
+                float v[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = 0.f;
+                for (int s = 0; s < p.splits; ++s) {
+                    const float* src = p.partials + (((size_t)s * tiles + tile_id) * TILE_P + row_in_tile) * BN + c;
+#pragma unroll
+                    for (int j = 0; j < LD_COLS; j += 4) {
+                        const float4 f = __ldcg((const float4*)(src + j));
+                        v[j] += f.x; v[j + 1] += f.y; v[j + 2] += f.z; v[j + 3] += f.w;
+                    }
+                }
+                store_tile_row<BN, SWAP>(p, lane_row, tile_q * BN + c, v, LD_COLS);
+            }
+        }
+    }
+
+    // ---- teardown ---------------------------------------------------------------------------------
+    if (!ok) {
+        // A wait ran out: give copies in flight time to land before the shared memory is released.
+        const unsigned long long t0 = global_ns();
+        while (global_ns() - t0 < 1000000ull) __nanosleep(1000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ---- host side ----------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)f;
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr; int rows, cols, ld, box_rows;
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+    }
+};
+struct MapHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = (size_t)k.ptr;
+        h = h * 1000003u ^ (size_t)k.rows; h = h * 1000003u ^ (size_t)k.cols;
+        h = h * 1000003u ^ (size_t)k.ld;   h = h * 1000003u ^ (size_t)k.box_rows;
+        return h;
+    }
+};
+
+// A [rows, cols] bf16 matrix with row pitch ld elements; boxes of box_rows x 64, 128-byte swizzle.
+bool make_map(CUtensorMap* out, const void* ptr, int rows, int cols, int ld, int box_rows) {
+    static std::unordered_map<MapKey, CUtensorMap, MapHash> cache;
+    static std::mutex mu;
+    MapKey key{ptr, rows, cols, ld, box_rows};
+    std::lock_guard<std::mutex> g(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return true; }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BLOCK_K, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return false;
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, *out);
+    return true;
+}
+
+template <int BN, int STAGES, bool SWAP>
+int launch(const CUtensorMap& mp, const CUtensorMap& mq, const Params& p, dim3 grid, cudaStream_t stream) {
+    constexpr size_t smem = (size_t)STAGES * (TILE_P * BLOCK_K * 2 + BN * BLOCK_K * 2) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    gemm_tc_kernel<BN, STAGES, SWAP><<<grid, NUM_THREADS, smem, stream>>>(mp, mq, p);
+    return tnx_launch_status();
+}
+
+}  // namespace
+
+// Bytes of 32-bit scratch and number of tile counters that tnx_gemm_tc needs for these sizes (0
+// when K is not split).  The caller owns both; the counters must be zero before the first call and
+// are left zero by every call.
+TNX_EXPORT int tnx_gemm_tc_plan(int M, int N, int K, int n_sms, int* splits, long long* scratch_bytes, int* n_counters) {
+    *splits = 1; *scratch_bytes = 0; *n_counters = 0;
+    if (M > 64) return 0;
+    const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    const int tiles = (N + TILE_P - 1) / TILE_P;
+    const int kb = (K + BLOCK_K - 1) / BLOCK_K;
+    int s = n_sms / tiles;
+    if (s > kb / 4) s = kb / 4;
+    if (s > 16) s = 16;
+    if (s < 1) s = 1;
+    const int per = (kb + s - 1) / s;
+    s = (kb + per - 1) / per;                 // no empty split
+    *splits = s;
+    if (s > 1) {
+        *scratch_bytes = (long long)s * tiles * TILE_P * bn * 4;
+        *n_counters = tiles;
+    }
+    return 0;
+}
+
+TNX_EXPORT int tnx_gemm_tc(const void* A, const void* W, const float* bias, const float* residual, void* C,
+                           int M, int N, int K, int lda, int ldw, int ldc, int relu, int c_bf16,
+                           int splits, float* scratch, int* counters, int* err_word, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 || lda % 8 || ldw % 8 || lda < K || ldw < K || ldc < N) return TNX_ERR_UNSUPPORTED;
+    if (((uintptr_t)A | (uintptr_t)W) & 15) return TNX_ERR_UNSUPPORTED;
+    if (residual && c_bf16) return TNX_ERR_BAD_ARG;
+    if (!err_word) return TNX_ERR_BAD_ARG;
+    Params p{};
+    p.K = K; p.ldc = ldc; p.relu = relu; p.c_is_bf16 = c_bf16; p.bias = bias; p.residual = residual; p.C = C;
+    p.err = err_word; p.partials = scratch; p.counters = counters;
+    const int kb = (K + BLOCK_K - 1) / BLOCK_K;
+    CUtensorMap mp, mq;
+    if (M > 64) {
+        p.rows_p = M; p.rows_q = N; p.splits = 1; p.kb_per_split = kb;
+        if (!make_map(&mp, A, M, K, lda, TILE_P) || !make_map(&mq, W, N, K, ldw, 128)) return TNX_ERR_UNSUPPORTED;
+        dim3 grid((M + TILE_P - 1) / TILE_P, (N + 127) / 128, 1);
+        return launch<128, 6, false>(mp, mq, p, grid, stream);
+    }
+    if (splits < 1) splits = 1;
+    if (splits > 1 && (!scratch || !counters)) return TNX_ERR_BAD_ARG;
+    p.rows_p = N; p.rows_q = M; p.splits = splits; p.kb_per_split = (kb + splits - 1) / splits;
+    const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    if (!make_map(&mp, W, N, K, ldw, TILE_P) || !make_map(&mq, A, M, K, lda, bn)) return TNX_ERR_UNSUPPORTED;
+    dim3 grid((N + TILE_P - 1) / TILE_P, 1, splits);
+    if (bn == 16) return launch<16, 8, true>(mp, mq, p, grid, stream);
+    if (bn == 32) return launch<32, 8, true>(mp, mq, p, grid, stream);
+    return launch<64, 8, true>(mp, mq, p, grid, stream);
+}

@@ -36,6 +36,7 @@ SOURCES: Dict[str, str] = {
     "kv_cache": "kv_cache.cu",
     "attention_simt": "attention_simt.cu",
     "sampling": "sampling.cu",
+    "gemm_tc": "gemm_tc.cu",
 }
 
 _loaded: Dict[str, ctypes.CDLL] = {}

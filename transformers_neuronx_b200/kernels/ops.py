@@ -216,19 +216,91 @@ def sample(logits, out, temperature=None, top_k=None, top_p=None, seeds=None, co
 
 
 # ---------------------------------------------------------------------------------------------
-# Tensor-core kernels (bfloat16).  Registered by their own modules when they are built.
-_gemm_tc_impl = None
+# Tensor-core kernels (bfloat16).
 _attention_impls = {}
+_dev_state = {}          # per device: error word, split-K scratch and counters, SM count
+
+
+def _state(device):
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    st = _dev_state.get(key)
+    if st is None:
+        st = {"err": torch.zeros(1, dtype=torch.int32, device=device),
+              "scratch": None, "counters": torch.zeros(1024, dtype=torch.int32, device=device),
+              "sms": torch.cuda.get_device_properties(device).multi_processor_count}
+        _dev_state[key] = st
+    return st
+
+
+def raise_on_device_error(device=None):
+    """Reads the error word that kernels with bounded waits set (this synchronises)."""
+    for key, st in _dev_state.items():
+        code = int(st["err"].item())
+        if code:
+            st["err"].zero_()
+            raise KernelError(f"a bounded wait ran out inside a kernel on cuda:{key} (where: {code}); "
+                              "its results are invalid")
 
 
 def has_gemm_tc() -> bool:
-    return _gemm_tc_impl is not None
+    return True
 
 
-def gemm_tc(a, w, out, bias=None, residual=None, relu=False):
-    if _gemm_tc_impl is None:
-        raise KernelError("the tensor-core matrix product is not available")
-    _gemm_tc_impl(a, w, out, bias, residual, relu)
+def gemm_tc_supported(a, w, out) -> bool:
+    """Size rules of the TMA descriptors: row pitches multiples of 16 bytes, 16-byte aligned bases."""
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        return False
+    K = a.shape[1]
+    if K % 8 or a.stride(0) % 8 or w.stride(0) % 8 or a.data_ptr() % 16 or w.data_ptr() % 16:
+        return False
+    return out.data_ptr() % 16 == 0
+
+
+def gemm_tc(a, w, out, bias=None, residual=None, relu=False, splits=None):
+    """out = epilogue(a @ w^T), bfloat16 operands on tcgen05 tensor cores, 32-bit accumulation."""
+    lib = _build.load("gemm_tc")
+    _need(a, "a", torch.bfloat16, None, contiguous=False)
+    _need(w, "w", torch.bfloat16, None, contiguous=False)
+    _need(out, "out", _FLOATS, None, contiguous=False)
+    M, K, lda = _rows_2d(a, "a")
+    N, Kw, ldw = _rows_2d(w, "w")
+    Mo, No, ldc = _rows_2d(out, "out")
+    if Kw != K or Mo != M or No != N:
+        raise KernelError(f"gemm shapes do not fit: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if not gemm_tc_supported(a, w, out):
+        raise KernelError("the tensor-core product needs K and the row pitches to be multiples of 8 elements "
+                          "and 16-byte aligned bases; use gemm_simt for other sizes")
+    if bias is not None:
+        _need(bias, "bias", torch.float32, 1)
+        if bias.shape[0] != N:
+            raise KernelError("bias length differs from the output width")
+    if residual is not None:
+        _need(residual, "residual", torch.float32, None, contiguous=False)
+        if tuple(residual.shape) != (M, N) or _rows_2d(residual, "residual")[2] != ldc or out.dtype != torch.float32:
+            raise KernelError("residual must be float32 with the shape and row stride of a float32 out")
+    st = _state(a.device)
+    n_splits, nbytes, ncnt = c_int(1), ctypes.c_longlong(0), c_int(0)
+    lib.tnx_gemm_tc_plan(c_int(M), c_int(N), c_int(K), c_int(st["sms"]), ctypes.byref(n_splits),
+                         ctypes.byref(nbytes), ctypes.byref(ncnt))
+    if splits is not None and M <= 64:
+        kb = -(-K // 64)
+        s = max(1, min(int(splits), kb))
+        per = -(-kb // s)
+        s = -(-kb // per)
+        bn = 16 if M <= 16 else (32 if M <= 32 else 64)
+        tiles = -(-N // 128)
+        n_splits, nbytes, ncnt = c_int(s), ctypes.c_longlong(s * tiles * 128 * bn * 4 if s > 1 else 0), c_int(tiles if s > 1 else 0)
+    scratch = None
+    if nbytes.value:
+        need = nbytes.value // 4
+        if st["scratch"] is None or st["scratch"].numel() < need:
+            st["scratch"] = torch.empty(max(need, 1 << 20), dtype=torch.float32, device=a.device)
+        if st["counters"].numel() < ncnt.value:
+            st["counters"] = torch.zeros(ncnt.value, dtype=torch.int32, device=a.device)
+        scratch = st["scratch"]
+    _check(lib.tnx_gemm_tc(_p(a), _p(w), _p(bias), _p(residual), _p(out), c_int(M), c_int(N), c_int(K),
+                           c_int(lda), c_int(ldw), c_int(ldc), c_int(1 if relu else 0), c_int(_is_bf16(out)),
+                           n_splits, _p(scratch), _p(st["counters"]), _p(st["err"]), _stream()), "gemm_tc")
 
 
 def attention(ctx, group, q, cache, out, n_heads, scale, window=0):

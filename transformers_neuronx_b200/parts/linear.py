@@ -19,8 +19,6 @@ from .base import Part, to_device
 from .spec import LinearSpec
 
 
-def tensor_core_ok(a_dtype, w_dtype, K: int) -> bool:
-    return a_dtype == torch.bfloat16 and w_dtype == torch.bfloat16 and K % 8 == 0 and ops.has_gemm_tc()
 
 
 class Linear(Part):
@@ -60,7 +58,7 @@ class Linear(Part):
 
 
 def linear_forward(a, weight, bias, out, residual=None, relu=False):
-    if tensor_core_ok(a.dtype, weight.dtype, weight.shape[1]):
+    if ops.gemm_tc_supported(a, weight, out):
         ops.gemm_tc(a, weight, out, bias=bias, residual=residual, relu=relu)
     else:
         ops.gemm_simt(a, weight, out, bias=bias, residual=residual, relu=relu)
