@@ -1,0 +1,270 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine on one B200, on the layer sizes of OPT-6.7B with
+random weights (the sizes come from BASELINE.json's configs[2]; nothing is published for them by
+the reference, so vs_baseline is null).
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line.  `value` is decoded tokens per second at batch 8 with the context ending at
+2,048, timed on the device over exactly K decode steps; `e2e` is the same through the Python entry
+point's engine loop (host token ids in through pinned memory, sampled ids out, every step);
+`prefill` is one 2,048-token prompt; `roofline` is the decode step's bytes (every weight once plus
+the live requests' cache) over its time; `points` are decode at batch 1 and 64.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+OPT_6_7B = dict(vocab_size=50272, hidden_size=4096, num_hidden_layers=32, num_attention_heads=32, ffn_dim=16384,
+                max_position_embeddings=2048, word_embed_proj_dim=4096, do_layer_norm_before=True, enable_bias=True,
+                layer_norm_elementwise_affine=True, activation_function="relu", init_std=0.02,
+                architectures=["OPTForCausalLM"], model_type="opt", torch_dtype="bfloat16")
+CONTEXT = 2048
+PREFILL_TOKENS = 2048
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    hbm, tf, src = 6650.0, 1590.0, "fallback"
+    if os.path.isfile(path):
+        try:
+            with open(path) as fp:
+                d = json.load(fp)
+            hbm = float(d.get("hbm_gbs", hbm))
+            tf = float(d.get("bf16_tflops", tf))
+            src = "measured"
+        except Exception:
+            pass
+    return hbm, tf, src
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows, self.proc = [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+        sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows if len(r) >= 6 for n, v in zip(names, r[2:6]) if v.lower().startswith("active")})
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(sm)}
+
+
+def build(n_layers, dtype="bfloat16"):
+    import torch
+    from transformers_neuronx_b200.config import OPTConfig
+    from transformers_neuronx_b200.engine import build_model
+    from transformers_neuronx_b200.models import opt as opt_arch
+    from transformers_neuronx_b200.models.decoder import DecoderModel
+    cfg = OPTConfig.from_dict(dict(OPT_6_7B, num_hidden_layers=n_layers))
+    spec = opt_arch.build_spec(cfg)
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device=dev).manual_seed(0)
+    tensors = {}
+    for s in DecoderModel(spec).tensor_specs():            # random weights made on the device
+        if s.tied_to is not None:
+            continue
+        t = torch.randn(s.shape, generator=g, device=dev, dtype=torch.float32) * cfg.init_std
+        if s.kind == "norm_weight":
+            tensors[s.name] = 1.0 + t
+        elif s.kind == "norm_bias":
+            tensors[s.name] = t
+        else:
+            tensors[s.name] = t.to(torch.bfloat16)
+    tensors["lm_head.weight"] = tensors["model.decoder.embed_tokens.weight"]
+    model = build_model(spec, tensors, dtype, verbose=False)
+    return model, cfg
+
+
+def decode_bytes(model, cfg, batch, ctx):
+    """Bytes one decode step has to read: every weight it uses once (the embedding table as the
+    output matrix; of the token and position tables only the batch's rows) and the live cache."""
+    H, L = cfg.hidden_size, cfg.num_hidden_layers
+    w = model.parameter_bytes()
+    pos_table = (cfg.max_position_embeddings + 2) * H * 2
+    w = w - pos_table + batch * H * 2 * 2
+    kv = batch * ctx * 2 * H * 2 * L
+    return w + kv
+
+
+def prefill_flops(cfg, T):
+    H, F, L, V = cfg.hidden_size, cfg.ffn_dim, cfg.num_hidden_layers, cfg.vocab_size
+    per_layer = 2 * T * (4 * H * H + 2 * H * F) + 2 * T * T * H      # products + causal attention
+    return L * per_layer + 2 * V * H
+
+
+def time_decode(model, cfg, batch, steps, warmup, use_engine=False):
+    """K decode steps at `batch`, the context ending at CONTEXT.  Returns (ms_per_step, launches, h2d, d2h)."""
+    import torch
+    from transformers_neuronx_b200.engine import StepEntry, StepRunner
+    from transformers_neuronx_b200.kernels import ops
+    total = steps + warmup
+    ctx0 = CONTEXT - total
+    pages = batch * (CONTEXT // 16)
+    runner = StepRunner(model, 16, pages, max(batch, 1), CONTEXT)
+    g = torch.Generator().manual_seed(1)
+    for b in range(batch):                                  # the cache as 2,048 - (W + K) earlier tokens left it:
+        runner.add_request(b)                               # synthetic keys and values, real bookkeeping
+        runner.cache.append(b, ctx0)
+    for cid in model.cache_needs():
+        runner.storage.tensor(cid).normal_(0, 0.5)
+    toks = torch.randint(3, cfg.vocab_size, (total, batch), generator=g).tolist()
+    from transformers_neuronx_b200.sampling import Sampler
+    sampler = Sampler(model.device)
+    pinned = torch.empty(batch, dtype=torch.int32).pin_memory()
+
+    def one(i):
+        entries = [StepEntry(b, [toks[i][b]], [0]) for b in range(batch)]
+        logits = runner.step(entries)
+        if use_engine:
+            ids = sampler.sample(logits, [0.0] * batch, [0] * batch, [1.0] * batch, [0] * batch, [i] * batch)
+            pinned.copy_(ids, non_blocking=False)            # device -> host read of the step's result
+        return logits
+
+    for i in range(warmup):
+        one(i)
+    torch.cuda.synchronize()
+    n0 = ops.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record()
+    for i in range(warmup, total):
+        one(i)
+    e1.record()
+    torch.cuda.synchronize()
+    wall = (time.perf_counter() - t0) * 1e3
+    launches = ops.launch_count() - n0
+    ops.raise_on_device_error()
+    ms = e0.elapsed_time(e1) / steps
+    if use_engine:
+        ms = wall / steps                                    # end to end: the host's clock around the loop
+    h2d = getattr(runner, "last_h2d_bytes", 0)
+    for b in range(batch):
+        runner.finish(b)
+    del runner
+    torch.cuda.empty_cache()
+    return ms, launches, h2d, batch * 4
+
+
+def time_prefill(model, cfg, steps, warmup):
+    import torch
+    from transformers_neuronx_b200.engine import StepEntry, StepRunner
+    runner = StepRunner(model, 16, PREFILL_TOKENS // 16, 1, CONTEXT)
+    g = torch.Generator().manual_seed(2)
+    prompt = torch.randint(3, cfg.vocab_size, (PREFILL_TOKENS,), generator=g).tolist()
+    times = []
+    for i in range(warmup + steps):
+        runner.add_request("p")
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        runner.step([StepEntry("p", prompt, [PREFILL_TOKENS - 1])])
+        e1.record()
+        torch.cuda.synchronize()
+        runner.finish("p")
+        if i >= warmup:
+            times.append(e0.elapsed_time(e1))
+    del runner
+    return sorted(times)[len(times) // 2]
+
+
+def reference_arm():
+    why = ("aws-neuron/transformers-neuronx needs torch_neuronx, libneuronxla and the neuronx-cc compiler for "
+           "Trainium/Inferentia; none exists for CUDA, so its OPT path cannot run on a B200")
+    print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=OPT_6_7B["num_hidden_layers"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--skip-points", action="store_true")
+    a = ap.parse_args()
+    if a.impl == "reference":
+        return reference_arm()
+    if a.gpus != 1:
+        print("bench.py: this engine runs on one GPU; --gpus must be 1")
+        return 2
+    a.warmup = max(a.warmup, 3)
+    import torch
+    hbm_gbs, tflops, peak_src = peaks()
+    model, cfg = build(a.layers)
+    L = cfg.num_hidden_layers
+
+    clocks = ClockSampler()
+    clocks.start()
+    ms, launches, _, _ = time_decode(model, cfg, a.batch, a.steps, a.warmup)
+    clk = clocks.stop()
+    value = a.batch / (ms / 1e3)
+    e2e_ms, _, h2d, d2h = time_decode(model, cfg, a.batch, a.steps, a.warmup, use_engine=True)
+    ctx_mean = CONTEXT - a.steps / 2
+    nbytes = decode_bytes(model, cfg, a.batch, ctx_mean)
+    achieved = nbytes / (ms / 1e3) / 1e9
+    pf_ms = time_prefill(model, cfg, max(3, min(a.steps, 5)), 3)
+    pf_flops = prefill_flops(cfg, PREFILL_TOKENS)
+    points = {}
+    if not a.skip_points:
+        for b in (1, 64):
+            m, _, _, _ = time_decode(model, cfg, b, a.steps, a.warmup)
+            points[f"decode_b{b}"] = round(b / (m / 1e3), 1)
+    out = {
+        "metric": "decode tokens/s (OPT-6.7B sizes, batch 8, context 2048, 1 B200)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic (random weights N(0,0.02), uniform token ids, synthetic cache contents)",
+        "config": {"model": "OPT-6.7B sizes", "layers": L, "layers_of_model": OPT_6_7B["num_hidden_layers"],
+                   "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "head_dim": cfg.head_dim,
+                   "ffn_dim": cfg.ffn_dim, "vocab": cfg.vocab_size, "max_positions": cfg.max_position_embeddings,
+                   "global_batch": a.batch, "seq_len": CONTEXT, "page_size": 16, "parallelism": "none (1 GPU)",
+                   "l2": "inputs larger than L2 (weights read once per step)", "peaks": peak_src},
+        "e2e": {"value": round(a.batch / (e2e_ms / 1e3), 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches,
+        "clocks": clk,
+        "prefill": {"value": round(PREFILL_TOKENS / (pf_ms / 1e3), 1), "tokens": PREFILL_TOKENS, "ms": round(pf_ms, 3),
+                    "frac": round(pf_flops / (pf_ms / 1e3) / (tflops * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_gbs, "unit": "GB/s",
+                     "frac": round(achieved / hbm_gbs, 4)},
+        "points": points,
+    }
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -179,6 +179,7 @@ class StepRunner:
         ctx.decode_only = all(n == 1 for n in hb.q_len)
         ctx.max_ctx = max(c + n for c, n in zip(hb.ctx_len, hb.q_len))
         ctx.h2d_bytes = o * 4
+        self.last_h2d_bytes = o * 4
         return ctx
 
     @torch.no_grad()

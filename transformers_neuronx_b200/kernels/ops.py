@@ -18,8 +18,18 @@ class KernelError(RuntimeError):
     pass
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many of this package's kernels have been launched by this process."""
+    return _launches
+
+
 def _check(code: int, what: str) -> None:
+    global _launches
     if code == 0:
+        _launches += 1
         return
     if code < 0:
         raise KernelError(f"{what}: {_ERRORS.get(code, 'error')} (code {code})")
