@@ -72,19 +72,26 @@ def _digest(src: str) -> str:
     return h.hexdigest()[:16]
 
 
+_build_dir_cached: Optional[str] = None
+
+
 def _build_dir() -> str:
-    first = os.path.join(CSRC, "_build")
-    try:
-        os.makedirs(first, exist_ok=True)
-        probe = os.path.join(first, f".w{os.getpid()}")
-        with open(probe, "w"):
-            pass
-        os.remove(probe)
-        return first
-    except OSError:
-        alt = os.path.join(tempfile.gettempdir(), f"tnx_b200_build_{os.getuid()}")
-        os.makedirs(alt, exist_ok=True)
-        return alt
+    global _build_dir_cached
+    with _lock:
+        if _build_dir_cached is not None:
+            return _build_dir_cached
+        first = os.path.join(CSRC, "_build")
+        try:
+            os.makedirs(first, exist_ok=True)
+            fd, probe = tempfile.mkstemp(prefix=".w", dir=first)
+            os.close(fd)
+            os.remove(probe)
+            _build_dir_cached = first
+        except OSError:
+            alt = os.path.join(tempfile.gettempdir(), f"tnx_b200_build_{os.getuid()}")
+            os.makedirs(alt, exist_ok=True)
+            _build_dir_cached = alt
+        return _build_dir_cached
 
 
 def library_path(name: str) -> str:
@@ -100,11 +107,11 @@ def build(name: str, verbose: bool = True) -> str:
     """Compiles one library if its up-to-date binary is not there yet; returns its path."""
     if name not in SOURCES:
         raise KernelBuildError(f"no kernel source registered under {name!r}")
+    out = library_path(name)
     with _lock:
         lk = _build_locks.setdefault(name, threading.Lock())
     with lk:
         src = os.path.join(CSRC, SOURCES[name])
-        out = library_path(name)
         if os.path.isfile(out):
             return out
         tmp = f"{out}.{os.getpid()}.{threading.get_ident()}.tmp"
