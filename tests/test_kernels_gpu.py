@@ -121,3 +121,139 @@ def test_gemm_tc_refuses_unaligned_sizes():
     assert not o.gemm_tc_supported(a, w, out)
     with pytest.raises(o.KernelError, match="multiples of 8"):
         o.gemm_tc(a, w, out)
+
+
+# ---- attention over the paged cache ----------------------------------------------------------------
+def plain_attention(q, k, v, n_heads, n_kv, scale, first_pos, window):
+    """q [Tq, n_heads, d] at positions first_pos.., k/v [Tk, n_kv, d] -> [Tq, n_heads, d], by the
+    plain implementation's own functions."""
+    rep = n_heads // n_kv
+    qh = q.float().transpose(0, 1)
+    kh = k.float().transpose(0, 1).repeat_interleave(rep, dim=0)
+    vh = v.float().transpose(0, 1).repeat_interleave(rep, dim=0)
+    s = P.attention_scores(qh, kh, q.shape[-1], scale)
+    mask = P.causal_mask(q.shape[0], k.shape[0], first_pos, window)
+    return P.attention_context(P.masked_softmax(s, mask[None]), vh).transpose(0, 1)
+
+
+class PagedCase:
+    """Requests with contexts and portions; keys/values scattered over shuffled pages."""
+
+    def __init__(self, lens, n_heads, n_kv, d, dtype, seed=0, plant=True):
+        # lens: list of (ctx_len, q_len)
+        g = torch.Generator().manual_seed(seed)
+        self.lens, self.n_heads, self.n_kv, self.d, self.dtype = lens, n_heads, n_kv, d, dtype
+        ps = 16
+        total_pages = sum(-(-(c + q) // ps) for c, q in lens) + 3
+        perm = torch.randperm(total_pages, generator=g).tolist()
+        self.cache = torch.full((total_pages, 2, n_kv, ps, d), float("nan"), dtype=dtype)   # unwritten rows are poison
+        self.k, self.v, self.q = [], [], []
+        tables, tok_req, positions, q_start, tile_req, tile_q0, decode_rows = [], [], [], [], [], [], []
+        row = 0
+        for r, (c, ql) in enumerate(lens):
+            T = c + ql
+            k = torch.randn(T, n_kv, d, generator=g)
+            v = torch.randn(T, n_kv, d, generator=g)
+            q = torch.randn(ql, n_heads, d, generator=g)
+            if plant and T > 20:
+                # one far key (at a page's edge) that every head of the last query must find
+                far = 15 if T > 40 else 0
+                k[far] *= 0.1
+                q[-1] = k[far].repeat_interleave(n_heads // n_kv, dim=0) * 60.0
+                v[far] += 5.0
+            k, v, q = k.to(dtype), v.to(dtype), q.to(dtype)
+            pages = [perm.pop() for _ in range(-(-T // ps))]
+            for t in range(T):
+                self.cache[pages[t // ps], 0, :, t % ps] = k[t]
+                self.cache[pages[t // ps], 1, :, t % ps] = v[t]
+            tables.append(pages)
+            self.k.append(k); self.v.append(v); self.q.append(q)
+            q_start.append(row)
+            tok_req += [r] * ql
+            positions += list(range(c, c + ql))
+            if ql == 1:
+                decode_rows.append(row)
+            else:
+                for q0 in range(0, ql, 64):
+                    tile_req.append(r); tile_q0.append(q0)
+            row += ql
+        mb = max(len(t) for t in tables)
+        bt = torch.full((len(lens), mb), -1, dtype=torch.int32)
+        for r, t in enumerate(tables):
+            bt[r, :len(t)] = torch.tensor(t, dtype=torch.int32)
+        i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+        self.bt = bt.to(DEV)
+        self.tok_req, self.positions = i32(tok_req), i32(positions)
+        self.q_start, self.q_len, self.ctx_len = i32(q_start), i32([q for _, q in lens]), i32([c for c, _ in lens])
+        self.tile_req, self.tile_q0, self.decode_rows = i32(tile_req), i32(tile_q0), i32(decode_rows)
+        self.q_flat = torch.cat([q.reshape(q.shape[0], -1) for q in self.q]).to(DEV)
+        self.cache = self.cache.to(DEV)
+        self.N = row
+
+    def want(self, scale, window):
+        outs = []
+        for (c, ql), q, k, v in zip(self.lens, self.q, self.k, self.v):
+            outs.append(plain_attention(q, k, v, self.n_heads, self.n_kv, scale, c, window).reshape(ql, -1))
+        return torch.cat(outs).to(DEV)
+
+
+ATT_SHAPES = [(4, 4, 16), (3, 3, 32), (6, 2, 48), (8, 8, 64), (5, 1, 80), (4, 2, 128), (2, 2, 256)]
+
+
+@pytest.mark.parametrize("n_heads,n_kv,d", ATT_SHAPES)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [None, 37])
+def test_attention_simt(n_heads, n_kv, d, dtype, window):
+    case = PagedCase([(0, 5), (17, 1), (40, 33), (100, 1), (3, 70)], n_heads, n_kv, d, dtype, seed=d)
+    scale = 1.0 / math.sqrt(d)
+    out = torch.zeros(case.N, n_heads * d, dtype=dtype, device=DEV)
+    ops().attention_simt(case.q_flat, case.cache, case.bt, case.tok_req, case.positions, out, n_heads, scale, window or 0)
+    assert rel_err(out, case.want(scale, window)) <= (1e-5 if dtype == torch.float32 else 1e-2)
+
+
+@pytest.mark.parametrize("n_heads,n_kv,d", ATT_SHAPES)
+@pytest.mark.parametrize("window", [None, 50])
+@pytest.mark.parametrize("n_splits", [None, 1, 3, 7])
+def test_attention_decode(n_heads, n_kv, d, window, n_splits):
+    lens = [(0, 1), (15, 1), (16, 1), (17, 1), (255, 1), (256, 1), (700, 1), (63, 1)]
+    case = PagedCase(lens, n_heads, n_kv, d, torch.bfloat16, seed=d + 1)
+    scale = 0.7 / math.sqrt(d)
+    out = torch.zeros(case.N, n_heads * d, dtype=torch.bfloat16, device=DEV)
+    o = ops()
+    for _ in range(2):          # twice: the split counters must be back at zero
+        out.zero_()
+        o.attention_decode(case.q_flat, case.cache, case.bt, case.tok_req, case.positions, out, n_heads, scale,
+                           window or 0, max_kv_len=701, n_splits=n_splits)
+        assert rel_err(out, case.want(scale, window)) <= 1e-2
+
+
+def test_attention_decode_row_list():
+    """Only the rows named are computed (a mixed batch: the others belong to the prefill kernel)."""
+    lens = [(5, 1), (0, 40), (99, 1), (10, 3), (33, 1)]
+    case = PagedCase(lens, 4, 4, 64, torch.bfloat16, seed=9)
+    scale = 1.0 / 8
+    out = torch.zeros(case.N, 4 * 64, dtype=torch.bfloat16, device=DEV)
+    ops().attention_decode(case.q_flat, case.cache, case.bt, case.tok_req, case.positions, out, 4, scale, 0,
+                           rows=case.decode_rows, max_kv_len=100)
+    want = case.want(scale, None)
+    rows = case.decode_rows.long()
+    assert rel_err(out[rows], want[rows]) <= 1e-2
+    others = torch.ones(case.N, dtype=torch.bool, device=DEV)
+    others[rows] = False
+    assert float(out[others].float().abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("n_heads,n_kv,d", ATT_SHAPES)
+@pytest.mark.parametrize("window", [None, 45])
+def test_attention_prefill(n_heads, n_kv, d, window):
+    lens = [(0, 2), (0, 64), (0, 65), (30, 7), (64, 130), (15, 17), (200, 300), (5, 1)]
+    case = PagedCase(lens, n_heads, n_kv, d, torch.bfloat16, seed=d + 2)
+    scale = 1.0 / math.sqrt(d)
+    out = torch.zeros(case.N, n_heads * d, dtype=torch.bfloat16, device=DEV)
+    ops().attention_prefill(case.q_flat, case.cache, case.bt, case.tile_req, case.tile_q0, case.q_start, case.q_len,
+                            case.ctx_len, out, n_heads, scale, window or 0)
+    want = case.want(scale, window)
+    keep = torch.ones(case.N, dtype=torch.bool, device=DEV)
+    keep[case.decode_rows.long()] = False          # the single-row request is not in the tile list
+    assert rel_err(out[keep], want[keep]) <= 1.5e-2
+    assert float(out[~keep].float().abs().max()) == 0.0

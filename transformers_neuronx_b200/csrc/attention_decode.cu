@@ -1,0 +1,233 @@
+// Decode attention over the paged bfloat16 cache: one query token per request, the keys and values
+// of its request streamed from the pages named by its block table.  Memory-bound: every key and
+// value of the live requests is read once per layer and step.
+//
+//   s_j = scale * <q, k_j>  (32-bit),  out = sum_j exp(s_j - max) v_j / sum_j exp(s_j - max)
+//
+// Grid (heads, rows, splits): a CTA takes one (row, head) and one contiguous range of pages; its
+// four warps take pages of the range in turn and keep an online softmax each.  A lane owns eight
+// consecutive dims of the head (one 16-byte load per key) of some of the keys of a page, so a page
+// of 16 keys x head_dim is read with fully used 16-byte loads.  The warps' states are merged in
+// shared memory.  With more than one split the CTA writes its (max, sum, accumulator) to scratch
+// memory, and the CTA of a (row, head) that finishes last merges the splits in split order.
+#include "common.cuh"
+
+namespace {
+
+constexpr int WARPS = 4;
+constexpr int PAGE = 16;
+
+struct DecodeParams {
+    const bf16* q; int q_stride;
+    const bf16* cache;
+    const int* block_tables; int bt_stride;
+    const int* rows;                 // rows of the batch that are decode tokens (null: all rows)
+    const int* token_request;
+    const int* positions;
+    bf16* out; int out_stride;
+    int n_heads, n_kv_heads, head_dim;
+    int window;
+    float scale;
+    int n_splits, pages_per_split;
+    float* scratch;                  // [rows][heads][splits][head_dim + 2]
+    int* counters;                   // [rows][heads], zero between calls
+};
+
+// LPK lanes share one key (each 8 dims); KPL = 32 / LPK keys are read per warp-wide load.
+template <int LPK>
+__global__ void __launch_bounds__(WARPS * 32)
+attention_decode_kernel(const DecodeParams p) {
+    constexpr int KPL = 32 / LPK;
+    constexpr int LOADS = PAGE / KPL;          // warp-wide loads per page (LPK = 32: 16, LPK = 2: 1)
+    __shared__ float sm_m[WARPS], sm_l[WARPS];
+    __shared__ float sm_acc[WARPS][LPK * 8];
+    __shared__ int last_flag;
+
+    const int h = blockIdx.x, ri = blockIdx.y, split = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = p.rows ? p.rows[ri] : ri;
+    const int req = p.token_request[row];
+    if (req < 0) return;                                        // a padded row of a captured batch
+    const int pos = p.positions[row];
+    const int kv_len = pos + 1;
+    const int first_key = (p.window > 0 && kv_len > p.window) ? kv_len - p.window : 0;
+    const int d = p.head_dim;
+    const int kvh = h / (p.n_heads / p.n_kv_heads);
+    const int sub = lane % LPK;                                  // which 8 dims
+    const int kgrp = lane / LPK;                                 // which key of a load
+    const bool dim_ok = sub * 8 < d;
+    const int* bt = p.block_tables + (size_t)req * p.bt_stride;
+
+    float q[8];
+    {
+        const bf16* qrow = p.q + (size_t)row * p.q_stride + (size_t)h * d + sub * 8;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) q[i] = dim_ok ? __bfloat162float(qrow[i]) * p.scale : 0.f;
+    }
+    float m = -INFINITY, l = 0.f, acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+
+    const int n_pages = (kv_len + PAGE - 1) / PAGE;
+    const int page_lo = max(split * p.pages_per_split, first_key / PAGE);
+    const int page_hi = min(n_pages, (split + 1) * p.pages_per_split);
+    const size_t head_block = (size_t)PAGE * d;
+
+    for (int pg = page_lo + warp; pg < page_hi; pg += WARPS) {
+        const int page = bt[pg];
+        const bf16* kbase = p.cache + (((size_t)page * 2 + 0) * p.n_kv_heads + kvh) * head_block;
+        const bf16* vbase = p.cache + (((size_t)page * 2 + 1) * p.n_kv_heads + kvh) * head_block;
+        uint4 kreg[LOADS], vreg[LOADS];
+#pragma unroll
+        for (int i = 0; i < LOADS; ++i) {
+            const int key = i * KPL + kgrp;
+            kreg[i] = dim_ok ? __ldg((const uint4*)(kbase + (size_t)key * d + sub * 8)) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int i = 0; i < LOADS; ++i) {
+            const int key = i * KPL + kgrp;
+            vreg[i] = dim_ok ? __ldg((const uint4*)(vbase + (size_t)key * d + sub * 8)) : make_uint4(0, 0, 0, 0);
+        }
+        float s[LOADS];
+        float page_max = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < LOADS; ++i) {
+            const __nv_bfloat162* kk = (const __nv_bfloat162*)&kreg[i];
+            float dot = 0.f;
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                const float2 f = __bfloat1622float2(kk[t]);
+                dot = fmaf(q[2 * t], f.x, dot);
+                dot = fmaf(q[2 * t + 1], f.y, dot);
+            }
+#pragma unroll
+            for (int o = LPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+            const int j = pg * PAGE + i * KPL + kgrp;
+            s[i] = (j >= first_key && j < kv_len) ? dot : -INFINITY;
+            page_max = fmaxf(page_max, s[i]);
+        }
+#pragma unroll
+        for (int o = 16; o >= LPK; o >>= 1) page_max = fmaxf(page_max, __shfl_xor_sync(0xffffffffu, page_max, o));
+        if (page_max == -INFINITY) continue;                     // every key of the page masked (warp-uniform)
+        const float m_new = fmaxf(m, page_max);
+        const float corr = (m == -INFINITY) ? 0.f : __expf(m - m_new);
+        l *= corr;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] *= corr;
+        m = m_new;
+#pragma unroll
+        for (int i = 0; i < LOADS; ++i) {
+            const float pj = (s[i] == -INFINITY) ? 0.f : __expf(s[i] - m);
+            l += pj;
+            const __nv_bfloat162* vv = (const __nv_bfloat162*)&vreg[i];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                const float2 f = __bfloat1622float2(vv[t]);
+                acc[2 * t] = fmaf(pj, f.x, acc[2 * t]);
+                acc[2 * t + 1] = fmaf(pj, f.y, acc[2 * t + 1]);
+            }
+        }
+    }
+    // lanes with the same dims but other keys -> one accumulator per dim slice; l counted once per key
+#pragma unroll
+    for (int o = 16; o >= LPK; o >>= 1) {
+        l += __shfl_xor_sync(0xffffffffu, l, o);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], o);
+    }
+    if (lane < LPK) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sm_acc[warp][lane * 8 + i] = acc[i];
+    }
+    if (lane == 0) { sm_m[warp] = m; sm_l[warp] = l; }
+    __syncthreads();
+
+    // merge the warps
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) M = fmaxf(M, sm_m[w]);
+    float L = 0.f, f[WARPS];
+    const int t = threadIdx.x;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) {
+        f[w] = (sm_m[w] == -INFINITY) ? 0.f : __expf(sm_m[w] - M);
+        L += sm_l[w] * f[w];
+    }
+    for (int t2 = t; t2 < d; t2 += WARPS * 32) {                  // head_dim may exceed the block size
+        float o_val = 0.f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) o_val += sm_acc[w][t2] * f[w];
+        if (p.n_splits == 1) {
+            p.out[(size_t)row * p.out_stride + (size_t)h * d + t2] = __float2bfloat16_rn(o_val / L);
+        } else {
+            float* dst = p.scratch + (((size_t)ri * p.n_heads + h) * p.n_splits + split) * (d + 2);
+            dst[2 + t2] = o_val;
+        }
+    }
+    if (p.n_splits == 1) return;
+    if (t == 0) {
+        float* dst = p.scratch + (((size_t)ri * p.n_heads + h) * p.n_splits + split) * (d + 2);
+        dst[0] = M; dst[1] = L;
+    }
+    __threadfence();
+    __syncthreads();
+    if (t == 0) {
+        int* c = p.counters + (size_t)ri * p.n_heads + h;
+        const int prev = atomicAdd(c, 1);
+        last_flag = (prev == p.n_splits - 1);
+        if (last_flag) *c = 0;
+    }
+    __syncthreads();
+    if (!last_flag) return;
+    __threadfence();
+    const float* base = p.scratch + ((size_t)ri * p.n_heads + h) * p.n_splits * (d + 2);
+    float GM = -INFINITY;
+    for (int s2 = 0; s2 < p.n_splits; ++s2) GM = fmaxf(GM, __ldcg(base + (size_t)s2 * (d + 2)));
+    float GL = 0.f;
+    for (int s2 = 0; s2 < p.n_splits; ++s2) {
+        const float ms = __ldcg(base + (size_t)s2 * (d + 2));
+        GL += (ms == -INFINITY) ? 0.f : __ldcg(base + (size_t)s2 * (d + 2) + 1) * __expf(ms - GM);
+    }
+    for (int t2 = t; t2 < d; t2 += WARPS * 32) {
+        float o = 0.f;
+        for (int s2 = 0; s2 < p.n_splits; ++s2) {
+            const float ms = __ldcg(base + (size_t)s2 * (d + 2));
+            if (ms != -INFINITY) o += __ldcg(base + (size_t)s2 * (d + 2) + 2 + t2) * __expf(ms - GM);
+        }
+        p.out[(size_t)row * p.out_stride + (size_t)h * d + t2] = __float2bfloat16_rn(o / GL);
+    }
+}
+
+}  // namespace
+
+// Scratch floats and counters needed for n_rows decode rows with n_splits splits.
+TNX_EXPORT long long tnx_attention_decode_scratch_floats(int n_rows, int n_heads, int head_dim, int n_splits) {
+    return n_splits > 1 ? (long long)n_rows * n_heads * n_splits * (head_dim + 2) : 0;
+}
+
+TNX_EXPORT int tnx_attention_decode(const void* q, int q_stride, const void* cache, const int* block_tables,
+                                    int bt_stride, const int* rows, const int* token_request, const int* positions,
+                                    void* out, int out_stride, int n_rows, int n_heads, int n_kv_heads, int head_dim,
+                                    int page_size, int window, float scale, int n_splits, int pages_per_split,
+                                    float* scratch, int* counters, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (page_size != PAGE || head_dim % 16 || head_dim < 16 || head_dim > 256 || n_kv_heads <= 0 ||
+        n_heads % n_kv_heads || q_stride % 8 || ((uintptr_t)q & 15) || ((uintptr_t)cache & 15))
+        return TNX_ERR_UNSUPPORTED;
+    if (n_splits < 1 || pages_per_split < 1) return TNX_ERR_BAD_ARG;
+    if (n_splits > 1 && (!scratch || !counters)) return TNX_ERR_BAD_ARG;
+    DecodeParams p;
+    p.q = (const bf16*)q; p.q_stride = q_stride; p.cache = (const bf16*)cache;
+    p.block_tables = block_tables; p.bt_stride = bt_stride; p.rows = rows; p.token_request = token_request;
+    p.positions = positions; p.out = (bf16*)out; p.out_stride = out_stride;
+    p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.head_dim = head_dim; p.window = window; p.scale = scale;
+    p.n_splits = n_splits; p.pages_per_split = pages_per_split; p.scratch = scratch; p.counters = counters;
+    dim3 grid(n_heads, n_rows, n_splits);
+    const int chunks = head_dim / 8;
+    if (chunks <= 2) attention_decode_kernel<2><<<grid, WARPS * 32, 0, stream>>>(p);
+    else if (chunks <= 4) attention_decode_kernel<4><<<grid, WARPS * 32, 0, stream>>>(p);
+    else if (chunks <= 8) attention_decode_kernel<8><<<grid, WARPS * 32, 0, stream>>>(p);
+    else if (chunks <= 16) attention_decode_kernel<16><<<grid, WARPS * 32, 0, stream>>>(p);
+    else attention_decode_kernel<32><<<grid, WARPS * 32, 0, stream>>>(p);
+    return tnx_launch_status();
+}

@@ -134,6 +134,15 @@ class StepRunner:
         parts = [tok.astype(np.int32), pos, treq,
                  np.asarray(hb.q_start, np.int32), np.asarray(hb.q_len, np.int32), np.asarray(hb.ctx_len, np.int32),
                  np.asarray(hb.slots, np.int32), np.asarray(logit_rows, np.int32)]
+        # work lists of the attention kernels: 64-row tiles of portions, and rows that decode
+        tile_req, tile_q0, decode_rows = [], [], []
+        for r in range(R):
+            if hb.q_len[r] == 1:
+                decode_rows.append(hb.q_start[r])
+            else:
+                for q0 in range(0, hb.q_len[r], 64):
+                    tile_req.append(r); tile_q0.append(q0)
+        parts += [np.asarray(tile_req, np.int32), np.asarray(tile_q0, np.int32), np.asarray(decode_rows, np.int32)]
         n_fixed = len(parts)
         max_blocks = []
         for g in range(self.n_groups):
@@ -170,6 +179,9 @@ class StepRunner:
         ctx.token_ids, ctx.positions, ctx.token_request = sec(0), sec(1), sec(2)
         ctx.q_start, ctx.q_len, ctx.ctx_len, ctx.state_slots = sec(3), sec(4), sec(5), sec(6)
         ctx.logit_rows = sec(7)
+        ctx.tile_req, ctx.tile_q0, ctx.decode_rows = sec(8), sec(9), sec(10)
+        ctx.n_prefill_tiles, ctx.n_decode_rows = len(tile_req), len(decode_rows)
+        ctx.max_decode_ctx = max([hb.ctx_len[r] + 1 for r in range(R) if hb.q_len[r] == 1], default=0)
         for g in range(self.n_groups):
             ctx.block_tables.append(sec(n_fixed + 2 * g).view(R, max_blocks[g]))
             ctx.slot_mapping.append(sec(n_fixed + 2 * g + 1))

@@ -37,6 +37,8 @@ SOURCES: Dict[str, str] = {
     "attention_simt": "attention_simt.cu",
     "sampling": "sampling.cu",
     "gemm_tc": "gemm_tc.cu",
+    "attention_decode": "attention_decode.cu",
+    "attention_prefill": "attention_prefill.cu",
 }
 
 _loaded: Dict[str, ctypes.CDLL] = {}

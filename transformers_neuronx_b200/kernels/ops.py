@@ -313,6 +313,82 @@ def gemm_tc(a, w, out, bias=None, residual=None, relu=False, splits=None):
                            n_splits, _p(scratch), _p(st["counters"]), _p(st["err"]), _stream()), "gemm_tc")
 
 
+def attention_decode(q, cache, block_tables, token_request, positions, out, n_heads, scale, window=0, rows=None,
+                     n_rows=None, max_kv_len=None, n_splits=None):
+    """One query token per row over the paged bfloat16 cache.  `rows` (int32) names the rows of q
+    that are decode tokens (None: all); max_kv_len bounds their contexts (for the split plan)."""
+    lib = _build.load("attention_decode")
+    _need(cache, "cache", torch.bfloat16, 5)
+    N, width, q_stride = _rows_2d(q, "q")
+    No, wo, out_stride = _rows_2d(out, "out")
+    _, _, n_kv, ps, d = cache.shape
+    if width != n_heads * d or (No, wo) != (N, width) or q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("q/out do not fit the cache's head size or dtype")
+    _need(block_tables, "block_tables", torch.int32, 2)
+    _need(token_request, "token_request", torch.int32, 1)
+    _need(positions, "positions", torch.int32, 1)
+    if rows is not None:
+        _need(rows, "rows", torch.int32, 1)
+    R = int(n_rows) if n_rows is not None else (rows.shape[0] if rows is not None else N)
+    st = _state(q.device)
+    max_pages = max(1, -(-(int(max_kv_len) if max_kv_len is not None else block_tables.shape[1] * ps) // ps))
+    if n_splits is None:
+        n_splits = max(1, min(-(-2 * st["sms"] // max(1, R * n_heads)), max(1, max_pages // 4), 32))
+    n_splits = max(1, min(int(n_splits), max_pages))
+    pps = -(-max_pages // n_splits)
+    n_splits = -(-max_pages // pps)
+    scratch = None
+    if n_splits > 1:
+        need = R * n_heads * n_splits * (d + 2)
+        if st.get("att_scratch") is None or st["att_scratch"].numel() < need:
+            st["att_scratch"] = torch.empty(max(need, 1 << 18), dtype=torch.float32, device=q.device)
+        if st.get("att_counters") is None or st["att_counters"].numel() < R * n_heads:
+            st["att_counters"] = torch.zeros(max(R * n_heads, 4096), dtype=torch.int32, device=q.device)
+        scratch = st["att_scratch"]
+    _check(lib.tnx_attention_decode(_p(q), c_int(q_stride), _p(cache), _p(block_tables), c_int(block_tables.stride(0)),
+                                    _p(rows), _p(token_request), _p(positions), _p(out), c_int(out_stride), c_int(R),
+                                    c_int(n_heads), c_int(n_kv), c_int(d), c_int(ps), c_int(window or 0), c_float(scale),
+                                    c_int(n_splits), c_int(pps), _p(scratch), _p(st.get("att_counters")), _stream()),
+           "attention_decode")
+
+
+def attention_prefill(q, cache, block_tables, tile_req, tile_q0, q_start, q_len, ctx_len, out, n_heads, scale,
+                      window=0, n_items=None):
+    """Causal attention of prompt portions: work items (request, first row of a 64-row tile)."""
+    lib = _build.load("attention_prefill")
+    _need(cache, "cache", torch.bfloat16, 5)
+    N, width, q_stride = _rows_2d(q, "q")
+    No, wo, out_stride = _rows_2d(out, "out")
+    _, _, n_kv, ps, d = cache.shape
+    if width != n_heads * d or (No, wo) != (N, width) or q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("q/out do not fit the cache's head size or dtype")
+    for t, nm in ((block_tables, "block_tables"), (tile_req, "tile_req"), (tile_q0, "tile_q0"), (q_start, "q_start"),
+                  (q_len, "q_len"), (ctx_len, "ctx_len")):
+        _need(t, nm, torch.int32, 2 if nm == "block_tables" else 1)
+    n = int(n_items) if n_items is not None else tile_req.shape[0]
+    _check(lib.tnx_attention_prefill(_p(q), c_int(q_stride), _p(cache), _p(block_tables), c_int(block_tables.stride(0)),
+                                     _p(tile_req), _p(tile_q0), _p(q_start), _p(q_len), _p(ctx_len), _p(out),
+                                     c_int(out_stride), c_int(n), c_int(n_heads), c_int(n_kv), c_int(d), c_int(ps),
+                                     c_int(window or 0), c_float(scale), _stream()), "attention_prefill")
+
+
+def _attention_bf16(ctx, group, q, cache, out, n_heads, scale, window):
+    if cache.shape[3] != 16 or q.stride(0) % 8 or q.data_ptr() % 16:
+        return False
+    bt = ctx.block_tables[group]
+    if ctx.n_prefill_tiles:
+        attention_prefill(q, cache, bt, ctx.tile_req, ctx.tile_q0, ctx.q_start, ctx.q_len, ctx.ctx_len, out,
+                          n_heads, scale, window, n_items=ctx.n_prefill_tiles)
+    if ctx.n_decode_rows:
+        attention_decode(q, cache, bt, ctx.token_request, ctx.positions, out, n_heads, scale, window,
+                         rows=None if ctx.decode_only else ctx.decode_rows, n_rows=ctx.n_decode_rows,
+                         max_kv_len=ctx.max_decode_ctx)
+    return True
+
+
+_attention_impls["bf16"] = _attention_bf16
+
+
 def attention(ctx, group, q, cache, out, n_heads, scale, window=0):
     """Attention of this step's queries over the cache of the running schedule entry.  32-bit
     caches, and head sizes or windows that the bfloat16 kernels do not take, run on the CUDA-core

@@ -49,6 +49,12 @@ class StepContext:
         self.page_size = 0
         self.decode_only = False              # every request has exactly one row
         self.max_ctx = 0                      # longest context (after this step) in the batch
+        self.tile_req = None                  # [tiles] request of each 64-row tile of a portion
+        self.tile_q0 = None                   # [tiles] its first row within the portion
+        self.decode_rows = None               # rows of requests that have exactly one row
+        self.n_prefill_tiles = 0
+        self.n_decode_rows = 0
+        self.max_decode_ctx = 0
 
     def empty(self, rows, cols, dtype=None) -> torch.Tensor:
         return torch.empty((rows, cols), dtype=dtype or self.act_dtype, device=self.device)
