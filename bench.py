@@ -214,6 +214,8 @@ def main():
     ap.add_argument("--layers", type=int, default=OPT_6_7B["num_hidden_layers"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--only", default=None, choices=["decode", "prefill"],
+                    help="run just this part and print its time (for profiling a small case)")
     a = ap.parse_args()
     if a.impl == "reference":
         return reference_arm()
@@ -226,6 +228,14 @@ def main():
     model, cfg = build(a.layers)
     L = cfg.num_hidden_layers
 
+    if a.only == "decode":
+        ms, launches, _, _ = time_decode(model, cfg, a.batch, a.steps, a.warmup)
+        print(json.dumps({"only": "decode", "batch": a.batch, "layers": L, "ms_per_step": round(ms, 4), "launches": launches}))
+        return 0
+    if a.only == "prefill":
+        ms = time_prefill(model, cfg, a.steps, a.warmup)
+        print(json.dumps({"only": "prefill", "tokens": PREFILL_TOKENS, "layers": L, "ms": round(ms, 4)}))
+        return 0
     clocks = ClockSampler()
     clocks.start()
     ms, launches, _, _ = time_decode(model, cfg, a.batch, a.steps, a.warmup)

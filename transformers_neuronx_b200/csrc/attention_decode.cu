@@ -117,8 +117,10 @@ attention_decode_kernel(const DecodeParams p) {
         m = m_new;
 #pragma unroll
         for (int i = 0; i < LOADS; ++i) {
-            const float pj = (s[i] == -INFINITY) ? 0.f : __expf(s[i] - m);
+            const bool live = s[i] != -INFINITY;
+            const float pj = live ? __expf(s[i] - m) : 0.f;
             l += pj;
+            if (!live) vreg[i] = make_uint4(0, 0, 0, 0);          // rows never written may hold anything, NaN included
             const __nv_bfloat162* vv = (const __nv_bfloat162*)&vreg[i];
 #pragma unroll
             for (int t = 0; t < 4; ++t) {
