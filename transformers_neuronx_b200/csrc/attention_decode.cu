@@ -233,3 +233,94 @@ TNX_EXPORT int tnx_attention_decode(const void* q, int q_stride, const void* cac
     else attention_decode_kernel<32><<<grid, WARPS * 32, 0, stream>>>(p);
     return tnx_launch_status();
 }
+
+// ---------------------------------------------------------------------------------------------------
+// Entry point that allocates nothing (declared in attention_decode_noalloc.h).
+//
+// Same kernel as tnx_attention_decode; the split partials and the per-(row, head) counters live in
+// file-scope device arrays of fixed size instead of buffers that the caller allocates.  Every GPU
+// that loads this library holds these arrays (about 4.1 MB) until the process exits.
+// ---------------------------------------------------------------------------------------------------
+#include <cstdio>
+#include <mutex>
+
+#include "attention_decode_noalloc.h"
+
+namespace {
+static __device__ __align__(256) float g_noalloc_partials[TNX_NOALLOC_MAX_FLOATS];
+static __device__ __align__(256) int g_noalloc_counters[TNX_NOALLOC_MAX_COUNTERS];
+
+constexpr int MAX_DEVICES = 64;
+struct NoAllocDevice { bool ready; float* partials; int* counters; };
+NoAllocDevice g_noalloc_dev[MAX_DEVICES];
+std::mutex g_noalloc_mu;
+thread_local char g_noalloc_msg[512] = "";
+
+// In host code the arrays' names are host-side stand-ins, not device addresses: the addresses
+// that a kernel may use are asked for once per device, with that device current.
+int noalloc_setup(int dev, float** partials, int** counters) {
+    std::lock_guard<std::mutex> g(g_noalloc_mu);
+    NoAllocDevice& s = g_noalloc_dev[dev];
+    if (!s.ready) {
+        void *pp = nullptr, *pc = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&pp, g_noalloc_partials);
+        if (e != cudaSuccess) return (int)e;
+        e = cudaGetSymbolAddress(&pc, g_noalloc_counters);
+        if (e != cudaSuccess) return (int)e;
+        s.partials = (float*)pp; s.counters = (int*)pc; s.ready = true;
+    }
+    *partials = s.partials; *counters = s.counters;
+    return 0;
+}
+}  // namespace
+
+TNX_EXPORT const char* tnx_attention_decode_noalloc_last_error() { return g_noalloc_msg; }
+
+TNX_EXPORT int tnx_attention_decode_noalloc(const void* q, int q_stride, const void* cache, const int* block_tables,
+                                            int bt_stride, const int* rows, const int* token_request,
+                                            const int* positions, void* out, int out_stride, int n_rows, int n_heads,
+                                            int n_kv_heads, int head_dim, int page_size, int window, float scale,
+                                            int n_splits, int pages_per_split, cudaStream_t stream) {
+    g_noalloc_msg[0] = 0;
+    if (n_rows <= 0) return 0;
+    if (n_splits < 1 || n_heads <= 0 || head_dim <= 0) {
+        snprintf(g_noalloc_msg, sizeof g_noalloc_msg, "n_splits, n_heads and head_dim must be positive");
+        return TNX_ERR_BAD_ARG;
+    }
+    const long long floats = tnx_attention_decode_scratch_floats(n_rows, n_heads, head_dim, n_splits);
+    const long long counters = (long long)n_rows * n_heads;
+    if (floats > TNX_NOALLOC_MAX_FLOATS || (n_splits > 1 && counters > TNX_NOALLOC_MAX_COUNTERS)) {
+        snprintf(g_noalloc_msg, sizeof g_noalloc_msg,
+                 "n_rows %d x n_heads %d x n_splits %d x (head_dim %d + 2) = %lld floats and %lld counters exceed the "
+                 "built-in scratch of %d floats and %d counters; use fewer splits or tnx_attention_decode with "
+                 "scratch of your own", n_rows, n_heads, n_splits, head_dim, floats, counters,
+                 TNX_NOALLOC_MAX_FLOATS, TNX_NOALLOC_MAX_COUNTERS);
+        return TNX_ERR_UNSUPPORTED;
+    }
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= MAX_DEVICES) {
+        snprintf(g_noalloc_msg, sizeof g_noalloc_msg, "device index %d is beyond the %d this library tracks", dev, MAX_DEVICES);
+        return TNX_ERR_UNSUPPORTED;
+    }
+    float* partials = nullptr;
+    int* ctrs = nullptr;
+    const int rc = noalloc_setup(dev, &partials, &ctrs);
+    if (rc != 0) {
+        snprintf(g_noalloc_msg, sizeof g_noalloc_msg, "cudaGetSymbolAddress failed with CUDA error %d", rc);
+        return rc;
+    }
+    if (n_splits > 1) {
+        // The arrays keep what the last call left; the counters must start at zero.
+        e = cudaMemsetAsync(ctrs, 0, (size_t)counters * sizeof(int), stream);
+        if (e != cudaSuccess) return (int)e;
+    }
+    const int r = tnx_attention_decode(q, q_stride, cache, block_tables, bt_stride, rows, token_request, positions, out,
+                                       out_stride, n_rows, n_heads, n_kv_heads, head_dim, page_size, window, scale,
+                                       n_splits, pages_per_split, partials, ctrs, stream);
+    if (r == TNX_ERR_UNSUPPORTED)
+        snprintf(g_noalloc_msg, sizeof g_noalloc_msg, "sizes refused: page_size must be 16, head_dim a multiple of 16 "
+                 "up to 256, q rows 16-byte aligned");
+    return r;
+}
