@@ -1,0 +1,162 @@
+"""The engine above the step function: greedy generation through the Python entry point, long
+decoding, the first tokens of a sequence, the scheduler with real pages (preemption), temperature
+sampling, the static-batch forward, and the command line."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from helpers import TOLERANCE, TinyModel
+from plain import opt_plain as P
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module", params=["A", "B"])
+def tiny(request):
+    return TinyModel(request.param, seed=21)
+
+
+def _engine(tiny, dtype, **kw):
+    from transformers_neuronx_b200.config import EngineConfig
+    from transformers_neuronx_b200.engine import LLMEngine, load_model
+    model, cfg = load_model(tiny.folder, dtype, verbose=False)
+    return LLMEngine(model, EngineConfig(dtype=dtype, **kw), eos_token_id=cfg.eos_token_id)
+
+
+def _plain_greedy_with_margin(tiny, prompt, n_new):
+    """Greedy continuation by the plain implementation, with the gap between the two best logits at
+    every step (a gap below the bf16 tolerance makes the token a legitimate tie)."""
+    ids, toks, gaps = list(prompt), [], []
+    for _ in range(n_new):
+        lg = tiny.plain_logits(ids)[-1]
+        top = torch.topk(lg, 2).values
+        toks.append(int(lg.argmax())); gaps.append(float(top[0] - top[1]) / float(lg.abs().max()))
+        ids.append(toks[-1])
+    return toks, gaps
+
+
+def _assert_greedy_equal(tiny, dtype, prompt, got, n_new):
+    want, gaps = _plain_greedy_with_margin(tiny, prompt, n_new)
+    for i, (g, w) in enumerate(zip(got, want)):
+        if g != w:
+            assert gaps[i] <= 2 * TOLERANCE[dtype], f"{dtype}: token {i} is {g}, plain {w}, gap {gaps[i]:.2e}"
+            return          # after a legitimate tie the sequences differ
+    assert len(got) == n_new
+
+
+@pytest.mark.parametrize("amp", ["f32", "bf16"])
+def test_greedy_through_the_entry_point(tiny, amp):
+    from transformers_neuronx_b200.opt.model import OPTForSampling
+    n_pos = 64
+    model = OPTForSampling.from_pretrained(tiny.folder, batch_size=3, amp=amp, n_positions=n_pos)
+    model.to_neuron()
+    prompts = [tiny.random_ids(12, seed=s) for s in (1, 2, 3)]
+    out = model.sample(torch.tensor(prompts), sequence_length=40, top_k=1)
+    assert out.shape == (3, 40) and out[:, :12].tolist() == prompts
+    dtype = "float32" if amp == "f32" else "bfloat16"
+    eos = tiny.cfg.eos_token_id
+    for row, prompt in zip(out.tolist(), prompts):
+        assert eos not in row[12:]                          # sample() never draws the end-of-sequence token
+        want, _ = _plain_greedy_with_margin(tiny, prompt, 28)
+        if eos not in want:
+            _assert_greedy_equal(tiny, dtype, prompt, row[12:], 28)
+    # left padding through start_ids: row 1 starts two places later
+    padded = [prompts[0], [tiny.cfg.pad_token_id] * 2 + prompts[1][:10]]
+    out2 = model.sample(torch.tensor(padded), sequence_length=20, start_ids=torch.tensor([0, 2]), top_k=1)
+    want, _ = _plain_greedy_with_margin(tiny, prompts[1][:10], 8)
+    if eos not in want:
+        _assert_greedy_equal(tiny, dtype, prompts[1][:10], out2[1, 12:].tolist(), 8)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(tiny, dtype):
+    """One token of prompt, then decoding to the model's full length: every page edge is crossed."""
+    eng = _engine(tiny, dtype, max_num_seqs=2)
+    n_new = tiny.cfg.max_position_embeddings - 1
+    prompt = [tiny.cfg.bos_token_id]
+    got = eng.generate([prompt], n_new, stop_on_eos=False)[0]
+    assert len(got) == n_new
+    _assert_greedy_equal(tiny, dtype, prompt, got, n_new)
+    assert eng.runner.cache.free_pages() == [eng.runner.cache.pools[0].num_pages]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_first_tokens_of_a_sequence(tiny, dtype):
+    """Logits at positions 0, 1, 2 (one key, two keys, ...) through forward(), fed one by one."""
+    from transformers_neuronx_b200.opt.model import OPTForSampling
+    amp = "f32" if dtype == "float32" else "bf16"
+    model = OPTForSampling.from_pretrained(tiny.folder, batch_size=2, amp=amp, n_positions=32).to_neuron()
+    ids = [tiny.random_ids(5, seed=8), tiny.random_ids(5, seed=9)]
+    t = torch.tensor(ids)
+    logits = [model.forward(t[:, :1])]
+    for p in range(1, 5):
+        logits.append(model(t[:, p:p + 1], torch.tensor([p]), None))
+    for b in range(2):
+        plain = tiny.plain_logits(ids[b])
+        for p in range(5):
+            err = float((logits[p][b] - plain[p]).abs().max()) / float(plain[p].abs().max())
+            assert err <= TOLERANCE[dtype], f"position {p}: {err:.2e}"
+    whole = model.forward(t)                                 # a new batch of whole prompts
+    for b in range(2):
+        plain = tiny.plain_logits(ids[b])[-1]
+        assert float((whole[b] - plain).abs().max()) / float(plain.abs().max()) <= TOLERANCE[dtype]
+    model.reset()
+    assert model.engine.runner.cache.live_requests() == []
+
+
+def test_scheduler_on_the_gpu_with_preemption(tiny):
+    """So few pages that running requests are preempted and computed again: the tokens that come
+    out are those of an engine with room for everything."""
+    prompts = [tiny.random_ids(n, seed=40 + i) for i, n in enumerate([30, 9, 25, 14, 40, 5])]
+    n_new = 40
+    roomy = _engine(tiny, "float32", max_num_seqs=8, max_batch_tokens=64)
+    want = roomy.generate(prompts, n_new, stop_on_eos=False)
+    tight = _engine(tiny, "float32", max_num_seqs=4, max_batch_tokens=24, num_pages=12)
+    got = tight.generate(prompts, n_new, stop_on_eos=False)
+    assert tight.stats["preemptions"] > 0, "the pool was meant to be too small"
+    assert got == want
+    assert tight.runner.cache.free_pages() == [12] and tight.runner.cache.pools[0].reuse_count > 0
+    tight.runner.cache.check()
+
+
+def test_temperature_sampling_is_seeded(tiny):
+    from transformers_neuronx_b200.engine import SamplingParams
+    eng = _engine(tiny, "bfloat16", max_num_seqs=4)
+    prompts = [tiny.random_ids(10, seed=s) for s in (1, 2)]
+    ps = [SamplingParams(temperature=0.8, top_k=50, seed=7), SamplingParams(temperature=0.8, top_p=0.9, seed=8)]
+    a = eng.generate(prompts, 32, ps, stop_on_eos=False)
+    b = eng.generate(prompts, 32, ps, stop_on_eos=False)
+    c = eng.generate(prompts, 32, [SamplingParams(temperature=0.8, top_k=50, seed=9)] * 2, stop_on_eos=False)
+    assert a == b and a != c
+    greedy = eng.generate(prompts, 32, None, stop_on_eos=False)
+    assert greedy != a
+
+
+def test_eos_stops_a_request(tiny):
+    eng = _engine(tiny, "float32", max_num_seqs=2)
+    prompt = tiny.random_ids(8, seed=3)
+    first = eng.generate([prompt], 5, stop_on_eos=False)[0]
+    eng.eos_token_id = first[2]                               # pretend the third new token ends the sequence
+    out = eng.generate([prompt], 5, stop_on_eos=True)[0]
+    assert out == first[:3]
+
+
+def test_command_line_save_and_run(tmp_path):
+    cfg = tmp_path / "cfg.json"
+    import json
+    from helpers import CONFIG_A
+    cfg.write_text(json.dumps(CONFIG_A))
+    folder = tmp_path / "model"
+    demo = os.path.join(ROOT, "bin", "opt_demo")
+    r = subprocess.run([sys.executable, demo, "--amp", "bf16", "save", str(folder), "--random", "--config", str(cfg)],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-1500:]
+    assert sorted(os.listdir(folder)) == ["config.json", "model.safetensors"]
+    r = subprocess.run([sys.executable, demo, "--amp", "bf16", "run", str(folder), "--batch_size", "2", "--n_positions", "24",
+                        "--print_latency"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-1500:]
+    assert "generated_sequence=" in r.stdout and "Latency:" in r.stdout

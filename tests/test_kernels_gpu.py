@@ -257,3 +257,117 @@ def test_attention_prefill(n_heads, n_kv, d, window):
     keep[case.decode_rows.long()] = False          # the single-row request is not in the tile list
     assert rel_err(out[keep], want[keep]) <= 1.5e-2
     assert float(out[~keep].float().abs().max()) == 0.0
+
+
+# ---- norms, embedding, cache append, sampling -----------------------------------------------------------
+@pytest.mark.parametrize("rows,H", [(1, 16), (5, 96), (33, 1000), (4, 4096), (2, 12288)])
+@pytest.mark.parametrize("affine", [True, False])
+def test_layer_norm(rows, H, affine):
+    g = torch.Generator().manual_seed(H)
+    x = (torch.randn(rows, H, generator=g) * 3 + 1.5).to(DEV)
+    w = torch.randn(H, generator=g).to(DEV) if affine else None
+    b = torch.randn(H, generator=g).to(DEV) if affine else None
+    for eps in (1e-5, 1e-2):
+        want = P.layer_norm(x.cpu(), None if w is None else w.cpu(), None if b is None else b.cpu(), eps).to(DEV)
+        o32 = torch.empty(rows, H, device=DEV)
+        ob = torch.empty(rows, H, dtype=torch.bfloat16, device=DEV)
+        ops().layer_norm(x, w, b, eps, out_f32=o32, out_act=ob)
+        assert rel_err(o32, want) <= 1e-5
+        assert rel_err(ob, want) <= 5e-3
+    picks = torch.tensor([rows - 1, 0], dtype=torch.int32, device=DEV)
+    o = torch.empty(2, H, device=DEV)
+    ops().layer_norm(x, w, b, 1e-5, out_act=o, rows=picks)
+    want = P.layer_norm(x.cpu()[[rows - 1, 0]], None if w is None else w.cpu(), None if b is None else b.cpu(), 1e-5)
+    assert rel_err(o, want.to(DEV)) <= 1e-5
+    xin = x.clone()
+    ops().layer_norm(xin, w, b, 1e-5, out_f32=xin)              # in place, as a post-norm block uses it
+    assert rel_err(xin, P.layer_norm(x.cpu(), None if w is None else w.cpu(), None if b is None else b.cpu(), 1e-5).to(DEV)) <= 1e-5
+
+
+@pytest.mark.parametrize("tdt", [torch.float32, torch.bfloat16])
+def test_embedding(tdt):
+    V, H, Pn, off = 301, 72, 50, 2
+    g = torch.Generator().manual_seed(1)
+    tok = torch.randn(V, H, generator=g).to(tdt)
+    pos = torch.randn(Pn + off, H, generator=g).to(tdt)
+    ids = torch.tensor([0, 300, 17, 5, 5], dtype=torch.int32)
+    ps = torch.tensor([0, 49, 3, 20, 21], dtype=torch.int32)
+    want = P.token_embedding(ids, tok.float()) + P.learned_position_embedding(ps, pos.float(), off)
+    x = torch.empty(5, H, device=DEV)
+    xa = torch.empty(5, H, dtype=torch.bfloat16, device=DEV)
+    ops().embed(tok.to(DEV), None, ids.to(DEV), pos.to(DEV), ps.to(DEV), off, x, xa)
+    assert rel_err(x, want.to(DEV)) <= 1e-6 and rel_err(xa, want.to(DEV)) <= 5e-3
+    pre = torch.randn(5, H, generator=g)
+    ops().embed(None, pre.to(DEV), ids.to(DEV), pos.to(DEV), ps.to(DEV), off, x, None)
+    assert rel_err(x, (pre + P.learned_position_embedding(ps, pos.float(), off)).to(DEV)) <= 1e-6
+    e = torch.empty(5, H, dtype=torch.bfloat16, device=DEV)
+    ops().gather_rows(tok.to(DEV), ids.to(DEV), e)
+    assert rel_err(e, tok.float()[ids.long()].to(DEV)) <= 5e-3
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_kv_append(dt):
+    n_kv, d, ps, pages = 3, 48, 16, 7
+    N = 20
+    g = torch.Generator().manual_seed(2)
+    qkv = torch.randn(N, (5 + 2 * n_kv) * d, generator=g).to(dt).to(DEV)
+    k, v = qkv[:, 5 * d:(5 + n_kv) * d], qkv[:, (5 + n_kv) * d:]
+    slots = torch.randperm(pages * ps, generator=g)[:N].to(torch.int32)
+    cache = torch.zeros(pages, 2, n_kv, ps, d, dtype=dt, device=DEV)
+    ops().kv_append(k, v, slots.to(DEV), cache, ps)
+    for n in range(N):
+        pg, r = int(slots[n]) // ps, int(slots[n]) % ps
+        assert torch.equal(cache[pg, 0, :, r].reshape(-1), k[n]) and torch.equal(cache[pg, 1, :, r].reshape(-1), v[n])
+    assert int((cache != 0).sum()) <= 2 * N * n_kv * d
+
+
+def test_sampling_greedy_and_ties():
+    logits = torch.randn(9, 50272, generator=torch.Generator().manual_seed(3)).to(DEV)
+    logits[2, 777] = logits[2, 40000] = 99.0                  # a tie: the lowest index wins
+    out = torch.empty(9, dtype=torch.int32, device=DEV)
+    ops().sample(logits, out)
+    want = P.greedy_token(logits.cpu())
+    assert out.cpu().tolist() == want.tolist() and int(out[2]) == 777
+    t0 = torch.zeros(9, device=DEV)
+    ops().sample(logits, out, temperature=t0, suppress_id=777)
+    assert int(out[2]) == 40000
+
+
+def _draws(logits_row, n, temperature, top_k=0, top_p=1.0, suppress=-1, seed=5):
+    V = logits_row.numel()
+    logits = logits_row.to(DEV)[None].repeat(n, 1).contiguous()
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    ops().sample(logits, out, temperature=torch.full((n,), temperature, device=DEV),
+                 top_k=torch.full((n,), top_k, dtype=torch.int32, device=DEV),
+                 top_p=torch.full((n,), top_p, device=DEV),
+                 seeds=torch.full((n,), seed, dtype=torch.int64, device=DEV),
+                 counters=torch.arange(n, dtype=torch.int64, device=DEV), suppress_id=suppress)
+    return out.cpu()
+
+
+@pytest.mark.parametrize("kw", [dict(temperature=1.0), dict(temperature=0.7, top_k=5), dict(temperature=1.3, top_p=0.8),
+                                dict(temperature=0.9, top_k=12, top_p=0.6), dict(temperature=1.0, suppress=3)])
+def test_sampling_distribution(kw):
+    V, n = 37, 40000
+    row = torch.randn(V, generator=torch.Generator().manual_seed(11)) * 2
+    got = _draws(row, n, **kw)
+    sup = [kw["suppress"]] if kw.get("suppress", -1) >= 0 else None
+    p = P.sampling_distribution(row[None], kw["temperature"], kw.get("top_k") or None, kw.get("top_p", 1.0), sup)[0]
+    counts = torch.bincount(got.long(), minlength=V).float()
+    assert int(counts[p == 0].sum()) == 0, "a token outside the kept set was drawn"
+    keep = p > 0
+    chi2 = float((((counts - n * p) ** 2)[keep] / (n * p[keep])).sum())
+    dof = int(keep.sum()) - 1
+    assert chi2 < dof + 6 * math.sqrt(2 * max(dof, 1)) + 10, f"chi2 {chi2:.1f} for {dof} degrees of freedom"
+    again = _draws(row, n, **kw)
+    assert torch.equal(got, again), "a draw is a function of logits, parameters, seed and counter"
+    other = _draws(row, n, seed=6, **kw)
+    assert not torch.equal(got, other)
+
+
+def test_sampling_large_vocabulary_top_k():
+    V = 50272
+    row = torch.randn(V, generator=torch.Generator().manual_seed(12))
+    got = _draws(row, 2000, temperature=1.0, top_k=50)
+    top = set(torch.topk(row, 50).indices.tolist())
+    assert set(got.tolist()) <= top and len(set(got.tolist())) > 25
