@@ -362,7 +362,7 @@ def test_sampling_distribution(kw):
     again = _draws(row, n, **kw)
     assert torch.equal(got, again), "a draw is a function of logits, parameters, seed and counter"
     other = _draws(row, n, seed=6, **kw)
-    assert not torch.equal(got, other)
+    assert int(keep.sum()) == 1 or not torch.equal(got, other)
 
 
 def test_sampling_large_vocabulary_top_k():

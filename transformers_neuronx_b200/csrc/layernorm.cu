@@ -58,10 +58,10 @@ TNX_EXPORT int tnx_layer_norm(const float* x, const int* rows, const float* gamm
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     const size_t smem = (size_t)H * sizeof(float);
     if (act_bf16) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(layer_norm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (smem + 1024 > 48 * 1024) cudaFuncSetAttribute(layer_norm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         layer_norm_kernel<bf16><<<n_rows, threads, smem, stream>>>(x, rows, gamma, beta, eps, out_f32, (bf16*)out_act, H);
     } else {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(layer_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (smem + 1024 > 48 * 1024) cudaFuncSetAttribute(layer_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         layer_norm_kernel<float><<<n_rows, threads, smem, stream>>>(x, rows, gamma, beta, eps, out_f32, (float*)out_act, H);
     }
     return tnx_launch_status();
