@@ -131,7 +131,7 @@ def time_decode(model, cfg, batch, steps, warmup, use_engine=False):
     total = steps + warmup
     ctx0 = CONTEXT - total
     pages = batch * (CONTEXT // 16)
-    runner = StepRunner(model, 16, pages, max(batch, 1), CONTEXT)
+    runner = StepRunner(model, 16, pages, max(batch, 1), CONTEXT, use_cuda_graphs=True)
     g = torch.Generator().manual_seed(1)
     for b in range(batch):                                  # the cache as 2,048 - (W + K) earlier tokens left it:
         runner.add_request(b)                               # synthetic keys and values, real bookkeeping

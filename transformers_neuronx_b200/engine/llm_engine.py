@@ -23,7 +23,8 @@ class LLMEngine:
         else:
             tokens = ec.max_tokens if ec.max_tokens is not None else ec.max_num_seqs * max_len
             num_pages = -(-tokens // ec.page_size)
-        self.runner = StepRunner(model, ec.page_size, num_pages, ec.max_num_seqs, max_len)
+        self.runner = StepRunner(model, ec.page_size, num_pages, ec.max_num_seqs, max_len,
+                                 use_cuda_graphs=ec.use_cuda_graphs)
         self.scheduler = Scheduler(self.runner.cache, ec.max_batch_tokens, ec.max_num_seqs, max_len)
         self.sampler = Sampler(model.device)
         self.eos_token_id = model.spec.eos_token_id if eos_token_id is None else eos_token_id

@@ -29,8 +29,9 @@ def build_model(spec, tensors, dtype: str, device="cuda:0", verbose=True) -> Dec
     dev = require_cuda(device)
     torch.cuda.set_device(dev)
     model = DecoderModel(spec)
-    kbuild.build_many(model.libraries(), verbose=verbose)
-    model.load(tensors, dev, _TORCH_DTYPE[canonical_dtype(dtype)])
+    act = _TORCH_DTYPE[canonical_dtype(dtype)]
+    kbuild.build_many(model.libraries(act), verbose=verbose)
+    model.load(tensors, dev, act)
     return model
 
 

@@ -34,7 +34,7 @@ def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines=None
     page = ecfg.page_size
     num_pages = max(1, -(-int(max_tokens) // page))
     runner = StepRunner(model, page_size=page, num_pages=num_pages, max_slots=8,
-                        max_model_len=model.spec.max_positions)
+                        max_model_len=model.spec.max_positions, use_cuda_graphs=True)
     for line in lines:
         line = line.strip()
         if not line:

@@ -41,7 +41,8 @@ class HostBatch:
 class StepRunner:
     """Owns the cache (bookkeeping and device memory) of one model and runs steps on it."""
 
-    def __init__(self, model, page_size: int, num_pages: int, max_slots: int, max_model_len: int):
+    def __init__(self, model, page_size: int, num_pages: int, max_slots: int, max_model_len: int,
+                 use_cuda_graphs: bool = False, max_graph_batch: int = 256):
         self.model = model
         self.device = model.device
         self.act_dtype = model.act_dtype
@@ -55,6 +56,12 @@ class StepRunner:
         self.vocab = model.spec.vocab_size
         self._pinned = None
         self.steps_run = 0
+        self.last_h2d_bytes = 0
+        # decode-only steps can be replayed as CUDA graphs, one per (batch bucket, context bucket)
+        self.use_cuda_graphs = bool(use_cuda_graphs) and getattr(model, "graph_safe", True)
+        self.max_graph_batch = max_graph_batch
+        self._graphs = {}
+        self._graph_pool = None
 
     # ---- requests -------------------------------------------------------------------------------
     def add_request(self, rid) -> int:
@@ -85,8 +92,7 @@ class StepRunner:
             slot[0] = torch.empty(max(n, 4096), dtype=torch.int32, pin_memory=True)
         return slot
 
-    def prepare(self, entries: Sequence[StepEntry]) -> StepContext:
-        """Reserves pages for every entry (all or none) and builds the step's index arrays."""
+    def _validate(self, entries: Sequence[StepEntry]) -> None:
         if not entries:
             raise ValueError("a step needs at least one entry")
         seen = set()
@@ -113,6 +119,10 @@ class StepRunner:
             if need[g] > free[g]:
                 raise OutOfPages(f"the step needs {need[g]} page(s) in cache group {g}, {free[g]} are free")
 
+    def _pack(self, entries: Sequence[StepEntry], pad_rows: Optional[int] = None, fixed_blocks: Optional[int] = None):
+        """Reserves the pages and builds the step's index arrays.  With pad_rows (a captured decode
+        step) every array has the size of pad_rows single-token requests: padded rows carry request
+        -1 and slot -1, which the kernels skip, and every row's logits are computed."""
         hb = HostBatch()
         tokens, positions, token_request, logit_rows = [], [], [], []
         row = 0
@@ -127,14 +137,16 @@ class StepRunner:
             logit_rows.extend(row + int(w) for w in e.want)
             row += n
         N, R = row, len(entries)
-        tok = np.asarray(tokens, dtype=np.int64)
+        Np = N if pad_rows is None else pad_rows
+        Rp = R if pad_rows is None else pad_rows
         ps = self.page_size
-        pos = np.asarray(positions, dtype=np.int32)
-        treq = np.asarray(token_request, dtype=np.int32)
-        parts = [tok.astype(np.int32), pos, treq,
-                 np.asarray(hb.q_start, np.int32), np.asarray(hb.q_len, np.int32), np.asarray(hb.ctx_len, np.int32),
-                 np.asarray(hb.slots, np.int32), np.asarray(logit_rows, np.int32)]
-        # work lists of the attention kernels: 64-row tiles of portions, and rows that decode
+
+        def padded(vals, size, fill):
+            a = np.full(size, fill, dtype=np.int32)
+            a[:len(vals)] = vals
+            return a
+
+        tok, pos, treq = padded(tokens, Np, 0), padded(positions, Np, 0), padded(token_request, Np, -1)
         tile_req, tile_q0, decode_rows = [], [], []
         for r in range(R):
             if hb.q_len[r] == 1:
@@ -142,64 +154,130 @@ class StepRunner:
             else:
                 for q0 in range(0, hb.q_len[r], 64):
                     tile_req.append(r); tile_q0.append(q0)
-        parts += [np.asarray(tile_req, np.int32), np.asarray(tile_q0, np.int32), np.asarray(decode_rows, np.int32)]
+        if pad_rows is not None:
+            logit_rows = list(range(Np))
+            decode_rows = list(range(Np))
+        parts = [tok, pos, treq, padded(hb.q_start, Rp, 0), padded(hb.q_len, Rp, 0), padded(hb.ctx_len, Rp, 0),
+                 padded(hb.slots, Rp, 0), np.asarray(logit_rows, np.int32),
+                 np.asarray(tile_req, np.int32), np.asarray(tile_q0, np.int32), np.asarray(decode_rows, np.int32)]
         n_fixed = len(parts)
         max_blocks = []
         for g in range(self.n_groups):
             tables = [self.cache.block_table(e.rid, g) for e in entries]
-            mb = max(len(t) for t in tables)
-            bt = np.full((R, mb), -1, dtype=np.int32)
+            mb = max(len(t) for t in tables) if fixed_blocks is None else fixed_blocks
+            bt = np.full((Rp, mb), -1, dtype=np.int32)
             for r, t in enumerate(tables):
                 bt[r, :len(t)] = t
-            sm = bt[treq, pos // ps] * ps + pos % ps
-            parts += [bt.reshape(-1), sm.astype(np.int32)]
+            sm = np.full(Np, -1, dtype=np.int32)
+            sm[:N] = bt[treq[:N], pos[:N] // ps] * ps + pos[:N] % ps
+            parts += [bt.reshape(-1), sm]
             max_blocks.append(mb)
         sizes = [p.size for p in parts]
-        # each section starts on a 16-byte boundary
-        offs, o = [], 0
-        for s in sizes:
+        offs, o = [], 0                       # each section starts on a 16-byte boundary
+        for sz in sizes:
             offs.append(o)
-            o += (s + 3) // 4 * 4
+            o += (sz + 3) // 4 * 4
         slot = self._pinned_buffer(o)
-        pinned = slot[0]
-        host = pinned.numpy()
+        host = slot[0].numpy()
         for p, off in zip(parts, offs):
             host[off:off + p.size] = p
-        dev = torch.empty(o, dtype=torch.int32, device=self.device)
-        dev.copy_(pinned[:o], non_blocking=True)
-        if slot[1] is None:
-            slot[1] = torch.cuda.Event()
-        slot[1].record()
+        return hb, slot, o, offs, sizes, max_blocks, n_fixed, (N, R, Np, Rp), (len(tile_req), len(decode_rows))
+
+    def _context(self, dev, hb, offs, sizes, max_blocks, n_fixed, dims, counts) -> StepContext:
+        N, R, Np, Rp = dims
 
         def sec(i):
             return dev[offs[i]:offs[i] + sizes[i]]
 
         ctx = StepContext(self.device, self.act_dtype)
-        ctx.n_tokens, ctx.n_requests = N, R
+        ctx.n_tokens, ctx.n_requests = Np, R
         ctx.token_ids, ctx.positions, ctx.token_request = sec(0), sec(1), sec(2)
         ctx.q_start, ctx.q_len, ctx.ctx_len, ctx.state_slots = sec(3), sec(4), sec(5), sec(6)
         ctx.logit_rows = sec(7)
         ctx.tile_req, ctx.tile_q0, ctx.decode_rows = sec(8), sec(9), sec(10)
-        ctx.n_prefill_tiles, ctx.n_decode_rows = len(tile_req), len(decode_rows)
-        ctx.max_decode_ctx = max([hb.ctx_len[r] + 1 for r in range(R) if hb.q_len[r] == 1], default=0)
+        ctx.n_prefill_tiles, ctx.n_decode_rows = counts
         for g in range(self.n_groups):
-            ctx.block_tables.append(sec(n_fixed + 2 * g).view(R, max_blocks[g]))
+            ctx.block_tables.append(sec(n_fixed + 2 * g).view(Rp, max_blocks[g]))
             ctx.slot_mapping.append(sec(n_fixed + 2 * g + 1))
         ctx.host = hb
         ctx.storage = self.storage
-        ctx.page_size = ps
+        ctx.page_size = self.page_size
         ctx.decode_only = all(n == 1 for n in hb.q_len)
         ctx.max_ctx = max(c + n for c, n in zip(hb.ctx_len, hb.q_len))
-        ctx.h2d_bytes = o * 4
-        self.last_h2d_bytes = o * 4
+        ctx.max_decode_ctx = max([c + 1 for c, n in zip(hb.ctx_len, hb.q_len) if n == 1], default=0)
         return ctx
+
+    def prepare(self, entries: Sequence[StepEntry]) -> StepContext:
+        """Reserves pages for every entry (all or none), builds the step's index arrays in pinned
+        memory and copies them to the device in one transfer."""
+        self._validate(entries)
+        hb, slot, o, offs, sizes, max_blocks, n_fixed, dims, counts = self._pack(entries)
+        dev = torch.empty(o, dtype=torch.int32, device=self.device)
+        dev.copy_(slot[0][:o], non_blocking=True)
+        if slot[1] is None:
+            slot[1] = torch.cuda.Event()
+        slot[1].record()
+        self.last_h2d_bytes = o * 4
+        return self._context(dev, hb, offs, sizes, max_blocks, n_fixed, dims, counts)
+
+    # ---- decode-only steps as CUDA graphs ----------------------------------------------------------
+    def _graph_key(self, entries):
+        R = len(entries)
+        bucket = 1
+        while bucket < R:
+            bucket *= 2
+        longest = max(self.cache.length(e.rid) for e in entries) + 1
+        ctx_bucket = 256
+        while ctx_bucket < longest:
+            ctx_bucket *= 2
+        return bucket, min(ctx_bucket, -(-self.max_model_len // self.page_size) * self.page_size)
+
+    def _graph_step(self, entries) -> torch.Tensor:
+        key = self._graph_key(entries)
+        bucket, ctx_bucket = key
+        fixed_blocks = -(-ctx_bucket // self.page_size)
+        hb, slot, o, offs, sizes, max_blocks, n_fixed, dims, counts = self._pack(entries, bucket, fixed_blocks)
+        g = self._graphs.get(key)
+        if g is None:
+            dev = torch.empty(o, dtype=torch.int32, device=self.device)
+            ctx = self._context(dev, hb, offs, sizes, max_blocks, n_fixed, dims, counts)
+            g = {"dev": dev, "ctx": ctx, "graph": None, "logits": None, "runs": 0}
+            self._graphs[key] = g
+        dev, ctx = g["dev"], g["ctx"]
+        dev.copy_(slot[0][:o], non_blocking=True)
+        if slot[1] is None:
+            slot[1] = torch.cuda.Event()
+        slot[1].record()
+        self.last_h2d_bytes = o * 4
+        ctx.host, ctx.n_requests = hb, len(entries)
+        ctx.max_decode_ctx = ctx_bucket               # the split plan is fixed for the whole bucket
+        ctx.max_ctx = ctx_bucket
+        if g["graph"] is None:
+            if g["runs"] == 0:                        # first use: run eagerly (kernels get built, scratch gets made)
+                g["runs"] = 1
+                return self.model.forward(ctx)[:len(entries)]
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, pool=self._graph_pool):
+                g["logits"] = self.model.forward(ctx)
+            g["graph"] = graph
+            if self._graph_pool is None:
+                self._graph_pool = graph.pool()
+            # the capture recorded the kernels without running them: fall through to the replay
+        g["graph"].replay()
+        g["runs"] += 1
+        return g["logits"][:len(entries)]
 
     @torch.no_grad()
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Runs one step; returns the 32-bit logits [wanted, vocab] (a device tensor) in the order
         of the entries and of their `want`."""
-        ctx = self.prepare(entries)
-        logits = self.model.forward(ctx)
+        if self.use_cuda_graphs and all(len(e.tokens) == 1 for e in entries) and len(entries) <= self.max_graph_batch:
+            self._validate(entries)
+            logits = self._graph_step(entries)
+        else:
+            ctx = self.prepare(entries)
+            logits = self.model.forward(ctx)
         for e in entries:
             self.cache.release_behind_window(e.rid)
         self.steps_run += 1

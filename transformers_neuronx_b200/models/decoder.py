@@ -46,11 +46,19 @@ class DecoderModel:
                     out.append(s)
         return out
 
-    def libraries(self) -> List[str]:
+    def libraries(self, act_dtype=None) -> List[str]:
+        """Kernel libraries worth compiling before the first step (the rest are compiled when first used)."""
         libs = []
         for p in self.all_parts():
             libs += [l for l in p.libraries if l in kbuild.SOURCES]
+        if act_dtype == torch.float32:
+            libs = [l for l in libs if l not in ("gemm_tc", "attention_prefill", "attention_decode")]
         return list(dict.fromkeys(libs))
+
+    @property
+    def graph_safe(self) -> bool:
+        """Whether a decode step of this model can be captured in a CUDA graph (every part says so)."""
+        return all(getattr(p, "graph_safe", False) for p in self.all_parts())
 
     def cache_needs(self) -> Dict[int, object]:
         """{cache id -> what the mixer(s) using it keep}; entries sharing a cache must agree."""

@@ -20,6 +20,7 @@ from .spec import AttentionSpec
 
 
 class PagedAttention(Mixer):
+    graph_safe = True
     def __init__(self, spec: AttentionSpec):
         s = self.spec = spec
         if s.n_heads % s.n_kv_heads:

@@ -69,6 +69,7 @@ class StepContext:
 
 class Part:
     libraries: Sequence[str] = ()
+    graph_safe = False       # True: forward launches kernels only (no host reads, no host loops over ctx.host)
 
     def tensor_specs(self) -> List[TensorSpec]:
         return []

@@ -19,6 +19,7 @@ from .spec import EmbeddingSpec, HeadSpec
 
 
 class Embedding(Part):
+    graph_safe = True
     def __init__(self, spec: EmbeddingSpec):
         self.spec = spec
         self.table = None
@@ -76,6 +77,7 @@ class Embedding(Part):
 
 
 class Head(Part):
+    graph_safe = True
     def __init__(self, spec: HeadSpec):
         self.spec = spec
         self.weight = None

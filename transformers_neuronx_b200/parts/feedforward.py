@@ -12,6 +12,7 @@ _FUSED_ACTIVATIONS = ("relu",)
 
 
 class DenseFeedForward(FeedForward):
+    graph_safe = True
     libraries = ("gemm_simt", "gemm_tc")
 
     def __init__(self, spec: DenseFeedForwardSpec):

@@ -22,6 +22,7 @@ from .spec import LinearSpec
 
 
 class Linear(Part):
+    graph_safe = True
     def __init__(self, spec: LinearSpec):
         self.spec = spec
         self.weight: Optional[torch.Tensor] = None

@@ -12,6 +12,7 @@ from .spec import NormSpec
 
 
 class LayerNorm(Norm):
+    graph_safe = True
     libraries = ("layernorm",)
 
     def __init__(self, spec: NormSpec):

@@ -10,6 +10,7 @@ from .spec import PositionSpec
 
 
 class LearnedPositions(PositionEncoding):
+    graph_safe = True
     libraries = ("embedding",)
 
     def __init__(self, spec: PositionSpec):
@@ -33,6 +34,7 @@ class LearnedPositions(PositionEncoding):
 
 
 class NoPositions(PositionEncoding):
+    graph_safe = True
     def __init__(self, spec=None):
         self.spec = spec
 
