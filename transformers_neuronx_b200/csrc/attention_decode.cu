@@ -42,6 +42,8 @@ attention_decode_kernel(const DecodeParams p) {
     __shared__ float sm_m[WARPS], sm_l[WARPS];
     __shared__ float sm_acc[WARPS][LPK * 8];
     __shared__ int last_flag;
+    pdl_launch_dependents();
+    pdl_wait();
 
     const int h = blockIdx.x, ri = blockIdx.y, split = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -226,12 +228,12 @@ TNX_EXPORT int tnx_attention_decode(const void* q, int q_stride, const void* cac
     p.n_splits = n_splits; p.pages_per_split = pages_per_split; p.scratch = scratch; p.counters = counters;
     dim3 grid(n_heads, n_rows, n_splits);
     const int chunks = head_dim / 8;
-    if (chunks <= 2) attention_decode_kernel<2><<<grid, WARPS * 32, 0, stream>>>(p);
-    else if (chunks <= 4) attention_decode_kernel<4><<<grid, WARPS * 32, 0, stream>>>(p);
-    else if (chunks <= 8) attention_decode_kernel<8><<<grid, WARPS * 32, 0, stream>>>(p);
-    else if (chunks <= 16) attention_decode_kernel<16><<<grid, WARPS * 32, 0, stream>>>(p);
-    else attention_decode_kernel<32><<<grid, WARPS * 32, 0, stream>>>(p);
-    return tnx_launch_status();
+    const dim3 block(WARPS * 32);
+    if (chunks <= 2) return tnx_launch_pdl(attention_decode_kernel<2>, grid, block, 0, stream, p);
+    if (chunks <= 4) return tnx_launch_pdl(attention_decode_kernel<4>, grid, block, 0, stream, p);
+    if (chunks <= 8) return tnx_launch_pdl(attention_decode_kernel<8>, grid, block, 0, stream, p);
+    if (chunks <= 16) return tnx_launch_pdl(attention_decode_kernel<16>, grid, block, 0, stream, p);
+    return tnx_launch_pdl(attention_decode_kernel<32>, grid, block, 0, stream, p);
 }
 
 // ---------------------------------------------------------------------------------------------------

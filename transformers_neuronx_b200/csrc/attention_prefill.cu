@@ -63,11 +63,12 @@ __device__ __forceinline__ uint32_t swz(int row, int chunk) {
 template <int HEAD>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_prefill_kernel(const PrefillParams p) {
-    constexpr int CHUNKS = HEAD / 8;             // 16-byte chunks per row
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* sQ = smem;
     uint8_t* sK = sQ + BQ * HEAD * 2;
     uint8_t* sV = sK + BKV * HEAD * 2;
+    pdl_launch_dependents();
+    pdl_wait();
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int item = blockIdx.x, h = blockIdx.y;
@@ -234,8 +235,7 @@ int launch(const PrefillParams& p, int n_items, cudaStream_t stream) {
         configured = true;
     }
     dim3 grid(n_items, p.n_heads);
-    attention_prefill_kernel<HEAD><<<grid, WARPS * 32, smem, stream>>>(p);
-    return tnx_launch_status();
+    return tnx_launch_pdl(attention_prefill_kernel<HEAD>, grid, dim3(WARPS * 32), smem, stream, p);
 }
 
 }  // namespace

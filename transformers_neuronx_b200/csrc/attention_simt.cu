@@ -21,6 +21,8 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, const T* __restrict
                       T* __restrict__ out, int out_stride, int n_tokens, int n_heads, int n_kv_heads,
                       int head_dim, int page_size, int window, float scale) {
     extern __shared__ float qsm[];                  // [warps per block][head_dim]
+    pdl_launch_dependents();
+    pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long pair = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
     if (pair >= (long long)n_tokens * n_heads) return;
@@ -96,12 +98,12 @@ TNX_EXPORT int tnx_attention_simt(const void* q, int q_stride, const void* cache
     const int blocks = (int)((pairs + warps - 1) / warps);
     const size_t smem = (size_t)warps * head_dim * sizeof(float);
     if (is_bf16)
-        attention_simt_kernel<bf16><<<blocks, warps * 32, smem, stream>>>(
-            (const bf16*)q, q_stride, (const bf16*)cache, block_tables, bt_stride, token_request, positions,
-            (bf16*)out, out_stride, n_tokens, n_heads, n_kv_heads, head_dim, page_size, window, scale);
-    else
-        attention_simt_kernel<float><<<blocks, warps * 32, smem, stream>>>(
-            (const float*)q, q_stride, (const float*)cache, block_tables, bt_stride, token_request, positions,
-            (float*)out, out_stride, n_tokens, n_heads, n_kv_heads, head_dim, page_size, window, scale);
-    return tnx_launch_status();
+        return tnx_launch_pdl(attention_simt_kernel<bf16>, dim3(blocks), dim3(warps * 32), smem, stream,
+                              (const bf16*)q, q_stride, (const bf16*)cache, block_tables, bt_stride, token_request,
+                              positions, (bf16*)out, out_stride, n_tokens, n_heads, n_kv_heads, head_dim, page_size,
+                              window, scale);
+    return tnx_launch_pdl(attention_simt_kernel<float>, dim3(blocks), dim3(warps * 32), smem, stream,
+                          (const float*)q, q_stride, (const float*)cache, block_tables, bt_stride, token_request,
+                          positions, (float*)out, out_stride, n_tokens, n_heads, n_kv_heads, head_dim, page_size,
+                          window, scale);
 }

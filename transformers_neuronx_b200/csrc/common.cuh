@@ -5,6 +5,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define TNX_EXPORT extern "C" __attribute__((visibility("default")))
 
@@ -20,6 +21,39 @@ static inline int tnx_launch_status() {
 }
 
 typedef __nv_bfloat16 bf16;
+
+// Programmatic dependent launch.  Every kernel of the engine is launched with the attribute that
+// lets it start while the kernel before it in the stream is still running.  The rules each kernel
+// keeps: it calls pdl_launch_dependents() at its start (the next kernel may begin its own set-up
+// and prefetch data that no kernel writes, i.e. weights), and it calls pdl_wait() before it reads
+// anything a preceding kernel wrote and before it writes anything at all.  pdl_wait() returns when
+// the preceding kernel has completed and its writes are visible; since every kernel waits before
+// it finishes, completion is transitive along the stream.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// early != 0: the kernel may start before the kernel ahead of it has finished (it must keep the
+// rules above).  early == 0: an ordinary launch; the calls above are then no-ops.
+template <typename... KArgs, typename... Args>
+static inline int tnx_launch_ex(int early, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    static const int mode = getenv("TNX_PDL") ? atoi(getenv("TNX_PDL")) : 1;   // 0 none, 1 as asked, 2 all
+    const bool on = mode == 2 || (mode == 1 && early);
+    cfg.attrs = attr; cfg.numAttrs = on ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+    if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
+    return 0;
+}
+template <typename... KArgs, typename... Args>
+static inline int tnx_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 Args... args) {
+    return tnx_launch_ex(0, kernel, grid, block, smem, stream, args...);
+}
 
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(bf16 v) { return __bfloat162float(v); }

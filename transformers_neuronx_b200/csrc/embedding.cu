@@ -13,6 +13,8 @@ __global__ void embed_kernel(const TT* __restrict__ tok_table, const float* __re
                              const int* __restrict__ ids, const TT* __restrict__ pos_table,
                              const int* __restrict__ positions, int pos_offset,
                              float* __restrict__ out_f32, TA* __restrict__ out_act, int H) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int n = blockIdx.x;
     const TT* trow = tok_table ? tok_table + (size_t)ids[n] * H : nullptr;
     const TT* prow = pos_table ? pos_table + (size_t)(positions[n] + pos_offset) * H : nullptr;
@@ -27,6 +29,8 @@ __global__ void embed_kernel(const TT* __restrict__ tok_table, const float* __re
 template <typename TT, typename TA>
 __global__ void gather_rows_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
                                    TA* __restrict__ out, int E) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int n = blockIdx.x;
     const TT* row = table + (size_t)ids[n] * E;
     for (int c = threadIdx.x; c < E; c += blockDim.x) out[(size_t)n * E + c] = from_float<TA>(to_float(row[c]));
@@ -39,15 +43,14 @@ TNX_EXPORT int tnx_embed(const void* tok_table, const float* pre, const int* ids
     if (N <= 0) return 0;
     if (H <= 0 || (!tok_table && !pre)) return TNX_ERR_BAD_ARG;
     const int threads = H >= 1024 ? 256 : 128;
-#define LAUNCH(TT, TA)                                                                            \
-    embed_kernel<TT, TA><<<N, threads, 0, stream>>>((const TT*)tok_table, pre, ids, (const TT*)pos_table, \
-                                                    positions, pos_offset, out_f32, (TA*)out_act, H)
-    if (table_bf16 && act_bf16) LAUNCH(bf16, bf16);
-    else if (table_bf16 && !act_bf16) LAUNCH(bf16, float);
-    else if (!table_bf16 && act_bf16) LAUNCH(float, bf16);
-    else LAUNCH(float, float);
+#define LAUNCH(TT, TA)                                                                                        \
+    tnx_launch_pdl(embed_kernel<TT, TA>, dim3(N), dim3(threads), 0, stream, (const TT*)tok_table, pre, ids,   \
+                   (const TT*)pos_table, positions, pos_offset, out_f32, (TA*)out_act, H)
+    if (table_bf16 && act_bf16) return LAUNCH(bf16, bf16);
+    if (table_bf16 && !act_bf16) return LAUNCH(bf16, float);
+    if (!table_bf16 && act_bf16) return LAUNCH(float, bf16);
+    return LAUNCH(float, float);
 #undef LAUNCH
-    return tnx_launch_status();
 }
 
 TNX_EXPORT int tnx_gather_rows(const void* table, const int* ids, void* out, int N, int E,
@@ -55,9 +58,8 @@ TNX_EXPORT int tnx_gather_rows(const void* table, const int* ids, void* out, int
     if (N <= 0) return 0;
     if (E <= 0) return TNX_ERR_BAD_ARG;
     const int threads = E >= 1024 ? 256 : 128;
-    if (table_bf16 && act_bf16) gather_rows_kernel<bf16, bf16><<<N, threads, 0, stream>>>((const bf16*)table, ids, (bf16*)out, E);
-    else if (table_bf16) gather_rows_kernel<bf16, float><<<N, threads, 0, stream>>>((const bf16*)table, ids, (float*)out, E);
-    else if (act_bf16) gather_rows_kernel<float, bf16><<<N, threads, 0, stream>>>((const float*)table, ids, (bf16*)out, E);
-    else gather_rows_kernel<float, float><<<N, threads, 0, stream>>>((const float*)table, ids, (float*)out, E);
-    return tnx_launch_status();
+    if (table_bf16 && act_bf16) return tnx_launch_pdl(gather_rows_kernel<bf16, bf16>, dim3(N), dim3(threads), 0, stream, (const bf16*)table, ids, (bf16*)out, E);
+    if (table_bf16) return tnx_launch_pdl(gather_rows_kernel<bf16, float>, dim3(N), dim3(threads), 0, stream, (const bf16*)table, ids, (float*)out, E);
+    if (act_bf16) return tnx_launch_pdl(gather_rows_kernel<float, bf16>, dim3(N), dim3(threads), 0, stream, (const float*)table, ids, (bf16*)out, E);
+    return tnx_launch_pdl(gather_rows_kernel<float, float>, dim3(N), dim3(threads), 0, stream, (const float*)table, ids, (float*)out, E);
 }

@@ -19,6 +19,8 @@ gemm_simt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, const float
                  int relu) {
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
+    pdl_launch_dependents();
+    pdl_wait();
     const int tid = threadIdx.x;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int tx = tid % 16, ty = tid / 16;          // thread's 4x4 patch: rows ty*4.., cols tx*4..
@@ -73,9 +75,8 @@ template <typename TA, typename TW, typename TO>
 int launch(const void* A, const void* W, const float* bias, const float* residual, void* C, int M,
            int N, int K, int lda, int ldw, int ldc, int relu, cudaStream_t stream) {
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-    gemm_simt_kernel<TA, TW, TO><<<grid, 256, 0, stream>>>((const TA*)A, (const TW*)W, bias, residual,
-                                                           (TO*)C, M, N, K, lda, ldw, ldc, relu);
-    return tnx_launch_status();
+    return tnx_launch_pdl(gemm_simt_kernel<TA, TW, TO>, grid, dim3(256), 0, stream, (const TA*)A, (const TW*)W, bias,
+                          residual, (TO*)C, M, N, K, lda, ldw, ldc, relu);
 }
 
 }  // namespace

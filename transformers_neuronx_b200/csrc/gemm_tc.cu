@@ -218,7 +218,7 @@ __device__ __forceinline__ void store_tile_row(const Params& p, int lane_row, in
 }
 
 template <int BN, int STAGES, bool SWAP>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(NUM_THREADS, SWAP ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, const Params p) {
     constexpr int A_BYTES = TILE_P * BLOCK_K * 2;            // 16 KB
     constexpr int B_BYTES = BN * BLOCK_K * 2;
@@ -239,15 +239,39 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     const int kb_end = min(num_kb_total, kb_begin + p.kb_per_split);
     const int num_kb = max(0, kb_end - kb_begin);
 
+    // One K block = one stage: the weight tile and the activation tile complete the same barrier.
+    // The weights are never written by a kernel, so their loads may start before the preceding
+    // kernel has finished (programmatic dependent launch); the activations may not.
+    auto load_weights = [&](int i) {
+        const int s = i % STAGES;
+        mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+        uint8_t* a_dst = smem + (size_t)s * STAGE_BYTES;
+        const int kx = (kb_begin + i) * BLOCK_K;
+        if (SWAP) tma_load_2d(a_dst, &map_p, &full_bar[s], kx, tile_p * TILE_P);
+        else tma_load_2d(a_dst + A_BYTES, &map_q, &full_bar[s], kx, tile_q * BN);
+    };
+    auto load_activations = [&](int i) {
+        const int s = i % STAGES;
+        uint8_t* a_dst = smem + (size_t)s * STAGE_BYTES;
+        const int kx = (kb_begin + i) * BLOCK_K;
+        if (SWAP) tma_load_2d(a_dst + A_BYTES, &map_q, &full_bar[s], kx, tile_q * BN);
+        else tma_load_2d(a_dst, &map_p, &full_bar[s], kx, tile_p * TILE_P);
+    };
+    pdl_launch_dependents();
+    int issued = 0;
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
         mbar_init(&tmem_full_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_p) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_q) : "memory");
+        for (; issued < num_kb && issued < STAGES; ++issued) load_weights(issued);
     }
     if (warp == 1) {
         tmem_alloc(&tmem_base_smem, TMEM_COLS);
         tmem_relinquish();
     }
+    pdl_wait();                       // from here on the preceding kernel's results may be read, and ours written
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -256,17 +280,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int i = 0; i < num_kb && ok; ++i) {
+            for (int i = 0; i < issued; ++i) load_activations(i);
+            for (int i = issued; i < num_kb && ok; ++i) {
                 const int s = i % STAGES;
                 const uint32_t ph = (i / STAGES) & 1;
                 ok = mbar_wait(&empty_bar[s], ph ^ 1, p.err, 1);
                 if (!ok) break;
-                mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-                uint8_t* a_dst = smem + (size_t)s * STAGE_BYTES;
-                uint8_t* b_dst = a_dst + A_BYTES;
-                const int kx = (kb_begin + i) * BLOCK_K;
-                tma_load_2d(a_dst, &map_p, &full_bar[s], kx, tile_p * TILE_P);
-                tma_load_2d(b_dst, &map_q, &full_bar[s], kx, tile_q * BN);
+                load_weights(i);
+                load_activations(i);
             }
         }
     } else if (warp == 1) {
@@ -313,10 +334,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                     store_tile_row<BN, SWAP>(p, lane_row, tile_q * BN + c, v, LD_COLS);
                 }
             } else {
-                // 32-bit partial tile -> scratch: [split][tile_p][tile_q][row 0..127][col 0..BN)
+                // 32-bit partial tile -> scratch: [split][tile][col 0..BN)[row 0..127]: the 32 lanes
+                // of a warp write 32 consecutive floats
                 const size_t tiles = (size_t)gridDim.x * gridDim.y;
                 const size_t tile_id = (size_t)tile_p * gridDim.y + tile_q;
-                float* dst = p.partials + (((size_t)split * tiles + tile_id) * TILE_P + row_in_tile) * BN;
+                float* dst = p.partials + ((size_t)split * tiles + tile_id) * TILE_P * BN + row_in_tile;
 #pragma unroll 1
                 for (int c = 0; c < BN; c += LD_COLS) {
                     uint32_t r[32];
@@ -324,12 +346,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                     if (LD_COLS == 32) tmem_ld32(taddr, r); else tmem_ld16(taddr, r);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < LD_COLS; j += 4) {
-                        float4 f = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                               __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                        if (num_kb == 0) f = make_float4(0.f, 0.f, 0.f, 0.f);
-                        *(float4*)(dst + c + j) = f;
-                    }
+                    for (int j = 0; j < LD_COLS; ++j)
+                        __stcg(dst + (size_t)(c + j) * TILE_P, num_kb > 0 ? __uint_as_float(r[j]) : 0.f);
                 }
             }
         }
@@ -358,13 +376,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 float v[32];
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] = 0.f;
-                for (int s = 0; s < p.splits; ++s) {
-                    const float* src = p.partials + (((size_t)s * tiles + tile_id) * TILE_P + row_in_tile) * BN + c;
+                for (int s = 0; s < p.splits; ++s) {          // split order: the sum does not depend on timing
+                    const float* src = p.partials + ((size_t)s * tiles + tile_id) * TILE_P * BN + row_in_tile +
+                                       (size_t)c * TILE_P;
+                    float f[LD_COLS];
 #pragma unroll
-                    for (int j = 0; j < LD_COLS; j += 4) {
-                        const float4 f = __ldcg((const float4*)(src + j));
-                        v[j] += f.x; v[j + 1] += f.y; v[j + 2] += f.z; v[j + 3] += f.w;
-                    }
+                    for (int j = 0; j < LD_COLS; ++j) f[j] = __ldcg(src + (size_t)j * TILE_P);
+#pragma unroll
+                    for (int j = 0; j < LD_COLS; ++j) v[j] += f[j];
                 }
                 store_tile_row<BN, SWAP>(p, lane_row, tile_q * BN + c, v, LD_COLS);
             }
@@ -382,6 +401,152 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ---- many tokens: persistent CTAs, 128 x 256 tiles, two accumulators in tensor memory ---------------
+//
+// One CTA per SM walks over output tiles (tile = first + i * CTAs; consecutive tiles share the weight
+// tile and differ in the token tile, so CTAs running at the same time reuse weights and activations
+// in L2).  The shared-memory ring of K blocks runs on across tiles.  Tensor memory holds two
+// 128 x 256 accumulators: while the epilogue warps drain one, the MMA warp fills the other.
+constexpr int PBN = 256;
+constexpr int PSTAGES = 4;
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
+                          const Params p, int tiles_m, int tiles_n) {
+    constexpr int A_BYTES = TILE_P * BLOCK_K * 2;             // 16 KB
+    constexpr int B_BYTES = PBN * BLOCK_K * 2;                // 32 KB
+    constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    __shared__ uint64_t full_bar[PSTAGES], empty_bar[PSTAGES], acc_full[2], acc_empty[2];
+    __shared__ uint32_t tmem_base_smem;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_kb = (p.K + BLOCK_K - 1) / BLOCK_K;
+    const int n_tiles = tiles_m * tiles_n;
+    const int first = blockIdx.x, stride = gridDim.x;
+    const int my_tiles = first < n_tiles ? (n_tiles - first + stride - 1) / stride : 0;
+    const long long total = (long long)my_tiles * num_kb;     // K blocks this CTA loads, over all its tiles
+
+    auto tile_of = [&](long long it, int& tm, int& tn, int& kb) {
+        const int t = first + (int)(it / num_kb) * stride;
+        kb = (int)(it % num_kb);
+        tm = t % tiles_m; tn = t / tiles_m;
+    };
+    auto load_weights = [&](long long it) {
+        int tm, tn, kb; tile_of(it, tm, tn, kb);
+        const int s = (int)(it % PSTAGES);
+        mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+        tma_load_2d(smem + (size_t)s * STAGE_BYTES + A_BYTES, &map_q, &full_bar[s], kb * BLOCK_K, tn * PBN);
+    };
+    auto load_activations = [&](long long it) {
+        int tm, tn, kb; tile_of(it, tm, tn, kb);
+        const int s = (int)(it % PSTAGES);
+        tma_load_2d(smem + (size_t)s * STAGE_BYTES, &map_p, &full_bar[s], kb * BLOCK_K, tm * TILE_P);
+    };
+
+    pdl_launch_dependents();
+    long long issued = 0;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PSTAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_p) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_q) : "memory");
+        for (; issued < total && issued < PSTAGES; ++issued) load_weights(issued);
+    }
+    if (warp == 1) {
+        tmem_alloc(&tmem_base_smem, 512);
+        tmem_relinquish();
+    }
+    pdl_wait();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_smem;
+    bool ok = true;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (long long it = 0; it < issued; ++it) load_activations(it);
+            for (long long it = issued; it < total && ok; ++it) {
+                const int s = (int)(it % PSTAGES);
+                const uint32_t ph = (uint32_t)((it / PSTAGES) & 1);
+                ok = mbar_wait(&empty_bar[s], ph ^ 1, p.err, 11);
+                if (!ok) break;
+                load_weights(it);
+                load_activations(it);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc(PBN);
+            long long it = 0;
+            for (int t = 0; t < my_tiles && ok; ++t) {
+                const int acc = t & 1;
+                const uint32_t acc_ph = (uint32_t)((t >> 1) & 1);
+                ok = mbar_wait(&acc_empty[acc], acc_ph ^ 1, p.err, 12);     // the epilogue has drained this accumulator
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * PBN);
+                for (int kb = 0; kb < num_kb && ok; ++kb, ++it) {
+                    const int s = (int)(it % PSTAGES);
+                    const uint32_t ph = (uint32_t)((it / PSTAGES) & 1);
+                    ok = mbar_wait(&full_bar[s], ph, p.err, 13);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem + (size_t)s * STAGE_BYTES);
+                    const uint64_t adesc = smem_desc_sw128(a_addr);
+                    const uint64_t bdesc = smem_desc_sw128(a_addr + A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
+                        umma_bf16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(&empty_bar[s]);
+                }
+                umma_commit(&acc_full[acc]);
+            }
+        }
+    } else {
+        const int quad = warp & 3;
+        const int row_in_tile = quad * 32 + lane;
+        for (int t = 0; t < my_tiles && ok; ++t) {
+            const int acc = t & 1;
+            const uint32_t acc_ph = (uint32_t)((t >> 1) & 1);
+            const int tile = first + t * stride;
+            const int tm = tile % tiles_m, tn = tile / tiles_m;
+            ok = mbar_wait(&acc_full[acc], acc_ph, p.err, 14);
+            if (!ok) break;
+            tc_fence_after();
+            const int lane_row = tm * TILE_P + row_in_tile;
+#pragma unroll 1
+            for (int c = 0; c < PBN; c += 32) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * PBN + c), r);
+                tmem_ld_wait();
+                float v[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                store_tile_row<PBN, false>(p, lane_row, tn * PBN + c, v, 32);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[acc])) : "memory");
+            }
+        }
+    }
+    if (!ok) {
+        const unsigned long long t0 = global_ns();
+        while (global_ns() - t0 < 1000000ull) __nanosleep(1000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
     }
 }
 
@@ -450,8 +615,7 @@ int launch(const CUtensorMap& mp, const CUtensorMap& mq, const Params& p, dim3 g
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    gemm_tc_kernel<BN, STAGES, SWAP><<<grid, NUM_THREADS, smem, stream>>>(mp, mq, p);
-    return tnx_launch_status();
+    return tnx_launch_ex(1, gemm_tc_kernel<BN, STAGES, SWAP>, grid, dim3(NUM_THREADS), smem, stream, mp, mq, p);
 }
 
 }  // namespace
@@ -465,9 +629,10 @@ TNX_EXPORT int tnx_gemm_tc_plan(int M, int N, int K, int n_sms, int* splits, lon
     const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
     const int tiles = (N + TILE_P - 1) / TILE_P;
     const int kb = (K + BLOCK_K - 1) / BLOCK_K;
-    int s = n_sms / tiles;
+    int s = (2 * n_sms + tiles / 2) / tiles;   // two CTAs fit on an SM: aim at 2 x SMs CTAs
+    const int cap = bn == 16 ? 12 : (bn == 32 ? 8 : 4);   // the partial tiles grow with the tokens
     if (s > kb / 4) s = kb / 4;
-    if (s > 16) s = 16;
+    if (s > cap) s = cap;
     if (s < 1) s = 1;
     const int per = (kb + s - 1) / s;
     s = (kb + per - 1) / per;                 // no empty split
@@ -494,9 +659,32 @@ TNX_EXPORT int tnx_gemm_tc(const void* A, const void* W, const float* bias, cons
     CUtensorMap mp, mq;
     if (M > 64) {
         p.rows_p = M; p.rows_q = N; p.splits = 1; p.kb_per_split = kb;
-        if (!make_map(&mp, A, M, K, lda, TILE_P) || !make_map(&mq, W, N, K, ldw, 128)) return TNX_ERR_UNSUPPORTED;
-        dim3 grid((M + TILE_P - 1) / TILE_P, (N + 127) / 128, 1);
-        return launch<128, 6, false>(mp, mq, p, grid, stream);
+        if (!make_map(&mp, A, M, K, lda, TILE_P)) return TNX_ERR_UNSUPPORTED;
+        int dev = 0, sms = 148;
+        cudaGetDevice(&dev);
+        static int cached_sms[64] = {0};
+        if (dev >= 0 && dev < 64) {
+            if (!cached_sms[dev]) cudaDeviceGetAttribute(&cached_sms[dev], cudaDevAttrMultiProcessorCount, dev);
+            sms = cached_sms[dev];
+        }
+        const int tiles_m = (M + TILE_P - 1) / TILE_P, tiles_n = (N + PBN - 1) / PBN;
+        // Few 128 x 256 tiles would leave SMs idle: 128 x 128 tiles, one per CTA, fill the GPU better then.
+        if (tiles_m * tiles_n * 4 < sms * 3) {
+            if (!make_map(&mq, W, N, K, ldw, 128)) return TNX_ERR_UNSUPPORTED;
+            dim3 grid((M + TILE_P - 1) / TILE_P, (N + 127) / 128, 1);
+            return launch<128, 6, false>(mp, mq, p, grid, stream);
+        }
+        if (!make_map(&mq, W, N, K, ldw, PBN)) return TNX_ERR_UNSUPPORTED;
+        constexpr size_t smem = (size_t)PSTAGES * (TILE_P * BLOCK_K * 2 + PBN * BLOCK_K * 2) + 1024;
+        static bool configured = false;
+        if (!configured) {
+            cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+            configured = true;
+        }
+        const int ctas = tiles_m * tiles_n < sms ? tiles_m * tiles_n : sms;
+        return tnx_launch_ex(1, gemm_tc_persistent_kernel, dim3(ctas), dim3(NUM_THREADS), smem, stream, mp, mq, p,
+                             tiles_m, tiles_n);
     }
     if (splits < 1) splits = 1;
     if (splits > 1 && (!scratch || !counters)) return TNX_ERR_BAD_ARG;
@@ -504,7 +692,8 @@ TNX_EXPORT int tnx_gemm_tc(const void* A, const void* W, const float* bias, cons
     const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
     if (!make_map(&mp, W, N, K, ldw, TILE_P) || !make_map(&mq, A, M, K, lda, bn)) return TNX_ERR_UNSUPPORTED;
     dim3 grid((N + TILE_P - 1) / TILE_P, 1, splits);
-    if (bn == 16) return launch<16, 8, true>(mp, mq, p, grid, stream);
-    if (bn == 32) return launch<32, 8, true>(mp, mq, p, grid, stream);
-    return launch<64, 8, true>(mp, mq, p, grid, stream);
+    // stage counts that let two CTAs share an SM's shared memory
+    if (bn == 16) return launch<16, 6, true>(mp, mq, p, grid, stream);
+    if (bn == 32) return launch<32, 5, true>(mp, mq, p, grid, stream);
+    return launch<64, 4, true>(mp, mq, p, grid, stream);
 }

@@ -9,6 +9,8 @@ template <typename T>
 __global__ void kv_append_kernel(const T* __restrict__ k_src, const T* __restrict__ v_src, int src_stride,
                                  const int* __restrict__ slot_mapping, T* __restrict__ cache,
                                  int n_kv_heads, int head_dim, int page_size) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int n = blockIdx.x, h = blockIdx.y;
     const int slot = slot_mapping[n];
     if (slot < 0) return;                       // a padded row of a captured batch
@@ -32,10 +34,8 @@ TNX_EXPORT int tnx_kv_append(const void* k_src, const void* v_src, int src_strid
     dim3 grid(N, n_kv_heads);
     const int threads = head_dim >= 128 ? 128 : (head_dim >= 64 ? 64 : 32);
     if (is_bf16)
-        kv_append_kernel<bf16><<<grid, threads, 0, stream>>>((const bf16*)k_src, (const bf16*)v_src, src_stride,
-                                                             slot_mapping, (bf16*)cache, n_kv_heads, head_dim, page_size);
-    else
-        kv_append_kernel<float><<<grid, threads, 0, stream>>>((const float*)k_src, (const float*)v_src, src_stride,
-                                                              slot_mapping, (float*)cache, n_kv_heads, head_dim, page_size);
-    return tnx_launch_status();
+        return tnx_launch_pdl(kv_append_kernel<bf16>, grid, dim3(threads), 0, stream, (const bf16*)k_src, (const bf16*)v_src,
+                              src_stride, slot_mapping, (bf16*)cache, n_kv_heads, head_dim, page_size);
+    return tnx_launch_pdl(kv_append_kernel<float>, grid, dim3(threads), 0, stream, (const float*)k_src, (const float*)v_src,
+                          src_stride, slot_mapping, (float*)cache, n_kv_heads, head_dim, page_size);
 }

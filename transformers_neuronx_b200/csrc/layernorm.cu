@@ -12,6 +12,8 @@ __global__ void layer_norm_kernel(const float* __restrict__ x, const int* __rest
                                   float eps, float* __restrict__ out_f32, TA* __restrict__ out_act, int H) {
     extern __shared__ float row[];
     __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     const float* src = x + (size_t)(rows ? rows[r] : r) * H;
     float s = 0.f;
@@ -41,6 +43,8 @@ __global__ void layer_norm_kernel(const float* __restrict__ x, const int* __rest
 template <typename TA>
 __global__ void pick_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows,
                                  float* __restrict__ out_f32, TA* __restrict__ out_act, int H) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     const float* src = x + (size_t)(rows ? rows[r] : r) * H;
     for (int c = threadIdx.x; c < H; c += blockDim.x) {
@@ -59,19 +63,17 @@ TNX_EXPORT int tnx_layer_norm(const float* x, const int* rows, const float* gamm
     const size_t smem = (size_t)H * sizeof(float);
     if (act_bf16) {
         if (smem + 1024 > 48 * 1024) cudaFuncSetAttribute(layer_norm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        layer_norm_kernel<bf16><<<n_rows, threads, smem, stream>>>(x, rows, gamma, beta, eps, out_f32, (bf16*)out_act, H);
+        return tnx_launch_pdl(layer_norm_kernel<bf16>, dim3(n_rows), dim3(threads), smem, stream, x, rows, gamma, beta, eps, out_f32, (bf16*)out_act, H);
     } else {
         if (smem + 1024 > 48 * 1024) cudaFuncSetAttribute(layer_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        layer_norm_kernel<float><<<n_rows, threads, smem, stream>>>(x, rows, gamma, beta, eps, out_f32, (float*)out_act, H);
+        return tnx_launch_pdl(layer_norm_kernel<float>, dim3(n_rows), dim3(threads), smem, stream, x, rows, gamma, beta, eps, out_f32, (float*)out_act, H);
     }
-    return tnx_launch_status();
 }
 
 TNX_EXPORT int tnx_pick_rows(const float* x, const int* rows, float* out_f32, void* out_act,
                              int n_rows, int H, int act_bf16, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     const int threads = H >= 1024 ? 256 : 128;
-    if (act_bf16) pick_rows_kernel<bf16><<<n_rows, threads, 0, stream>>>(x, rows, out_f32, (bf16*)out_act, H);
-    else pick_rows_kernel<float><<<n_rows, threads, 0, stream>>>(x, rows, out_f32, (float*)out_act, H);
-    return tnx_launch_status();
+    if (act_bf16) return tnx_launch_pdl(pick_rows_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, x, rows, out_f32, (bf16*)out_act, H);
+    return tnx_launch_pdl(pick_rows_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, rows, out_f32, (float*)out_act, H);
 }

@@ -56,6 +56,8 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
     __shared__ unsigned int sh_prefix, sh_remaining;
     __shared__ unsigned long long sh_above, sh_total;
     __shared__ int sh_owner;
+    pdl_launch_dependents();
+    pdl_wait();
 
     const int r = blockIdx.x, tid = threadIdx.x;
     const float* row = logits + (size_t)r * ld;
@@ -219,7 +221,6 @@ TNX_EXPORT int tnx_sample(const float* logits, int ld, int n_rows, int V, const 
                           const unsigned long long* counters, int suppress_id, int* out, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (V <= 0 || ld < V) return TNX_ERR_BAD_ARG;
-    sample_kernel<<<n_rows, THREADS, 0, stream>>>(logits, ld, V, temperature, top_k, top_p, seeds, counters,
-                                                  suppress_id, out);
-    return tnx_launch_status();
+    return tnx_launch_pdl(sample_kernel, dim3(n_rows), dim3(THREADS), 0, stream, logits, ld, V, temperature, top_k, top_p,
+                          seeds, counters, suppress_id, out);
 }

@@ -18,6 +18,7 @@ import numpy as np
 import torch
 
 from ..cache import CacheManager, CacheStorage, OutOfPages, group_needs
+from ..kernels import ops
 from ..parts.base import StepContext
 
 
@@ -258,13 +259,17 @@ class StepRunner:
                 return self.model.forward(ctx)[:len(entries)]
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
+            n0 = ops.launch_count()
             with torch.cuda.graph(graph, pool=self._graph_pool):
                 g["logits"] = self.model.forward(ctx)
+            g["kernels"] = ops.launch_count() - n0       # recorded, not run
+            ops.add_launches(-g["kernels"])
             g["graph"] = graph
             if self._graph_pool is None:
                 self._graph_pool = graph.pool()
             # the capture recorded the kernels without running them: fall through to the replay
         g["graph"].replay()
+        ops.add_launches(g["kernels"])
         g["runs"] += 1
         return g["logits"][:len(entries)]
 

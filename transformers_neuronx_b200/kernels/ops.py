@@ -22,8 +22,14 @@ _launches = 0
 
 
 def launch_count() -> int:
-    """How many of this package's kernels have been launched by this process."""
+    """How many of this package's kernels have been launched by this process (kernels replayed
+    from a CUDA graph are added by the code that replays it)."""
     return _launches
+
+
+def add_launches(n: int) -> None:
+    global _launches
+    _launches += int(n)
 
 
 def _check(code: int, what: str) -> None:
