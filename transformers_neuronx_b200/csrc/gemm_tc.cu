@@ -157,14 +157,22 @@ __device__ __forceinline__ void store_tile_row(const Params& p, int lane_row, in
         // P axis = feature n, Q axis = token m: lanes of a warp write consecutive n.
         const int n = lane_row;
         const float b = p.bias ? p.bias[n] : 0.f;
+        // The residual may be the output itself: read all of it before the first store, so that
+        // the loads are in flight together instead of each waiting behind the store before it.
+        float res[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const int m = col0 + j;
+            res[j] = (p.residual && j < ncols && m < p.rows_q) ? __ldcg(p.residual + (size_t)m * p.ldc + n) : 0.f;
+        }
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
             const int m = col0 + j;
             if (j < ncols && m < p.rows_q) {
                 float x = v[j] + b;
                 if (p.relu) x = fmaxf(x, 0.f);
+                x += res[j];
                 const size_t o = (size_t)m * p.ldc + n;
-                if (p.residual) x += p.residual[o];
                 if (p.c_is_bf16) ((bf16*)p.C)[o] = __float2bfloat16_rn(x);
                 else ((float*)p.C)[o] = x;
             }
