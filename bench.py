@@ -176,6 +176,42 @@ def time_decode(model, cfg, batch, steps, warmup, use_engine=False):
     return ms, launches, h2d, batch * 4
 
 
+def time_e2e(model, cfg, batch, steps, warmup):
+    """Decode tokens per second through the Python entry point's engine: requests are submitted as
+    host token lists, prefilled by the scheduler, and then exactly K decode steps of
+    LLMEngine.step() are timed with the host's clock.  Every step packs its inputs into pinned host
+    memory, copies them to the device, runs the model, samples on the device and reads the sampled
+    ids back to the host."""
+    import torch
+    from transformers_neuronx_b200.config import EngineConfig
+    from transformers_neuronx_b200.engine import LLMEngine
+    total = steps + warmup
+    prompt_len = CONTEXT - total - 1
+    eng = LLMEngine(model, EngineConfig(dtype="bfloat16", max_num_seqs=batch, max_batch_tokens=batch * prompt_len,
+                                        max_tokens=batch * CONTEXT, max_model_len=CONTEXT))   # all prompts in one step
+    g = torch.Generator().manual_seed(3)
+    for b in range(batch):
+        prompt = torch.randint(3, cfg.vocab_size, (prompt_len,), generator=g).tolist()
+        eng.add_request(prompt, total + 1, stop_on_eos=False)
+    while any(r.computed < len(r.prompt) for r in eng.scheduler.running) or eng.scheduler.waiting:
+        eng.step()                                            # prefill (not timed)
+    for _ in range(warmup):
+        eng.step()
+    torch.cuda.synchronize()
+    run0 = eng.stats["tokens_run"]
+    h2d = 0
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        eng.step()
+        h2d = max(h2d, eng.runner.last_h2d_bytes)
+    torch.cuda.synchronize()
+    ms = (time.perf_counter() - t0) * 1e3 / steps
+    assert eng.stats["tokens_run"] - run0 == batch * steps, "every timed step must decode the whole batch"
+    del eng
+    torch.cuda.empty_cache()
+    return ms, h2d, batch * 4
+
+
 def time_prefill(model, cfg, steps, warmup):
     import torch
     from transformers_neuronx_b200.engine import StepEntry, StepRunner
@@ -241,7 +277,7 @@ def main():
     ms, launches, _, _ = time_decode(model, cfg, a.batch, a.steps, a.warmup)
     clk = clocks.stop()
     value = a.batch / (ms / 1e3)
-    e2e_ms, _, h2d, d2h = time_decode(model, cfg, a.batch, a.steps, a.warmup, use_engine=True)
+    e2e_ms, h2d, d2h = time_e2e(model, cfg, a.batch, a.steps, a.warmup)
     ctx_mean = CONTEXT - a.steps / 2
     nbytes = decode_bytes(model, cfg, a.batch, ctx_mean)
     achieved = nbytes / (ms / 1e3) / 1e9
