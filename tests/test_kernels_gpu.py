@@ -174,7 +174,7 @@ class PagedCase:
             if ql == 1:
                 decode_rows.append(row)
             else:
-                for q0 in range(0, ql, 64):
+                for q0 in range(0, ql, ops().ATTN_PREFILL_TILE):
                     tile_req.append(r); tile_q0.append(q0)
             row += ql
         mb = max(len(t) for t in tables)

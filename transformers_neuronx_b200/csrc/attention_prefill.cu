@@ -1,13 +1,14 @@
 // Causal attention of prompt portions over the paged bfloat16 cache (flash style: one pass over the
 // keys with an online softmax, nothing of size tokens x tokens is stored).
 //
-// Work item = (request, tile of 64 of its query rows, head).  The queries of a portion sit at
+// Work item = (request, tile of 128 of its query rows, head).  The queries of a portion sit at
 // positions ctx_len .. ctx_len + q_len - 1 of their request and read the keys 0 .. their own
 // position (or the last `window` of them) from the pages of the request's block table: the keys
 // and values of this very portion were written to the pages before the kernel runs.
 //
-// Four warps, 16 query rows each.  K and V tiles of 64 keys (four pages) are copied to shared
-// memory with cp.async (16-byte chunks, XOR-swizzled rows); S = Q K^T and O += P V run on tensor
+// Eight warps, 16 query rows each.  K and V tiles of 64 keys (four pages) are copied to shared
+// memory with cp.async (16-byte chunks, XOR-swizzled rows) into two buffers, the next tile while
+// the current one is used; S = Q K^T and O += P V run on tensor
 // cores (mma.sync m16n8k16, bf16 in, 32-bit accumulate); scores, softmax and the running sums are
 // 32-bit.  HEAD is the head size rounded up to 64, 128 or 256; the columns beyond the real head
 // size are zero in shared memory.
@@ -15,7 +16,7 @@
 
 namespace {
 
-constexpr int BQ = 64, BKV = 64, PAGE = 16, WARPS = 4;
+constexpr int BQ = 128, BKV = 64, PAGE = 16, WARPS = 8;
 
 struct PrefillParams {
     const bf16* q; int q_stride;
@@ -36,6 +37,7 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -49,6 +51,11 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
     return *(uint32_t*)&h;
@@ -61,17 +68,19 @@ __device__ __forceinline__ uint32_t swz(int row, int chunk) {
 }
 
 template <int HEAD>
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(WARPS * 32, HEAD <= 128 ? 2 : 1)
 attention_prefill_kernel(const PrefillParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int KV_BYTES = BKV * HEAD * 2;
     uint8_t* sQ = smem;
-    uint8_t* sK = sQ + BQ * HEAD * 2;
-    uint8_t* sV = sK + BKV * HEAD * 2;
+    uint8_t* sKV = sQ + BQ * HEAD * 2;             // [2 buffers][K tile, V tile]
     pdl_launch_dependents();
     pdl_wait();
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int item = blockIdx.x, h = blockIdx.y;
+    // Work items are listed in ascending position: the last have the most keys.  Heaviest first, so
+    // that the short ones fill the tail.
+    const int item = gridDim.x - 1 - blockIdx.x, h = blockIdx.y;
     const int req = p.tile_req[item], q0 = p.tile_q0[item];
     const int qs = p.q_start[req], ql = p.q_len[req], ctx = p.ctx_len[req];
     const int rows = min(BQ, ql - q0);                       // valid query rows of this tile
@@ -84,7 +93,7 @@ attention_prefill_kernel(const PrefillParams p) {
     const int kv_total = ctx + ql;                           // keys of the request that exist
 
     // zero the padding columns (and everything else) once
-    for (int i = tid; i < (BQ + 2 * BKV) * HEAD * 2 / 16; i += WARPS * 32) ((uint4*)smem)[i] = make_uint4(0, 0, 0, 0);
+    for (int i = tid; i < (BQ + 4 * BKV) * HEAD * 2 / 16; i += WARPS * 32) ((uint4*)smem)[i] = make_uint4(0, 0, 0, 0);
     __syncthreads();
     // Q tile
     for (int i = tid; i < BQ * real_chunks; i += WARPS * 32) {
@@ -105,8 +114,9 @@ attention_prefill_kernel(const PrefillParams p) {
     if (p.window > 0) key_begin = max(0, pos0 - p.window + 1) / BKV * BKV;
     const size_t head_block = (size_t)PAGE * d;
 
-    for (int k0 = key_begin; k0 <= pos_last; k0 += BKV) {
-        __syncthreads();                                     // the previous tile has been read by all warps
+    auto load_tile = [&](int k0, int buf) {
+        uint8_t* sK = sKV + (size_t)buf * 2 * KV_BYTES;
+        uint8_t* sV = sK + KV_BYTES;
         for (int i = tid; i < BKV * real_chunks; i += WARPS * 32) {
             const int r = i / real_chunks, c = i % real_chunks;
             const int key = k0 + r;
@@ -121,8 +131,17 @@ attention_prefill_kernel(const PrefillParams p) {
             }
         }
         cp_async_commit();
-        cp_async_wait_all();
+    };
+    load_tile(key_begin, 0);
+    int tile_no = 0;
+    for (int k0 = key_begin; k0 <= pos_last; k0 += BKV, ++tile_no) {
+        const int buf = tile_no & 1;
+        const bool has_next = k0 + BKV <= pos_last;
+        if (has_next) load_tile(k0 + BKV, buf ^ 1);          // its buffer was released by the barrier below
+        if (has_next) cp_async_wait_one(); else cp_async_wait_all();
         __syncthreads();
+        const uint8_t* sK = sKV + (size_t)buf * 2 * KV_BYTES;
+        const uint8_t* sV = sK + KV_BYTES;
 
         // ---- S = Q K^T for this warp's 16 rows x 64 keys ----------------------------------------
         float s[BKV / 8][4];
@@ -145,28 +164,39 @@ attention_prefill_kernel(const PrefillParams p) {
             }
         }
         // ---- mask, online softmax ------------------------------------------------------------------
+        // The running maximum is kept on the raw scores (the scale is positive); one FMA folds the
+        // scale and the maximum into the argument of ex2.  Only tiles that reach past the smallest
+        // position of this warp's rows (or fall partly behind the window) need the mask.
+        const int warp_pos_lo = pos0 + warp * 16, warp_pos_hi = warp_pos_lo + 15;
+        bool need_mask = k0 + BKV - 1 > warp_pos_lo;
+        if (p.window > 0) need_mask = need_mask || (k0 <= warp_pos_hi - p.window);
+        if (need_mask) {
+#pragma unroll
+            for (int nt = 0; nt < BKV / 8; ++nt) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = k0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+                    const int qp = (e < 2) ? qpos_lo : qpos_hi;
+                    bool ok = key <= qp;
+                    if (p.window > 0) ok = ok && key > qp - p.window;
+                    if (!ok) s[nt][e] = -INFINITY;
+                }
+            }
+        }
         float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
         for (int nt = 0; nt < BKV / 8; ++nt) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int key = k0 + nt * 8 + (lane & 3) * 2 + (e & 1);
-                const int qp = (e < 2) ? qpos_lo : qpos_hi;
-                bool ok = key <= qp;
-                if (p.window > 0) ok = ok && key > qp - p.window;
-                const float v = ok ? s[nt][e] * p.scale_log2 : -INFINITY;
-                s[nt][e] = v;
-                mx[e >> 1] = fmaxf(mx[e >> 1], v);
-            }
+            mx[0] = fmaxf(mx[0], fmaxf(s[nt][0], s[nt][1]));
+            mx[1] = fmaxf(mx[1], fmaxf(s[nt][2], s[nt][3]));
         }
-        float corr[2], m_use[2];
+        float corr[2], m_scaled[2];
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
             mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
             const float m_new = fmaxf(m_run[r], mx[r]);
-            m_use[r] = (m_new == -INFINITY) ? 0.f : m_new;
-            corr[r] = (m_run[r] == -INFINITY) ? 0.f : exp2f(m_run[r] - m_use[r]);
+            m_scaled[r] = (m_new == -INFINITY) ? 0.f : m_new * p.scale_log2;
+            corr[r] = (m_run[r] == -INFINITY) ? 0.f : ex2_approx(m_run[r] * p.scale_log2 - m_scaled[r]);
             m_run[r] = m_new;
             l_run[r] *= corr[r];
         }
@@ -179,7 +209,7 @@ attention_prefill_kernel(const PrefillParams p) {
         for (int nt = 0; nt < BKV / 8; ++nt) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const float pv = exp2f(s[nt][e] - m_use[e >> 1]);      // exp2(-inf) = 0 for masked keys
+                const float pv = ex2_approx(fmaf(s[nt][e], p.scale_log2, -m_scaled[e >> 1]));   // ex2(-inf) = 0
                 s[nt][e] = pv;
                 rs[e >> 1] += pv;
             }
@@ -203,6 +233,7 @@ attention_prefill_kernel(const PrefillParams p) {
                 mma_bf16(o[2 * nn + 1], a, b[2], b[3]);
             }
         }
+        __syncthreads();                                     // every warp is done with this buffer
     }
     // ---- finish: rows' sums over the quad, normalise, store ------------------------------------------
 #pragma unroll
@@ -227,7 +258,7 @@ attention_prefill_kernel(const PrefillParams p) {
 
 template <int HEAD>
 int launch(const PrefillParams& p, int n_items, cudaStream_t stream) {
-    constexpr int smem = (BQ + 2 * BKV) * HEAD * 2;
+    constexpr int smem = (BQ + 4 * BKV) * HEAD * 2;
     static bool configured = false;
     if (!configured && smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<HEAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);

@@ -153,7 +153,7 @@ class StepRunner:
             if hb.q_len[r] == 1:
                 decode_rows.append(hb.q_start[r])
             else:
-                for q0 in range(0, hb.q_len[r], 64):
+                for q0 in range(0, hb.q_len[r], ops.ATTN_PREFILL_TILE):
                     tile_req.append(r); tile_q0.append(q0)
         if pad_rows is not None:
             logit_rows = list(range(Np))

@@ -358,9 +358,12 @@ def attention_decode(q, cache, block_tables, token_request, positions, out, n_he
            "attention_decode")
 
 
+ATTN_PREFILL_TILE = 128      # query rows of one work item of the prefill attention kernel
+
+
 def attention_prefill(q, cache, block_tables, tile_req, tile_q0, q_start, q_len, ctx_len, out, n_heads, scale,
                       window=0, n_items=None):
-    """Causal attention of prompt portions: work items (request, first row of a 64-row tile)."""
+    """Causal attention of prompt portions: work items (request, first row of an ATTN_PREFILL_TILE-row tile)."""
     lib = _build.load("attention_prefill")
     _need(cache, "cache", torch.bfloat16, 5)
     N, width, q_stride = _rows_2d(q, "q")

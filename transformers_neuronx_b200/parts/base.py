@@ -49,7 +49,7 @@ class StepContext:
         self.page_size = 0
         self.decode_only = False              # every request has exactly one row
         self.max_ctx = 0                      # longest context (after this step) in the batch
-        self.tile_req = None                  # [tiles] request of each 64-row tile of a portion
+        self.tile_req = None                  # [tiles] request of each tile of query rows of a portion
         self.tile_q0 = None                   # [tiles] its first row within the portion
         self.decode_rows = None               # rows of requests that have exactly one row
         self.n_prefill_tiles = 0
