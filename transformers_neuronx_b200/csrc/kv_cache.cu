@@ -3,26 +3,31 @@
 // A cache is one tensor [num_pages, 2 (key, value), n_kv_heads, page_size, head_dim]: for one
 // head the page_size rows of a page are contiguous.  `slot_mapping[n]` = page * page_size + row
 // for token n, made on the host from the request's block table.
+#include <type_traits>
+
 #include "common.cuh"
 
-template <typename T>
+// One block per token; each thread moves 16-byte pieces (VEC elements) of the token's keys and values.
+template <typename T, int VEC>
 __global__ void kv_append_kernel(const T* __restrict__ k_src, const T* __restrict__ v_src, int src_stride,
                                  const int* __restrict__ slot_mapping, T* __restrict__ cache,
                                  int n_kv_heads, int head_dim, int page_size) {
     pdl_launch_dependents();
     pdl_wait();
-    const int n = blockIdx.x, h = blockIdx.y;
+    const int n = blockIdx.x;
     const int slot = slot_mapping[n];
     if (slot < 0) return;                       // a padded row of a captured batch
     const int page = slot / page_size, row = slot % page_size;
     const size_t head_block = (size_t)page_size * head_dim;
-    T* kdst = cache + (((size_t)page * 2 + 0) * n_kv_heads + h) * head_block + (size_t)row * head_dim;
-    T* vdst = cache + (((size_t)page * 2 + 1) * n_kv_heads + h) * head_block + (size_t)row * head_dim;
-    const T* ks = k_src + (size_t)n * src_stride + (size_t)h * head_dim;
-    const T* vs = v_src + (size_t)n * src_stride + (size_t)h * head_dim;
-    for (int c = threadIdx.x; c < head_dim; c += blockDim.x) {
-        kdst[c] = ks[c];
-        vdst[c] = vs[c];
+    const int pieces_per_head = head_dim / VEC;
+    const int pieces = n_kv_heads * pieces_per_head;
+    typedef typename std::conditional<VEC == 1, T, uint4>::type Piece;
+    for (int i = threadIdx.x; i < 2 * pieces; i += blockDim.x) {
+        const int kv = i / pieces, j = i % pieces;
+        const int h = j / pieces_per_head, c = (j % pieces_per_head) * VEC;
+        const T* src = (kv ? v_src : k_src) + (size_t)n * src_stride + (size_t)h * head_dim + c;
+        T* dst = cache + (((size_t)page * 2 + kv) * n_kv_heads + h) * head_block + (size_t)row * head_dim + c;
+        *(Piece*)dst = *(const Piece*)src;
     }
 }
 
@@ -31,11 +36,15 @@ TNX_EXPORT int tnx_kv_append(const void* k_src, const void* v_src, int src_strid
                              int is_bf16, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (n_kv_heads <= 0 || head_dim <= 0 || page_size <= 0) return TNX_ERR_BAD_ARG;
-    dim3 grid(N, n_kv_heads);
-    const int threads = head_dim >= 128 ? 128 : (head_dim >= 64 ? 64 : 32);
-    if (is_bf16)
-        return tnx_launch_pdl(kv_append_kernel<bf16>, grid, dim3(threads), 0, stream, (const bf16*)k_src, (const bf16*)v_src,
-                              src_stride, slot_mapping, (bf16*)cache, n_kv_heads, head_dim, page_size);
-    return tnx_launch_pdl(kv_append_kernel<float>, grid, dim3(threads), 0, stream, (const float*)k_src, (const float*)v_src,
-                          src_stride, slot_mapping, (float*)cache, n_kv_heads, head_dim, page_size);
+    const int esz = is_bf16 ? 2 : 4, vec = 16 / esz;
+    const bool wide = head_dim % vec == 0 && src_stride % vec == 0 && ((uintptr_t)k_src % 16) == 0 &&
+                      ((uintptr_t)v_src % 16) == 0 && ((uintptr_t)cache % 16) == 0;
+    const int work = 2 * n_kv_heads * head_dim / (wide ? vec : 1);
+    const dim3 grid(N), block(work >= 256 ? 256 : (work >= 128 ? 128 : 64));
+#define KV_LAUNCH(T, V)                                                                                          \
+    tnx_launch_pdl(kv_append_kernel<T, V>, grid, block, 0, stream, (const T*)k_src, (const T*)v_src, src_stride, \
+                   slot_mapping, (T*)cache, n_kv_heads, head_dim, page_size)
+    if (is_bf16) return wide ? KV_LAUNCH(bf16, 8) : KV_LAUNCH(bf16, 1);
+    return wide ? KV_LAUNCH(float, 4) : KV_LAUNCH(float, 1);
+#undef KV_LAUNCH
 }

@@ -39,6 +39,60 @@ __global__ void layer_norm_kernel(const float* __restrict__ x, const int* __rest
     }
 }
 
+// The same with the row held in registers: four consecutive elements per load, NV loads per
+// thread (H == 4 * NV * threads exactly is not required: pieces beyond the row are skipped).
+template <typename TA, int NV>
+__global__ void layer_norm_reg_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+                                      const float* __restrict__ gamma, const float* __restrict__ beta,
+                                      float eps, float* __restrict__ out_f32, TA* __restrict__ out_act, int H) {
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const float4* src = (const float4*)(x + (size_t)(rows ? rows[r] : r) * H);
+    const int n4 = H / 4;
+    float4 v[NV];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        v[i] = c < n4 ? src[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    }
+    const float mean = block_sum(s, scratch) / (float)H;
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < n4) {
+            const float a = v[i].x - mean, b = v[i].y - mean, cc = v[i].z - mean, d = v[i].w - mean;
+            q += (a * a + b * b) + (cc * cc + d * d);
+        }
+    }
+    const float var = block_sum(q, scratch) / (float)H;
+    const float rstd = 1.0f / sqrtf(var + eps);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c >= n4) continue;
+        float4 y = make_float4((v[i].x - mean) * rstd, (v[i].y - mean) * rstd, (v[i].z - mean) * rstd, (v[i].w - mean) * rstd);
+        if (gamma) { const float4 g = ((const float4*)gamma)[c]; y.x *= g.x; y.y *= g.y; y.z *= g.z; y.w *= g.w; }
+        if (beta) { const float4 b = ((const float4*)beta)[c]; y.x += b.x; y.y += b.y; y.z += b.z; y.w += b.w; }
+        if (out_f32) ((float4*)(out_f32 + (size_t)r * H))[c] = y;
+        if (out_act) {
+            TA* dst = out_act + (size_t)r * H + 4 * c;
+            if constexpr (sizeof(TA) == 2) {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(y.x, y.y), hi = __floats2bfloat162_rn(y.z, y.w);
+                uint2 u;
+                u.x = *(uint32_t*)&lo; u.y = *(uint32_t*)&hi;
+                *(uint2*)dst = u;
+            } else {
+                *(float4*)dst = y;
+            }
+        }
+    }
+}
+
 // Copies (and converts) picked rows without normalising: the head of a model with no final norm.
 template <typename TA>
 __global__ void pick_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows,
@@ -59,6 +113,23 @@ TNX_EXPORT int tnx_layer_norm(const float* x, const int* rows, const float* gamm
                               int act_bf16, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (H <= 0 || (size_t)H * sizeof(float) > 200 * 1024) return TNX_ERR_UNSUPPORTED;
+    // Rows of a multiple of four elements, 16-byte aligned, up to 8,192 elements: the register kernel.
+    const bool aligned = H % 4 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)gamma % 16) == 0 &&
+                         ((uintptr_t)beta % 16) == 0 && ((uintptr_t)out_f32 % 16) == 0 && ((uintptr_t)out_act % 16) == 0;
+    if (aligned && H <= 8192) {
+        const int n4 = H / 4;
+        const int threads = n4 >= 1024 ? 256 : (n4 >= 256 ? 128 : 64);
+        const int nv = (n4 + threads - 1) / threads;
+#define LN_LAUNCH(TA, NV)                                                                                      \
+    tnx_launch_pdl(layer_norm_reg_kernel<TA, NV>, dim3(n_rows), dim3(threads), 0, stream, x, rows, gamma, beta, \
+                   eps, out_f32, (TA*)out_act, H)
+#define LN_PICK(TA)                                                                        \
+    (nv <= 1 ? LN_LAUNCH(TA, 1) : nv <= 2 ? LN_LAUNCH(TA, 2) : nv <= 4 ? LN_LAUNCH(TA, 4) : LN_LAUNCH(TA, 8))
+        if (act_bf16) return LN_PICK(bf16);
+        return LN_PICK(float);
+#undef LN_PICK
+#undef LN_LAUNCH
+    }
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     const size_t smem = (size_t)H * sizeof(float);
     if (act_bf16) {
