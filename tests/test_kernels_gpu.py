@@ -52,7 +52,8 @@ def test_gemm_simt_rows_do_not_depend_on_the_batch():
 
 
 TC_SHAPES = [(1, 128, 64), (3, 96, 320), (16, 4096, 1024), (17, 1000, 96), (33, 200, 136), (64, 512, 4096),
-             (65, 384, 256), (128, 128, 64), (200, 1000, 328), (300, 520, 1032), (2048, 768, 512)]
+             (65, 384, 256), (128, 128, 64), (200, 1000, 328), (300, 520, 1032), (2048, 768, 512),
+             (1024, 4096, 512), (1000, 4000, 328), (300, 9000, 136), (513, 7100, 72)]
 
 
 @pytest.mark.parametrize("M,N,K", TC_SHAPES)

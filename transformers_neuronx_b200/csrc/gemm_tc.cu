@@ -150,7 +150,8 @@ struct Params {
 };
 
 template <int BN, bool SWAP>
-__device__ __forceinline__ void store_tile_row(const Params& p, int lane_row, int col0, const float (&v)[32], int ncols) {
+__device__ __forceinline__ void store_tile_row(const Params& p, int lane_row, int col0, const float (&v)[32], int ncols,
+                                               const float* bias_s = nullptr) {
     // lane_row: index on the P axis; col0..col0+ncols: indices on the Q axis.
     if (lane_row >= p.rows_p) return;
     if (SWAP) {
@@ -178,23 +179,31 @@ __device__ __forceinline__ void store_tile_row(const Params& p, int lane_row, in
             }
         }
     } else {
-        // P axis = token m, Q axis = feature n: a thread writes a run of its own row.
+        // P axis = token m, Q axis = feature n: a thread writes a run of its own row.  `bias_s`
+        // (shared memory, the tile's bias from column col0 on) is read by all lanes at one address.
         const int m = lane_row;
         const size_t rowo = (size_t)m * p.ldc;
         const bool full = (col0 + 32 <= p.rows_q) && ncols == 32 && (p.ldc % 8 == 0);
         float x[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-            const int n = col0 + j;
-            float t = v[j];
-            if (n < p.rows_q) {
-                if (p.bias) t += __ldg(p.bias + n);
-                if (p.relu) t = fmaxf(t, 0.f);
-                if (p.residual) t += p.residual[rowo + n];
-            }
-            x[j] = t;
-        }
         if (full) {
+            if (p.residual) {
+                const float4* rp = (const float4*)(p.residual + rowo + col0);
+                float4 rr[8];
+#pragma unroll
+                for (int q = 0; q < 8; ++q) rr[q] = __ldcg(rp + q);          // all loads before the first store
+#pragma unroll
+                for (int q = 0; q < 8; ++q) { x[4 * q] = rr[q].x; x[4 * q + 1] = rr[q].y; x[4 * q + 2] = rr[q].z; x[4 * q + 3] = rr[q].w; }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) x[j] = 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                float t = v[j];
+                if (p.bias) t += bias_s ? bias_s[j] : __ldg(p.bias + col0 + j);
+                if (p.relu) t = fmaxf(t, 0.f);
+                x[j] += t;
+            }
             if (p.c_is_bf16) {
                 uint4* dst = (uint4*)((bf16*)p.C + rowo + col0);
 #pragma unroll
@@ -213,6 +222,17 @@ __device__ __forceinline__ void store_tile_row(const Params& p, int lane_row, in
                 for (int q = 0; q < 8; ++q) dst[q] = make_float4(x[4 * q], x[4 * q + 1], x[4 * q + 2], x[4 * q + 3]);
             }
         } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const int n = col0 + j;
+                float t = v[j];
+                if (j < ncols && n < p.rows_q) {
+                    if (p.bias) t += __ldg(p.bias + n);
+                    if (p.relu) t = fmaxf(t, 0.f);
+                    if (p.residual) t += p.residual[rowo + n];
+                }
+                x[j] = t;
+            }
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
                 const int n = col0 + j;
@@ -306,7 +326,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 const uint32_t ph = (i / STAGES) & 1;
                 ok = mbar_wait(&full_bar[s], ph, p.err, 2);
                 if (!ok) break;
-                tc_fence_after();
                 const uint32_t a_addr = smem_u32(smem + (size_t)s * STAGE_BYTES);
                 const uint32_t b_addr = a_addr + A_BYTES;
                 const uint64_t adesc = smem_desc_sw128(a_addr);
@@ -431,6 +450,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     __shared__ uint64_t full_bar[PSTAGES], empty_bar[PSTAGES], acc_full[2], acc_empty[2];
     __shared__ uint32_t tmem_base_smem;
+    __shared__ float bias_tile[2][PBN];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_kb = (p.K + BLOCK_K - 1) / BLOCK_K;
@@ -505,7 +525,6 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
                     const uint32_t ph = (uint32_t)((it / PSTAGES) & 1);
                     ok = mbar_wait(&full_bar[s], ph, p.err, 13);
                     if (!ok) break;
-                    tc_fence_after();
                     const uint32_t a_addr = smem_u32(smem + (size_t)s * STAGE_BYTES);
                     const uint64_t adesc = smem_desc_sw128(a_addr);
                     const uint64_t bdesc = smem_desc_sw128(a_addr + A_BYTES);
@@ -525,6 +544,11 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
             const uint32_t acc_ph = (uint32_t)((t >> 1) & 1);
             const int tile = first + t * stride;
             const int tm = tile % tiles_m, tn = tile / tiles_m;
+            if (p.bias) {                                  // this tile's bias -> shared memory (epilogue threads only)
+                const int et = threadIdx.x - 64;
+                for (int j = et; j < PBN; j += 128) bias_tile[acc][j] = (tn * PBN + j < p.rows_q) ? p.bias[tn * PBN + j] : 0.f;
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+            }
             ok = mbar_wait(&acc_full[acc], acc_ph, p.err, 14);
             if (!ok) break;
             tc_fence_after();
@@ -537,7 +561,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
                 float v[32];
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-                store_tile_row<PBN, false>(p, lane_row, tn * PBN + c, v, 32);
+                store_tile_row<PBN, false>(p, lane_row, tn * PBN + c, v, 32, p.bias ? bias_tile[acc] + c : nullptr);
             }
             tc_fence_before();
             __syncwarp();
@@ -555,6 +579,203 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// ---- many tokens, CTA pairs: 256 x 256 tiles with tcgen05 cta_group::2 -------------------------------
+//
+// Two CTAs on neighbouring SMs form a cluster and share one MMA: CTA r of the pair holds rows
+// r*128.. of the A tile and rows r*128.. of the (256-row) B tile in its own shared memory, and the
+// 128 x 256 accumulator of its rows in its own tensor memory.  One thread of CTA 0 issues the MMAs
+// for both.  A stage is 32 KB per CTA instead of 48 KB for the same MMA work, so six stages fit
+// and each SM takes in a third fewer bytes per FLOP.  Each CTA loads its own tiles with TMA (no
+// multicast); loads of both CTAs complete the full-barrier of CTA 0; the MMA thread's commits
+// release the stage in both CTAs.
+constexpr int CSTAGES = 6;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// TMA load into this CTA's shared memory whose bytes are counted on a barrier given by its
+// shared::cluster address (CTA 0's barrier).
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"((unsigned long long)map), "r"(bar_cluster_addr), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+__host__ __device__ constexpr uint32_t instr_desc_pair(int n) {      // M = 256 over the pair
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
+                    const Params p, int tiles_m, int tiles_n) {
+    constexpr int A_BYTES = TILE_P * BLOCK_K * 2;             // 16 KB: this CTA's 128 rows of A
+    constexpr int B_BYTES = 128 * BLOCK_K * 2;                // 16 KB: this CTA's 128 rows of the 256-row B tile
+    constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    __shared__ uint64_t full_bar[CSTAGES], empty_bar[CSTAGES], acc_full[2], acc_empty[2];
+    __shared__ uint32_t tmem_base_smem;
+    __shared__ float bias_tile[2][256];
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+    const int num_kb = (p.K + BLOCK_K - 1) / BLOCK_K;
+    const int n_tiles = tiles_m * tiles_n;                    // 256 x 256 tiles
+    const int first = blockIdx.x >> 1, stride = gridDim.x >> 1;
+    const int my_tiles = first < n_tiles ? (n_tiles - first + stride - 1) / stride : 0;
+    const long long total = (long long)my_tiles * num_kb;
+
+    auto tile_of = [&](long long it, int& tm, int& tn, int& kb) {
+        const int t = first + (int)(it / num_kb) * stride;
+        kb = (int)(it % num_kb);
+        tm = t % tiles_m; tn = t / tiles_m;
+    };
+    // shared::cluster addresses of CTA 0's full barriers (the ones the MMA thread waits on)
+    auto full0 = [&](int s) { return map_to_cta(smem_u32(&full_bar[s]), 0); };
+    auto load_weights = [&](long long it) {
+        int tm, tn, kb; tile_of(it, tm, tn, kb);
+        const int s = (int)(it % CSTAGES);
+        if (leader) mbar_expect_tx(&full_bar[s], 2 * STAGE_BYTES);     // both CTAs' bytes land on this barrier
+        tma_load_2d_pair(smem + (size_t)s * STAGE_BYTES + A_BYTES, &map_q, full0(s), kb * BLOCK_K, tn * 256 + (int)rank * 128);
+    };
+    auto load_activations = [&](long long it) {
+        int tm, tn, kb; tile_of(it, tm, tn, kb);
+        const int s = (int)(it % CSTAGES);
+        tma_load_2d_pair(smem + (size_t)s * STAGE_BYTES, &map_p, full0(s), kb * BLOCK_K, tm * 256 + (int)rank * 128);
+    };
+
+    pdl_launch_dependents();
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < CSTAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 8); }   // 4 warps x 2 CTAs
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_p) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_q) : "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_smem)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();                                           // both CTAs' barriers exist before anything remote
+    tc_fence_after();
+    long long issued = 0;
+    if (threadIdx.x == 0)
+        for (; issued < total && issued < CSTAGES; ++issued) load_weights(issued);   // weights: before the dependency wait
+    pdl_wait();
+    const uint32_t tmem_base = tmem_base_smem;
+    bool ok = true;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (long long it = 0; it < issued; ++it) load_activations(it);
+            for (long long it = issued; it < total && ok; ++it) {
+                const int s = (int)(it % CSTAGES);
+                const uint32_t ph = (uint32_t)((it / CSTAGES) & 1);
+                ok = mbar_wait(&empty_bar[s], ph ^ 1, p.err, 21);
+                if (!ok) break;
+                load_weights(it);
+                load_activations(it);
+            }
+        }
+    } else if (warp == 1) {
+        if (leader && lane == 0) {
+            constexpr uint32_t idesc = instr_desc_pair(256);
+            long long it = 0;
+            for (int t = 0; t < my_tiles && ok; ++t) {
+                const int acc = t & 1;
+                const uint32_t acc_ph = (uint32_t)((t >> 1) & 1);
+                ok = mbar_wait(&acc_empty[acc], acc_ph ^ 1, p.err, 22);      // both CTAs drained this accumulator
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * 256);
+                for (int kb = 0; kb < num_kb && ok; ++kb, ++it) {
+                    const int s = (int)(it % CSTAGES);
+                    const uint32_t ph = (uint32_t)((it / CSTAGES) & 1);
+                    ok = mbar_wait(&full_bar[s], ph, p.err, 23);
+                    if (!ok) break;
+                    const uint32_t a_addr = smem_u32(smem + (size_t)s * STAGE_BYTES);
+                    const uint64_t adesc = smem_desc_sw128(a_addr);
+                    const uint64_t bdesc = smem_desc_sw128(a_addr + A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
+                        umma_bf16_pair(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    umma_commit_pair(map_to_cta(smem_u32(&empty_bar[s]), 0));    // the stage is free in both CTAs
+                    umma_commit_pair(map_to_cta(smem_u32(&empty_bar[s]), 1));
+                }
+                umma_commit_pair(map_to_cta(smem_u32(&acc_full[acc]), 0));
+                umma_commit_pair(map_to_cta(smem_u32(&acc_full[acc]), 1));
+            }
+        }
+    } else {
+        const int quad = warp & 3;
+        const int row_in_tile = quad * 32 + lane;
+        for (int t = 0; t < my_tiles && ok; ++t) {
+            const int acc = t & 1;
+            const uint32_t acc_ph = (uint32_t)((t >> 1) & 1);
+            const int tile = first + t * stride;
+            const int tm = tile % tiles_m, tn = tile / tiles_m;
+            if (p.bias) {                                  // this tile's bias -> shared memory (epilogue threads only)
+                const int et = threadIdx.x - 64;
+                for (int j = et; j < 256; j += 128) bias_tile[acc][j] = (tn * 256 + j < p.rows_q) ? p.bias[tn * 256 + j] : 0.f;
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+            }
+            ok = mbar_wait(&acc_full[acc], acc_ph, p.err, 24);
+            if (!ok) break;
+            tc_fence_after();
+            const int lane_row = tm * 256 + (int)rank * 128 + row_in_tile;
+#pragma unroll 1
+            for (int c = 0; c < 256; c += 32) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * 256 + c), r);
+                tmem_ld_wait();
+                float v[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                store_tile_row<256, false>(p, lane_row, tn * 256 + c, v, 32, p.bias ? bias_tile[acc] + c : nullptr);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[acc]), 0));
+        }
+    }
+    if (!ok) {
+        const unsigned long long t0 = global_ns();
+        while (global_ns() - t0 < 1000000ull) __nanosleep(1000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();                                           // neither CTA leaves while the other may still reach into it
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
     }
 }
 
@@ -681,6 +902,22 @@ TNX_EXPORT int tnx_gemm_tc(const void* A, const void* W, const float* bias, cons
             if (!make_map(&mq, W, N, K, ldw, 128)) return TNX_ERR_UNSUPPORTED;
             dim3 grid((M + TILE_P - 1) / TILE_P, (N + 127) / 128, 1);
             return launch<128, 6, false>(mp, mq, p, grid, stream);
+        }
+        static const int pair_mode = getenv("TNX_GEMM_PAIR") ? atoi(getenv("TNX_GEMM_PAIR")) : 1;
+        const int ptiles_m = (M + 255) / 256, ptiles_n = (N + 255) / 256;
+        if (pair_mode && M >= 256 && ptiles_m * ptiles_n * 8 >= sms * 3) {
+            if (!make_map(&mq, W, N, K, ldw, 128)) return TNX_ERR_UNSUPPORTED;
+            constexpr size_t psmem = (size_t)CSTAGES * (TILE_P * BLOCK_K * 2 + 128 * BLOCK_K * 2) + 1024;
+            static bool pconfigured = false;
+            if (!pconfigured) {
+                cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)psmem);
+                if (e != cudaSuccess) return (int)e;
+                pconfigured = true;
+            }
+            int pairs = sms / 2;
+            if (pairs > ptiles_m * ptiles_n) pairs = ptiles_m * ptiles_n;
+            return tnx_launch_ex(1, gemm_tc_pair_kernel, dim3(2 * pairs), dim3(NUM_THREADS), psmem, stream, mp, mq, p,
+                                 ptiles_m, ptiles_n);
         }
         if (!make_map(&mq, W, N, K, ldw, PBN)) return TNX_ERR_UNSUPPORTED;
         constexpr size_t smem = (size_t)PSTAGES * (TILE_P * BLOCK_K * 2 + PBN * BLOCK_K * 2) + 1024;
