@@ -52,7 +52,8 @@ class LLMEngine:
         plan: StepPlan = self.scheduler.schedule()
         entries, rows = [], []
         for it in plan.items:
-            toks = it.request.tokens[it.start:it.start + it.count]
+            all_tokens = it.request.tokens
+            toks = all_tokens[it.start:it.start + it.count] if it.count > 1 else [all_tokens[it.start]]
             entries.append(StepEntry(it.request.rid, toks, [it.count - 1] if it.sample else []))
             if it.sample:
                 rows.append(it.request)
@@ -70,6 +71,10 @@ class LLMEngine:
             host = ids.tolist()                       # the step's one device-to-host read
             sampled = {r.rid: t for r, t in zip(rows, host)}
         done = self.scheduler.commit(plan, sampled)
+        for r in done:
+            self.runner.forget(r.rid)
+        for r in plan.preempted:
+            self.runner.forget(r.rid)
         self.stats["steps"] += 1
         self.stats["tokens_run"] += plan.n_tokens
         self.stats["tokens_sampled"] += len(rows)

@@ -52,13 +52,20 @@ class Request:
     preemptions: int = 0
     arrival: int = 0
 
+    def __post_init__(self):
+        self._all = list(self.prompt) + list(self.output)      # prompt and output as one list, kept in step
+
     @property
     def tokens(self) -> List[int]:
-        return self.prompt + self.output
+        return self._all
 
     @property
     def total(self) -> int:
-        return len(self.prompt) + len(self.output)
+        return len(self._all)
+
+    def append_output(self, tok: int) -> None:
+        self.output.append(tok)
+        self._all.append(tok)
 
 
 @dataclass
@@ -133,11 +140,24 @@ class Scheduler:
         return True
 
     def _pages_free_after(self, plan: StepPlan) -> List[int]:
+        """Free pages of every group once the items planned so far have taken theirs."""
+        cached = getattr(plan, "_free", None)
+        if cached is not None and cached[0] == len(plan.items) and cached[2] == self.num_preemptions:
+            return list(cached[1])
         free = self.cache.free_pages()
         for it in plan.items:
             for g, n in enumerate(self.cache.pages_needed(it.request.rid, it.count)):
                 free[g] -= n
+        plan._free = (len(plan.items), list(free), self.num_preemptions)
         return free
+
+    def _take(self, plan: StepPlan, item: "Scheduled") -> None:
+        """Adds an item to the plan and keeps the running count of free pages current."""
+        free = self._pages_free_after(plan)
+        for g, n in enumerate(self.cache.pages_needed(item.request.rid, item.count)):
+            free[g] -= n
+        plan.items.append(item)
+        plan._free = (len(plan.items), free, self.num_preemptions)
 
     def _fits(self, plan: StepPlan, rid, count: int) -> bool:
         free = self._pages_free_after(plan)
@@ -170,22 +190,21 @@ class Scheduler:
                 if not self._preempt(plan, keep=req):
                     raise RuntimeError(f"request {req.rid!r} cannot get a page although it runs alone")
             if req in self.running:
-                plan.items.append(Scheduled(req, req.total - 1, 1, True))
+                self._take(plan, Scheduled(req, req.total - 1, 1, True))
                 budget -= 1
         # 2. portions of prompts of running requests, oldest first
+        planned = {id(i.request) for i in plan.items}
         for req in self.running:
             if budget <= 0:
                 break
             remaining = req.total - req.computed
-            if remaining <= 1 and any(i.request is req for i in plan.items):
-                continue
-            if any(i.request is req for i in plan.items):
+            if id(req) in planned:
                 continue
             n = min(remaining, budget, self.max_portion or remaining)
             n = self._largest_fitting(plan, req.rid, n)
             if n <= 0:
                 continue
-            plan.items.append(Scheduled(req, req.computed, n, req.computed + n == req.total))
+            self._take(plan, Scheduled(req, req.computed, n, req.computed + n == req.total))
             budget -= n
         # 3. admit waiting requests, first come first served
         while self.waiting and budget > 0 and len(self.running) < self.max_num_seqs and not plan.preempted:
@@ -206,7 +225,7 @@ class Scheduler:
             self.cache.add_request(req.rid)
             self.running.append(req)
             plan.admitted.append(req)
-            plan.items.append(Scheduled(req, req.computed, n, req.computed + n == req.total))
+            self._take(plan, Scheduled(req, req.computed, n, req.computed + n == req.total))
             budget -= n
         if not plan.items and self.has_work():
             raise RuntimeError("the scheduler found nothing to run although requests are pending "
@@ -224,7 +243,7 @@ class Scheduler:
             if not it.sample:
                 continue
             tok = int(sampled[req.rid])
-            req.output.append(tok)
+            req.append_output(tok)
             hit_eos = req.stop_on_eos and req.eos_token_id is not None and tok == req.eos_token_id
             if len(req.output) >= req.max_new_tokens or hit_eos:
                 req.finished = True

@@ -63,6 +63,9 @@ class StepRunner:
         self.max_graph_batch = max_graph_batch
         self._graphs = {}
         self._graph_pool = None
+        self._decode_layouts = {}
+        self._table_arrays = {}
+        self._arange_cache = None
 
     # ---- requests -------------------------------------------------------------------------------
     def add_request(self, rid) -> int:
@@ -70,6 +73,12 @@ class StepRunner:
 
     def finish(self, rid) -> None:
         self.cache.free_request(rid)
+        self.forget(rid)
+
+    def forget(self, rid) -> None:
+        """Drops what the runner keeps about a request whose pages were given back."""
+        for g in range(self.n_groups):
+            self._table_arrays.pop((rid, g), None)
 
     def pages_needed(self, entries: Sequence[StepEntry]) -> List[int]:
         tot = [0] * self.n_groups
@@ -233,11 +242,87 @@ class StepRunner:
             ctx_bucket *= 2
         return bucket, min(ctx_bucket, -(-self.max_model_len // self.page_size) * self.page_size)
 
+    def _pack_decode(self, entries, bucket: int, fixed_blocks: int):
+        """_pack for a step in which every request has one token, with little host work: the same
+        sections at the same offsets, filled with array operations; block tables are kept as arrays
+        per request and only their new entries are copied."""
+        R, ps, G = len(entries), self.page_size, self.n_groups
+        hb = HostBatch()
+        cache = self.cache
+        toks, starts = [], []
+        for e in entries:
+            starts.append(cache.append(e.rid, 1))
+            toks.append(int(e.tokens[0]))
+            hb.rids.append(e.rid)
+            hb.slots.append(cache.slot(e.rid))
+        hb.q_start = list(range(R)); hb.q_len = [1] * R; hb.ctx_len = starts
+        lay = self._decode_layouts.get((bucket, fixed_blocks))
+        if lay is None:
+            sizes = [bucket] * 8 + [0, 0, bucket]
+            for _ in range(G):
+                sizes += [bucket * fixed_blocks, bucket]
+            offs, o = [], 0
+            for sz in sizes:
+                offs.append(o)
+                o += (sz + 3) // 4 * 4
+            lay = (sizes, offs, o)
+            self._decode_layouts[(bucket, fixed_blocks)] = lay
+        sizes, offs, o = lay
+        slot = self._pinned_buffer(o)
+        host = slot[0].numpy()
+        pos = np.asarray(starts, dtype=np.int32)
+
+        def sec(i):
+            return host[offs[i]:offs[i] + sizes[i]]
+
+        ar = self._arange(bucket)
+        for i, vals, fill in ((0, toks, 0), (1, pos, 0), (2, ar[:R], -1), (3, ar[:R], 0), (4, 1, 0), (5, pos, 0), (6, hb.slots, 0)):
+            a = sec(i)
+            a[:R] = vals
+            a[R:] = fill
+        sec(7)[:] = ar
+        sec(10)[:] = ar
+        n_fixed = 11
+        for g in range(G):
+            bt = sec(n_fixed + 2 * g).reshape(bucket, fixed_blocks)
+            for r, e in enumerate(entries):
+                bt[r] = self._table_array(e.rid, g, fixed_blocks)
+            bt[R:] = -1
+            sm = sec(n_fixed + 2 * g + 1)
+            sm[:R] = bt[ar[:R], pos // ps] * ps + pos % ps
+            sm[R:] = -1
+        return hb, slot, o, offs, sizes, [fixed_blocks] * G, n_fixed, (R, R, bucket, bucket), (0, bucket)
+
+    def _arange(self, n: int):
+        if self._arange_cache is None or self._arange_cache.size < n:
+            self._arange_cache = np.arange(max(n, 256), dtype=np.int32)
+        return self._arange_cache[:n]
+
+    def _table_array(self, rid, g: int, width: int):
+        """The request's block table of group g as an int32 array of `width` entries (-1 beyond its
+        blocks), brought up to date from the cache manager's list."""
+        table = self.cache.block_table(rid, g)
+        key = (rid, g)
+        ent = self._table_arrays.get(key)
+        if ent is None or ent[0].size != width or ent[2] is not table:
+            arr = np.full(width, -1, dtype=np.int32)
+            ent = [arr, 0, table]
+            self._table_arrays[key] = ent
+        arr, filled = ent[0], ent[1]
+        n = len(table)
+        if n > filled:
+            arr[filled:n] = table[filled:n]
+            ent[1] = n
+        if self.cache.paged_groups[g].window is not None:       # released blocks turn to -1
+            first = next((i for i, p in enumerate(table) if p >= 0), n)
+            arr[:first] = -1
+        return arr
+
     def _graph_step(self, entries) -> torch.Tensor:
         key = self._graph_key(entries)
         bucket, ctx_bucket = key
         fixed_blocks = -(-ctx_bucket // self.page_size)
-        hb, slot, o, offs, sizes, max_blocks, n_fixed, dims, counts = self._pack(entries, bucket, fixed_blocks)
+        hb, slot, o, offs, sizes, max_blocks, n_fixed, dims, counts = self._pack_decode(entries, bucket, fixed_blocks)
         g = self._graphs.get(key)
         if g is None:
             dev = torch.empty(o, dtype=torch.int32, device=self.device)
