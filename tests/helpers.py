@@ -25,7 +25,15 @@ CONFIG_B = dict(vocab_size=1000, hidden_size=96, num_hidden_layers=3, num_attent
                 max_position_embeddings=256, word_embed_proj_dim=48, do_layer_norm_before=False,
                 enable_bias=False, layer_norm_elementwise_affine=False, layer_norm_eps=1e-6,
                 activation_function="relu", init_std=0.05, architectures=["OPTForCausalLM"], model_type="opt")
-CONFIGS = {"A": CONFIG_A, "B": CONFIG_B}
+# Sizes that leave the fast kernels' rules: head size 48 (no power of two), a feed-forward width and
+# an embedding width that are no multiples of 8 (the tensor-core product refuses them), an odd vocabulary,
+# no final LayerNorm although the layers are pre-norm.
+CONFIG_C = dict(vocab_size=333, hidden_size=96, num_hidden_layers=2, num_attention_heads=2, ffn_dim=100,
+                max_position_embeddings=80, word_embed_proj_dim=36, do_layer_norm_before=True,
+                _remove_final_layer_norm=True, enable_bias=True, layer_norm_elementwise_affine=False,
+                layer_norm_eps=1e-4, activation_function="relu", init_std=0.04,
+                architectures=["OPTForCausalLM"], model_type="opt")
+CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C}
 
 # Largest allowed |engine - plain| as a fraction of the largest |plain logit| of the compared rows.
 # float32: both sides compute in 32-bit and differ by the order of additions only.

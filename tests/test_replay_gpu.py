@@ -117,6 +117,17 @@ def test_mixed_with_page_reuse(tiny, dtype):
     compare_trace(tiny, reqs, steps, res, dtype)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_sizes_outside_the_fast_kernels_rules(dtype):
+    """Configuration C: head size 48, widths that are no multiples of 8, an odd vocabulary: the engine
+    takes the slower kernels where the fast ones refuse, and the logits are still right."""
+    tiny = TinyModel("C", seed=13)
+    reqs = {f"c{i}": tiny.random_ids(n, seed=300 + i) for i, n in enumerate([70, 33, 9, 78, 50, 21])}
+    steps, peak = mixed_steps(reqs, chunk_sizes=(5, 16, 2, 19), decode_tail=10, max_live=3)
+    res = run_trace_inprocess(tiny.folder, dtype, steps, peak)
+    compare_trace(tiny, reqs, steps, res, dtype)
+
+
 def test_program_in_a_subprocess():
     """bin/trace_run itself, as a user calls it: steps on stdin, `done` lines, files, exit code 0."""
     tiny = TinyModel("A", seed=3)
