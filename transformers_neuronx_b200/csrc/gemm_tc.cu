@@ -431,6 +431,60 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     }
 }
 
+// Epilogue of one warp of the many-token kernels: its 32 accumulator rows x WIDTH columns -> C.
+// With a residual (32-bit, possibly C itself) the loads of the next 32 columns are issued before
+// the current ones are stored, so that a tile costs one memory round trip, not one per chunk.
+template <int WIDTH>
+__device__ __forceinline__ void drain_accumulator(const Params& p, uint32_t tmem_addr, int row, int col_base,
+                                                  const float* bias_tile) {
+    // The choice of path must be the same for all lanes of the warp: tcgen05.ld is a warp-wide
+    // instruction.  Rows beyond the matrix are handled by predicating the loads and stores.
+    const bool pipelined = p.residual && (p.ldc % 8 == 0) && (col_base + WIDTH <= p.rows_q);
+    const bool valid = row < p.rows_p;
+    if (!pipelined) {
+#pragma unroll 1
+        for (int c = 0; c < WIDTH; c += 32) {
+            uint32_t r[32];
+            tmem_ld32(tmem_addr + (uint32_t)c, r);
+            tmem_ld_wait();
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+            store_tile_row<WIDTH, false>(p, row, col_base + c, v, 32, p.bias ? bias_tile + c : nullptr);
+        }
+        return;
+    }
+    const size_t row_off = valid ? (size_t)row * p.ldc + col_base : 0;
+    const float* res_row = p.residual + row_off;
+    float* out_row = (float*)p.C + row_off;
+    float4 cur[8], nxt[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) cur[q] = valid ? __ldcg((const float4*)res_row + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 1
+    for (int c = 0; c < WIDTH; c += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem_addr + (uint32_t)c, r);
+        if (c + 32 < WIDTH && valid) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) nxt[q] = __ldcg((const float4*)(res_row + c + 32) + q);
+        }
+        tmem_ld_wait();
+        const float* b = p.bias ? bias_tile + c : nullptr;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            float4 o;
+            float t0 = __uint_as_float(r[4 * q]), t1 = __uint_as_float(r[4 * q + 1]);
+            float t2 = __uint_as_float(r[4 * q + 2]), t3 = __uint_as_float(r[4 * q + 3]);
+            if (b) { t0 += b[4 * q]; t1 += b[4 * q + 1]; t2 += b[4 * q + 2]; t3 += b[4 * q + 3]; }
+            if (p.relu) { t0 = fmaxf(t0, 0.f); t1 = fmaxf(t1, 0.f); t2 = fmaxf(t2, 0.f); t3 = fmaxf(t3, 0.f); }
+            o.x = cur[q].x + t0; o.y = cur[q].y + t1; o.z = cur[q].z + t2; o.w = cur[q].w + t3;
+            if (valid) ((float4*)(out_row + c))[q] = o;
+        }
+#pragma unroll
+        for (int q = 0; q < 8; ++q) cur[q] = nxt[q];
+    }
+}
+
 // ---- many tokens: persistent CTAs, 128 x 256 tiles, two accumulators in tensor memory ---------------
 //
 // One CTA per SM walks over output tiles (tile = first + i * CTAs; consecutive tiles share the weight
@@ -552,17 +606,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
             ok = mbar_wait(&acc_full[acc], acc_ph, p.err, 14);
             if (!ok) break;
             tc_fence_after();
-            const int lane_row = tm * TILE_P + row_in_tile;
-#pragma unroll 1
-            for (int c = 0; c < PBN; c += 32) {
-                uint32_t r[32];
-                tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * PBN + c), r);
-                tmem_ld_wait();
-                float v[32];
-#pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-                store_tile_row<PBN, false>(p, lane_row, tn * PBN + c, v, 32, p.bias ? bias_tile[acc] + c : nullptr);
-            }
+            drain_accumulator<PBN>(p, tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * PBN),
+                                   tm * TILE_P + row_in_tile, tn * PBN, bias_tile[acc]);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) {
@@ -750,17 +795,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             ok = mbar_wait(&acc_full[acc], acc_ph, p.err, 24);
             if (!ok) break;
             tc_fence_after();
-            const int lane_row = tm * 256 + (int)rank * 128 + row_in_tile;
-#pragma unroll 1
-            for (int c = 0; c < 256; c += 32) {
-                uint32_t r[32];
-                tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * 256 + c), r);
-                tmem_ld_wait();
-                float v[32];
-#pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-                store_tile_row<256, false>(p, lane_row, tn * 256 + c, v, 32, p.bias ? bias_tile[acc] + c : nullptr);
-            }
+            drain_accumulator<256>(p, tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * 256),
+                                   tm * 256 + (int)rank * 128 + row_in_tile, tn * 256, bias_tile[acc]);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[acc]), 0));
