@@ -26,7 +26,9 @@ from .step import StepEntry, StepRunner
 
 
 def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines=None, out=None) -> int:
-    lines = sys.stdin if lines is None else lines
+    # readline, not iteration: a step must be read as soon as its line is there (the sender waits
+    # for `done` before it writes the next one)
+    lines = iter(sys.stdin.readline, "") if lines is None else lines
     out = sys.stdout if out is None else out
     os.makedirs(out_dir, exist_ok=True)
     model, cfg = load_model(model_dir, dtype)
