@@ -123,6 +123,28 @@ def test_scheduler_on_the_gpu_with_preemption(tiny):
     tight.runner.cache.check()
 
 
+def test_launching_ahead_changes_no_token(tiny):
+    """The engine launches a step before the ids of the step before it are read back (the next
+    input is taken from the device).  With that switched off the same tokens must come out, under
+    preemption and with requests that end on the end-of-sequence token at different times."""
+    from transformers_neuronx_b200.engine import SamplingParams
+    prompts = [tiny.random_ids(n, seed=60 + i) for i, n in enumerate([22, 7, 31, 12, 18])]
+    params = [SamplingParams(temperature=0.9, top_k=40, seed=3 + i) for i in range(len(prompts))]
+    outs = {}
+    for ahead in (True, False):
+        eng = _engine(tiny, "float32", max_num_seqs=3, max_batch_tokens=24, num_pages=10, async_scheduling=ahead)
+        first = eng.generate(prompts, 30, params, stop_on_eos=False)
+        eng.eos_token_id = first[0][9]                      # some requests now end early, at different steps
+        outs[ahead] = (first, eng.generate(prompts, 30, params, stop_on_eos=True), eng.stats["preemptions"])
+        assert eng.runner.cache.free_pages() == [10] and eng.runner.cache.slots.num_free == 3
+    assert outs[True][0] == outs[False][0] and outs[True][1] == outs[False][1]
+    assert outs[True][2] > 0
+    eos = outs[True][0][0][9]
+    for full, cut in zip(*outs[True][:2]):
+        want = full[:full.index(eos) + 1] if eos in full else full
+        assert cut == want and -1 not in cut
+
+
 def test_temperature_sampling_is_seeded(tiny):
     from transformers_neuronx_b200.engine import SamplingParams
     eng = _engine(tiny, "bfloat16", max_num_seqs=4)

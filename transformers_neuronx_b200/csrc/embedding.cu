@@ -36,6 +36,21 @@ __global__ void gather_rows_kernel(const TT* __restrict__ table, const int* __re
     for (int c = threadIdx.x; c < E; c += blockDim.x) out[(size_t)n * E + c] = from_float<TA>(to_float(row[c]));
 }
 
+// tokens[i] = sampled[src[i]] where src[i] >= 0: a request's next input is the id that the sampling
+// kernel left on the device in the step before, so the host need not wait for it.
+__global__ void patch_tokens_kernel(int* __restrict__ tokens, const int* __restrict__ src,
+                                    const int* __restrict__ sampled, int n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n && src[i] >= 0) tokens[i] = sampled[src[i]];
+}
+
+TNX_EXPORT int tnx_patch_tokens(int* tokens, const int* src, const int* sampled, int n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    return tnx_launch_pdl(patch_tokens_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, tokens, src, sampled, n);
+}
+
 // table_bf16 / act_bf16: 1 when the tables / the activation output are bfloat16, 0 for float.
 TNX_EXPORT int tnx_embed(const void* tok_table, const float* pre, const int* ids, const void* pos_table,
                          const int* positions, int pos_offset, float* out_f32, void* out_act,

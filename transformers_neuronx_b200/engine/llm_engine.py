@@ -30,6 +30,13 @@ class LLMEngine:
         self.eos_token_id = model.spec.eos_token_id if eos_token_id is None else eos_token_id
         self._ids = itertools.count()
         self.requests: Dict[Hashable, Request] = {}
+        n_ids = max(64, 2 * ec.max_num_seqs)
+        self._ids_dev = [torch.zeros(n_ids, dtype=torch.int32, device=model.device) for _ in range(2)]
+        self._ids_host = [torch.zeros(n_ids, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._events = [torch.cuda.Event() for _ in range(2)]
+        self._parity = 0
+        self._inflight = None          # the last step's sampled ids, not yet read back
+        self._awaiting: List[Request] = []   # finished requests whose last ids are still on their way
         self.stats = {"steps": 0, "tokens_run": 0, "tokens_sampled": 0, "preemptions": 0}
 
     def add_request(self, prompt: Sequence[int], max_new_tokens: int, params: Optional[SamplingParams] = None,
@@ -44,42 +51,118 @@ class LLMEngine:
         return rid
 
     def has_work(self) -> bool:
-        return self.scheduler.has_work()
+        return self.scheduler.has_work() or self._inflight is not None
+
+    # A sampled id is needed by the host for three things: as the next input of its request, to
+    # notice the end-of-sequence token, and to hand it to the caller.  Only the first is urgent,
+    # and it does not need the host: the next step takes the id from where the sampling kernel
+    # left it on the device.  So a step is launched before the ids of the step before it have
+    # been read back; the request's output holds -1 at that place meanwhile.  A request that
+    # produced the end-of-sequence token is noticed one step late: the step that was already
+    # launched for it is wasted and its token dropped.
+    PENDING = -1
 
     @torch.no_grad()
     def step(self) -> List[Request]:
-        """One scheduler decision, one model step, one sampling call.  Returns finished requests."""
+        """One scheduler decision, one model step, one sampling call.  Returns the requests that
+        finished and whose tokens are all known."""
+        if not self.scheduler.has_work():
+            finished = self._resolve(self._inflight)
+            self._inflight = None
+            return finished
         plan: StepPlan = self.scheduler.schedule()
+        for r in plan.preempted:
+            self.runner.forget(r.rid)
         entries, rows = [], []
+        any_from_device = False
         for it in plan.items:
-            all_tokens = it.request.tokens
-            toks = all_tokens[it.start:it.start + it.count] if it.count > 1 else [all_tokens[it.start]]
-            entries.append(StepEntry(it.request.rid, toks, [it.count - 1] if it.sample else []))
+            req = it.request
+            all_tokens = req.tokens
+            src = None
+            if it.count == 1:
+                tok = all_tokens[it.start]
+                if tok == self.PENDING:
+                    src, tok = req._dev_row, 0
+                    any_from_device = True
+                toks = [tok]
+            else:
+                toks = all_tokens[it.start:it.start + it.count]
+                if self.PENDING in toks[-2:]:
+                    raise AssertionError(f"request {req.rid!r}: a portion holds a token that is not known yet")
+            entries.append(StepEntry(req.rid, toks, [it.count - 1] if it.sample else [], from_device=src))
             if it.sample:
-                rows.append(it.request)
-        logits = self.runner.step(entries)
-        sampled: Dict[Hashable, int] = {}
+                rows.append(req)
+        prev_ids = self._ids_dev[self._parity ^ 1] if any_from_device else None
+        logits = self.runner.step(entries, prev_ids)
+        cur = None
         if rows:
+            R = len(rows)
             suppress = self.eos_token_id if (self.eos_token_id is not None and
                                              all(r.params.suppress_eos for r in rows)) else -1
             if suppress < 0 and any(r.params.suppress_eos for r in rows):
                 raise ValueError("suppress_eos must be set for all requests of a step or for none")
-            ids = self.sampler.sample(
+            if self._ids_dev[self._parity].shape[0] < R:
+                self._ids_dev = [torch.zeros(2 * R, dtype=torch.int32, device=self.model.device) for _ in range(2)]
+                self._ids_host = [torch.zeros(2 * R, dtype=torch.int32).pin_memory() for _ in range(2)]
+                if any_from_device:
+                    raise AssertionError("the batch outgrew the id buffers while ids were still on the device")
+            out = self._ids_dev[self._parity]
+            self.sampler.sample(
                 logits, [r.params.temperature for r in rows], [r.params.top_k for r in rows],
                 [r.params.top_p for r in rows], [r.params.seed for r in rows],
-                [len(r.output) for r in rows], suppress_id=suppress)
-            host = ids.tolist()                       # the step's one device-to-host read
-            sampled = {r.rid: t for r, t in zip(rows, host)}
-        done = self.scheduler.commit(plan, sampled)
-        for r in done:
+                [len(r.output) for r in rows], suppress_id=suppress, out=out)
+            host = self._ids_host[self._parity]
+            host[:R].copy_(out[:R], non_blocking=True)            # the step's device-to-host read, waited for later
+            ev = self._events[self._parity]
+            ev.record()
+            for i, r in enumerate(rows):
+                r._dev_row = i
+            cur = (rows, [len(r.output) for r in rows], host, ev, R)
+        done_by_count = self.scheduler.commit(plan, {r.rid: self.PENDING for r in rows})
+        for r in done_by_count:
             self.runner.forget(r.rid)
-        for r in plan.preempted:
-            self.runner.forget(r.rid)
+        self._awaiting.extend(done_by_count)
         self.stats["steps"] += 1
         self.stats["tokens_run"] += plan.n_tokens
         self.stats["tokens_sampled"] += len(rows)
         self.stats["preemptions"] = self.scheduler.num_preemptions
-        return done
+        if self.config.async_scheduling:
+            finished = self._resolve(self._inflight)      # the step before this one
+            self._inflight = cur
+        else:
+            finished = self._resolve(self._inflight) + self._resolve(cur)
+            self._inflight = None
+        self._parity ^= 1
+        return finished
+
+    def _resolve(self, inflight) -> List[Request]:
+        """Waits for a step's sampled ids, writes them over the placeholders, and ends requests
+        that produced the end-of-sequence token.  Returns requests that are finished with all
+        their tokens known."""
+        if inflight is not None:
+            rows, places, host, ev, R = inflight
+            ev.synchronize()
+            ids = host[:R].tolist()
+            for req, place, tok in zip(rows, places, ids):
+                if place >= len(req.output):
+                    continue                                   # cut off by an earlier end-of-sequence token
+                req.output[place] = tok
+                req._all[len(req.prompt) + place] = tok
+                if req.stop_on_eos and req.eos_token_id is not None and tok == req.eos_token_id:
+                    del req.output[place + 1:]
+                    del req._all[len(req.prompt) + place + 1:]
+                    if not req.finished:
+                        req.finished = True
+                        if req in self.scheduler.running:
+                            self.scheduler.running.remove(req)
+                            self.runner.cache.free_request(req.rid)
+                            self.runner.forget(req.rid)
+                        elif req in self.scheduler.waiting:    # preempted meanwhile
+                            self.scheduler.waiting.remove(req)
+                        self._awaiting.append(req)
+        ready = [r for r in self._awaiting if not r.output or r.output[-1] != self.PENDING]
+        self._awaiting = [r for r in self._awaiting if r.output and r.output[-1] == self.PENDING]
+        return ready
 
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens, params=None,
                  stop_on_eos: bool = True) -> List[List[int]]:

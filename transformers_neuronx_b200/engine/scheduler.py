@@ -54,6 +54,7 @@ class Request:
 
     def __post_init__(self):
         self._all = list(self.prompt) + list(self.output)      # prompt and output as one list, kept in step
+        self._dev_row = -1          # row of this request in the ids the sampling kernel wrote last
 
     @property
     def tokens(self) -> List[int]:

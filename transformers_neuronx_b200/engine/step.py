@@ -27,6 +27,7 @@ class StepEntry:
     rid: Hashable
     tokens: Sequence[int]
     want: Sequence[int] = ()          # places among `tokens` whose logits are asked for
+    from_device: Optional[int] = None  # the (single) token is row `from_device` of the ids sampled last step
 
 
 @dataclass
@@ -114,6 +115,8 @@ class StepRunner:
                 raise KeyError(f"request {e.rid!r} is not live")
             if len(e.tokens) == 0:
                 raise ValueError(f"request {e.rid!r}: a step entry needs at least one token")
+            if e.from_device is not None and len(e.tokens) != 1:
+                raise ValueError(f"request {e.rid!r}: a token taken from the device must be the entry's only token")
             if self.cache.length(e.rid) + len(e.tokens) > self.max_model_len:
                 raise ValueError(f"request {e.rid!r} would hold {self.cache.length(e.rid) + len(e.tokens)} "
                                  f"tokens; the limit is {self.max_model_len}")
@@ -134,11 +137,12 @@ class StepRunner:
         step) every array has the size of pad_rows single-token requests: padded rows carry request
         -1 and slot -1, which the kernels skip, and every row's logits are computed."""
         hb = HostBatch()
-        tokens, positions, token_request, logit_rows = [], [], [], []
+        tokens, positions, token_request, logit_rows, tok_src = [], [], [], [], []
         row = 0
         for r, e in enumerate(entries):
             start = self.cache.append(e.rid, len(e.tokens))
             n = len(e.tokens)
+            tok_src.extend([-1] * n if e.from_device is None else [int(e.from_device)])
             hb.rids.append(e.rid); hb.q_start.append(row); hb.q_len.append(n); hb.ctx_len.append(start)
             hb.slots.append(self.cache.slot(e.rid))
             tokens.extend(int(t) for t in e.tokens)
@@ -169,7 +173,8 @@ class StepRunner:
             decode_rows = list(range(Np))
         parts = [tok, pos, treq, padded(hb.q_start, Rp, 0), padded(hb.q_len, Rp, 0), padded(hb.ctx_len, Rp, 0),
                  padded(hb.slots, Rp, 0), np.asarray(logit_rows, np.int32),
-                 np.asarray(tile_req, np.int32), np.asarray(tile_q0, np.int32), np.asarray(decode_rows, np.int32)]
+                 np.asarray(tile_req, np.int32), np.asarray(tile_q0, np.int32), np.asarray(decode_rows, np.int32),
+                 padded(tok_src, Np, -1)]
         n_fixed = len(parts)
         max_blocks = []
         for g in range(self.n_groups):
@@ -205,6 +210,7 @@ class StepRunner:
         ctx.q_start, ctx.q_len, ctx.ctx_len, ctx.state_slots = sec(3), sec(4), sec(5), sec(6)
         ctx.logit_rows = sec(7)
         ctx.tile_req, ctx.tile_q0, ctx.decode_rows = sec(8), sec(9), sec(10)
+        ctx.token_source = sec(11)
         ctx.n_prefill_tiles, ctx.n_decode_rows = counts
         for g in range(self.n_groups):
             ctx.block_tables.append(sec(n_fixed + 2 * g).view(Rp, max_blocks[g]))
@@ -217,9 +223,10 @@ class StepRunner:
         ctx.max_decode_ctx = max([c + 1 for c, n in zip(hb.ctx_len, hb.q_len) if n == 1], default=0)
         return ctx
 
-    def prepare(self, entries: Sequence[StepEntry]) -> StepContext:
+    def prepare(self, entries: Sequence[StepEntry], sampled: Optional[torch.Tensor] = None) -> StepContext:
         """Reserves pages for every entry (all or none), builds the step's index arrays in pinned
-        memory and copies them to the device in one transfer."""
+        memory and copies them to the device in one transfer.  `sampled`: the ids the sampling kernel
+        left on the device, for entries that take their token from there."""
         self._validate(entries)
         hb, slot, o, offs, sizes, max_blocks, n_fixed, dims, counts = self._pack(entries)
         dev = torch.empty(o, dtype=torch.int32, device=self.device)
@@ -228,7 +235,15 @@ class StepRunner:
             slot[1] = torch.cuda.Event()
         slot[1].record()
         self.last_h2d_bytes = o * 4
-        return self._context(dev, hb, offs, sizes, max_blocks, n_fixed, dims, counts)
+        ctx = self._context(dev, hb, offs, sizes, max_blocks, n_fixed, dims, counts)
+        self._patch_tokens(entries, ctx, sampled)
+        return ctx
+
+    def _patch_tokens(self, entries, ctx, sampled) -> None:
+        if any(e.from_device is not None for e in entries):
+            if sampled is None:
+                raise ValueError("an entry takes its token from the device but no sampled ids were given")
+            ops.patch_tokens(ctx.token_ids, ctx.token_source, sampled)
 
     # ---- decode-only steps as CUDA graphs ----------------------------------------------------------
     def _graph_key(self, entries):
@@ -258,7 +273,7 @@ class StepRunner:
         hb.q_start = list(range(R)); hb.q_len = [1] * R; hb.ctx_len = starts
         lay = self._decode_layouts.get((bucket, fixed_blocks))
         if lay is None:
-            sizes = [bucket] * 8 + [0, 0, bucket]
+            sizes = [bucket] * 8 + [0, 0, bucket, bucket]
             for _ in range(G):
                 sizes += [bucket * fixed_blocks, bucket]
             offs, o = [], 0
@@ -282,7 +297,10 @@ class StepRunner:
             a[R:] = fill
         sec(7)[:] = ar
         sec(10)[:] = ar
-        n_fixed = 11
+        src = sec(11)
+        src[:R] = [-1 if e.from_device is None else int(e.from_device) for e in entries]
+        src[R:] = -1
+        n_fixed = 12
         for g in range(G):
             bt = sec(n_fixed + 2 * g).reshape(bucket, fixed_blocks)
             for r, e in enumerate(entries):
@@ -318,7 +336,7 @@ class StepRunner:
             arr[:first] = -1
         return arr
 
-    def _graph_step(self, entries) -> torch.Tensor:
+    def _graph_step(self, entries, sampled=None) -> torch.Tensor:
         key = self._graph_key(entries)
         bucket, ctx_bucket = key
         fixed_blocks = -(-ctx_bucket // self.page_size)
@@ -336,6 +354,7 @@ class StepRunner:
         slot[1].record()
         self.last_h2d_bytes = o * 4
         ctx.host, ctx.n_requests = hb, len(entries)
+        self._patch_tokens(entries, ctx, sampled)
         ctx.max_decode_ctx = ctx_bucket               # the split plan is fixed for the whole bucket
         ctx.max_ctx = ctx_bucket
         if g["graph"] is None:
@@ -359,14 +378,15 @@ class StepRunner:
         return g["logits"][:len(entries)]
 
     @torch.no_grad()
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], sampled: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Runs one step; returns the 32-bit logits [wanted, vocab] (a device tensor) in the order
-        of the entries and of their `want`."""
+        of the entries and of their `want`.  `sampled` (int32, device): ids sampled in the step
+        before, for entries with `from_device`."""
         if self.use_cuda_graphs and all(len(e.tokens) == 1 for e in entries) and len(entries) <= self.max_graph_batch:
             self._validate(entries)
-            logits = self._graph_step(entries)
+            logits = self._graph_step(entries, sampled)
         else:
-            ctx = self.prepare(entries)
+            ctx = self.prepare(entries, sampled)
             logits = self.model.forward(ctx)
         for e in entries:
             self.cache.release_behind_window(e.rid)

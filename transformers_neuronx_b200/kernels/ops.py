@@ -112,6 +112,16 @@ def embed(tok_table, pre, ids, pos_table, positions, pos_offset, out_f32, out_ac
                          _stream()), "embed")
 
 
+def patch_tokens(tokens, src, sampled):
+    """tokens[i] = sampled[src[i]] wherever src[i] >= 0 (all int32, on the device)."""
+    lib = _build.load("embedding")
+    for t, nm in ((tokens, "tokens"), (src, "src"), (sampled, "sampled")):
+        _need(t, nm, torch.int32, 1)
+    if src.shape[0] < tokens.shape[0]:
+        raise KernelError("src is shorter than tokens")
+    _check(lib.tnx_patch_tokens(_p(tokens), _p(src), _p(sampled), c_int(tokens.shape[0]), _stream()), "patch_tokens")
+
+
 def gather_rows(table, ids, out):
     lib = _build.load("embedding")
     _need(table, "table", _FLOATS, 2)

@@ -119,10 +119,10 @@ def run(args):
         runner = model.engine.runner
         inner = runner.step
 
-        def timed(entries):
+        def timed(entries, *args, **kwargs):
             torch.cuda.synchronize()
             t0 = time.time()
-            out = inner(entries)
+            out = inner(entries, *args, **kwargs)
             torch.cuda.synchronize()
             print(f"cache_offset: {max(runner.cache.length(e.rid) for e in entries) - 1}")
             print(f"Latency: {math.ceil((time.time() - t0) * 1000)} ms")

@@ -36,6 +36,7 @@ class StepContext:
         self.token_ids = None                 # [N]
         self.positions = None                 # [N] position of each token in its request
         self.token_request = None             # [N] index of the token's request in this batch
+        self.token_source = None              # [N] row of last step's sampled ids that is this token, or -1
         self.q_start = None                   # [R] first row of each request
         self.q_len = None                     # [R] rows of each request
         self.ctx_len = None                   # [R] tokens the request had in the cache before this step

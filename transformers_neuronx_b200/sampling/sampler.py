@@ -21,10 +21,10 @@ class Sampler:
 
     def sample(self, logits: torch.Tensor, temperatures: Sequence[float], top_ks: Sequence[int],
                top_ps: Sequence[float], seeds: Sequence[int], counters: Sequence[int],
-               suppress_id: int = -1) -> torch.Tensor:
-        """logits: 32-bit [R, V] on the device -> int32 [R] on the device."""
+               suppress_id: int = -1, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """logits: 32-bit [R, V] on the device -> int32 [R] on the device (written to `out` when given)."""
         R = logits.shape[0]
-        out = torch.empty(R, dtype=torch.int32, device=self.device)
+        out = torch.empty(R, dtype=torch.int32, device=self.device) if out is None else out[:R]
         if R == 0:
             return out
         if all(t <= 0 for t in temperatures) and suppress_id < 0:
