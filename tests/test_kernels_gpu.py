@@ -140,14 +140,14 @@ def plain_attention(q, k, v, n_heads, n_kv, scale, first_pos, window):
 class PagedCase:
     """Requests with contexts and portions; keys/values scattered over shuffled pages."""
 
-    def __init__(self, lens, n_heads, n_kv, d, dtype, seed=0, plant=True):
+    def __init__(self, lens, n_heads, n_kv, d, dtype, seed=0, plant=True, poison=float("nan")):
         # lens: list of (ctx_len, q_len)
         g = torch.Generator().manual_seed(seed)
         self.lens, self.n_heads, self.n_kv, self.d, self.dtype = lens, n_heads, n_kv, d, dtype
         ps = 16
         total_pages = sum(-(-(c + q) // ps) for c, q in lens) + 3
         perm = torch.randperm(total_pages, generator=g).tolist()
-        self.cache = torch.full((total_pages, 2, n_kv, ps, d), float("nan"), dtype=dtype)   # unwritten rows are poison
+        self.cache = torch.full((total_pages, 2, n_kv, ps, d), poison, dtype=dtype)   # unwritten rows are poison
         self.k, self.v, self.q = [], [], []
         tables, tok_req, positions, q_start, tile_req, tile_q0, decode_rows = [], [], [], [], [], [], []
         row = 0
@@ -372,3 +372,25 @@ def test_sampling_large_vocabulary_top_k():
     got = _draws(row, 2000, temperature=1.0, top_k=50)
     top = set(torch.topk(row, 50).indices.tolist())
     assert set(got.tolist()) <= top and len(set(got.tolist())) > 25
+
+
+@pytest.mark.parametrize("n_heads,n_kv", [(4, 2), (3, 3), (8, 1)])
+@pytest.mark.parametrize("window", [None, 45, 200])
+def test_attention_prefill_tc(n_heads, n_kv, window):
+    """The tcgen05 prefill kernel (head size 128).  Unwritten rows of pages hold a large finite number:
+    they are loaded with their page and must be weighted by exactly zero."""
+    d = 128
+    lens = [(0, 2), (0, 64), (0, 129), (30, 7), (64, 130), (15, 17), (200, 300), (5, 1), (1000, 260)]
+    case = PagedCase(lens, n_heads, n_kv, d, torch.bfloat16, seed=77, poison=3.0e4)
+    scale = 1.0 / math.sqrt(d)
+    out = torch.zeros(case.N, n_heads * d, dtype=torch.bfloat16, device=DEV)
+    o = ops()
+    assert o.attention_prefill_tc_supported(case.q_flat, case.cache, out)
+    o.attention_prefill_tc(case.q_flat, case.cache, case.bt, case.tile_req, case.tile_q0, case.q_start, case.q_len,
+                           case.ctx_len, out, n_heads, scale, window or 0)
+    o.raise_on_device_error()
+    want = case.want(scale, window)
+    keep = torch.ones(case.N, dtype=torch.bool, device=DEV)
+    keep[case.decode_rows.long()] = False
+    assert rel_err(out[keep], want[keep]) <= 1.5e-2
+    assert float(out[~keep].float().abs().max()) == 0.0

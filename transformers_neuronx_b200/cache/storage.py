@@ -1,7 +1,9 @@
 """Device memory of the caches: for a paged cache one tensor
 [pages, 2 (key, value), n_kv_heads, page_size, head_dim] in the activation type, for state of fixed
-size one tensor [slots, *shape].  Never zeroed: what a request may read is decided by its own
-length and block table, never by the contents of a page."""
+size one tensor [slots, *shape].  What a request may read is decided by its own length and block
+table, never by the contents of a page; pages are not cleared when they change hands.  The memory
+is zeroed once, when it is made: the tensor-core attention multiplies rows that no token has
+written yet by probabilities that are exactly zero, so they must hold finite numbers."""
 from __future__ import annotations
 
 from typing import Dict, List
@@ -25,7 +27,7 @@ class CacheStorage:
                 self._group[cid] = gi
         for cid, need in needs.items():
             if isinstance(need, PagedKVNeed):
-                self._tensors[cid] = torch.empty((num_pages, 2, need.n_kv_heads, page_size, need.head_dim),
+                self._tensors[cid] = torch.zeros((num_pages, 2, need.n_kv_heads, page_size, need.head_dim),
                                                  dtype=act_dtype, device=device)
             elif isinstance(need, FixedStateNeed):
                 self._tensors[cid] = torch.zeros((max_slots,) + tuple(need.shape), dtype=_DT[need.dtype],

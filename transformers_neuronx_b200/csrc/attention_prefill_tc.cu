@@ -1,0 +1,355 @@
+// Causal attention of prompt portions over the paged bfloat16 cache on the 5th-generation tensor
+// cores (tcgen05), for head size 128.  Same work items and the same result as attention_prefill.cu;
+// this kernel is the fast one.
+//
+// Work item = (request, tile of 128 of its query rows, head); keys in tiles of 64 (four pages).
+//   S = Q K^T   : tcgen05.mma M=128 (queries) N=64 (keys) K=128 (head), Q and K from shared memory
+//                 (TMA, 128-byte swizzle, K-major), S in tensor memory (two buffers)
+//   softmax     : four warps, one thread per query row: the row of S is read from tensor memory,
+//                 masked, exponentiated with the running maximum (32-bit), the row of P written to
+//                 shared memory as bfloat16 in the swizzled layout the MMA expects
+//   O += P V    : tcgen05.mma M=128 N=128 (head) K=64 (keys); V is the [key][head] tile as it lies
+//                 in the cache's pages, i.e. the "MN-major" form of the B operand; O stays in tensor
+//                 memory over all key tiles and is rescaled there when the running maximum grows
+// Warp 0 issues the TMA loads (K and V of a tile complete one barrier; two stages), warp 1 the MMAs
+// (one elected lane; the scores of tile j+1 are issued before P V of tile j so that the tensor core
+// works while the softmax warps do), warps 2-5 are the softmax warps.  Two CTAs fit on an SM.
+// Every wait is bounded and reports through the error word.
+//
+// The cache's memory must hold finite numbers everywhere (it is allocated zeroed): rows of a page
+// that no token has written yet are loaded with their page and multiplied by probabilities that
+// are exactly zero.
+#include "common.cuh"
+#include "tc_common.cuh"
+
+namespace {
+
+constexpr int D = 128;                       // head size
+constexpr int BQ = 128, BKV = 64, PAGE = 16;
+constexpr int ATOM_Q = BQ * 128;             // bytes of one 64-column half of the Q tile (16 KB)
+constexpr int ATOM_KV = BKV * 128;           // bytes of one 64-column half of a K or V tile (8 KB)
+constexpr int Q_BYTES = 2 * ATOM_Q, KV_BYTES = 2 * ATOM_KV, P_BYTES = BQ * 128;
+constexpr int SMEM_BYTES = Q_BYTES + 2 * 2 * KV_BYTES + P_BYTES + 1024;   // 113 KB + alignment
+constexpr uint32_t TMEM_COLS = 256;          // S0 [0,64) S1 [64,128) O [128,256)
+constexpr int THREADS = 192;
+
+struct TcPrefillParams {
+    const int* block_tables; int bt_stride;
+    const int* tile_req; const int* tile_q0;
+    const int* q_start; const int* q_len; const int* ctx_len;
+    bf16* out; int out_stride;
+    int n_heads, n_kv_heads;
+    int window;
+    float scale_log2;
+    int* err;
+};
+
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// B operand given as [K rows][N contiguous] (MN-major), rows 128 bytes, 128-byte swizzle: groups of
+// 8 rows (K) are 1024 bytes apart, the next 64 columns (N) `lbo_bytes` further.
+__device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t saddr, uint32_t lbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+    d |= (uint64_t)(lbo_bytes >> 4) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// D = f32, A = B = bf16, M = 128, N = n; b_mn: B is MN-major.
+__host__ __device__ constexpr uint32_t idesc_attn(int n, int b_mn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+
+__global__ void __launch_bounds__(THREADS, 2)
+attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
+                            const TcPrefillParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* sQ = smem;
+    uint8_t* sKV = sQ + Q_BYTES;                  // [stage][K tile, V tile]
+    uint8_t* sP = sKV + 2 * 2 * KV_BYTES;
+    __shared__ uint64_t q_full, kv_full[2], kv_empty[2], s_full[2], s_empty[2], p_full, o_full;
+    __shared__ uint32_t tmem_base_smem;
+
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int item = gridDim.x - 1 - blockIdx.x, h = blockIdx.y;      // heaviest tiles first
+    const int req = p.tile_req[item], q0 = p.tile_q0[item];
+    const int qs = p.q_start[req], ql = p.q_len[req], ctx = p.ctx_len[req];
+    const int rows = min(BQ, ql - q0);
+    const int kvh = h / (p.n_heads / p.n_kv_heads);
+    const int* bt = p.block_tables + (size_t)req * p.bt_stride;
+    const int pos0 = ctx + q0, pos_last = pos0 + rows - 1;
+    const int kv_total = ctx + ql;
+    int key_begin = 0;
+    if (p.window > 0) key_begin = max(0, pos0 - p.window + 1) / BKV * BKV;
+    const int n_tiles = (pos_last - key_begin) / BKV + 1;
+
+    // K and V stages start as zeros: pages that do not exist are not loaded, and what a stage holds
+    // then must be finite (it is multiplied by probabilities that are zero).
+    for (int i = threadIdx.x; i < 2 * 2 * KV_BYTES / 16; i += THREADS) ((uint4*)sKV)[i] = make_uint4(0, 0, 0, 0);
+    if (threadIdx.x == 0) {
+        mbar_init(&q_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1);
+            mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 4);
+        }
+        mbar_init(&p_full, 4); mbar_init(&o_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_q) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_kv) : "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(&tmem_base_smem, TMEM_COLS);
+        tmem_relinquish();
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the zeros, before TMA writes beside them
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_smem;
+    bool ok = true;
+
+    if (warp == 0) {
+        // ---- TMA producer ---------------------------------------------------------------------------
+        if (lane == 0) {
+            mbar_expect_tx(&q_full, Q_BYTES);
+            tma_load_2d(sQ, &map_q, &q_full, h * D, qs + q0);
+            tma_load_2d(sQ + ATOM_Q, &map_q, &q_full, h * D + 64, qs + q0);
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int s = j & 1;
+                ok = mbar_wait(&kv_empty[s], (uint32_t)(((j >> 1) & 1) ^ 1), p.err, 31);
+                if (!ok) break;
+                const int k0 = key_begin + j * BKV;
+                int pages[4], n_valid = 0;
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    const int key = k0 + g * PAGE;
+                    pages[g] = key < kv_total ? bt[key / PAGE] : -1;
+                    n_valid += pages[g] >= 0;
+                }
+                mbar_expect_tx(&kv_full[s], (uint32_t)(n_valid * 2 * 2 * PAGE * 128));
+                uint8_t* sK = sKV + (size_t)s * 2 * KV_BYTES;
+                uint8_t* sV = sK + KV_BYTES;
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    if (pages[g] < 0) continue;
+                    const int row_k = ((pages[g] * 2 + 0) * p.n_kv_heads + kvh) * PAGE;
+                    const int row_v = ((pages[g] * 2 + 1) * p.n_kv_heads + kvh) * PAGE;
+#pragma unroll
+                    for (int a = 0; a < 2; ++a) {
+                        tma_load_2d(sK + a * ATOM_KV + g * PAGE * 128, &map_kv, &kv_full[s], a * 64, row_k);
+                        tma_load_2d(sV + a * ATOM_KV + g * PAGE * 128, &map_kv, &kv_full[s], a * 64, row_v);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer -----------------------------------------------------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = idesc_attn(BKV, 0), idesc_pv = idesc_attn(D, 1);
+            const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
+            auto issue_qk = [&](int j) {
+                const uint32_t k_addr = smem_u32(sKV + (size_t)(j & 1) * 2 * KV_BYTES);
+                const uint32_t d_tmem = tmem_base + (uint32_t)((j & 1) * BKV);
+#pragma unroll
+                for (int k = 0; k < D / 16; ++k) {
+                    const uint64_t adesc = smem_desc_sw128(q_addr + (k >> 2) * ATOM_Q + (k & 3) * 32);
+                    const uint64_t bdesc = smem_desc_sw128(k_addr + (k >> 2) * ATOM_KV + (k & 3) * 32);
+                    umma_bf16(d_tmem, adesc, bdesc, idesc_qk, k > 0 ? 1u : 0u);
+                }
+                umma_commit(&s_full[j & 1]);
+            };
+            ok = mbar_wait(&q_full, 0, p.err, 32);
+            if (ok) ok = mbar_wait(&kv_full[0], 0, p.err, 33);
+            if (ok) { tc_fence_after(); issue_qk(0); }
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                if (j + 1 < n_tiles) {
+                    const int n = j + 1;
+                    ok = mbar_wait(&kv_full[n & 1], (uint32_t)((n >> 1) & 1), p.err, 34);
+                    if (ok) ok = mbar_wait(&s_empty[n & 1], (uint32_t)(((n >> 1) & 1) ^ 1), p.err, 35);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_qk(n);
+                }
+                ok = mbar_wait(&p_full, (uint32_t)(j & 1), p.err, 36);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t v_addr = smem_u32(sKV + (size_t)(j & 1) * 2 * KV_BYTES + KV_BYTES);
+#pragma unroll
+                for (int k = 0; k < BKV / 16; ++k) {
+                    const uint64_t adesc = smem_desc_sw128(p_addr + k * 32);
+                    const uint64_t bdesc = smem_desc_sw128_mn(v_addr + k * 16 * 128, ATOM_KV);
+                    umma_bf16(tmem_base + 128, adesc, bdesc, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(&o_full);
+                umma_commit(&kv_empty[j & 1]);
+            }
+        }
+    } else {
+        // ---- softmax warps: thread = query row ----------------------------------------------------------
+        const int quad = warp & 3;
+        const int r = quad * 32 + lane;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
+        const int qpos = pos0 + r;
+        float m_run = -INFINITY, l_run = 0.f;
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            const int b = j & 1;
+            const int k0 = key_begin + j * BKV;
+            ok = mbar_wait(&s_full[b], (uint32_t)((j >> 1) & 1), p.err, 37);
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t raw0[32], raw1[32];
+            tmem_ld32(lane_base + (uint32_t)(b * BKV), raw0);
+            tmem_ld32(lane_base + (uint32_t)(b * BKV + 32), raw1);
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_empty[b]);             // the scores are in registers
+            float s[64];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) { s[i] = __uint_as_float(raw0[i]); s[32 + i] = __uint_as_float(raw1[i]); }
+            bool need_mask = k0 + BKV - 1 > qpos;
+            if (p.window > 0) need_mask = need_mask || (k0 <= qpos - p.window);
+            if (need_mask) {
+#pragma unroll
+                for (int i = 0; i < 64; ++i) {
+                    const int key = k0 + i;
+                    bool keep = key <= qpos;
+                    if (p.window > 0) keep = keep && key > qpos - p.window;
+                    if (!keep) s[i] = -INFINITY;
+                }
+            }
+            float mx = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < 64; ++i) mx = fmaxf(mx, s[i]);
+            const float m_new = fmaxf(m_run, mx);
+            const float m_scaled = (m_new == -INFINITY) ? 0.f : m_new * p.scale_log2;
+            const float corr = (m_run == -INFINITY) ? 0.f : ex2_approx(m_run * p.scale_log2 - m_scaled);
+            float sum = 0.f;
+            uint32_t packed[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                const float p0 = ex2_approx(fmaf(s[2 * i], p.scale_log2, -m_scaled));
+                const float p1 = ex2_approx(fmaf(s[2 * i + 1], p.scale_log2, -m_scaled));
+                sum += p0 + p1;
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
+                packed[i] = *(uint32_t*)&h2;
+            }
+            l_run = l_run * corr + sum;
+            m_run = m_new;
+            if (j > 0) {
+                // P V of the tile before has finished: its O is complete and the P buffer is free
+                ok = mbar_wait(&o_full, (uint32_t)((j - 1) & 1), p.err, 38);
+                if (!ok) break;
+                tc_fence_after();
+                if (!__all_sync(0xffffffffu, corr == 1.f)) {     // the maximum of some row grew: rescale O
+#pragma unroll 1
+                    for (int c = 0; c < D; c += 32) {
+                        uint32_t o[32];
+                        tmem_ld32(lane_base + 128u + (uint32_t)c, o);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+                        tmem_st32(lane_base + 128u + (uint32_t)c, o);
+                    }
+                    tmem_st_wait();
+                }
+            }
+            // this row of P -> shared memory, 16-byte chunks XOR-swizzled as the MMA reads them
+            uint8_t* prow = sP + r * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+                *(uint4*)(prow + ((c ^ (r & 7)) << 4)) = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_full);
+        }
+        if (ok) ok = mbar_wait(&o_full, (uint32_t)((n_tiles - 1) & 1), p.err, 39);
+        if (ok) {
+            tc_fence_after();
+            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            bf16* orow = p.out + (size_t)(qs + q0 + r) * p.out_stride + (size_t)h * D;
+#pragma unroll 1
+            for (int c = 0; c < D; c += 32) {
+                uint32_t o[32];
+                tmem_ld32(lane_base + 128u + (uint32_t)c, o);
+                tmem_ld_wait();
+                if (r < rows) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        uint4 u;
+                        __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(o[8 * q]) * inv, __uint_as_float(o[8 * q + 1]) * inv);
+                        __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(o[8 * q + 2]) * inv, __uint_as_float(o[8 * q + 3]) * inv);
+                        __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(o[8 * q + 4]) * inv, __uint_as_float(o[8 * q + 5]) * inv);
+                        __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(o[8 * q + 6]) * inv, __uint_as_float(o[8 * q + 7]) * inv);
+                        u.x = *(uint32_t*)&h0; u.y = *(uint32_t*)&h1; u.z = *(uint32_t*)&h2; u.w = *(uint32_t*)&h3;
+                        *(uint4*)(orow + c + 8 * q) = u;
+                    }
+                }
+            }
+        }
+    }
+    if (!ok) {
+        const unsigned long long t0 = global_ns();
+        while (global_ns() - t0 < 1000000ull) __nanosleep(1000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+}  // namespace
+
+// Same arguments as tnx_attention_prefill plus the error word; head_dim must be 128 and n_rows_q is
+// the number of rows of the q / out buffers (for the TMA descriptor).
+TNX_EXPORT int tnx_attention_prefill_tc(const void* q, int q_stride, int n_rows_q, const void* cache, long long cache_rows,
+                                        const int* block_tables, int bt_stride, const int* tile_req, const int* tile_q0,
+                                        const int* q_start, const int* q_len, const int* ctx_len, void* out,
+                                        int out_stride, int n_items, int n_heads, int n_kv_heads, int head_dim,
+                                        int page_size, int window, float scale, int* err_word, cudaStream_t stream) {
+    if (n_items <= 0) return 0;
+    if (head_dim != D || page_size != PAGE || n_kv_heads <= 0 || n_heads % n_kv_heads || q_stride % 8 || out_stride % 8 ||
+        ((uintptr_t)q & 15) || ((uintptr_t)cache & 15) || ((uintptr_t)out & 15) || cache_rows > 0x7fffffffLL || !err_word)
+        return TNX_ERR_UNSUPPORTED;
+    CUtensorMap mq, mkv;
+    if (!make_map(&mq, q, n_rows_q, n_heads * D, q_stride, BQ)) return TNX_ERR_UNSUPPORTED;
+    if (!make_map(&mkv, cache, (int)cache_rows, D, D, PAGE)) return TNX_ERR_UNSUPPORTED;
+    TcPrefillParams p;
+    p.block_tables = block_tables; p.bt_stride = bt_stride; p.tile_req = tile_req; p.tile_q0 = tile_q0;
+    p.q_start = q_start; p.q_len = q_len; p.ctx_len = ctx_len; p.out = (bf16*)out; p.out_stride = out_stride;
+    p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.window = window; p.scale_log2 = scale * 1.4426950408889634f;
+    p.err = err_word;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    return tnx_launch_pdl(attention_prefill_tc_kernel, dim3(n_items, n_heads), dim3(THREADS), SMEM_BYTES, stream, mq, mkv, p);
+}

@@ -39,6 +39,7 @@ SOURCES: Dict[str, str] = {
     "gemm_tc": "gemm_tc.cu",
     "attention_decode": "attention_decode.cu",
     "attention_prefill": "attention_prefill.cu",
+    "attention_prefill_tc": "attention_prefill_tc.cu",
 }
 
 _loaded: Dict[str, ctypes.CDLL] = {}

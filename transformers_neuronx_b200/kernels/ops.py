@@ -391,13 +391,44 @@ def attention_prefill(q, cache, block_tables, tile_req, tile_q0, q_start, q_len,
                                      c_int(window or 0), c_float(scale), _stream()), "attention_prefill")
 
 
+def attention_prefill_tc_supported(q, cache, out) -> bool:
+    """The tcgen05 prefill kernel takes head size 128, pages of 16 and 16-byte aligned rows."""
+    return (cache.dtype == torch.bfloat16 and cache.shape[4] == 128 and cache.shape[3] == 16 and q.stride(0) % 8 == 0 and
+            out.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0 and
+            cache.shape[0] * 2 * cache.shape[2] * 16 < 2 ** 31)
+
+
+def attention_prefill_tc(q, cache, block_tables, tile_req, tile_q0, q_start, q_len, ctx_len, out, n_heads, scale,
+                         window=0, n_items=None):
+    """attention_prefill on the tcgen05 tensor cores (head size 128).  The cache must hold finite
+    numbers in every row, written or not (CacheStorage allocates it zeroed)."""
+    lib = _build.load("attention_prefill_tc")
+    _need(cache, "cache", torch.bfloat16, 5)
+    N, width, q_stride = _rows_2d(q, "q")
+    No, wo, out_stride = _rows_2d(out, "out")
+    n_pages, _, n_kv, ps, d = cache.shape
+    if not attention_prefill_tc_supported(q, cache, out) or width != n_heads * d or (No, wo) != (N, width):
+        raise KernelError("attention_prefill_tc takes bfloat16, head size 128, pages of 16, 16-byte aligned rows")
+    for t, nm in ((block_tables, "block_tables"), (tile_req, "tile_req"), (tile_q0, "tile_q0"), (q_start, "q_start"),
+                  (q_len, "q_len"), (ctx_len, "ctx_len")):
+        _need(t, nm, torch.int32, 2 if nm == "block_tables" else 1)
+    n = int(n_items) if n_items is not None else tile_req.shape[0]
+    st = _state(q.device)
+    _check(lib.tnx_attention_prefill_tc(_p(q), c_int(q_stride), c_int(N), _p(cache), ctypes.c_longlong(n_pages * 2 * n_kv * ps),
+                                        _p(block_tables), c_int(block_tables.stride(0)), _p(tile_req), _p(tile_q0),
+                                        _p(q_start), _p(q_len), _p(ctx_len), _p(out), c_int(out_stride), c_int(n),
+                                        c_int(n_heads), c_int(n_kv), c_int(d), c_int(ps), c_int(window or 0),
+                                        c_float(scale), _p(st["err"]), _stream()), "attention_prefill_tc")
+
+
 def _attention_bf16(ctx, group, q, cache, out, n_heads, scale, window):
     if cache.shape[3] != 16 or q.stride(0) % 8 or q.data_ptr() % 16:
         return False
     bt = ctx.block_tables[group]
     if ctx.n_prefill_tiles:
-        attention_prefill(q, cache, bt, ctx.tile_req, ctx.tile_q0, ctx.q_start, ctx.q_len, ctx.ctx_len, out,
-                          n_heads, scale, window, n_items=ctx.n_prefill_tiles)
+        prefill = attention_prefill_tc if attention_prefill_tc_supported(q, cache, out) else attention_prefill
+        prefill(q, cache, bt, ctx.tile_req, ctx.tile_q0, ctx.q_start, ctx.q_len, ctx.ctx_len, out,
+                n_heads, scale, window, n_items=ctx.n_prefill_tiles)
     if ctx.n_decode_rows:
         attention_decode(q, cache, bt, ctx.token_request, ctx.positions, out, n_heads, scale, window,
                          rows=None if ctx.decode_only else ctx.decode_rows, n_rows=ctx.n_decode_rows,
