@@ -11,9 +11,11 @@
 //   O += P V    : tcgen05.mma M=128 N=128 (head) K=64 (keys); V is the [key][head] tile as it lies
 //                 in the cache's pages, i.e. the "MN-major" form of the B operand; O stays in tensor
 //                 memory over all key tiles and is rescaled there when the running maximum grows
-// Warp 0 issues the TMA loads (K and V of a tile complete one barrier; two stages), warp 1 the MMAs
-// (one elected lane; the scores of tile j+1 are issued before P V of tile j so that the tensor core
-// works while the softmax warps do), warps 2-5 are the softmax warps.  Two CTAs fit on an SM.
+// Warp 0 issues the TMA loads (three stages of K, two of V; the page numbers of the work item are
+// read into shared memory first), warp 1 the MMAs (one elected lane; the scores of tile j+1 are
+// issued before P V of tile j whenever their K tile is there, so that the tensor core works while
+// the softmax warps do), warps 2-5 are the softmax warps.  P of a tile is written over the K tile it
+// came from, which is dead by then.  Two CTAs fit on an SM.
 // Every wait is bounded and reports through the error word.
 //
 // The cache's memory must hold finite numbers everywhere (it is allocated zeroed): rows of a page
@@ -28,8 +30,14 @@ constexpr int D = 128;                       // head size
 constexpr int BQ = 128, BKV = 64, PAGE = 16;
 constexpr int ATOM_Q = BQ * 128;             // bytes of one 64-column half of the Q tile (16 KB)
 constexpr int ATOM_KV = BKV * 128;           // bytes of one 64-column half of a K or V tile (8 KB)
-constexpr int Q_BYTES = 2 * ATOM_Q, KV_BYTES = 2 * ATOM_KV, P_BYTES = BQ * 128;
-constexpr int SMEM_BYTES = Q_BYTES + 2 * 2 * KV_BYTES + P_BYTES + 1024;   // 113 KB + alignment
+constexpr int Q_BYTES = 2 * ATOM_Q, KV_BYTES = 2 * ATOM_KV;
+constexpr int K_STAGES = 3, V_STAGES = 2;
+constexpr int MAX_PAGES_SMEM = 128;          // page numbers kept in shared memory (2,048 keys); beyond: read from global
+constexpr int TILE_BYTES = Q_BYTES + (K_STAGES + V_STAGES) * KV_BYTES;          // 112 KB
+// Everything lives in dynamic shared memory, the tiles first: with no static shared memory the
+// dynamic part starts at the CTA's shared window, which is 1024-byte aligned as the swizzled tiles
+// need (checked at run time), and two CTAs fit on an SM to the byte.
+constexpr int SMEM_BYTES = TILE_BYTES + 256 + MAX_PAGES_SMEM * 4;
 constexpr uint32_t TMEM_COLS = 256;          // S0 [0,64) S1 [64,128) O [128,256)
 constexpr int THREADS = 192;
 
@@ -83,13 +91,26 @@ __host__ __device__ constexpr uint32_t idesc_attn(int n, int b_mn) {
 __global__ void __launch_bounds__(THREADS, 2)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                             const TcPrefillParams p) {
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sQ = smem;
-    uint8_t* sKV = sQ + Q_BYTES;                  // [stage][K tile, V tile]
-    uint8_t* sP = sKV + 2 * 2 * KV_BYTES;
-    __shared__ uint64_t q_full, kv_full[2], kv_empty[2], s_full[2], s_empty[2], p_full, o_full;
-    __shared__ uint32_t tmem_base_smem;
+    uint8_t* sK = sQ + Q_BYTES;                   // [K_STAGES] K tiles; P of a tile overwrites its K tile
+    uint8_t* sV = sK + K_STAGES * KV_BYTES;       // [V_STAGES] V tiles
+    uint64_t* bars = (uint64_t*)(smem + TILE_BYTES);
+    uint64_t& q_full = bars[0];
+    uint64_t* k_full = bars + 1;                  // [K_STAGES]
+    uint64_t* k_empty = k_full + K_STAGES;
+    uint64_t* v_full = k_empty + K_STAGES;        // [V_STAGES]
+    uint64_t* v_empty = v_full + V_STAGES;
+    uint64_t* s_full = v_empty + V_STAGES;        // [2]
+    uint64_t* s_empty = s_full + 2;
+    uint64_t& p_full = s_empty[2];
+    uint64_t& o_full = s_empty[3];
+    uint32_t& tmem_base_smem = *(uint32_t*)(s_empty + 4);
+    int* pages_s = (int*)(smem + TILE_BYTES + 256);
+    if (smem_u32(smem) & 1023u) {                 // cannot happen with no static shared memory; never compute on a wrong layout
+        if (threadIdx.x == 0) atomicExch(p.err, 30);
+        return;
+    }
 
     pdl_launch_dependents();
     pdl_wait();
@@ -108,13 +129,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
     // K and V stages start as zeros: pages that do not exist are not loaded, and what a stage holds
     // then must be finite (it is multiplied by probabilities that are zero).
-    for (int i = threadIdx.x; i < 2 * 2 * KV_BYTES / 16; i += THREADS) ((uint4*)sKV)[i] = make_uint4(0, 0, 0, 0);
+    for (int i = threadIdx.x; i < (K_STAGES + V_STAGES) * KV_BYTES / 16; i += THREADS) ((uint4*)sK)[i] = make_uint4(0, 0, 0, 0);
+    const int first_page = key_begin / PAGE;
+    const int n_pages = (min(kv_total, key_begin + n_tiles * BKV) - key_begin + PAGE - 1) / PAGE;   // pages that exist
+    for (int i = threadIdx.x; i < n_pages && i < MAX_PAGES_SMEM; i += THREADS) pages_s[i] = bt[first_page + i];
     if (threadIdx.x == 0) {
         mbar_init(&q_full, 1);
-        for (int s = 0; s < 2; ++s) {
-            mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1);
-            mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 4);
-        }
+        for (int s = 0; s < K_STAGES; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
+        for (int s = 0; s < V_STAGES; ++s) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
+        for (int s = 0; s < 2; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 4); }
         mbar_init(&p_full, 4); mbar_init(&o_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_q) : "memory");
@@ -138,30 +161,36 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             tma_load_2d(sQ, &map_q, &q_full, h * D, qs + q0);
             tma_load_2d(sQ + ATOM_Q, &map_q, &q_full, h * D + 64, qs + q0);
             for (int j = 0; j < n_tiles && ok; ++j) {
-                const int s = j & 1;
-                ok = mbar_wait(&kv_empty[s], (uint32_t)(((j >> 1) & 1) ^ 1), p.err, 31);
-                if (!ok) break;
-                const int k0 = key_begin + j * BKV;
                 int pages[4], n_valid = 0;
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
-                    const int key = k0 + g * PAGE;
-                    pages[g] = key < kv_total ? bt[key / PAGE] : -1;
+                    const int i = j * 4 + g;
+                    pages[g] = i < n_pages ? (i < MAX_PAGES_SMEM ? pages_s[i] : bt[first_page + i]) : -1;
                     n_valid += pages[g] >= 0;
                 }
-                mbar_expect_tx(&kv_full[s], (uint32_t)(n_valid * 2 * 2 * PAGE * 128));
-                uint8_t* sK = sKV + (size_t)s * 2 * KV_BYTES;
-                uint8_t* sV = sK + KV_BYTES;
+                // K of tile j: its stage was last used by tile j - 3 (as K, then as P)
+                const int ks = j % K_STAGES, vs = j % V_STAGES;
+                ok = mbar_wait(&k_empty[ks], (uint32_t)(((j / K_STAGES) & 1) ^ 1), p.err, 31);
+                if (!ok) break;
+                mbar_expect_tx(&k_full[ks], (uint32_t)(n_valid * 2 * PAGE * 128));
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
                     if (pages[g] < 0) continue;
                     const int row_k = ((pages[g] * 2 + 0) * p.n_kv_heads + kvh) * PAGE;
+#pragma unroll
+                    for (int a = 0; a < 2; ++a)
+                        tma_load_2d(sK + ks * KV_BYTES + a * ATOM_KV + g * PAGE * 128, &map_kv, &k_full[ks], a * 64, row_k);
+                }
+                ok = mbar_wait(&v_empty[vs], (uint32_t)(((j / V_STAGES) & 1) ^ 1), p.err, 40);
+                if (!ok) break;
+                mbar_expect_tx(&v_full[vs], (uint32_t)(n_valid * 2 * PAGE * 128));
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    if (pages[g] < 0) continue;
                     const int row_v = ((pages[g] * 2 + 1) * p.n_kv_heads + kvh) * PAGE;
 #pragma unroll
-                    for (int a = 0; a < 2; ++a) {
-                        tma_load_2d(sK + a * ATOM_KV + g * PAGE * 128, &map_kv, &kv_full[s], a * 64, row_k);
-                        tma_load_2d(sV + a * ATOM_KV + g * PAGE * 128, &map_kv, &kv_full[s], a * 64, row_v);
-                    }
+                    for (int a = 0; a < 2; ++a)
+                        tma_load_2d(sV + vs * KV_BYTES + a * ATOM_KV + g * PAGE * 128, &map_kv, &v_full[vs], a * 64, row_v);
                 }
             }
         }
@@ -169,9 +198,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         // ---- MMA issuer -----------------------------------------------------------------------------
         if (lane == 0) {
             constexpr uint32_t idesc_qk = idesc_attn(BKV, 0), idesc_pv = idesc_attn(D, 1);
-            const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
+            const uint32_t q_addr = smem_u32(sQ);
             auto issue_qk = [&](int j) {
-                const uint32_t k_addr = smem_u32(sKV + (size_t)(j & 1) * 2 * KV_BYTES);
+                const uint32_t k_addr = smem_u32(sK + (j % K_STAGES) * KV_BYTES);
                 const uint32_t d_tmem = tmem_base + (uint32_t)((j & 1) * BKV);
 #pragma unroll
                 for (int k = 0; k < D / 16; ++k) {
@@ -182,21 +211,24 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 umma_commit(&s_full[j & 1]);
             };
             ok = mbar_wait(&q_full, 0, p.err, 32);
-            if (ok) ok = mbar_wait(&kv_full[0], 0, p.err, 33);
+            if (ok) ok = mbar_wait(&k_full[0], 0, p.err, 33);
             if (ok) { tc_fence_after(); issue_qk(0); }
             for (int j = 0; j < n_tiles && ok; ++j) {
-                if (j + 1 < n_tiles) {
-                    const int n = j + 1;
-                    ok = mbar_wait(&kv_full[n & 1], (uint32_t)((n >> 1) & 1), p.err, 34);
-                    if (ok) ok = mbar_wait(&s_empty[n & 1], (uint32_t)(((n >> 1) & 1) ^ 1), p.err, 35);
-                    if (!ok) break;
+                const int n = j + 1;
+                const uint32_t kf_ph = (uint32_t)((n / K_STAGES) & 1), se_ph = (uint32_t)(((n >> 1) & 1) ^ 1);
+                bool next_issued = n >= n_tiles;
+                // the scores of the next tile first, if its K tile has landed and its S buffer is free
+                if (!next_issued && mbar_try_wait(&k_full[n % K_STAGES], kf_ph) && mbar_try_wait(&s_empty[n & 1], se_ph)) {
                     tc_fence_after();
                     issue_qk(n);
+                    next_issued = true;
                 }
                 ok = mbar_wait(&p_full, (uint32_t)(j & 1), p.err, 36);
+                if (ok) ok = mbar_wait(&v_full[j % V_STAGES], (uint32_t)((j / V_STAGES) & 1), p.err, 41);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t v_addr = smem_u32(sKV + (size_t)(j & 1) * 2 * KV_BYTES + KV_BYTES);
+                const uint32_t p_addr = smem_u32(sK + (j % K_STAGES) * KV_BYTES);      // P lies over K of this tile
+                const uint32_t v_addr = smem_u32(sV + (j % V_STAGES) * KV_BYTES);
 #pragma unroll
                 for (int k = 0; k < BKV / 16; ++k) {
                     const uint64_t adesc = smem_desc_sw128(p_addr + k * 32);
@@ -204,7 +236,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     umma_bf16(tmem_base + 128, adesc, bdesc, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
                 }
                 umma_commit(&o_full);
-                umma_commit(&kv_empty[j & 1]);
+                umma_commit(&k_empty[j % K_STAGES]);
+                umma_commit(&v_empty[j % V_STAGES]);
+                if (!next_issued) {
+                    ok = mbar_wait(&k_full[n % K_STAGES], kf_ph, p.err, 34);
+                    if (ok) ok = mbar_wait(&s_empty[n & 1], se_ph, p.err, 35);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_qk(n);
+                }
             }
         }
     } else {
@@ -278,7 +318,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 }
             }
             // this row of P -> shared memory, 16-byte chunks XOR-swizzled as the MMA reads them
-            uint8_t* prow = sP + r * 128;
+            uint8_t* prow = sK + (j % K_STAGES) * KV_BYTES + r * 128;
 #pragma unroll
             for (int c = 0; c < 8; ++c)
                 *(uint4*)(prow + ((c ^ (r & 7)) << 4)) = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
