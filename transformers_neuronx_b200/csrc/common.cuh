@@ -5,7 +5,6 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
-#include <stdlib.h>
 
 #define TNX_EXPORT extern "C" __attribute__((visibility("default")))
 
@@ -42,9 +41,7 @@ static inline int tnx_launch_ex(int early, void (*kernel)(KArgs...), dim3 grid, 
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
-    static const int mode = getenv("TNX_PDL") ? atoi(getenv("TNX_PDL")) : 1;   // 0: never, 1: as asked, 2: every kernel
-    const bool on = mode == 2 || (mode == 1 && early);
-    cfg.attrs = attr; cfg.numAttrs = on ? 1 : 0;
+    cfg.attrs = attr; cfg.numAttrs = early ? 1 : 0;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
     if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
     return 0;

@@ -786,9 +786,10 @@ TNX_EXPORT int tnx_gemm_tc(const void* A, const void* W, const float* bias, cons
             dim3 grid((M + TILE_P - 1) / TILE_P, (N + 127) / 128, 1);
             return launch<128, 6, false>(mp, mq, p, grid, stream);
         }
-        static const int pair_mode = getenv("TNX_GEMM_PAIR") ? atoi(getenv("TNX_GEMM_PAIR")) : 1;
+        // Enough 256 x 256 tiles to keep the CTA pairs busy: the paired kernel; otherwise the
+        // single-CTA persistent kernel with 128 x 256 tiles.
         const int ptiles_m = (M + 255) / 256, ptiles_n = (N + 255) / 256;
-        if (pair_mode && M >= 256 && ptiles_m * ptiles_n * 8 >= sms * 3) {
+        if (M >= 256 && ptiles_m * ptiles_n * 8 >= sms * 3) {
             if (!make_map(&mq, W, N, K, ldw, 128)) return TNX_ERR_UNSUPPORTED;
             constexpr size_t psmem = (size_t)CSTAGES * (TILE_P * BLOCK_K * 2 + 128 * BLOCK_K * 2) + 1024;
             static bool pconfigured = false;
