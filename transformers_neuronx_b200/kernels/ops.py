@@ -258,6 +258,18 @@ def _state(device):
     return st
 
 
+def _grow(st, key, need, dtype, device, minimum, zero=False):
+    """Scratch buffer `key` with at least `need` elements.  A buffer that is outgrown is kept alive:
+    captured CUDA graphs still hold its address."""
+    cur = st.get(key)
+    if cur is None or cur.numel() < need:
+        if cur is not None:
+            st.setdefault("retired", []).append(cur)
+        n = max(int(need), int(minimum))
+        st[key] = torch.zeros(n, dtype=dtype, device=device) if zero else torch.empty(n, dtype=dtype, device=device)
+    return st[key]
+
+
 def raise_on_device_error(device=None):
     """Reads the error word that kernels with bounded waits set (this synchronises)."""
     for key, st in _dev_state.items():
@@ -319,11 +331,8 @@ def gemm_tc(a, w, out, bias=None, residual=None, relu=False, splits=None):
     scratch = None
     if nbytes.value:
         need = nbytes.value // 4
-        if st["scratch"] is None or st["scratch"].numel() < need:
-            st["scratch"] = torch.empty(max(need, 1 << 20), dtype=torch.float32, device=a.device)
-        if st["counters"].numel() < ncnt.value:
-            st["counters"] = torch.zeros(ncnt.value, dtype=torch.int32, device=a.device)
-        scratch = st["scratch"]
+        scratch = _grow(st, "scratch", need, torch.float32, a.device, 1 << 22)
+        _grow(st, "counters", ncnt.value, torch.int32, a.device, 1024, zero=True)
     _check(lib.tnx_gemm_tc(_p(a), _p(w), _p(bias), _p(residual), _p(out), c_int(M), c_int(N), c_int(K),
                            c_int(lda), c_int(ldw), c_int(ldc), c_int(1 if relu else 0), c_int(_is_bf16(out)),
                            n_splits, _p(scratch), _p(st["counters"]), _p(st["err"]), _stream()), "gemm_tc")
@@ -356,11 +365,8 @@ def attention_decode(q, cache, block_tables, token_request, positions, out, n_he
     scratch = None
     if n_splits > 1:
         need = R * n_heads * n_splits * (d + 2)
-        if st.get("att_scratch") is None or st["att_scratch"].numel() < need:
-            st["att_scratch"] = torch.empty(max(need, 1 << 18), dtype=torch.float32, device=q.device)
-        if st.get("att_counters") is None or st["att_counters"].numel() < R * n_heads:
-            st["att_counters"] = torch.zeros(max(R * n_heads, 4096), dtype=torch.int32, device=q.device)
-        scratch = st["att_scratch"]
+        scratch = _grow(st, "att_scratch", need, torch.float32, q.device, 1 << 20)
+        _grow(st, "att_counters", R * n_heads, torch.int32, q.device, 8192, zero=True)
     _check(lib.tnx_attention_decode(_p(q), c_int(q_stride), _p(cache), _p(block_tables), c_int(block_tables.stride(0)),
                                     _p(rows), _p(token_request), _p(positions), _p(out), c_int(out_stride), c_int(R),
                                     c_int(n_heads), c_int(n_kv), c_int(d), c_int(ps), c_int(window or 0), c_float(scale),
