@@ -36,7 +36,7 @@ PROMPT_TEXT = "Hello, I'm a language model,"
 
 def _parser():
     ap = argparse.ArgumentParser(prog="opt_demo")
-    ap.add_argument("--amp", default="f32", choices=["f32", "bf16"])
+    ap.add_argument("--amp", default="f32", choices=["f32", "f16", "bf16"], help="f16 is served as bf16")
     ap.add_argument("--model_name", default=None, help="local folder of a pretrained model (for save)")
     sub = ap.add_subparsers(dest="which", required=True)
     sp = sub.add_parser("save")
@@ -62,7 +62,7 @@ def _parser():
 
 
 def save(args):
-    dtype = torch.bfloat16 if canonical_dtype(args.amp) == "bfloat16" else torch.float32
+    dtype = torch.float32 if args.amp == "f32" else torch.bfloat16
     if args.random:
         assert args.config, "Please provide the config.json like: --config=./config.json"
         assert os.path.exists(args.config), f"File {args.config} does not exist."

@@ -36,6 +36,10 @@ class OPTForSampling:
             raise KeyError(f"unknown argument(s): {sorted(kwargs)}")
         if amp is None:
             amp = "bf16" if str(config.torch_dtype).replace("torch.", "") in ("float16", "bfloat16") else "f32"
+        if str(amp).replace("torch.", "") in ("f16", "fp16", "float16", "half"):
+            warnings.warn("amp='f16' is served as bfloat16: this engine's 16-bit type (same size and speed, "
+                          "8 bits of mantissa instead of 11)")
+            amp = "bf16"
         self.amp = amp
         self.dtype = canonical_dtype(amp)
         max_bucket = max(n_positions) if isinstance(n_positions, (list, tuple)) else n_positions
