@@ -4,7 +4,9 @@ It rests on the formulas of aws-neuron/transformers-neuronx alone: that project
 states the model only as an HLO graph for the Neuron compiler (its
 ``OPTDecoderLayer`` in ``src/transformers_neuronx/opt/model.py:247-257`` has no
 forward method), so its model code can neither be imported nor compiled on a
-CPU here and no golden output of it exists.  Each function below cites the
+CPU here and no golden logits of it exist.  What of it does run on the CPU (the
+checkpoint writer's tensor names and shapes, the top-k / top-p filter) is pinned
+by tests/golden/ and tests/test_golden.py.  Each function below cites the
 place of its formula, by the file's path within that project
 (``T/`` = ``src/transformers_neuronx/``).
 
