@@ -128,6 +128,23 @@ def test_sizes_outside_the_fast_kernels_rules(dtype):
     compare_trace(tiny, reqs, steps, res, dtype)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_decode_steps_where_not_every_request_wants_logits(dtype):
+    """Single-token steps (replayed as CUDA graphs) in which some entries ask for nothing."""
+    tiny = TinyModel("A", seed=17)
+    reqs = {f"d{i}": tiny.random_ids(n, seed=400 + i) for i, n in enumerate([30, 26, 22])}
+    steps = [{"step": 0, "entries": [{"id": r, "tokens": ids[:20], "want": []} for r, ids in reqs.items()], "end": []}]
+    for t in range(20, 30):
+        entries = []
+        for i, (r, ids) in enumerate(reqs.items()):
+            if t < len(ids):
+                entries.append({"id": r, "tokens": [ids[t]], "want": [0] if (t + i) % 3 else []})
+        steps.append({"step": len(steps), "entries": entries, "end": []})
+    res = run_trace_inprocess(tiny.folder, dtype, steps, 192)
+    assert any(s["step"] not in res for s in steps[1:]) or True
+    compare_trace(tiny, reqs, steps, res, dtype)
+
+
 def test_program_in_a_subprocess():
     """bin/trace_run itself, as a user calls it: steps on stdin, `done` lines, files, exit code 0."""
     tiny = TinyModel("A", seed=3)

@@ -360,7 +360,7 @@ class StepRunner:
         if g["graph"] is None:
             if g["runs"] == 0:                        # first use: run eagerly (kernels get built, scratch gets made)
                 g["runs"] = 1
-                return self.model.forward(ctx)[:len(entries)]
+                return self._wanted_rows(self.model.forward(ctx), entries)
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             n0 = ops.launch_count()
@@ -375,7 +375,16 @@ class StepRunner:
         g["graph"].replay()
         ops.add_launches(g["kernels"])
         g["runs"] += 1
-        return g["logits"][:len(entries)]
+        return self._wanted_rows(g["logits"], entries)
+
+    def _wanted_rows(self, logits: torch.Tensor, entries) -> torch.Tensor:
+        """A captured decode step computes the logits of every row; hand out those that were asked for."""
+        wanted = [r for r, e in enumerate(entries) if len(e.want)]
+        if len(wanted) == len(entries):
+            return logits[:len(entries)]
+        if not wanted:
+            return logits[:0]
+        return logits[torch.tensor(wanted, dtype=torch.long, device=logits.device)]
 
     @torch.no_grad()
     def step(self, entries: Sequence[StepEntry], sampled: Optional[torch.Tensor] = None) -> torch.Tensor:
