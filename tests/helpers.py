@@ -33,7 +33,12 @@ CONFIG_C = dict(vocab_size=333, hidden_size=96, num_hidden_layers=2, num_attenti
                 _remove_final_layer_norm=True, enable_bias=True, layer_norm_elementwise_affine=False,
                 layer_norm_eps=1e-4, activation_function="relu", init_std=0.04,
                 architectures=["OPTForCausalLM"], model_type="opt")
-CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C}
+# Head size 128 (the size of the large OPT models): the tcgen05 attention kernel, longer contexts.
+CONFIG_D = dict(vocab_size=2003, hidden_size=256, num_hidden_layers=2, num_attention_heads=2, ffn_dim=520,
+                max_position_embeddings=600, word_embed_proj_dim=256, do_layer_norm_before=True, enable_bias=True,
+                layer_norm_elementwise_affine=True, layer_norm_eps=1e-5, activation_function="relu", init_std=0.03,
+                architectures=["OPTForCausalLM"], model_type="opt")
+CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C, "D": CONFIG_D}
 
 # Largest allowed |engine - plain| as a fraction of the largest |plain logit| of the compared rows.
 # float32: both sides compute in 32-bit and differ by the order of additions only.

@@ -129,6 +129,17 @@ def test_sizes_outside_the_fast_kernels_rules(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+def test_head_size_128_long_contexts(dtype):
+    """Configuration D: head size 128 (the tcgen05 attention kernel in bfloat16), prompts of several
+    hundred tokens in portions that start inside a page and cross 128-row tiles, beside decode tokens."""
+    tiny = TinyModel("D", seed=19)
+    reqs = {f"l{i}": tiny.random_ids(n, seed=500 + i) for i, n in enumerate([590, 133, 300, 64, 411, 257])}
+    steps, peak = mixed_steps(reqs, chunk_sizes=(129, 16, 2, 200, 75, 128), decode_tail=9, max_live=3)
+    res = run_trace_inprocess(tiny.folder, dtype, steps, peak)
+    compare_trace(tiny, reqs, steps, res, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_decode_steps_where_not_every_request_wants_logits(dtype):
     """Single-token steps (replayed as CUDA graphs) in which some entries ask for nothing."""
     tiny = TinyModel("A", seed=17)
