@@ -29,6 +29,8 @@ OPT_6_7B = dict(vocab_size=50272, hidden_size=4096, num_hidden_layers=32, num_at
                 max_position_embeddings=2048, word_embed_proj_dim=4096, do_layer_norm_before=True, enable_bias=True,
                 layer_norm_elementwise_affine=True, activation_function="relu", init_std=0.02,
                 architectures=["OPTForCausalLM"], model_type="opt", torch_dtype="bfloat16")
+OPT_13B = dict(OPT_6_7B, hidden_size=5120, num_hidden_layers=40, num_attention_heads=40, ffn_dim=20480, word_embed_proj_dim=5120)
+OPT_30B = dict(OPT_6_7B, hidden_size=7168, num_hidden_layers=48, num_attention_heads=56, ffn_dim=28672, word_embed_proj_dim=7168)
 CONTEXT = 2048
 PREFILL_TOKENS = 2048
 
@@ -80,13 +82,13 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def build(n_layers, dtype="bfloat16"):
+def build(n_layers, dtype="bfloat16", base=None):
     import torch
     from transformers_neuronx_b200.config import OPTConfig
     from transformers_neuronx_b200.engine import build_model
     from transformers_neuronx_b200.models import opt as opt_arch
     from transformers_neuronx_b200.models.decoder import DecoderModel
-    cfg = OPTConfig.from_dict(dict(OPT_6_7B, num_hidden_layers=n_layers))
+    cfg = OPTConfig.from_dict(dict(base or OPT_6_7B, num_hidden_layers=n_layers))
     spec = opt_arch.build_spec(cfg)
     dev = torch.device("cuda:0")
     g = torch.Generator(device=dev).manual_seed(0)
@@ -234,6 +236,44 @@ def time_prefill(model, cfg, steps, warmup):
     return sorted(times)[len(times) // 2]
 
 
+def extra_workload(name, steps, warmup):
+    """The two further workloads that BASELINE.md lists, each printed as one JSON line of its own:
+    decode30b: OPT-30B sizes, batch 16, context ending at 2,048, greedy;
+    mixed13b:  OPT-13B sizes, 32 requests with prompts of 64..1,536 tokens, 512-token prompt portions
+               beside the decode tokens of the others, 256 new tokens each at temperature 0.7,
+               through LLMEngine.generate (tokens per second of wall clock, prefill included)."""
+    import torch
+    if name == "decode30b":
+        model, cfg = build(OPT_30B["num_hidden_layers"], base=OPT_30B)
+        ms, launches, _, _ = time_decode(model, cfg, 16, steps, warmup)
+        nbytes = decode_bytes(model, cfg, 16, CONTEXT - steps / 2)
+        hbm, _, src = peaks()
+        print(json.dumps({"workload": name, "value": round(16 / (ms / 1e3), 1), "unit": "tokens/s", "ms_per_step": round(ms, 3),
+                          "batch": 16, "context": CONTEXT, "layers": cfg.num_hidden_layers,
+                          "roofline_frac": round(nbytes / (ms / 1e3) / 1e9 / hbm, 4), "peaks": src}))
+        return 0
+    from transformers_neuronx_b200.config import EngineConfig
+    from transformers_neuronx_b200.engine import LLMEngine, SamplingParams
+    model, cfg = build(OPT_13B["num_hidden_layers"], base=OPT_13B)
+    g = torch.Generator().manual_seed(4)
+    lens = torch.randint(64, 1537, (32,), generator=g).tolist()
+    prompts = [torch.randint(3, cfg.vocab_size, (n,), generator=g).tolist() for n in lens]
+    eng = LLMEngine(model, EngineConfig(dtype="bfloat16", max_num_seqs=32, max_batch_tokens=512 + 32,
+                                        max_tokens=32 * 1792, max_model_len=CONTEXT))
+    params = [SamplingParams(temperature=0.7, seed=i) for i in range(32)]
+    eng.generate(prompts[:4], 8, params[:4], stop_on_eos=False)           # warm-up: kernels, graphs
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    out = eng.generate(prompts, 256, params, stop_on_eos=False)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    n_new = sum(len(o) for o in out)
+    print(json.dumps({"workload": name, "value": round(n_new / dt, 1), "unit": "new tokens/s (wall clock, prefill included)",
+                      "seconds": round(dt, 3), "requests": 32, "prompt_tokens": sum(lens), "new_tokens": n_new,
+                      "steps": eng.stats["steps"], "preemptions": eng.stats["preemptions"], "layers": cfg.num_hidden_layers}))
+    return 0
+
+
 def reference_arm():
     why = ("aws-neuron/transformers-neuronx needs torch_neuronx, libneuronxla and the neuronx-cc compiler for "
            "Trainium/Inferentia; none exists for CUDA, so its OPT path cannot run on a B200")
@@ -250,6 +290,8 @@ def main():
     ap.add_argument("--layers", type=int, default=OPT_6_7B["num_hidden_layers"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--workload", default=None, choices=["decode30b", "mixed13b"],
+                    help="run one of the further workloads instead of the default line")
     ap.add_argument("--only", default=None, choices=["decode", "prefill"],
                     help="run just this part and print its time (for profiling a small case)")
     a = ap.parse_args()
@@ -259,6 +301,8 @@ def main():
         print("bench.py: this engine runs on one GPU; --gpus must be 1")
         return 2
     a.warmup = max(a.warmup, 3)
+    if a.workload:
+        return extra_workload(a.workload, a.steps, a.warmup)
     import torch
     hbm_gbs, tflops, peak_src = peaks()
     model, cfg = build(a.layers)
