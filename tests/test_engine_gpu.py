@@ -167,6 +167,20 @@ def test_eos_stops_a_request(tiny):
     assert out == first[:first.index(first[2]) + 1]
 
 
+def test_kernel_profile(tiny):
+    """The profiling helper brackets every kernel call with events and names the families."""
+    from transformers_neuronx_b200.kernels import kernel_profile
+    eng = _engine(tiny, "bfloat16", max_num_seqs=2, use_cuda_graphs=False)
+    with kernel_profile() as prof:
+        eng.generate([tiny.random_ids(20, seed=1)], 4, stop_on_eos=False)
+    t = prof.totals()
+    assert {"embed", "layer_norm", "kv_append", "sample"} <= set(t)
+    assert ("gemm_tc" in t) or ("gemm_simt" in t)
+    assert all(ms >= 0 and n > 0 for ms, n in t.values()) and "share" in prof.report()
+    from transformers_neuronx_b200.kernels import ops
+    assert ops.embed.__name__ == "embed"                      # the wrappers are gone
+
+
 def test_command_line_save_and_run(tmp_path):
     cfg = tmp_path / "cfg.json"
     import json

@@ -394,3 +394,15 @@ def test_attention_prefill_tc(n_heads, n_kv, window):
     keep[case.decode_rows.long()] = False
     assert rel_err(out[keep], want[keep]) <= 1.5e-2
     assert float(out[~keep].float().abs().max()) == 0.0
+
+
+def test_attention_prefill_tc_more_pages_than_fit_in_shared_memory():
+    """A context of more than 2,048 keys: the page numbers beyond the first 128 are read from global memory."""
+    d, n_heads = 128, 2
+    case = PagedCase([(2900, 150), (0, 300)], n_heads, n_heads, d, torch.bfloat16, seed=5, poison=1.0e4)
+    scale = 1.0 / math.sqrt(d)
+    out = torch.zeros(case.N, n_heads * d, dtype=torch.bfloat16, device=DEV)
+    ops().attention_prefill_tc(case.q_flat, case.cache, case.bt, case.tile_req, case.tile_q0, case.q_start, case.q_len,
+                               case.ctx_len, out, n_heads, scale, 0)
+    ops().raise_on_device_error()
+    assert rel_err(out, case.want(scale, None)) <= 1.5e-2
