@@ -53,7 +53,8 @@ def test_gemm_simt_rows_do_not_depend_on_the_batch():
 
 TC_SHAPES = [(1, 128, 64), (3, 96, 320), (16, 4096, 1024), (17, 1000, 96), (33, 200, 136), (64, 512, 4096),
              (65, 384, 256), (128, 128, 64), (200, 1000, 328), (300, 520, 1032), (2048, 768, 512),
-             (1024, 4096, 512), (1000, 4000, 328), (300, 9000, 136), (513, 7100, 72)]
+             (1024, 4096, 512), (1000, 4000, 328), (300, 9000, 136), (513, 7100, 72), (520, 7102, 72), (2100, 2300, 1096),
+             (1792, 2048, 16384), (2000, 3300, 8200), (1100, 4090, 4096)]     # the last three share tiles out by K blocks
 
 
 @pytest.mark.parametrize("M,N,K", TC_SHAPES)
@@ -76,6 +77,12 @@ def test_gemm_tc(M, N, K):
     o.gemm_tc(a, w, res, bias=bias, residual=res)
     o.raise_on_device_error()
     assert rel_err(res, want3) <= 2e-5, "bias + residual in place"
+    res2 = torch.randn(M, N, generator=g).to(DEV)
+    keep = res2.clone()
+    out4 = torch.full((M, N), 7.0, dtype=torch.float32, device=DEV)
+    o.gemm_tc(a, w, out4, residual=res2)
+    o.raise_on_device_error()
+    assert rel_err(out4, want + keep) <= 2e-5 and torch.equal(res2, keep), "residual beside the output"
 
 
 @pytest.mark.parametrize("M,N,K,splits", [(8, 256, 4096, 4), (64, 130, 1024, 16), (1, 128, 512, 2), (20, 300, 1160, 3)])

@@ -49,6 +49,7 @@ struct Params {
     float* partials;             // [splits][rows_p_padded][rows_q_padded] when splits > 1
     int* counters;               // one per output tile, zero between calls
     int* err;
+    int sk_tiles;                // paired kernel: the last sk_tiles output tiles are shared out by K blocks
 };
 
 template <int BN, bool SWAP>
@@ -246,7 +247,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         // Epilogue warps 2..5: TMEM lane quadrant = warp % 4.
         const int quad = warp & 3;
         const int row_in_tile = quad * 32 + lane;
-        ok = mbar_wait(&tmem_full_bar, 0, p.err, 3);
+        ok = __all_sync(0xffffffffu, mbar_wait(&tmem_full_bar, 0, p.err, 3));     // one answer for the warp
         tc_fence_after();
         const int lane_row = tile_p * TILE_P + row_in_tile;
         if (ok) {
@@ -333,11 +334,42 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     }
 }
 
+// Where an epilogue warp takes its 32 rows x 32 columns of sums from: tensor memory, or (a tile
+// whose K range was shared out over several CTAs) the partial tiles in scratch memory, added in the
+// order of the contributors so that the sum does not depend on who finished last.
+struct AccSource {
+    uint32_t tmem_addr;          // this warp's lanes, column 0 of the accumulator
+    const float* part0;          // null, or the partial tiles (this thread's row): contributor 0 lies at
+    int n_parts;                 // part0 + first_off, contributor s > 0 at part0 + s * stride
+    long long first_off, stride;
+};
+constexpr int PART_LD = 128;     // partial tiles are [column][128 rows]: the lanes of a warp write 128 bytes
+
+__device__ __forceinline__ void acc_load_begin(const AccSource& a, int c, uint32_t (&r)[32]) {
+    if (a.part0 == nullptr) { tmem_ld32(a.tmem_addr + (uint32_t)c, r); return; }
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = 0.f;
+    for (int s = 0; s < a.n_parts; ++s) {
+        const float* src = a.part0 + (s == 0 ? a.first_off : a.stride * s) + (size_t)c * PART_LD;
+        float f[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) f[j] = __ldcg(src + (size_t)j * PART_LD);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] += f[j];
+    }
+#pragma unroll
+    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(v[j]);
+}
+__device__ __forceinline__ void acc_load_end(const AccSource& a) {
+    if (a.part0 == nullptr) tmem_ld_wait();
+}
+
 // Epilogue of one warp of the many-token kernels: its 32 accumulator rows x WIDTH columns -> C.
 // With a residual (32-bit, possibly C itself) the loads of the next 32 columns are issued before
 // the current ones are stored, so that a tile costs one memory round trip, not one per chunk.
 template <int WIDTH>
-__device__ __forceinline__ void drain_accumulator(const Params& p, uint32_t tmem_addr, int row, int col_base,
+__device__ __forceinline__ void drain_accumulator(const Params& p, const AccSource& acc, int row, int col_base,
                                                   const float* bias_tile) {
     // The choice of path must be the same for all lanes of the warp: tcgen05.ld is a warp-wide
     // instruction.  Rows beyond the matrix are handled by predicating the loads and stores.
@@ -347,8 +379,8 @@ __device__ __forceinline__ void drain_accumulator(const Params& p, uint32_t tmem
 #pragma unroll 1
         for (int c = 0; c < WIDTH; c += 32) {
             uint32_t r[32];
-            tmem_ld32(tmem_addr + (uint32_t)c, r);
-            tmem_ld_wait();
+            acc_load_begin(acc, c, r);
+            acc_load_end(acc);
             float v[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
@@ -365,12 +397,12 @@ __device__ __forceinline__ void drain_accumulator(const Params& p, uint32_t tmem
 #pragma unroll 1
     for (int c = 0; c < WIDTH; c += 32) {
         uint32_t r[32];
-        tmem_ld32(tmem_addr + (uint32_t)c, r);
+        acc_load_begin(acc, c, r);
         if (c + 32 < WIDTH && valid) {
 #pragma unroll
             for (int q = 0; q < 8; ++q) nxt[q] = __ldcg((const float4*)(res_row + c + 32) + q);
         }
-        tmem_ld_wait();
+        acc_load_end(acc);
         const float* b = p.bias ? bias_tile + c : nullptr;
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
@@ -505,11 +537,11 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
                 for (int j = et; j < PBN; j += 128) bias_tile[acc][j] = (tn * PBN + j < p.rows_q) ? p.bias[tn * PBN + j] : 0.f;
                 asm volatile("bar.sync 1, 128;" ::: "memory");
             }
-            ok = mbar_wait(&acc_full[acc], acc_ph, p.err, 14);
+            ok = __all_sync(0xffffffffu, mbar_wait(&acc_full[acc], acc_ph, p.err, 14));
             if (!ok) break;
             tc_fence_after();
-            drain_accumulator<PBN>(p, tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * PBN),
-                                   tm * TILE_P + row_in_tile, tn * PBN, bias_tile[acc]);
+            const AccSource src{tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * PBN), nullptr, 0, 0, 0};
+            drain_accumulator<PBN>(p, src, tm * TILE_P + row_in_tile, tn * PBN, bias_tile[acc]);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) {
@@ -529,6 +561,79 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
     }
 }
 
+// Epilogue of one warp with a 32-bit residual, through TMA: the residual's 32 x 32 boxes are
+// fetched into shared memory two boxes ahead (the first two while the MMAs of the tile still run),
+// the accumulator is added in place and the box is written back by a TMA store.  Global memory is
+// then read and written in whole 128-byte rows instead of one 16-byte piece per thread and row, and
+// no thread waits for a load.  Rows and columns beyond the matrix are zero-filled by the load and
+// clipped by the store.  `n` counts the boxes this warp has handled since the kernel began: box n
+// uses buffer n % 3 and the phase (n / 3) & 1 of that buffer's barrier.
+constexpr int EPI_BUFS = 3;
+constexpr int EPI_BOX_BYTES = 32 * 32 * 4;                    // 4 KB: 32 rows x 128 bytes, 128-byte swizzle
+
+struct EpilogueTma {
+    const CUtensorMap* map_res;
+    const CUtensorMap* map_out;
+    uint8_t* bufs;                // this warp's EPI_BUFS boxes, 1024-byte aligned
+    uint64_t* bars;               // this warp's EPI_BUFS barriers
+    uint32_t n;
+};
+
+// Lane 0 only.  Fetch box `c` of the tile (columns col_base + 32 c .., rows row0 ..) as box number `n`.
+__device__ __forceinline__ void epilogue_tma_fetch(const EpilogueTma& e, uint32_t n, int row0, int col) {
+    const uint32_t b = n % EPI_BUFS;
+    mbar_expect_tx(&e.bars[b], EPI_BOX_BYTES);
+    tma_load_2d(e.bufs + (size_t)b * EPI_BOX_BYTES, e.map_res, &e.bars[b], col, row0);
+}
+
+// Lane 0, before the accumulator is ready: start the first two boxes of the tile.
+__device__ __forceinline__ void epilogue_tma_begin(const EpilogueTma& e, int row0, int col_base) {
+    tma_store_wait_read<1>();                                 // the buffers of boxes n and n+1 are no longer being stored from
+    epilogue_tma_fetch(e, e.n, row0, col_base);
+    epilogue_tma_fetch(e, e.n + 1, row0, col_base + 32);
+}
+
+template <int WIDTH>
+__device__ __forceinline__ bool drain_accumulator_tma(const Params& p, EpilogueTma& e, const AccSource& acc, int row0,
+                                                      int col_base, const float* bias_tile, int lane) {
+#pragma unroll 1
+    for (int c = 0; c < WIDTH; c += 32) {
+        const uint32_t b = e.n % EPI_BUFS;
+        uint32_t r[32];
+        acc_load_begin(acc, c, r);
+        const bool got = __all_sync(0xffffffffu, mbar_wait(&e.bars[b], (e.n / EPI_BUFS) & 1, p.err, 31));
+        acc_load_end(acc);
+        if (!got) return false;                               // the same answer in every lane of the warp
+        // lane = row of the box; its 128 bytes are eight 16-byte pieces, piece j stored at j ^ (row % 8)
+        uint8_t* rowp = e.bufs + (size_t)b * EPI_BOX_BYTES + lane * 128;
+        const float* bias = p.bias ? bias_tile + c : nullptr;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            float4* cell = (float4*)(rowp + ((q ^ (lane & 7)) << 4));
+            float4 x = *cell;
+            float t0 = __uint_as_float(r[4 * q]), t1 = __uint_as_float(r[4 * q + 1]);
+            float t2 = __uint_as_float(r[4 * q + 2]), t3 = __uint_as_float(r[4 * q + 3]);
+            if (bias) { t0 += bias[4 * q]; t1 += bias[4 * q + 1]; t2 += bias[4 * q + 2]; t3 += bias[4 * q + 3]; }
+            if (p.relu) { t0 = fmaxf(t0, 0.f); t1 = fmaxf(t1, 0.f); t2 = fmaxf(t2, 0.f); t3 = fmaxf(t3, 0.f); }
+            x.x += t0; x.y += t1; x.z += t2; x.w += t3;
+            *cell = x;
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+            tma_store_2d(e.map_out, e.bufs + (size_t)b * EPI_BOX_BYTES, col_base + c, row0);
+            tma_store_commit();
+            if (c + 64 < WIDTH) {
+                tma_store_wait_read<1>();                     // the box before this one has left its buffer
+                epilogue_tma_fetch(e, e.n + 2, row0, col_base + c + 64);
+            }
+        }
+        __syncwarp();
+        ++e.n;
+    }
+    return true;
+}
+
 // ---- many tokens, CTA pairs: 256 x 256 tiles with tcgen05 cta_group::2 -------------------------------
 //
 // Two CTAs on neighbouring SMs form a cluster and share one MMA: CTA r of the pair holds rows
@@ -537,8 +642,9 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
 // for both.  A stage is 32 KB per CTA instead of 48 KB for the same MMA work, so six stages fit
 // and each SM takes in a third fewer bytes per FLOP.  Each CTA loads its own tiles with TMA (no
 // multicast); loads of both CTAs complete the full-barrier of CTA 0; the MMA thread's commits
-// release the stage in both CTAs.
-constexpr int CSTAGES = 6;
+// release the stage in both CTAs.  Five stages leave room for the boxes of the TMA epilogue.
+constexpr int CSTAGES = 5;
+constexpr int PAIR_EPI_BYTES = 4 * EPI_BUFS * EPI_BOX_BYTES;     // 48 KB: three boxes for each epilogue warp
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
@@ -579,13 +685,15 @@ __host__ __device__ constexpr uint32_t instr_desc_pair(int n) {      // M = 256 
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
-                    const Params p, int tiles_m, int tiles_n) {
+                    const __grid_constant__ CUtensorMap map_res, const __grid_constant__ CUtensorMap map_out,
+                    const Params p, int tiles_m, int tiles_n, int tma_epilogue) {
     constexpr int A_BYTES = TILE_P * BLOCK_K * 2;             // 16 KB: this CTA's 128 rows of A
     constexpr int B_BYTES = 128 * BLOCK_K * 2;                // 16 KB: this CTA's 128 rows of the 256-row B tile
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    __shared__ uint64_t full_bar[CSTAGES], empty_bar[CSTAGES], acc_full[2], acc_empty[2];
+    uint8_t* epi_smem = smem + (size_t)CSTAGES * STAGE_BYTES;  // 1024-byte aligned: the stages are 32 KB
+    __shared__ uint64_t full_bar[CSTAGES], empty_bar[CSTAGES], acc_full[2], acc_empty[2], epi_bar[4][EPI_BUFS];
     __shared__ uint32_t tmem_base_smem;
     __shared__ float bias_tile[2][256];
 
@@ -594,33 +702,61 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     const bool leader = rank == 0;
     const int num_kb = (p.K + BLOCK_K - 1) / BLOCK_K;
     const int n_tiles = tiles_m * tiles_n;                    // 256 x 256 tiles
-    const int first = blockIdx.x >> 1, stride = gridDim.x >> 1;
-    const int my_tiles = first < n_tiles ? (n_tiles - first + stride - 1) / stride : 0;
-    const long long total = (long long)my_tiles * num_kb;
+    // Work of pair g of G.  Tiles [0, dp_tiles) are computed whole, tile g + t * G by pair g.  The
+    // last sk_tiles tiles (fewer than G: they would leave pairs idle in a last wave) are laid end to
+    // end as sk_tiles * num_kb K blocks and cut into G equal runs; a run covers parts of at most
+    // two tiles (its "segments"), which come first in the pair's list of items.
+    const int G = gridDim.x >> 1, g = blockIdx.x >> 1;
+    const int dp_tiles = n_tiles - p.sk_tiles;
+    const int my_dp = g < dp_tiles ? (dp_tiles - g + G - 1) / G : 0;
+    const long long U = (long long)p.sk_tiles * num_kb;
+    const long long u0 = U * g / G, u1 = U * (g + 1) / G;
+    const int seg_tile0 = (int)(u0 / num_kb);                 // first shared tile this pair touches
+    const int n_seg = u1 > u0 ? (int)((u1 - 1) / num_kb) - seg_tile0 + 1 : 0;
+    const int n_items = n_seg + my_dp;
+    const long long total = (u1 - u0) + (long long)my_dp * num_kb;
 
-    auto tile_of = [&](long long it, int& tm, int& tn, int& kb) {
-        const int t = first + (int)(it / num_kb) * stride;
-        kb = (int)(it % num_kb);
-        tm = t % tiles_m; tn = t / tiles_m;
+    // item i -> tile, K blocks [kb0, kb1)
+    auto item_of = [&](int i, int& tile, int& kb0, int& kb1) {
+        if (i < n_seg) {
+            const int rel = seg_tile0 + i;
+            const long long lo = (long long)rel * num_kb, hi = lo + num_kb;
+            kb0 = (int)((u0 > lo ? u0 : lo) - lo);
+            kb1 = (int)((u1 < hi ? u1 : hi) - lo);
+            tile = dp_tiles + rel;
+        } else {
+            tile = g + (i - n_seg) * G; kb0 = 0; kb1 = num_kb;
+        }
+    };
+    // A walk over the K blocks this pair loads, item after item, without a division per step: the
+    // loading thread has a few hundred cycles for each.
+    struct Cursor { int item, kb, kb1, x_row, w_row, stage; };
+    auto cursor_set = [&](Cursor& c) {
+        if (c.item >= n_items) return;
+        int tile; item_of(c.item, tile, c.kb, c.kb1);
+        c.x_row = (tile % tiles_m) * 256 + (int)rank * 128;
+        c.w_row = (tile / tiles_m) * 256 + (int)rank * 128;
+    };
+    auto cursor_next = [&](Cursor& c) {
+        c.stage = c.stage + 1 == CSTAGES ? 0 : c.stage + 1;
+        if (++c.kb == c.kb1) { ++c.item; cursor_set(c); }
     };
     // shared::cluster addresses of CTA 0's full barriers (the ones the MMA thread waits on)
     auto full0 = [&](int s) { return map_to_cta(smem_u32(&full_bar[s]), 0); };
-    auto load_weights = [&](long long it) {
-        int tm, tn, kb; tile_of(it, tm, tn, kb);
-        const int s = (int)(it % CSTAGES);
-        if (leader) mbar_expect_tx(&full_bar[s], 2 * STAGE_BYTES);     // both CTAs' bytes land on this barrier
-        tma_load_2d_pair(smem + (size_t)s * STAGE_BYTES + A_BYTES, &map_q, full0(s), kb * BLOCK_K, tn * 256 + (int)rank * 128);
+    auto load_weights = [&](const Cursor& c) {
+        if (leader) mbar_expect_tx(&full_bar[c.stage], 2 * STAGE_BYTES);     // both CTAs' bytes land on this barrier
+        tma_load_2d_pair(smem + (size_t)c.stage * STAGE_BYTES + A_BYTES, &map_q, full0(c.stage), c.kb * BLOCK_K, c.w_row);
     };
-    auto load_activations = [&](long long it) {
-        int tm, tn, kb; tile_of(it, tm, tn, kb);
-        const int s = (int)(it % CSTAGES);
-        tma_load_2d_pair(smem + (size_t)s * STAGE_BYTES, &map_p, full0(s), kb * BLOCK_K, tm * 256 + (int)rank * 128);
+    auto load_activations = [&](const Cursor& c) {
+        tma_load_2d_pair(smem + (size_t)c.stage * STAGE_BYTES, &map_p, full0(c.stage), c.kb * BLOCK_K, c.x_row);
     };
 
     pdl_launch_dependents();
     if (threadIdx.x == 0) {
         for (int s = 0; s < CSTAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 8); }   // 4 warps x 2 CTAs
+        for (int w = 0; w < 4; ++w)
+            for (int b = 0; b < EPI_BUFS; ++b) mbar_init(&epi_bar[w][b], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_p) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_q) : "memory");
@@ -633,47 +769,55 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     __syncthreads();
     cluster_sync();                                           // both CTAs' barriers exist before anything remote
     tc_fence_after();
-    long long issued = 0;
-    if (threadIdx.x == 0)
-        for (; issued < total && issued < CSTAGES; ++issued) load_weights(issued);   // weights: before the dependency wait
+    int issued = 0;
+    Cursor cw{0, 0, 0, 0, 0, 0};
+    if (threadIdx.x == 0) {
+        cursor_set(cw);
+        for (; issued < total && issued < CSTAGES; ++issued) { load_weights(cw); cursor_next(cw); }   // weights: before the dependency wait
+    }
     pdl_wait();
     const uint32_t tmem_base = tmem_base_smem;
     bool ok = true;
 
     if (warp == 0) {
         if (lane == 0) {
-            for (long long it = 0; it < issued; ++it) load_activations(it);
+            Cursor ca{0, 0, 0, 0, 0, 0};
+            cursor_set(ca);
+            for (int it = 0; it < issued; ++it) { load_activations(ca); cursor_next(ca); }
+            uint32_t ph = 0;                                  // parity of the stages' second use
             for (long long it = issued; it < total && ok; ++it) {
-                const int s = (int)(it % CSTAGES);
-                const uint32_t ph = (uint32_t)((it / CSTAGES) & 1);
-                ok = mbar_wait(&empty_bar[s], ph ^ 1, p.err, 21);
+                ok = mbar_wait(&empty_bar[cw.stage], ph, p.err, 21);
                 if (!ok) break;
-                load_weights(it);
-                load_activations(it);
+                load_weights(cw);
+                load_activations(cw);
+                cursor_next(cw);
+                if (cw.stage == 0) ph ^= 1;
             }
         }
     } else if (warp == 1) {
         if (leader && lane == 0) {
             constexpr uint32_t idesc = instr_desc_pair(256);
-            long long it = 0;
-            for (int t = 0; t < my_tiles && ok; ++t) {
+            int mma_stage = 0;
+            uint32_t mma_phase = 0;
+            for (int t = 0; t < n_items && ok; ++t) {
                 const int acc = t & 1;
                 const uint32_t acc_ph = (uint32_t)((t >> 1) & 1);
+                int tile, kb0, kb1; item_of(t, tile, kb0, kb1);
                 ok = mbar_wait(&acc_empty[acc], acc_ph ^ 1, p.err, 22);      // both CTAs drained this accumulator
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * 256);
-                for (int kb = 0; kb < num_kb && ok; ++kb, ++it) {
-                    const int s = (int)(it % CSTAGES);
-                    const uint32_t ph = (uint32_t)((it / CSTAGES) & 1);
-                    ok = mbar_wait(&full_bar[s], ph, p.err, 23);
+                for (int kb = kb0; kb < kb1 && ok; ++kb) {
+                    const int s = mma_stage;
+                    ok = mbar_wait(&full_bar[s], mma_phase, p.err, 23);
                     if (!ok) break;
+                    if (++mma_stage == CSTAGES) { mma_stage = 0; mma_phase ^= 1; }
                     const uint32_t a_addr = smem_u32(smem + (size_t)s * STAGE_BYTES);
                     const uint64_t adesc = smem_desc_sw128(a_addr);
                     const uint64_t bdesc = smem_desc_sw128(a_addr + A_BYTES);
 #pragma unroll
                     for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
-                        umma_bf16_pair(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        umma_bf16_pair(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
                     umma_commit_pair(map_to_cta(smem_u32(&empty_bar[s]), 0));    // the stage is free in both CTAs
                     umma_commit_pair(map_to_cta(smem_u32(&empty_bar[s]), 1));
                 }
@@ -683,26 +827,76 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         }
     } else {
         const int quad = warp & 3;
-        const int row_in_tile = quad * 32 + lane;
-        for (int t = 0; t < my_tiles && ok; ++t) {
+        EpilogueTma epi{&map_res, &map_out, epi_smem + (size_t)quad * EPI_BUFS * EPI_BOX_BYTES, epi_bar[quad], 0u};
+        constexpr long long HALF_TILE = 256LL * PART_LD;      // floats of one CTA's half of a partial tile
+        for (int t = 0; t < n_items && ok; ++t) {
             const int acc = t & 1;
             const uint32_t acc_ph = (uint32_t)((t >> 1) & 1);
-            const int tile = first + t * stride;
+            int tile, kb0, kb1; item_of(t, tile, kb0, kb1);
             const int tm = tile % tiles_m, tn = tile / tiles_m;
+            const bool whole = kb0 == 0 && kb1 == num_kb;
             if (p.bias) {                                  // this tile's bias -> shared memory (epilogue threads only)
                 const int et = threadIdx.x - 64;
                 for (int j = et; j < 256; j += 128) bias_tile[acc][j] = (tn * 256 + j < p.rows_q) ? p.bias[tn * 256 + j] : 0.f;
                 asm volatile("bar.sync 1, 128;" ::: "memory");
             }
-            ok = mbar_wait(&acc_full[acc], acc_ph, p.err, 24);
+            const int row0 = tm * 256 + (int)rank * 128 + quad * 32;
+            if (whole && tma_epilogue && lane == 0) epilogue_tma_begin(epi, row0, tn * 256);
+            ok = __all_sync(0xffffffffu, mbar_wait(&acc_full[acc], acc_ph, p.err, 24));
             if (!ok) break;
             tc_fence_after();
-            drain_accumulator<256>(p, tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * 256),
-                                   tm * 256 + (int)rank * 128 + row_in_tile, tn * 256, bias_tile[acc]);
+            AccSource src{tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * 256), nullptr, 0, 0, 0};
+            if (whole) {
+                if (tma_epilogue) ok = drain_accumulator_tma<256>(p, epi, src, row0, tn * 256, bias_tile[acc], lane);
+                else drain_accumulator<256>(p, src, row0 + lane, tn * 256, bias_tile[acc]);
+                tc_fence_before();
+                __syncwarp();
+                if (!ok) break;
+                if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[acc]), 0));
+                continue;
+            }
+            // A segment: this warp's 32 rows of the partial sums -> scratch memory, as item t of pair g.
+            float* mine = p.partials + ((long long)(g * 2 + t) * 2 + rank) * HALF_TILE + quad * 32 + lane;
+#pragma unroll 1
+            for (int c = 0; c < 256; c += 32) {
+                uint32_t r[32];
+                tmem_ld32(src.tmem_addr + (uint32_t)c, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) __stcg(mine + (size_t)(c + j) * PART_LD, __uint_as_float(r[j]));
+            }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[acc]), 0));
+            // Who else works on this tile: the pairs whose runs hold its first and its last K block.
+            const int rel = tile - dp_tiles;
+            const long long x0 = (long long)rel * num_kb, x1 = x0 + num_kb - 1;
+            const int g_first = (int)(((x0 + 1) * G - 1) / U), g_last = (int)(((x1 + 1) * G - 1) / U);
+            __threadfence();
+            __syncwarp();
+            int last = 0;
+            if (lane == 0) {
+                int* counter = p.counters + (rel * 2 + (int)rank) * 4 + quad;
+                last = atomicAdd(counter, 1) == g_last - g_first;
+                if (last) *counter = 0;                      // ready for the next call
+            }
+            last = __shfl_sync(0xffffffffu, last, 0);
+            if (!last) continue;
+            // The warp that arrives last adds the partial tiles, first contributor first, and finishes the tile.
+            __threadfence();
+            const int first_seg = rel - (int)((U * g_first / G) / num_kb);
+            src.part0 = p.partials + ((long long)(g_first * 2) * 2 + rank) * HALF_TILE + quad * 32 + lane;
+            src.n_parts = g_last - g_first + 1;
+            src.first_off = (long long)first_seg * 2 * HALF_TILE;
+            src.stride = 4 * HALF_TILE;
+            if (tma_epilogue) {
+                if (lane == 0) epilogue_tma_begin(epi, row0, tn * 256);
+                ok = drain_accumulator_tma<256>(p, epi, src, row0, tn * 256, bias_tile[acc], lane);
+            } else {
+                drain_accumulator<256>(p, src, row0 + lane, tn * 256, bias_tile[acc]);
+            }
         }
+        if (tma_epilogue && lane == 0) tma_store_wait_read<0>();      // shared memory is read out before the CTA ends
     }
     if (!ok) {
         const unsigned long long t0 = global_ns();
@@ -732,12 +926,46 @@ int launch(const CUtensorMap& mp, const CUtensorMap& mq, const Params& p, dim3 g
 
 }  // namespace
 
+// Many tokens: which kernel, and how many of the paired kernel's tiles are shared out by K blocks.
+struct ManyTokensPlan { int kind; int pairs; int sk_tiles; };      // kind 0: 128 x 128 tiles, 1: CTA pairs, 2: persistent
+static ManyTokensPlan plan_many_tokens(int M, int N, int K, int sms) {
+    ManyTokensPlan r{2, 0, 0};
+    const int tiles_m = (M + TILE_P - 1) / TILE_P, tiles_n = (N + 255) / 256;
+    // Few 128 x 256 tiles would leave SMs idle: 128 x 128 tiles, one per CTA, fill the GPU better then.
+    if (tiles_m * tiles_n * 4 < sms * 3) { r.kind = 0; return r; }
+    // Enough 256 x 256 tiles to keep the CTA pairs busy: the paired kernel; otherwise the
+    // single-CTA persistent kernel with 128 x 256 tiles.
+    const int n_tiles = ((M + 255) / 256) * ((N + 255) / 256);
+    if (M >= 256 && n_tiles * 8 >= sms * 3) {
+        r.kind = 1;
+        const int G = sms / 2, kb = (K + BLOCK_K - 1) / BLOCK_K;
+        r.pairs = n_tiles < G ? n_tiles : G;
+        // The tiles of a last, partly filled wave are shared out by K blocks over all pairs instead,
+        // when that pays: it saves (G - rest) / G of a tile's time (kb K blocks of about 0.45 us) and
+        // costs about G + rest partial tiles written and read again (0.1 us each at the rate the
+        // second-level cache gives beside the main loop's loads), with a margin of 1.3 for what was
+        // measured at 2,048 tokens.  Every pair must get at least four K blocks.
+        const int rest = n_tiles % G;
+        if (rest > 0 && (long long)rest * kb >= 4LL * G &&
+            (long long)(G - rest) * kb * 7 > 2LL * G * (G + rest)) { r.sk_tiles = rest; r.pairs = G; }
+    }
+    return r;
+}
+
 // Bytes of 32-bit scratch and number of tile counters that tnx_gemm_tc needs for these sizes (0
 // when K is not split).  The caller owns both; the counters must be zero before the first call and
 // are left zero by every call.
 TNX_EXPORT int tnx_gemm_tc_plan(int M, int N, int K, int n_sms, int* splits, long long* scratch_bytes, int* n_counters) {
     *splits = 1; *scratch_bytes = 0; *n_counters = 0;
-    if (M > 64) return 0;
+    if (M > 64) {
+        // paired kernel: two partial 256 x 256 tiles per pair, and a counter per shared tile, CTA and epilogue warp
+        const ManyTokensPlan mt = plan_many_tokens(M, N, K, n_sms);
+        if (mt.sk_tiles > 0) {
+            *scratch_bytes = (long long)mt.pairs * 2 * 256 * 256 * 4;
+            *n_counters = mt.sk_tiles * 8;
+        }
+        return 0;
+    }
     const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
     const int tiles = (N + TILE_P - 1) / TILE_P;
     const int kb = (K + BLOCK_K - 1) / BLOCK_K;
@@ -780,28 +1008,34 @@ TNX_EXPORT int tnx_gemm_tc(const void* A, const void* W, const float* bias, cons
             sms = cached_sms[dev];
         }
         const int tiles_m = (M + TILE_P - 1) / TILE_P, tiles_n = (N + PBN - 1) / PBN;
-        // Few 128 x 256 tiles would leave SMs idle: 128 x 128 tiles, one per CTA, fill the GPU better then.
-        if (tiles_m * tiles_n * 4 < sms * 3) {
+        ManyTokensPlan mt = plan_many_tokens(M, N, K, sms);
+        if (mt.kind == 0) {
             if (!make_map(&mq, W, N, K, ldw, 128)) return TNX_ERR_UNSUPPORTED;
             dim3 grid((M + TILE_P - 1) / TILE_P, (N + 127) / 128, 1);
             return launch<128, 6, false>(mp, mq, p, grid, stream);
         }
-        // Enough 256 x 256 tiles to keep the CTA pairs busy: the paired kernel; otherwise the
-        // single-CTA persistent kernel with 128 x 256 tiles.
-        const int ptiles_m = (M + 255) / 256, ptiles_n = (N + 255) / 256;
-        if (M >= 256 && ptiles_m * ptiles_n * 8 >= sms * 3) {
+        if (mt.kind == 1) {
+            const int ptiles_m = (M + 255) / 256, ptiles_n = (N + 255) / 256;
+            if (mt.sk_tiles > 0 && (!scratch || !counters)) {          // no scratch given: whole tiles only
+                mt.sk_tiles = 0;
+                if (mt.pairs > ptiles_m * ptiles_n) mt.pairs = ptiles_m * ptiles_n;
+            }
+            p.sk_tiles = mt.sk_tiles;
             if (!make_map(&mq, W, N, K, ldw, 128)) return TNX_ERR_UNSUPPORTED;
-            constexpr size_t psmem = (size_t)CSTAGES * (TILE_P * BLOCK_K * 2 + 128 * BLOCK_K * 2) + 1024;
+            constexpr size_t psmem = (size_t)CSTAGES * (TILE_P * BLOCK_K * 2 + 128 * BLOCK_K * 2) + PAIR_EPI_BYTES + 1024;
+            // A 32-bit residual goes through TMA boxes when the row pitch and the addresses allow it.
+            CUtensorMap mres = mp, mout = mp;
+            int tma_epilogue = 0;
+            if (residual && !c_bf16 && ldc % 4 == 0 && !(((uintptr_t)residual | (uintptr_t)C) & 15))
+                tma_epilogue = make_map_f32(&mres, residual, M, N, ldc, 32) && make_map_f32(&mout, C, M, N, ldc, 32);
             static bool pconfigured = false;
             if (!pconfigured) {
                 cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)psmem);
                 if (e != cudaSuccess) return (int)e;
                 pconfigured = true;
             }
-            int pairs = sms / 2;
-            if (pairs > ptiles_m * ptiles_n) pairs = ptiles_m * ptiles_n;
-            return tnx_launch_ex(1, gemm_tc_pair_kernel, dim3(2 * pairs), dim3(NUM_THREADS), psmem, stream, mp, mq, p,
-                                 ptiles_m, ptiles_n);
+            return tnx_launch_ex(1, gemm_tc_pair_kernel, dim3(2 * mt.pairs), dim3(NUM_THREADS), psmem, stream, mp, mq, mres, mout, p,
+                                 ptiles_m, ptiles_n, tma_epilogue);
         }
         if (!make_map(&mq, W, N, K, ldw, PBN)) return TNX_ERR_UNSUPPORTED;
         constexpr size_t smem = (size_t)PSTAGES * (TILE_P * BLOCK_K * 2 + PBN * BLOCK_K * 2) + 1024;

@@ -51,6 +51,17 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(smem_u32(dst)), "l"((unsigned long long)map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
 }
+// Shared memory -> global memory through TMA; completion is tracked by the issuing thread's bulk groups.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"((unsigned long long)map), "r"(smem_u32(src)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Returns once all but the newest `N` groups of this thread have finished READING shared memory.
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+// Makes this thread's writes to shared memory visible to the TMA engine (the async proxy).
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols) : "memory");
 }
@@ -124,7 +135,7 @@ EncodeTiledFn encode_fn() {
 }
 
 struct MapKey {
-    const void* ptr; int rows, cols, ld, box_rows;
+    const void* ptr; int rows, cols, ld, box_rows;      // box_rows < 0: a 32-bit map (make_map_f32)
     bool operator==(const MapKey& o) const {
         return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
     }
@@ -138,27 +149,35 @@ struct MapHash {
     }
 };
 
-// A [rows, cols] bf16 matrix with row pitch ld elements; boxes of box_rows x 64, 128-byte swizzle.
-bool make_map(CUtensorMap* out, const void* ptr, int rows, int cols, int ld, int box_rows) {
+// A [rows, cols] matrix with row pitch ld elements, 128-byte swizzle: bf16 in boxes of box_rows x 64,
+// or (f32) 32-bit floats in boxes of box_rows x 32.  Either way a box row is 128 bytes.
+bool make_map_any(CUtensorMap* out, const void* ptr, int rows, int cols, int ld, int box_rows, bool f32) {
     static std::unordered_map<MapKey, CUtensorMap, MapHash> cache;
     static std::mutex mu;
-    MapKey key{ptr, rows, cols, ld, box_rows};
+    MapKey key{ptr, rows, cols, ld, f32 ? -box_rows : box_rows};
     std::lock_guard<std::mutex> g(mu);
     auto it = cache.find(key);
     if (it != cache.end()) { *out = it->second; return true; }
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
     cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * (f32 ? 4 : 2)};
+    cuuint32_t box[2] = {f32 ? 32u : 64u, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+    CUresult r = fn(out, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                    const_cast<void*>(ptr), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return false;
     if (cache.size() > 4096) cache.clear();
     cache.emplace(key, *out);
     return true;
+}
+inline bool make_map(CUtensorMap* out, const void* ptr, int rows, int cols, int ld, int box_rows) {
+    return make_map_any(out, ptr, rows, cols, ld, box_rows, false);
+}
+inline bool make_map_f32(CUtensorMap* out, const void* ptr, int rows, int cols, int ld, int box_rows) {
+    return make_map_any(out, ptr, rows, cols, ld, box_rows, true);
 }
 
 
