@@ -50,6 +50,7 @@ struct Params {
     int* counters;               // one per output tile, zero between calls
     int* err;
     int sk_tiles;                // paired kernel: the last sk_tiles output tiles are shared out by K blocks
+    int sk_pairs;                // ... over the first sk_pairs pairs
 };
 
 template <int BN, bool SWAP>
@@ -345,30 +346,49 @@ struct AccSource {
 };
 constexpr int PART_LD = 128;     // partial tiles are [column][128 rows]: the lanes of a warp write 128 bytes
 
+template <bool FROM_SCRATCH>
 __device__ __forceinline__ void acc_load_begin(const AccSource& a, int c, uint32_t (&r)[32]) {
-    if (a.part0 == nullptr) { tmem_ld32(a.tmem_addr + (uint32_t)c, r); return; }
-    float v[32];
+    if (!FROM_SCRATCH) { tmem_ld32(a.tmem_addr + (uint32_t)c, r); return; }
+    // Sixteen columns at a time; the loads of contributor s + 1 are issued before the values of
+    // contributor s are added, so that two round trips to the second-level cache are in flight.
+    auto part = [&](int s) { return a.part0 + (s == 0 ? a.first_off : a.stride * s) + (size_t)c * PART_LD; };
 #pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] = 0.f;
-    for (int s = 0; s < a.n_parts; ++s) {
-        const float* src = a.part0 + (s == 0 ? a.first_off : a.stride * s) + (size_t)c * PART_LD;
-        float f[32];
+    for (int h = 0; h < 32; h += 16) {
+        float f[16], g[16];
+        {
+            const float* src = part(0) + (size_t)h * PART_LD;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) f[j] = __ldcg(src + (size_t)j * PART_LD);
+            for (int j = 0; j < 16; ++j) { f[j] = __ldcg(src + (size_t)j * PART_LD); r[h + j] = 0u; }
+        }
+        for (int s = 0; s < a.n_parts; s += 2) {
+            if (s + 1 < a.n_parts) {
+                const float* src = part(s + 1) + (size_t)h * PART_LD;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] += f[j];
+                for (int j = 0; j < 16; ++j) g[j] = __ldcg(src + (size_t)j * PART_LD);
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) r[h + j] = __float_as_uint(__uint_as_float(r[h + j]) + f[j]);
+            if (s + 1 < a.n_parts) {
+                if (s + 2 < a.n_parts) {
+                    const float* src = part(s + 2) + (size_t)h * PART_LD;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) f[j] = __ldcg(src + (size_t)j * PART_LD);
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) r[h + j] = __float_as_uint(__uint_as_float(r[h + j]) + g[j]);
+            }
+        }
     }
-#pragma unroll
-    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(v[j]);
 }
+template <bool FROM_SCRATCH>
 __device__ __forceinline__ void acc_load_end(const AccSource& a) {
-    if (a.part0 == nullptr) tmem_ld_wait();
+    if (!FROM_SCRATCH) tmem_ld_wait();
 }
 
 // Epilogue of one warp of the many-token kernels: its 32 accumulator rows x WIDTH columns -> C.
 // With a residual (32-bit, possibly C itself) the loads of the next 32 columns are issued before
 // the current ones are stored, so that a tile costs one memory round trip, not one per chunk.
-template <int WIDTH>
+template <int WIDTH, bool FROM_SCRATCH = false>
 __device__ __forceinline__ void drain_accumulator(const Params& p, const AccSource& acc, int row, int col_base,
                                                   const float* bias_tile) {
     // The choice of path must be the same for all lanes of the warp: tcgen05.ld is a warp-wide
@@ -379,8 +399,8 @@ __device__ __forceinline__ void drain_accumulator(const Params& p, const AccSour
 #pragma unroll 1
         for (int c = 0; c < WIDTH; c += 32) {
             uint32_t r[32];
-            acc_load_begin(acc, c, r);
-            acc_load_end(acc);
+            acc_load_begin<FROM_SCRATCH>(acc, c, r);
+            acc_load_end<FROM_SCRATCH>(acc);
             float v[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
@@ -397,12 +417,12 @@ __device__ __forceinline__ void drain_accumulator(const Params& p, const AccSour
 #pragma unroll 1
     for (int c = 0; c < WIDTH; c += 32) {
         uint32_t r[32];
-        acc_load_begin(acc, c, r);
+        acc_load_begin<FROM_SCRATCH>(acc, c, r);
         if (c + 32 < WIDTH && valid) {
 #pragma unroll
             for (int q = 0; q < 8; ++q) nxt[q] = __ldcg((const float4*)(res_row + c + 32) + q);
         }
-        acc_load_end(acc);
+        acc_load_end<FROM_SCRATCH>(acc);
         const float* b = p.bias ? bias_tile + c : nullptr;
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
@@ -593,16 +613,16 @@ __device__ __forceinline__ void epilogue_tma_begin(const EpilogueTma& e, int row
     epilogue_tma_fetch(e, e.n + 1, row0, col_base + 32);
 }
 
-template <int WIDTH>
+template <int WIDTH, bool FROM_SCRATCH = false>
 __device__ __forceinline__ bool drain_accumulator_tma(const Params& p, EpilogueTma& e, const AccSource& acc, int row0,
                                                       int col_base, const float* bias_tile, int lane) {
 #pragma unroll 1
     for (int c = 0; c < WIDTH; c += 32) {
         const uint32_t b = e.n % EPI_BUFS;
         uint32_t r[32];
-        acc_load_begin(acc, c, r);
+        acc_load_begin<FROM_SCRATCH>(acc, c, r);
         const bool got = __all_sync(0xffffffffu, mbar_wait(&e.bars[b], (e.n / EPI_BUFS) & 1, p.err, 31));
-        acc_load_end(acc);
+        acc_load_end<FROM_SCRATCH>(acc);
         if (!got) return false;                               // the same answer in every lane of the warp
         // lane = row of the box; its 128 bytes are eight 16-byte pieces, piece j stored at j ^ (row % 8)
         uint8_t* rowp = e.bufs + (size_t)b * EPI_BOX_BYTES + lane * 128;
@@ -704,13 +724,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     const int n_tiles = tiles_m * tiles_n;                    // 256 x 256 tiles
     // Work of pair g of G.  Tiles [0, dp_tiles) are computed whole, tile g + t * G by pair g.  The
     // last sk_tiles tiles (fewer than G: they would leave pairs idle in a last wave) are laid end to
-    // end as sk_tiles * num_kb K blocks and cut into G equal runs; a run covers parts of at most
-    // two tiles (its "segments"), which come first in the pair's list of items.
-    const int G = gridDim.x >> 1, g = blockIdx.x >> 1;
+    // end as sk_tiles * num_kb K blocks and cut into GS equal runs for the first GS pairs (GS is
+    // chosen so that a tile has few contributors); a run covers parts of at most two tiles (its
+    // "segments"), which come first in the pair's list of items.
+    const int G = gridDim.x >> 1, g = blockIdx.x >> 1, GS = p.sk_pairs;
     const int dp_tiles = n_tiles - p.sk_tiles;
     const int my_dp = g < dp_tiles ? (dp_tiles - g + G - 1) / G : 0;
     const long long U = (long long)p.sk_tiles * num_kb;
-    const long long u0 = U * g / G, u1 = U * (g + 1) / G;
+    const long long u0 = g < GS ? U * g / GS : 0, u1 = g < GS ? U * (g + 1) / GS : 0;
     const int seg_tile0 = (int)(u0 / num_kb);                 // first shared tile this pair touches
     const int n_seg = u1 > u0 ? (int)((u1 - 1) / num_kb) - seg_tile0 + 1 : 0;
     const int n_items = n_seg + my_dp;
@@ -871,7 +892,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             // Who else works on this tile: the pairs whose runs hold its first and its last K block.
             const int rel = tile - dp_tiles;
             const long long x0 = (long long)rel * num_kb, x1 = x0 + num_kb - 1;
-            const int g_first = (int)(((x0 + 1) * G - 1) / U), g_last = (int)(((x1 + 1) * G - 1) / U);
+            const int g_first = (int)(((x0 + 1) * GS - 1) / U), g_last = (int)(((x1 + 1) * GS - 1) / U);
             __threadfence();
             __syncwarp();
             int last = 0;
@@ -884,16 +905,16 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             if (!last) continue;
             // The warp that arrives last adds the partial tiles, first contributor first, and finishes the tile.
             __threadfence();
-            const int first_seg = rel - (int)((U * g_first / G) / num_kb);
+            const int first_seg = rel - (int)((U * g_first / GS) / num_kb);
             src.part0 = p.partials + ((long long)(g_first * 2) * 2 + rank) * HALF_TILE + quad * 32 + lane;
             src.n_parts = g_last - g_first + 1;
             src.first_off = (long long)first_seg * 2 * HALF_TILE;
             src.stride = 4 * HALF_TILE;
             if (tma_epilogue) {
                 if (lane == 0) epilogue_tma_begin(epi, row0, tn * 256);
-                ok = drain_accumulator_tma<256>(p, epi, src, row0, tn * 256, bias_tile[acc], lane);
+                ok = drain_accumulator_tma<256, true>(p, epi, src, row0, tn * 256, bias_tile[acc], lane);
             } else {
-                drain_accumulator<256>(p, src, row0 + lane, tn * 256, bias_tile[acc]);
+                drain_accumulator<256, true>(p, src, row0 + lane, tn * 256, bias_tile[acc]);
             }
         }
         if (tma_epilogue && lane == 0) tma_store_wait_read<0>();      // shared memory is read out before the CTA ends
@@ -927,28 +948,42 @@ int launch(const CUtensorMap& mp, const CUtensorMap& mq, const Params& p, dim3 g
 }  // namespace
 
 // Many tokens: which kernel, and how many of the paired kernel's tiles are shared out by K blocks.
-struct ManyTokensPlan { int kind; int pairs; int sk_tiles; };      // kind 0: 128 x 128 tiles, 1: CTA pairs, 2: persistent
+struct ManyTokensPlan { int kind; int pairs; int sk_tiles; int sk_pairs; };   // kind 0: 128 x 128 tiles, 1: CTA pairs, 2: persistent
 static ManyTokensPlan plan_many_tokens(int M, int N, int K, int sms) {
-    ManyTokensPlan r{2, 0, 0};
-    const int tiles_m = (M + TILE_P - 1) / TILE_P, tiles_n = (N + 255) / 256;
-    // Few 128 x 256 tiles would leave SMs idle: 128 x 128 tiles, one per CTA, fill the GPU better then.
-    if (tiles_m * tiles_n * 4 < sms * 3) { r.kind = 0; return r; }
-    // Enough 256 x 256 tiles to keep the CTA pairs busy: the paired kernel; otherwise the
-    // single-CTA persistent kernel with 128 x 256 tiles.
-    const int n_tiles = ((M + 255) / 256) * ((N + 255) / 256);
-    if (M >= 256 && n_tiles * 8 >= sms * 3) {
-        r.kind = 1;
-        const int G = sms / 2, kb = (K + BLOCK_K - 1) / BLOCK_K;
-        r.pairs = n_tiles < G ? n_tiles : G;
-        // The tiles of a last, partly filled wave are shared out by K blocks over all pairs instead,
-        // when that pays: it saves (G - rest) / G of a tile's time (kb K blocks of about 0.45 us) and
-        // costs about G + rest partial tiles written and read again (0.1 us each at the rate the
-        // second-level cache gives beside the main loop's loads), with a margin of 1.3 for what was
-        // measured at 2,048 tokens.  Every pair must get at least four K blocks.
-        const int rest = n_tiles % G;
-        if (rest > 0 && (long long)rest * kb >= 4LL * G &&
-            (long long)(G - rest) * kb * 7 > 2LL * G * (G + rest)) { r.sk_tiles = rest; r.pairs = G; }
+    ManyTokensPlan r{2, 0, 0, 0};
+    const int kb = (K + BLOCK_K - 1) / BLOCK_K;
+    const int tiles_m = (M + TILE_P - 1) / TILE_P;
+    // Estimated times in microseconds, from measurements at 256..2,048 tokens: a K block of a
+    // 256 x 256 pair tile takes 0.45 us, of a 128 x 128 single tile 0.38 us; start and drain 8 / 6 us.
+    const float t_single = (float)((tiles_m * ((N + 127) / 128) + sms - 1) / sms) * kb * 0.38f + 6.f;
+    if (M < 256) {
+        // Few 128 x 256 tiles would leave SMs idle: 128 x 128 tiles, one per CTA, fill the GPU better
+        // then; otherwise the single-CTA persistent kernel with 128 x 256 tiles.
+        if (tiles_m * ((N + 255) / 256) * 4 < sms * 3) r.kind = 0;
+        return r;
     }
+    const int G = sms / 2;
+    const int n_tiles = ((M + 255) / 256) * ((N + 255) / 256);          // 256 x 256 tiles of the paired kernel
+    const int full = n_tiles / G, rest = n_tiles % G;
+    const float t_tile = kb * 0.45f;
+    float t_pair = (float)(full + (rest > 0)) * t_tile + 8.f;
+    // The tiles of a partly filled last wave (all tiles, when there are fewer than pairs) can be
+    // shared out by K blocks over GS pairs, at most four to a tile: that wave then takes rest / GS
+    // of a tile's time, but GS + rest partial tiles are written and read again (0.1 us each at the
+    // rate the second-level cache gives beside the main loop's loads) and the warp that adds them
+    // up needs 2.8 us per contributor, which hides behind a following whole tile if there is one.
+    // A margin of 1.3 on these costs; every pair must get at least four K blocks.
+    int sk_pairs = rest * 4 < G ? rest * 4 : G;
+    float t_share = 1e30f;
+    if (rest > 0 && (long long)rest * kb >= 4LL * sk_pairs) {
+        const float reduce = ((float)sk_pairs / rest + 1.f) * 2.8f;
+        const float exposed = full > 0 ? (reduce > t_tile ? reduce - t_tile : 0.f) : reduce;
+        t_share = ((float)full + (float)rest / sk_pairs) * t_tile + 8.f + 1.3f * ((sk_pairs + rest) * 0.1f + exposed);
+    }
+    if (t_single <= t_pair && t_single <= t_share) { r.kind = 0; return r; }
+    r.kind = 1;
+    if (t_share < t_pair) { r.pairs = G; r.sk_tiles = rest; r.sk_pairs = sk_pairs; }
+    else r.pairs = n_tiles < G ? n_tiles : G;
     return r;
 }
 
@@ -1017,10 +1052,10 @@ TNX_EXPORT int tnx_gemm_tc(const void* A, const void* W, const float* bias, cons
         if (mt.kind == 1) {
             const int ptiles_m = (M + 255) / 256, ptiles_n = (N + 255) / 256;
             if (mt.sk_tiles > 0 && (!scratch || !counters)) {          // no scratch given: whole tiles only
-                mt.sk_tiles = 0;
+                mt.sk_tiles = 0; mt.sk_pairs = 0;
                 if (mt.pairs > ptiles_m * ptiles_n) mt.pairs = ptiles_m * ptiles_n;
             }
-            p.sk_tiles = mt.sk_tiles;
+            p.sk_tiles = mt.sk_tiles; p.sk_pairs = mt.sk_pairs;
             if (!make_map(&mq, W, N, K, ldw, 128)) return TNX_ERR_UNSUPPORTED;
             constexpr size_t psmem = (size_t)CSTAGES * (TILE_P * BLOCK_K * 2 + 128 * BLOCK_K * 2) + PAIR_EPI_BYTES + 1024;
             // A 32-bit residual goes through TMA boxes when the row pitch and the addresses allow it.
