@@ -239,9 +239,10 @@ def time_prefill(model, cfg, steps, warmup):
 def extra_workload(name, steps, warmup):
     """The two further workloads that BASELINE.md lists, each printed as one JSON line of its own:
     decode30b: OPT-30B sizes, batch 16, context ending at 2,048, greedy;
-    mixed13b:  OPT-13B sizes, 32 requests with prompts of 64..1,536 tokens, 512-token prompt portions
-               beside the decode tokens of the others, 256 new tokens each at temperature 0.7,
-               through LLMEngine.generate (tokens per second of wall clock, prefill included)."""
+    mixed13b:  OPT-13B sizes, 32 requests with prompts of 64..1,536 tokens, a budget of 512 tokens a
+               step (one prompt portion beside the decode tokens of the others), 256 new tokens each at
+               temperature 0.7, through LLMEngine.generate (tokens per second of wall clock, prefill
+               included; the same workload has run once before as warm-up)."""
     import torch
     if name == "decode30b":
         model, cfg = build(OPT_30B["num_hidden_layers"], base=OPT_30B)
@@ -258,11 +259,14 @@ def extra_workload(name, steps, warmup):
     g = torch.Generator().manual_seed(4)
     lens = torch.randint(64, 1537, (32,), generator=g).tolist()
     prompts = [torch.randint(3, cfg.vocab_size, (n,), generator=g).tolist() for n in lens]
-    eng = LLMEngine(model, EngineConfig(dtype="bfloat16", max_num_seqs=32, max_batch_tokens=512 + 32,
+    # a step's token budget is 512: the decode tokens of the running requests and one prompt portion
+    eng = LLMEngine(model, EngineConfig(dtype="bfloat16", max_num_seqs=32, max_batch_tokens=512,
                                         max_tokens=32 * 1792, max_model_len=CONTEXT))
     params = [SamplingParams(temperature=0.7, seed=i) for i in range(32)]
-    eng.generate(prompts[:4], 8, params[:4], stop_on_eos=False)           # warm-up: kernels, graphs
+    for _ in range(max(1, min(warmup, 1))):                               # warm-up: the whole workload once
+        eng.generate(prompts, 256, params, stop_on_eos=False)             # (kernels loaded, every graph captured)
     torch.cuda.synchronize()
+    steps0, pre0 = eng.stats["steps"], eng.stats["preemptions"]
     t0 = time.perf_counter()
     out = eng.generate(prompts, 256, params, stop_on_eos=False)
     torch.cuda.synchronize()
@@ -270,7 +274,8 @@ def extra_workload(name, steps, warmup):
     n_new = sum(len(o) for o in out)
     print(json.dumps({"workload": name, "value": round(n_new / dt, 1), "unit": "new tokens/s (wall clock, prefill included)",
                       "seconds": round(dt, 3), "requests": 32, "prompt_tokens": sum(lens), "new_tokens": n_new,
-                      "steps": eng.stats["steps"], "preemptions": eng.stats["preemptions"], "layers": cfg.num_hidden_layers}))
+                      "steps": eng.stats["steps"] - steps0, "preemptions": eng.stats["preemptions"] - pre0,
+                      "token_budget": 512, "layers": cfg.num_hidden_layers}))
     return 0
 
 
