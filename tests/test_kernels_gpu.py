@@ -65,16 +65,17 @@ def test_gemm_tc(M, N, K):
     w = (torch.randn(N, K, generator=g) / math.sqrt(K)).bfloat16().to(DEV)
     bias = torch.randn(N, generator=g).to(DEV)
     want = a.float() @ w.float().t()
+    tc = dict(few_tokens_kernel=False)                  # the tensor-core kernel also for one to four tokens
     out = torch.empty(M, N, dtype=torch.float32, device=DEV)
-    o.gemm_tc(a, w, out)
+    o.gemm_tc(a, w, out, **tc)
     o.raise_on_device_error()
     assert rel_err(out, want) <= 2e-5, "plain product"
     outb = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
-    o.gemm_tc(a, w, outb, bias=bias, relu=True)
+    o.gemm_tc(a, w, outb, bias=bias, relu=True, **tc)
     assert rel_err(outb, torch.relu(want + bias)) <= 5e-3, "bias + relu -> bf16"
     res = torch.randn(M, N, generator=g).to(DEV)
     want3 = want + bias + res
-    o.gemm_tc(a, w, res, bias=bias, residual=res)
+    o.gemm_tc(a, w, res, bias=bias, residual=res, **tc)
     o.raise_on_device_error()
     assert rel_err(res, want3) <= 2e-5, "bias + residual in place"
     res2 = torch.randn(M, N, generator=g).to(DEV)
@@ -83,6 +84,41 @@ def test_gemm_tc(M, N, K):
     o.gemm_tc(a, w, out4, residual=res2)
     o.raise_on_device_error()
     assert rel_err(out4, want + keep) <= 2e-5 and torch.equal(res2, keep), "residual beside the output"
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (1, 4099, 4096), (2, 1000, 328), (2, 515, 16384), (3, 96, 320),
+                                   (4, 12288, 4096), (4, 50, 8), (1, 7, 28672), (3, 300, 10920)])
+def test_gemv_few_tokens(M, N, K):
+    """The kernel for one to four tokens: the weights streamed through the multiply-add units."""
+    o = ops()
+    g = torch.Generator(device="cpu").manual_seed(M * 7 + N + K)
+    a = torch.randn(M, K, generator=g).bfloat16().to(DEV)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).bfloat16().to(DEV)
+    bias = torch.randn(N, generator=g).to(DEV)
+    want = a.float() @ w.float().t()
+    launches = o.launch_count()
+    out = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    o.gemv(a, w, out)
+    assert rel_err(out, want) <= 2e-5, "plain product"
+    outb = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    o.gemv(a, w, outb, bias=bias, relu=True)
+    assert rel_err(outb, torch.relu(want + bias)) <= 5e-3, "bias + relu -> bf16"
+    res = torch.randn(M, N, generator=g).to(DEV)
+    want3 = want + bias + res
+    o.gemv(a, w, res, bias=bias, residual=res)
+    assert rel_err(res, want3) <= 2e-5, "bias + residual in place"
+    # a token's row is the same alone and beside others, bit for bit
+    one = torch.empty(1, N, dtype=torch.float32, device=DEV)
+    o.gemv(a[M - 1:M], w, one)
+    assert torch.equal(one[0], out[M - 1])
+    # rows of a wider buffer (the fused q/k/v output, a slice of the activations)
+    wide = torch.zeros(M, N + 24, dtype=torch.float32, device=DEV)
+    o.gemv(a, w, wide[:, 8:8 + N])
+    assert torch.equal(wide[:, 8:8 + N], out) and float(wide[:, :8].abs().max()) == 0.0
+    if M == 1:                                           # gemm_tc hands a single token to this kernel
+        again = torch.empty_like(out)
+        o.gemm_tc(a, w, again)
+        assert torch.equal(again, out)
 
 
 @pytest.mark.parametrize("M,N,K,splits", [(8, 256, 4096, 4), (64, 130, 1024, 16), (1, 128, 512, 2), (20, 300, 1160, 3)])

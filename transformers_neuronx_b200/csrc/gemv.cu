@@ -1,0 +1,182 @@
+// Matrix product for one to four tokens (the decode step of one to four requests):
+//
+//   C[m, n] = epilogue( sum_k A[m, k] * W[n, k] )        A: [M, K] bf16, W: [N, K] bf16, row-major
+//   epilogue: + bias[n] (32-bit); ReLU; + residual[m, n] (32-bit); stored as bfloat16 or float.
+//
+// With so few tokens the product is a stream of the weight matrix through the multiply-add units:
+// there is nothing for the tensor cores to win, and plain 16-byte loads keep more bytes in flight
+// per SM than the TMA path of the tensor-core kernel does.  A block of 128 or 256 threads holds the
+// tokens' activations in shared memory and walks over groups of R weight rows; thread t takes the
+// 16-byte pieces t, t + threads, ... of each row, with the loads of the next step (or of the next group
+// of rows) issued before the current pieces are used.  Blocks share the rows out evenly.  Sums are 32-bit; the order of the additions
+// depends only on K, never on M or on the other tokens, so a token's result is the same alone and
+// beside others.  The weights are read before the kernel ahead has finished (they are never
+// written by a kernel); the activations after.
+#include "common.cuh"
+
+namespace {
+
+
+__device__ __forceinline__ uint4 load_stream(const uint4* p) { return __ldcs(p); }
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+    // a bf16 is the upper half of the float with the same value
+    f[0] = __uint_as_float(v.x << 16); f[1] = __uint_as_float(v.x & 0xffff0000u);
+    f[2] = __uint_as_float(v.y << 16); f[3] = __uint_as_float(v.y & 0xffff0000u);
+    f[4] = __uint_as_float(v.z << 16); f[5] = __uint_as_float(v.z & 0xffff0000u);
+    f[6] = __uint_as_float(v.w << 16); f[7] = __uint_as_float(v.w & 0xffff0000u);
+}
+
+template <int M, int R, int THREADS>
+__global__ void __launch_bounds__(THREADS)
+gemv_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict__ W, int ldw,
+            const float* __restrict__ bias, const float* residual, void* C, int ldc,
+            int relu, int c_is_bf16, int N, int K) {
+    extern __shared__ uint4 xs[];                         // [M][K / 8] pieces of the activations
+    __shared__ float red[THREADS / 32][R * M];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int K8 = K >> 3;
+    // This block's rows: an equal share of the N rows (to within one row), taken R at a time; the
+    // last group of a block may be shorter.
+    const int row_begin = (int)((long long)N * blockIdx.x / gridDim.x);
+    const int row_end = (int)((long long)N * (blockIdx.x + 1) / gridDim.x);
+
+    auto fetch = [&](uint4 (&dst)[R], int row0, int p) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            if (row0 + r < row_end) dst[r] = load_stream((const uint4*)(W + (size_t)(row0 + r) * ldw) + p);
+            else dst[r] = make_uint4(0u, 0u, 0u, 0u);
+        }
+    };
+
+    pdl_launch_dependents();
+    uint4 cur[R];
+    if (row_begin < row_end && tid < K8) fetch(cur, row_begin, tid);
+    pdl_wait();                                           // from here on the activations may be read, and C written
+    for (int i = tid; i < M * K8; i += THREADS) {
+        const int m = i / K8, p = i - m * K8;
+        xs[i] = *((const uint4*)(A + (size_t)m * lda) + p);
+    }
+    __syncthreads();
+
+    for (int row0 = row_begin; row0 < row_end; row0 += R) {
+        float acc[R][M];
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int m = 0; m < M; ++m) acc[r][m] = 0.f;
+        for (int p = tid; p < K8; p += THREADS) {
+            uint4 nxt[R];
+            const int pn = p + THREADS;
+            if (pn < K8) fetch(nxt, row0, pn);
+            else if (row0 + R < row_end) fetch(nxt, row0 + R, tid);
+            float xf[M][8];
+#pragma unroll
+            for (int m = 0; m < M; ++m) unpack8(xs[m * K8 + p], xf[m]);
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                float wf[8];
+                unpack8(cur[r], wf);
+#pragma unroll
+                for (int m = 0; m < M; ++m)
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) acc[r][m] = fmaf(wf[e], xf[m][e], acc[r][m]);
+            }
+#pragma unroll
+            for (int r = 0; r < R; ++r) cur[r] = nxt[r];
+        }
+        // the block's sum: lanes, then warps, in a fixed order
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+                const float v = warp_sum(acc[r][m]);
+                if (lane == 0) red[warp][r * M + m] = v;
+            }
+        __syncthreads();
+        if (tid < R * M) {
+            const int r = tid / M, m = tid - r * M;
+            const int n = row0 + r;
+            if (n < row_end) {
+                float v = 0.f;
+#pragma unroll
+                for (int w = 0; w < THREADS / 32; ++w) v += red[w][tid];
+                if (bias) v += bias[n];
+                if (relu) v = fmaxf(v, 0.f);
+                const size_t o = (size_t)m * ldc + n;
+                if (residual) v += residual[o];
+                if (c_is_bf16) ((bf16*)C)[o] = __float2bfloat16_rn(v);
+                else ((float*)C)[o] = v;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+template <int M, int R, int THREADS>
+int launch(const bf16* A, int lda, const bf16* W, int ldw, const float* bias, const float* residual, void* C, int ldc,
+           int relu, int c_bf16, int N, int K, int sms, cudaStream_t stream) {
+    const size_t smem = (size_t)M * K * 2;
+    static size_t configured = 48 * 1024 - 1024;
+    if (smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemv_kernel<M, R, THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = smem;
+    }
+    static size_t asked_smem = ~(size_t)0;                 // blocks per SM for the last shared-memory size asked about
+    static int asked_per_sm = 0;
+    if (smem != asked_smem) {
+        int n = 0;
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, gemv_kernel<M, R, THREADS>, THREADS, smem);
+        if (e != cudaSuccess) return (int)e;
+        asked_per_sm = n; asked_smem = smem;
+    }
+    const int per_sm = asked_per_sm;
+    if (per_sm < 1) return TNX_ERR_UNSUPPORTED;
+    int blocks = sms * per_sm;
+    if (blocks > (N + R - 1) / R) blocks = (N + R - 1) / R;
+    return tnx_launch_ex(1, gemv_kernel<M, R, THREADS>, dim3(blocks), dim3(THREADS), smem, stream, A, lda, W, ldw, bias, residual, C, ldc,
+                         relu, c_bf16, N, K);
+}
+
+}  // namespace
+
+// Whether tnx_gemv takes these sizes: one to four tokens, K a multiple of 8, the activations of
+// all tokens within the shared memory of a block (and of several blocks per SM for 3 or 4 tokens).
+// It is the faster kernel for one token; with two it is level with the tensor-core kernel and with
+// three and four the multiply-adds, not the memory, set its pace (measured).
+TNX_EXPORT int tnx_gemv_supported(int M, int N, int K) {
+    if (M < 1 || M > 4 || N < 1 || K < 8 || K % 8) return 0;
+    const long long smem = (long long)M * K * 2;
+    return smem <= (M <= 2 ? 112 * 1024 : 64 * 1024);
+}
+
+TNX_EXPORT int tnx_gemv(const void* A, const void* W, const float* bias, const float* residual, void* C,
+                        int M, int N, int K, int lda, int ldw, int ldc, int relu, int c_bf16, cudaStream_t stream) {
+    if (!tnx_gemv_supported(M, N, K)) return TNX_ERR_UNSUPPORTED;
+    if (lda % 8 || ldw % 8 || lda < K || ldw < K || ldc < N) return TNX_ERR_UNSUPPORTED;
+    if (((uintptr_t)A | (uintptr_t)W) & 15) return TNX_ERR_UNSUPPORTED;
+    if (residual && c_bf16) return TNX_ERR_BAD_ARG;
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    static int cached_sms[64] = {0};
+    if (dev >= 0 && dev < 64) {
+        if (!cached_sms[dev]) cudaDeviceGetAttribute(&cached_sms[dev], cudaDevAttrMultiProcessorCount, dev);
+        sms = cached_sms[dev];
+    }
+    const bf16* a = (const bf16*)A;
+    const bf16* w = (const bf16*)W;
+    // Rows of up to 4,096 elements: blocks of 128 threads (four steps of a row instead of two between
+    // the block-wide sums); longer rows: 256 threads.  The choice depends on K alone, so that the
+    // order of the additions does not depend on the number of tokens.
+#define GEMV_LAUNCH(M_, R_)                                                                                              \
+    (K <= 4096 ? launch<M_, R_, 128>(a, lda, w, ldw, bias, residual, C, ldc, relu, c_bf16, N, K, sms, stream)           \
+               : launch<M_, R_, 256>(a, lda, w, ldw, bias, residual, C, ldc, relu, c_bf16, N, K, sms, stream))
+    switch (M) {
+        case 1: return GEMV_LAUNCH(1, 8);
+        case 2: return GEMV_LAUNCH(2, 8);
+        case 3: return GEMV_LAUNCH(3, 4);
+        default: return GEMV_LAUNCH(4, 4);
+    }
+#undef GEMV_LAUNCH
+}

@@ -37,6 +37,7 @@ SOURCES: Dict[str, str] = {
     "attention_simt": "attention_simt.cu",
     "sampling": "sampling.cu",
     "gemm_tc": "gemm_tc.cu",
+    "gemv": "gemv.cu",
     "attention_decode": "attention_decode.cu",
     "attention_prefill": "attention_prefill.cu",
     "attention_prefill_tc": "attention_prefill_tc.cu",

@@ -294,8 +294,37 @@ def gemm_tc_supported(a, w, out) -> bool:
     return out.data_ptr() % 16 == 0
 
 
-def gemm_tc(a, w, out, bias=None, residual=None, relu=False, splits=None):
-    """out = epilogue(a @ w^T), bfloat16 operands on tcgen05 tensor cores, 32-bit accumulation."""
+def gemv(a, w, out, bias=None, residual=None, relu=False):
+    """out = epilogue(a @ w^T) for one to four tokens, the weights streamed through the multiply-add
+    units (bfloat16 operands, 32-bit sums).  gemm_tc() picks it by itself for one token."""
+    lib = _build.load("gemv")
+    _need(a, "a", torch.bfloat16, None, contiguous=False)
+    _need(w, "w", torch.bfloat16, None, contiguous=False)
+    _need(out, "out", _FLOATS, None, contiguous=False)
+    M, K, lda = _rows_2d(a, "a")
+    N, Kw, ldw = _rows_2d(w, "w")
+    Mo, No, ldc = _rows_2d(out, "out")
+    if Kw != K or Mo != M or No != N:
+        raise KernelError(f"gemv shapes do not fit: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if not lib.tnx_gemv_supported(c_int(M), c_int(N), c_int(K)) or not gemm_tc_supported(a, w, out):
+        raise KernelError("gemv takes one to four tokens, K a multiple of 8 and 16-byte aligned rows")
+    if bias is not None:
+        _need(bias, "bias", torch.float32, 1)
+        if bias.shape[0] != N:
+            raise KernelError("bias length differs from the output width")
+    if residual is not None:
+        _need(residual, "residual", torch.float32, None, contiguous=False)
+        if tuple(residual.shape) != (M, N) or _rows_2d(residual, "residual")[2] != ldc or out.dtype != torch.float32:
+            raise KernelError("residual must be float32 with the shape and row stride of a float32 out")
+    _check(lib.tnx_gemv(_p(a), _p(w), _p(bias), _p(residual), _p(out), c_int(M), c_int(N), c_int(K),
+                        c_int(lda), c_int(ldw), c_int(ldc), c_int(1 if relu else 0), c_int(_is_bf16(out)),
+                        _stream()), "gemv")
+
+
+def gemm_tc(a, w, out, bias=None, residual=None, relu=False, splits=None, few_tokens_kernel=True):
+    """out = epilogue(a @ w^T), bfloat16 operands, 32-bit accumulation: on the tcgen05 tensor cores,
+    or (one token, unless few_tokens_kernel is False or splits is given) as a stream of the
+    weights through the multiply-add units."""
     lib = _build.load("gemm_tc")
     _need(a, "a", torch.bfloat16, None, contiguous=False)
     _need(w, "w", torch.bfloat16, None, contiguous=False)
@@ -316,6 +345,13 @@ def gemm_tc(a, w, out, bias=None, residual=None, relu=False, splits=None):
         _need(residual, "residual", torch.float32, None, contiguous=False)
         if tuple(residual.shape) != (M, N) or _rows_2d(residual, "residual")[2] != ldc or out.dtype != torch.float32:
             raise KernelError("residual must be float32 with the shape and row stride of a float32 out")
+    if few_tokens_kernel and splits is None and M == 1:    # with two tokens and more the tensor-core kernel is as fast (measured)
+        gv = _build.load("gemv")
+        if gv.tnx_gemv_supported(c_int(M), c_int(N), c_int(K)):
+            _check(gv.tnx_gemv(_p(a), _p(w), _p(bias), _p(residual), _p(out), c_int(M), c_int(N), c_int(K),
+                               c_int(lda), c_int(ldw), c_int(ldc), c_int(1 if relu else 0), c_int(_is_bf16(out)),
+                               _stream()), "gemv")
+            return
     st = _state(a.device)
     n_splits, nbytes, ncnt = c_int(1), ctypes.c_longlong(0), c_int(0)
     lib.tnx_gemm_tc_plan(c_int(M), c_int(N), c_int(K), c_int(st["sms"]), ctypes.byref(n_splits),

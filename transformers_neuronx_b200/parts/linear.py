@@ -30,7 +30,7 @@ class Linear(Part):
 
     @property
     def libraries(self):
-        return ("gemm_simt", "gemm_tc")
+        return ("gemm_simt", "gemm_tc", "gemv")
 
     def tensor_specs(self) -> List[TensorSpec]:
         s = self.spec
