@@ -51,7 +51,7 @@ def test_gemm_simt_rows_do_not_depend_on_the_batch():
     assert torch.equal(full[33:34], one)                 # bit for bit
 
 
-TC_SHAPES = [(1, 128, 64), (3, 96, 320), (16, 4096, 1024), (17, 1000, 96), (33, 200, 136), (64, 512, 4096),
+TC_SHAPES = [(1, 128, 64), (3, 96, 320), (8, 256, 2112), (40, 4096, 4096), (16, 4096, 1024), (17, 1000, 96), (33, 200, 136), (64, 512, 4096),
              (65, 384, 256), (128, 128, 64), (200, 1000, 328), (300, 520, 1032), (2048, 768, 512),
              (1024, 4096, 512), (1000, 4000, 328), (300, 9000, 136), (513, 7100, 72), (520, 7102, 72), (2100, 2300, 1096),
              (1792, 2048, 16384), (2000, 3300, 8200), (1100, 4090, 4096)]     # the last three share tiles out by K blocks
@@ -136,6 +136,37 @@ def test_gemm_tc_split_k(M, N, K, splits):
     o.raise_on_device_error()
     assert rel_err(out1, want) <= 2e-5
     assert torch.equal(out1, out2), "the order of the additions is fixed"
+
+
+@pytest.mark.parametrize("M,N,K,splits", [(8, 256, 4096, 4), (64, 130, 1024, 8), (2, 128, 512, 2), (20, 300, 1160, 3),
+                                          (16, 4096, 4096, 8), (33, 520, 2048, 5), (64, 1000, 4104, 7), (5, 96, 640, 8)])
+def test_gemm_tc_split_k_in_clusters(M, N, K, splits):
+    """K split over the CTAs of a cluster, partial tiles added through distributed shared memory."""
+    o = ops()
+    g = torch.Generator(device="cpu").manual_seed(splits + M)
+    a = torch.randn(M, K, generator=g).bfloat16().to(DEV)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).bfloat16().to(DEV)
+    bias = torch.randn(N, generator=g).to(DEV)
+    want = a.float() @ w.float().t()
+    out1 = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    out2 = torch.empty_like(out1)
+    o.gemm_tc(a, w, out1, bias=bias, relu=True, splits=splits, cluster=True)
+    o.gemm_tc(a, w, out2, bias=bias, relu=True, splits=splits, cluster=True)
+    o.raise_on_device_error()
+    assert rel_err(out1, torch.relu(want + bias)) <= 2e-5
+    assert torch.equal(out1, out2), "the order of the additions is fixed"
+    res = torch.randn(M, N, generator=g).to(DEV)
+    want3 = want + bias + res
+    o.gemm_tc(a, w, res, bias=bias, residual=res, splits=splits, cluster=True)
+    assert rel_err(res, want3) <= 2e-5, "bias + residual in place"
+    outb = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    o.gemm_tc(a, w, outb, splits=splits, cluster=True)
+    o.raise_on_device_error()
+    assert rel_err(outb, want) <= 5e-3
+    # the same sums as with scratch memory: both add the partial tiles in split order
+    out3 = torch.empty_like(out1)
+    o.gemm_tc(a, w, out3, bias=bias, relu=True, splits=splits)
+    assert torch.equal(out1, out3)
 
 
 def test_gemm_tc_finds_a_planted_column():

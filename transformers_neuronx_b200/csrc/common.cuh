@@ -46,6 +46,22 @@ static inline int tnx_launch_ex(int early, void (*kernel)(KArgs...), dim3 grid, 
     if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
     return 0;
 }
+// The same with the thread blocks grouped into clusters of `cluster` (which must divide the grid).
+template <typename... KArgs, typename... Args>
+static inline int tnx_launch_cluster(int early, dim3 cluster, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                     cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cluster.x; attr[0].val.clusterDim.y = cluster.y; attr[0].val.clusterDim.z = cluster.z;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = early ? 2 : 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+    if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
+    return 0;
+}
 template <typename... KArgs, typename... Args>
 static inline int tnx_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                                  Args... args) {

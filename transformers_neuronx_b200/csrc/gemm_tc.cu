@@ -49,9 +49,30 @@ struct Params {
     float* partials;             // [splits][rows_p_padded][rows_q_padded] when splits > 1
     int* counters;               // one per output tile, zero between calls
     int* err;
+    int cluster_reduce;          // few tokens, split K: the CTAs of a tile form a cluster and add their partial tiles
+                                 // through distributed shared memory instead of scratch memory
     int sk_tiles;                // paired kernel: the last sk_tiles output tiles are shared out by K blocks
     int sk_pairs;                // ... over the first sk_pairs pairs
 };
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t cluster_addr) {
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr) : "memory");
+    return v;
+}
 
 template <int BN, bool SWAP>
 __device__ __forceinline__ void store_tile_row(const Params& p, int lane_row, int col0, const float (&v)[32], int ncols,
@@ -264,6 +285,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                     for (int j = 0; j < 32; ++j) v[j] = (j < LD_COLS && num_kb > 0) ? __uint_as_float(r[j]) : 0.f;
                     store_tile_row<BN, SWAP>(p, lane_row, tile_q * BN + c, v, LD_COLS);
                 }
+            } else if (p.cluster_reduce) {
+                // 32-bit partial tile -> this CTA's shared memory, [col 0..BN)[row 0..127], over the
+                // first stages (every load into them has been consumed by now)
+                float* part = (float*)smem + row_in_tile;
+#pragma unroll 1
+                for (int c = 0; c < BN; c += LD_COLS) {
+                    uint32_t r[32];
+                    const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c;
+                    if (LD_COLS == 32) tmem_ld32(taddr, r); else tmem_ld16(taddr, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < LD_COLS; ++j) part[(c + j) * TILE_P] = num_kb > 0 ? __uint_as_float(r[j]) : 0.f;
+                }
             } else {
                 // 32-bit partial tile -> scratch: [split][tile][col 0..BN)[row 0..127]: the 32 lanes
                 // of a warp write 32 consecutive floats
@@ -284,8 +318,39 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         }
     }
 
+    // ---- split-K within a cluster: every CTA adds a band of rows over all partial tiles ----------
+    if (p.splits > 1 && p.cluster_reduce) {
+        if (warp >= 2 && !ok) {                           // a wait ran out: the partial tile must still be defined
+            float* part = (float*)smem + (warp & 3) * 32 + lane;
+            for (int c = 0; c < BN; ++c) part[c * TILE_P] = 0.f;
+        }
+        tc_fence_before();
+        cluster_sync();                                   // all partial tiles of the cluster are written
+        const int S = p.splits, r = (int)cluster_ctarank();
+        const int row_lo = TILE_P * r / S, n_rows = TILE_P * (r + 1) / S - row_lo;
+        const uint32_t part_addr = smem_u32(smem);
+        for (int item = threadIdx.x; item < n_rows * BN; item += NUM_THREADS) {
+            const int col = item / n_rows, row = row_lo + item - col * n_rows;
+            const int n = tile_p * TILE_P + row, m = tile_q * BN + col;     // feature, token
+            const bool live = n < p.rows_p && m < p.rows_q;
+            const size_t o = (size_t)m * p.ldc + n;
+            const float res = (live && p.residual) ? __ldcg(p.residual + o) : 0.f;      // in flight during the sum
+            const uint32_t a = part_addr + (uint32_t)((col * TILE_P + row) * 4);
+            float v = 0.f;
+            for (int s = 0; s < S; ++s) v += ld_cluster_f32(map_to_cta(a, (uint32_t)s));   // split order
+            if (live) {
+                if (p.bias) v += __ldg(p.bias + n);
+                if (p.relu) v = fmaxf(v, 0.f);
+                v += res;
+                if (p.c_is_bf16) ((bf16*)p.C)[o] = __float2bfloat16_rn(v);
+                else ((float*)p.C)[o] = v;
+            }
+        }
+        cluster_sync();                                   // no CTA leaves while its partial tile may still be read
+    }
+
     // ---- split-K: the CTA that finishes last adds the partial tiles in split order -------------
-    if (p.splits > 1) {
+    if (p.splits > 1 && !p.cluster_reduce) {
         __threadfence();
         __syncthreads();
         if (threadIdx.x == 0) {
@@ -307,14 +372,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 float v[32];
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] = 0.f;
-                for (int s = 0; s < p.splits; ++s) {          // split order: the sum does not depend on timing
-                    const float* src = p.partials + ((size_t)s * tiles + tile_id) * TILE_P * BN + row_in_tile +
-                                       (size_t)c * TILE_P;
-                    float f[LD_COLS];
+                // Split order: the sum does not depend on timing.  The loads of four splits are issued
+                // together, so that the sum costs a few round trips to the second-level cache, not one
+                // per split.
+                constexpr int GROUP = LD_COLS == 16 ? 4 : 2;
+                const float* src0 = p.partials + tile_id * TILE_P * BN + row_in_tile + (size_t)c * TILE_P;
+                const size_t split_stride = tiles * TILE_P * BN;
+                for (int s0 = 0; s0 < p.splits; s0 += GROUP) {
+                    float f[GROUP][LD_COLS];
 #pragma unroll
-                    for (int j = 0; j < LD_COLS; ++j) f[j] = __ldcg(src + (size_t)j * TILE_P);
+                    for (int g = 0; g < GROUP; ++g) {
+                        if (s0 + g < p.splits) {
+                            const float* src = src0 + (size_t)(s0 + g) * split_stride;
 #pragma unroll
-                    for (int j = 0; j < LD_COLS; ++j) v[j] += f[j];
+                            for (int j = 0; j < LD_COLS; ++j) f[g][j] = __ldcg(src + (size_t)j * TILE_P);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < LD_COLS; ++j) f[g][j] = 0.f;
+                        }
+                    }
+#pragma unroll
+                    for (int g = 0; g < GROUP; ++g)
+#pragma unroll
+                        for (int j = 0; j < LD_COLS; ++j) v[j] += f[g][j];
                 }
                 store_tile_row<BN, SWAP>(p, lane_row, tile_q * BN + c, v, LD_COLS);
             }
@@ -666,19 +746,6 @@ __device__ __forceinline__ bool drain_accumulator_tma(const Params& p, EpilogueT
 constexpr int CSTAGES = 5;
 constexpr int PAIR_EPI_BYTES = 4 * EPI_BUFS * EPI_BOX_BYTES;     // 48 KB: three boxes for each epilogue warp
 
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
-    return r;
-}
-__device__ __forceinline__ void cluster_sync() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
 // TMA load into this CTA's shared memory whose bytes are counted on a barrier given by its
 // shared::cluster address (CTA 0's barrier).
 __device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int x, int y) {
@@ -942,12 +1009,16 @@ int launch(const CUtensorMap& mp, const CUtensorMap& mq, const Params& p, dim3 g
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
+    if (p.cluster_reduce)
+        return tnx_launch_cluster(1, dim3(1, 1, grid.z), gemm_tc_kernel<BN, STAGES, SWAP>, grid, dim3(NUM_THREADS), smem, stream, mp, mq, p);
     return tnx_launch_ex(1, gemm_tc_kernel<BN, STAGES, SWAP>, grid, dim3(NUM_THREADS), smem, stream, mp, mq, p);
 }
 
 }  // namespace
 
 // Many tokens: which kernel, and how many of the paired kernel's tiles are shared out by K blocks.
+constexpr int MAX_CLUSTER = 8;               // the portable cluster size
+
 struct ManyTokensPlan { int kind; int pairs; int sk_tiles; int sk_pairs; };   // kind 0: 128 x 128 tiles, 1: CTA pairs, 2: persistent
 static ManyTokensPlan plan_many_tokens(int M, int N, int K, int sms) {
     ManyTokensPlan r{2, 0, 0, 0};
@@ -1001,21 +1072,16 @@ TNX_EXPORT int tnx_gemm_tc_plan(int M, int N, int K, int n_sms, int* splits, lon
         }
         return 0;
     }
-    const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    // Few tokens: the weight matrix has (N / 128) tiles; K is split 2, 4 or 8 ways, as far as the
+    // CTAs still fit on the GPU at once (two to an SM) and every split keeps at least four K blocks.
+    // The CTAs of a tile form a cluster and add their partial tiles through shared memory, so no
+    // scratch memory is needed.  (Measured on the layer sizes of the 6.7B and 13B models at 8 and
+    // 64 tokens: a second round of CTAs, or a cluster of 3, costs more than a coarser split.)
     const int tiles = (N + TILE_P - 1) / TILE_P;
     const int kb = (K + BLOCK_K - 1) / BLOCK_K;
-    int s = (2 * n_sms + tiles / 2) / tiles;   // two CTAs fit on an SM: aim at 2 x SMs CTAs
-    const int cap = bn == 16 ? 12 : (bn == 32 ? 8 : 4);   // the partial tiles grow with the tokens
-    if (s > kb / 4) s = kb / 4;
-    if (s > cap) s = cap;
-    if (s < 1) s = 1;
-    const int per = (kb + s - 1) / s;
-    s = (kb + per - 1) / per;                 // no empty split
+    int s = MAX_CLUSTER;
+    while (s > 1 && (tiles * s > 2 * n_sms || s * 4 > kb)) s >>= 1;
     *splits = s;
-    if (s > 1) {
-        *scratch_bytes = (long long)s * tiles * TILE_P * bn * 4;
-        *n_counters = tiles;
-    }
     return 0;
 }
 
@@ -1085,7 +1151,12 @@ TNX_EXPORT int tnx_gemm_tc(const void* A, const void* W, const float* bias, cons
                              tiles_m, tiles_n);
     }
     if (splits < 1) splits = 1;
-    if (splits > 1 && (!scratch || !counters)) return TNX_ERR_BAD_ARG;
+    // Split K: with scratch memory and counters the CTA that finishes last adds the partial tiles;
+    // without them the CTAs of a tile form a cluster (at most 8) and add up through shared memory.
+    if (splits > 1 && (!scratch || !counters)) {
+        if (splits > MAX_CLUSTER) return TNX_ERR_BAD_ARG;
+        p.cluster_reduce = 1;
+    }
     p.rows_p = N; p.rows_q = M; p.splits = splits; p.kb_per_split = (kb + splits - 1) / splits;
     const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
     if (!make_map(&mp, W, N, K, ldw, TILE_P) || !make_map(&mq, A, M, K, lda, bn)) return TNX_ERR_UNSUPPORTED;

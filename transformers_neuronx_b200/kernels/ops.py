@@ -321,10 +321,12 @@ def gemv(a, w, out, bias=None, residual=None, relu=False):
                         _stream()), "gemv")
 
 
-def gemm_tc(a, w, out, bias=None, residual=None, relu=False, splits=None, few_tokens_kernel=True):
+def gemm_tc(a, w, out, bias=None, residual=None, relu=False, splits=None, few_tokens_kernel=True, cluster=False):
     """out = epilogue(a @ w^T), bfloat16 operands, 32-bit accumulation: on the tcgen05 tensor cores,
     or (one token, unless few_tokens_kernel is False or splits is given) as a stream of the
-    weights through the multiply-add units."""
+    weights through the multiply-add units.  `splits` forces a split of K for up to 64 tokens (a test
+    hook): partial tiles added by the CTA that finishes last, or (cluster=True, at most 8 splits) by
+    the CTAs of a cluster through their shared memory, which is what the kernel's own plan uses."""
     lib = _build.load("gemm_tc")
     _need(a, "a", torch.bfloat16, None, contiguous=False)
     _need(w, "w", torch.bfloat16, None, contiguous=False)
@@ -364,6 +366,10 @@ def gemm_tc(a, w, out, bias=None, residual=None, relu=False, splits=None, few_to
         bn = 16 if M <= 16 else (32 if M <= 32 else 64)
         tiles = -(-N // 128)
         n_splits, nbytes, ncnt = c_int(s), ctypes.c_longlong(s * tiles * 128 * bn * 4 if s > 1 else 0), c_int(tiles if s > 1 else 0)
+        if cluster:
+            if s > 8:
+                raise KernelError("a cluster holds at most 8 thread blocks")
+            nbytes, ncnt = ctypes.c_longlong(0), c_int(0)
     scratch = None
     if nbytes.value:
         need = nbytes.value // 4
