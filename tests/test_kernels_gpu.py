@@ -302,6 +302,32 @@ def test_attention_decode(n_heads, n_kv, d, window, n_splits):
         assert rel_err(out, case.want(scale, window)) <= 1e-2
 
 
+@pytest.mark.parametrize("n_heads,n_kv,d", [(4, 4, 128), (6, 2, 64), (3, 1, 80), (2, 2, 256)])
+@pytest.mark.parametrize("n_splits", [1, 3])
+def test_attention_decode_appends_the_new_token(n_heads, n_kv, d, n_splits):
+    """The decode kernel writes the token's own key and value into its page and reads them back: the
+    result and the cache must be those of an append followed by attention."""
+    lens = [(0, 1), (15, 1), (16, 1), (17, 1), (255, 1), (256, 1), (700, 1), (63, 1)]
+    case = PagedCase(lens, n_heads, n_kv, d, torch.bfloat16, seed=d + 3)
+    scale = 0.9 / math.sqrt(d)
+    full = case.cache.clone()
+    k_new = torch.zeros(case.N, n_kv * d + 8, dtype=torch.bfloat16, device=DEV)[:, :n_kv * d]     # a row pitch of its own
+    v_new = torch.zeros(case.N, n_kv * d + 8, dtype=torch.bfloat16, device=DEV)[:, :n_kv * d]
+    pages = case.bt.cpu()
+    for r, (c, _) in enumerate(lens):                       # take the last token out of the cache again
+        pg, slot = int(pages[r, c // 16]), c % 16
+        k_new[r] = full[pg, 0, :, slot].reshape(-1)
+        v_new[r] = full[pg, 1, :, slot].reshape(-1)
+        case.cache[pg, :, :, slot] = float("nan")
+    out = torch.zeros(case.N, n_heads * d, dtype=torch.bfloat16, device=DEV)
+    ops().attention_decode(case.q_flat, case.cache, case.bt, case.tok_req, case.positions, out, n_heads, scale,
+                           0, max_kv_len=701, n_splits=n_splits, new_kv=(k_new, v_new))
+    assert rel_err(out, case.want(scale, None)) <= 1e-2
+    written = ~torch.isnan(full.float())
+    assert torch.equal(case.cache[written], full[written]), "the cache holds the appended keys and values"
+    assert bool(torch.isnan(case.cache.float()[~written]).all()), "nothing else was written"
+
+
 def test_attention_decode_row_list():
     """Only the rows named are computed (a mixed batch: the others belong to the prefill kernel)."""
     lens = [(5, 1), (0, 40), (99, 1), (10, 3), (33, 1)]

@@ -10,6 +10,12 @@
 // of 16 keys x head_dim is read with fully used 16-byte loads.  The warps' states are merged in
 // shared memory.  With more than one split the CTA writes its (max, sum, accumulator) to scratch
 // memory, and the CTA of a (row, head) that finishes last merges the splits in split order.
+//
+// The kernel can also do the cache append of a decode step: given the new keys and values of the
+// rows' tokens, the CTA whose range of pages holds a token's own position copies that token's key
+// and value (of its key/value head) into the page for later steps, and takes them into its own
+// softmax straight from where the projection left them; the pages are read for the earlier keys
+// only.  The append kernel and its launch are then not needed.
 #include "common.cuh"
 
 namespace {
@@ -31,6 +37,10 @@ struct DecodeParams {
     int n_splits, pages_per_split;
     float* scratch;                  // [rows][heads][splits][head_dim + 2]
     int* counters;                   // [rows][heads], zero between calls
+    const bf16* k_new;               // [rows, kv_heads * head_dim] keys of the rows' own tokens, or null:
+    const bf16* v_new;               //   then the cache already holds them
+    int kv_stride;
+    bf16* cache_w;
 };
 
 // LPK lanes share one key (each 8 dims); KPL = 32 / LPK keys are read per warp-wide load.
@@ -75,6 +85,22 @@ attention_decode_kernel(const DecodeParams p) {
     const int page_hi = min(n_pages, (split + 1) * p.pages_per_split);
     const size_t head_block = (size_t)PAGE * d;
 
+    // With the append fused in, the cache holds the keys before this token's own; its own key and
+    // value come from k_new / v_new.
+    const bool own_here = p.k_new != nullptr && (pos / PAGE) / p.pages_per_split == split;    // one answer for the CTA
+    const int cached_len = p.k_new != nullptr ? pos : kv_len;
+    if (own_here) {
+        // for later steps: CTAs of heads that share a key/value head write the same bytes
+        const int page = bt[pos / PAGE];
+        const int pieces = d / 8;
+        for (int i = threadIdx.x; i < 2 * pieces; i += WARPS * 32) {
+            const int which = i / pieces, piece = i - which * pieces;
+            const bf16* src = (which ? p.v_new : p.k_new) + (size_t)row * p.kv_stride + (size_t)kvh * d;
+            bf16* dst = p.cache_w + (((size_t)page * 2 + which) * p.n_kv_heads + kvh) * head_block + (size_t)(pos % PAGE) * d;
+            ((uint4*)dst)[piece] = ((const uint4*)src)[piece];
+        }
+    }
+
     for (int pg = page_lo + warp; pg < page_hi; pg += WARPS) {
         const int page = bt[pg];
         const bf16* kbase = p.cache + (((size_t)page * 2 + 0) * p.n_kv_heads + kvh) * head_block;
@@ -105,7 +131,7 @@ attention_decode_kernel(const DecodeParams p) {
 #pragma unroll
             for (int o = LPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
             const int j = pg * PAGE + i * KPL + kgrp;
-            s[i] = (j >= first_key && j < kv_len) ? dot : -INFINITY;
+            s[i] = (j >= first_key && j < cached_len) ? dot : -INFINITY;
             page_max = fmaxf(page_max, s[i]);
         }
 #pragma unroll
@@ -124,6 +150,41 @@ attention_decode_kernel(const DecodeParams p) {
             l += pj;
             if (!live) vreg[i] = make_uint4(0, 0, 0, 0);          // rows never written may hold anything, NaN included
             const __nv_bfloat162* vv = (const __nv_bfloat162*)&vreg[i];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                const float2 f = __bfloat1622float2(vv[t]);
+                acc[2 * t] = fmaf(pj, f.x, acc[2 * t]);
+                acc[2 * t + 1] = fmaf(pj, f.y, acc[2 * t + 1]);
+            }
+        }
+    }
+    if (own_here && warp == 0) {
+        // the token's own key and value, as one more key of warp 0 (the lanes of key group 0)
+        const bf16* ksrc = p.k_new + (size_t)row * p.kv_stride + (size_t)kvh * d + sub * 8;
+        const bf16* vsrc = p.v_new + (size_t)row * p.kv_stride + (size_t)kvh * d + sub * 8;
+        const uint4 kown = dim_ok ? *(const uint4*)ksrc : make_uint4(0, 0, 0, 0);
+        const uint4 vown = dim_ok ? *(const uint4*)vsrc : make_uint4(0, 0, 0, 0);
+        const __nv_bfloat162* kk = (const __nv_bfloat162*)&kown;
+        float dot = 0.f;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            const float2 f = __bfloat1622float2(kk[t]);
+            dot = fmaf(q[2 * t], f.x, dot);
+            dot = fmaf(q[2 * t + 1], f.y, dot);
+        }
+#pragma unroll
+        for (int o = LPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        const float s_own = __shfl_sync(0xffffffffu, dot, 0);
+        const float m_new = fmaxf(m, s_own);
+        const float corr = (m == -INFINITY) ? 0.f : __expf(m - m_new);
+        l *= corr;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] *= corr;
+        m = m_new;
+        if (kgrp == 0) {
+            const float pj = __expf(s_own - m);
+            l += pj;
+            const __nv_bfloat162* vv = (const __nv_bfloat162*)&vown;
 #pragma unroll
             for (int t = 0; t < 4; ++t) {
                 const float2 f = __bfloat1622float2(vv[t]);
@@ -209,15 +270,20 @@ TNX_EXPORT long long tnx_attention_decode_scratch_floats(int n_rows, int n_heads
     return n_splits > 1 ? (long long)n_rows * n_heads * n_splits * (head_dim + 2) : 0;
 }
 
-TNX_EXPORT int tnx_attention_decode(const void* q, int q_stride, const void* cache, const int* block_tables,
-                                    int bt_stride, const int* rows, const int* token_request, const int* positions,
-                                    void* out, int out_stride, int n_rows, int n_heads, int n_kv_heads, int head_dim,
-                                    int page_size, int window, float scale, int n_splits, int pages_per_split,
-                                    float* scratch, int* counters, cudaStream_t stream) {
+// k_new / v_new: the keys and values of the rows' own tokens ([rows, kv_heads * head_dim], row pitch
+// kv_stride elements), which the kernel then writes into the cache itself; null: already appended.
+TNX_EXPORT int tnx_attention_decode_append(const void* q, int q_stride, void* cache, const int* block_tables,
+                                           int bt_stride, const int* rows, const int* token_request, const int* positions,
+                                           void* out, int out_stride, int n_rows, int n_heads, int n_kv_heads, int head_dim,
+                                           int page_size, int window, float scale, int n_splits, int pages_per_split,
+                                           float* scratch, int* counters, const void* k_new, const void* v_new,
+                                           int kv_stride, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (page_size != PAGE || head_dim % 16 || head_dim < 16 || head_dim > 256 || n_kv_heads <= 0 ||
         n_heads % n_kv_heads || q_stride % 8 || ((uintptr_t)q & 15) || ((uintptr_t)cache & 15))
         return TNX_ERR_UNSUPPORTED;
+    if ((k_new == nullptr) != (v_new == nullptr)) return TNX_ERR_BAD_ARG;
+    if (k_new && (kv_stride % 8 || (((uintptr_t)k_new | (uintptr_t)v_new) & 15))) return TNX_ERR_UNSUPPORTED;
     if (n_splits < 1 || pages_per_split < 1) return TNX_ERR_BAD_ARG;
     if (n_splits > 1 && (!scratch || !counters)) return TNX_ERR_BAD_ARG;
     DecodeParams p;
@@ -226,6 +292,7 @@ TNX_EXPORT int tnx_attention_decode(const void* q, int q_stride, const void* cac
     p.positions = positions; p.out = (bf16*)out; p.out_stride = out_stride;
     p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.head_dim = head_dim; p.window = window; p.scale = scale;
     p.n_splits = n_splits; p.pages_per_split = pages_per_split; p.scratch = scratch; p.counters = counters;
+    p.k_new = (const bf16*)k_new; p.v_new = (const bf16*)v_new; p.kv_stride = kv_stride; p.cache_w = (bf16*)cache;
     dim3 grid(n_heads, n_rows, n_splits);
     const int chunks = head_dim / 8;
     const dim3 block(WARPS * 32);
@@ -234,6 +301,16 @@ TNX_EXPORT int tnx_attention_decode(const void* q, int q_stride, const void* cac
     if (chunks <= 8) return tnx_launch_pdl(attention_decode_kernel<8>, grid, block, 0, stream, p);
     if (chunks <= 16) return tnx_launch_pdl(attention_decode_kernel<16>, grid, block, 0, stream, p);
     return tnx_launch_pdl(attention_decode_kernel<32>, grid, block, 0, stream, p);
+}
+
+TNX_EXPORT int tnx_attention_decode(const void* q, int q_stride, const void* cache, const int* block_tables,
+                                    int bt_stride, const int* rows, const int* token_request, const int* positions,
+                                    void* out, int out_stride, int n_rows, int n_heads, int n_kv_heads, int head_dim,
+                                    int page_size, int window, float scale, int n_splits, int pages_per_split,
+                                    float* scratch, int* counters, cudaStream_t stream) {
+    return tnx_attention_decode_append(q, q_stride, const_cast<void*>(cache), block_tables, bt_stride, rows, token_request,
+                                       positions, out, out_stride, n_rows, n_heads, n_kv_heads, head_dim, page_size, window,
+                                       scale, n_splits, pages_per_split, scratch, counters, nullptr, nullptr, 0, stream);
 }
 
 // ---------------------------------------------------------------------------------------------------

@@ -381,9 +381,11 @@ def gemm_tc(a, w, out, bias=None, residual=None, relu=False, splits=None, few_to
 
 
 def attention_decode(q, cache, block_tables, token_request, positions, out, n_heads, scale, window=0, rows=None,
-                     n_rows=None, max_kv_len=None, n_splits=None):
+                     n_rows=None, max_kv_len=None, n_splits=None, new_kv=None):
     """One query token per row over the paged bfloat16 cache.  `rows` (int32) names the rows of q
-    that are decode tokens (None: all); max_kv_len bounds their contexts (for the split plan)."""
+    that are decode tokens (None: all); max_kv_len bounds their contexts (for the split plan).
+    new_kv = (k, v), [rows of q, kv_heads * head_dim] bfloat16: the keys and values of the rows' own
+    tokens, which the kernel then writes into their pages itself (no kv_append before it)."""
     lib = _build.load("attention_decode")
     _need(cache, "cache", torch.bfloat16, 5)
     N, width, q_stride = _rows_2d(q, "q")
@@ -409,11 +411,23 @@ def attention_decode(q, cache, block_tables, token_request, positions, out, n_he
         need = R * n_heads * n_splits * (d + 2)
         scratch = _grow(st, "att_scratch", need, torch.float32, q.device, 1 << 20)
         _grow(st, "att_counters", R * n_heads, torch.int32, q.device, 8192, zero=True)
-    _check(lib.tnx_attention_decode(_p(q), c_int(q_stride), _p(cache), _p(block_tables), c_int(block_tables.stride(0)),
-                                    _p(rows), _p(token_request), _p(positions), _p(out), c_int(out_stride), c_int(R),
-                                    c_int(n_heads), c_int(n_kv), c_int(d), c_int(ps), c_int(window or 0), c_float(scale),
-                                    c_int(n_splits), c_int(pps), _p(scratch), _p(st.get("att_counters")), _stream()),
-           "attention_decode")
+    k_new = v_new = None
+    kv_stride = 0
+    if new_kv is not None:
+        k_new, v_new = new_kv
+        for t, nm in ((k_new, "k"), (v_new, "v")):
+            _need(t, nm, torch.bfloat16, None, contiguous=False)
+            if _rows_2d(t, nm)[:2] != (N, n_kv * d):
+                raise KernelError(f"new {nm} must be [{N}, {n_kv * d}]")
+        kv_stride = k_new.stride(0)
+        if v_new.stride(0) != kv_stride:
+            raise KernelError("new k and v must have the same row pitch")
+    _check(lib.tnx_attention_decode_append(
+        _p(q), c_int(q_stride), _p(cache), _p(block_tables), c_int(block_tables.stride(0)),
+        _p(rows), _p(token_request), _p(positions), _p(out), c_int(out_stride), c_int(R),
+        c_int(n_heads), c_int(n_kv), c_int(d), c_int(ps), c_int(window or 0), c_float(scale),
+        c_int(n_splits), c_int(pps), _p(scratch), _p(st.get("att_counters")), _p(k_new), _p(v_new), c_int(kv_stride),
+        _stream()), "attention_decode")
 
 
 ATTN_PREFILL_TILE = 128      # query rows of one work item of the prefill attention kernel
@@ -469,10 +483,18 @@ def attention_prefill_tc(q, cache, block_tables, tile_req, tile_q0, q_start, q_l
                                         c_float(scale), _p(st["err"]), _stream()), "attention_prefill_tc")
 
 
-def _attention_bf16(ctx, group, q, cache, out, n_heads, scale, window):
+def _attention_bf16(ctx, group, q, cache, out, n_heads, scale, window, new_kv):
     if cache.shape[3] != 16 or q.stride(0) % 8 or q.data_ptr() % 16:
         return False
     bt = ctx.block_tables[group]
+    fused = None
+    if new_kv is not None:
+        k, v, slots = new_kv
+        if ctx.decode_only and not ctx.n_prefill_tiles and k.stride(0) % 8 == 0 and k.data_ptr() % 16 == 0 \
+                and v.data_ptr() % 16 == 0:
+            fused = (k, v)                       # a decode step: the attention kernel appends by itself
+        else:
+            kv_append(k, v, slots, cache, ctx.page_size)
     if ctx.n_prefill_tiles:
         prefill = attention_prefill_tc if attention_prefill_tc_supported(q, cache, out) else attention_prefill
         prefill(q, cache, bt, ctx.tile_req, ctx.tile_q0, ctx.q_start, ctx.q_len, ctx.ctx_len, out,
@@ -480,20 +502,24 @@ def _attention_bf16(ctx, group, q, cache, out, n_heads, scale, window):
     if ctx.n_decode_rows:
         attention_decode(q, cache, bt, ctx.token_request, ctx.positions, out, n_heads, scale, window,
                          rows=None if ctx.decode_only else ctx.decode_rows, n_rows=ctx.n_decode_rows,
-                         max_kv_len=ctx.max_decode_ctx)
+                         max_kv_len=ctx.max_decode_ctx, new_kv=fused)
     return True
 
 
 _attention_impls["bf16"] = _attention_bf16
 
 
-def attention(ctx, group, q, cache, out, n_heads, scale, window=0):
+def attention(ctx, group, q, cache, out, n_heads, scale, window=0, new_kv=None):
     """Attention of this step's queries over the cache of the running schedule entry.  32-bit
     caches, and head sizes or windows that the bfloat16 kernels do not take, run on the CUDA-core
     kernel; bfloat16 runs the prefill kernel for requests with several rows and the split
-    decode kernel for requests with one."""
+    decode kernel for requests with one.  new_kv = (k, v, slot_mapping): the keys and values of
+    this step's tokens, not yet in the cache; they are appended here, by kv_append or (a step of
+    decode tokens only, bfloat16) by the decode kernel itself."""
     impl = _attention_impls.get("bf16") if cache.dtype == torch.bfloat16 else None
-    if impl is not None and impl(ctx, group, q, cache, out, n_heads, scale, window):
+    if impl is not None and impl(ctx, group, q, cache, out, n_heads, scale, window, new_kv):
         return
+    if new_kv is not None:
+        kv_append(new_kv[0], new_kv[1], new_kv[2], cache, ctx.page_size)
     attention_simt(q, cache, ctx.block_tables[group], ctx.token_request, ctx.positions, out, n_heads, scale,
                    window)

@@ -4,8 +4,9 @@ As the reference computes it (src/transformers_neuronx/opt/model.py:388-524): q,
 with bias, q scaled by `scale` (1/sqrt(head_dim) for OPT, :458-459), scores against every earlier
 key and the token's own, softmax in 32-bit, context, output projection with bias; the residual add
 is fused into the output projection here.  Heads, key/value heads, head size, scale and window are
-parameters.  The keys and values of this step's tokens are written into the cache's pages first;
-the attention kernels then read keys and values from the pages alone, whatever the cut of the batch.
+parameters.  The keys and values of this step's tokens are written into the cache's pages first (by
+the append kernel, or in a step of decode tokens only by the decode attention kernel itself); the
+attention kernels then read keys and values from the pages alone, whatever the cut of the batch.
 """
 from __future__ import annotations
 
@@ -72,9 +73,8 @@ class PagedAttention(Mixer):
         if self.position is not None:
             self.position.rotate(ctx, q, k)
         cache, g = ctx.cache(), ctx.cache_group()
-        ops.kv_append(k, v, ctx.slot_mapping[g], cache, ctx.page_size)
         att = ctx.empty(N, qd)
-        ops.attention(ctx, g, q, cache, att, s.n_heads, s.scale, s.window or 0)
+        ops.attention(ctx, g, q, cache, att, s.n_heads, s.scale, s.window or 0, new_kv=(k, v, ctx.slot_mapping[g]))
         self.out.forward(att, residual, residual=residual)
 
 
