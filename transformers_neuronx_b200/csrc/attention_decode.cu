@@ -5,7 +5,8 @@
 //   s_j = scale * <q, k_j>  (32-bit),  out = sum_j exp(s_j - max) v_j / sum_j exp(s_j - max)
 //
 // Grid (heads, rows, splits): a CTA takes one (row, head) and one contiguous range of pages; its
-// four warps take pages of the range in turn and keep an online softmax each.  A lane owns eight
+// four warps take pages of the range in turn and keep an online softmax each (half a page at a
+// time, the next half's loads in flight meanwhile).  A lane owns eight
 // consecutive dims of the head (one 16-byte load per key) of some of the keys of a page, so a page
 // of 16 keys x head_dim is read with fully used 16-byte loads.  The warps' states are merged in
 // shared memory.  With more than one split the CTA writes its (max, sum, accumulator) to scratch
@@ -101,61 +102,84 @@ attention_decode_kernel(const DecodeParams p) {
         }
     }
 
-    for (int pg = page_lo + warp; pg < page_hi; pg += WARPS) {
+    // The warp's pages (page_lo + warp, + WARPS, ...) are taken in chunks of CH warp-wide loads of
+    // keys and as many of values: half a page, or a whole one where a page is a single load.  The
+    // loads of the next chunk are issued before the current one is used, so that the warp always
+    // has loads in flight; each chunk does its own step of the online softmax.
+    constexpr int CH = LOADS >= 2 ? LOADS / 2 : 1;           // loads per chunk
+    constexpr int CPP = LOADS / CH;                          // chunks per page
+    const int my_pages = page_hi > page_lo + warp ? (page_hi - page_lo - warp + WARPS - 1) / WARPS : 0;
+    const int n_chunks = my_pages * CPP;
+    auto issue = [&](int t, uint4 (&kb)[CH], uint4 (&vb)[CH]) {
+        const int pg = page_lo + warp + (t / CPP) * WARPS;
         const int page = bt[pg];
         const bf16* kbase = p.cache + (((size_t)page * 2 + 0) * p.n_kv_heads + kvh) * head_block;
         const bf16* vbase = p.cache + (((size_t)page * 2 + 1) * p.n_kv_heads + kvh) * head_block;
-        uint4 kreg[LOADS], vreg[LOADS];
+        const int i0 = (t % CPP) * CH;
 #pragma unroll
-        for (int i = 0; i < LOADS; ++i) {
-            const int key = i * KPL + kgrp;
-            kreg[i] = dim_ok ? __ldg((const uint4*)(kbase + (size_t)key * d + sub * 8)) : make_uint4(0, 0, 0, 0);
+        for (int i = 0; i < CH; ++i) {
+            const int key = (i0 + i) * KPL + kgrp;
+            kb[i] = dim_ok ? __ldg((const uint4*)(kbase + (size_t)key * d + sub * 8)) : make_uint4(0, 0, 0, 0);
         }
 #pragma unroll
-        for (int i = 0; i < LOADS; ++i) {
-            const int key = i * KPL + kgrp;
-            vreg[i] = dim_ok ? __ldg((const uint4*)(vbase + (size_t)key * d + sub * 8)) : make_uint4(0, 0, 0, 0);
+        for (int i = 0; i < CH; ++i) {
+            const int key = (i0 + i) * KPL + kgrp;
+            vb[i] = dim_ok ? __ldg((const uint4*)(vbase + (size_t)key * d + sub * 8)) : make_uint4(0, 0, 0, 0);
         }
-        float s[LOADS];
-        float page_max = -INFINITY;
+    };
+    auto consume = [&](int t, uint4 (&kb)[CH], uint4 (&vb)[CH]) {
+        const int pg = page_lo + warp + (t / CPP) * WARPS;
+        const int i0 = (t % CPP) * CH;
+        float s[CH];
+        float chunk_max = -INFINITY;
 #pragma unroll
-        for (int i = 0; i < LOADS; ++i) {
-            const __nv_bfloat162* kk = (const __nv_bfloat162*)&kreg[i];
+        for (int i = 0; i < CH; ++i) {
+            const __nv_bfloat162* kk = (const __nv_bfloat162*)&kb[i];
             float dot = 0.f;
 #pragma unroll
-            for (int t = 0; t < 4; ++t) {
-                const float2 f = __bfloat1622float2(kk[t]);
-                dot = fmaf(q[2 * t], f.x, dot);
-                dot = fmaf(q[2 * t + 1], f.y, dot);
+            for (int u = 0; u < 4; ++u) {
+                const float2 f = __bfloat1622float2(kk[u]);
+                dot = fmaf(q[2 * u], f.x, dot);
+                dot = fmaf(q[2 * u + 1], f.y, dot);
             }
 #pragma unroll
             for (int o = LPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-            const int j = pg * PAGE + i * KPL + kgrp;
+            const int j = pg * PAGE + (i0 + i) * KPL + kgrp;
             s[i] = (j >= first_key && j < cached_len) ? dot : -INFINITY;
-            page_max = fmaxf(page_max, s[i]);
+            chunk_max = fmaxf(chunk_max, s[i]);
         }
 #pragma unroll
-        for (int o = 16; o >= LPK; o >>= 1) page_max = fmaxf(page_max, __shfl_xor_sync(0xffffffffu, page_max, o));
-        if (page_max == -INFINITY) continue;                     // every key of the page masked (warp-uniform)
-        const float m_new = fmaxf(m, page_max);
+        for (int o = 16; o >= LPK; o >>= 1) chunk_max = fmaxf(chunk_max, __shfl_xor_sync(0xffffffffu, chunk_max, o));
+        if (chunk_max == -INFINITY) return;                      // every key of the chunk masked (warp-uniform)
+        const float m_new = fmaxf(m, chunk_max);
         const float corr = (m == -INFINITY) ? 0.f : __expf(m - m_new);
         l *= corr;
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i] *= corr;
         m = m_new;
 #pragma unroll
-        for (int i = 0; i < LOADS; ++i) {
+        for (int i = 0; i < CH; ++i) {
             const bool live = s[i] != -INFINITY;
             const float pj = live ? __expf(s[i] - m) : 0.f;
             l += pj;
-            if (!live) vreg[i] = make_uint4(0, 0, 0, 0);          // rows never written may hold anything, NaN included
-            const __nv_bfloat162* vv = (const __nv_bfloat162*)&vreg[i];
+            if (!live) vb[i] = make_uint4(0, 0, 0, 0);            // rows never written may hold anything, NaN included
+            const __nv_bfloat162* vv = (const __nv_bfloat162*)&vb[i];
 #pragma unroll
-            for (int t = 0; t < 4; ++t) {
-                const float2 f = __bfloat1622float2(vv[t]);
-                acc[2 * t] = fmaf(pj, f.x, acc[2 * t]);
-                acc[2 * t + 1] = fmaf(pj, f.y, acc[2 * t + 1]);
+            for (int u = 0; u < 4; ++u) {
+                const float2 f = __bfloat1622float2(vv[u]);
+                acc[2 * u] = fmaf(pj, f.x, acc[2 * u]);
+                acc[2 * u + 1] = fmaf(pj, f.y, acc[2 * u + 1]);
             }
+        }
+    };
+    {
+        uint4 k0[CH], v0[CH], k1[CH], v1[CH];
+        if (n_chunks > 0) issue(0, k0, v0);
+        for (int t = 0; t < n_chunks; t += 2) {
+            if (t + 1 < n_chunks) issue(t + 1, k1, v1);
+            consume(t, k0, v0);
+            if (t + 2 < n_chunks) issue(t + 2, k0, v0);
+            if (t + 1 < n_chunks) consume(t + 1, k1, v1);
         }
     }
     if (own_here && warp == 0) {
