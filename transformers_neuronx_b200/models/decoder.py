@@ -52,7 +52,7 @@ class DecoderModel:
         for p in self.all_parts():
             libs += [l for l in p.libraries if l in kbuild.SOURCES]
         if act_dtype == torch.float32:
-            libs = [l for l in libs if l not in ("gemm_tc", "attention_prefill", "attention_prefill_tc", "attention_decode")]
+            libs = [l for l in libs if l not in ("gemm_tc", "gemv", "attention_prefill", "attention_prefill_tc", "attention_decode")]
         return list(dict.fromkeys(libs))
 
     @property

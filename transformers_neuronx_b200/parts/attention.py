@@ -35,7 +35,7 @@ class PagedAttention(Mixer):
 
     @property
     def libraries(self):
-        libs = ["gemm_simt", "gemm_tc", "kv_cache", "attention_simt", "attention_prefill", "attention_prefill_tc", "attention_decode"]
+        libs = ["gemm_simt", "gemm_tc", "gemv", "kv_cache", "attention_simt", "attention_prefill", "attention_prefill_tc", "attention_decode"]
         if self.position is not None:
             libs += list(self.position.libraries)
         return tuple(libs)

@@ -86,7 +86,7 @@ class Head(Part):
 
     @property
     def libraries(self):
-        libs = ["layernorm", "gemm_simt", "gemm_tc"]
+        libs = ["layernorm", "gemm_simt", "gemm_tc", "gemv"]
         return tuple(libs)
 
     def tensor_specs(self):

@@ -13,7 +13,7 @@ _FUSED_ACTIVATIONS = ("relu",)
 
 class DenseFeedForward(FeedForward):
     graph_safe = True
-    libraries = ("gemm_simt", "gemm_tc")
+    libraries = ("gemm_simt", "gemm_tc", "gemv")
 
     def __init__(self, spec: DenseFeedForwardSpec):
         self.spec = spec
