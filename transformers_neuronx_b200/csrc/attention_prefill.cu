@@ -80,7 +80,7 @@ attention_prefill_kernel(const PrefillParams p) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // Work items are listed in ascending position: the last have the most keys.  Heaviest first, so
     // that the short ones fill the tail.
-    const int item = gridDim.x - 1 - blockIdx.x, h = blockIdx.y;
+    const int item = gridDim.y - 1 - blockIdx.y, h = blockIdx.x;      // heaviest tiles first, of all heads
     const int req = p.tile_req[item], q0 = p.tile_q0[item];
     const int qs = p.q_start[req], ql = p.q_len[req], ctx = p.ctx_len[req];
     const int rows = min(BQ, ql - q0);                       // valid query rows of this tile
@@ -265,7 +265,7 @@ int launch(const PrefillParams& p, int n_items, cudaStream_t stream) {
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    dim3 grid(n_items, p.n_heads);
+    dim3 grid(p.n_heads, n_items);        // heads vary fastest: CTAs start in the order of the work items
     return tnx_launch_pdl(attention_prefill_kernel<HEAD>, grid, dim3(WARPS * 32), smem, stream, p);
 }
 

@@ -115,7 +115,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     pdl_launch_dependents();
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int item = gridDim.x - 1 - blockIdx.x, h = blockIdx.y;      // heaviest tiles first
+    const int item = gridDim.y - 1 - blockIdx.y, h = blockIdx.x;      // heaviest tiles first, of all heads
     const int req = p.tile_req[item], q0 = p.tile_q0[item];
     const int qs = p.q_start[req], ql = p.q_len[req], ctx = p.ctx_len[req];
     const int rows = min(BQ, ql - q0);
@@ -391,5 +391,5 @@ TNX_EXPORT int tnx_attention_prefill_tc(const void* q, int q_stride, int n_rows_
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    return tnx_launch_pdl(attention_prefill_tc_kernel, dim3(n_items, n_heads), dim3(THREADS), SMEM_BYTES, stream, mq, mkv, p);
+    return tnx_launch_pdl(attention_prefill_tc_kernel, dim3(n_heads, n_items), dim3(THREADS), SMEM_BYTES, stream, mq, mkv, p);   // heads vary fastest
 }

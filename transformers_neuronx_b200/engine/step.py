@@ -161,13 +161,18 @@ class StepRunner:
             return a
 
         tok, pos, treq = padded(tokens, Np, 0), padded(positions, Np, 0), padded(token_request, Np, -1)
-        tile_req, tile_q0, decode_rows = [], [], []
+        tiles, decode_rows = [], []
         for r in range(R):
             if hb.q_len[r] == 1:
                 decode_rows.append(hb.q_start[r])
             else:
                 for q0 in range(0, hb.q_len[r], ops.ATTN_PREFILL_TILE):
-                    tile_req.append(r); tile_q0.append(q0)
+                    last_key = hb.ctx_len[r] + min(hb.q_len[r], q0 + ops.ATTN_PREFILL_TILE)
+                    tiles.append((last_key, r, q0))
+        # The attention kernels start their work items from the end of the list: tiles with more
+        # keys to read come later here, so that the long ones start first and the short ones fill in.
+        tiles.sort()
+        tile_req, tile_q0 = [t[1] for t in tiles], [t[2] for t in tiles]
         if pad_rows is not None:
             logit_rows = list(range(Np))
             decode_rows = list(range(Np))
