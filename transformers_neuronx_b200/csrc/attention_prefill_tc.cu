@@ -6,16 +6,17 @@
 //   S = Q K^T   : tcgen05.mma M=128 (queries) N=64 (keys) K=128 (head), Q and K from shared memory
 //                 (TMA, 128-byte swizzle, K-major), S in tensor memory (two buffers)
 //   softmax     : four warps, one thread per query row: the row of S is read from tensor memory,
-//                 masked, exponentiated with the running maximum (32-bit), the row of P written to
-//                 shared memory as bfloat16 in the swizzled layout the MMA expects
-//   O += P V    : tcgen05.mma M=128 N=128 (head) K=64 (keys); V is the [key][head] tile as it lies
+//                 masked, exponentiated with the running maximum (32-bit), the row of P written
+//                 back to tensor memory as bfloat16, over the scores it came from
+//   O += P V    : tcgen05.mma M=128 N=128 (head) K=64 (keys), P read from tensor memory (no trip
+//                 through shared memory and its proxy fence); V is the [key][head] tile as it lies
 //                 in the cache's pages, i.e. the "MN-major" form of the B operand; O stays in tensor
 //                 memory over all key tiles and is rescaled there when the running maximum grows
-// Warp 0 issues the TMA loads (three stages of K, two of V; the page numbers of the work item are
-// read into shared memory first), warp 1 the MMAs (one elected lane; the scores of tile j+1 are
-// issued before P V of tile j whenever their K tile is there, so that the tensor core works while
-// the softmax warps do), warps 2-5 are the softmax warps.  P of a tile is written over the K tile it
-// came from, which is dead by then.  Two CTAs fit on an SM.
+// Warp 0 issues the TMA loads (two stages of K, three of V, eight lanes a copy each; the page
+// numbers of the work item are read into shared memory first), one lane of warp 1 the MMAs of
+// O += P V and one lane of warp 6 those of S = Q K^T (the scores of tile j+1 are issued as soon as
+// their K tile is there and their buffer free, so that the tensor core works while the softmax
+// warps do), warps 2-5 are the softmax warps.  Two CTAs fit on an SM.
 // Every wait is bounded and reports through the error word.
 //
 // The cache's memory must hold finite numbers everywhere (it is allocated zeroed): rows of a page
@@ -31,7 +32,7 @@ constexpr int BQ = 128, BKV = 64, PAGE = 16;
 constexpr int ATOM_Q = BQ * 128;             // bytes of one 64-column half of the Q tile (16 KB)
 constexpr int ATOM_KV = BKV * 128;           // bytes of one 64-column half of a K or V tile (8 KB)
 constexpr int Q_BYTES = 2 * ATOM_Q, KV_BYTES = 2 * ATOM_KV;
-constexpr int K_STAGES = 3, V_STAGES = 2;
+constexpr int K_STAGES = 2, V_STAGES = 3;   // a K tile is free once its scores are done, a V tile a whole softmax later
 constexpr int MAX_PAGES_SMEM = 128;          // page numbers kept in shared memory (2,048 keys); beyond: read from global
 constexpr int TILE_BYTES = Q_BYTES + (K_STAGES + V_STAGES) * KV_BYTES;          // 112 KB
 // Everything lives in dynamic shared memory, the tiles first: with no static shared memory the
@@ -39,7 +40,9 @@ constexpr int TILE_BYTES = Q_BYTES + (K_STAGES + V_STAGES) * KV_BYTES;          
 // need (checked at run time), and two CTAs fit on an SM to the byte.
 constexpr int SMEM_BYTES = TILE_BYTES + 256 + MAX_PAGES_SMEM * 4;
 constexpr uint32_t TMEM_COLS = 256;          // S0 [0,64) S1 [64,128) O [128,256)
-constexpr int THREADS = 192;
+constexpr int THREADS = 224;
+constexpr int QK_WARP = 6;
+constexpr float RESCALE_STEP = 8.f;          // log2 units: see the softmax warps
 
 struct TcPrefillParams {
     const int* block_tables; int bt_stride;
@@ -68,6 +71,14 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
           "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
+// D (+)= A B with A read from tensor memory (lane = row, a column = two consecutive bf16 of K).
+__device__ __forceinline__ void umma_bf16_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -93,7 +104,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const TcPrefillParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sQ = smem;
-    uint8_t* sK = sQ + Q_BYTES;                   // [K_STAGES] K tiles; P of a tile overwrites its K tile
+    uint8_t* sK = sQ + Q_BYTES;                   // [K_STAGES] K tiles
     uint8_t* sV = sK + K_STAGES * KV_BYTES;       // [V_STAGES] V tiles
     uint64_t* bars = (uint64_t*)(smem + TILE_BYTES);
     uint64_t& q_full = bars[0];
@@ -156,95 +167,101 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
     if (warp == 0) {
         // ---- TMA producer ---------------------------------------------------------------------------
+        // A tile is eight copies of 2 KB (four pages x two 64-column halves).  One thread issuing
+        // sixteen of them per key tile was the slowest part of the kernel, so eight lanes issue one
+        // copy each; lane 0 waits for the stage and announces the bytes.
         if (lane == 0) {
             mbar_expect_tx(&q_full, Q_BYTES);
             tma_load_2d(sQ, &map_q, &q_full, h * D, qs + q0);
             tma_load_2d(sQ + ATOM_Q, &map_q, &q_full, h * D + 64, qs + q0);
-            for (int j = 0; j < n_tiles && ok; ++j) {
-                int pages[4], n_valid = 0;
-#pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    const int i = j * 4 + g;
-                    pages[g] = i < n_pages ? (i < MAX_PAGES_SMEM ? pages_s[i] : bt[first_page + i]) : -1;
-                    n_valid += pages[g] >= 0;
-                }
-                // K of tile j: its stage was last used by tile j - 3 (as K, then as P)
-                const int ks = j % K_STAGES, vs = j % V_STAGES;
-                ok = mbar_wait(&k_empty[ks], (uint32_t)(((j / K_STAGES) & 1) ^ 1), p.err, 31);
-                if (!ok) break;
-                mbar_expect_tx(&k_full[ks], (uint32_t)(n_valid * 2 * PAGE * 128));
-#pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    if (pages[g] < 0) continue;
-                    const int row_k = ((pages[g] * 2 + 0) * p.n_kv_heads + kvh) * PAGE;
-#pragma unroll
-                    for (int a = 0; a < 2; ++a)
-                        tma_load_2d(sK + ks * KV_BYTES + a * ATOM_KV + g * PAGE * 128, &map_kv, &k_full[ks], a * 64, row_k);
-                }
-                ok = mbar_wait(&v_empty[vs], (uint32_t)(((j / V_STAGES) & 1) ^ 1), p.err, 40);
-                if (!ok) break;
-                mbar_expect_tx(&v_full[vs], (uint32_t)(n_valid * 2 * PAGE * 128));
-#pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    if (pages[g] < 0) continue;
-                    const int row_v = ((pages[g] * 2 + 1) * p.n_kv_heads + kvh) * PAGE;
-#pragma unroll
-                    for (int a = 0; a < 2; ++a)
-                        tma_load_2d(sV + vs * KV_BYTES + a * ATOM_KV + g * PAGE * 128, &map_kv, &v_full[vs], a * 64, row_v);
-                }
+        }
+        const int g = (lane >> 1) & 3, a = lane & 1;          // this lane's page of the tile and half of the head
+        // the page this lane copies for key tile j (-1 where the context ends before), and how many pages exist
+        auto tile_page = [&](int j, int& n_valid) {
+            const int first = j * 4;
+            n_valid = min(4, max(0, n_pages - first));
+            const int i = first + g;
+            return i < n_pages ? (i < MAX_PAGES_SMEM ? pages_s[i] : bt[first_page + i]) : -1;
+        };
+        auto load_tile = [&](int j, int which, uint8_t* stage, uint64_t* full, uint64_t* empty, uint32_t parity, int code) {
+            int n_valid;
+            const int page = tile_page(j, n_valid);
+            int good = 1;
+            if (lane == 0) {
+                good = mbar_wait(empty, parity, p.err, code) ? 1 : 0;
+                if (good) mbar_expect_tx(full, (uint32_t)(n_valid * 2 * PAGE * 128));
             }
+            good = __shfl_sync(0xffffffffu, good, 0);
+            if (good && lane < 8 && page >= 0) {
+                const int row = ((page * 2 + which) * p.n_kv_heads + kvh) * PAGE;
+                tma_load_2d(stage + a * ATOM_KV + g * PAGE * 128, &map_kv, full, a * 64, row);
+            }
+            return good != 0;
+        };
+        auto load_k = [&](int j) {
+            const int ks = j % K_STAGES;                     // last used by tile j - K_STAGES
+            return load_tile(j, 0, sK + ks * KV_BYTES, &k_full[ks], &k_empty[ks], (uint32_t)(((j / K_STAGES) & 1) ^ 1), 31);
+        };
+        auto load_v = [&](int j) {
+            const int vs = j % V_STAGES;
+            return load_tile(j, 1, sV + vs * KV_BYTES, &v_full[vs], &v_empty[vs], (uint32_t)(((j / V_STAGES) & 1) ^ 1), 40);
+        };
+        // Keys run K_STAGES tiles ahead of the values: the scores of a tile are wanted a whole
+        // softmax earlier than its values, and a K stage is free as soon as its scores are done.
+        for (int j = 0; j < K_STAGES && j < n_tiles && ok; ++j) ok = load_k(j);
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            ok = load_v(j);
+            if (ok && j + K_STAGES < n_tiles) ok = load_k(j + K_STAGES);
         }
     } else if (warp == 1) {
-        // ---- MMA issuer -----------------------------------------------------------------------------
+        // ---- MMA issuer of O += P V ---------------------------------------------------------------------
+        // (The scores have an issuing thread of their own, warp 6: one thread issuing the twelve MMAs
+        // and four commits of a key tile was the slowest part of the kernel.)
         if (lane == 0) {
-            constexpr uint32_t idesc_qk = idesc_attn(BKV, 0), idesc_pv = idesc_attn(D, 1);
+            constexpr uint32_t idesc_pv = idesc_attn(D, 1);
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                ok = mbar_wait(&p_full, (uint32_t)(j & 1), p.err, 36);
+                if (ok) ok = mbar_wait(&v_full[j % V_STAGES], (uint32_t)((j / V_STAGES) & 1), p.err, 41);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t p_tmem = tmem_base + (uint32_t)((j & 1) * BKV);         // P lies over the scores it came from
+                const uint32_t v_addr = smem_u32(sV + (j % V_STAGES) * KV_BYTES);
+#pragma unroll
+                for (int k = 0; k < BKV / 16; ++k) {
+                    // 16 keys further: 8 columns of P (two bf16 each), 16 rows of V
+                    const uint64_t bdesc = smem_desc_sw128_mn(v_addr + k * 16 * 128, ATOM_KV);
+                    umma_bf16_a_tmem(tmem_base + 128, p_tmem + (uint32_t)(k * 8), bdesc, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(&o_full);
+                umma_commit(&v_empty[j % V_STAGES]);          // the V tile is free, and so is P's place in the score buffer
+            }
+        }
+    } else if (warp == QK_WARP) {
+        // ---- MMA issuer of S = Q K^T ----------------------------------------------------------------------
+        // Tile n goes to score buffer n & 1, which must be free twice over: the softmax warps have
+        // read the scores of tile n - 2 (s_empty), and P V of tile n - 2, whose P lay in the same
+        // columns, has finished (v_empty of that tile's V stage; its next completion is P V of tile
+        // n + 1, which cannot come before these scores).
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = idesc_attn(BKV, 0);
             const uint32_t q_addr = smem_u32(sQ);
-            auto issue_qk = [&](int j) {
-                const uint32_t k_addr = smem_u32(sK + (j % K_STAGES) * KV_BYTES);
-                const uint32_t d_tmem = tmem_base + (uint32_t)((j & 1) * BKV);
+            ok = mbar_wait(&q_full, 0, p.err, 32);
+            for (int n = 0; n < n_tiles && ok; ++n) {
+                ok = mbar_wait(&k_full[n % K_STAGES], (uint32_t)((n / K_STAGES) & 1), p.err, 33);
+                if (ok) ok = mbar_wait(&s_empty[n & 1], (uint32_t)(((n >> 1) & 1) ^ 1), p.err, 35);
+                if (ok && n >= 2) ok = mbar_wait(&v_empty[(n - 2) % V_STAGES], (uint32_t)(((n - 2) / V_STAGES) & 1), p.err, 34);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t k_addr = smem_u32(sK + (n % K_STAGES) * KV_BYTES);
+                const uint32_t d_tmem = tmem_base + (uint32_t)((n & 1) * BKV);
 #pragma unroll
                 for (int k = 0; k < D / 16; ++k) {
                     const uint64_t adesc = smem_desc_sw128(q_addr + (k >> 2) * ATOM_Q + (k & 3) * 32);
                     const uint64_t bdesc = smem_desc_sw128(k_addr + (k >> 2) * ATOM_KV + (k & 3) * 32);
                     umma_bf16(d_tmem, adesc, bdesc, idesc_qk, k > 0 ? 1u : 0u);
                 }
-                umma_commit(&s_full[j & 1]);
-            };
-            ok = mbar_wait(&q_full, 0, p.err, 32);
-            if (ok) ok = mbar_wait(&k_full[0], 0, p.err, 33);
-            if (ok) { tc_fence_after(); issue_qk(0); }
-            for (int j = 0; j < n_tiles && ok; ++j) {
-                const int n = j + 1;
-                const uint32_t kf_ph = (uint32_t)((n / K_STAGES) & 1), se_ph = (uint32_t)(((n >> 1) & 1) ^ 1);
-                bool next_issued = n >= n_tiles;
-                // the scores of the next tile first, if its K tile has landed and its S buffer is free
-                if (!next_issued && mbar_try_wait(&k_full[n % K_STAGES], kf_ph) && mbar_try_wait(&s_empty[n & 1], se_ph)) {
-                    tc_fence_after();
-                    issue_qk(n);
-                    next_issued = true;
-                }
-                ok = mbar_wait(&p_full, (uint32_t)(j & 1), p.err, 36);
-                if (ok) ok = mbar_wait(&v_full[j % V_STAGES], (uint32_t)((j / V_STAGES) & 1), p.err, 41);
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t p_addr = smem_u32(sK + (j % K_STAGES) * KV_BYTES);      // P lies over K of this tile
-                const uint32_t v_addr = smem_u32(sV + (j % V_STAGES) * KV_BYTES);
-#pragma unroll
-                for (int k = 0; k < BKV / 16; ++k) {
-                    const uint64_t adesc = smem_desc_sw128(p_addr + k * 32);
-                    const uint64_t bdesc = smem_desc_sw128_mn(v_addr + k * 16 * 128, ATOM_KV);
-                    umma_bf16(tmem_base + 128, adesc, bdesc, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
-                }
-                umma_commit(&o_full);
-                umma_commit(&k_empty[j % K_STAGES]);
-                umma_commit(&v_empty[j % V_STAGES]);
-                if (!next_issued) {
-                    ok = mbar_wait(&k_full[n % K_STAGES], kf_ph, p.err, 34);
-                    if (ok) ok = mbar_wait(&s_empty[n & 1], se_ph, p.err, 35);
-                    if (!ok) break;
-                    tc_fence_after();
-                    issue_qk(n);
-                }
+                umma_commit(&s_full[n & 1]);
+                umma_commit(&k_empty[n % K_STAGES]);          // the K tile is free once these MMAs have read it
             }
         }
     } else {
@@ -281,22 +298,31 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     if (!keep) s[i] = -INFINITY;
                 }
             }
-            float mx = -INFINITY;
+            // the row's maximum and sum as four chains each: no instruction waits for the one before it
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int i = 0; i < 64; ++i) mx = fmaxf(mx, s[i]);
-            const float m_new = fmaxf(m_run, mx);
-            const float m_scaled = (m_new == -INFINITY) ? 0.f : m_new * p.scale_log2;
-            const float corr = (m_run == -INFINITY) ? 0.f : ex2_approx(m_run * p.scale_log2 - m_scaled);
-            float sum = 0.f;
+            for (int i = 0; i < 64; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], s[i]);
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            // The reference the exponentials are taken against moves up only when the maximum has
+            // grown by more than 2^RESCALE_STEP: until then P holds values up to 2^RESCALE_STEP
+            // instead of 1, which 32-bit sums and bfloat16 products carry as well, and O (which a
+            // move of the reference has to rescale in tensor memory) is left alone.
+            const float mx_scaled = (mx == -INFINITY) ? -INFINITY : mx * p.scale_log2;
+            const bool grow = mx_scaled > m_run + RESCALE_STEP;            // m_run: the reference, in log2 units
+            const float m_new = grow ? mx_scaled : m_run;
+            const float m_scaled = (m_new == -INFINITY) ? 0.f : m_new;
+            const float corr = (!grow || m_run == -INFINITY) ? (grow ? 0.f : 1.f) : ex2_approx(m_run - m_new);
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
             uint32_t packed[32];
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
                 const float p0 = ex2_approx(fmaf(s[2 * i], p.scale_log2, -m_scaled));
                 const float p1 = ex2_approx(fmaf(s[2 * i + 1], p.scale_log2, -m_scaled));
-                sum += p0 + p1;
+                sum4[i & 3] += p0 + p1;
                 __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
                 packed[i] = *(uint32_t*)&h2;
             }
+            const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             l_run = l_run * corr + sum;
             m_run = m_new;
             if (j > 0) {
@@ -317,12 +343,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     tmem_st_wait();
                 }
             }
-            // this row of P -> shared memory, 16-byte chunks XOR-swizzled as the MMA reads them
-            uint8_t* prow = sK + (j % K_STAGES) * KV_BYTES + r * 128;
-#pragma unroll
-            for (int c = 0; c < 8; ++c)
-                *(uint4*)(prow + ((c ^ (r & 7)) << 4)) = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            // this row of P -> tensor memory, over the first half of the scores it came from (which
+            // are in registers): 64 bfloat16 in 32 columns.  The MMA warp issues P V of this tile
+            // before the scores of tile j + 2 (which go to this buffer), and the tensor core works
+            // in the order of issue.
+            tmem_st32(lane_base + (uint32_t)(b * BKV), packed);
+            tmem_st_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&p_full);
