@@ -38,7 +38,12 @@ CONFIG_D = dict(vocab_size=2003, hidden_size=256, num_hidden_layers=2, num_atten
                 max_position_embeddings=600, word_embed_proj_dim=256, do_layer_norm_before=True, enable_bias=True,
                 layer_norm_elementwise_affine=True, layer_norm_eps=1e-5, activation_function="relu", init_std=0.03,
                 architectures=["OPTForCausalLM"], model_type="opt")
-CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C, "D": CONFIG_D}
+# Head size 64 (the size of the small OPT models), three heads, post-norm, a projected embedding.
+CONFIG_E = dict(vocab_size=1501, hidden_size=192, num_hidden_layers=2, num_attention_heads=3, ffn_dim=264,
+                max_position_embeddings=420, word_embed_proj_dim=96, do_layer_norm_before=False, enable_bias=True,
+                layer_norm_elementwise_affine=True, layer_norm_eps=1e-5, activation_function="relu", init_std=0.03,
+                architectures=["OPTForCausalLM"], model_type="opt")
+CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C, "D": CONFIG_D, "E": CONFIG_E}
 
 # Largest allowed |engine - plain| as a fraction of the largest |plain logit| of the compared rows.
 # float32: both sides compute in 32-bit and differ by the order of additions only.

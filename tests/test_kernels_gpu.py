@@ -476,10 +476,10 @@ def test_sampling_large_vocabulary_top_k():
 
 @pytest.mark.parametrize("n_heads,n_kv", [(4, 2), (3, 3), (8, 1)])
 @pytest.mark.parametrize("window", [None, 45, 200])
-def test_attention_prefill_tc(n_heads, n_kv, window):
-    """The tcgen05 prefill kernel (head size 128).  Unwritten rows of pages hold a large finite number:
-    they are loaded with their page and must be weighted by exactly zero."""
-    d = 128
+@pytest.mark.parametrize("d", [128, 64])
+def test_attention_prefill_tc(n_heads, n_kv, window, d):
+    """The tcgen05 prefill kernel (head sizes 128 and 64).  Unwritten rows of pages hold a large finite
+    number: they are loaded with their page and must be weighted by exactly zero."""
     lens = [(0, 2), (0, 64), (0, 129), (30, 7), (64, 130), (15, 17), (200, 300), (5, 1), (1000, 260)]
     case = PagedCase(lens, n_heads, n_kv, d, torch.bfloat16, seed=77, poison=3.0e4)
     scale = 1.0 / math.sqrt(d)
@@ -496,9 +496,10 @@ def test_attention_prefill_tc(n_heads, n_kv, window):
     assert float(out[~keep].float().abs().max()) == 0.0
 
 
-def test_attention_prefill_tc_more_pages_than_fit_in_shared_memory():
+@pytest.mark.parametrize("d", [128, 64])
+def test_attention_prefill_tc_more_pages_than_fit_in_shared_memory(d):
     """A context of more than 2,048 keys: the page numbers beyond the first 128 are read from global memory."""
-    d, n_heads = 128, 2
+    n_heads = 2
     case = PagedCase([(2900, 150), (0, 300)], n_heads, n_heads, d, torch.bfloat16, seed=5, poison=1.0e4)
     scale = 1.0 / math.sqrt(d)
     out = torch.zeros(case.N, n_heads * d, dtype=torch.bfloat16, device=DEV)

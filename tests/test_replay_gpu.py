@@ -140,6 +140,16 @@ def test_head_size_128_long_contexts(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+def test_head_size_64(dtype):
+    """Configuration E: head size 64 (the tcgen05 attention kernel's other size), post-norm blocks."""
+    tiny = TinyModel("E", seed=23)
+    reqs = {f"e{i}": tiny.random_ids(n, seed=600 + i) for i, n in enumerate([410, 130, 257, 66, 300])}
+    steps, peak = mixed_steps(reqs, chunk_sizes=(130, 2, 64, 17, 150), decode_tail=9, max_live=3)
+    res = run_trace_inprocess(tiny.folder, dtype, steps, peak)
+    compare_trace(tiny, reqs, steps, res, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_decode_steps_where_not_every_request_wants_logits(dtype):
     """Single-token steps (replayed as CUDA graphs) in which some entries ask for nothing."""
     tiny = TinyModel("A", seed=17)

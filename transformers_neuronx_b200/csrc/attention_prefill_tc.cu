@@ -27,19 +27,23 @@
 
 namespace {
 
-constexpr int D = 128;                       // head size
 constexpr int BQ = 128, BKV = 64, PAGE = 16;
-constexpr int ATOM_Q = BQ * 128;             // bytes of one 64-column half of the Q tile (16 KB)
-constexpr int ATOM_KV = BKV * 128;           // bytes of one 64-column half of a K or V tile (8 KB)
-constexpr int Q_BYTES = 2 * ATOM_Q, KV_BYTES = 2 * ATOM_KV;
-constexpr int K_STAGES = 2, V_STAGES = 3;   // a K tile is free once its scores are done, a V tile a whole softmax later
+constexpr int ATOM_Q = BQ * 128;             // bytes of one 64-column slice of the Q tile (16 KB)
+constexpr int ATOM_KV = BKV * 128;           // bytes of one 64-column slice of a K or V tile (8 KB)
 constexpr int MAX_PAGES_SMEM = 128;          // page numbers kept in shared memory (2,048 keys); beyond: read from global
-constexpr int TILE_BYTES = Q_BYTES + (K_STAGES + V_STAGES) * KV_BYTES;          // 112 KB
-// Everything lives in dynamic shared memory, the tiles first: with no static shared memory the
-// dynamic part starts at the CTA's shared window, which is 1024-byte aligned as the swizzled tiles
-// need (checked at run time), and two CTAs fit on an SM to the byte.
-constexpr int SMEM_BYTES = TILE_BYTES + 256 + MAX_PAGES_SMEM * 4;
-constexpr uint32_t TMEM_COLS = 256;          // S0 [0,64) S1 [64,128) O [128,256)
+// Head size D (64 or 128), KS stages of K tiles and VS of V tiles.  Everything lives in dynamic
+// shared memory, the tiles first: with no static shared memory the dynamic part starts at the
+// CTA's shared window, which is 1024-byte aligned as the swizzled tiles need (checked at run time).
+// D = 128: Q 32 KB + (2 + 3) x 16 KB, so that two CTAs fit on an SM to the byte; D = 64: Q 16 KB +
+// (3 + 4) x 8 KB, stages enough to cover the time a tile takes to arrive.
+template <int D, int KS, int VS>
+struct Layout {
+    static constexpr int SLICES = D / 64;                        // 64-column slices of a row
+    static constexpr int Q_BYTES = SLICES * ATOM_Q, KV_BYTES = SLICES * ATOM_KV;
+    static constexpr int TILE_BYTES = Q_BYTES + (KS + VS) * KV_BYTES;
+    static constexpr int SMEM_BYTES = TILE_BYTES + 256 + MAX_PAGES_SMEM * 4;
+};
+constexpr uint32_t TMEM_COLS = 256;          // S0 [0,64) S1 [64,128) O [128,128 + D)
 constexpr int THREADS = 224;
 constexpr int QK_WARP = 6;
 constexpr float RESCALE_STEP = 8.f;          // log2 units: see the softmax warps
@@ -99,9 +103,12 @@ __host__ __device__ constexpr uint32_t idesc_attn(int n, int b_mn) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
 
+template <int D, int K_STAGES, int V_STAGES>
 __global__ void __launch_bounds__(THREADS, 2)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                             const TcPrefillParams p) {
+    using L = Layout<D, K_STAGES, V_STAGES>;
+    constexpr int SLICES = L::SLICES, Q_BYTES = L::Q_BYTES, KV_BYTES = L::KV_BYTES, TILE_BYTES = L::TILE_BYTES;
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sQ = smem;
     uint8_t* sK = sQ + Q_BYTES;                   // [K_STAGES] K tiles
@@ -167,13 +174,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
     if (warp == 0) {
         // ---- TMA producer ---------------------------------------------------------------------------
-        // A tile is eight copies of 2 KB (four pages x two 64-column halves).  One thread issuing
+        // A tile is up to eight copies of 2 KB (four pages x the 64-column slices of the head).  One thread issuing
         // sixteen of them per key tile was the slowest part of the kernel, so eight lanes issue one
         // copy each; lane 0 waits for the stage and announces the bytes.
         if (lane == 0) {
             mbar_expect_tx(&q_full, Q_BYTES);
-            tma_load_2d(sQ, &map_q, &q_full, h * D, qs + q0);
-            tma_load_2d(sQ + ATOM_Q, &map_q, &q_full, h * D + 64, qs + q0);
+#pragma unroll
+            for (int sl = 0; sl < SLICES; ++sl) tma_load_2d(sQ + sl * ATOM_Q, &map_q, &q_full, h * D + sl * 64, qs + q0);
         }
         const int g = (lane >> 1) & 3, a = lane & 1;          // this lane's page of the tile and half of the head
         // the page this lane copies for key tile j (-1 where the context ends before), and how many pages exist
@@ -189,10 +196,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             int good = 1;
             if (lane == 0) {
                 good = mbar_wait(empty, parity, p.err, code) ? 1 : 0;
-                if (good) mbar_expect_tx(full, (uint32_t)(n_valid * 2 * PAGE * 128));
+                if (good) mbar_expect_tx(full, (uint32_t)(n_valid * SLICES * PAGE * 128));
             }
             good = __shfl_sync(0xffffffffu, good, 0);
-            if (good && lane < 8 && page >= 0) {
+            if (good && lane < 8 && a < SLICES && page >= 0) {
                 const int row = ((page * 2 + which) * p.n_kv_heads + kvh) * PAGE;
                 tma_load_2d(stage + a * ATOM_KV + g * PAGE * 128, &map_kv, full, a * 64, row);
             }
@@ -390,32 +397,40 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
 }
 
+template <int D, int KS, int VS>
+int launch_tc(const CUtensorMap& mq, const CUtensorMap& mkv, const TcPrefillParams& p, int n_heads, int n_items, cudaStream_t stream) {
+    constexpr int smem = Layout<D, KS, VS>::SMEM_BYTES;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<D, KS, VS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    return tnx_launch_pdl(attention_prefill_tc_kernel<D, KS, VS>, dim3(n_heads, n_items), dim3(THREADS), smem, stream, mq, mkv, p);   // heads vary fastest
+}
+
 }  // namespace
 
-// Same arguments as tnx_attention_prefill plus the error word; head_dim must be 128 and n_rows_q is
-// the number of rows of the q / out buffers (for the TMA descriptor).
+// Same arguments as tnx_attention_prefill plus the error word; head_dim must be 64 or 128 and
+// n_rows_q is the number of rows of the q / out buffers (for the TMA descriptor).
 TNX_EXPORT int tnx_attention_prefill_tc(const void* q, int q_stride, int n_rows_q, const void* cache, long long cache_rows,
                                         const int* block_tables, int bt_stride, const int* tile_req, const int* tile_q0,
                                         const int* q_start, const int* q_len, const int* ctx_len, void* out,
                                         int out_stride, int n_items, int n_heads, int n_kv_heads, int head_dim,
                                         int page_size, int window, float scale, int* err_word, cudaStream_t stream) {
     if (n_items <= 0) return 0;
-    if (head_dim != D || page_size != PAGE || n_kv_heads <= 0 || n_heads % n_kv_heads || q_stride % 8 || out_stride % 8 ||
-        ((uintptr_t)q & 15) || ((uintptr_t)cache & 15) || ((uintptr_t)out & 15) || cache_rows > 0x7fffffffLL || !err_word)
+    if ((head_dim != 64 && head_dim != 128) || page_size != PAGE || n_kv_heads <= 0 || n_heads % n_kv_heads || q_stride % 8 ||
+        out_stride % 8 || ((uintptr_t)q & 15) || ((uintptr_t)cache & 15) || ((uintptr_t)out & 15) ||
+        cache_rows > 0x7fffffffLL || !err_word)
         return TNX_ERR_UNSUPPORTED;
     CUtensorMap mq, mkv;
-    if (!make_map(&mq, q, n_rows_q, n_heads * D, q_stride, BQ)) return TNX_ERR_UNSUPPORTED;
-    if (!make_map(&mkv, cache, (int)cache_rows, D, D, PAGE)) return TNX_ERR_UNSUPPORTED;
+    if (!make_map(&mq, q, n_rows_q, n_heads * head_dim, q_stride, BQ)) return TNX_ERR_UNSUPPORTED;
+    if (!make_map(&mkv, cache, (int)cache_rows, head_dim, head_dim, PAGE)) return TNX_ERR_UNSUPPORTED;
     TcPrefillParams p;
     p.block_tables = block_tables; p.bt_stride = bt_stride; p.tile_req = tile_req; p.tile_q0 = tile_q0;
     p.q_start = q_start; p.q_len = q_len; p.ctx_len = ctx_len; p.out = (bf16*)out; p.out_stride = out_stride;
     p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.window = window; p.scale_log2 = scale * 1.4426950408889634f;
     p.err = err_word;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
-    return tnx_launch_pdl(attention_prefill_tc_kernel, dim3(n_heads, n_items), dim3(THREADS), SMEM_BYTES, stream, mq, mkv, p);   // heads vary fastest
+    if (head_dim == 128) return launch_tc<128, 2, 3>(mq, mkv, p, n_heads, n_items, stream);
+    return launch_tc<64, 3, 4>(mq, mkv, p, n_heads, n_items, stream);
 }
