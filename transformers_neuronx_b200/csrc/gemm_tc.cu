@@ -8,9 +8,15 @@
 //   normal (many tokens): P = A (128 tokens), Q = W (BN = 128 features)
 //   swapped (few tokens): P = W (128 features), Q = A (BN = 16/32/64 tokens): the weight matrix,
 //     which is what a decode step has to stream from HBM, fills the 128-row operand and nothing
-//     is wasted on padding tokens.  Few output tiles -> K is split over several CTAs; each writes
-//     its 32-bit partial tile to scratch memory and the CTA that finishes last adds the partials in
-//     split order (a fixed order) and applies the epilogue.
+//     is wasted on padding tokens.  Few output tiles -> K is split over several CTAs.  With 2, 4
+//     or 8 splits the CTAs of a tile form a thread-block cluster: each writes its 32-bit partial
+//     tile to its own shared memory and then adds one band of rows over all CTAs' tiles (split
+//     order, a fixed order) through distributed shared memory and applies the epilogue.  With
+//     other split counts (a caller's choice) the partial tiles go to scratch memory and the CTA
+//     that finishes last adds them, in the same order.
+// Many tokens have two further kernels below: persistent CTAs with 128 x 256 tiles, and CTA pairs
+// (tcgen05 cta_group::2) with 256 x 256 tiles, whose last, partly filled round of tiles can be
+// shared out over all pairs by K blocks.
 //
 // Warp roles: warp 0 issues TMA loads, warp 1 allocates tensor memory and issues the MMAs (one
 // elected lane), warps 2-5 read the accumulators (tcgen05.ld, one 32-lane quadrant each) and write
