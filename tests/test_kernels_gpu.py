@@ -51,7 +51,8 @@ def test_gemm_simt_rows_do_not_depend_on_the_batch():
     assert torch.equal(full[33:34], one)                 # bit for bit
 
 
-TC_SHAPES = [(1, 128, 64), (3, 96, 320), (8, 256, 2112), (40, 4096, 4096), (16, 4096, 1024), (17, 1000, 96), (33, 200, 136), (64, 512, 4096),
+TC_SHAPES = [(1, 128, 64), (3, 96, 320), (8, 256, 2112), (40, 4096, 4096), (130, 4096, 16384), (100, 520, 8200),
+             (250, 12288, 4096), (16, 4096, 1024), (17, 1000, 96), (33, 200, 136), (64, 512, 4096),
              (65, 384, 256), (128, 128, 64), (200, 1000, 328), (300, 520, 1032), (2048, 768, 512),
              (1024, 4096, 512), (1000, 4000, 328), (300, 9000, 136), (513, 7100, 72), (520, 7102, 72), (2100, 2300, 1096),
              (1792, 2048, 16384), (2000, 3300, 8200), (1100, 4090, 4096)]     # the last three share tiles out by K blocks

@@ -1033,12 +1033,6 @@ static ManyTokensPlan plan_many_tokens(int M, int N, int K, int sms) {
     // Estimated times in microseconds, from measurements at 256..2,048 tokens: a K block of a
     // 256 x 256 pair tile takes 0.45 us, of a 128 x 128 single tile 0.38 us; start and drain 8 / 6 us.
     const float t_single = (float)((tiles_m * ((N + 127) / 128) + sms - 1) / sms) * kb * 0.38f + 6.f;
-    if (M < 256) {
-        // Few 128 x 256 tiles would leave SMs idle: 128 x 128 tiles, one per CTA, fill the GPU better
-        // then; otherwise the single-CTA persistent kernel with 128 x 256 tiles.
-        if (tiles_m * ((N + 255) / 256) * 4 < sms * 3) r.kind = 0;
-        return r;
-    }
     const int G = sms / 2;
     const int n_tiles = ((M + 255) / 256) * ((N + 255) / 256);          // 256 x 256 tiles of the paired kernel
     const int full = n_tiles / G, rest = n_tiles % G;
@@ -1057,7 +1051,17 @@ static ManyTokensPlan plan_many_tokens(int M, int N, int K, int sms) {
         const float exposed = full > 0 ? (reduce > t_tile ? reduce - t_tile : 0.f) : reduce;
         t_share = ((float)full + (float)rest / sk_pairs) * t_tile + 8.f + 1.3f * ((sk_pairs + rest) * 0.1f + exposed);
     }
-    if (t_single <= t_pair && t_single <= t_share) { r.kind = 0; return r; }
+    if (M < 256) {
+        // 65..255 tokens: the weights are streamed once and the tensor cores idle.  Few 128 x 256
+        // tiles would leave SMs idle: 128 x 128 tiles, one per CTA, fill the GPU better then;
+        // otherwise the single-CTA persistent kernel with 128 x 256 tiles (a K block 0.45 us).  The
+        // paired kernel (half of whose 256 token rows may be empty) wins where K is long and the
+        // tiles are few, by sharing them out.
+        const int tiles_p = tiles_m * ((N + 255) / 256);
+        const bool single = tiles_p * 4 < sms * 3;
+        const float t_here = single ? t_single : (float)((tiles_p + sms - 1) / sms) * kb * 0.45f + 8.f;
+        if (t_here <= t_pair && t_here <= t_share) { r.kind = single ? 0 : 2; return r; }
+    } else if (t_single <= t_pair && t_single <= t_share) { r.kind = 0; return r; }
     r.kind = 1;
     if (t_share < t_pair) { r.pairs = G; r.sk_tiles = rest; r.sk_pairs = sk_pairs; }
     else r.pairs = n_tiles < G ? n_tiles : G;
