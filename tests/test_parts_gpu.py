@@ -263,6 +263,79 @@ def test_toy_parts_are_registered_built_and_stepped():
     assert runner.cache.free_pages() == [12] and runner.cache.slots.num_free == 3
 
 
+def test_toy_feed_forward_with_routing():
+    """A feed-forward that routes each token to one of three experts (router logits in 32-bit, top-1),
+    defined here, registered and stepped in portions beside the framework's attention."""
+    from transformers_neuronx_b200.engine import StepEntry, StepRunner, build_model
+    from transformers_neuronx_b200.parts import FeedForward, register_feed_forward, to_device
+    from transformers_neuronx_b200.parts.spec import (AttentionSpec, EmbeddingSpec, HeadSpec, LayerSpec, LinearSpec,
+                                                      ModelSpec, NormSpec, PositionSpec, ScheduleEntry)
+    from transformers_neuronx_b200.weights import TensorSpec
+    H, V, F, E, heads = 48, 61, 40, 3, 3
+
+    class RoutedFeedForward(FeedForward):
+        def __init__(self, spec):
+            self.spec = spec
+
+        def tensor_specs(self):
+            return [TensorSpec("moe.router", (E, H)), TensorSpec("moe.up", (E * F, H)), TensorSpec("moe.down", (E * H, F))]
+
+        def load(self, tensors, device, act_dtype):
+            self.router = to_device(tensors["moe.router"], device, torch.float32)
+            self.up = to_device(tensors["moe.up"], device, torch.float32).view(E, F, H)
+            self.down = to_device(tensors["moe.down"], device, torch.float32).view(E, H, F)
+
+        def forward(self, ctx, h, residual):
+            x = h.float()
+            expert = (x @ self.router.t()).argmax(dim=-1)                  # one expert per token
+            for e in range(E):
+                rows = (expert == e).nonzero().flatten()
+                if rows.numel():
+                    residual[rows] += torch.relu(x[rows] @ self.up[e].t()) @ self.down[e].t()
+
+    class RoutedSpec:
+        kind = "toy_routed"
+
+    register_feed_forward("toy_routed", RoutedFeedForward)
+    g = torch.Generator().manual_seed(11)
+    rn = lambda *s: (torch.randn(*s, generator=g) / math.sqrt(s[-1])).bfloat16()
+    t = {"emb": torch.randn(V, H, generator=g).bfloat16(), "moe.router": rn(E, H) * 4, "moe.up": rn(E * F, H),
+         "moe.down": rn(E * H, F)}
+    for n in "qkvo":
+        t[f"att.{n}"] = rn(H, H)
+    t["head"] = t["emb"]
+    norm = lambda: NormSpec("layer_norm", H, 1e-5)
+    att = AttentionSpec("attention", H, heads, heads, H // heads, 1 / math.sqrt(H // heads),
+                        q=LinearSpec(H, H, "att.q"), k=LinearSpec(H, H, "att.k"), v=LinearSpec(H, H, "att.v"),
+                        out=LinearSpec(H, H, "att.o"))
+    spec = ModelSpec(H, V, 128, EmbeddingSpec("emb", V, H, None, PositionSpec("none")),
+                     (LayerSpec("pre_norm", norm(), att, norm(), RoutedSpec()),), (ScheduleEntry(0, 0),),
+                     HeadSpec("head", V, H, tied_to="emb", final_norm=norm()))
+    model = build_model(spec, t, "float32", verbose=False)
+    ids = torch.randint(0, V, (70,), generator=g).tolist()
+
+    w = {k: v.float() for k, v in t.items()}
+    x = w["emb"][torch.tensor(ids)]
+    T, d = len(ids), H // heads
+    hh = P.layer_norm(x, None, None)
+    q, k, v = ((hh @ w[f"att.{n}"].t()).view(T, heads, d).transpose(0, 1) for n in "qkv")
+    p = P.masked_softmax(P.attention_scores(q, k, d), P.causal_mask(T, T, 0, None)[None])
+    x = x + P.attention_context(p, v).transpose(0, 1).reshape(T, H) @ w["att.o"].t()
+    hh = P.layer_norm(x, None, None)
+    expert = (hh @ w["moe.router"].t()).argmax(dim=-1)
+    up, down = w["moe.up"].view(E, F, H), w["moe.down"].view(E, H, F)
+    x = x + torch.stack([torch.relu(hh[i] @ up[e].t()) @ down[e].t() for i, e in enumerate(expert.tolist())])
+    want = P.layer_norm(x, None, None) @ w["emb"].t()
+    assert len(set(expert.tolist())) == E, "the test's weights should use every expert"
+
+    runner = StepRunner(model, 16, 8, 1, 128)
+    runner.add_request("r")
+    got, pos = [], 0
+    for n in (33, 2, 1, 1, 20, 13):
+        got.append(runner.step([StepEntry("r", ids[pos:pos + n], list(range(n)))]).cpu()); pos += n
+    assert rel_err(torch.cat(got), want) <= 5e-5
+
+
 def test_schedule_may_share_a_cache():
     """Two schedule entries with one cache id: the second reads what the first wrote (and writes the
     same rows again); entries with different needs must not share."""
