@@ -51,6 +51,12 @@ CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C, "D": CONFIG_D, "E": CONF
 TOLERANCE = {"float32": 2e-5, "bfloat16": 2e-2}
 
 
+def rel_error(got, want) -> float:
+    """Largest |got - want| as a fraction of the largest |want| (both moved to the CPU in 32-bit)."""
+    got, want = got.detach().float().cpu(), want.detach().float().cpu()
+    return float((got - want).abs().max() / want.abs().max().clamp_min(1e-30))
+
+
 class TinyModel:
     """A model folder with random weights plus what the tests need to know about it."""
 
