@@ -1,7 +1,6 @@
 #!/usr/bin/env python3
 """Decode and prefill throughput of the engine on one B200, on the layer sizes of OPT-6.7B with
-random weights (the sizes come from BASELINE.json's configs[2]; nothing is published for them by
-the reference, so vs_baseline is null).
+random weights (the reference publishes no number for them, so vs_baseline is null).
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
 
@@ -237,7 +236,7 @@ def time_prefill(model, cfg, steps, warmup):
 
 
 def extra_workload(name, steps, warmup):
-    """The two further workloads that BASELINE.md lists, each printed as one JSON line of its own:
+    """Two further workloads, each printed as one JSON line of its own:
     decode30b: OPT-30B sizes, batch 16, context ending at 2,048, greedy;
     mixed13b:  OPT-13B sizes, 32 requests with prompts of 64..1,536 tokens, a budget of 512 tokens a
                step (one prompt portion beside the decode tokens of the others), 256 new tokens each at

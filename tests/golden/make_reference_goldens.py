@@ -90,4 +90,4 @@ def main(src):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference/src")
+    main(sys.argv[1] if len(sys.argv) > 1 else os.path.join(os.environ.get("TNX_REFERENCE", "reference"), "src"))
