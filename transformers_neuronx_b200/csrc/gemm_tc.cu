@@ -35,6 +35,7 @@ constexpr int BLOCK_K = 64;          // 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int TILE_P = 128;          // rows of the 128-row operand = TMEM lanes
 constexpr int NUM_THREADS = 192;
+constexpr int MAX_CLUSTER = 8;               // the portable cluster size
 
 // Instruction descriptor: D = f32, A = B = bf16, both K-major, M = 128, N = n.
 __host__ __device__ constexpr uint32_t instr_desc(int n) {
@@ -342,8 +343,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             const size_t o = (size_t)m * p.ldc + n;
             const float res = (live && p.residual) ? __ldcg(p.residual + o) : 0.f;      // in flight during the sum
             const uint32_t a = part_addr + (uint32_t)((col * TILE_P + row) * 4);
+            // all loads first (they travel to the other SMs together), then the sum in split order
+            float f[MAX_CLUSTER];
+#pragma unroll
+            for (int s = 0; s < MAX_CLUSTER; ++s) f[s] = s < S ? ld_cluster_f32(map_to_cta(a, (uint32_t)s)) : 0.f;
             float v = 0.f;
-            for (int s = 0; s < S; ++s) v += ld_cluster_f32(map_to_cta(a, (uint32_t)s));   // split order
+#pragma unroll
+            for (int s = 0; s < MAX_CLUSTER; ++s) if (s < S) v += f[s];
             if (live) {
                 if (p.bias) v += __ldg(p.bias + n);
                 if (p.relu) v = fmaxf(v, 0.f);
@@ -1023,7 +1029,6 @@ int launch(const CUtensorMap& mp, const CUtensorMap& mq, const Params& p, dim3 g
 }  // namespace
 
 // Many tokens: which kernel, and how many of the paired kernel's tiles are shared out by K blocks.
-constexpr int MAX_CLUSTER = 8;               // the portable cluster size
 
 struct ManyTokensPlan { int kind; int pairs; int sk_tiles; int sk_pairs; };   // kind 0: 128 x 128 tiles, 1: CTA pairs, 2: persistent
 static ManyTokensPlan plan_many_tokens(int M, int N, int K, int sms) {
