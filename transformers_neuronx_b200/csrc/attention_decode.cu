@@ -269,19 +269,41 @@ attention_decode_kernel(const DecodeParams p) {
     __syncthreads();
     if (!last_flag) return;
     __threadfence();
+    // Merge in split order.  Loads are issued eight splits at a time before their values are used,
+    // so that the merge costs a few round trips to the second-level cache, not one per split.
     const float* base = p.scratch + ((size_t)ri * p.n_heads + h) * p.n_splits * (d + 2);
+    const size_t stride = (size_t)(d + 2);
+    const int S = p.n_splits;
     float GM = -INFINITY;
-    for (int s2 = 0; s2 < p.n_splits; ++s2) GM = fmaxf(GM, __ldcg(base + (size_t)s2 * (d + 2)));
+    for (int s0 = 0; s0 < S; s0 += 8) {
+        float ms[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ms[i] = s0 + i < S ? __ldcg(base + (s0 + i) * stride) : -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) GM = fmaxf(GM, ms[i]);
+    }
     float GL = 0.f;
-    for (int s2 = 0; s2 < p.n_splits; ++s2) {
-        const float ms = __ldcg(base + (size_t)s2 * (d + 2));
-        GL += (ms == -INFINITY) ? 0.f : __ldcg(base + (size_t)s2 * (d + 2) + 1) * __expf(ms - GM);
+    for (int s0 = 0; s0 < S; s0 += 8) {
+        float ms[8], ls[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            ms[i] = s0 + i < S ? __ldcg(base + (s0 + i) * stride) : -INFINITY;
+            ls[i] = s0 + i < S ? __ldcg(base + (s0 + i) * stride + 1) : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) GL += (ms[i] == -INFINITY) ? 0.f : ls[i] * __expf(ms[i] - GM);
     }
     for (int t2 = t; t2 < d; t2 += WARPS * 32) {
         float o = 0.f;
-        for (int s2 = 0; s2 < p.n_splits; ++s2) {
-            const float ms = __ldcg(base + (size_t)s2 * (d + 2));
-            if (ms != -INFINITY) o += __ldcg(base + (size_t)s2 * (d + 2) + 2 + t2) * __expf(ms - GM);
+        for (int s0 = 0; s0 < S; s0 += 8) {
+            float ms[8], vs[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                ms[i] = s0 + i < S ? __ldcg(base + (s0 + i) * stride) : -INFINITY;
+                vs[i] = s0 + i < S ? __ldcg(base + (s0 + i) * stride + 2 + t2) : 0.f;
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) if (ms[i] != -INFINITY) o += vs[i] * __expf(ms[i] - GM);
         }
         p.out[(size_t)row * p.out_stride + (size_t)h * d + t2] = __float2bfloat16_rn(o / GL);
     }
