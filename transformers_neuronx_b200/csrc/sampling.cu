@@ -16,7 +16,10 @@
 namespace {
 
 constexpr int THREADS = 1024;
-constexpr double FX_ONE = 1099511627776.0;   // 2^40
+constexpr int GROUPS = 8;                    // copies of the mass histogram: four warps share one
+// The 64-bit mass histogram of the top-p passes is kept in GROUPS copies that are added up after
+// a pass: nearly all tokens of a row fall into a few bins of the keys' top byte, and 1,024 threads
+// adding into the same few shared-memory words was most of this kernel's time (0.7 ms a call).
 
 __device__ __forceinline__ uint32_t ordered_key(float v) {
     uint32_t u = __float_as_uint(v);
@@ -37,22 +40,33 @@ __device__ __forceinline__ void philox4x32_10(uint32_t c0, uint32_t c1, uint32_t
     out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
 }
 
+// exp(s - mx) as a 2^-40 fixed-point integer.  The product with 2^40 is exact in 32-bit (a change of
+// the exponent), so this is the value a 64-bit computation would truncate to as well.
+__device__ __forceinline__ unsigned long long mass_of(float s, float mx) {
+    return __float2ull_rz(expf(s - mx) * 1099511627776.0f);
+}
+
 struct ArgMax { float v; int i; };
 __device__ __forceinline__ ArgMax better(ArgMax a, ArgMax b) {
     if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
     return a;
 }
 
+// TOP_P false: the caller passes no top_p array; the kernel then does without the copies of the
+// mass histogram (shared memory that would otherwise be taken from the first-level cache).
+template <bool TOP_P>
 __global__ void __launch_bounds__(THREADS)
 sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const float* __restrict__ top_p,
               const unsigned long long* __restrict__ seeds, const unsigned long long* __restrict__ counters,
               int suppress_id, int* __restrict__ out) {
+    __shared__ unsigned long long warp_hist64[TOP_P ? GROUPS * 256 : THREADS];
+    unsigned long long* sums = warp_hist64;                      // [THREADS], used after the histogram passes
+    static_assert(GROUPS * 256 >= THREADS, "the partial sums of the last phase reuse the histogram copies");
     __shared__ float fscratch[32];
     __shared__ ArgMax ascratch[32];
     __shared__ unsigned int chist[256];
     __shared__ unsigned long long mhist[256];
-    __shared__ unsigned long long sums[THREADS];
     __shared__ unsigned int sh_prefix, sh_remaining;
     __shared__ unsigned long long sh_above, sh_total;
     __shared__ int sh_owner;
@@ -120,30 +134,38 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
     }
 
     // ---- top-p over the tokens that top-k kept -------------------------------------------------
-    const float P = top_p ? top_p[r] : 1.f;
-    if (P < 1.f) {
+    const float P = (TOP_P && top_p) ? top_p[r] : 1.f;
+    if (TOP_P && P < 1.f) {
         unsigned long long local = 0;
         for (int i = tid; i < V; i += THREADS) {
             const float s = SCORE(i);
-            if (ordered_key(s) >= thr) local += (unsigned long long)((double)expf(s - mx) * FX_ONE);
+            if (ordered_key(s) >= thr) local += mass_of(s, mx);
         }
         if (tid == 0) sh_total = 0;
         __syncthreads();
-        atomicAdd(&sh_total, local);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
+        if ((tid & 31) == 0) atomicAdd(&sh_total, local);
         __syncthreads();
         unsigned long long limit = (unsigned long long)((double)P * (double)sh_total);
         if (limit < 1) limit = 1;                      // the most likely token is always kept
         if (tid == 0) { sh_prefix = 0; sh_above = 0; }
         uint32_t mask = 0;
         for (int shift = 24; shift >= 0; shift -= 8) {
-            if (tid < 256) mhist[tid] = 0;
+            for (int j = tid; j < GROUPS * 256; j += THREADS) warp_hist64[j] = 0;
             __syncthreads();
             const uint32_t prefix = sh_prefix;
+            unsigned long long* mine64 = warp_hist64 + (tid >> 5) % GROUPS * 256;
             for (int i = tid; i < V; i += THREADS) {
                 const float s = SCORE(i);
                 const uint32_t key = ordered_key(s);
-                if (key >= thr && (key & mask) == prefix)
-                    atomicAdd(&mhist[(key >> shift) & 255u], (unsigned long long)((double)expf(s - mx) * FX_ONE));
+                if (key >= thr && (key & mask) == prefix) atomicAdd(&mine64[(key >> shift) & 255u], mass_of(s, mx));
+            }
+            __syncthreads();
+            if (tid < 256) {
+                unsigned long long c = 0;
+                for (int w = 0; w < GROUPS; ++w) c += warp_hist64[w * 256 + tid];
+                mhist[tid] = c;
             }
             __syncthreads();
             if (tid == 0) {
@@ -168,7 +190,7 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
     unsigned long long local = 0;
     for (int i = lo; i < hi; ++i) {
         const float s = SCORE(i);
-        if (ordered_key(s) >= thr) local += (unsigned long long)((double)expf(s - mx) * FX_ONE);
+        if (ordered_key(s) >= thr) local += mass_of(s, mx);
     }
     sums[tid] = local;
     __syncthreads();
@@ -200,7 +222,7 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
         for (int i = lo; i < hi; ++i) {
             const float s = SCORE(i);
             if (ordered_key(s) >= thr) {
-                run += (unsigned long long)((double)expf(s - mx) * FX_ONE);
+                run += mass_of(s, mx);
                 pick = i;
                 if (run > target) break;
             }
@@ -221,6 +243,9 @@ TNX_EXPORT int tnx_sample(const float* logits, int ld, int n_rows, int V, const 
                           const unsigned long long* counters, int suppress_id, int* out, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (V <= 0 || ld < V) return TNX_ERR_BAD_ARG;
-    return tnx_launch_pdl(sample_kernel, dim3(n_rows), dim3(THREADS), 0, stream, logits, ld, V, temperature, top_k, top_p,
-                          seeds, counters, suppress_id, out);
+    if (top_p)
+        return tnx_launch_pdl(sample_kernel<true>, dim3(n_rows), dim3(THREADS), 0, stream, logits, ld, V, temperature, top_k,
+                              top_p, seeds, counters, suppress_id, out);
+    return tnx_launch_pdl(sample_kernel<false>, dim3(n_rows), dim3(THREADS), 0, stream, logits, ld, V, temperature, top_k,
+                          top_p, seeds, counters, suppress_id, out);
 }

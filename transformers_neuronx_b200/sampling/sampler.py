@@ -41,6 +41,7 @@ class Sampler:
         temp = dev[0].to(torch.int32).view(torch.float32)
         topk = dev[1].to(torch.int32)
         topp = dev[2].to(torch.int32).view(torch.float32)
-        ops.sample(logits, out, temperature=temp, top_k=topk, top_p=topp, seeds=dev[3].contiguous(),
-                   counters=dev[4].contiguous(), suppress_id=suppress_id)
+        # no top-p anywhere in the batch: the kernel variant without the mass histograms
+        ops.sample(logits, out, temperature=temp, top_k=topk, top_p=topp if any(p < 1.0 for p in top_ps) else None,
+                   seeds=dev[3].contiguous(), counters=dev[4].contiguous(), suppress_id=suppress_id)
         return out
