@@ -117,15 +117,36 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
                 if ((key & mask) == prefix) atomicAdd(&chist[(key >> shift) & 255u], 1u);
             }
             __syncthreads();
-            if (tid == 0) {
-                unsigned cum = 0, remaining = sh_remaining;
-                int b = 255;
-                for (; b > 0; --b) {
-                    if (cum + chist[b] >= remaining) break;
-                    cum += chist[b];
+            if (tid < 32) {
+                // The highest digit b with count(digits >= b) >= remaining (0 if none): lane l looks at
+                // digits 8 l .. 8 l + 7, the counts of the lanes above it come from a suffix sum.
+                const unsigned remaining = sh_remaining;
+                unsigned v[8], tot = 0;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) { v[j] = chist[tid * 8 + j]; tot += v[j]; }
+                unsigned incl = tot;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const unsigned nb = __shfl_down_sync(0xffffffffu, incl, o);
+                    if (tid + o < 32) incl += nb;
                 }
-                sh_remaining = remaining - cum;
-                sh_prefix = prefix | ((uint32_t)b << shift);
+                unsigned cum = incl - tot;                 // tokens with digits in the lanes above
+                int b_found = -1;
+                unsigned cum_found = 0;
+#pragma unroll
+                for (int j = 7; j >= 0; --j) {
+                    const int b = tid * 8 + j;
+                    if (b_found < 0 && (cum + v[j] >= remaining || b == 0)) { b_found = b; cum_found = cum; }
+                    cum += v[j];
+                }
+                const unsigned who = __ballot_sync(0xffffffffu, b_found >= 0);     // lane 0 always answers
+                const int src = 31 - __clz(who);
+                const int b = __shfl_sync(0xffffffffu, b_found, src);
+                const unsigned cum_b = __shfl_sync(0xffffffffu, cum_found, src);
+                if (tid == 0) {
+                    sh_remaining = remaining - cum_b;
+                    sh_prefix = prefix | ((uint32_t)b << shift);
+                }
             }
             mask |= 255u << shift;
             __syncthreads();
@@ -168,15 +189,35 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
                 mhist[tid] = c;
             }
             __syncthreads();
-            if (tid == 0) {
-                unsigned long long cum = sh_above, chosen_above = sh_above;
-                int chosen = 255;
-                for (int b = 255; b >= 0; --b) {       // lowest digit whose tokens may still be kept
-                    if (cum < limit || b == 255) { chosen = b; chosen_above = cum; } else break;
-                    cum += mhist[b];
+            if (tid < 32) {
+                // The lowest digit whose tokens may still be kept: the lowest b with
+                // (mass above the prefix) + mass(digits > b) < limit, or 255 if there is none.
+                unsigned long long v[8], tot = 0;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) { v[j] = mhist[tid * 8 + j]; tot += v[j]; }
+                unsigned long long incl = tot;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const unsigned long long nb = __shfl_down_sync(0xffffffffu, incl, o);
+                    if (tid + o < 32) incl += nb;
                 }
-                sh_above = chosen_above;
-                sh_prefix = prefix | ((uint32_t)chosen << shift);
+                unsigned long long above = sh_above + (incl - tot);      // mass above this lane's highest digit
+                int b_found = -1;
+                unsigned long long above_found = 0;
+#pragma unroll
+                for (int j = 7; j >= 0; --j) {
+                    const int b = tid * 8 + j;
+                    if (above < limit || b == 255) { b_found = b; above_found = above; }     // keeps the lowest
+                    above += v[j];
+                }
+                const unsigned who = __ballot_sync(0xffffffffu, b_found >= 0);     // lane 31 always answers
+                const int src = __ffs(who) - 1;
+                const int chosen = __shfl_sync(0xffffffffu, b_found, src);
+                const unsigned long long chosen_above = __shfl_sync(0xffffffffu, above_found, src);
+                if (tid == 0) {
+                    sh_above = chosen_above;
+                    sh_prefix = prefix | ((uint32_t)chosen << shift);
+                }
             }
             mask |= 255u << shift;
             __syncthreads();
