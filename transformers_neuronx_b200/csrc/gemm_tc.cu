@@ -295,15 +295,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             } else if (p.cluster_reduce) {
                 // 32-bit partial tile -> this CTA's shared memory, [col 0..BN)[row 0..127], over the
                 // first stages (every load into them has been consumed by now)
-                float* part = (float*)smem + row_in_tile;
+                // (swapped: [col][row], the lanes of a warp write consecutive floats; otherwise [row][col]
+                // with rows of BN + 4 floats, written 16 bytes at a time: eight lanes then cover all banks)
+                float* part = (float*)smem + (SWAP ? row_in_tile : row_in_tile * (BN + 4));
 #pragma unroll 1
                 for (int c = 0; c < BN; c += LD_COLS) {
                     uint32_t r[32];
                     const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c;
                     if (LD_COLS == 32) tmem_ld32(taddr, r); else tmem_ld16(taddr, r);
                     tmem_ld_wait();
+                    if (SWAP) {
 #pragma unroll
-                    for (int j = 0; j < LD_COLS; ++j) part[(c + j) * TILE_P] = num_kb > 0 ? __uint_as_float(r[j]) : 0.f;
+                        for (int j = 0; j < LD_COLS; ++j) part[(c + j) * TILE_P] = num_kb > 0 ? __uint_as_float(r[j]) : 0.f;
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < LD_COLS; j += 4)
+                            *(float4*)(part + c + j) = num_kb > 0 ? make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]))
+                                                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
                 }
             } else {
                 // 32-bit partial tile -> scratch: [split][tile][col 0..BN)[row 0..127]: the 32 lanes
@@ -328,21 +337,85 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     // ---- split-K within a cluster: every CTA adds a band of rows over all partial tiles ----------
     if (p.splits > 1 && p.cluster_reduce) {
         if (warp >= 2 && !ok) {                           // a wait ran out: the partial tile must still be defined
-            float* part = (float*)smem + (warp & 3) * 32 + lane;
-            for (int c = 0; c < BN; ++c) part[c * TILE_P] = 0.f;
+            const int rr = (warp & 3) * 32 + lane;
+            float* part = (float*)smem + (SWAP ? rr : rr * (BN + 4));
+            for (int c = 0; c < BN; ++c) part[SWAP ? c * TILE_P : c] = 0.f;
         }
         tc_fence_before();
         cluster_sync();                                   // all partial tiles of the cluster are written
         const int S = p.splits, r = (int)cluster_ctarank();
         const int row_lo = TILE_P * r / S, n_rows = TILE_P * (r + 1) / S - row_lo;
         const uint32_t part_addr = smem_u32(smem);
+        // Four neighbouring features at a time where the band and the output allow it (16-byte
+        // loads from the other SMs' shared memory, 16- or 8-byte stores), else one by one.
+        const bool vec = (S == 2 || S == 4 || S == 8) && p.ldc % 4 == 0 && !(((uintptr_t)p.C | (uintptr_t)p.residual | (uintptr_t)p.bias) & 15);
+        if (vec) {
+            constexpr int LD = SWAP ? TILE_P : BN + 4;        // floats between consecutive columns (swapped) or rows
+            const int n_items = SWAP ? (n_rows / 4) * BN : n_rows * (BN / 4);
+            for (int item = threadIdx.x; item < n_items; item += NUM_THREADS) {
+                int row, col;                                 // of the first of the four elements
+                if (SWAP) { col = item / (n_rows / 4); row = row_lo + 4 * (item - col * (n_rows / 4)); }
+                else { row = row_lo + item / (BN / 4); col = 4 * (item - (item / (BN / 4)) * (BN / 4)); }
+                const int n = SWAP ? tile_p * TILE_P + row : tile_q * BN + col;      // first feature
+                const int m = SWAP ? tile_q * BN + col : tile_p * TILE_P + row;      // token
+                const int n_lim = SWAP ? p.rows_p : p.rows_q, m_lim = SWAP ? p.rows_q : p.rows_p;
+                if (m >= m_lim || n >= n_lim) continue;
+                const size_t o = (size_t)m * p.ldc + n;
+                const bool whole = n + 3 < n_lim;
+                float4 res = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (p.residual) {
+                    if (whole) res = __ldcg((const float4*)(p.residual + o));
+                    else { res.x = p.residual[o]; if (n + 1 < n_lim) res.y = p.residual[o + 1]; if (n + 2 < n_lim) res.z = p.residual[o + 2]; }
+                }
+                const uint32_t a = part_addr + (uint32_t)((SWAP ? col * LD + row : row * LD + col) * 4);
+                float4 f[MAX_CLUSTER];
+#pragma unroll
+                for (int s = 0; s < MAX_CLUSTER; ++s) {
+                    if (s < S) {
+                        asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                     : "=f"(f[s].x), "=f"(f[s].y), "=f"(f[s].z), "=f"(f[s].w) : "r"(map_to_cta(a, (uint32_t)s)) : "memory");
+                    } else {
+                        f[s] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+                }
+                float v[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int s = 0; s < MAX_CLUSTER; ++s)
+                    if (s < S) { v[0] += f[s].x; v[1] += f[s].y; v[2] += f[s].z; v[3] += f[s].w; }      // split order
+                const float rr[4] = {res.x, res.y, res.z, res.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    if (p.bias && n + e < n_lim) v[e] += __ldg(p.bias + n + e);
+                    if (p.relu) v[e] = fmaxf(v[e], 0.f);
+                    v[e] += rr[e];
+                }
+                if (whole) {
+                    if (p.c_is_bf16) {
+                        __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]), h1 = __floats2bfloat162_rn(v[2], v[3]);
+                        uint2 u; u.x = *(uint32_t*)&h0; u.y = *(uint32_t*)&h1;
+                        *(uint2*)((bf16*)p.C + o) = u;
+                    } else {
+                        *(float4*)((float*)p.C + o) = make_float4(v[0], v[1], v[2], v[3]);
+                    }
+                } else {
+                    for (int e = 0; e < 4 && n + e < n_lim; ++e) {
+                        if (p.c_is_bf16) ((bf16*)p.C)[o + e] = __float2bfloat16_rn(v[e]);
+                        else ((float*)p.C)[o + e] = v[e];
+                    }
+                }
+            }
+        } else
         for (int item = threadIdx.x; item < n_rows * BN; item += NUM_THREADS) {
-            const int col = item / n_rows, row = row_lo + item - col * n_rows;
-            const int n = tile_p * TILE_P + row, m = tile_q * BN + col;     // feature, token
-            const bool live = n < p.rows_p && m < p.rows_q;
+            // consecutive threads: consecutive features, which lie side by side in the output
+            int row, col;
+            if (SWAP) { col = item / n_rows; row = row_lo + item - col * n_rows; }
+            else { row = row_lo + item / BN; col = item - (item / BN) * BN; }
+            const int n = SWAP ? tile_p * TILE_P + row : tile_q * BN + col;      // feature
+            const int m = SWAP ? tile_q * BN + col : tile_p * TILE_P + row;      // token
+            const bool live = SWAP ? (n < p.rows_p && m < p.rows_q) : (m < p.rows_p && n < p.rows_q);
             const size_t o = (size_t)m * p.ldc + n;
             const float res = (live && p.residual) ? __ldcg(p.residual + o) : 0.f;      // in flight during the sum
-            const uint32_t a = part_addr + (uint32_t)((col * TILE_P + row) * 4);
+            const uint32_t a = part_addr + (uint32_t)((SWAP ? col * TILE_P + row : row * (BN + 4) + col) * 4);
             // all loads first (they travel to the other SMs together), then the sum in split order
             float f[MAX_CLUSTER];
 #pragma unroll
@@ -1030,9 +1103,9 @@ int launch(const CUtensorMap& mp, const CUtensorMap& mq, const Params& p, dim3 g
 
 // Many tokens: which kernel, and how many of the paired kernel's tiles are shared out by K blocks.
 
-struct ManyTokensPlan { int kind; int pairs; int sk_tiles; int sk_pairs; };   // kind 0: 128 x 128 tiles, 1: CTA pairs, 2: persistent
+struct ManyTokensPlan { int kind; int pairs; int sk_tiles; int sk_pairs; int splits; };   // kind 0: 128 x 128 tiles, 1: CTA pairs, 2: persistent, 3: 128 x 256 tiles with K split in clusters
 static ManyTokensPlan plan_many_tokens(int M, int N, int K, int sms) {
-    ManyTokensPlan r{2, 0, 0, 0};
+    ManyTokensPlan r{2, 0, 0, 0, 1};
     const int kb = (K + BLOCK_K - 1) / BLOCK_K;
     const int tiles_m = (M + TILE_P - 1) / TILE_P;
     // Estimated times in microseconds, from measurements at 256..2,048 tokens: a K block of a
@@ -1063,6 +1136,15 @@ static ManyTokensPlan plan_many_tokens(int M, int N, int K, int sms) {
         // paired kernel (half of whose 256 token rows may be empty) wins where K is long and the
         // tiles are few, by sharing them out.
         const int tiles_p = tiles_m * ((N + 255) / 256);
+        // Few tiles and a long K (the output projections of a layer): 128 x 256 tiles with K split 4 or
+        // 8 ways over the CTAs of a cluster, which add up through shared memory like the few-token
+        // form does (measured at 65..255 tokens: 22 against 28 us for [4096 x 4096], 44-50 against 60 us
+        // for [4096 x 16384]; with more tiles and a split of 2 the kernels below are faster).
+        {
+            int sp = MAX_CLUSTER;
+            while (sp > 1 && (tiles_p * sp > sms || sp * 4 > kb)) sp >>= 1;
+            if (sp >= 4) { r.kind = 3; r.splits = sp; return r; }
+        }
         const bool single = tiles_p * 4 < sms * 3;
         const float t_here = single ? t_single : (float)((tiles_p + sms - 1) / sms) * kb * 0.45f + 8.f;
         if (t_here <= t_pair && t_here <= t_share) { r.kind = single ? 0 : 2; return r; }
@@ -1129,6 +1211,12 @@ TNX_EXPORT int tnx_gemm_tc(const void* A, const void* W, const float* bias, cons
             if (!make_map(&mq, W, N, K, ldw, 128)) return TNX_ERR_UNSUPPORTED;
             dim3 grid((M + TILE_P - 1) / TILE_P, (N + 127) / 128, 1);
             return launch<128, 6, false>(mp, mq, p, grid, stream);
+        }
+        if (mt.kind == 3) {
+            if (!make_map(&mq, W, N, K, ldw, 256)) return TNX_ERR_UNSUPPORTED;
+            p.splits = mt.splits; p.kb_per_split = (kb + mt.splits - 1) / mt.splits; p.cluster_reduce = mt.splits > 1;
+            dim3 grid((M + TILE_P - 1) / TILE_P, (N + 255) / 256, mt.splits);
+            return launch<256, 4, false>(mp, mq, p, grid, stream);
         }
         if (mt.kind == 1) {
             const int ptiles_m = (M + 255) / 256, ptiles_n = (N + 255) / 256;
