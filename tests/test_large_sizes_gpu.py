@@ -103,6 +103,15 @@ def test_one_layer_at_the_sizes_of_the_benchmark():
         runner.step([StepEntry("q", seqs[1][:900], [])])
         out = runner.step([StepEntry("p", seqs[0][:512], [511]), StepEntry("q", [seqs[1][900]], [0])])
         assert rel_error(out, torch.stack([plain(seqs[0][:512])[-1], plain(seqs[1][:901])[-1]])) <= tol
+        for r in ("p", "q"):
+            runner.finish(r)
+        # short prompts alone: 65..255 tokens take kernels of their own (128 x 256 tiles, K split in clusters)
+        for n in (130, 250, 66):
+            runner.add_request("s")
+            out = runner.step([StepEntry("s", seqs[2][:n], [n - 1, 0])])
+            want = plain(seqs[2][:n])
+            assert rel_error(out, want[[n - 1, 0]]) <= tol, n
+            runner.finish("s")
         ops.raise_on_device_error()
     finally:
         torch.backends.cuda.matmul.allow_tf32 = tf32
