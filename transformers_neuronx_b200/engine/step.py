@@ -365,12 +365,14 @@ class StepRunner:
         if g["graph"] is None:
             if g["runs"] == 0:                        # first use: run eagerly (kernels get built, scratch gets made)
                 g["runs"] = 1
-                return self._wanted_rows(self.model.forward(ctx), entries)
+                with ops.stream_scope():
+                    return self._wanted_rows(self.model.forward(ctx), entries)
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             n0 = ops.launch_count()
             with torch.cuda.graph(graph, pool=self._graph_pool):
-                g["logits"] = self.model.forward(ctx)
+                with ops.stream_scope():
+                    g["logits"] = self.model.forward(ctx)
             g["kernels"] = ops.launch_count() - n0       # recorded, not run
             ops.add_launches(-g["kernels"])
             g["graph"] = graph
@@ -401,7 +403,8 @@ class StepRunner:
             logits = self._graph_step(entries, sampled)
         else:
             ctx = self.prepare(entries, sampled)
-            logits = self.model.forward(ctx)
+            with ops.stream_scope():
+                logits = self.model.forward(ctx)
         for e in entries:
             self.cache.release_behind_window(e.rid)
         self.steps_run += 1

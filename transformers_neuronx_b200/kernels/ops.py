@@ -42,8 +42,30 @@ def _check(code: int, what: str) -> None:
     raise KernelError(f"{what}: CUDA error {code} at launch")
 
 
+_scoped_stream = None
+
+
 def _stream() -> c_void_p:
+    if _scoped_stream is not None:
+        return _scoped_stream
     return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class stream_scope:
+    """Looks the current CUDA stream up once for all kernel launches inside the block (asking torch
+    for it costs a few microseconds per launch, which a model step of a few tokens notices).  Enter
+    it where the stream is already the one to launch on, e.g. inside a graph capture."""
+
+    def __enter__(self):
+        global _scoped_stream
+        self._prev = _scoped_stream
+        _scoped_stream = c_void_p(torch.cuda.current_stream().cuda_stream)
+        return self
+
+    def __exit__(self, *exc):
+        global _scoped_stream
+        _scoped_stream = self._prev
+        return False
 
 
 def _p(t: Optional[torch.Tensor]) -> c_void_p:
@@ -244,6 +266,7 @@ def sample(logits, out, temperature=None, top_k=None, top_p=None, seeds=None, co
 # ---------------------------------------------------------------------------------------------
 # Tensor-core kernels (bfloat16).
 _attention_impls = {}
+_gemm_plans = {}          # (M, N, K, SMs) -> (splits, scratch bytes, counters) as the library plans them
 _dev_state = {}          # per device: error word, split-K scratch and counters, SM count
 
 
@@ -355,9 +378,15 @@ def gemm_tc(a, w, out, bias=None, residual=None, relu=False, splits=None, few_to
                                _stream()), "gemv")
             return
     st = _state(a.device)
-    n_splits, nbytes, ncnt = c_int(1), ctypes.c_longlong(0), c_int(0)
-    lib.tnx_gemm_tc_plan(c_int(M), c_int(N), c_int(K), c_int(st["sms"]), ctypes.byref(n_splits),
-                         ctypes.byref(nbytes), ctypes.byref(ncnt))
+    plan = _gemm_plans.get((M, N, K, st["sms"]))
+    if plan is None:
+        n_splits, nbytes, ncnt = c_int(1), ctypes.c_longlong(0), c_int(0)
+        lib.tnx_gemm_tc_plan(c_int(M), c_int(N), c_int(K), c_int(st["sms"]), ctypes.byref(n_splits),
+                             ctypes.byref(nbytes), ctypes.byref(ncnt))
+        if len(_gemm_plans) > 4096:
+            _gemm_plans.clear()
+        plan = _gemm_plans[(M, N, K, st["sms"])] = (n_splits.value, nbytes.value, ncnt.value)
+    n_splits, nbytes, ncnt = c_int(plan[0]), ctypes.c_longlong(plan[1]), c_int(plan[2])
     if splits is not None and M <= 64:
         kb = -(-K // 64)
         s = max(1, min(int(splits), kb))

@@ -104,6 +104,7 @@ class DecoderModel:
             if block.needs_act_input and not act_current:
                 ops.pick_rows(x, None, out_act=x_act)
             ctx.cache_id = e.cache
+            ctx.begin_entry()
             block.forward(ctx, x, x_act)
             act_current = block.keeps_act_current
         if ctx.logit_rows is None or ctx.logit_rows.shape[0] == 0:

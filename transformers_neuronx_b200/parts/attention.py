@@ -67,13 +67,13 @@ class PagedAttention(Mixer):
         s = self.spec
         N = h.shape[0]
         qd, kd = s.n_heads * s.head_dim, s.n_kv_heads * s.head_dim
-        qkv = ctx.empty(N, qd + 2 * kd)
+        qkv = ctx.scratch(N, qd + 2 * kd)
         self.qkv.forward(h, qkv)
         q, k, v = qkv[:, :qd], qkv[:, qd:qd + kd], qkv[:, qd + kd:]
         if self.position is not None:
             self.position.rotate(ctx, q, k)
         cache, g = ctx.cache(), ctx.cache_group()
-        att = ctx.empty(N, qd)
+        att = ctx.scratch(N, qd)
         ops.attention(ctx, g, q, cache, att, s.n_heads, s.scale, s.window or 0, new_kv=(k, v, ctx.slot_mapping[g]))
         self.out.forward(att, residual, residual=residual)
 

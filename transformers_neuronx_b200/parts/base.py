@@ -56,9 +56,27 @@ class StepContext:
         self.n_prefill_tiles = 0
         self.n_decode_rows = 0
         self.max_decode_ctx = 0
+        self._scratch_pool = {}
+        self._scratch_used = {}
 
     def empty(self, rows, cols, dtype=None) -> torch.Tensor:
         return torch.empty((rows, cols), dtype=dtype or self.act_dtype, device=self.device)
+
+    def scratch(self, rows, cols, dtype=None) -> torch.Tensor:
+        """A buffer that is dead when the running schedule entry ends: the next entry's requests of
+        the same shape get the same memory again (an allocation per buffer and layer is what a step
+        of a few tokens spends its time on).  Distinct calls within one entry get distinct buffers."""
+        key = (rows, cols, dtype or self.act_dtype)
+        i = self._scratch_used.get(key, 0)
+        self._scratch_used[key] = i + 1
+        have = self._scratch_pool.setdefault(key, [])
+        if i == len(have):
+            have.append(torch.empty((rows, cols), dtype=key[2], device=self.device))
+        return have[i]
+
+    def begin_entry(self) -> None:
+        """Called before each schedule entry runs: the scratch buffers of the entry before are free."""
+        self._scratch_used = {}
 
     # what the mixer of the running schedule entry owns
     def cache(self) -> torch.Tensor:

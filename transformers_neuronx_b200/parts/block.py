@@ -24,7 +24,7 @@ class PreNormBlock:
         return [p for p in (self.norm1, self.mixer, self.norm2, self.feed_forward) if p is not None]
 
     def forward(self, ctx, x, x_act):
-        h = ctx.empty(x.shape[0], x.shape[1])
+        h = ctx.scratch(x.shape[0], x.shape[1])
         self.norm1.forward(ctx, x, out_act=h)
         self.mixer.forward(ctx, h, x)
         self.norm2.forward(ctx, x, out_act=h)

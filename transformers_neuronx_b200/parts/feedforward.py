@@ -32,7 +32,7 @@ class DenseFeedForward(FeedForward):
         return self.fc1.parameter_bytes() + self.fc2.parameter_bytes()
 
     def forward(self, ctx, h, residual):
-        a = ctx.empty(h.shape[0], self.spec.fc1.out_features)
+        a = ctx.scratch(h.shape[0], self.spec.fc1.out_features)
         self.fc1.forward(h, a, relu=True)
         self.fc2.forward(a, residual, residual=residual)
 
