@@ -51,7 +51,7 @@ def test_gemm_simt_rows_do_not_depend_on_the_batch():
     assert torch.equal(full[33:34], one)                 # bit for bit
 
 
-TC_SHAPES = [(1, 128, 64), (3, 96, 320), (8, 256, 2112), (40, 4096, 4096), (130, 4096, 16384), (100, 520, 8200),
+TC_SHAPES = [(1, 128, 64), (3, 96, 320), (8, 256, 2112), (40, 4096, 4096), (128, 4096, 4096), (96, 12288, 4096), (72, 1000, 328), (130, 4096, 16384), (100, 520, 8200),
              (250, 12288, 4096), (16, 4096, 1024), (17, 1000, 96), (33, 200, 136), (64, 512, 4096),
              (65, 384, 256), (128, 128, 64), (200, 1000, 328), (300, 520, 1032), (2048, 768, 512),
              (1024, 4096, 512), (1000, 4000, 328), (300, 9000, 136), (513, 7100, 72), (520, 7102, 72), (2100, 2300, 1096),
@@ -122,7 +122,8 @@ def test_gemv_few_tokens(M, N, K):
         assert torch.equal(again, out)
 
 
-@pytest.mark.parametrize("M,N,K,splits", [(8, 256, 4096, 4), (64, 130, 1024, 16), (1, 128, 512, 2), (20, 300, 1160, 3)])
+@pytest.mark.parametrize("M,N,K,splits", [(8, 256, 4096, 4), (64, 130, 1024, 16), (1, 128, 512, 2), (20, 300, 1160, 3),
+                                          (100, 300, 2048, 4), (128, 256, 4096, 16)])
 def test_gemm_tc_split_k(M, N, K, splits):
     o = ops()
     g = torch.Generator(device="cpu").manual_seed(splits)
@@ -140,7 +141,8 @@ def test_gemm_tc_split_k(M, N, K, splits):
 
 
 @pytest.mark.parametrize("M,N,K,splits", [(8, 256, 4096, 4), (64, 130, 1024, 8), (2, 128, 512, 2), (20, 300, 1160, 3),
-                                          (16, 4096, 4096, 8), (33, 520, 2048, 5), (64, 1000, 4104, 7), (5, 96, 640, 8)])
+                                          (16, 4096, 4096, 8), (33, 520, 2048, 5), (64, 1000, 4104, 7), (5, 96, 640, 8),
+                                          (100, 520, 2048, 4), (128, 4096, 4096, 2), (70, 130, 1160, 3), (97, 1000, 8200, 8)])
 def test_gemm_tc_split_k_in_clusters(M, N, K, splits):
     """K split over the CTAs of a cluster, partial tiles added through distributed shared memory."""
     o = ops()

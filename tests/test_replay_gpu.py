@@ -187,3 +187,47 @@ def test_program_in_a_subprocess():
     for got, p in ((got0[0], 29), (got1[0], 30), (got1[1], 39)):
         err = float(np.abs(got - plain[p].numpy()).max()) / float(plain[p].abs().max())
         assert err <= TOLERANCE["float32"]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_small_steps_with_portions_are_captured_and_replayed(tiny, dtype):
+    """Steps of a few tokens with prompt portions run as CUDA graphs padded to a few sizes: the
+    same shapes come again and again here (first use eager, second captured, then replayed), with
+    portions beside decoded tokens, none, few and all logits wanted, and pages used again."""
+    from transformers_neuronx_b200.engine import StepEntry, StepRunner, load_model
+    model, _ = load_model(tiny.folder, dtype, verbose=False)
+    runner = StepRunner(model, 16, 20, 4, 256, use_cuda_graphs=True)
+    worst = 0.0
+    for rnd in range(6):
+        reqs = {f"s{rnd}_{i}": tiny.random_ids(n, seed=900 + 10 * rnd + i) for i, n in enumerate([70, 45, 61])}
+        plain = {r: tiny.plain_logits(ids) for r, ids in reqs.items()}
+        pos = {r: 0 for r in reqs}
+        for r in reqs:
+            runner.add_request(r)
+        sizes = {0: [9, 1, 1, 14, 2, 1], 1: [5, 30, 1, 3, 1, 1], 2: [17, 2, 1, 1, 8, 1]}
+        k = 0
+        while any(pos[r] < len(reqs[r]) for r in reqs):
+            entries, checks = [], []
+            for i, r in enumerate(reqs):
+                left = len(reqs[r]) - pos[r]
+                if left == 0 or (k + i) % 4 == 3:                    # a request may sit a step out
+                    continue
+                n = min(sizes[i][k % 6], left)
+                want = [] if (k + i) % 3 == 0 else ([n - 1] if (k + i) % 3 == 1 else list(range(n)))
+                entries.append(StepEntry(r, reqs[r][pos[r]:pos[r] + n], want))
+                checks += [(r, pos[r] + w) for w in want]
+                pos[r] += n
+            k += 1
+            if not entries:
+                continue
+            logits = runner.step(entries).cpu()
+            assert logits.shape[0] == len(checks)
+            for row, (r, p) in enumerate(checks):
+                err = float((logits[row] - plain[r][p]).abs().max()) / float(plain[r][p].abs().max())
+                worst = max(worst, err)
+                assert err <= TOLERANCE[dtype], f"{dtype} round {rnd} step {k} request {r} position {p}: {err:.3e}"
+        for r in reqs:
+            runner.finish(r)
+        runner.cache.check()
+    replayed = {key: runs for key, runs in runner.captured_steps().items() if isinstance(key[0], tuple) and key[0][0] == "portions"}
+    assert replayed and max(replayed.values()) >= 4, runner.captured_steps()

@@ -36,7 +36,7 @@ class EngineConfig:
     max_num_seqs: int = 64             # slots for per-request state
     max_batch_tokens: int = 2048       # token budget of one step
     max_model_len: Optional[int] = None  # longest request; None: the model's own limit
-    use_cuda_graphs: bool = True       # capture decode-only steps
+    use_cuda_graphs: bool = True       # capture decode-only steps and steps of a few prompt tokens
     async_scheduling: bool = True      # launch a step before the ids of the step before it are read back
     seed: int = 0
 

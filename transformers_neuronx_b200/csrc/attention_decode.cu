@@ -59,6 +59,7 @@ attention_decode_kernel(const DecodeParams p) {
     const int h = blockIdx.x, ri = blockIdx.y, split = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row = p.rows ? p.rows[ri] : ri;
+    if (row < 0) return;                                        // a padded entry of the row list of a captured step
     const int req = p.token_request[row];
     if (req < 0) return;                                        // a padded row of a captured batch
     const int pos = p.positions[row];

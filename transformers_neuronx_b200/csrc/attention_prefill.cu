@@ -82,6 +82,7 @@ attention_prefill_kernel(const PrefillParams p) {
     // that the short ones fill the tail.
     const int item = gridDim.y - 1 - blockIdx.y, h = blockIdx.x;      // heaviest tiles first, of all heads
     const int req = p.tile_req[item], q0 = p.tile_q0[item];
+    if (req < 0) return;                                     // a padded work item of a captured step
     const int qs = p.q_start[req], ql = p.q_len[req], ctx = p.ctx_len[req];
     const int rows = min(BQ, ql - q0);                       // valid query rows of this tile
     const int d = p.head_dim;

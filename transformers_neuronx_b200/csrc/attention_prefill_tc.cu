@@ -135,6 +135,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int item = gridDim.y - 1 - blockIdx.y, h = blockIdx.x;      // heaviest tiles first, of all heads
     const int req = p.tile_req[item], q0 = p.tile_q0[item];
+    if (req < 0) return;                                              // a padded work item of a captured step
     const int qs = p.q_start[req], ql = p.q_len[req], ctx = p.ctx_len[req];
     const int rows = min(BQ, ql - q0);
     const int kvh = h / (p.n_heads / p.n_kv_heads);

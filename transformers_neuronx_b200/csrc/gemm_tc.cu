@@ -6,7 +6,7 @@
 //
 // One CTA computes one 128 x BN tile of D = P Q^T over a range of K.  Two forms:
 //   normal (many tokens): P = A (128 tokens), Q = W (BN = 128 features)
-//   swapped (few tokens): P = W (128 features), Q = A (BN = 16/32/64 tokens): the weight matrix,
+//   swapped (few tokens): P = W (128 features), Q = A (BN = 16/32/64/128 tokens): the weight matrix,
 //     which is what a decode step has to stream from HBM, fills the 128-row operand and nothing
 //     is wasted on padding tokens.  Few output tiles -> K is split over several CTAs.  With 2, 4
 //     or 8 splits the CTAs of a tile form a thread-block cluster: each writes its 32-bit partial
@@ -1103,6 +1103,13 @@ int launch(const CUtensorMap& mp, const CUtensorMap& mq, const Params& p, dim3 g
 
 // Many tokens: which kernel, and how many of the paired kernel's tiles are shared out by K blocks.
 
+// Up to this many tokens the swapped form runs (the tokens are the N extent of one MMA tile).
+// (Measured at 65..128 tokens against 128 x 128 and 128 x 256 tiles of the many-token kernels: equal
+// or faster on every layer product of the 6.7B and 13B sizes, [4096 x 16384] 32 against 50 us.)
+static constexpr int FEW_TOKENS_MAX = 128;
+static int few_tokens_max() { return FEW_TOKENS_MAX; }
+TNX_EXPORT int tnx_gemm_tc_few_tokens() { return few_tokens_max(); }
+
 struct ManyTokensPlan { int kind; int pairs; int sk_tiles; int sk_pairs; int splits; };   // kind 0: 128 x 128 tiles, 1: CTA pairs, 2: persistent, 3: 128 x 256 tiles with K split in clusters
 static ManyTokensPlan plan_many_tokens(int M, int N, int K, int sms) {
     ManyTokensPlan r{2, 0, 0, 0, 1};
@@ -1130,7 +1137,7 @@ static ManyTokensPlan plan_many_tokens(int M, int N, int K, int sms) {
         t_share = ((float)full + (float)rest / sk_pairs) * t_tile + 8.f + 1.3f * ((sk_pairs + rest) * 0.1f + exposed);
     }
     if (M < 256) {
-        // 65..255 tokens: the weights are streamed once and the tensor cores idle.  Few 128 x 256
+        // 129..255 tokens: the weights are streamed once and the tensor cores idle.  Few 128 x 256
         // tiles would leave SMs idle: 128 x 128 tiles, one per CTA, fill the GPU better then;
         // otherwise the single-CTA persistent kernel with 128 x 256 tiles (a K block 0.45 us).  The
         // paired kernel (half of whose 256 token rows may be empty) wins where K is long and the
@@ -1138,7 +1145,7 @@ static ManyTokensPlan plan_many_tokens(int M, int N, int K, int sms) {
         const int tiles_p = tiles_m * ((N + 255) / 256);
         // Few tiles and a long K (the output projections of a layer): 128 x 256 tiles with K split 4 or
         // 8 ways over the CTAs of a cluster, which add up through shared memory like the few-token
-        // form does (measured at 65..255 tokens: 22 against 28 us for [4096 x 4096], 44-50 against 60 us
+        // form does (measured at 129..255 tokens: 22 against 28 us for [4096 x 4096], 44-50 against 60 us
         // for [4096 x 16384]; with more tiles and a split of 2 the kernels below are faster).
         {
             int sp = MAX_CLUSTER;
@@ -1160,7 +1167,7 @@ static ManyTokensPlan plan_many_tokens(int M, int N, int K, int sms) {
 // are left zero by every call.
 TNX_EXPORT int tnx_gemm_tc_plan(int M, int N, int K, int n_sms, int* splits, long long* scratch_bytes, int* n_counters) {
     *splits = 1; *scratch_bytes = 0; *n_counters = 0;
-    if (M > 64) {
+    if (M > few_tokens_max()) {
         // paired kernel: two partial 256 x 256 tiles per pair, and a counter per shared tile, CTA and epilogue warp
         const ManyTokensPlan mt = plan_many_tokens(M, N, K, n_sms);
         if (mt.sk_tiles > 0) {
@@ -1195,7 +1202,7 @@ TNX_EXPORT int tnx_gemm_tc(const void* A, const void* W, const float* bias, cons
     p.err = err_word; p.partials = scratch; p.counters = counters;
     const int kb = (K + BLOCK_K - 1) / BLOCK_K;
     CUtensorMap mp, mq;
-    if (M > 64) {
+    if (M > few_tokens_max()) {
         p.rows_p = M; p.rows_q = N; p.splits = 1; p.kb_per_split = kb;
         if (!make_map(&mp, A, M, K, lda, TILE_P)) return TNX_ERR_UNSUPPORTED;
         int dev = 0, sms = 148;
@@ -1261,11 +1268,12 @@ TNX_EXPORT int tnx_gemm_tc(const void* A, const void* W, const float* bias, cons
         p.cluster_reduce = 1;
     }
     p.rows_p = N; p.rows_q = M; p.splits = splits; p.kb_per_split = (kb + splits - 1) / splits;
-    const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
     if (!make_map(&mp, W, N, K, ldw, TILE_P) || !make_map(&mq, A, M, K, lda, bn)) return TNX_ERR_UNSUPPORTED;
     dim3 grid((N + TILE_P - 1) / TILE_P, 1, splits);
     // stage counts that let two CTAs share an SM's shared memory
     if (bn == 16) return launch<16, 6, true>(mp, mq, p, grid, stream);
     if (bn == 32) return launch<32, 5, true>(mp, mq, p, grid, stream);
-    return launch<64, 4, true>(mp, mq, p, grid, stream);
+    if (bn == 64) return launch<64, 4, true>(mp, mq, p, grid, stream);
+    return launch<128, 3, true>(mp, mq, p, grid, stream);
 }

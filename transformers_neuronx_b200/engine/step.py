@@ -132,10 +132,11 @@ class StepRunner:
             if need[g] > free[g]:
                 raise OutOfPages(f"the step needs {need[g]} page(s) in cache group {g}, {free[g]} are free")
 
-    def _pack(self, entries: Sequence[StepEntry], pad_rows: Optional[int] = None, fixed_blocks: Optional[int] = None):
-        """Reserves the pages and builds the step's index arrays.  With pad_rows (a captured decode
-        step) every array has the size of pad_rows single-token requests: padded rows carry request
-        -1 and slot -1, which the kernels skip, and every row's logits are computed."""
+    def _pack(self, entries: Sequence[StepEntry], pad=None, fixed_blocks: Optional[int] = None):
+        """Reserves the pages and builds the step's index arrays.  pad = (tokens, requests, tiles,
+        decode rows, wanted rows): the sizes of a captured step's arrays.  Padded token rows carry
+        request -1 and slot -1, padded tiles request -1 and padded decode rows -1, all of which the
+        kernels skip; padded wanted rows repeat row 0."""
         hb = HostBatch()
         tokens, positions, token_request, logit_rows, tok_src = [], [], [], [], []
         row = 0
@@ -151,8 +152,7 @@ class StepRunner:
             logit_rows.extend(row + int(w) for w in e.want)
             row += n
         N, R = row, len(entries)
-        Np = N if pad_rows is None else pad_rows
-        Rp = R if pad_rows is None else pad_rows
+        Np, Rp = (N, R) if pad is None else pad[:2]
         ps = self.page_size
 
         def padded(vals, size, fill):
@@ -173,9 +173,12 @@ class StepRunner:
         # keys to read come later here, so that the long ones start first and the short ones fill in.
         tiles.sort()
         tile_req, tile_q0 = [t[1] for t in tiles], [t[2] for t in tiles]
-        if pad_rows is not None:
-            logit_rows = list(range(Np))
-            decode_rows = list(range(Np))
+        if pad is not None:
+            Tp, Dp, Wp = pad[2:]
+            tile_req = [-1] * (Tp - len(tile_req)) + tile_req          # padding first: the kernels start from the end
+            tile_q0 = [0] * (Tp - len(tile_q0)) + tile_q0
+            decode_rows = decode_rows + [-1] * (Dp - len(decode_rows))
+            logit_rows = logit_rows + [0] * (Wp - len(logit_rows))
         parts = [tok, pos, treq, padded(hb.q_start, Rp, 0), padded(hb.q_len, Rp, 0), padded(hb.ctx_len, Rp, 0),
                  padded(hb.slots, Rp, 0), np.asarray(logit_rows, np.int32),
                  np.asarray(tile_req, np.int32), np.asarray(tile_q0, np.int32), np.asarray(decode_rows, np.int32),
@@ -345,7 +348,52 @@ class StepRunner:
         key = self._graph_key(entries)
         bucket, ctx_bucket = key
         fixed_blocks = -(-ctx_bucket // self.page_size)
-        hb, slot, o, offs, sizes, max_blocks, n_fixed, dims, counts = self._pack_decode(entries, bucket, fixed_blocks)
+        packed = self._pack_decode(entries, bucket, fixed_blocks)
+        return self._wanted_rows(self._run_captured(key, packed, entries, sampled, ctx_bucket), entries)
+
+    # ---- small steps with prompt portions as CUDA graphs --------------------------------------------
+    SMALL_STEP_TOKENS = 128        # a step of at most this many tokens ...
+    SMALL_STEP_REQUESTS = 8        # ... of at most this many requests is launch-bound: it is captured
+
+    def _small_step_key(self, entries):
+        """The graph a step with prompt portions runs as, or None when it is large enough for the
+        kernels to hide the host's work: (tokens, requests, tiles, decode rows, wanted rows) padded
+        to a few sizes, and the context bucket."""
+        N = sum(len(e.tokens) for e in entries)
+        R = len(entries)
+        if N > self.SMALL_STEP_TOKENS or R > self.SMALL_STEP_REQUESTS or N == R:
+            return None
+        Np = 16
+        while Np < N:
+            Np *= 2
+        Rp = self.SMALL_STEP_REQUESTS
+        W = sum(len(e.want) for e in entries)
+        if W > max(Np, Rp):
+            return None
+        Wp = 0 if W == 0 else (Rp if W <= Rp else Np)
+        Dp = Rp if any(len(e.tokens) == 1 for e in entries) else 0
+        tiles = sum(-(-len(e.tokens) // ops.ATTN_PREFILL_TILE) for e in entries if len(e.tokens) > 1)
+        if tiles > Rp:
+            return None
+        longest = max(self.cache.length(e.rid) + len(e.tokens) for e in entries)
+        ctx_bucket = 256
+        while ctx_bucket < longest:
+            ctx_bucket *= 2
+        ctx_bucket = min(ctx_bucket, -(-self.max_model_len // self.page_size) * self.page_size)
+        return ("portions", Np, Rp, Rp, Dp, Wp), ctx_bucket
+
+    def _small_graph_step(self, key, entries, sampled=None) -> torch.Tensor:
+        pad, ctx_bucket = key
+        packed = self._pack(entries, pad=pad[1:], fixed_blocks=-(-ctx_bucket // self.page_size))
+        logits = self._run_captured(key, packed, entries, sampled, ctx_bucket)
+        return logits[:sum(len(e.want) for e in entries)]
+
+    def _run_captured(self, key, packed, entries, sampled, ctx_bucket) -> torch.Tensor:
+        """Runs the packed step through the graph of `key`: the first step of a key runs eagerly
+        (kernels get built, scratch gets made), the second is captured, and from then on the graph
+        is replayed on the index arrays copied into its fixed device buffer.  Returns the logits of
+        all (padded) wanted rows."""
+        hb, slot, o, offs, sizes, max_blocks, n_fixed, dims, counts = packed
         g = self._graphs.get(key)
         if g is None:
             dev = torch.empty(o, dtype=torch.int32, device=self.device)
@@ -363,10 +411,10 @@ class StepRunner:
         ctx.max_decode_ctx = ctx_bucket               # the split plan is fixed for the whole bucket
         ctx.max_ctx = ctx_bucket
         if g["graph"] is None:
-            if g["runs"] == 0:                        # first use: run eagerly (kernels get built, scratch gets made)
+            if g["runs"] == 0:
                 g["runs"] = 1
                 with ops.stream_scope():
-                    return self._wanted_rows(self.model.forward(ctx), entries)
+                    return self.model.forward(ctx)
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             n0 = ops.launch_count()
@@ -382,7 +430,11 @@ class StepRunner:
         g["graph"].replay()
         ops.add_launches(g["kernels"])
         g["runs"] += 1
-        return self._wanted_rows(g["logits"], entries)
+        return g["logits"]
+
+    def captured_steps(self) -> dict:
+        """{graph key: steps run through it} of the graphs that have been captured."""
+        return {k: g["runs"] for k, g in self._graphs.items() if g["graph"] is not None}
 
     def _wanted_rows(self, logits: torch.Tensor, entries) -> torch.Tensor:
         """A captured decode step computes the logits of every row; hand out those that were asked for."""
@@ -401,6 +453,9 @@ class StepRunner:
         if self.use_cuda_graphs and all(len(e.tokens) == 1 for e in entries) and len(entries) <= self.max_graph_batch:
             self._validate(entries)
             logits = self._graph_step(entries, sampled)
+        elif self.use_cuda_graphs and (key := self._small_step_key(entries)) is not None:
+            self._validate(entries)
+            logits = self._small_graph_step(key, entries, sampled)
         else:
             ctx = self.prepare(entries, sampled)
             with ops.stream_scope():

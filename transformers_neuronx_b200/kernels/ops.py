@@ -347,7 +347,7 @@ def gemv(a, w, out, bias=None, residual=None, relu=False):
 def gemm_tc(a, w, out, bias=None, residual=None, relu=False, splits=None, few_tokens_kernel=True, cluster=False):
     """out = epilogue(a @ w^T), bfloat16 operands, 32-bit accumulation: on the tcgen05 tensor cores,
     or (one token, unless few_tokens_kernel is False or splits is given) as a stream of the
-    weights through the multiply-add units.  `splits` forces a split of K for up to 64 tokens (a test
+    weights through the multiply-add units.  `splits` forces a split of K for up to 128 tokens (a test
     hook): partial tiles added by the CTA that finishes last, or (cluster=True, at most 8 splits) by
     the CTAs of a cluster through their shared memory, which is what the kernel's own plan uses."""
     lib = _build.load("gemm_tc")
@@ -387,12 +387,12 @@ def gemm_tc(a, w, out, bias=None, residual=None, relu=False, splits=None, few_to
             _gemm_plans.clear()
         plan = _gemm_plans[(M, N, K, st["sms"])] = (n_splits.value, nbytes.value, ncnt.value)
     n_splits, nbytes, ncnt = c_int(plan[0]), ctypes.c_longlong(plan[1]), c_int(plan[2])
-    if splits is not None and M <= 64:
+    if splits is not None and M <= lib.tnx_gemm_tc_few_tokens():
         kb = -(-K // 64)
         s = max(1, min(int(splits), kb))
         per = -(-kb // s)
         s = -(-kb // per)
-        bn = 16 if M <= 16 else (32 if M <= 32 else 64)
+        bn = 16 if M <= 16 else (32 if M <= 32 else (64 if M <= 64 else 128))
         tiles = -(-N // 128)
         n_splits, nbytes, ncnt = c_int(s), ctypes.c_longlong(s * tiles * 128 * bn * 4 if s > 1 else 0), c_int(tiles if s > 1 else 0)
         if cluster:
