@@ -276,6 +276,43 @@ def sampling_distribution(logits: torch.Tensor, temperature: float = 1.0,
     return torch.softmax(scores, dim=-1)
 
 
+def top_p_on_device(sorted_scores: torch.Tensor, top_p: float, top_p_min_tokens: int = 1) -> torch.Tensor:
+    """The reference's on-device top-p over scores sorted from the largest down (T/hlo.py:2277-2364):
+    p = softmax(scores); positions whose summed probability is still < top_p are counted; positions
+    0 .. max(top_p_min_tokens - 1, that count) are kept.  Returns the mask of kept positions."""
+    cum = torch.softmax(sorted_scores.double(), dim=-1).cumsum(dim=-1)      # 64-bit: the sums of a long row, exactly
+    keep_positions = int((cum < top_p).sum())
+    limit = max(top_p_min_tokens - 1, keep_positions)
+    return torch.arange(sorted_scores.shape[-1]) <= limit
+
+
+def multinomial_on_device(sorted_probs: torch.Tensor, uniform: float) -> int:
+    """The reference's single draw over probabilities sorted from the largest down
+    (T/hlo.py:2422-2467): the summed probabilities are divided by their last value and the answer
+    is how many of them the uniform number exceeds (`deterministic`: the number is 0.5)."""
+    cum = sorted_probs.double().cumsum(dim=-1)
+    cum = cum / cum[-1]
+    return int((uniform > cum).sum())
+
+
+def sample_on_device(logits: torch.Tensor, top_k: Optional[int], top_p: float, top_p_min_tokens: int,
+                     temperature: float, uniform: float = 0.5):
+    """One row through the reference's on-device choice (T/layers/generation.py:147-199): scores /
+    temperature, the top_k largest (sorted), top-p with its least number of tokens, softmax over
+    what is left, one draw.  Returns (token, distance of the uniform number from the nearest
+    summed probability), the latter so that a caller can tell a choice that rounding may flip."""
+    scores = logits.float() / temperature
+    k = scores.shape[-1] if not top_k else min(top_k, scores.shape[-1])
+    vals, idx = torch.topk(scores, k)                      # sorted from the largest down
+    if top_p < 1.0:
+        keep = top_p_on_device(vals, top_p, top_p_min_tokens)
+        vals, idx = vals[keep], idx[keep]
+    probs = torch.softmax(vals.double(), dim=-1)
+    j = multinomial_on_device(probs, uniform)
+    cum = probs.cumsum(-1) / probs.sum()
+    return int(idx[j]), float((cum - uniform).abs().min())
+
+
 def greedy_generate(prompt: List[int], n_new: int, weights, cfg, dtype=torch.float32) -> List[int]:
     """Greedy continuation by running the whole sequence again for each new token."""
     ids = list(prompt)

@@ -167,6 +167,52 @@ def test_eos_stops_a_request(tiny):
     assert out == first[:first.index(first[2]) + 1]
 
 
+def test_on_device_generation_config_through_the_entry_point(tiny):
+    """neuron_config=NeuronConfig(on_device_generation=...): greedy by default; with do_sample the
+    reference's fixed draw (deterministic) is followed token by token against the plain choice; with
+    eos_token_id finished rows are filled with it and the result ends where the last row finished."""
+    from transformers_neuronx_b200 import GenerationConfig, NeuronConfig
+    from transformers_neuronx_b200.opt.model import OPTForSampling
+    prompts = [tiny.random_ids(9, seed=s) for s in (4, 5)]
+    ids = torch.tensor(prompts)
+
+    def model(gen):
+        m = OPTForSampling.from_pretrained(tiny.folder, batch_size=2, amp="f32", n_positions=48,
+                                           neuron_config=NeuronConfig(on_device_generation=gen))
+        return m.to_neuron()
+
+    greedy = model(GenerationConfig()).sample(ids, sequence_length=30)
+    assert greedy.shape == (2, 30)
+    for b in range(2):
+        _assert_greedy_equal(tiny, "float32", prompts[b], greedy[b, 9:].tolist(), 21)
+
+    gen = GenerationConfig(do_sample=True, top_k=[12, 40], top_p=[0.9, 0.7], temperature=[1.5, 3.0], top_p_min_tokens=[1, 5],
+                           per_batch_line=True, deterministic=True)
+    out = model(gen).sample(ids, sequence_length=30)
+    for b in range(2):
+        k, p, t, n_min = gen.for_row(b)
+        seq = list(prompts[b])
+        for i in range(21):
+            want, margin = P.sample_on_device(tiny.plain_logits(seq)[-1], k, p, n_min, t)
+            got = int(out[b, 9 + i])
+            if got != want:
+                assert margin <= 1e-3, f"row {b} token {i}: {got}, plain {want}, margin {margin:.2e}"
+                break                                # one half lay on a summed probability: the sequences part
+            seq.append(got)
+
+    # the id that row 0 produces greedily as its 6th new token ends that row; row 1 runs on
+    eos = int(greedy[0, 9 + 5])
+    first = [t == eos for t in greedy[0, 9:].tolist()].index(True)
+    stop = model(GenerationConfig(eos_token_id=eos)).sample(ids, sequence_length=30)
+    hits1 = [i for i, t in enumerate(greedy[1, 9:].tolist()) if t == eos]
+    end = max(first, hits1[0] if hits1 else 20) + 1
+    assert stop.shape == (2, 9 + end), (stop.shape, first, hits1)
+    assert stop[0, 9:9 + first + 1].tolist() == greedy[0, 9:9 + first + 1].tolist()
+    assert all(t == eos for t in stop[0, 9 + first:].tolist())
+    n1 = (hits1[0] + 1) if hits1 else end
+    assert stop[1, 9:9 + n1].tolist() == greedy[1, 9:9 + n1].tolist()
+
+
 def test_kernel_profile(tiny):
     """The profiling helper brackets every kernel call with events and names the families."""
     from transformers_neuronx_b200.kernels import kernel_profile

@@ -469,6 +469,60 @@ def test_sampling_distribution(kw):
     assert int(keep.sum()) == 1 or not torch.equal(got, other)
 
 
+@pytest.mark.parametrize("V", [37, 1000, 50272])
+def test_sampling_with_a_fixed_uniform_number_matches_the_reference_choice(V):
+    """deterministic: the kernel takes the kept tokens from the most likely down and chooses the one
+    at which the summed probability reaches one half, which the plain on-device choice of the
+    reference gives exactly (rows where one half lies within 2e-6 of a summed probability aside: the
+    kernel's exponentials are 32-bit)."""
+    g = torch.Generator().manual_seed(V)
+    cases = [(None, 1.0, 1, 1.0), (5, 1.0, 1, 0.7), (50, 0.9, 1, 1.3), (None, 0.6, 1, 2.0), (20, 0.3, 4, 3.0),
+             (3, 0.5, 8, 5.0), (None, 0.05, 6, 4.0), (1, 1.0, 1, 1.0)]
+    n = 12 * len(cases)
+    logits = torch.randn(n, V, generator=g) * 2.5
+    ks, ps, ms, ts = [], [], [], []
+    for i in range(n):
+        k, p, m, t = cases[i % len(cases)]
+        ks.append(k or 0); ps.append(p); ms.append(m); ts.append(t)
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    ops().sample(logits.to(DEV), out, temperature=torch.tensor(ts, device=DEV), top_k=torch.tensor(ks, dtype=torch.int32, device=DEV),
+                 top_p=torch.tensor(ps, device=DEV), min_keep=torch.tensor(ms, dtype=torch.int32, device=DEV), deterministic=True)
+    got = out.cpu().tolist()
+    checked = 0
+    for i in range(n):
+        want, margin = P.sample_on_device(logits[i], ks[i] or None, ps[i], ms[i], ts[i])
+        if margin > 2e-6:
+            assert got[i] == want, f"row {i} (top_k {ks[i]}, top_p {ps[i]}, at least {ms[i]}, temperature {ts[i]})"
+            checked += 1
+    assert checked > n * 0.8
+    # without a top_p array the same kernel variant runs (it needs the mass histogram)
+    out2 = torch.empty(n, dtype=torch.int32, device=DEV)
+    ops().sample(logits.to(DEV), out2, temperature=torch.tensor(ts, device=DEV), deterministic=True)
+    for i in range(0, n, 7):
+        want, margin = P.sample_on_device(logits[i], None, 1.0, 1, ts[i])
+        assert margin <= 2e-6 or int(out2[i]) == want
+
+
+def test_sampling_top_p_keeps_at_least_min_tokens():
+    V, n = 41, 20000
+    row = torch.randn(V, generator=torch.Generator().manual_seed(13)) * 3
+    logits = row.to(DEV)[None].repeat(n, 1).contiguous()
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    full = lambda v, dt: torch.full((n,), v, dtype=dt, device=DEV)
+    for k, p, m in ((0, 0.2, 5), (10, 0.1, 3), (4, 0.1, 9), (0, 0.9999, 2)):
+        ops().sample(logits, out, temperature=full(1.5, torch.float32), top_k=full(k, torch.int32), top_p=full(p, torch.float32),
+                     min_keep=full(m, torch.int32), seeds=full(3, torch.int64), counters=torch.arange(n, dtype=torch.int64, device=DEV))
+        scores = row / 1.5
+        vals, idx = torch.topk(scores, k or V)
+        keep = P.top_p_on_device(vals, p, m)
+        kept = set(idx[keep].tolist())
+        drawn = set(out.cpu().tolist())
+        assert drawn <= kept, (k, p, m)
+        probs = torch.softmax(vals[keep], -1)
+        likely = {int(t) for t, q in zip(idx[keep], probs) if q * n > 50}
+        assert likely <= drawn, (k, p, m)
+
+
 def test_sampling_large_vocabulary_top_k():
     V = 50272
     row = torch.randn(V, generator=torch.Generator().manual_seed(12))

@@ -75,6 +75,47 @@ def test_sampling_filters():
     assert int(P.greedy_token(torch.tensor([1.0, 3.0, 3.0]))) == 1
 
 
+def test_on_device_sampling_of_the_reference():
+    probs = torch.tensor([0.4, 0.3, 0.2, 0.06, 0.04])
+    scores = probs.log()
+    assert P.top_p_on_device(scores, 0.65).tolist() == [True, True, False, False, False]     # 0.4 < 0.65 <= 0.7
+    assert P.top_p_on_device(scores, 0.65, top_p_min_tokens=4).tolist() == [True, True, True, True, False]
+    assert P.top_p_on_device(scores, 0.3).tolist() == [True, False, False, False, False]
+    assert P.multinomial_on_device(probs, 0.5) == 1 and P.multinomial_on_device(probs, 0.05) == 0
+    assert P.multinomial_on_device(probs, 0.95) == 3 and P.multinomial_on_device(probs[:2], 0.5) == 0     # 0.4 / 0.7 > 0.5
+    logits = torch.tensor([0.0, 3.0, 1.0, 2.5, -1.0, 2.0])
+    tok, _ = P.sample_on_device(logits, top_k=3, top_p=1.0, top_p_min_tokens=1, temperature=1.0)
+    assert tok == 1                                       # softmax(3, 2.5, 2) = .51 .31 .19: the first crosses one half
+    tok, _ = P.sample_on_device(logits, top_k=3, top_p=1.0, top_p_min_tokens=1, temperature=4.0)
+    assert tok == 3                                       # flatter: .38 .33 .29, the second crosses
+    tok, _ = P.sample_on_device(logits, top_k=None, top_p=0.3, top_p_min_tokens=1, temperature=4.0)
+    assert tok == 1                                       # top-p leaves one token
+    tok, _ = P.sample_on_device(logits, top_k=None, top_p=0.3, top_p_min_tokens=3, temperature=4.0)
+    assert tok == 3
+
+
+def test_generation_config():
+    from transformers_neuronx_b200 import GenerationConfig, NeuronConfig
+    g = GenerationConfig()
+    assert g.is_greedy() and g.for_row(0) == (50, 1.0, 1.0, 1) and g.eos_ids() is None
+    g = GenerationConfig(do_sample=True, top_k=[5, None], top_p=[0.9, 1.0], temperature=[0.5, 2.0], top_p_min_tokens=[1, 3],
+                         per_batch_line=True, dynamic=True, global_top_k=4, eos_token_id=[2, 7])
+    assert not g.is_greedy() and g.for_row(0) == (4, 0.9, 0.5, 1) and g.for_row(1) == (4, 1.0, 2.0, 3) and g.eos_ids() == [2, 7]
+    assert GenerationConfig(dynamic=True).is_greedy() is False          # a dynamic configuration always samples
+    for bad in (dict(top_p=1.5), dict(top_p_min_tokens=0), dict(top_k=0), dict(temperature=0.0), dict(global_top_k=5),
+                dict(top_k=[1, 2])):
+        try:
+            GenerationConfig(**bad)
+        except ValueError:
+            continue
+        raise AssertionError(f"{bad} was accepted")
+    import warnings
+    with warnings.catch_warnings(record=True) as w:
+        warnings.simplefilter("always")
+        n = NeuronConfig(on_device_generation=g, fuse_qkv=True, quant="int8")
+    assert n.on_device_generation is g and list(n.ignored) == ["quant"] and len(w) == 1
+
+
 def test_greedy_generate():
     m = TinyModel("A", seed=4)
     out = P.greedy_generate(m.random_ids(6, seed=1), 5, m.tensors, m.cfg.to_dict())

@@ -3,3 +3,5 @@ weights by name, layers put together from parts, a paged cache, one step functio
 sampling, and hand-written CUDA kernels.  Capabilities follow aws-neuron/transformers-neuronx's OPT
 support; the design does not."""
 __version__ = "0.1.0"
+
+from .config.generation_config import GenerationConfig, NeuronConfig      # as `from transformers_neuronx import ...`

@@ -2,3 +2,4 @@ from .model_config import OPTConfig, ConfigError
 from .engine_config import EngineConfig, canonical_dtype
 from .registry import (Architecture, register_architecture, resolve_architecture, architectures,
                        load_config)
+from .generation_config import GenerationConfig, NeuronConfig

@@ -58,6 +58,7 @@ template <bool TOP_P>
 __global__ void __launch_bounds__(THREADS)
 sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const float* __restrict__ top_p,
+              const int* __restrict__ min_keep, int deterministic,
               const unsigned long long* __restrict__ seeds, const unsigned long long* __restrict__ counters,
               int suppress_id, int* __restrict__ out) {
     __shared__ unsigned long long warp_hist64[TOP_P ? GROUPS * 256 : THREADS];
@@ -102,10 +103,9 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
     for (int i = tid; i < V; i += THREADS) mx = fmaxf(mx, SCORE(i));
     mx = block_max(mx, fscratch);
 
-    // ---- top-k: the key of the k-th largest score (0 keeps everything) ----------------------
-    uint32_t thr = 0;
-    const int k = top_k ? top_k[r] : 0;
-    if (k > 0 && k < V) {
+    // The key of the k-th largest score, by radix selection on the keys' four bytes (1 <= k < V).
+    auto kth_largest_key = [&](int k) -> uint32_t {
+        __syncthreads();
         if (tid == 0) { sh_prefix = 0; sh_remaining = (unsigned)k; }
         uint32_t mask = 0;
         for (int shift = 24; shift >= 0; shift -= 8) {
@@ -151,25 +151,13 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
             mask |= 255u << shift;
             __syncthreads();
         }
-        thr = sh_prefix;
-    }
+        return sh_prefix;
+    };
 
-    // ---- top-p over the tokens that top-k kept -------------------------------------------------
-    const float P = (TOP_P && top_p) ? top_p[r] : 1.f;
-    if (TOP_P && P < 1.f) {
-        unsigned long long local = 0;
-        for (int i = tid; i < V; i += THREADS) {
-            const float s = SCORE(i);
-            if (ordered_key(s) >= thr) local += mass_of(s, mx);
-        }
-        if (tid == 0) sh_total = 0;
+    // Of the tokens with keys >= floor_key, taken from the most likely down: the lowest key that is
+    // still kept when a token is kept as long as the mass of all keys above its own is < limit.
+    auto lowest_key_within_mass = [&](unsigned long long limit, uint32_t floor_key) -> uint32_t {
         __syncthreads();
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
-        if ((tid & 31) == 0) atomicAdd(&sh_total, local);
-        __syncthreads();
-        unsigned long long limit = (unsigned long long)((double)P * (double)sh_total);
-        if (limit < 1) limit = 1;                      // the most likely token is always kept
         if (tid == 0) { sh_prefix = 0; sh_above = 0; }
         uint32_t mask = 0;
         for (int shift = 24; shift >= 0; shift -= 8) {
@@ -180,7 +168,7 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
             for (int i = tid; i < V; i += THREADS) {
                 const float s = SCORE(i);
                 const uint32_t key = ordered_key(s);
-                if (key >= thr && (key & mask) == prefix) atomicAdd(&mine64[(key >> shift) & 255u], mass_of(s, mx));
+                if (key >= floor_key && (key & mask) == prefix) atomicAdd(&mine64[(key >> shift) & 255u], mass_of(s, mx));
             }
             __syncthreads();
             if (tid < 256) {
@@ -222,7 +210,64 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
             mask |= 255u << shift;
             __syncthreads();
         }
-        if (sh_prefix > thr) thr = sh_prefix;
+        return sh_prefix;
+    };
+
+    // The mass of all tokens with keys >= floor_key.
+    auto mass_from = [&](uint32_t floor_key) -> unsigned long long {
+        unsigned long long local = 0;
+        for (int i = tid; i < V; i += THREADS) {
+            const float s = SCORE(i);
+            if (ordered_key(s) >= floor_key) local += mass_of(s, mx);
+        }
+        __syncthreads();
+        if (tid == 0) sh_total = 0;
+        __syncthreads();
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
+        if ((tid & 31) == 0) atomicAdd(&sh_total, local);
+        __syncthreads();
+        return sh_total;
+    };
+
+    // ---- top-k: the key of the k-th largest score (0 keeps everything) ----------------------
+    uint32_t thr = 0;
+    const int k = top_k ? top_k[r] : 0;
+    if (k > 0 && k < V) thr = kth_largest_key(k);
+
+    // ---- top-p over the tokens that top-k kept, but never fewer than min_keep of them ----------
+    const float P = (TOP_P && top_p) ? top_p[r] : 1.f;
+    if (TOP_P && P < 1.f) {
+        unsigned long long limit = (unsigned long long)((double)P * (double)mass_from(thr));
+        if (limit < 1) limit = 1;                      // the most likely token is always kept
+        uint32_t thr_p = lowest_key_within_mass(limit, thr);
+        const int n_min = min_keep ? min_keep[r] : 1;
+        if (n_min > 1) {
+            const uint32_t thr_n = n_min < V ? kth_largest_key(n_min) : 0u;
+            if (thr_n < thr_p) thr_p = thr_n;
+        }
+        if (thr_p > thr) thr = thr_p;
+    }
+
+    // ---- the reference's fixed draw (its uniform replaced by 0.5): the kept tokens from the most
+    // likely down, the first at which the summed probability reaches one half; the lowest index of a tie
+    if (TOP_P && deterministic) {
+        const unsigned long long total = mass_from(thr);
+        if (total == 0) { if (tid == 0) out[r] = 0; return; }
+        const uint32_t key = lowest_key_within_mass((total + 1) / 2, thr);
+        int first = 0x7fffffff;
+        for (int i = tid; i < V; i += THREADS)
+            if (ordered_key(SCORE(i)) == key) { first = i; break; }
+        for (int o = 16; o > 0; o >>= 1) first = min(first, __shfl_xor_sync(0xffffffffu, first, o));
+        __syncthreads();
+        if ((tid & 31) == 0) ascratch[tid >> 5].i = first;
+        __syncthreads();
+        if (tid < 32) {
+            first = ascratch[tid].i;
+            for (int o = 16; o > 0; o >>= 1) first = min(first, __shfl_xor_sync(0xffffffffu, first, o));
+            if (tid == 0) out[r] = first == 0x7fffffff ? 0 : first;
+        }
+        return;
     }
 
     // ---- inverse CDF in index order over the kept tokens --------------------------------------
@@ -279,14 +324,17 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
 }
 }  // namespace
 
+// min_keep (per row, may be null: 1): top-p never keeps fewer tokens than this.  deterministic: the
+// draw's uniform number is replaced by one half and the tokens are taken from the most likely down.
 TNX_EXPORT int tnx_sample(const float* logits, int ld, int n_rows, int V, const float* temperature,
-                          const int* top_k, const float* top_p, const unsigned long long* seeds,
-                          const unsigned long long* counters, int suppress_id, int* out, cudaStream_t stream) {
+                          const int* top_k, const float* top_p, const int* min_keep, int deterministic,
+                          const unsigned long long* seeds, const unsigned long long* counters, int suppress_id,
+                          int* out, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (V <= 0 || ld < V) return TNX_ERR_BAD_ARG;
-    if (top_p)
+    if (top_p || deterministic)
         return tnx_launch_pdl(sample_kernel<true>, dim3(n_rows), dim3(THREADS), 0, stream, logits, ld, V, temperature, top_k,
-                              top_p, seeds, counters, suppress_id, out);
+                              top_p, min_keep, deterministic, seeds, counters, suppress_id, out);
     return tnx_launch_pdl(sample_kernel<false>, dim3(n_rows), dim3(THREADS), 0, stream, logits, ld, V, temperature, top_k,
-                          top_p, seeds, counters, suppress_id, out);
+                          top_p, min_keep, deterministic, seeds, counters, suppress_id, out);
 }

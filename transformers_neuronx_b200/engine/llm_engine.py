@@ -40,12 +40,12 @@ class LLMEngine:
         self.stats = {"steps": 0, "tokens_run": 0, "tokens_sampled": 0, "preemptions": 0}
 
     def add_request(self, prompt: Sequence[int], max_new_tokens: int, params: Optional[SamplingParams] = None,
-                    rid: Optional[Hashable] = None, stop_on_eos: bool = True) -> Hashable:
+                    rid: Optional[Hashable] = None, stop_on_eos: bool = True, eos_token_id=None) -> Hashable:
         rid = next(self._ids) if rid is None else rid
         if rid in self.requests and not self.requests[rid].finished:
             raise ValueError(f"request {rid!r} is still running")
         req = Request(rid, [int(t) for t in prompt], int(max_new_tokens), params or SamplingParams(),
-                      stop_on_eos=stop_on_eos, eos_token_id=self.eos_token_id)
+                      stop_on_eos=stop_on_eos, eos_token_id=self.eos_token_id if eos_token_id is None else eos_token_id)
         self.scheduler.add(req)
         self.requests[rid] = req
         return rid
@@ -101,6 +101,9 @@ class LLMEngine:
                                              all(r.params.suppress_eos for r in rows)) else -1
             if suppress < 0 and any(r.params.suppress_eos for r in rows):
                 raise ValueError("suppress_eos must be set for all requests of a step or for none")
+            deterministic = rows[0].params.deterministic
+            if any(r.params.deterministic != deterministic for r in rows):
+                raise ValueError("deterministic must be set for all requests of a step or for none")
             if self._ids_dev[self._parity].shape[0] < R:
                 self._ids_dev = [torch.zeros(2 * R, dtype=torch.int32, device=self.model.device) for _ in range(2)]
                 self._ids_host = [torch.zeros(2 * R, dtype=torch.int32).pin_memory() for _ in range(2)]
@@ -110,7 +113,8 @@ class LLMEngine:
             self.sampler.sample(
                 logits, [r.params.temperature for r in rows], [r.params.top_k for r in rows],
                 [r.params.top_p for r in rows], [r.params.seed for r in rows],
-                [len(r.output) for r in rows], suppress_id=suppress, out=out)
+                [len(r.output) for r in rows], suppress_id=suppress, out=out,
+                min_keeps=[r.params.top_p_min_tokens for r in rows], deterministic=deterministic)
             host = self._ids_host[self._parity]
             host[:R].copy_(out[:R], non_blocking=True)            # the step's device-to-host read, waited for later
             ev = self._events[self._parity]
@@ -148,7 +152,7 @@ class LLMEngine:
                     continue                                   # cut off by an earlier end-of-sequence token
                 req.output[place] = tok
                 req._all[len(req.prompt) + place] = tok
-                if req.stop_on_eos and req.eos_token_id is not None and tok == req.eos_token_id:
+                if req.stop_on_eos and req.is_eos(tok):
                     del req.output[place + 1:]
                     del req._all[len(req.prompt) + place + 1:]
                     if not req.finished:
@@ -165,12 +169,13 @@ class LLMEngine:
         return ready
 
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens, params=None,
-                 stop_on_eos: bool = True) -> List[List[int]]:
+                 stop_on_eos: bool = True, eos_token_id=None) -> List[List[int]]:
         """Runs the given prompts to the end; returns the new tokens of each."""
         n = len(prompts)
         mnt = max_new_tokens if isinstance(max_new_tokens, (list, tuple)) else [max_new_tokens] * n
         ps = params if isinstance(params, (list, tuple)) else [params] * n
-        rids = [self.add_request(p, m, q, stop_on_eos=stop_on_eos) for p, m, q in zip(prompts, mnt, ps)]
+        rids = [self.add_request(p, m, q, stop_on_eos=stop_on_eos, eos_token_id=eos_token_id)
+                for p, m, q in zip(prompts, mnt, ps)]
         while self.has_work():
             self.step()
         out = [self.requests[r].output for r in rids]

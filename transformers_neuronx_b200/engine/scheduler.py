@@ -35,6 +35,8 @@ class SamplingParams:
     top_p: float = 1.0              # 1: off
     seed: int = 0
     suppress_eos: bool = False      # never sample the end-of-sequence token (sampling.py:144)
+    top_p_min_tokens: int = 1       # the fewest tokens top-p keeps (config.py:113, hlo.py:2349-2361)
+    deterministic: bool = False     # the draw's uniform number is one half (config.py:118, hlo.py:2452-2453)
 
 
 @dataclass
@@ -44,13 +46,19 @@ class Request:
     max_new_tokens: int
     params: SamplingParams = field(default_factory=SamplingParams)
     stop_on_eos: bool = True
-    eos_token_id: Optional[int] = None
+    eos_token_id: Optional[object] = None      # one id, or several (any of them ends the request)
     # progress
     output: List[int] = field(default_factory=list)
     computed: int = 0               # tokens of prompt+output whose keys/values are in the cache
     finished: bool = False
     preemptions: int = 0
     arrival: int = 0
+
+    def is_eos(self, tok: int) -> bool:
+        e = self.eos_token_id
+        if e is None:
+            return False
+        return tok in e if isinstance(e, (list, tuple, set, frozenset)) else tok == e
 
     def __post_init__(self):
         self._all = list(self.prompt) + list(self.output)      # prompt and output as one list, kept in step
@@ -245,7 +253,7 @@ class Scheduler:
                 continue
             tok = int(sampled[req.rid])
             req.append_output(tok)
-            hit_eos = req.stop_on_eos and req.eos_token_id is not None and tok == req.eos_token_id
+            hit_eos = req.stop_on_eos and req.is_eos(tok)
             if len(req.output) >= req.max_new_tokens or hit_eos:
                 req.finished = True
                 self.running.remove(req)

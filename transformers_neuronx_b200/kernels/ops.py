@@ -245,22 +245,26 @@ def attention_simt(q, cache, block_tables, token_request, positions, out, n_head
                                   c_float(scale), c_int(_is_bf16(cache)), _stream()), "attention_simt")
 
 
-def sample(logits, out, temperature=None, top_k=None, top_p=None, seeds=None, counters=None, suppress_id=-1):
+def sample(logits, out, temperature=None, top_k=None, top_p=None, seeds=None, counters=None, suppress_id=-1,
+           min_keep=None, deterministic=False):
     """out[r] = next token of row r; per-row float32 temperature (<= 0: greedy), int32 top_k
-    (0: off), float32 top_p (1: off), int64 seeds and counters for the Philox draw."""
+    (0: off), float32 top_p (1: off), int32 min_keep (the fewest tokens top-p keeps; None: 1), int64
+    seeds and counters for the Philox draw.  deterministic: no draw; the kept tokens are taken from
+    the most likely down and the first at which the summed probability reaches one half is chosen."""
     lib = _build.load("sampling")
     _need(logits, "logits", torch.float32, None, contiguous=False)
     R, V, ld = _rows_2d(logits, "logits")
     _need(out, "out", torch.int32, 1)
     for t, nm, dt in ((temperature, "temperature", torch.float32), (top_k, "top_k", torch.int32),
-                      (top_p, "top_p", torch.float32), (seeds, "seeds", torch.int64),
-                      (counters, "counters", torch.int64)):
+                      (top_p, "top_p", torch.float32), (min_keep, "min_keep", torch.int32),
+                      (seeds, "seeds", torch.int64), (counters, "counters", torch.int64)):
         if t is not None:
             _need(t, nm, dt, 1)
             if t.shape[0] < R:
                 raise KernelError(f"{nm} has fewer entries than there are rows")
     _check(lib.tnx_sample(_p(logits), c_int(ld), c_int(R), c_int(V), _p(temperature), _p(top_k), _p(top_p),
-                          _p(seeds), _p(counters), c_int(suppress_id), _p(out), _stream()), "sample")
+                          _p(min_keep), c_int(1 if deterministic else 0), _p(seeds), _p(counters),
+                          c_int(suppress_id), _p(out), _stream()), "sample")
 
 
 # ---------------------------------------------------------------------------------------------

@@ -9,9 +9,11 @@ total length (prompt included); ``sample`` draws from the top_k (default 50) mos
 never draws the end-of-sequence token (sampling.py:26-30, :131-180); ``top_k=1`` is greedy, as in
 the reference's own validation (testing/validation.py:68-101); ``forward(input_ids, cache_ids,
 start_ids)`` returns the 32-bit logits [batch, vocab] of each row's last token; ``start_ids`` marks
-left padding.  ``tp_degree``, ``unroll``, ``context_length_estimate`` and ``neuron_config`` have no
-meaning on one GPU and are accepted and ignored with a warning.  ``to_neuron`` loads the weights
-onto the GPU and compiles the kernels that the model needs.
+left padding.  With ``neuron_config=NeuronConfig(on_device_generation=GenerationConfig(...))``
+``sample`` chooses tokens as that configuration says (opt/model.py:187-189, sampling.py:34-105).
+``tp_degree``, ``unroll`` and ``context_length_estimate`` have no meaning on one GPU and are accepted
+and ignored with a warning.  ``to_neuron`` loads the weights onto the GPU and compiles the kernels
+that the model needs.
 """
 from __future__ import annotations
 
@@ -21,7 +23,7 @@ from typing import List, Optional
 
 import torch
 
-from ..config import EngineConfig, OPTConfig, canonical_dtype, load_config
+from ..config import EngineConfig, GenerationConfig, NeuronConfig, OPTConfig, canonical_dtype, load_config
 from ..engine import LLMEngine, SamplingParams, StepEntry, load_model
 
 
@@ -29,9 +31,12 @@ class OPTForSampling:
     def __init__(self, folder: str, config: OPTConfig, batch_size=1, amp=None, tp_degree=None, n_positions=2048,
                  unroll=None, context_length_estimate=None, context_unroll=None, neuron_config=None, **kwargs):
         for name, val in (("tp_degree", tp_degree), ("unroll", unroll), ("context_unroll", context_unroll),
-                          ("context_length_estimate", context_length_estimate), ("neuron_config", neuron_config)):
+                          ("context_length_estimate", context_length_estimate)):
             if val is not None:
                 warnings.warn(f"{name}={val!r} has no meaning for the one-GPU engine and is ignored")
+        if neuron_config is not None and not isinstance(neuron_config, NeuronConfig):
+            raise TypeError("neuron_config must be a NeuronConfig of this package")
+        self.neuron_config = neuron_config or NeuronConfig()
         if kwargs:
             raise KeyError(f"unknown argument(s): {sorted(kwargs)}")
         if amp is None:
@@ -85,10 +90,15 @@ class OPTForSampling:
     # ---- generation ---------------------------------------------------------------------------------
     def sample(self, input_ids, sequence_length, start_ids=None, top_k=50, streamer=None, temperature=1.0,
                top_p=1.0, seed=0):
-        """[batch, prompt] ids -> [batch, sequence_length] ids (prompt included)."""
+        """[batch, prompt] ids -> [batch, sequence_length] ids (prompt included).  With an
+        on_device_generation configuration the tokens are chosen as it says and top_k, temperature
+        and top_p of this call are not used."""
         self._ready()
         input_ids = torch.as_tensor(input_ids)
         B, T0 = input_ids.shape
+        if self.neuron_config.on_device_generation is not None:
+            return self._sample_tokens(input_ids, sequence_length, start_ids, self.neuron_config.on_device_generation,
+                                       streamer, seed)
         if B > self.batch_size:
             raise ValueError(f"batch of {B} rows; the model was made for batch_size={self.batch_size}")
         if sequence_length > self.n_positions:
@@ -106,6 +116,42 @@ class OPTForSampling:
         result = torch.cat([input_ids, torch.as_tensor(outs, dtype=input_ids.dtype)], dim=1)
         if streamer is not None:
             for t in range(T0, sequence_length):
+                streamer.put(result[:, t:t + 1])
+            streamer.end()
+        return result
+
+    def _sample_tokens(self, input_ids, sequence_length, start_ids, gen: GenerationConfig, streamer, seed):
+        """The reference's loop for a model that chooses its tokens itself (sampling.py:34-105):
+        without eos_token_id every row runs to sequence_length; with it, a row that produced the id
+        is filled with it from there on and the result ends where the last row finished."""
+        B, T0 = input_ids.shape
+        if B > self.batch_size:
+            raise ValueError(f"batch of {B} rows; the model was made for batch_size={self.batch_size}")
+        limit = self.n_positions if gen.max_length is None else min(self.n_positions, int(gen.max_length))
+        if sequence_length > limit:
+            raise ValueError(f"sequence_length {sequence_length} exceeds the longest sequence {limit}")
+        starts = [0] * B if start_ids is None else [int(s) for s in torch.as_tensor(start_ids).tolist()]
+        rows = input_ids.tolist()
+        prompts = [rows[b][starts[b]:] for b in range(B)]
+        n_new = sequence_length - T0
+        if n_new <= 0:
+            return input_ids[:, :sequence_length]
+        params = []
+        for b in range(B):
+            k, p, t, n_min = gen.for_row(b)
+            if gen.is_greedy():
+                params.append(SamplingParams(temperature=0.0))
+            else:
+                params.append(SamplingParams(temperature=t, top_k=k, top_p=p, seed=int(seed) + b, top_p_min_tokens=n_min,
+                                             deterministic=gen.deterministic))
+        eos = gen.eos_ids()
+        outs = self.engine.generate(prompts, n_new, params, stop_on_eos=eos is not None,
+                                    eos_token_id=tuple(eos) if eos else None)
+        length = max(len(o) for o in outs)
+        outs = [o + [eos[0]] * (length - len(o)) for o in outs] if eos else outs
+        result = torch.cat([input_ids, torch.as_tensor(outs, dtype=input_ids.dtype)], dim=1)
+        if streamer is not None:
+            for t in range(T0, result.shape[1]):
                 streamer.put(result[:, t:t + 1])
             streamer.end()
         return result
