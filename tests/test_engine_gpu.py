@@ -213,6 +213,70 @@ def test_on_device_generation_config_through_the_entry_point(tiny):
     assert stop[1, 9:9 + n1].tolist() == greedy[1, 9:9 + n1].tolist()
 
 
+def test_streamer_gets_tokens_while_they_are_generated(tiny):
+    from transformers_neuronx_b200 import GenerationConfig, NeuronConfig
+    from transformers_neuronx_b200.opt.model import OPTForSampling
+    model = OPTForSampling.from_pretrained(tiny.folder, batch_size=2, amp="f32", n_positions=40).to_neuron()
+
+    class Recorder:
+        def __init__(self):
+            self.cols, self.at_step, self.ended = [], [], False
+
+        def put(self, t):
+            assert not self.ended and tuple(t.shape) == (2, 1)
+            self.cols.append(t.clone()); self.at_step.append(model.engine.stats["steps"])
+
+        def end(self):
+            self.ended = True
+
+    ids = torch.tensor([tiny.random_ids(7, seed=s) for s in (8, 9)])
+    rec = Recorder()
+    out = model.sample(ids, sequence_length=25, top_k=1, streamer=rec)
+    assert rec.ended and torch.equal(torch.cat(rec.cols, dim=1), out[:, 7:])
+    assert rec.at_step[-1] - rec.at_step[0] >= 15, "the tokens came while the engine was stepping, not at the end"
+    assert torch.equal(out, model.sample(ids, sequence_length=25, top_k=1))
+    # with early stop: the streamed columns are the returned ones, finished rows filled with the id
+    eos = int(out[0, 7 + 4])
+    stopping = OPTForSampling.from_pretrained(tiny.folder, batch_size=2, amp="f32", n_positions=40, neuron_config=NeuronConfig(
+        on_device_generation=GenerationConfig(eos_token_id=eos))).to_neuron()
+    rec2 = Recorder()
+    model = stopping
+    out2 = stopping.sample(ids, sequence_length=25, streamer=rec2)
+    assert rec2.ended and torch.equal(torch.cat(rec2.cols, dim=1), out2[:, 7:])
+    assert torch.equal(out2, stopping.sample(ids, sequence_length=25))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_tapped_hidden_states_match_the_plain_layers(tiny, dtype):
+    """model.tap_hidden_states(): the residual stream after the embedding and after every layer, for
+    a prompt run in two portions, against the plain implementation layer by layer (a fault shows at
+    the first layer that has it); captured graphs are not used while tapping and are used after."""
+    from transformers_neuronx_b200.engine import StepEntry, StepRunner, load_model
+    model, _ = load_model(tiny.folder, dtype, verbose=False)
+    runner = StepRunner(model, 16, 8, 2, 128, use_cuda_graphs=True)
+    ids = tiny.random_ids(45, seed=31)
+    cfg = tiny.cfg.to_dict()
+    w = {k: v.float() for k, v in tiny.tensors.items()}
+    want = [P.embed(torch.tensor(ids), w)]
+    for i in range(cfg["num_hidden_layers"]):
+        want.append(P.decoder_layer(want[-1], w, i, cfg))
+    runner.add_request("t")
+    with model.tap_hidden_states() as taps:
+        runner.step([StepEntry("t", ids[:29], [])])
+        first = {k: v.cpu() for k, v in taps.items()}
+        lg = runner.step([StepEntry("t", ids[29:], [15])])
+        second = {k: v.cpu() for k, v in taps.items()}
+    assert not runner.captured_steps() and "logits" not in first and torch.equal(second["logits"], lg.cpu())
+    tol = TOLERANCE[dtype]
+    for name, i in [("embedding", 0)] + [(f"entry{j}", j + 1) for j in range(cfg["num_hidden_layers"])]:
+        got = torch.cat([first[name], second[name]])
+        err = float((got - want[i]).abs().max()) / float(want[i].abs().max())
+        assert err <= tol, f"{dtype} {name}: {err:.2e}"
+    for t in range(3):                                        # afterwards single tokens are captured again
+        runner.step([StepEntry("t", [ids[t]], [0])])
+    assert runner.captured_steps()
+
+
 def test_kernel_profile(tiny):
     """The profiling helper brackets every kernel call with events and names the families."""
     from transformers_neuronx_b200.kernels import kernel_profile

@@ -11,6 +11,7 @@ device once, run the model.
 """
 from __future__ import annotations
 
+import gc
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence
 
@@ -418,9 +419,18 @@ class StepRunner:
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             n0 = ops.launch_count()
-            with torch.cuda.graph(graph, pool=self._graph_pool):
-                with ops.stream_scope():
-                    g["logits"] = self.model.forward(ctx)
+            # Garbage that owns device memory (an older runner's graphs and their pool) must not be
+            # collected while the stream is capturing: freeing device memory invalidates the capture.
+            gc.collect()
+            gc_was_on = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph, pool=self._graph_pool):
+                    with ops.stream_scope():
+                        g["logits"] = self.model.forward(ctx)
+            finally:
+                if gc_was_on:
+                    gc.enable()
             g["kernels"] = ops.launch_count() - n0       # recorded, not run
             ops.add_launches(-g["kernels"])
             g["graph"] = graph
@@ -450,10 +460,11 @@ class StepRunner:
         """Runs one step; returns the 32-bit logits [wanted, vocab] (a device tensor) in the order
         of the entries and of their `want`.  `sampled` (int32, device): ids sampled in the step
         before, for entries with `from_device`."""
-        if self.use_cuda_graphs and all(len(e.tokens) == 1 for e in entries) and len(entries) <= self.max_graph_batch:
+        graphs = self.use_cuda_graphs and getattr(self.model, "graph_safe", True)      # not while results are tapped
+        if graphs and all(len(e.tokens) == 1 for e in entries) and len(entries) <= self.max_graph_batch:
             self._validate(entries)
             logits = self._graph_step(entries, sampled)
-        elif self.use_cuda_graphs and (key := self._small_step_key(entries)) is not None:
+        elif graphs and (key := self._small_step_key(entries)) is not None:
             self._validate(entries)
             logits = self._small_graph_step(key, entries, sampled)
         else:

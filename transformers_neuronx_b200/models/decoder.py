@@ -2,7 +2,8 @@
 head.  It knows no architecture: models/opt.py (or a test) supplies the specification."""
 from __future__ import annotations
 
-from typing import Dict, List
+import contextlib
+from typing import Dict, List, Optional
 
 import torch
 
@@ -28,6 +29,22 @@ class DecoderModel:
                 raise ValueError(f"schedule names layer {e.layer}, the model has {len(self.blocks)}")
         self.device = None
         self.act_dtype = None
+        self._taps: Optional[Dict[str, torch.Tensor]] = None
+
+    # ---- taps -----------------------------------------------------------------------------------
+    @contextlib.contextmanager
+    def tap_hidden_states(self):
+        """Inside the block every step leaves copies of its intermediate results in the dictionary
+        that is yielded: "embedding", "entry<i>" (the 32-bit residual stream [tokens, hidden] after
+        the i-th schedule entry) and "logits"; a later step overwrites them.  Steps run eagerly
+        meanwhile (a captured graph would write into buffers of its own).  The counterpart of the
+        reference's named debug tensors (src/transformers_neuronx/global_debugger.py:27-91)."""
+        taps: Dict[str, torch.Tensor] = {}
+        prev, self._taps = self._taps, taps
+        try:
+            yield taps
+        finally:
+            self._taps = prev
 
     # ---- parts, tensors, kernels --------------------------------------------------------------
     def all_parts(self):
@@ -57,8 +74,9 @@ class DecoderModel:
 
     @property
     def graph_safe(self) -> bool:
-        """Whether a decode step of this model can be captured in a CUDA graph (every part says so)."""
-        return all(getattr(p, "graph_safe", False) for p in self.all_parts())
+        """Whether a step of this model can be captured in a CUDA graph now (every part says so,
+        and nobody is tapping intermediate results)."""
+        return self._taps is None and all(getattr(p, "graph_safe", False) for p in self.all_parts())
 
     def cache_needs(self) -> Dict[int, object]:
         """{cache id -> what the mixer(s) using it keep}; entries sharing a cache must agree."""
@@ -99,7 +117,11 @@ class DecoderModel:
         x_act = ctx.empty(N, H) if want_act else None
         self.embedding.forward(ctx, x, x_act if (first is not None and first.needs_act_input) else None)
         act_current = first is not None and first.needs_act_input
-        for e in self.spec.schedule:
+        taps = self._taps
+        if taps is not None:
+            taps.clear()
+            taps["embedding"] = x.clone()
+        for i, e in enumerate(self.spec.schedule):
             block = self.blocks[e.layer]
             if block.needs_act_input and not act_current:
                 ops.pick_rows(x, None, out_act=x_act)
@@ -107,6 +129,11 @@ class DecoderModel:
             ctx.begin_entry()
             block.forward(ctx, x, x_act)
             act_current = block.keeps_act_current
+            if taps is not None:
+                taps[f"entry{i}"] = x.clone()
         if ctx.logit_rows is None or ctx.logit_rows.shape[0] == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=ctx.device)
-        return self.head.forward(ctx, x, ctx.logit_rows)
+        logits = self.head.forward(ctx, x, ctx.logit_rows)
+        if taps is not None:
+            taps["logits"] = logits.clone()
+        return logits

@@ -112,13 +112,45 @@ class OPTForSampling:
         greedy = top_k == 1
         params = [SamplingParams(temperature=0.0 if greedy else float(temperature), top_k=0 if greedy else int(top_k or 0),
                                  top_p=float(top_p), seed=int(seed) + b, suppress_eos=True) for b in range(B)]
-        outs = self.engine.generate(prompts, n_new, params, stop_on_eos=False)
-        result = torch.cat([input_ids, torch.as_tensor(outs, dtype=input_ids.dtype)], dim=1)
-        if streamer is not None:
-            for t in range(T0, sequence_length):
-                streamer.put(result[:, t:t + 1])
+        outs = self._generate(prompts, n_new, params, streamer, input_ids.dtype)
+        return torch.cat([input_ids, torch.as_tensor(outs, dtype=input_ids.dtype)], dim=1)
+
+    def _generate(self, prompts, n_new, params, streamer, dtype, eos=None):
+        """Runs the rows to the end.  With a streamer every new column of tokens is handed to it
+        (`put` of a [batch, 1] tensor) as soon as all its ids are known, and `end` is called last
+        (sampling.py:159-160, :172-173); rows that are finished are filled with the first eos id."""
+        eng = self.engine
+        stop = eos is not None
+        if streamer is None:
+            outs = eng.generate(prompts, n_new, params, stop_on_eos=stop, eos_token_id=eos)
+        else:
+            rids = [eng.add_request(p, n_new, q, stop_on_eos=stop, eos_token_id=eos) for p, q in zip(prompts, params)]
+            reqs = [eng.requests[r] for r in rids]
+            sent = 0
+            while eng.has_work():
+                eng.step()
+                while True:
+                    col = []
+                    for r in reqs:
+                        if sent < len(r.output) and r.output[sent] != eng.PENDING:
+                            col.append(r.output[sent])
+                        elif r.finished and sent >= len(r.output) and stop and any(sent < len(o.output) for o in reqs):
+                            col.append(eos[0])
+                        else:
+                            col = None
+                            break
+                    if col is None:
+                        break
+                    streamer.put(torch.tensor(col, dtype=dtype)[:, None])
+                    sent += 1
             streamer.end()
-        return result
+            outs = [r.output for r in reqs]
+            for rid in rids:
+                del eng.requests[rid]
+        if stop:
+            length = max(len(o) for o in outs)
+            outs = [o + [eos[0]] * (length - len(o)) for o in outs]
+        return outs
 
     def _sample_tokens(self, input_ids, sequence_length, start_ids, gen: GenerationConfig, streamer, seed):
         """The reference's loop for a model that chooses its tokens itself (sampling.py:34-105):
@@ -145,16 +177,8 @@ class OPTForSampling:
                 params.append(SamplingParams(temperature=t, top_k=k, top_p=p, seed=int(seed) + b, top_p_min_tokens=n_min,
                                              deterministic=gen.deterministic))
         eos = gen.eos_ids()
-        outs = self.engine.generate(prompts, n_new, params, stop_on_eos=eos is not None,
-                                    eos_token_id=tuple(eos) if eos else None)
-        length = max(len(o) for o in outs)
-        outs = [o + [eos[0]] * (length - len(o)) for o in outs] if eos else outs
-        result = torch.cat([input_ids, torch.as_tensor(outs, dtype=input_ids.dtype)], dim=1)
-        if streamer is not None:
-            for t in range(T0, result.shape[1]):
-                streamer.put(result[:, t:t + 1])
-            streamer.end()
-        return result
+        outs = self._generate(prompts, n_new, params, streamer, input_ids.dtype, eos=tuple(eos) if eos else None)
+        return torch.cat([input_ids, torch.as_tensor(outs, dtype=input_ids.dtype)], dim=1)
 
     # ---- the static-batch forward of the reference ---------------------------------------------------------
     def reset(self):
