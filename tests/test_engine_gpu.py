@@ -277,6 +277,43 @@ def test_tapped_hidden_states_match_the_plain_layers(tiny, dtype):
     assert runner.captured_steps()
 
 
+def test_generate_adapter_with_left_padded_rows(tiny):
+    from transformers_neuronx_b200.generation_utils import HuggingFaceGenerationModelAdapter
+    from transformers_neuronx_b200.opt.model import OPTForSampling
+    model = OPTForSampling.from_pretrained(tiny.folder, batch_size=3, amp="f32", n_positions=48).to_neuron()
+    adapter = HuggingFaceGenerationModelAdapter(model.config, model)
+    prompts = [tiny.random_ids(n, seed=40 + n) for n in (5, 9, 12)]
+    pad = tiny.cfg.pad_token_id
+    ids = torch.tensor([[pad] * (12 - len(p)) + p for p in prompts])
+    mask = torch.tensor([[0] * (12 - len(p)) + [1] * len(p) for p in prompts])
+    assert adapter.start_ids_of(mask).tolist() == [7, 3, 0]
+    out = adapter.generate(ids, attention_mask=mask, max_new_tokens=10)
+    assert out.shape == (3, 22) and torch.equal(out[:, :12], ids)
+    for b in range(3):
+        _assert_greedy_equal(tiny, "float32", prompts[b], out[b, 12:].tolist(), 10)
+    assert torch.equal(adapter.generate(ids, attention_mask=mask, max_length=22), out)
+    # forward, as a generation loop of the caller's would use it
+    adapter.reset_generation()
+    lg = adapter(ids, None, attention_mask=mask)[0]
+    assert lg.shape == (3, 1, tiny.cfg.vocab_size) and adapter.cur_len == 12
+    for b in range(3):
+        want = tiny.plain_logits(prompts[b])[-1]
+        assert float((lg[b, 0] - want).abs().max()) / float(want.abs().max()) <= TOLERANCE["float32"]
+    # eos ends a row; the pad id follows it
+    eos = int(out[0, 12 + 3])
+    first = out[0, 12:].tolist().index(eos)
+    stopped = adapter.generate(ids, attention_mask=mask, max_new_tokens=10, eos_token_id=eos, pad_token_id=pad)
+    assert stopped[0, 12:12 + first + 1].tolist() == out[0, 12:12 + first + 1].tolist()
+    assert all(t == pad for t in stopped[0, 12 + first + 1:].tolist())
+    sampled = adapter.generate(ids, attention_mask=mask, max_new_tokens=6, do_sample=True, top_k=5, temperature=0.8, seed=3)
+    assert torch.equal(sampled, adapter.generate(ids, attention_mask=mask, max_new_tokens=6, do_sample=True, top_k=5,
+                                                 temperature=0.8, seed=3))
+    with pytest.raises(NotImplementedError):
+        adapter.generate(ids, num_beams=4)
+    with pytest.raises(TypeError):
+        adapter.generate(ids, logits_processor=[])
+
+
 def test_kernel_profile(tiny):
     """The profiling helper brackets every kernel call with events and names the families."""
     from transformers_neuronx_b200.kernels import kernel_profile

@@ -115,12 +115,14 @@ class OPTForSampling:
         outs = self._generate(prompts, n_new, params, streamer, input_ids.dtype)
         return torch.cat([input_ids, torch.as_tensor(outs, dtype=input_ids.dtype)], dim=1)
 
-    def _generate(self, prompts, n_new, params, streamer, dtype, eos=None):
+    def _generate(self, prompts, n_new, params, streamer, dtype, eos=None, pad=None):
         """Runs the rows to the end.  With a streamer every new column of tokens is handed to it
         (`put` of a [batch, 1] tensor) as soon as all its ids are known, and `end` is called last
-        (sampling.py:159-160, :172-173); rows that are finished are filled with the first eos id."""
+        (sampling.py:159-160, :172-173); rows that are finished are filled with `pad` (the first eos
+        id when none is given)."""
         eng = self.engine
         stop = eos is not None
+        fill = (eos[0] if pad is None else int(pad)) if stop else None
         if streamer is None:
             outs = eng.generate(prompts, n_new, params, stop_on_eos=stop, eos_token_id=eos)
         else:
@@ -135,7 +137,7 @@ class OPTForSampling:
                         if sent < len(r.output) and r.output[sent] != eng.PENDING:
                             col.append(r.output[sent])
                         elif r.finished and sent >= len(r.output) and stop and any(sent < len(o.output) for o in reqs):
-                            col.append(eos[0])
+                            col.append(fill)
                         else:
                             col = None
                             break
@@ -149,7 +151,7 @@ class OPTForSampling:
                 del eng.requests[rid]
         if stop:
             length = max(len(o) for o in outs)
-            outs = [o + [eos[0]] * (length - len(o)) for o in outs]
+            outs = [o + [fill] * (length - len(o)) for o in outs]
         return outs
 
     def _sample_tokens(self, input_ids, sequence_length, start_ids, gen: GenerationConfig, streamer, seed):
