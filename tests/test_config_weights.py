@@ -146,3 +146,20 @@ def test_sharded_index(tmp_path):
         {"weight_map": {"model.a.weight": "s1.safetensors", "model.a.bias": "s2.safetensors"}}))
     out = load_tensors(str(tmp_path), _specs())
     assert torch.equal(out["model.a.bias"], b["model.a.bias"])
+
+
+def test_compiled_kernels_can_be_kept_in_a_folder(tmp_path):
+    """export_libraries / import_libraries (model.save / model.load): libraries carry the digest of
+    their source in their names; a file of another version or of another origin is not taken."""
+    from transformers_neuronx_b200.kernels import build as kb
+    out = kb.export_libraries(["embedding"], str(tmp_path))
+    assert [os.path.basename(p) for p in out] == [os.path.basename(kb.library_path("embedding"))]
+    (tmp_path / "embedding.0000000000000000.so").write_bytes(b"stale")
+    (tmp_path / "notes.txt").write_text("x")
+    assert kb.import_libraries(str(tmp_path)) == ["embedding"]
+    try:
+        kb.import_libraries(str(tmp_path / "missing"))
+    except kb.KernelBuildError:
+        pass
+    else:
+        raise AssertionError("a missing folder was accepted")

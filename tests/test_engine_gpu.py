@@ -314,6 +314,31 @@ def test_generate_adapter_with_left_padded_rows(tiny):
         adapter.generate(ids, logits_processor=[])
 
 
+def test_all_logits_of_a_prompt_and_kept_kernels(tiny, tmp_path):
+    from transformers_neuronx_b200 import NeuronConfig
+    from transformers_neuronx_b200.opt.model import OPTForSampling
+    model = OPTForSampling.from_pretrained(tiny.folder, batch_size=2, amp="f32", n_positions=32,
+                                           neuron_config=NeuronConfig(output_all_logits=True))
+    model.to_neuron()
+    prompts = [tiny.random_ids(n, seed=60 + n) for n in (6, 11)]
+    pad = tiny.cfg.pad_token_id
+    ids = torch.tensor([[pad] * (11 - len(p)) + p for p in prompts])
+    lg = model(ids, None, torch.tensor([5, 0]))
+    assert lg.shape == (2, 11, tiny.cfg.vocab_size) and float(lg[0, :5].abs().max()) == 0.0
+    for b, p in enumerate(prompts):
+        want = tiny.plain_logits(p)
+        got = lg[b, 11 - len(p):]
+        assert float((got - want).abs().max()) / float(want.abs().max()) <= TOLERANCE["float32"]
+    nxt = model(torch.tensor([[7], [9]]), torch.tensor([11]), torch.tensor([5, 0]))       # a decode call: last token only
+    assert nxt.shape == (2, tiny.cfg.vocab_size)
+    model.save(str(tmp_path / "kernels"))
+    kept = os.listdir(tmp_path / "kernels")
+    assert kept and all(f.endswith(".so") for f in kept)
+    other = OPTForSampling.from_pretrained(tiny.folder, batch_size=1, amp="f32", n_positions=32)
+    other.load(str(tmp_path / "kernels"))
+    assert other.to_neuron().sample(ids[1:], sequence_length=14, top_k=1).shape == (1, 14)
+
+
 def test_kernel_profile(tiny):
     """The profiling helper brackets every kernel call with events and names the families."""
     from transformers_neuronx_b200.kernels import kernel_profile

@@ -106,18 +106,20 @@ class GenerationConfig:
 
 
 class NeuronConfig:
-    """The reference's bag of options (config.py:160-330).  `on_device_generation` is the one with a
-    meaning here; `output_all_logits`, `on_device_embedding`, `fuse_qkv` and `padding_side='left'`
-    name what this engine does anyway.  Anything else set to a value of its own is kept in
+    """The reference's bag of options (config.py:160-330).  `on_device_generation` and
+    `output_all_logits` have a meaning here; `on_device_embedding`, `fuse_qkv` and
+    `padding_side='left'` name what this engine does anyway.  Anything else set to a value of its own is kept in
     `ignored` and reported once."""
 
     _AS_BUILT = {"on_device_embedding", "fuse_qkv", "fuse_mlp", "cast_logits_dtype", "padding_side",
                  "attention_layout", "collectives_layout", "cache_layout", "compilation_worker_count"}
 
-    def __init__(self, *, on_device_generation: Optional[GenerationConfig] = None, **options):
+    def __init__(self, *, on_device_generation: Optional[GenerationConfig] = None, output_all_logits: bool = False,
+                 **options):
         if on_device_generation is not None and not isinstance(on_device_generation, GenerationConfig):
             raise TypeError("on_device_generation must be a GenerationConfig")
         self.on_device_generation = on_device_generation
+        self.output_all_logits = bool(output_all_logits)      # forward() of a prompt returns every position's logits
         self.ignored = {k: v for k, v in options.items()
                         if k not in self._AS_BUILT and v not in (None, False)}
         if self.ignored:

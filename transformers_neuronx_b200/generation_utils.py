@@ -35,7 +35,8 @@ class HuggingFaceGenerationModelAdapter:
         (left-padded) prompts; otherwise input_ids holds the next token of every row."""
         if start_ids is None and attention_mask is not None:
             start_ids = self.start_ids_of(attention_mask)
-        logits = self.model(torch.as_tensor(input_ids), cache_ids, start_ids)[:, None, :]
+        logits = self.model(torch.as_tensor(input_ids), cache_ids, start_ids)
+        logits = (logits[:, -1] if logits.dim() == 3 else logits)[:, None, :]      # all positions asked for: the last
         if cache_ids is None:
             self.cur_len = int(torch.as_tensor(input_ids).shape[1])
         else:

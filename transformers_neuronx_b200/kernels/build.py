@@ -141,6 +141,41 @@ def build(name: str, verbose: bool = True) -> str:
         return out
 
 
+def export_libraries(names: Iterable[str], directory: str) -> List[str]:
+    """Copies the compiled libraries of `names` (building what is missing) into `directory`, under
+    the names that carry their source's digest; returns the paths written."""
+    os.makedirs(directory, exist_ok=True)
+    out = []
+    for n in dict.fromkeys(names):
+        path = build(n)
+        dst = os.path.join(directory, os.path.basename(path))
+        if not os.path.isfile(dst):
+            tmp = f"{dst}.{os.getpid()}.tmp"
+            shutil.copyfile(path, tmp)
+            os.replace(tmp, dst)
+        out.append(dst)
+    return out
+
+
+def import_libraries(directory: str) -> List[str]:
+    """Takes from `directory` every library whose name carries the digest of today's source (a
+    library of another source version, or of a file that is not ours, is left alone), so that
+    build() finds it instead of compiling; returns the kernel names taken."""
+    taken = []
+    if not os.path.isdir(directory):
+        raise KernelBuildError(f"{directory!r} is not a folder of compiled kernels")
+    for n in SOURCES:
+        want = library_path(n)
+        src = os.path.join(directory, os.path.basename(want))
+        if os.path.isfile(src) and not os.path.isfile(want):
+            tmp = f"{want}.{os.getpid()}.tmp"
+            shutil.copyfile(src, tmp)
+            os.replace(tmp, want)
+        if os.path.isfile(src):
+            taken.append(n)
+    return taken
+
+
 def build_many(names: Iterable[str], verbose: bool = True) -> None:
     names = [n for n in dict.fromkeys(names) if n not in _loaded]
     todo = [n for n in names if not os.path.isfile(library_path(n))]

@@ -8,8 +8,9 @@ Names and meanings follow src/transformers_neuronx/opt/model.py:34-192: ``sequen
 total length (prompt included); ``sample`` draws from the top_k (default 50) most likely tokens and
 never draws the end-of-sequence token (sampling.py:26-30, :131-180); ``top_k=1`` is greedy, as in
 the reference's own validation (testing/validation.py:68-101); ``forward(input_ids, cache_ids,
-start_ids)`` returns the 32-bit logits [batch, vocab] of each row's last token; ``start_ids`` marks
-left padding.  With ``neuron_config=NeuronConfig(on_device_generation=GenerationConfig(...))``
+start_ids)`` returns the 32-bit logits [batch, vocab] of each row's last token (of every position of
+the prompts with ``NeuronConfig(output_all_logits=True)``); ``start_ids`` marks left padding;
+``save`` / ``load`` keep the compiled kernels in a folder between processes.  With ``neuron_config=NeuronConfig(on_device_generation=GenerationConfig(...))``
 ``sample`` chooses tokens as that configuration says (opt/model.py:187-189, sampling.py:34-105).
 ``tp_degree``, ``unroll`` and ``context_length_estimate`` have no meaning on one GPU and are accepted
 and ignored with a warning.  ``to_neuron`` loads the weights onto the GPU and compiles the kernels
@@ -82,6 +83,19 @@ class OPTForSampling:
         return self
 
     to_gpu = to_neuron
+
+    # ---- compiled kernels kept between processes (base.py:110-190: save / load of compiled artifacts) ----
+    def save(self, directory: str) -> None:
+        """Writes the compiled kernel libraries this model uses into `directory`."""
+        from ..kernels import build as kbuild
+        self._ready()
+        kbuild.export_libraries(self.model.libraries(self.model.act_dtype), directory)
+
+    def load(self, directory: str) -> None:
+        """Call before to_neuron(): kernels compiled earlier (by save) from the same sources are
+        taken from `directory` instead of being compiled again."""
+        from ..kernels import build as kbuild
+        kbuild.import_libraries(directory)
 
     def _ready(self):
         if self.engine is None:
@@ -212,6 +226,16 @@ class OPTForSampling:
                 have = runner.cache.length(rid)
                 if have != first - starts[b]:
                     raise ValueError(f"row {b} holds {have} tokens; cache_ids says {first - starts[b]}")
+        if self.neuron_config.output_all_logits and cache_ids is None:
+            # logits of every position [batch, tokens, vocab] (base.py:716-717); left padding holds zeros
+            entries = [StepEntry(rid, t, list(range(len(t)))) for rid, t in zip(self._rows, toks)]
+            flat = runner.step(entries).to("cpu", torch.float32)
+            out = torch.zeros(B, T, flat.shape[1])
+            row = 0
+            for b, t in enumerate(toks):
+                out[b, T - len(t):] = flat[row:row + len(t)]
+                row += len(t)
+            return out
         entries = [StepEntry(rid, t, [len(t) - 1]) for rid, t in zip(self._rows, toks)]
         return runner.step(entries).to("cpu", torch.float32)
 
