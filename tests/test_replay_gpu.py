@@ -231,3 +231,20 @@ def test_small_steps_with_portions_are_captured_and_replayed(tiny, dtype):
         runner.cache.check()
     replayed = {key: runs for key, runs in runner.captured_steps().items() if isinstance(key[0], tuple) and key[0][0] == "portions"}
     assert replayed and max(replayed.values()) >= 4, runner.captured_steps()
+
+
+def test_shapes_beyond_the_graph_limit_run_eagerly():
+    from transformers_neuronx_b200.engine import StepEntry, StepRunner, load_model
+    tiny = TinyModel("A", seed=29)
+    model, _ = load_model(tiny.folder, "bfloat16", verbose=False)
+    runner = StepRunner(model, 16, 16, 2, 128, use_cuda_graphs=True, max_graphs=2)
+    ids = tiny.random_ids(120, seed=77)
+    plain = tiny.plain_logits(ids)
+    runner.add_request("g")
+    pos = 0
+    for n in [3, 3, 3, 20, 20, 20, 1, 1, 1, 35, 1, 1, 5]:        # four shapes; only the first two are kept
+        lg = runner.step([StepEntry("g", ids[pos:pos + n], [n - 1])]).cpu()
+        err = float((lg[0] - plain[pos + n - 1]).abs().max()) / float(plain[pos + n - 1].abs().max())
+        assert err <= TOLERANCE["bfloat16"], (pos, n, err)
+        pos += n
+    assert len(runner.captured_steps()) == 2

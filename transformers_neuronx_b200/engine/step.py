@@ -45,7 +45,7 @@ class StepRunner:
     """Owns the cache (bookkeeping and device memory) of one model and runs steps on it."""
 
     def __init__(self, model, page_size: int, num_pages: int, max_slots: int, max_model_len: int,
-                 use_cuda_graphs: bool = False, max_graph_batch: int = 256):
+                 use_cuda_graphs: bool = False, max_graph_batch: int = 256, max_graphs: int = 128):
         self.model = model
         self.device = model.device
         self.act_dtype = model.act_dtype
@@ -63,6 +63,7 @@ class StepRunner:
         # decode-only steps can be replayed as CUDA graphs, one per (batch bucket, context bucket)
         self.use_cuda_graphs = bool(use_cuda_graphs) and getattr(model, "graph_safe", True)
         self.max_graph_batch = max_graph_batch
+        self.max_graphs = max_graphs              # shapes kept as graphs (each holds its buffers)
         self._graphs = {}
         self._graph_pool = None
         self._decode_layouts = {}
@@ -400,7 +401,8 @@ class StepRunner:
             dev = torch.empty(o, dtype=torch.int32, device=self.device)
             ctx = self._context(dev, hb, offs, sizes, max_blocks, n_fixed, dims, counts)
             g = {"dev": dev, "ctx": ctx, "graph": None, "logits": None, "runs": 0}
-            self._graphs[key] = g
+            if len(self._graphs) < self.max_graphs:
+                self._graphs[key] = g                 # beyond the limit a new shape runs eagerly every time
         dev, ctx = g["dev"], g["ctx"]
         dev.copy_(slot[0][:o], non_blocking=True)
         if slot[1] is None:
