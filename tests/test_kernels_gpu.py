@@ -55,7 +55,8 @@ TC_SHAPES = [(1, 128, 64), (3, 96, 320), (8, 256, 2112), (40, 4096, 4096), (128,
              (250, 12288, 4096), (16, 4096, 1024), (17, 1000, 96), (33, 200, 136), (64, 512, 4096),
              (65, 384, 256), (128, 128, 64), (200, 1000, 328), (300, 520, 1032), (2048, 768, 512),
              (1024, 4096, 512), (1000, 4000, 328), (300, 9000, 136), (513, 7100, 72), (520, 7102, 72), (2100, 2300, 1096),
-             (1792, 2048, 16384), (2000, 3300, 8200), (1100, 4090, 4096)]     # the last three share tiles out by K blocks
+             (1280, 2048, 16384), (2000, 3300, 8200), (1100, 4090, 4096),     # the first and the third share tiles out by K blocks (long K; four runs a tile)
+             (256, 4096, 4096), (384, 4096, 8192), (384, 12288, 4096), (300, 4000, 4104)]   # 128 x 256 tiles, K split 4, 2, 1, 2 ways in clusters
 
 
 @pytest.mark.parametrize("M,N,K", TC_SHAPES)

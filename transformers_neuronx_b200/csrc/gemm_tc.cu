@@ -1131,7 +1131,14 @@ static ManyTokensPlan plan_many_tokens(int M, int N, int K, int sms) {
     // A margin of 1.3 on these costs; every pair must get at least four K blocks.
     int sk_pairs = rest * 4 < G ? rest * 4 : G;
     float t_share = 1e30f;
-    if (rest > 0 && (long long)rest * kb >= 4LL * sk_pairs) {
+    // Measured at 384..1,536 tokens on the layer products of the 6.7B and 13B sizes: sharing out pays where
+    // every shared tile is cut into exactly four runs (a pair then holds part of one tile only: 6-44 %
+    // faster), and with a long K (256 blocks and more) after a wave of whole tiles, or without one down to
+    // 1.6 pairs per tile (8-38 %); elsewhere, with runs that straddle two tiles, it lost 6-34 % against whole
+    // tiles in one more wave.
+    const bool four_runs = rest * 4 <= G;
+    const bool long_k = kb >= 256 && (full > 0 || sk_pairs * 10 >= rest * 16);
+    if (rest > 0 && (long long)rest * kb >= 4LL * sk_pairs && (four_runs || long_k)) {
         const float reduce = ((float)sk_pairs / rest + 1.f) * 2.8f;
         const float exposed = full > 0 ? (reduce > t_tile ? reduce - t_tile : 0.f) : reduce;
         t_share = ((float)full + (float)rest / sk_pairs) * t_tile + 8.f + 1.3f * ((sk_pairs + rest) * 0.1f + exposed);
@@ -1155,7 +1162,23 @@ static ManyTokensPlan plan_many_tokens(int M, int N, int K, int sms) {
         const bool single = tiles_p * 4 < sms * 3;
         const float t_here = single ? t_single : (float)((tiles_p + sms - 1) / sms) * kb * 0.45f + 8.f;
         if (t_here <= t_pair && t_here <= t_share) { r.kind = single ? 0 : 2; return r; }
-    } else if (t_single <= t_pair && t_single <= t_share) { r.kind = 0; return r; }
+    } else {
+        // 256 tokens and more: where the 128 x 256 tiles fit the GPU in one wave they can split K 1, 2, 4 or
+        // 8 ways in clusters as above.  A K block of such a tile takes 0.45 us; start and drain 8 us, the sum
+        // over a cluster 2 + splits us (measured at 256..768 tokens: [4096 x 16384] 43 / 69 / 71 us at
+        // 256 / 384 / 512 tokens against 63 / 87 / 89 us; [12288 x 4096] 40 against 50 us at 384).  It has to
+        // win by a tenth: where the estimates tie, the paired kernel was the faster one.
+        const int tiles_p = tiles_m * ((N + 255) / 256);
+        int best_sp = 0;
+        float t_split = 1e30f;
+        for (int sp = 1; sp <= MAX_CLUSTER && tiles_p * sp <= sms && (sp == 1 || sp * 4 <= kb); sp <<= 1) {
+            const float t = (float)((kb + sp - 1) / sp) * 0.45f + 8.f + (sp > 1 ? 2.f + (float)sp : 0.f);
+            if (t < t_split) { t_split = t; best_sp = sp; }
+        }
+        const float t_other = fminf(t_single, fminf(t_pair, t_share));
+        if (best_sp > 0 && t_split * 1.1f < t_other) { r.kind = 3; r.splits = best_sp; return r; }
+        if (t_single <= t_pair && t_single <= t_share) { r.kind = 0; return r; }
+    }
     r.kind = 1;
     if (t_share < t_pair) { r.pairs = G; r.sk_tiles = rest; r.sk_pairs = sk_pairs; }
     else r.pairs = n_tiles < G ? n_tiles : G;
