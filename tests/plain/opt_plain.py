@@ -161,12 +161,20 @@ def multi_head_attention(h: torch.Tensor, w: Dict[str, torch.Tensor], prefix: st
 
 
 def activation(name: str, x: torch.Tensor) -> torch.Tensor:
-    """Activation looked up by config.activation_function (T/hlo.py:485-501); relu = max(x, 0)
-    (T/activations.py:43-48)."""
+    """Activation looked up by config.activation_function (T/hlo.py:485-501): relu = max(x, 0)
+    (T/activations.py:43-48); gelu_new = 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3)))
+    (T/activations.py:20-41); sigmoid (T/activations.py:66-67); silu = x sigmoid(x)
+    (T/activations.py:70-72); gelu is the exact form x Phi(x), which the reference does not have."""
     if name == "relu":
         return torch.clamp(x, min=0)
     if name == "gelu":
-        return torch.nn.functional.gelu(x)
+        return 0.5 * x * (1.0 + torch.erf(x / math.sqrt(2.0)))
+    if name in ("gelu_new", "gelu_new_legacy"):
+        return 0.5 * x * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (x + 0.044715 * x * x * x)))
+    if name == "sigmoid":
+        return 1.0 / (1.0 + torch.exp(-x))
+    if name == "silu":
+        return x / (1.0 + torch.exp(-x))
     raise ValueError(f"plain implementation has no activation {name!r}")
 
 
@@ -320,3 +328,33 @@ def greedy_generate(prompt: List[int], n_new: int, weights, cfg, dtype=torch.flo
         logits = forward_logits(ids, weights, cfg, dtype)
         ids.append(int(greedy_token(logits[-1])))
     return ids[len(prompt):]
+
+
+# ----------------------------------------------------------------------------------------------
+# The engine's own draw (no counterpart in the reference, whose host loops use torch's global
+# generator, T/gpt_demo.py:101 and T/sampling.py:156): one uniform number per (seed, counter) from
+# the Philox 4x32-10 counter generator, and the token whose interval of the summed probabilities,
+# taken in index order, holds it.
+# ----------------------------------------------------------------------------------------------
+
+def philox_uniform(seed: int, counter: int) -> float:
+    """First output word of Philox 4x32-10 with counter (counter, 0) and key = seed, as a number in
+    [0, 1) with 32 bits."""
+    M0, M1, W0, W1, mask = 0xD2511F53, 0xCD9E8D57, 0x9E3779B9, 0xBB67AE85, 0xFFFFFFFF
+    c = [counter & mask, (counter >> 32) & mask, 0, 0]
+    k = [seed & mask, (seed >> 32) & mask]
+    for _ in range(10):
+        p0, p1 = M0 * c[0], M1 * c[2]
+        c = [(p1 >> 32) ^ c[1] ^ k[0], p1 & mask, (p0 >> 32) ^ c[3] ^ k[1], p0 & mask]
+        k = [(k[0] + W0) & mask, (k[1] + W1) & mask]
+    return c[0] / 4294967296.0
+
+
+def draw_in_index_order(probs: torch.Tensor, uniform: float):
+    """The first token (in index order) at which the summed probability exceeds uniform * total.
+    Returns (token, distance of uniform from the nearest summed probability)."""
+    cum = probs.double().cumsum(-1)
+    cum = cum / cum[-1]
+    tok = int((cum <= uniform).sum())
+    tok = min(tok, probs.shape[-1] - 1)
+    return tok, float((cum - uniform).abs().min())

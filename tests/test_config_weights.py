@@ -43,8 +43,9 @@ def test_registry():
 def test_dtype_names():
     assert canonical_dtype("f32") == "float32" and canonical_dtype("bf16") == "bfloat16"
     assert canonical_dtype(torch.bfloat16) == "bfloat16"
-    with pytest.raises(ValueError, match="bfloat16"):
-        canonical_dtype("f16")
+    assert canonical_dtype("f16") == "float16" and canonical_dtype(torch.float16) == "float16"   # dtypes.py:18-35
+    with pytest.raises(ValueError, match="f32, f16, bf16"):
+        canonical_dtype("f8")
     with pytest.raises(ValueError):
         EngineConfig(page_size=24)
 
@@ -106,7 +107,7 @@ def test_prefix_and_tie(tmp_path):
     (tmp_path / "config.json").write_text("{}")
     out = load_tensors(str(tmp_path), _specs())
     assert out["head.weight"] is out["model.a.weight"]
-    assert out["model.a.bias"].dtype == torch.bfloat16           # float16 becomes bfloat16
+    assert out["model.a.bias"].dtype == torch.float16 and torch.equal(out["model.a.bias"], t["a.bias"])   # kept as stored
     # a stored head that differs from the table it is tied to is an error
     t["head.weight"] = torch.randn(4, 3).bfloat16()
     save_safetensors(t, str(tmp_path / "model.safetensors"))
@@ -163,3 +164,51 @@ def test_compiled_kernels_can_be_kept_in_a_folder(tmp_path):
         pass
     else:
         raise AssertionError("a missing folder was accepted")
+
+
+def test_files_agree_with_the_safetensors_package_in_both_directions(tmp_path):
+    """The engine has a reader and a writer of its own; a mistake that both share (header padding,
+    dtype tags, offsets) would be invisible to a test that only ever feeds one to the other.  So:
+    a file written by the `safetensors` package is read by the engine's reader, a file written by the
+    engine's writer is read by the package, in every type the engine stores, and a sharded folder
+    with an index as the package's users write it."""
+    import json
+    from safetensors import safe_open
+    from safetensors.torch import load_file, save_file
+    from transformers_neuronx_b200.weights import SafetensorsFile, open_model_files
+    g = torch.Generator().manual_seed(3)
+    t = {"w.bf16": torch.randn(7, 5, generator=g).bfloat16(), "w.f16": torch.randn(3, 11, generator=g).half(),
+         "w.f32": torch.randn(2, 3, 4, generator=g), "i.i32": torch.arange(6, dtype=torch.int32).view(2, 3),
+         "i.i64": torch.arange(5), "scalar": torch.tensor(1.5), "empty": torch.zeros(0, 4)}
+    theirs, ours = str(tmp_path / "theirs.safetensors"), str(tmp_path / "ours.safetensors")
+    save_file(t, theirs, metadata={"format": "pt"})
+    f = SafetensorsFile(theirs)
+    assert sorted(f.keys()) == sorted(t)
+    for k, v in t.items():
+        got = f.tensor(k)
+        assert got.dtype == v.dtype and tuple(got.shape) == tuple(v.shape) and torch.equal(got, v), k
+        assert f.info(k) == (v.dtype, tuple(v.shape))
+    f.close()
+    save_safetensors(t, ours, metadata={"format": "pt", "seed": 3})
+    back = load_file(ours)
+    assert sorted(back) == sorted(t)
+    for k, v in t.items():
+        assert back[k].dtype == v.dtype and torch.equal(back[k], v), k
+    with safe_open(ours, framework="pt") as fp:
+        assert fp.metadata()["format"] == "pt" and fp.metadata()["seed"] == "3"
+    # a sharded folder: two files and model.safetensors.index.json
+    folder = tmp_path / "sharded"
+    folder.mkdir()
+    names = sorted(t)
+    save_file({k: t[k] for k in names[:3]}, str(folder / "model-00001-of-00002.safetensors"))
+    save_file({k: t[k] for k in names[3:]}, str(folder / "model-00002-of-00002.safetensors"))
+    index = {"metadata": {}, "weight_map": {k: ("model-00001-of-00002.safetensors" if k in names[:3]
+                                                 else "model-00002-of-00002.safetensors") for k in names}}
+    (folder / "model.safetensors.index.json").write_text(json.dumps(index))
+    files = open_model_files(str(folder))
+    seen = {}
+    for fl in files:
+        for k in fl.keys():
+            seen[k] = fl.tensor(k).clone()
+        fl.close()
+    assert sorted(seen) == names and all(torch.equal(seen[k], t[k]) for k in names)

@@ -31,7 +31,7 @@ def test_gemm_simt(M, N, K, combo):
     w = torch.randn(N, K, generator=g).to(dt[combo[1]]).to(DEV)
     bias = torch.randn(N, generator=g).to(DEV)
     out = torch.empty(M, N, dtype=dt[combo[2]], device=DEV)
-    ops().gemm_simt(a, w, out, bias=bias, relu=True)
+    ops().gemm_simt(a, w, out, bias=bias, activation="relu")
     want = torch.relu(a.float() @ w.float().t() + bias)
     assert rel_err(out, want) <= (1e-5 if combo[2] == "f" else 5e-3)
     if combo[2] == "f":
@@ -73,7 +73,7 @@ def test_gemm_tc(M, N, K):
     o.raise_on_device_error()
     assert rel_err(out, want) <= 2e-5, "plain product"
     outb = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
-    o.gemm_tc(a, w, outb, bias=bias, relu=True, **tc)
+    o.gemm_tc(a, w, outb, bias=bias, activation="relu", **tc)
     assert rel_err(outb, torch.relu(want + bias)) <= 5e-3, "bias + relu -> bf16"
     res = torch.randn(M, N, generator=g).to(DEV)
     want3 = want + bias + res
@@ -103,7 +103,7 @@ def test_gemv_few_tokens(M, N, K):
     o.gemv(a, w, out)
     assert rel_err(out, want) <= 2e-5, "plain product"
     outb = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
-    o.gemv(a, w, outb, bias=bias, relu=True)
+    o.gemv(a, w, outb, bias=bias, activation="relu")
     assert rel_err(outb, torch.relu(want + bias)) <= 5e-3, "bias + relu -> bf16"
     res = torch.randn(M, N, generator=g).to(DEV)
     want3 = want + bias + res
@@ -134,8 +134,8 @@ def test_gemm_tc_split_k(M, N, K, splits):
     want = torch.relu(a.float() @ w.float().t() + bias)
     out1 = torch.empty(M, N, dtype=torch.float32, device=DEV)
     out2 = torch.empty_like(out1)
-    o.gemm_tc(a, w, out1, bias=bias, relu=True, splits=splits)
-    o.gemm_tc(a, w, out2, bias=bias, relu=True, splits=splits)      # the counters were left at zero
+    o.gemm_tc(a, w, out1, bias=bias, activation="relu", splits=splits)
+    o.gemm_tc(a, w, out2, bias=bias, activation="relu", splits=splits)      # the counters were left at zero
     o.raise_on_device_error()
     assert rel_err(out1, want) <= 2e-5
     assert torch.equal(out1, out2), "the order of the additions is fixed"
@@ -154,8 +154,8 @@ def test_gemm_tc_split_k_in_clusters(M, N, K, splits):
     want = a.float() @ w.float().t()
     out1 = torch.empty(M, N, dtype=torch.float32, device=DEV)
     out2 = torch.empty_like(out1)
-    o.gemm_tc(a, w, out1, bias=bias, relu=True, splits=splits, cluster=True)
-    o.gemm_tc(a, w, out2, bias=bias, relu=True, splits=splits, cluster=True)
+    o.gemm_tc(a, w, out1, bias=bias, activation="relu", splits=splits, cluster=True)
+    o.gemm_tc(a, w, out2, bias=bias, activation="relu", splits=splits, cluster=True)
     o.raise_on_device_error()
     assert rel_err(out1, torch.relu(want + bias)) <= 2e-5
     assert torch.equal(out1, out2), "the order of the additions is fixed"
@@ -169,7 +169,7 @@ def test_gemm_tc_split_k_in_clusters(M, N, K, splits):
     assert rel_err(outb, want) <= 5e-3
     # the same sums as with scratch memory: both add the partial tiles in split order
     out3 = torch.empty_like(out1)
-    o.gemm_tc(a, w, out3, bias=bias, relu=True, splits=splits)
+    o.gemm_tc(a, w, out3, bias=bias, activation="relu", splits=splits)
     assert torch.equal(out1, out3)
 
 

@@ -6,12 +6,10 @@ The plain implementation (tests/plain/opt_plain.py) works on the CPU and would t
 size, so its formulas are restated below with the tensors on the GPU (torch in 32-bit, TF32 off);
 the first assertion checks the restatement against the plain implementation on a short sequence.
 """
-import math
-
 import pytest
 import torch
 
-from helpers import opt_plain, rel_error
+from helpers import opt_plain, plain_one_layer_on_gpu, rel_error
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -42,25 +40,6 @@ def _build():
     return build_model(spec, tensors, "bfloat16", verbose=False), cfg, tensors
 
 
-def _plain_on_gpu(ids, w, cfg):
-    """opt_plain.forward_logits for one pre-norm layer, tensors on the GPU."""
-    H, heads = cfg.hidden_size, cfg.num_attention_heads
-    d, T = H // heads, len(ids)
-    ln = lambda x, a, b: torch.nn.functional.layer_norm(x, (H,), w[a], w[b], 1e-5)
-    x = w[P + "embed_tokens.weight"][torch.tensor(ids, device=DEV)] + \
-        w[P + "embed_positions.weight"][torch.arange(T, device=DEV) + 2]
-    h = ln(x, L0 + "self_attn_layer_norm.weight", L0 + "self_attn_layer_norm.bias")
-    q, k, v = ((h @ w[L0 + f"self_attn.{n}_proj.weight"].t() + w[L0 + f"self_attn.{n}_proj.bias"])
-               .view(T, heads, d).transpose(0, 1) for n in "qkv")
-    s = (q @ k.transpose(1, 2)) / math.sqrt(d)
-    s = s.masked_fill(torch.ones(T, T, device=DEV, dtype=torch.bool).triu(1), float("-inf"))
-    a = (torch.softmax(s, -1) @ v).transpose(0, 1).reshape(T, H)
-    x = x + a @ w[L0 + "self_attn.out_proj.weight"].t() + w[L0 + "self_attn.out_proj.bias"]
-    h = ln(x, L0 + "final_layer_norm.weight", L0 + "final_layer_norm.bias")
-    x = x + torch.relu(h @ w[L0 + "fc1.weight"].t() + w[L0 + "fc1.bias"]) @ w[L0 + "fc2.weight"].t() + w[L0 + "fc2.bias"]
-    return ln(x, P + "final_layer_norm.weight", P + "final_layer_norm.bias") @ w[P + "embed_tokens.weight"].t()
-
-
 def test_one_layer_at_the_sizes_of_the_benchmark():
     from transformers_neuronx_b200.engine import StepEntry, StepRunner
     from transformers_neuronx_b200.kernels import ops
@@ -72,7 +51,7 @@ def test_one_layer_at_the_sizes_of_the_benchmark():
         gen = torch.Generator().manual_seed(9)
         lens = [2040, 1500, 700, 300, 130, 64, 17, 5]
         seqs = [torch.randint(3, cfg.vocab_size, (n + 6,), generator=gen).tolist() for n in lens]
-        plain = lambda ids: _plain_on_gpu(ids, w, cfg)
+        plain = lambda ids: plain_one_layer_on_gpu(ids, w, cfg)
 
         short = seqs[6][:17]
         cpu = opt_plain.forward_logits(short, {k: v.cpu() for k, v in tensors.items()}, cfg.to_dict())

@@ -82,7 +82,7 @@ def test_attention_part_alone(name, dtype, tol):
         mixer.forward(ctx, h, res)
         outs.append(res)
     got = torch.cat(outs)
-    w = {k: v.float() for k, v in tiny.tensors.items()}
+    w = {k: v.float() for k, v in tiny.plain_tensors.items()}
     hin = hs.to(model.act_dtype).float()
     want = P.multi_head_attention(hin, w, "model.decoder.layers.0.self_attn.", tiny.cfg.num_attention_heads)
     assert rel_err(got, want.to(DEV)) <= tol
@@ -113,8 +113,8 @@ def _register_toys():
             state = ctx.cache()                                  # [slots, hidden]
             u = h.float() @ self.w.t()
             hb = ctx.host
-            for r in range(ctx.n_requests):                     # a portion is run in order, from the state before it
-                s = state[hb.slots[r]] if hb.ctx_len[r] > 0 else torch.zeros_like(state[0])
+            for r in range(ctx.n_requests):                     # a portion is run in order, from the state before it;
+                s = state[hb.slots[r]]                          # a new request finds its slot's state zeroed
                 for i in range(hb.q_start[r], hb.q_start[r] + hb.q_len[r]):
                     s = self.spec.decay * s + u[i]
                     residual[i] += s
@@ -257,10 +257,20 @@ def test_toy_parts_are_registered_built_and_stepped():
     for r in seqs:
         want = _toy_plain(seqs[r], t)
         assert rel_err(torch.cat(got[r]), want) <= 5e-5, r
+    slots = {r: runner.cache.slot(r) for r in seqs}
     for r in seqs:
         runner.finish(r)
     runner.cache.check()
     assert runner.cache.free_pages() == [12] and runner.cache.slots.num_free == 3
+    # A request that takes a slot another one has used finds clean state there: the mixer above
+    # never looks at the context length, the cache manager zeroes the slot's row at admission.
+    assert float(runner.storage.tensor(0)[slots["b"]].abs().max()) > 0, "the last owner left its state behind"
+    ids = torch.randint(0, 97, (37,), generator=g).tolist()
+    assert runner.add_request("c") in slots.values()
+    lg = torch.cat([runner.step([StepEntry("c", ids[:20], list(range(20)))]).cpu(),
+                    runner.step([StepEntry("c", ids[20:], list(range(17)))]).cpu()])
+    assert rel_err(lg, _toy_plain(ids, t)) <= 5e-5
+    runner.finish("c")
 
 
 def test_toy_feed_forward_with_routing():

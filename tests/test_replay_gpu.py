@@ -12,16 +12,30 @@ import pytest
 import torch
 
 from helpers import (TOLERANCE, TinyModel, compare_trace, live_tokens_rounded, run_trace_inprocess,
-                     trace_lines)
+                     storage_for, trace_lines)
 
 pytestmark = pytest.mark.gpu
-DTYPES = ["float32", "bfloat16"]
+DTYPES = ["float32", "bfloat16", "float16"]
 LENGTHS = {"A": [5, 17, 33, 64, 120], "B": [1, 40, 120, 250]}
+_models = {}
+
+
+def _model(name, dtype, seed):
+    """One model folder per (configuration, storage type): a 16-bit engine reads matrices stored in its own type."""
+    key = (name, storage_for(dtype), seed)
+    if key not in _models:
+        _models[key] = TinyModel(name, seed=seed, matrix_dtype=storage_for(dtype))
+    return _models[key]
 
 
 @pytest.fixture(scope="module", params=["A", "B"])
-def tiny(request):
-    return TinyModel(request.param, seed=11)
+def tiny_name(request):
+    return request.param
+
+
+@pytest.fixture
+def tiny(tiny_name, dtype):
+    return _model(tiny_name, dtype, 11)
 
 
 def _requests(tiny, lengths=None):
@@ -121,7 +135,7 @@ def test_mixed_with_page_reuse(tiny, dtype):
 def test_sizes_outside_the_fast_kernels_rules(dtype):
     """Configuration C: head size 48, widths that are no multiples of 8, an odd vocabulary: the engine
     takes the slower kernels where the fast ones refuse, and the logits are still right."""
-    tiny = TinyModel("C", seed=13)
+    tiny = _model("C", dtype, 13)
     reqs = {f"c{i}": tiny.random_ids(n, seed=300 + i) for i, n in enumerate([70, 33, 9, 78, 50, 21])}
     steps, peak = mixed_steps(reqs, chunk_sizes=(5, 16, 2, 19), decode_tail=10, max_live=3)
     res = run_trace_inprocess(tiny.folder, dtype, steps, peak)
@@ -132,7 +146,7 @@ def test_sizes_outside_the_fast_kernels_rules(dtype):
 def test_head_size_128_long_contexts(dtype):
     """Configuration D: head size 128 (the tcgen05 attention kernel in bfloat16), prompts of several
     hundred tokens in portions that start inside a page and cross 128-row tiles, beside decode tokens."""
-    tiny = TinyModel("D", seed=19)
+    tiny = _model("D", dtype, 19)
     reqs = {f"l{i}": tiny.random_ids(n, seed=500 + i) for i, n in enumerate([590, 133, 300, 64, 411, 257])}
     steps, peak = mixed_steps(reqs, chunk_sizes=(129, 16, 2, 200, 75, 128), decode_tail=9, max_live=3)
     res = run_trace_inprocess(tiny.folder, dtype, steps, peak)
@@ -142,7 +156,7 @@ def test_head_size_128_long_contexts(dtype):
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_head_size_64(dtype):
     """Configuration E: head size 64 (the tcgen05 attention kernel's other size), post-norm blocks."""
-    tiny = TinyModel("E", seed=23)
+    tiny = _model("E", dtype, 23)
     reqs = {f"e{i}": tiny.random_ids(n, seed=600 + i) for i, n in enumerate([410, 130, 257, 66, 300])}
     steps, peak = mixed_steps(reqs, chunk_sizes=(130, 2, 64, 17, 150), decode_tail=9, max_live=3)
     res = run_trace_inprocess(tiny.folder, dtype, steps, peak)
@@ -152,7 +166,7 @@ def test_head_size_64(dtype):
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_decode_steps_where_not_every_request_wants_logits(dtype):
     """Single-token steps (replayed as CUDA graphs) in which some entries ask for nothing."""
-    tiny = TinyModel("A", seed=17)
+    tiny = _model("A", dtype, 17)
     reqs = {f"d{i}": tiny.random_ids(n, seed=400 + i) for i, n in enumerate([30, 26, 22])}
     steps = [{"step": 0, "entries": [{"id": r, "tokens": ids[:20], "want": []} for r, ids in reqs.items()], "end": []}]
     for t in range(20, 30):
@@ -162,8 +176,65 @@ def test_decode_steps_where_not_every_request_wants_logits(dtype):
                 entries.append({"id": r, "tokens": [ids[t]], "want": [0] if (t + i) % 3 else []})
         steps.append({"step": len(steps), "entries": entries, "end": []})
     res = run_trace_inprocess(tiny.folder, dtype, steps, 192)
-    assert any(s["step"] not in res for s in steps[1:]) or True
+    assert 0 not in res, "a step in which nothing is wanted writes no file (run_trace_inprocess checks there is none)"
+    assert any(s["step"] not in res for s in steps[1:]), "the trace was meant to hold decode steps without a wanted row"
     compare_trace(tiny, reqs, steps, res, dtype)
+
+
+def test_32_bit_logits_do_not_depend_on_the_cut_bit_for_bit(tiny_name):
+    """The 32-bit path adds every sum in an order that the row alone decides (products in ascending
+    k with one accumulator, attention key by key, norms per row): the logits of a position are the
+    same bits whether its request ran whole, token by token, in portions, or beside other requests
+    on other pages."""
+    tiny = _model(tiny_name, "float32", 11)
+    ids = tiny.random_ids(LENGTHS[tiny.name][-1], seed=100)
+    other = {f"o{i}": tiny.random_ids(n, seed=140 + i) for i, n in enumerate([50, 23, 64])}
+    n = len(ids)
+    want_all = list(range(n))
+    whole = [{"step": 0, "entries": [{"id": "x", "tokens": ids, "want": want_all}], "end": ["x"]}]
+    cut = n - 32
+    tail = [{"step": 0, "entries": [{"id": "x", "tokens": ids[:cut], "want": list(range(cut))}], "end": []}]
+    tail += [{"step": 1 + j, "entries": [{"id": "x", "tokens": [ids[cut + j]], "want": [0]}], "end": []} for j in range(32)]
+    sizes, portions, p, j = [2, 3, 16, 2, 7, 17, 5, 2, 31, 4, 15, 33], [], 0, 0
+    while p < n:
+        m = min(sizes[j % len(sizes)], n - p)
+        portions.append({"step": len(portions), "entries": [{"id": "x", "tokens": ids[p:p + m], "want": list(range(m))}], "end": []})
+        p += m; j += 1
+    # mixed: other requests come first and take the low pages, end, and x goes on over their pages
+    mixed, p, k = [], 0, 0
+    opos = {r: 0 for r in other}
+    mixed.append({"step": 0, "entries": [{"id": r, "tokens": t[:20], "want": []} for r, t in other.items()], "end": []})
+    for r in other:
+        opos[r] = 20
+    while p < n:
+        m = min(sizes[(k + 5) % len(sizes)], n - p)
+        entries = [{"id": "x", "tokens": ids[p:p + m], "want": list(range(m))}]
+        end = []
+        for r, t in other.items():
+            if r in opos and opos[r] < len(t):
+                entries.insert(0, {"id": r, "tokens": [t[opos[r]]], "want": [0] if k % 2 else []})
+                opos[r] += 1
+                if opos[r] == len(t):
+                    end.append(r)
+        mixed.append({"step": len(mixed), "entries": entries, "end": end})
+        p += m; k += 1
+
+    def rows_of_x(steps, max_tokens):
+        res = run_trace_inprocess(tiny.folder, "float32", steps, max_tokens)
+        rows = []
+        for s_ in steps:
+            row = 0
+            for e in s_["entries"]:
+                nw = len(e.get("want", []))
+                if e["id"] == "x" and nw:
+                    rows.append(torch.from_numpy(res[s_["step"]][row:row + nw].copy()))
+                row += nw
+        return torch.cat(rows)
+    a = rows_of_x(whole, 256)
+    assert a.shape[0] == n
+    for name, steps, room in (("one by one", tail, 256), ("portions", portions, 256), ("mixed", mixed, 256 + 3 * 64)):
+        b = rows_of_x(steps, room)
+        assert torch.equal(a, b), f"{tiny.name}: {name} differs from whole by {float((a - b).abs().max()):.3e}"
 
 
 def test_program_in_a_subprocess():

@@ -1,12 +1,13 @@
 """The kernels at the sizes of real OPT models (6.7B, 13B, 30B layer shapes, one layer each, random
-weights): the bfloat16 engine against the 32-bit engine on the same weights, through a long prompt
-(the CTA-pair matrix product), portions, and decode steps of a small batch (the swapped product with
-split-K, the split decode attention, CUDA graphs); and the 32-bit engine against the plain
-implementation at the 6.7B shape."""
+weights).  The 32-bit engine against the plain implementation (restated on the GPU, and checked
+against the CPU original on a short sequence) at 2e-5: a long portion, a mixed step of a portion
+beside decode tokens, and decode steps; then the bfloat16 and float16 engines against the same
+32-bit numbers, through the CTA-pair product, the swapped product with split-K, the split decode
+attention and captured steps."""
 import pytest
 import torch
 
-from helpers import TOLERANCE
+from helpers import TOLERANCE, plain_one_layer_on_gpu, rel_error
 from plain import opt_plain
 
 pytestmark = pytest.mark.gpu
@@ -17,7 +18,7 @@ SHAPES = {
 }
 
 
-def _build(shape, dtype, tensors=None):
+def _build(shape, dtype, tensors=None, stored=torch.bfloat16):
     from transformers_neuronx_b200.config import OPTConfig
     from transformers_neuronx_b200.engine import build_model
     from transformers_neuronx_b200.models import opt as opt_arch
@@ -32,41 +33,67 @@ def _build(shape, dtype, tensors=None):
             if s.tied_to is not None:
                 continue
             t = torch.randn(s.shape, generator=g, device="cuda:0", dtype=torch.float32) * cfg.init_std
-            tensors[s.name] = (1.0 + t) if s.kind == "norm_weight" else (t if s.kind == "norm_bias" else t.to(torch.bfloat16))
+            tensors[s.name] = (1.0 + t) if s.kind == "norm_weight" else (t if s.kind == "norm_bias" else t.to(stored))
         tensors["lm_head.weight"] = tensors["model.decoder.embed_tokens.weight"]
     return build_model(spec, tensors, dtype, verbose=False), cfg, tensors
 
 
-def _run(model, cfg, prompts):
-    """Prefill in one step (all rows wanted for the first request's tail), then decode three steps."""
+def _run(model, prompts):
+    """A long portion of request 0 alone; then the rest of it beside the whole of request 1 and a
+    decode token of request 2 (a mixed step); then three decode steps of all.  Returns the logits
+    of every wanted row and, for each of them, (request, position)."""
     from transformers_neuronx_b200.engine import StepEntry, StepRunner
     runner = StepRunner(model, 16, 64, 4, 2048, use_cuda_graphs=True)
-    outs = []
-    for i in range(len(prompts)):
+    for i in range(3):
         runner.add_request(i)
-    entries = [StepEntry(i, p[:-3], [len(p) - 8, len(p) - 4]) for i, p in enumerate(prompts)]
-    outs.append(runner.step(entries).float().cpu())
+    p0, p1, p2 = prompts
+    outs, where = [], []
+    n0 = len(p0) - 3
+    outs.append(runner.step([StepEntry(0, p0[:260], [0, 259]), StepEntry(2, p2[:-4], [])]))
+    where += [(0, 0), (0, 259)]
+    outs.append(runner.step([StepEntry(0, p0[260:n0], [n0 - 261]), StepEntry(1, p1[:-3], [len(p1) - 4]),
+                             StepEntry(2, [p2[-4]], [0])]))
+    where += [(0, n0 - 1), (1, len(p1) - 4), (2, len(p2) - 4)]
     for k in (3, 2, 1):
-        outs.append(runner.step([StepEntry(i, [p[-k]], [0]) for i, p in enumerate(prompts)]).float().cpu())
-    return torch.cat(outs)
+        outs.append(runner.step([StepEntry(i, [p[-k]], [0]) for i, p in enumerate(prompts)]))
+        where += [(i, len(p) - k) for i, p in enumerate(prompts)]
+    return torch.cat([o.float() for o in outs]), where
 
 
 @pytest.mark.parametrize("shape", list(SHAPES))
-def test_bf16_engine_against_32bit_engine(shape):
-    g = torch.Generator().manual_seed(1)
-    prompts = [torch.randint(3, 50272, (n,), generator=g).tolist() for n in (300, 41)]
-    m16, cfg, tensors = _build(shape, "bfloat16")
-    got = _run(m16, cfg, prompts)
-    del m16
-    m32, _, _ = _build(shape, "float32", tensors)
-    want = _run(m32, cfg, prompts)
-    err = float((got - want).abs().max()) / float(want.abs().max())
-    assert torch.isfinite(got).all() and err <= TOLERANCE["bfloat16"], f"{shape}: {err:.3e}"
-    if shape == "6.7b":
-        cpu = {k: v.cpu() for k, v in tensors.items()}
-        for i, p in enumerate(prompts):
-            plain = opt_plain.forward_logits(p, cpu, cfg.to_dict())
-            rows = [len(p) - 8, len(p) - 4]                        # the wanted places of the prefill step
-            mine = want[2 * i:2 * i + 2]
-            e = float((mine - plain[rows]).abs().max()) / float(plain[rows].abs().max())
-            assert e <= TOLERANCE["float32"], f"32-bit engine vs plain, request {i}: {e:.3e}"
+def test_layer_sizes_of_the_large_models(shape):
+    tf32 = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        g = torch.Generator().manual_seed(1)
+        prompts = [torch.randint(3, 50272, (n,), generator=g).tolist() for n in (300, 41, 77)]
+        m32, cfg, tensors = _build(shape, "float32")
+        w = {k: v.float() for k, v in tensors.items()}
+        short = prompts[1][:9]
+        cpu = opt_plain.forward_logits(short, {k: v.cpu() for k, v in tensors.items()}, cfg.to_dict())
+        assert rel_error(plain_one_layer_on_gpu(short, w, cfg).cpu(), cpu) <= 1e-5, "the restatement is the plain implementation"
+        plain = [plain_one_layer_on_gpu(p, w, cfg) for p in prompts]
+        got32, where = _run(m32, prompts)
+        want = torch.stack([plain[r][pos] for r, pos in where])
+        for row, (r, pos) in enumerate(where):
+            e = rel_error(got32[row], want[row])
+            assert e <= TOLERANCE["float32"], f"{shape} float32: request {r} position {pos}: {e:.3e}"
+        del m32, w, plain
+        for dtype in ("bfloat16", "float16"):
+            # a float16 engine is given the same values stored as float16 (random N(0, 0.02) values lose
+            # bits going from bfloat16 storage to float16 only below 2^-14, which they do not reach)
+            t16 = tensors if dtype == "bfloat16" else {k: (v.to(torch.float16) if v.dtype == torch.bfloat16 else v)
+                                                         for k, v in tensors.items()}
+            if dtype == "float16":
+                t16["lm_head.weight"] = t16["model.decoder.embed_tokens.weight"]
+            m16, _, _ = _build(shape, dtype, t16)
+            got16, _ = _run(m16, prompts)
+            del m16
+            assert torch.isfinite(got16).all()
+            for row, (r, pos) in enumerate(where):
+                e = rel_error(got16[row], want[row])
+                assert e <= TOLERANCE[dtype], f"{shape} {dtype}: request {r} position {pos}: {e:.3e}"
+        from transformers_neuronx_b200.kernels import ops
+        ops.raise_on_device_error()
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = tf32

@@ -19,27 +19,62 @@ from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 from .allocator import OutOfPages, PagePool, SlotTable
 
 
+# What a mixer keeps between steps is described by a *need*: any (hashable, comparable) object with
+#
+#   group_key                    ("paged", window, ...) for a cache that lives in pages, anything else
+#                                for state that is indexed by the request's slot; needs with equal
+#                                keys share a page pool and the request's block table
+#   window                       (paged needs) None, or how many last positions are read
+#   make_storage(page_size, num_pages, max_slots, act_dtype, device) -> the device tensor
+#   bytes_per_page(page_size, act_dtype)   (paged needs) for sizing a pool
+#   clear_on_admission           True: the slot's row is zeroed when a request takes the slot
+#
+# The two kinds below are what the package's own mixers use; another kind (keys and values in a
+# compressed form, in another element type, ...) is a class with this interface, defined anywhere:
+# neither this file nor storage.py has to know it.
+def _element_size(dtype) -> int:
+    import torch
+    return torch.empty((), dtype=dtype).element_size()
+
+
 @dataclass(frozen=True)
 class PagedKVNeed:
-    """Keys and values of every position (window None) or of the last `window` positions."""
+    """Keys and values of every position (window None) or of the last `window` positions, in the
+    engine's activation type: one tensor [pages, 2 (key, value), n_kv_heads, page_size, head_dim]."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    clear_on_admission = False
 
     @property
     def group_key(self):
         return ("paged", self.window)
 
+    def make_storage(self, page_size, num_pages, max_slots, act_dtype, device):
+        import torch
+        # zeroed once: the tensor-core attention multiplies rows that no token has written yet by
+        # probabilities that are exactly zero, so they must hold finite numbers
+        return torch.zeros((num_pages, 2, self.n_kv_heads, page_size, self.head_dim), dtype=act_dtype, device=device)
+
+    def bytes_per_page(self, page_size, act_dtype) -> int:
+        return 2 * self.n_kv_heads * page_size * self.head_dim * _element_size(act_dtype)
+
 
 @dataclass(frozen=True)
 class FixedStateNeed:
-    """State of fixed size per request, e.g. of a recurrent mixer: shape and dtype name."""
+    """State of fixed size per request, e.g. of a recurrent mixer: shape and dtype name; one tensor
+    [slots, *shape].  A request that takes a slot finds its row zeroed."""
     shape: Tuple[int, ...]
     dtype: str = "float32"
+    clear_on_admission = True
 
     @property
     def group_key(self):
         return ("state",)
+
+    def make_storage(self, page_size, num_pages, max_slots, act_dtype, device):
+        import torch
+        return torch.zeros((max_slots,) + tuple(self.shape), dtype=getattr(torch, self.dtype), device=device)
 
 
 @dataclass
@@ -82,6 +117,7 @@ class CacheManager:
         self.pools = [PagePool(num_pages) for _ in self.paged_groups]
         self.slots = SlotTable(max_slots)
         self._req: Dict[Hashable, _Request] = {}
+        self.on_slot_taken = None      # called with the slot when a request is admitted (the storage clears state there)
 
     # ---- queries ------------------------------------------------------------------------
     def __contains__(self, rid) -> bool:
@@ -127,6 +163,8 @@ class CacheManager:
             raise ValueError(f"request {rid!r} is already live")
         slot = self.slots.take(rid)
         self._req[rid] = _Request(slot=slot, tables=[[] for _ in self.paged_groups])
+        if self.on_slot_taken is not None:
+            self.on_slot_taken(slot)
         return slot
 
     def append(self, rid, n_new: int) -> int:

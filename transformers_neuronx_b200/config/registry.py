@@ -14,9 +14,8 @@ from typing import Any, Callable, Dict
 class Architecture:
     name: str                 # e.g. "OPTForCausalLM"
     model_type: str           # e.g. "opt"
-    config_class: Any         # has from_dict(dict)
+    config_class: Any         # has from_dict(dict), from_pretrained(folder), save(folder), init_std
     build_spec: Callable      # config -> ModelSpec
-    random_tensors: Callable  # (config, seed) -> {name: tensor}; the seeded random-weights mode
 
 
 _ARCHITECTURES: Dict[str, Architecture] = {}
@@ -31,9 +30,17 @@ def architectures() -> Dict[str, Architecture]:
     return dict(_ARCHITECTURES)
 
 
+_builtin_loaded = False
+
+
 def _ensure_builtin() -> None:
-    if "OPTForCausalLM" not in _ARCHITECTURES:
-        from ..models import opt  # noqa: F401  (registers itself)
+    """The architectures that ship with the package register themselves when the `models` package
+    is imported (models/__init__.py lists them); anything else calls register_architecture()."""
+    global _builtin_loaded
+    if not _builtin_loaded:
+        _builtin_loaded = True
+        import importlib
+        importlib.import_module(__name__.rsplit(".", 2)[0] + ".models")
 
 
 def resolve_architecture(config_dict: Dict[str, Any]) -> Architecture:
@@ -49,6 +56,12 @@ def resolve_architecture(config_dict: Dict[str, Any]) -> Architecture:
     raise KeyError(
         f"no model registered for architectures={names!r} / model_type={mt!r}; "
         f"supported: {sorted(_ARCHITECTURES)}")
+
+
+def config_from_dict(d: Dict[str, Any]):
+    """(architecture, typed config) for the contents of a config.json."""
+    arch = resolve_architecture(d)
+    return arch, arch.config_class.from_dict(d)
 
 
 def load_config(folder: str):

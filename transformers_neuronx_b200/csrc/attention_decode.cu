@@ -25,23 +25,23 @@ constexpr int WARPS = 4;
 constexpr int PAGE = 16;
 
 struct DecodeParams {
-    const bf16* q; int q_stride;
-    const bf16* cache;
+    const h16* q; int q_stride;
+    const h16* cache;
     const int* block_tables; int bt_stride;
     const int* rows;                 // rows of the batch that are decode tokens (null: all rows)
     const int* token_request;
     const int* positions;
-    bf16* out; int out_stride;
+    h16* out; int out_stride;
     int n_heads, n_kv_heads, head_dim;
     int window;
     float scale;
     int n_splits, pages_per_split;
     float* scratch;                  // [rows][heads][splits][head_dim + 2]
     int* counters;                   // [rows][heads], zero between calls
-    const bf16* k_new;               // [rows, kv_heads * head_dim] keys of the rows' own tokens, or null:
-    const bf16* v_new;               //   then the cache already holds them
+    const h16* k_new;               // [rows, kv_heads * head_dim] keys of the rows' own tokens, or null:
+    const h16* v_new;               //   then the cache already holds them
     int kv_stride;
-    bf16* cache_w;
+    h16* cache_w;
 };
 
 // LPK lanes share one key (each 8 dims); KPL = 32 / LPK keys are read per warp-wide load.
@@ -74,9 +74,9 @@ attention_decode_kernel(const DecodeParams p) {
 
     float q[8];
     {
-        const bf16* qrow = p.q + (size_t)row * p.q_stride + (size_t)h * d + sub * 8;
+        const h16* qrow = p.q + (size_t)row * p.q_stride + (size_t)h * d + sub * 8;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) q[i] = dim_ok ? __bfloat162float(qrow[i]) * p.scale : 0.f;
+        for (int i = 0; i < 8; ++i) q[i] = dim_ok ? h16_to_float(qrow[i]) * p.scale : 0.f;
     }
     float m = -INFINITY, l = 0.f, acc[8];
 #pragma unroll
@@ -97,8 +97,8 @@ attention_decode_kernel(const DecodeParams p) {
         const int pieces = d / 8;
         for (int i = threadIdx.x; i < 2 * pieces; i += WARPS * 32) {
             const int which = i / pieces, piece = i - which * pieces;
-            const bf16* src = (which ? p.v_new : p.k_new) + (size_t)row * p.kv_stride + (size_t)kvh * d;
-            bf16* dst = p.cache_w + (((size_t)page * 2 + which) * p.n_kv_heads + kvh) * head_block + (size_t)(pos % PAGE) * d;
+            const h16* src = (which ? p.v_new : p.k_new) + (size_t)row * p.kv_stride + (size_t)kvh * d;
+            h16* dst = p.cache_w + (((size_t)page * 2 + which) * p.n_kv_heads + kvh) * head_block + (size_t)(pos % PAGE) * d;
             ((uint4*)dst)[piece] = ((const uint4*)src)[piece];
         }
     }
@@ -114,8 +114,8 @@ attention_decode_kernel(const DecodeParams p) {
     auto issue = [&](int t, uint4 (&kb)[CH], uint4 (&vb)[CH]) {
         const int pg = page_lo + warp + (t / CPP) * WARPS;
         const int page = bt[pg];
-        const bf16* kbase = p.cache + (((size_t)page * 2 + 0) * p.n_kv_heads + kvh) * head_block;
-        const bf16* vbase = p.cache + (((size_t)page * 2 + 1) * p.n_kv_heads + kvh) * head_block;
+        const h16* kbase = p.cache + (((size_t)page * 2 + 0) * p.n_kv_heads + kvh) * head_block;
+        const h16* vbase = p.cache + (((size_t)page * 2 + 1) * p.n_kv_heads + kvh) * head_block;
         const int i0 = (t % CPP) * CH;
 #pragma unroll
         for (int i = 0; i < CH; ++i) {
@@ -135,11 +135,11 @@ attention_decode_kernel(const DecodeParams p) {
         float chunk_max = -INFINITY;
 #pragma unroll
         for (int i = 0; i < CH; ++i) {
-            const __nv_bfloat162* kk = (const __nv_bfloat162*)&kb[i];
+            const h16x2* kk = (const h16x2*)&kb[i];
             float dot = 0.f;
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-                const float2 f = __bfloat1622float2(kk[u]);
+                const float2 f = h16x2_to_float2(kk[u]);
                 dot = fmaf(q[2 * u], f.x, dot);
                 dot = fmaf(q[2 * u + 1], f.y, dot);
             }
@@ -164,10 +164,10 @@ attention_decode_kernel(const DecodeParams p) {
             const float pj = live ? __expf(s[i] - m) : 0.f;
             l += pj;
             if (!live) vb[i] = make_uint4(0, 0, 0, 0);            // rows never written may hold anything, NaN included
-            const __nv_bfloat162* vv = (const __nv_bfloat162*)&vb[i];
+            const h16x2* vv = (const h16x2*)&vb[i];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-                const float2 f = __bfloat1622float2(vv[u]);
+                const float2 f = h16x2_to_float2(vv[u]);
                 acc[2 * u] = fmaf(pj, f.x, acc[2 * u]);
                 acc[2 * u + 1] = fmaf(pj, f.y, acc[2 * u + 1]);
             }
@@ -185,15 +185,15 @@ attention_decode_kernel(const DecodeParams p) {
     }
     if (own_here && warp == 0) {
         // the token's own key and value, as one more key of warp 0 (the lanes of key group 0)
-        const bf16* ksrc = p.k_new + (size_t)row * p.kv_stride + (size_t)kvh * d + sub * 8;
-        const bf16* vsrc = p.v_new + (size_t)row * p.kv_stride + (size_t)kvh * d + sub * 8;
+        const h16* ksrc = p.k_new + (size_t)row * p.kv_stride + (size_t)kvh * d + sub * 8;
+        const h16* vsrc = p.v_new + (size_t)row * p.kv_stride + (size_t)kvh * d + sub * 8;
         const uint4 kown = dim_ok ? *(const uint4*)ksrc : make_uint4(0, 0, 0, 0);
         const uint4 vown = dim_ok ? *(const uint4*)vsrc : make_uint4(0, 0, 0, 0);
-        const __nv_bfloat162* kk = (const __nv_bfloat162*)&kown;
+        const h16x2* kk = (const h16x2*)&kown;
         float dot = 0.f;
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
-            const float2 f = __bfloat1622float2(kk[t]);
+            const float2 f = h16x2_to_float2(kk[t]);
             dot = fmaf(q[2 * t], f.x, dot);
             dot = fmaf(q[2 * t + 1], f.y, dot);
         }
@@ -209,10 +209,10 @@ attention_decode_kernel(const DecodeParams p) {
         if (kgrp == 0) {
             const float pj = __expf(s_own - m);
             l += pj;
-            const __nv_bfloat162* vv = (const __nv_bfloat162*)&vown;
+            const h16x2* vv = (const h16x2*)&vown;
 #pragma unroll
             for (int t = 0; t < 4; ++t) {
-                const float2 f = __bfloat1622float2(vv[t]);
+                const float2 f = h16x2_to_float2(vv[t]);
                 acc[2 * t] = fmaf(pj, f.x, acc[2 * t]);
                 acc[2 * t + 1] = fmaf(pj, f.y, acc[2 * t + 1]);
             }
@@ -248,7 +248,7 @@ attention_decode_kernel(const DecodeParams p) {
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) o_val += sm_acc[w][t2] * f[w];
         if (p.n_splits == 1) {
-            p.out[(size_t)row * p.out_stride + (size_t)h * d + t2] = __float2bfloat16_rn(o_val / L);
+            p.out[(size_t)row * p.out_stride + (size_t)h * d + t2] = float_to_h16(o_val / L);
         } else {
             float* dst = p.scratch + (((size_t)ri * p.n_heads + h) * p.n_splits + split) * (d + 2);
             dst[2 + t2] = o_val;
@@ -306,7 +306,7 @@ attention_decode_kernel(const DecodeParams p) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) if (ms[i] != -INFINITY) o += vs[i] * __expf(ms[i] - GM);
         }
-        p.out[(size_t)row * p.out_stride + (size_t)h * d + t2] = __float2bfloat16_rn(o / GL);
+        p.out[(size_t)row * p.out_stride + (size_t)h * d + t2] = float_to_h16(o / GL);
     }
 }
 
@@ -334,12 +334,12 @@ TNX_EXPORT int tnx_attention_decode_append(const void* q, int q_stride, void* ca
     if (n_splits < 1 || pages_per_split < 1) return TNX_ERR_BAD_ARG;
     if (n_splits > 1 && (!scratch || !counters)) return TNX_ERR_BAD_ARG;
     DecodeParams p;
-    p.q = (const bf16*)q; p.q_stride = q_stride; p.cache = (const bf16*)cache;
+    p.q = (const h16*)q; p.q_stride = q_stride; p.cache = (const h16*)cache;
     p.block_tables = block_tables; p.bt_stride = bt_stride; p.rows = rows; p.token_request = token_request;
-    p.positions = positions; p.out = (bf16*)out; p.out_stride = out_stride;
+    p.positions = positions; p.out = (h16*)out; p.out_stride = out_stride;
     p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.head_dim = head_dim; p.window = window; p.scale = scale;
     p.n_splits = n_splits; p.pages_per_split = pages_per_split; p.scratch = scratch; p.counters = counters;
-    p.k_new = (const bf16*)k_new; p.v_new = (const bf16*)v_new; p.kv_stride = kv_stride; p.cache_w = (bf16*)cache;
+    p.k_new = (const h16*)k_new; p.v_new = (const h16*)v_new; p.kv_stride = kv_stride; p.cache_w = (h16*)cache;
     dim3 grid(n_heads, n_rows, n_splits);
     const int chunks = head_dim / 8;
     const dim3 block(WARPS * 32);

@@ -9,7 +9,7 @@
 // Eight warps, 16 query rows each.  K and V tiles of 64 keys (four pages) are copied to shared
 // memory with cp.async (16-byte chunks, XOR-swizzled rows) into two buffers, the next tile while
 // the current one is used; S = Q K^T and O += P V run on tensor
-// cores (mma.sync m16n8k16, bf16 in, 32-bit accumulate); scores, softmax and the running sums are
+// cores (mma.sync m16n8k16, h16 in, 32-bit accumulate); scores, softmax and the running sums are
 // 32-bit.  HEAD is the head size rounded up to 64, 128 or 256; the columns beyond the real head
 // size are zero in shared memory.
 #include "common.cuh"
@@ -19,13 +19,13 @@ namespace {
 constexpr int BQ = 128, BKV = 64, PAGE = 16, WARPS = 8;
 
 struct PrefillParams {
-    const bf16* q; int q_stride;
-    const bf16* cache;
+    const h16* q; int q_stride;
+    const h16* cache;
     const int* block_tables; int bt_stride;
     const int* tile_req;             // per work item: request index in the batch
     const int* tile_q0;              // per work item: first query row within the request's portion
     const int* q_start; const int* q_len; const int* ctx_len;
-    bf16* out; int out_stride;
+    h16* out; int out_stride;
     int n_heads, n_kv_heads, head_dim;
     int window;
     float scale_log2;                // scale * log2(e)
@@ -46,8 +46,12 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t add
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
-__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+__device__ __forceinline__ void mma_h16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+#ifdef TNX_F16
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+#else
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+#endif
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
@@ -56,12 +60,12 @@ __device__ __forceinline__ float ex2_approx(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+__device__ __forceinline__ uint32_t pack_h16(float lo, float hi) {
+    h16x2 h = floats_to_h16x2(lo, hi);
     return *(uint32_t*)&h;
 }
 
-// Byte offset of (row, 16-byte chunk) in a tile whose rows hold HEAD bf16, chunks XOR-swizzled.
+// Byte offset of (row, 16-byte chunk) in a tile whose rows hold HEAD h16, chunks XOR-swizzled.
 template <int HEAD>
 __device__ __forceinline__ uint32_t swz(int row, int chunk) {
     return (uint32_t)(row * (HEAD * 2) + ((chunk ^ (row & 7)) << 4));
@@ -124,7 +128,7 @@ attention_prefill_kernel(const PrefillParams p) {
             if (key < kv_total) {
                 const int page = bt[key / PAGE];
                 if (page >= 0) {
-                    const bf16* kb = p.cache + (((size_t)page * 2 + 0) * p.n_kv_heads + kvh) * head_block +
+                    const h16* kb = p.cache + (((size_t)page * 2 + 0) * p.n_kv_heads + kvh) * head_block +
                                      (size_t)(key % PAGE) * d + c * 8;
                     cp_async16(sK + swz<HEAD>(r, c), kb);
                     cp_async16(sV + swz<HEAD>(r, c), kb + (size_t)p.n_kv_heads * head_block);
@@ -160,8 +164,8 @@ attention_prefill_kernel(const PrefillParams p) {
                 uint32_t b[4];
                 const int row = nn * 16 + (lane & 7) + ((lane >> 4) << 3), chunk = kk * 2 + ((lane >> 3) & 1);
                 ldmatrix_x4(b, smem_addr(sK + swz<HEAD>(row, chunk)));
-                mma_bf16(s[2 * nn], a, b[0], b[1]);
-                mma_bf16(s[2 * nn + 1], a, b[2], b[3]);
+                mma_h16(s[2 * nn], a, b[0], b[1]);
+                mma_h16(s[2 * nn + 1], a, b[2], b[3]);
             }
         }
         // ---- mask, online softmax ------------------------------------------------------------------
@@ -221,17 +225,17 @@ attention_prefill_kernel(const PrefillParams p) {
 #pragma unroll
         for (int kk = 0; kk < BKV / 16; ++kk) {
             uint32_t a[4];
-            a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
-            a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
-            a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-            a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+            a[0] = pack_h16(s[2 * kk][0], s[2 * kk][1]);
+            a[1] = pack_h16(s[2 * kk][2], s[2 * kk][3]);
+            a[2] = pack_h16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+            a[3] = pack_h16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
 #pragma unroll
             for (int nn = 0; nn < HEAD / 16; ++nn) {
                 uint32_t b[4];
                 const int row = kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3), chunk = nn * 2 + (lane >> 4);
                 ldmatrix_x4_trans(b, smem_addr(sV + swz<HEAD>(row, chunk)));
-                mma_bf16(o[2 * nn], a, b[0], b[1]);
-                mma_bf16(o[2 * nn + 1], a, b[2], b[3]);
+                mma_h16(o[2 * nn], a, b[0], b[1]);
+                mma_h16(o[2 * nn + 1], a, b[2], b[3]);
             }
         }
         __syncthreads();                                     // every warp is done with this buffer
@@ -249,10 +253,10 @@ attention_prefill_kernel(const PrefillParams p) {
         if (col < d) {
             if (r_lo < rows)
                 *(uint32_t*)(p.out + (size_t)(qs + q0 + r_lo) * p.out_stride + (size_t)h * d + col) =
-                    pack_bf16(o[nt][0] * inv0, o[nt][1] * inv0);
+                    pack_h16(o[nt][0] * inv0, o[nt][1] * inv0);
             if (r_lo + 8 < rows)
                 *(uint32_t*)(p.out + (size_t)(qs + q0 + r_lo + 8) * p.out_stride + (size_t)h * d + col) =
-                    pack_bf16(o[nt][2] * inv1, o[nt][3] * inv1);
+                    pack_h16(o[nt][2] * inv1, o[nt][3] * inv1);
         }
     }
 }
@@ -283,9 +287,9 @@ TNX_EXPORT int tnx_attention_prefill(const void* q, int q_stride, const void* ca
         ((uintptr_t)out & 3))
         return TNX_ERR_UNSUPPORTED;
     PrefillParams p;
-    p.q = (const bf16*)q; p.q_stride = q_stride; p.cache = (const bf16*)cache; p.block_tables = block_tables;
+    p.q = (const h16*)q; p.q_stride = q_stride; p.cache = (const h16*)cache; p.block_tables = block_tables;
     p.bt_stride = bt_stride; p.tile_req = tile_req; p.tile_q0 = tile_q0; p.q_start = q_start; p.q_len = q_len;
-    p.ctx_len = ctx_len; p.out = (bf16*)out; p.out_stride = out_stride; p.n_heads = n_heads; p.n_kv_heads = n_kv_heads;
+    p.ctx_len = ctx_len; p.out = (h16*)out; p.out_stride = out_stride; p.n_heads = n_heads; p.n_kv_heads = n_kv_heads;
     p.head_dim = head_dim; p.window = window; p.scale_log2 = scale * 1.4426950408889634f;
     if (head_dim <= 64) return launch<64>(p, n_items, stream);
     if (head_dim <= 128) return launch<128>(p, n_items, stream);

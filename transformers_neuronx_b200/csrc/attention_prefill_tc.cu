@@ -52,7 +52,7 @@ struct TcPrefillParams {
     const int* block_tables; int bt_stride;
     const int* tile_req; const int* tile_q0;
     const int* q_start; const int* q_len; const int* ctx_len;
-    bf16* out; int out_stride;
+    h16* out; int out_stride;
     int n_heads, n_kv_heads;
     int window;
     float scale_log2;
@@ -75,8 +75,8 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
           "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
-// D (+)= A B with A read from tensor memory (lane = row, a column = two consecutive bf16 of K).
-__device__ __forceinline__ void umma_bf16_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+// D (+)= A B with A read from tensor memory (lane = row, a column = two consecutive h16 of K).
+__device__ __forceinline__ void umma_h16_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
@@ -98,9 +98,9 @@ __device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t saddr, uint32_t 
     d |= (uint64_t)2 << 61;
     return d;
 }
-// D = f32, A = B = bf16, M = 128, N = n; b_mn: B is MN-major.
+// D = f32, A = B = h16, M = 128, N = n; b_mn: B is MN-major.
 __host__ __device__ constexpr uint32_t idesc_attn(int n, int b_mn) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+    return (1u << 4) | IDESC_H16_AB | ((uint32_t)b_mn << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
 
 template <int D, int K_STAGES, int V_STAGES>
@@ -194,6 +194,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         auto load_tile = [&](int j, int which, uint8_t* stage, uint64_t* full, uint64_t* empty, uint32_t parity, int code) {
             int n_valid;
             const int page = tile_page(j, n_valid);
+            // Only pages that are copied are announced: behind a sliding window the first tile may
+            // begin with blocks that were given back already (-1 in the block table); their part of
+            // the stage keeps finite numbers, and the window masks those keys.
+            n_valid = __popc(__ballot_sync(0xffffffffu, lane < 8 && a == 0 && page >= 0));
             int good = 1;
             if (lane == 0) {
                 good = mbar_wait(empty, parity, p.err, code) ? 1 : 0;
@@ -236,9 +240,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 const uint32_t v_addr = smem_u32(sV + (j % V_STAGES) * KV_BYTES);
 #pragma unroll
                 for (int k = 0; k < BKV / 16; ++k) {
-                    // 16 keys further: 8 columns of P (two bf16 each), 16 rows of V
+                    // 16 keys further: 8 columns of P (two h16 each), 16 rows of V
                     const uint64_t bdesc = smem_desc_sw128_mn(v_addr + k * 16 * 128, ATOM_KV);
-                    umma_bf16_a_tmem(tmem_base + 128, p_tmem + (uint32_t)(k * 8), bdesc, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+                    umma_h16_a_tmem(tmem_base + 128, p_tmem + (uint32_t)(k * 8), bdesc, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
                 }
                 umma_commit(&o_full);
                 umma_commit(&v_empty[j % V_STAGES]);          // the V tile is free, and so is P's place in the score buffer
@@ -266,7 +270,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 for (int k = 0; k < D / 16; ++k) {
                     const uint64_t adesc = smem_desc_sw128(q_addr + (k >> 2) * ATOM_Q + (k & 3) * 32);
                     const uint64_t bdesc = smem_desc_sw128(k_addr + (k >> 2) * ATOM_KV + (k & 3) * 32);
-                    umma_bf16(d_tmem, adesc, bdesc, idesc_qk, k > 0 ? 1u : 0u);
+                    umma_h16(d_tmem, adesc, bdesc, idesc_qk, k > 0 ? 1u : 0u);
                 }
                 umma_commit(&s_full[n & 1]);
                 umma_commit(&k_empty[n % K_STAGES]);          // the K tile is free once these MMAs have read it
@@ -327,7 +331,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 const float p0 = ex2_approx(fmaf(s[2 * i], p.scale_log2, -m_scaled));
                 const float p1 = ex2_approx(fmaf(s[2 * i + 1], p.scale_log2, -m_scaled));
                 sum4[i & 3] += p0 + p1;
-                __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
+                h16x2 h2 = floats_to_h16x2(p0, p1);
                 packed[i] = *(uint32_t*)&h2;
             }
             const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
@@ -365,7 +369,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (ok) {
             tc_fence_after();
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-            bf16* orow = p.out + (size_t)(qs + q0 + r) * p.out_stride + (size_t)h * D;
+            h16* orow = p.out + (size_t)(qs + q0 + r) * p.out_stride + (size_t)h * D;
 #pragma unroll 1
             for (int c = 0; c < D; c += 32) {
                 uint32_t o[32];
@@ -375,10 +379,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
                         uint4 u;
-                        __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(o[8 * q]) * inv, __uint_as_float(o[8 * q + 1]) * inv);
-                        __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(o[8 * q + 2]) * inv, __uint_as_float(o[8 * q + 3]) * inv);
-                        __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(o[8 * q + 4]) * inv, __uint_as_float(o[8 * q + 5]) * inv);
-                        __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(o[8 * q + 6]) * inv, __uint_as_float(o[8 * q + 7]) * inv);
+                        h16x2 h0 = floats_to_h16x2(__uint_as_float(o[8 * q]) * inv, __uint_as_float(o[8 * q + 1]) * inv);
+                        h16x2 h1 = floats_to_h16x2(__uint_as_float(o[8 * q + 2]) * inv, __uint_as_float(o[8 * q + 3]) * inv);
+                        h16x2 h2 = floats_to_h16x2(__uint_as_float(o[8 * q + 4]) * inv, __uint_as_float(o[8 * q + 5]) * inv);
+                        h16x2 h3 = floats_to_h16x2(__uint_as_float(o[8 * q + 6]) * inv, __uint_as_float(o[8 * q + 7]) * inv);
                         u.x = *(uint32_t*)&h0; u.y = *(uint32_t*)&h1; u.z = *(uint32_t*)&h2; u.w = *(uint32_t*)&h3;
                         *(uint4*)(orow + c + 8 * q) = u;
                     }
@@ -429,7 +433,7 @@ TNX_EXPORT int tnx_attention_prefill_tc(const void* q, int q_stride, int n_rows_
     if (!make_map(&mkv, cache, (int)cache_rows, head_dim, head_dim, PAGE)) return TNX_ERR_UNSUPPORTED;
     TcPrefillParams p;
     p.block_tables = block_tables; p.bt_stride = bt_stride; p.tile_req = tile_req; p.tile_q0 = tile_q0;
-    p.q_start = q_start; p.q_len = q_len; p.ctx_len = ctx_len; p.out = (bf16*)out; p.out_stride = out_stride;
+    p.q_start = q_start; p.q_len = q_len; p.ctx_len = ctx_len; p.out = (h16*)out; p.out_stride = out_stride;
     p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.window = window; p.scale_log2 = scale * 1.4426950408889634f;
     p.err = err_word;
     if (head_dim == 128) return launch_tc<128, 2, 3>(mq, mkv, p, n_heads, n_items, stream);

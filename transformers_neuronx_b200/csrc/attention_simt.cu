@@ -89,7 +89,7 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, const T* __restrict
 TNX_EXPORT int tnx_attention_simt(const void* q, int q_stride, const void* cache, const int* block_tables,
                                   int bt_stride, const int* token_request, const int* positions, void* out,
                                   int out_stride, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
-                                  int page_size, int window, float scale, int is_bf16, cudaStream_t stream) {
+                                  int page_size, int window, float scale, int is_h16, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (head_dim <= 0 || head_dim > 32 * MAX_DIMS_PER_LANE || n_kv_heads <= 0 || n_heads % n_kv_heads)
         return TNX_ERR_UNSUPPORTED;
@@ -97,10 +97,10 @@ TNX_EXPORT int tnx_attention_simt(const void* q, int q_stride, const void* cache
     const long long pairs = (long long)n_tokens * n_heads;
     const int blocks = (int)((pairs + warps - 1) / warps);
     const size_t smem = (size_t)warps * head_dim * sizeof(float);
-    if (is_bf16)
-        return tnx_launch_pdl(attention_simt_kernel<bf16>, dim3(blocks), dim3(warps * 32), smem, stream,
-                              (const bf16*)q, q_stride, (const bf16*)cache, block_tables, bt_stride, token_request,
-                              positions, (bf16*)out, out_stride, n_tokens, n_heads, n_kv_heads, head_dim, page_size,
+    if (is_h16)
+        return tnx_launch_pdl(attention_simt_kernel<h16>, dim3(blocks), dim3(warps * 32), smem, stream,
+                              (const h16*)q, q_stride, (const h16*)cache, block_tables, bt_stride, token_request,
+                              positions, (h16*)out, out_stride, n_tokens, n_heads, n_kv_heads, head_dim, page_size,
                               window, scale);
     return tnx_launch_pdl(attention_simt_kernel<float>, dim3(blocks), dim3(warps * 32), smem, stream,
                           (const float*)q, q_stride, (const float*)cache, block_tables, bt_stride, token_request,

@@ -3,6 +3,7 @@
 // ctypes, passes device pointers and the current CUDA stream, and checks the returned code.
 #pragma once
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -19,7 +20,35 @@ static inline int tnx_launch_status() {
     return (int)e;
 }
 
-typedef __nv_bfloat16 bf16;
+// The 16-bit floating type of this build.  Every library is compiled once with bfloat16 as `h16` and,
+// when a model asks for it, once more with TNX_F16 defined, where `h16` is IEEE half precision
+// (float16): the same kernels, other conversions, other operand formats of the tensor-core instructions.
+// An entry point's `*_h16` flags say "this tensor holds h16" (0: 32-bit floats).
+#ifdef TNX_F16
+typedef __half h16;
+typedef __half2 h16x2;
+#define TNX_H16_NAME "float16"
+__device__ __forceinline__ float h16_to_float(h16 v) { return __half2float(v); }
+__device__ __forceinline__ h16 float_to_h16(float v) { return __float2half_rn(v); }
+__device__ __forceinline__ float2 h16x2_to_float2(h16x2 v) { return __half22float2(v); }
+__device__ __forceinline__ h16x2 floats_to_h16x2(float a, float b) { return __floats2half2_rn(a, b); }
+#else
+typedef __nv_bfloat16 h16;
+typedef __nv_bfloat162 h16x2;
+#define TNX_H16_NAME "bfloat16"
+__device__ __forceinline__ float h16_to_float(h16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ h16 float_to_h16(float v) { return __float2bfloat16_rn(v); }
+__device__ __forceinline__ float2 h16x2_to_float2(h16x2 v) { return __bfloat1622float2(v); }
+__device__ __forceinline__ h16x2 floats_to_h16x2(float a, float b) { return __floats2bfloat162_rn(a, b); }
+#endif
+// 1 when this library was built with float16 as its 16-bit type, 0 for bfloat16.
+TNX_EXPORT int tnx_h16_is_float16() {
+#ifdef TNX_F16
+    return 1;
+#else
+    return 0;
+#endif
+}
 
 // Programmatic dependent launch.  Every kernel of the engine is launched with the attribute that
 // lets it start while the kernel before it in the stream is still running.  The rules each kernel
@@ -69,11 +98,33 @@ static inline int tnx_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block
 }
 
 __device__ __forceinline__ float to_float(float v) { return v; }
-__device__ __forceinline__ float to_float(bf16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float to_float(h16 v) { return h16_to_float(v); }
 
 template <typename T> __device__ __forceinline__ T from_float(float v);
 template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
-template <> __device__ __forceinline__ bf16 from_float<bf16>(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ h16 from_float<h16>(float v) { return float_to_h16(v); }
+
+// Activations that a product's epilogue applies to (sum + bias), by code: the names of
+// src/transformers_neuronx/activations.py (relu :43-48, gelu_new :17-41 with its tanh form, sigmoid
+// :66-67, silu :70-72) plus the exact (erf) gelu.  The code travels to the kernel as a number, so
+// another activation is one more case here and one more name in kernels/ops.py.
+#define TNX_ACT_NONE 0
+#define TNX_ACT_RELU 1
+#define TNX_ACT_GELU_NEW 2
+#define TNX_ACT_SILU 3
+#define TNX_ACT_SIGMOID 4
+#define TNX_ACT_GELU 5
+#define TNX_ACT_COUNT 6
+__device__ __forceinline__ float apply_activation(float v, int act) {
+    switch (act) {
+        case TNX_ACT_RELU: return fmaxf(v, 0.f);
+        case TNX_ACT_GELU_NEW: return 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+        case TNX_ACT_SILU: return v / (1.f + expf(-v));
+        case TNX_ACT_SIGMOID: return 1.f / (1.f + expf(-v));
+        case TNX_ACT_GELU: return 0.5f * v * (1.f + erff(v * 0.7071067811865476f));
+        default: return v;
+    }
+}
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

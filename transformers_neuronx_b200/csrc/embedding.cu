@@ -51,30 +51,30 @@ TNX_EXPORT int tnx_patch_tokens(int* tokens, const int* src, const int* sampled,
     return tnx_launch_pdl(patch_tokens_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, tokens, src, sampled, n);
 }
 
-// table_bf16 / act_bf16: 1 when the tables / the activation output are bfloat16, 0 for float.
+// table_h16 / act_h16: 1 when the tables / the activation output are bfloat16, 0 for float.
 TNX_EXPORT int tnx_embed(const void* tok_table, const float* pre, const int* ids, const void* pos_table,
                          const int* positions, int pos_offset, float* out_f32, void* out_act,
-                         int N, int H, int table_bf16, int act_bf16, cudaStream_t stream) {
+                         int N, int H, int table_h16, int act_h16, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (H <= 0 || (!tok_table && !pre)) return TNX_ERR_BAD_ARG;
     const int threads = H >= 1024 ? 256 : 128;
 #define LAUNCH(TT, TA)                                                                                        \
     tnx_launch_pdl(embed_kernel<TT, TA>, dim3(N), dim3(threads), 0, stream, (const TT*)tok_table, pre, ids,   \
                    (const TT*)pos_table, positions, pos_offset, out_f32, (TA*)out_act, H)
-    if (table_bf16 && act_bf16) return LAUNCH(bf16, bf16);
-    if (table_bf16 && !act_bf16) return LAUNCH(bf16, float);
-    if (!table_bf16 && act_bf16) return LAUNCH(float, bf16);
+    if (table_h16 && act_h16) return LAUNCH(h16, h16);
+    if (table_h16 && !act_h16) return LAUNCH(h16, float);
+    if (!table_h16 && act_h16) return LAUNCH(float, h16);
     return LAUNCH(float, float);
 #undef LAUNCH
 }
 
 TNX_EXPORT int tnx_gather_rows(const void* table, const int* ids, void* out, int N, int E,
-                               int table_bf16, int act_bf16, cudaStream_t stream) {
+                               int table_h16, int act_h16, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (E <= 0) return TNX_ERR_BAD_ARG;
     const int threads = E >= 1024 ? 256 : 128;
-    if (table_bf16 && act_bf16) return tnx_launch_pdl(gather_rows_kernel<bf16, bf16>, dim3(N), dim3(threads), 0, stream, (const bf16*)table, ids, (bf16*)out, E);
-    if (table_bf16) return tnx_launch_pdl(gather_rows_kernel<bf16, float>, dim3(N), dim3(threads), 0, stream, (const bf16*)table, ids, (float*)out, E);
-    if (act_bf16) return tnx_launch_pdl(gather_rows_kernel<float, bf16>, dim3(N), dim3(threads), 0, stream, (const float*)table, ids, (bf16*)out, E);
+    if (table_h16 && act_h16) return tnx_launch_pdl(gather_rows_kernel<h16, h16>, dim3(N), dim3(threads), 0, stream, (const h16*)table, ids, (h16*)out, E);
+    if (table_h16) return tnx_launch_pdl(gather_rows_kernel<h16, float>, dim3(N), dim3(threads), 0, stream, (const h16*)table, ids, (float*)out, E);
+    if (act_h16) return tnx_launch_pdl(gather_rows_kernel<float, h16>, dim3(N), dim3(threads), 0, stream, (const float*)table, ids, (h16*)out, E);
     return tnx_launch_pdl(gather_rows_kernel<float, float>, dim3(N), dim3(threads), 0, stream, (const float*)table, ids, (float*)out, E);
 }

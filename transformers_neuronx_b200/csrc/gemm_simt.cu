@@ -2,7 +2,7 @@
 // cores, no reduced-precision mode), and the path for sizes that the tensor-core kernel refuses.
 //
 //   C[m, n] = epilogue( sum_k A[m, k] * W[n, k] )           A: [M, K], W: [N, K] (both row-major)
-//   epilogue: + bias[n]; ReLU; + residual[m, n] (32-bit); stored as float or bfloat16.
+//   epilogue: + bias[n]; activation (by code, common.cuh); + residual[m, n] (32-bit); stored as float or in the 16-bit type.
 //
 // Every output element adds its products in ascending k with one accumulator, so a row's result
 // does not depend on which other rows are in the call.
@@ -16,7 +16,7 @@ template <typename TA, typename TW, typename TO>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, const float* __restrict__ bias,
                  const float* residual, TO* C, int M, int N, int K, int lda, int ldw, int ldc,
-                 int relu) {
+                 int act) {
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     pdl_launch_dependents();
@@ -64,7 +64,7 @@ gemm_simt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, const float
             if (n >= N) continue;
             float v = acc[i][j];
             if (bias) v += bias[n];
-            if (relu) v = fmaxf(v, 0.f);
+            v = apply_activation(v, act);
             if (residual) v += residual[(size_t)m * ldc + n];
             C[(size_t)m * ldc + n] = from_float<TO>(v);
         }
@@ -73,30 +73,31 @@ gemm_simt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, const float
 
 template <typename TA, typename TW, typename TO>
 int launch(const void* A, const void* W, const float* bias, const float* residual, void* C, int M,
-           int N, int K, int lda, int ldw, int ldc, int relu, cudaStream_t stream) {
+           int N, int K, int lda, int ldw, int ldc, int act, cudaStream_t stream) {
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     return tnx_launch_pdl(gemm_simt_kernel<TA, TW, TO>, grid, dim3(256), 0, stream, (const TA*)A, (const TW*)W, bias,
-                          residual, (TO*)C, M, N, K, lda, ldw, ldc, relu);
+                          residual, (TO*)C, M, N, K, lda, ldw, ldc, act);
 }
 
 }  // namespace
 
-// a_bf16 / w_bf16 / c_bf16: element types (1 = bfloat16, 0 = float).  residual (32-bit, same
+// a_h16 / w_h16 / c_h16: element types (1 = bfloat16, 0 = float).  residual (32-bit, same
 // leading dimension as C) may alias C when C is float.
 TNX_EXPORT int tnx_gemm_simt(const void* A, const void* W, const float* bias, const float* residual,
-                             void* C, int M, int N, int K, int lda, int ldw, int ldc, int relu,
-                             int a_bf16, int w_bf16, int c_bf16, cudaStream_t stream) {
+                             void* C, int M, int N, int K, int lda, int ldw, int ldc, int act,
+                             int a_h16, int w_h16, int c_h16, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || lda < K || ldw < K || ldc < N) return TNX_ERR_BAD_ARG;
-    if (residual && c_bf16) return TNX_ERR_BAD_ARG;
-    const int code = (a_bf16 ? 4 : 0) | (w_bf16 ? 2 : 0) | (c_bf16 ? 1 : 0);
+    if (residual && c_h16) return TNX_ERR_BAD_ARG;
+    if (act < 0 || act >= TNX_ACT_COUNT) return TNX_ERR_BAD_ARG;
+    const int code = (a_h16 ? 4 : 0) | (w_h16 ? 2 : 0) | (c_h16 ? 1 : 0);
     switch (code) {
-        case 0: return launch<float, float, float>(A, W, bias, residual, C, M, N, K, lda, ldw, ldc, relu, stream);
-        case 2: return launch<float, bf16, float>(A, W, bias, residual, C, M, N, K, lda, ldw, ldc, relu, stream);
-        case 4: return launch<bf16, float, float>(A, W, bias, residual, C, M, N, K, lda, ldw, ldc, relu, stream);
-        case 5: return launch<bf16, float, bf16>(A, W, bias, residual, C, M, N, K, lda, ldw, ldc, relu, stream);
-        case 6: return launch<bf16, bf16, float>(A, W, bias, residual, C, M, N, K, lda, ldw, ldc, relu, stream);
-        case 7: return launch<bf16, bf16, bf16>(A, W, bias, residual, C, M, N, K, lda, ldw, ldc, relu, stream);
+        case 0: return launch<float, float, float>(A, W, bias, residual, C, M, N, K, lda, ldw, ldc, act, stream);
+        case 2: return launch<float, h16, float>(A, W, bias, residual, C, M, N, K, lda, ldw, ldc, act, stream);
+        case 4: return launch<h16, float, float>(A, W, bias, residual, C, M, N, K, lda, ldw, ldc, act, stream);
+        case 5: return launch<h16, float, h16>(A, W, bias, residual, C, M, N, K, lda, ldw, ldc, act, stream);
+        case 6: return launch<h16, h16, float>(A, W, bias, residual, C, M, N, K, lda, ldw, ldc, act, stream);
+        case 7: return launch<h16, h16, h16>(A, W, bias, residual, C, M, N, K, lda, ldw, ldc, act, stream);
         default: return TNX_ERR_UNSUPPORTED;
     }
 }

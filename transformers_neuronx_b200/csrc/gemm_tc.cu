@@ -1,8 +1,8 @@
-// bfloat16 matrix product on the 5th-generation tensor cores (tcgen05), operands brought into
+// 16-bit (bfloat16, or float16 in the f16 build) matrix product on the 5th-generation tensor cores (tcgen05), operands brought into
 // shared memory by TMA, 32-bit accumulators in tensor memory.
 //
-//   C[m, n] = epilogue( sum_k A[m, k] * W[n, k] )        A: [M, K] bf16, W: [N, K] bf16, row-major
-//   epilogue: + bias[n] (32-bit); ReLU; + residual[m, n] (32-bit); stored as bfloat16 or float.
+//   C[m, n] = epilogue( sum_k A[m, k] * W[n, k] )        A: [M, K] h16, W: [N, K] h16, row-major
+//   epilogue: + bias[n] (32-bit); activation (by code, common.cuh); + residual[m, n] (32-bit); stored in the 16-bit type or as float.
 //
 // One CTA computes one 128 x BN tile of D = P Q^T over a range of K.  Two forms:
 //   normal (many tokens): P = A (128 tokens), Q = W (BN = 128 features)
@@ -31,15 +31,15 @@
 
 namespace {
 
-constexpr int BLOCK_K = 64;          // 64 bf16 = 128 bytes = one swizzle row
+constexpr int BLOCK_K = 64;          // 64 h16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int TILE_P = 128;          // rows of the 128-row operand = TMEM lanes
 constexpr int NUM_THREADS = 192;
 constexpr int MAX_CLUSTER = 8;               // the portable cluster size
 
-// Instruction descriptor: D = f32, A = B = bf16, both K-major, M = 128, N = n.
+// Instruction descriptor: D = f32, A = B = the build's 16-bit type, both K-major, M = 128, N = n.
 __host__ __device__ constexpr uint32_t instr_desc(int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TILE_P >> 4) << 24);
+    return (1u << 4) | IDESC_H16_AB | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TILE_P >> 4) << 24);
 }
 
 struct Params {
@@ -48,8 +48,8 @@ struct Params {
     int kb_per_split;            // K blocks per split
     int splits;
     int ldc;
-    int relu;
-    int c_is_bf16;
+    int act;
+    int c_is_h16;
     const float* bias;           // indexed by feature
     const float* residual;       // [M, ldc] 32-bit, may alias C
     void* C;
@@ -103,10 +103,10 @@ __device__ __forceinline__ void store_tile_row(const Params& p, int lane_row, in
             const int m = col0 + j;
             if (j < ncols && m < p.rows_q) {
                 float x = v[j] + b;
-                if (p.relu) x = fmaxf(x, 0.f);
+                x = apply_activation(x, p.act);
                 x += res[j];
                 const size_t o = (size_t)m * p.ldc + n;
-                if (p.c_is_bf16) ((bf16*)p.C)[o] = __float2bfloat16_rn(x);
+                if (p.c_is_h16) ((h16*)p.C)[o] = float_to_h16(x);
                 else ((float*)p.C)[o] = x;
             }
         }
@@ -133,17 +133,17 @@ __device__ __forceinline__ void store_tile_row(const Params& p, int lane_row, in
             for (int j = 0; j < 32; ++j) {
                 float t = v[j];
                 if (p.bias) t += bias_s ? bias_s[j] : __ldg(p.bias + col0 + j);
-                if (p.relu) t = fmaxf(t, 0.f);
+                t = apply_activation(t, p.act);
                 x[j] += t;
             }
-            if (p.c_is_bf16) {
-                uint4* dst = (uint4*)((bf16*)p.C + rowo + col0);
+            if (p.c_is_h16) {
+                uint4* dst = (uint4*)((h16*)p.C + rowo + col0);
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
-                    __nv_bfloat162 h0 = __floats2bfloat162_rn(x[8 * q + 0], x[8 * q + 1]);
-                    __nv_bfloat162 h1 = __floats2bfloat162_rn(x[8 * q + 2], x[8 * q + 3]);
-                    __nv_bfloat162 h2 = __floats2bfloat162_rn(x[8 * q + 4], x[8 * q + 5]);
-                    __nv_bfloat162 h3 = __floats2bfloat162_rn(x[8 * q + 6], x[8 * q + 7]);
+                    h16x2 h0 = floats_to_h16x2(x[8 * q + 0], x[8 * q + 1]);
+                    h16x2 h1 = floats_to_h16x2(x[8 * q + 2], x[8 * q + 3]);
+                    h16x2 h2 = floats_to_h16x2(x[8 * q + 4], x[8 * q + 5]);
+                    h16x2 h3 = floats_to_h16x2(x[8 * q + 6], x[8 * q + 7]);
                     uint4 u;
                     u.x = *(uint32_t*)&h0; u.y = *(uint32_t*)&h1; u.z = *(uint32_t*)&h2; u.w = *(uint32_t*)&h3;
                     dst[q] = u;
@@ -160,7 +160,7 @@ __device__ __forceinline__ void store_tile_row(const Params& p, int lane_row, in
                 float t = v[j];
                 if (j < ncols && n < p.rows_q) {
                     if (p.bias) t += __ldg(p.bias + n);
-                    if (p.relu) t = fmaxf(t, 0.f);
+                    t = apply_activation(t, p.act);
                     if (p.residual) t += p.residual[rowo + n];
                 }
                 x[j] = t;
@@ -169,7 +169,7 @@ __device__ __forceinline__ void store_tile_row(const Params& p, int lane_row, in
             for (int j = 0; j < 32; ++j) {
                 const int n = col0 + j;
                 if (j < ncols && n < p.rows_q) {
-                    if (p.c_is_bf16) ((bf16*)p.C)[rowo + n] = __float2bfloat16_rn(x[j]);
+                    if (p.c_is_h16) ((h16*)p.C)[rowo + n] = float_to_h16(x[j]);
                     else ((float*)p.C)[rowo + n] = x[j];
                 }
             }
@@ -265,7 +265,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
 #pragma unroll
                 for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
                     // advancing 16 elements along K = 32 bytes = 2 units of the address field
-                    umma_bf16(tmem_base, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
+                    umma_h16(tmem_base, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
                               (i > 0 || k > 0) ? 1u : 0u);
                 }
                 umma_commit(&empty_bar[s]);          // the stage is free once these MMAs have read it
@@ -386,20 +386,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     if (p.bias && n + e < n_lim) v[e] += __ldg(p.bias + n + e);
-                    if (p.relu) v[e] = fmaxf(v[e], 0.f);
+                    v[e] = apply_activation(v[e], p.act);
                     v[e] += rr[e];
                 }
                 if (whole) {
-                    if (p.c_is_bf16) {
-                        __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]), h1 = __floats2bfloat162_rn(v[2], v[3]);
+                    if (p.c_is_h16) {
+                        h16x2 h0 = floats_to_h16x2(v[0], v[1]), h1 = floats_to_h16x2(v[2], v[3]);
                         uint2 u; u.x = *(uint32_t*)&h0; u.y = *(uint32_t*)&h1;
-                        *(uint2*)((bf16*)p.C + o) = u;
+                        *(uint2*)((h16*)p.C + o) = u;
                     } else {
                         *(float4*)((float*)p.C + o) = make_float4(v[0], v[1], v[2], v[3]);
                     }
                 } else {
                     for (int e = 0; e < 4 && n + e < n_lim; ++e) {
-                        if (p.c_is_bf16) ((bf16*)p.C)[o + e] = __float2bfloat16_rn(v[e]);
+                        if (p.c_is_h16) ((h16*)p.C)[o + e] = float_to_h16(v[e]);
                         else ((float*)p.C)[o + e] = v[e];
                     }
                 }
@@ -425,9 +425,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             for (int s = 0; s < MAX_CLUSTER; ++s) if (s < S) v += f[s];
             if (live) {
                 if (p.bias) v += __ldg(p.bias + n);
-                if (p.relu) v = fmaxf(v, 0.f);
+                v = apply_activation(v, p.act);
                 v += res;
-                if (p.c_is_bf16) ((bf16*)p.C)[o] = __float2bfloat16_rn(v);
+                if (p.c_is_h16) ((h16*)p.C)[o] = float_to_h16(v);
                 else ((float*)p.C)[o] = v;
             }
         }
@@ -595,7 +595,7 @@ __device__ __forceinline__ void drain_accumulator(const Params& p, const AccSour
             float t0 = __uint_as_float(r[4 * q]), t1 = __uint_as_float(r[4 * q + 1]);
             float t2 = __uint_as_float(r[4 * q + 2]), t3 = __uint_as_float(r[4 * q + 3]);
             if (b) { t0 += b[4 * q]; t1 += b[4 * q + 1]; t2 += b[4 * q + 2]; t3 += b[4 * q + 3]; }
-            if (p.relu) { t0 = fmaxf(t0, 0.f); t1 = fmaxf(t1, 0.f); t2 = fmaxf(t2, 0.f); t3 = fmaxf(t3, 0.f); }
+            if (p.act) { t0 = apply_activation(t0, p.act); t1 = apply_activation(t1, p.act); t2 = apply_activation(t2, p.act); t3 = apply_activation(t3, p.act); }
             o.x = cur[q].x + t0; o.y = cur[q].y + t1; o.z = cur[q].z + t2; o.w = cur[q].w + t3;
             if (valid) ((float4*)(out_row + c))[q] = o;
         }
@@ -703,7 +703,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
                     const uint64_t bdesc = smem_desc_sw128(a_addr + A_BYTES);
 #pragma unroll
                     for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
-                        umma_bf16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        umma_h16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
                     umma_commit(&empty_bar[s]);
                 }
                 umma_commit(&acc_full[acc]);
@@ -799,7 +799,7 @@ __device__ __forceinline__ bool drain_accumulator_tma(const Params& p, EpilogueT
             float t0 = __uint_as_float(r[4 * q]), t1 = __uint_as_float(r[4 * q + 1]);
             float t2 = __uint_as_float(r[4 * q + 2]), t3 = __uint_as_float(r[4 * q + 3]);
             if (bias) { t0 += bias[4 * q]; t1 += bias[4 * q + 1]; t2 += bias[4 * q + 2]; t3 += bias[4 * q + 3]; }
-            if (p.relu) { t0 = fmaxf(t0, 0.f); t1 = fmaxf(t1, 0.f); t2 = fmaxf(t2, 0.f); t3 = fmaxf(t3, 0.f); }
+            if (p.act) { t0 = apply_activation(t0, p.act); t1 = apply_activation(t1, p.act); t2 = apply_activation(t2, p.act); t3 = apply_activation(t3, p.act); }
             x.x += t0; x.y += t1; x.z += t2; x.w += t3;
             *cell = x;
         }
@@ -838,7 +838,7 @@ __device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* m
         "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(smem_u32(dst)), "l"((unsigned long long)map), "r"(bar_cluster_addr), "r"(x), "r"(y) : "memory");
 }
-__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+__device__ __forceinline__ void umma_h16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
@@ -852,7 +852,7 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
 __host__ __device__ constexpr uint32_t instr_desc_pair(int n) {      // M = 256 over the pair
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+    return (1u << 4) | IDESC_H16_AB | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
 }
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
@@ -990,7 +990,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                     const uint64_t bdesc = smem_desc_sw128(a_addr + A_BYTES);
 #pragma unroll
                     for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
-                        umma_bf16_pair(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                        umma_h16_pair(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
                     umma_commit_pair(map_to_cta(smem_u32(&empty_bar[s]), 0));    // the stage is free in both CTAs
                     umma_commit_pair(map_to_cta(smem_u32(&empty_bar[s]), 1));
                 }
@@ -1213,15 +1213,16 @@ TNX_EXPORT int tnx_gemm_tc_plan(int M, int N, int K, int n_sms, int* splits, lon
 }
 
 TNX_EXPORT int tnx_gemm_tc(const void* A, const void* W, const float* bias, const float* residual, void* C,
-                           int M, int N, int K, int lda, int ldw, int ldc, int relu, int c_bf16,
+                           int M, int N, int K, int lda, int ldw, int ldc, int act, int c_h16,
                            int splits, float* scratch, int* counters, int* err_word, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 || lda % 8 || ldw % 8 || lda < K || ldw < K || ldc < N) return TNX_ERR_UNSUPPORTED;
     if (((uintptr_t)A | (uintptr_t)W) & 15) return TNX_ERR_UNSUPPORTED;
-    if (residual && c_bf16) return TNX_ERR_BAD_ARG;
+    if (residual && c_h16) return TNX_ERR_BAD_ARG;
+    if (act < 0 || act >= TNX_ACT_COUNT) return TNX_ERR_BAD_ARG;
     if (!err_word) return TNX_ERR_BAD_ARG;
     Params p{};
-    p.K = K; p.ldc = ldc; p.relu = relu; p.c_is_bf16 = c_bf16; p.bias = bias; p.residual = residual; p.C = C;
+    p.K = K; p.ldc = ldc; p.act = act; p.c_is_h16 = c_h16; p.bias = bias; p.residual = residual; p.C = C;
     p.err = err_word; p.partials = scratch; p.counters = counters;
     const int kb = (K + BLOCK_K - 1) / BLOCK_K;
     CUtensorMap mp, mq;
@@ -1260,7 +1261,7 @@ TNX_EXPORT int tnx_gemm_tc(const void* A, const void* W, const float* bias, cons
             // A 32-bit residual goes through TMA boxes when the row pitch and the addresses allow it.
             CUtensorMap mres = mp, mout = mp;
             int tma_epilogue = 0;
-            if (residual && !c_bf16 && ldc % 4 == 0 && !(((uintptr_t)residual | (uintptr_t)C) & 15))
+            if (residual && !c_h16 && ldc % 4 == 0 && !(((uintptr_t)residual | (uintptr_t)C) & 15))
                 tma_epilogue = make_map_f32(&mres, residual, M, N, ldc, 32) && make_map_f32(&mout, C, M, N, ldc, 32);
             static bool pconfigured = false;
             if (!pconfigured) {
@@ -1300,3 +1301,25 @@ TNX_EXPORT int tnx_gemm_tc(const void* A, const void* W, const float* bias, cons
     if (bn == 64) return launch<64, 4, true>(mp, mq, p, grid, stream);
     return launch<128, 3, true>(mp, mq, p, grid, stream);
 }
+
+// ---- a wait that runs out, for the tests of the error path --------------------------------------------
+// One warp waits, with a limit of `limit_ns`, on an mbarrier at which nothing ever arrives.  The wait
+// gives up by itself, the kernel records `code` in the error word and returns: this is what every
+// bounded wait of the kernels above does when a copy or a product never completes.
+namespace {
+__global__ void wait_runs_out_kernel(int* err, int code, unsigned long long limit_ns) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) mbar_wait_limit(&bar, 0, err, code, limit_ns);
+}
+}  // namespace
+
+TNX_EXPORT int tnx_selftest_wait_runs_out(int* err, int code, long long limit_ns, cudaStream_t stream) {
+    if (!err || limit_ns <= 0 || limit_ns > 100000000ll) return TNX_ERR_BAD_ARG;      // 0.1 s at most
+    return tnx_launch_pdl(wait_runs_out_kernel, dim3(1), dim3(32), 0, stream, err, code, (unsigned long long)limit_ns);
+}
+

@@ -1,7 +1,7 @@
 // Matrix product for one to four tokens (the decode step of one to four requests):
 //
-//   C[m, n] = epilogue( sum_k A[m, k] * W[n, k] )        A: [M, K] bf16, W: [N, K] bf16, row-major
-//   epilogue: + bias[n] (32-bit); ReLU; + residual[m, n] (32-bit); stored as bfloat16 or float.
+//   C[m, n] = epilogue( sum_k A[m, k] * W[n, k] )        A: [M, K] h16, W: [N, K] h16, row-major
+//   epilogue: + bias[n] (32-bit); activation (by code, common.cuh); + residual[m, n] (32-bit); stored in the 16-bit type or as float.
 //
 // With so few tokens the product is a stream of the weight matrix through the multiply-add units:
 // there is nothing for the tensor cores to win, and plain 16-byte loads keep more bytes in flight
@@ -20,18 +20,24 @@ namespace {
 __device__ __forceinline__ uint4 load_stream(const uint4* p) { return __ldcs(p); }
 
 __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
-    // a bf16 is the upper half of the float with the same value
+#ifdef TNX_F16
+    const h16x2* h = (const h16x2*)&v;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 t = h16x2_to_float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+#else
+    // a bfloat16 is the upper half of the float with the same value
     f[0] = __uint_as_float(v.x << 16); f[1] = __uint_as_float(v.x & 0xffff0000u);
     f[2] = __uint_as_float(v.y << 16); f[3] = __uint_as_float(v.y & 0xffff0000u);
     f[4] = __uint_as_float(v.z << 16); f[5] = __uint_as_float(v.z & 0xffff0000u);
     f[6] = __uint_as_float(v.w << 16); f[7] = __uint_as_float(v.w & 0xffff0000u);
+#endif
 }
 
 template <int M, int R, int THREADS>
 __global__ void __launch_bounds__(THREADS)
-gemv_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict__ W, int ldw,
+gemv_kernel(const h16* __restrict__ A, int lda, const h16* __restrict__ W, int ldw,
             const float* __restrict__ bias, const float* residual, void* C, int ldc,
-            int relu, int c_is_bf16, int N, int K) {
+            int act, int c_is_h16, int N, int K) {
     extern __shared__ uint4 xs[];                         // [M][K / 8] pieces of the activations
     __shared__ float red[THREADS / 32][R * M];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -102,10 +108,10 @@ gemv_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict__ W, int
 #pragma unroll
                 for (int w = 0; w < THREADS / 32; ++w) v += red[w][tid];
                 if (bias) v += bias[n];
-                if (relu) v = fmaxf(v, 0.f);
+                v = apply_activation(v, act);
                 const size_t o = (size_t)m * ldc + n;
                 if (residual) v += residual[o];
-                if (c_is_bf16) ((bf16*)C)[o] = __float2bfloat16_rn(v);
+                if (c_is_h16) ((h16*)C)[o] = float_to_h16(v);
                 else ((float*)C)[o] = v;
             }
         }
@@ -114,8 +120,8 @@ gemv_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict__ W, int
 }
 
 template <int M, int R, int THREADS>
-int launch(const bf16* A, int lda, const bf16* W, int ldw, const float* bias, const float* residual, void* C, int ldc,
-           int relu, int c_bf16, int N, int K, int sms, cudaStream_t stream) {
+int launch(const h16* A, int lda, const h16* W, int ldw, const float* bias, const float* residual, void* C, int ldc,
+           int act, int c_h16, int N, int K, int sms, cudaStream_t stream) {
     const size_t smem = (size_t)M * K * 2;
     static size_t configured = 48 * 1024 - 1024;
     if (smem > configured) {
@@ -136,7 +142,7 @@ int launch(const bf16* A, int lda, const bf16* W, int ldw, const float* bias, co
     int blocks = sms * per_sm;
     if (blocks > (N + R - 1) / R) blocks = (N + R - 1) / R;
     return tnx_launch_ex(1, gemv_kernel<M, R, THREADS>, dim3(blocks), dim3(THREADS), smem, stream, A, lda, W, ldw, bias, residual, C, ldc,
-                         relu, c_bf16, N, K);
+                         act, c_h16, N, K);
 }
 
 }  // namespace
@@ -152,11 +158,12 @@ TNX_EXPORT int tnx_gemv_supported(int M, int N, int K) {
 }
 
 TNX_EXPORT int tnx_gemv(const void* A, const void* W, const float* bias, const float* residual, void* C,
-                        int M, int N, int K, int lda, int ldw, int ldc, int relu, int c_bf16, cudaStream_t stream) {
+                        int M, int N, int K, int lda, int ldw, int ldc, int act, int c_h16, cudaStream_t stream) {
     if (!tnx_gemv_supported(M, N, K)) return TNX_ERR_UNSUPPORTED;
     if (lda % 8 || ldw % 8 || lda < K || ldw < K || ldc < N) return TNX_ERR_UNSUPPORTED;
     if (((uintptr_t)A | (uintptr_t)W) & 15) return TNX_ERR_UNSUPPORTED;
-    if (residual && c_bf16) return TNX_ERR_BAD_ARG;
+    if (residual && c_h16) return TNX_ERR_BAD_ARG;
+    if (act < 0 || act >= TNX_ACT_COUNT) return TNX_ERR_BAD_ARG;
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     static int cached_sms[64] = {0};
@@ -164,14 +171,14 @@ TNX_EXPORT int tnx_gemv(const void* A, const void* W, const float* bias, const f
         if (!cached_sms[dev]) cudaDeviceGetAttribute(&cached_sms[dev], cudaDevAttrMultiProcessorCount, dev);
         sms = cached_sms[dev];
     }
-    const bf16* a = (const bf16*)A;
-    const bf16* w = (const bf16*)W;
+    const h16* a = (const h16*)A;
+    const h16* w = (const h16*)W;
     // Rows of up to 4,096 elements: blocks of 128 threads (four steps of a row instead of two between
     // the block-wide sums); longer rows: 256 threads.  The choice depends on K alone, so that the
     // order of the additions does not depend on the number of tokens.
 #define GEMV_LAUNCH(M_, R_)                                                                                              \
-    (K <= 4096 ? launch<M_, R_, 128>(a, lda, w, ldw, bias, residual, C, ldc, relu, c_bf16, N, K, sms, stream)           \
-               : launch<M_, R_, 256>(a, lda, w, ldw, bias, residual, C, ldc, relu, c_bf16, N, K, sms, stream))
+    (K <= 4096 ? launch<M_, R_, 128>(a, lda, w, ldw, bias, residual, C, ldc, act, c_h16, N, K, sms, stream)           \
+               : launch<M_, R_, 256>(a, lda, w, ldw, bias, residual, C, ldc, act, c_h16, N, K, sms, stream))
     switch (M) {
         case 1: return GEMV_LAUNCH(1, 8);
         case 2: return GEMV_LAUNCH(2, 8);

@@ -33,10 +33,10 @@ __global__ void kv_append_kernel(const T* __restrict__ k_src, const T* __restric
 
 TNX_EXPORT int tnx_kv_append(const void* k_src, const void* v_src, int src_stride, const int* slot_mapping,
                              void* cache, int N, int n_kv_heads, int head_dim, int page_size,
-                             int is_bf16, cudaStream_t stream) {
+                             int is_h16, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (n_kv_heads <= 0 || head_dim <= 0 || page_size <= 0) return TNX_ERR_BAD_ARG;
-    const int esz = is_bf16 ? 2 : 4, vec = 16 / esz;
+    const int esz = is_h16 ? 2 : 4, vec = 16 / esz;
     const bool wide = head_dim % vec == 0 && src_stride % vec == 0 && ((uintptr_t)k_src % 16) == 0 &&
                       ((uintptr_t)v_src % 16) == 0 && ((uintptr_t)cache % 16) == 0;
     const int work = 2 * n_kv_heads * head_dim / (wide ? vec : 1);
@@ -44,7 +44,7 @@ TNX_EXPORT int tnx_kv_append(const void* k_src, const void* v_src, int src_strid
 #define KV_LAUNCH(T, V)                                                                                          \
     tnx_launch_pdl(kv_append_kernel<T, V>, grid, block, 0, stream, (const T*)k_src, (const T*)v_src, src_stride, \
                    slot_mapping, (T*)cache, n_kv_heads, head_dim, page_size)
-    if (is_bf16) return wide ? KV_LAUNCH(bf16, 8) : KV_LAUNCH(bf16, 1);
+    if (is_h16) return wide ? KV_LAUNCH(h16, 8) : KV_LAUNCH(h16, 1);
     return wide ? KV_LAUNCH(float, 4) : KV_LAUNCH(float, 1);
 #undef KV_LAUNCH
 }

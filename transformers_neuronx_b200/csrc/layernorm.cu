@@ -85,7 +85,7 @@ __global__ void layer_norm_reg_kernel(const float* __restrict__ x, const int* __
         if (out_act) {
             TA* dst = out_act + (size_t)r * H + 4 * c;
             if constexpr (sizeof(TA) == 2) {
-                __nv_bfloat162 lo = __floats2bfloat162_rn(y.x, y.y), hi = __floats2bfloat162_rn(y.z, y.w);
+                h16x2 lo = floats_to_h16x2(y.x, y.y), hi = floats_to_h16x2(y.z, y.w);
                 uint2 u;
                 u.x = *(uint32_t*)&lo; u.y = *(uint32_t*)&hi;
                 *(uint2*)dst = u;
@@ -113,7 +113,7 @@ __global__ void pick_rows_kernel(const float* __restrict__ x, const int* __restr
 
 TNX_EXPORT int tnx_layer_norm(const float* x, const int* rows, const float* gamma, const float* beta,
                               float eps, float* out_f32, void* out_act, int n_rows, int H,
-                              int act_bf16, cudaStream_t stream) {
+                              int act_h16, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (H <= 0 || (size_t)H * sizeof(float) > 200 * 1024) return TNX_ERR_UNSUPPORTED;
     // Rows of a multiple of four elements, 16-byte aligned, up to 8,192 elements: the register kernel.
@@ -128,16 +128,16 @@ TNX_EXPORT int tnx_layer_norm(const float* x, const int* rows, const float* gamm
                    eps, out_f32, (TA*)out_act, H)
 #define LN_PICK(TA)                                                                        \
     (nv <= 1 ? LN_LAUNCH(TA, 1) : nv <= 2 ? LN_LAUNCH(TA, 2) : nv <= 4 ? LN_LAUNCH(TA, 4) : nv <= 5 ? LN_LAUNCH(TA, 5) : LN_LAUNCH(TA, 8))
-        if (act_bf16) return LN_PICK(bf16);
+        if (act_h16) return LN_PICK(h16);
         return LN_PICK(float);
 #undef LN_PICK
 #undef LN_LAUNCH
     }
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     const size_t smem = (size_t)H * sizeof(float);
-    if (act_bf16) {
-        if (smem + 1024 > 48 * 1024) cudaFuncSetAttribute(layer_norm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        return tnx_launch_pdl(layer_norm_kernel<bf16>, dim3(n_rows), dim3(threads), smem, stream, x, rows, gamma, beta, eps, out_f32, (bf16*)out_act, H);
+    if (act_h16) {
+        if (smem + 1024 > 48 * 1024) cudaFuncSetAttribute(layer_norm_kernel<h16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        return tnx_launch_pdl(layer_norm_kernel<h16>, dim3(n_rows), dim3(threads), smem, stream, x, rows, gamma, beta, eps, out_f32, (h16*)out_act, H);
     } else {
         if (smem + 1024 > 48 * 1024) cudaFuncSetAttribute(layer_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         return tnx_launch_pdl(layer_norm_kernel<float>, dim3(n_rows), dim3(threads), smem, stream, x, rows, gamma, beta, eps, out_f32, (float*)out_act, H);
@@ -145,9 +145,9 @@ TNX_EXPORT int tnx_layer_norm(const float* x, const int* rows, const float* gamm
 }
 
 TNX_EXPORT int tnx_pick_rows(const float* x, const int* rows, float* out_f32, void* out_act,
-                             int n_rows, int H, int act_bf16, cudaStream_t stream) {
+                             int n_rows, int H, int act_h16, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     const int threads = H >= 1024 ? 256 : 128;
-    if (act_bf16) return tnx_launch_pdl(pick_rows_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, x, rows, out_f32, (bf16*)out_act, H);
+    if (act_h16) return tnx_launch_pdl(pick_rows_kernel<h16>, dim3(n_rows), dim3(threads), 0, stream, x, rows, out_f32, (h16*)out_act, H);
     return tnx_launch_pdl(pick_rows_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, rows, out_f32, (float*)out_act, H);
 }

@@ -7,6 +7,11 @@
 //                      before it is < top_p); then draw from softmax over the kept tokens by
 //                      inverse CDF in index order with one Philox uniform per (seed, counter).
 //
+// A row's parameters come either from one array per parameter (null: the default) or packed, 16
+// 32-bit words a row (ROW_WORDS below), which is how the engine sends them: in the same buffer
+// and the same copy as the step's other index arrays.  Up to four ids per row can be suppressed
+// (a request's end-of-sequence ids), and the fixed draw is a per-row flag.
+//
 // Everything that decides the outcome is integer arithmetic: the thresholds are found by radix
 // selection on order-preserving integer keys, and probability masses are summed as 2^-40
 // fixed-point integers, so a draw depends on (logits, parameters, seed, counter) alone and not
@@ -54,13 +59,23 @@ __device__ __forceinline__ ArgMax better(ArgMax a, ArgMax b) {
 
 // TOP_P false: the caller passes no top_p array; the kernel then does without the copies of the
 // mass histogram (shared memory that would otherwise be taken from the first-level cache).
+// Packed parameters of a row: word 0 temperature (float), 1 top_k, 2 top_p (float), 3 min_keep,
+// 4-5 seed (low, high), 6-7 counter (low, high), 8 flags (bit 0: the fixed draw), 9-12 suppressed
+// ids (-1: none), 13-15 zero.
+constexpr int ROW_WORDS = 16;
+
+struct SampleArgs {
+    const float* temperature; const int* top_k; const float* top_p; const int* min_keep;
+    const unsigned long long* seeds; const unsigned long long* counters;
+    int deterministic, suppress_id;
+    const int* packed;               // [rows][ROW_WORDS], or null: the arrays above
+    const int* err_word;             // when given, out[rows] receives its value (the kernels' error word
+    int n_rows;                      //   travels to the host with the sampled ids)
+};
+
 template <bool TOP_P>
 __global__ void __launch_bounds__(THREADS)
-sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __restrict__ temperature,
-              const int* __restrict__ top_k, const float* __restrict__ top_p,
-              const int* __restrict__ min_keep, int deterministic,
-              const unsigned long long* __restrict__ seeds, const unsigned long long* __restrict__ counters,
-              int suppress_id, int* __restrict__ out) {
+sample_kernel(const float* __restrict__ logits, int ld, int V, const SampleArgs a, int* __restrict__ out) {
     __shared__ unsigned long long warp_hist64[TOP_P ? GROUPS * 256 : THREADS];
     unsigned long long* sums = warp_hist64;                      // [THREADS], used after the histogram passes
     static_assert(GROUPS * 256 >= THREADS, "the partial sums of the last phase reuse the histogram copies");
@@ -76,11 +91,32 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
 
     const int r = blockIdx.x, tid = threadIdx.x;
     const float* row = logits + (size_t)r * ld;
-    const float T = temperature ? temperature[r] : 0.f;
+    if (a.err_word && r == 0 && tid == 0) out[a.n_rows] = *a.err_word;
+    float T, P;
+    int k, n_min, deterministic, sup0, sup1 = -1, sup2 = -1, sup3 = -1;
+    unsigned long long seed, ctr;
+    if (a.packed) {
+        const int* w = a.packed + (size_t)r * ROW_WORDS;
+        T = __int_as_float(w[0]); k = w[1]; P = __int_as_float(w[2]); n_min = w[3];
+        seed = (unsigned long long)(unsigned)w[4] | ((unsigned long long)(unsigned)w[5] << 32);
+        ctr = (unsigned long long)(unsigned)w[6] | ((unsigned long long)(unsigned)w[7] << 32);
+        deterministic = w[8] & 1;
+        sup0 = w[9]; sup1 = w[10]; sup2 = w[11]; sup3 = w[12];
+    } else {
+        T = a.temperature ? a.temperature[r] : 0.f;
+        k = a.top_k ? a.top_k[r] : 0;
+        P = a.top_p ? a.top_p[r] : 1.f;
+        n_min = a.min_keep ? a.min_keep[r] : 1;
+        seed = a.seeds ? a.seeds[r] : 0ull;
+        ctr = a.counters ? a.counters[r] : 0ull;
+        deterministic = a.deterministic;
+        sup0 = a.suppress_id;
+    }
+#define SUPPRESSED(i) ((i) == sup0 || (i) == sup1 || (i) == sup2 || (i) == sup3)
 
     if (!(T > 0.f)) {
         ArgMax best{-INFINITY, 0x7fffffff};
-        for (int i = tid; i < V; i += THREADS) best = better(best, ArgMax{i == suppress_id ? -INFINITY : row[i], i});
+        for (int i = tid; i < V; i += THREADS) best = better(best, ArgMax{SUPPRESSED(i) ? -INFINITY : row[i], i});
         for (int o = 16; o > 0; o >>= 1) {
             ArgMax other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
             best = better(best, other);
@@ -98,7 +134,7 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
         return;
     }
 
-#define SCORE(i) (((i) == suppress_id) ? -INFINITY : row[(i)] / T)
+#define SCORE(i) (SUPPRESSED(i) ? -INFINITY : row[(i)] / T)
     float mx = -INFINITY;
     for (int i = tid; i < V; i += THREADS) mx = fmaxf(mx, SCORE(i));
     mx = block_max(mx, fscratch);
@@ -232,16 +268,13 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
 
     // ---- top-k: the key of the k-th largest score (0 keeps everything) ----------------------
     uint32_t thr = 0;
-    const int k = top_k ? top_k[r] : 0;
     if (k > 0 && k < V) thr = kth_largest_key(k);
 
     // ---- top-p over the tokens that top-k kept, but never fewer than min_keep of them ----------
-    const float P = (TOP_P && top_p) ? top_p[r] : 1.f;
     if (TOP_P && P < 1.f) {
         unsigned long long limit = (unsigned long long)((double)P * (double)mass_from(thr));
         if (limit < 1) limit = 1;                      // the most likely token is always kept
         uint32_t thr_p = lowest_key_within_mass(limit, thr);
-        const int n_min = min_keep ? min_keep[r] : 1;
         if (n_min > 1) {
             const uint32_t thr_n = n_min < V ? kth_largest_key(n_min) : 0u;
             if (thr_n < thr_p) thr_p = thr_n;
@@ -297,7 +330,6 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
     __syncthreads();
     const unsigned long long total = sh_total;
     uint32_t rnd[4];
-    const unsigned long long seed = seeds ? seeds[r] : 0ull, ctr = counters ? counters[r] : 0ull;
     philox4x32_10((uint32_t)ctr, (uint32_t)(ctr >> 32), 0u, 0u, (uint32_t)seed, (uint32_t)(seed >> 32), rnd);
     // target = floor(total * u), u = rnd / 2^32 in [0, 1)
     const unsigned long long target = __umul64hi(total, (unsigned long long)rnd[0] << 32);
@@ -321,6 +353,7 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
         out[r] = 0;
     }
 #undef SCORE
+#undef SUPPRESSED
 }
 }  // namespace
 
@@ -332,9 +365,23 @@ TNX_EXPORT int tnx_sample(const float* logits, int ld, int n_rows, int V, const 
                           int* out, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (V <= 0 || ld < V) return TNX_ERR_BAD_ARG;
+    SampleArgs a = {temperature, top_k, top_p, min_keep, seeds, counters, deterministic, suppress_id, nullptr, nullptr, n_rows};
     if (top_p || deterministic)
-        return tnx_launch_pdl(sample_kernel<true>, dim3(n_rows), dim3(THREADS), 0, stream, logits, ld, V, temperature, top_k,
-                              top_p, min_keep, deterministic, seeds, counters, suppress_id, out);
-    return tnx_launch_pdl(sample_kernel<false>, dim3(n_rows), dim3(THREADS), 0, stream, logits, ld, V, temperature, top_k,
-                          top_p, min_keep, deterministic, seeds, counters, suppress_id, out);
+        return tnx_launch_pdl(sample_kernel<true>, dim3(n_rows), dim3(THREADS), 0, stream, logits, ld, V, a, out);
+    return tnx_launch_pdl(sample_kernel<false>, dim3(n_rows), dim3(THREADS), 0, stream, logits, ld, V, a, out);
 }
+
+// The same with every row's parameters packed (ROW_WORDS 32-bit words a row, see above).  with_top_p: 0
+// when no row uses top-p or the fixed draw (the lighter kernel variant).  err_word (may be null): a
+// device word copied to out[n_rows], so `out` then holds n_rows + 1 entries.
+TNX_EXPORT int tnx_sample_packed(const float* logits, int ld, int n_rows, int V, const int* packed, int with_top_p,
+                                 const int* err_word, int* out, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (V <= 0 || ld < V || !packed) return TNX_ERR_BAD_ARG;
+    SampleArgs a = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0, -1, packed, err_word, n_rows};
+    if (with_top_p)
+        return tnx_launch_pdl(sample_kernel<true>, dim3(n_rows), dim3(THREADS), 0, stream, logits, ld, V, a, out);
+    return tnx_launch_pdl(sample_kernel<false>, dim3(n_rows), dim3(THREADS), 0, stream, logits, ld, V, a, out);
+}
+
+TNX_EXPORT int tnx_sample_row_words() { return ROW_WORDS; }

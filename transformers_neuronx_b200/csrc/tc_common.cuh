@@ -9,6 +9,16 @@
 
 namespace {
 
+// Operand format of tcgen05.mma kind::f16 in the instruction descriptor (bits 7-9 for A, 10-12 for B):
+// 0 = float16, 1 = bfloat16; and the matching element type of a TMA descriptor.
+#ifdef TNX_F16
+constexpr uint32_t IDESC_H16_AB = 0u;
+#define TNX_TMA_H16 CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+#else
+constexpr uint32_t IDESC_H16_AB = (1u << 7) | (1u << 10);
+#define TNX_TMA_H16 CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+#endif
+
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // 2 s: every spin below gives up after this
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -34,17 +44,20 @@ __device__ __forceinline__ unsigned long long global_ns() {
     return t;
 }
 // Bounded wait: false (and *err set) when the phase did not complete within the limit.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err, int code) {
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, int* err, int code, unsigned long long limit_ns) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
     for (;;) {
         for (int i = 0; i < 256; ++i)
             if (mbar_try_wait(bar, parity)) return true;
-        if (global_ns() - t0 > WAIT_LIMIT_NS) {
+        if (global_ns() - t0 > limit_ns) {
             atomicExch(err, code);
             return false;
         }
     }
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err, int code) {
+    return mbar_wait_limit(bar, parity, err, code, WAIT_LIMIT_NS);
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
     asm volatile(
@@ -73,7 +86,7 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+__device__ __forceinline__ void umma_h16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
@@ -149,7 +162,7 @@ struct MapHash {
     }
 };
 
-// A [rows, cols] matrix with row pitch ld elements, 128-byte swizzle: bf16 in boxes of box_rows x 64,
+// A [rows, cols] matrix with row pitch ld elements, 128-byte swizzle: 16-bit elements in boxes of box_rows x 64,
 // or (f32) 32-bit floats in boxes of box_rows x 32.  Either way a box row is 128 bytes.
 bool make_map_any(CUtensorMap* out, const void* ptr, int rows, int cols, int ld, int box_rows, bool f32) {
     static std::unordered_map<MapKey, CUtensorMap, MapHash> cache;
@@ -164,7 +177,7 @@ bool make_map_any(CUtensorMap* out, const void* ptr, int rows, int cols, int ld,
     cuuint64_t strides[1] = {(cuuint64_t)ld * (f32 ? 4 : 2)};
     cuuint32_t box[2] = {f32 ? 32u : 64u, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(out, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+    CUresult r = fn(out, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : TNX_TMA_H16, 2,
                     const_cast<void*>(ptr), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);

@@ -7,7 +7,8 @@ from typing import Dict, Hashable, List, Optional, Sequence
 import torch
 
 from ..config import EngineConfig
-from ..sampling import Sampler
+from ..kernels import ops
+from ..sampling import MAX_SUPPRESSED, Sampler, needs_top_p, pack_rows
 from .scheduler import Request, SamplingParams, Scheduler, StepPlan
 from .step import StepEntry, StepRunner
 
@@ -25,14 +26,17 @@ class LLMEngine:
             num_pages = -(-tokens // ec.page_size)
         self.runner = StepRunner(model, ec.page_size, num_pages, ec.max_num_seqs, max_len,
                                  use_cuda_graphs=ec.use_cuda_graphs)
-        self.scheduler = Scheduler(self.runner.cache, ec.max_batch_tokens, ec.max_num_seqs, max_len)
+        self.scheduler = Scheduler(self.runner.cache, ec.max_batch_tokens, ec.max_num_seqs, max_len,
+                                   max_portion=ec.max_portion)
         self.sampler = Sampler(model.device)
         self.eos_token_id = model.spec.eos_token_id if eos_token_id is None else eos_token_id
         self._ids = itertools.count()
         self.requests: Dict[Hashable, Request] = {}
-        n_ids = max(64, 2 * ec.max_num_seqs)
+        # the ids sampled in a step, and after them the kernels' error word (one more entry)
+        n_ids = max(64, 2 * ec.max_num_seqs) + 1
         self._ids_dev = [torch.zeros(n_ids, dtype=torch.int32, device=model.device) for _ in range(2)]
         self._ids_host = [torch.zeros(n_ids, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._err_word = ops.error_word(model.device)
         self._events = [torch.cuda.Event() for _ in range(2)]
         self._parity = 0
         self._inflight = None          # the last step's sampled ids, not yet read back
@@ -46,6 +50,9 @@ class LLMEngine:
             raise ValueError(f"request {rid!r} is still running")
         req = Request(rid, [int(t) for t in prompt], int(max_new_tokens), params or SamplingParams(),
                       stop_on_eos=stop_on_eos, eos_token_id=self.eos_token_id if eos_token_id is None else eos_token_id)
+        if req.params.suppress_eos and len(req.eos_ids()) > MAX_SUPPRESSED:
+            raise ValueError(f"request {rid!r}: suppress_eos takes at most {MAX_SUPPRESSED} end-of-sequence ids, "
+                             f"got {len(req.eos_ids())}")
         self.scheduler.add(req)
         self.requests[rid] = req
         return rid
@@ -93,35 +100,34 @@ class LLMEngine:
             if it.sample:
                 rows.append(req)
         prev_ids = self._ids_dev[self._parity ^ 1] if any_from_device else None
-        logits = self.runner.step(entries, prev_ids)
+        # The rows to sample, with every row's own parameters (temperature, top-k, top-p, seed and
+        # counter, the fixed draw, the ids it must not draw), packed into the step's own staging buffer.
+        extra = None
+        if rows:
+            ps = [r.params for r in rows]
+            extra = pack_rows([p.temperature for p in ps], [p.top_k for p in ps], [p.top_p for p in ps],
+                              [p.seed for p in ps], [len(r.output) for r in rows], [p.top_p_min_tokens for p in ps],
+                              [p.deterministic for p in ps], [r.eos_ids() if r.params.suppress_eos else () for r in rows])
+        logits = self.runner.step(entries, prev_ids, extra)
         cur = None
         if rows:
             R = len(rows)
-            suppress = self.eos_token_id if (self.eos_token_id is not None and
-                                             all(r.params.suppress_eos for r in rows)) else -1
-            if suppress < 0 and any(r.params.suppress_eos for r in rows):
-                raise ValueError("suppress_eos must be set for all requests of a step or for none")
-            deterministic = rows[0].params.deterministic
-            if any(r.params.deterministic != deterministic for r in rows):
-                raise ValueError("deterministic must be set for all requests of a step or for none")
-            if self._ids_dev[self._parity].shape[0] < R:
-                self._ids_dev = [torch.zeros(2 * R, dtype=torch.int32, device=self.model.device) for _ in range(2)]
-                self._ids_host = [torch.zeros(2 * R, dtype=torch.int32).pin_memory() for _ in range(2)]
+            if self._ids_dev[self._parity].shape[0] < R + 1:
                 if any_from_device:
                     raise AssertionError("the batch outgrew the id buffers while ids were still on the device")
+                self._ids_dev = [torch.zeros(2 * R + 1, dtype=torch.int32, device=self.model.device) for _ in range(2)]
+                self._ids_host = [torch.zeros(2 * R + 1, dtype=torch.int32).pin_memory() for _ in range(2)]
             out = self._ids_dev[self._parity]
-            self.sampler.sample(
-                logits, [r.params.temperature for r in rows], [r.params.top_k for r in rows],
-                [r.params.top_p for r in rows], [r.params.seed for r in rows],
-                [len(r.output) for r in rows], suppress_id=suppress, out=out,
-                min_keeps=[r.params.top_p_min_tokens for r in rows], deterministic=deterministic)
+            self.sampler.sample_packed(logits, self.runner.extra_dev, needs_top_p([p.top_p for p in ps],
+                                                                                 [p.deterministic for p in ps]),
+                                       out, err_word=self._err_word)
             host = self._ids_host[self._parity]
-            host[:R].copy_(out[:R], non_blocking=True)            # the step's device-to-host read, waited for later
+            host[:R + 1].copy_(out[:R + 1], non_blocking=True)    # the step's device-to-host read, waited for later
             ev = self._events[self._parity]
             ev.record()
             for i, r in enumerate(rows):
                 r._dev_row = i
-            cur = (rows, [len(r.output) for r in rows], host, ev, R)
+            cur = (rows, [len(r.output) for r in rows], host, ev, R, self.stats["steps"])
         done_by_count = self.scheduler.commit(plan, {r.rid: self.PENDING for r in rows})
         for r in done_by_count:
             self.runner.forget(r.rid)
@@ -144,9 +150,10 @@ class LLMEngine:
         that produced the end-of-sequence token.  Returns requests that are finished with all
         their tokens known."""
         if inflight is not None:
-            rows, places, host, ev, R = inflight
+            rows, places, host, ev, R, step_no = inflight
             ev.synchronize()
-            ids = host[:R].tolist()
+            ids = host[:R + 1].tolist()
+            ops.raise_if_error_code(ids.pop(), f" during or before step {step_no}")
             for req, place, tok in zip(rows, places, ids):
                 if place >= len(req.output):
                     continue                                   # cut off by an earlier end-of-sequence token

@@ -3,15 +3,17 @@ from __future__ import annotations
 
 import sys
 import time
+import warnings
 
 import torch
 
 from ..config import canonical_dtype, load_config
 from ..kernels import build as kbuild
 from ..models.decoder import DecoderModel
+from ..parts.base import rounding_report
 from ..weights import load_tensors
 
-_TORCH_DTYPE = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+_TORCH_DTYPE = {"float32": torch.float32, "bfloat16": torch.bfloat16, "float16": torch.float16}
 
 
 def require_cuda(device="cuda:0") -> torch.device:
@@ -30,8 +32,17 @@ def build_model(spec, tensors, dtype: str, device="cuda:0", verbose=True) -> Dec
     torch.cuda.set_device(dev)
     model = DecoderModel(spec)
     act = _TORCH_DTYPE[canonical_dtype(dtype)]
-    kbuild.build_many(model.libraries(act), verbose=verbose)
+    # the libraries' flavour: the engine's 16-bit type, or (32-bit engine) that of the stored matrices
+    sixteen = act if act != torch.float32 else (
+        torch.float16 if any(t.dtype == torch.float16 for t in tensors.values()) else torch.bfloat16)
+    kbuild.build_many(kbuild.with_flavour(model.libraries(act), sixteen), verbose=verbose)
+    rounding_report()
     model.load(tensors, dev, act)
+    n, example = rounding_report()
+    if n:
+        warnings.warn(f"{n} tensors are stored in another 16-bit type than the engine's and were rounded to "
+                      f"{canonical_dtype(dtype)} (e.g. {example}): the logits are no longer the checkpoint's own; "
+                      f"run the engine in the checkpoint's type, or in float32, to avoid this")
     return model
 
 

@@ -21,6 +21,7 @@ import numpy as np
 import torch
 
 from ..config import EngineConfig
+from ..kernels import ops
 from .loading import load_model
 from .step import StepEntry, StepRunner
 
@@ -55,6 +56,7 @@ def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines=None
                 arr.tofile(os.path.join(out_dir, f"{step}.f32"))
             else:
                 torch.cuda.synchronize()
+            ops.raise_on_device_error()       # a bounded wait that ran out inside a kernel: no `done` for this step
         for rid in rec.get("end", []):
             if rid in runner.cache:
                 runner.finish(rid)
@@ -65,7 +67,7 @@ def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines=None
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="trace_run", description=__doc__.split("\n\n")[0])
     ap.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
-    ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
+    ap.add_argument("--dtype", required=True, choices=["bfloat16", "float16", "float32"])
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens that live requests hold at any time (each request rounded up to 64)")

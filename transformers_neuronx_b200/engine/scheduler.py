@@ -54,6 +54,12 @@ class Request:
     preemptions: int = 0
     arrival: int = 0
 
+    def eos_ids(self):
+        e = self.eos_token_id
+        if e is None:
+            return ()
+        return tuple(e) if isinstance(e, (list, tuple, set, frozenset)) else (e,)
+
     def is_eos(self, tok: int) -> bool:
         e = self.eos_token_id
         if e is None:
@@ -113,8 +119,9 @@ class Scheduler:
     def add(self, req: Request) -> None:
         if not req.prompt:
             raise ValueError(f"request {req.rid!r}: empty prompt")
-        if req.max_new_tokens < 0:
-            raise ValueError(f"request {req.rid!r}: max_new_tokens must not be negative")
+        if req.max_new_tokens < 1:
+            raise ValueError(f"request {req.rid!r}: max_new_tokens must be at least 1 (a request that asks for "
+                             "no token has nothing to run)")
         need = len(req.prompt) + req.max_new_tokens
         if need > self.max_model_len:
             raise ValueError(f"request {req.rid!r} needs {need} positions; the limit is {self.max_model_len}")

@@ -55,6 +55,7 @@ class StepRunner:
         groups = group_needs(needs)
         self.cache = CacheManager(groups, page_size, num_pages, max_slots)
         self.storage = CacheStorage(needs, groups, page_size, num_pages, max_slots, self.act_dtype, self.device)
+        self.cache.on_slot_taken = self.storage.clear_slot
         self.n_groups = len(self.cache.paged_groups)
         self.vocab = model.spec.vocab_size
         self._pinned = None
@@ -69,6 +70,7 @@ class StepRunner:
         self._decode_layouts = {}
         self._table_arrays = {}
         self._arange_cache = None
+        self.extra_dev = None                     # device copy of the last step's `extra` section
 
     # ---- requests -------------------------------------------------------------------------------
     def add_request(self, rid) -> int:
@@ -134,8 +136,11 @@ class StepRunner:
             if need[g] > free[g]:
                 raise OutOfPages(f"the step needs {need[g]} page(s) in cache group {g}, {free[g]} are free")
 
-    def _pack(self, entries: Sequence[StepEntry], pad=None, fixed_blocks: Optional[int] = None):
-        """Reserves the pages and builds the step's index arrays.  pad = (tokens, requests, tiles,
+    EXTRA_WORDS = 16        # words per request of the section a caller may send along (sampling parameters)
+
+    def _pack(self, entries: Sequence[StepEntry], pad=None, fixed_blocks: Optional[int] = None, extra=None):
+        """Reserves the pages and builds the step's index arrays.  `extra` (int32 array, at most
+        EXTRA_WORDS per request): the caller's own section, copied along as the last one.  pad = (tokens, requests, tiles,
         decode rows, wanted rows): the sizes of a captured step's arrays.  Padded token rows carry
         request -1 and slot -1, padded tiles request -1 and padded decode rows -1, all of which the
         kernels skip; padded wanted rows repeat row 0."""
@@ -197,6 +202,10 @@ class StepRunner:
             sm[:N] = bt[treq[:N], pos[:N] // ps] * ps + pos[:N] % ps
             parts += [bt.reshape(-1), sm]
             max_blocks.append(mb)
+        ex = np.zeros(Rp * self.EXTRA_WORDS, dtype=np.int32)
+        if extra is not None:
+            ex[:extra.size] = extra.reshape(-1)
+        parts.append(ex)
         sizes = [p.size for p in parts]
         offs, o = [], 0                       # each section starts on a 16-byte boundary
         for sz in sizes:
@@ -225,6 +234,7 @@ class StepRunner:
         for g in range(self.n_groups):
             ctx.block_tables.append(sec(n_fixed + 2 * g).view(Rp, max_blocks[g]))
             ctx.slot_mapping.append(sec(n_fixed + 2 * g + 1))
+        ctx.extra = sec(n_fixed + 2 * self.n_groups)
         ctx.host = hb
         ctx.storage = self.storage
         ctx.page_size = self.page_size
@@ -233,12 +243,12 @@ class StepRunner:
         ctx.max_decode_ctx = max([c + 1 for c, n in zip(hb.ctx_len, hb.q_len) if n == 1], default=0)
         return ctx
 
-    def prepare(self, entries: Sequence[StepEntry], sampled: Optional[torch.Tensor] = None) -> StepContext:
+    def prepare(self, entries: Sequence[StepEntry], sampled: Optional[torch.Tensor] = None, extra=None) -> StepContext:
         """Reserves pages for every entry (all or none), builds the step's index arrays in pinned
         memory and copies them to the device in one transfer.  `sampled`: the ids the sampling kernel
         left on the device, for entries that take their token from there."""
         self._validate(entries)
-        hb, slot, o, offs, sizes, max_blocks, n_fixed, dims, counts = self._pack(entries)
+        hb, slot, o, offs, sizes, max_blocks, n_fixed, dims, counts = self._pack(entries, extra=extra)
         dev = torch.empty(o, dtype=torch.int32, device=self.device)
         dev.copy_(slot[0][:o], non_blocking=True)
         if slot[1] is None:
@@ -267,7 +277,7 @@ class StepRunner:
             ctx_bucket *= 2
         return bucket, min(ctx_bucket, -(-self.max_model_len // self.page_size) * self.page_size)
 
-    def _pack_decode(self, entries, bucket: int, fixed_blocks: int):
+    def _pack_decode(self, entries, bucket: int, fixed_blocks: int, extra=None):
         """_pack for a step in which every request has one token, with little host work: the same
         sections at the same offsets, filled with array operations; block tables are kept as arrays
         per request and only their new entries are copied."""
@@ -286,6 +296,7 @@ class StepRunner:
             sizes = [bucket] * 8 + [0, 0, bucket, bucket]
             for _ in range(G):
                 sizes += [bucket * fixed_blocks, bucket]
+            sizes.append(bucket * self.EXTRA_WORDS)
             offs, o = [], 0
             for sz in sizes:
                 offs.append(o)
@@ -319,6 +330,8 @@ class StepRunner:
             sm = sec(n_fixed + 2 * g + 1)
             sm[:R] = bt[ar[:R], pos // ps] * ps + pos % ps
             sm[R:] = -1
+        if extra is not None:
+            sec(n_fixed + 2 * G)[:extra.size] = extra.reshape(-1)
         return hb, slot, o, offs, sizes, [fixed_blocks] * G, n_fixed, (R, R, bucket, bucket), (0, bucket)
 
     def _arange(self, n: int):
@@ -346,11 +359,11 @@ class StepRunner:
             arr[:first] = -1
         return arr
 
-    def _graph_step(self, entries, sampled=None) -> torch.Tensor:
+    def _graph_step(self, entries, sampled=None, extra=None) -> torch.Tensor:
         key = self._graph_key(entries)
         bucket, ctx_bucket = key
         fixed_blocks = -(-ctx_bucket // self.page_size)
-        packed = self._pack_decode(entries, bucket, fixed_blocks)
+        packed = self._pack_decode(entries, bucket, fixed_blocks, extra)
         return self._wanted_rows(self._run_captured(key, packed, entries, sampled, ctx_bucket), entries)
 
     # ---- small steps with prompt portions as CUDA graphs --------------------------------------------
@@ -384,9 +397,9 @@ class StepRunner:
         ctx_bucket = min(ctx_bucket, -(-self.max_model_len // self.page_size) * self.page_size)
         return ("portions", Np, Rp, Rp, Dp, Wp), ctx_bucket
 
-    def _small_graph_step(self, key, entries, sampled=None) -> torch.Tensor:
+    def _small_graph_step(self, key, entries, sampled=None, extra=None) -> torch.Tensor:
         pad, ctx_bucket = key
-        packed = self._pack(entries, pad=pad[1:], fixed_blocks=-(-ctx_bucket // self.page_size))
+        packed = self._pack(entries, pad=pad[1:], fixed_blocks=-(-ctx_bucket // self.page_size), extra=extra)
         logits = self._run_captured(key, packed, entries, sampled, ctx_bucket)
         return logits[:sum(len(e.want) for e in entries)]
 
@@ -410,6 +423,7 @@ class StepRunner:
         slot[1].record()
         self.last_h2d_bytes = o * 4
         ctx.host, ctx.n_requests = hb, len(entries)
+        self.extra_dev = ctx.extra
         self._patch_tokens(entries, ctx, sampled)
         ctx.max_decode_ctx = ctx_bucket               # the split plan is fixed for the whole bucket
         ctx.max_ctx = ctx_bucket
@@ -458,19 +472,22 @@ class StepRunner:
         return logits[torch.tensor(wanted, dtype=torch.long, device=logits.device)]
 
     @torch.no_grad()
-    def step(self, entries: Sequence[StepEntry], sampled: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], sampled: Optional[torch.Tensor] = None, extra=None) -> torch.Tensor:
         """Runs one step; returns the 32-bit logits [wanted, vocab] (a device tensor) in the order
         of the entries and of their `want`.  `sampled` (int32, device): ids sampled in the step
-        before, for entries with `from_device`."""
+        before, for entries with `from_device`.  `extra` (int32 numpy array of at most EXTRA_WORDS
+        words per entry): travels to the device in the step's one copy; `self.extra_dev` is its
+        device copy afterwards (the engine sends the sampling parameters this way)."""
         graphs = self.use_cuda_graphs and getattr(self.model, "graph_safe", True)      # not while results are tapped
         if graphs and all(len(e.tokens) == 1 for e in entries) and len(entries) <= self.max_graph_batch:
             self._validate(entries)
-            logits = self._graph_step(entries, sampled)
+            logits = self._graph_step(entries, sampled, extra)
         elif graphs and (key := self._small_step_key(entries)) is not None:
             self._validate(entries)
-            logits = self._small_graph_step(key, entries, sampled)
+            logits = self._small_graph_step(key, entries, sampled, extra)
         else:
-            ctx = self.prepare(entries, sampled)
+            ctx = self.prepare(entries, sampled, extra)
+            self.extra_dev = ctx.extra
             with ops.stream_scope():
                 logits = self.model.forward(ctx)
         for e in entries:

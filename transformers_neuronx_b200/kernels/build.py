@@ -2,7 +2,9 @@
 
 Each .cu file becomes one library with plain C entry points, compiled for sm_100a by nvcc when it
 is first needed (a model builds what its parts need, nothing else) and kept under csrc/_build/,
-named by a hash of the source, the headers and the flags.  When that folder cannot be written,
+named by a hash of the source, the headers and the flags.  A library exists in two flavours: the
+default one, whose 16-bit type is bfloat16, and "f16" (compiled with -DTNX_F16), whose 16-bit type is
+float16; a library name may carry the flavour as a suffix ("gemm_tc.f16").  When that folder cannot be written,
 a per-user folder under the system's temporary directory is used.  There is no fallback: a
 library that cannot be built or loaded raises.
 """
@@ -98,8 +100,32 @@ def _build_dir() -> str:
         return _build_dir_cached
 
 
+FLAVOURS = {"": [], "f16": ["-DTNX_F16"]}
+
+
+def split_name(name: str):
+    """'gemm_tc.f16' -> ('gemm_tc', 'f16'); 'gemm_tc' -> ('gemm_tc', '')."""
+    base, _, flavour = name.partition(".")
+    if base not in SOURCES:
+        raise KernelBuildError(f"no kernel source registered under {base!r}")
+    if flavour not in FLAVOURS:
+        raise KernelBuildError(f"unknown flavour {flavour!r} of {base!r}; known: {sorted(FLAVOURS)}")
+    return base, flavour
+
+
+def flavour_of(dtype) -> str:
+    """The flavour whose 16-bit type is `dtype` (a torch dtype or its name); '' for bfloat16 and float32."""
+    return "f16" if str(dtype).replace("torch.", "") in ("float16", "half") else ""
+
+
+def with_flavour(names: Iterable[str], dtype) -> List[str]:
+    f = flavour_of(dtype)
+    return [n if (not f or "." in n) else f"{n}.{f}" for n in names]
+
+
 def library_path(name: str) -> str:
-    src = os.path.join(CSRC, SOURCES[name])
+    base, flavour = split_name(name)
+    src = os.path.join(CSRC, SOURCES[base])
     return os.path.join(_build_dir(), f"{name}.{_digest(src)}.so")
 
 
@@ -109,19 +135,19 @@ def _say(msg: str) -> None:
 
 def build(name: str, verbose: bool = True) -> str:
     """Compiles one library if its up-to-date binary is not there yet; returns its path."""
-    if name not in SOURCES:
-        raise KernelBuildError(f"no kernel source registered under {name!r}")
+    base, flavour = split_name(name)
     out = library_path(name)
     with _lock:
         lk = _build_locks.setdefault(name, threading.Lock())
     with lk:
-        src = os.path.join(CSRC, SOURCES[name])
+        src = os.path.join(CSRC, SOURCES[base])
         if os.path.isfile(out):
             return out
         tmp = f"{out}.{os.getpid()}.{threading.get_ident()}.tmp"
-        cmd = [_nvcc()] + NVCC_FLAGS + ["-I", CSRC, "-o", tmp, src]
+        cmd = [_nvcc()] + NVCC_FLAGS + FLAVOURS[flavour] + ["-I", CSRC, "-o", tmp, src]
+        what = SOURCES[base] + (f" ({flavour})" if flavour else "")
         if verbose:
-            _say(f"compiling {SOURCES[name]} for sm_100a ...")
+            _say(f"compiling {what} for sm_100a ...")
         t0 = time.time()
         proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
         while True:                      # a line now and then while a long compile runs
@@ -130,7 +156,7 @@ def build(name: str, verbose: bool = True) -> str:
                 break
             except subprocess.TimeoutExpired:
                 if verbose:
-                    _say(f"  still compiling {SOURCES[name]} ({time.time() - t0:.0f} s)")
+                    _say(f"  still compiling {what} ({time.time() - t0:.0f} s)")
         if proc.returncode != 0:
             if os.path.exists(tmp):
                 os.remove(tmp)
@@ -164,7 +190,7 @@ def import_libraries(directory: str) -> List[str]:
     taken = []
     if not os.path.isdir(directory):
         raise KernelBuildError(f"{directory!r} is not a folder of compiled kernels")
-    for n in SOURCES:
+    for n in [b if not f else f"{b}.{f}" for b in SOURCES for f in FLAVOURS]:
         want = library_path(n)
         src = os.path.join(directory, os.path.basename(want))
         if os.path.isfile(src) and not os.path.isfile(want):
@@ -186,10 +212,16 @@ def build_many(names: Iterable[str], verbose: bool = True) -> None:
 
 
 def build_all(verbose: bool = True) -> None:
-    build_many(list(SOURCES), verbose)
+    """Every library in every flavour."""
+    build_many([b if not f else f"{b}.{f}" for f in FLAVOURS for b in SOURCES], verbose)
 
 
-def load(name: str) -> ctypes.CDLL:
+def load(name: str, dtype=None) -> ctypes.CDLL:
+    """The library `name`; with `dtype` given, in the flavour whose 16-bit type it is."""
+    if dtype is not None and "." not in name:
+        f = flavour_of(dtype)
+        if f:
+            name = f"{name}.{f}"
     lib = _loaded.get(name)
     if lib is not None:
         return lib

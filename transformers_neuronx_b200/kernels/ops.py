@@ -85,11 +85,32 @@ def _need(t: torch.Tensor, name: str, dtype=None, ndim=None, contiguous=True) ->
         raise KernelError(f"{name} must be contiguous")
 
 
-_FLOATS = (torch.float32, torch.bfloat16)
+_H16 = (torch.bfloat16, torch.float16)          # the 16-bit types: one library flavour each (kernels/build.py)
+_FLOATS = (torch.float32,) + _H16
+
+# Activations a product's epilogue applies, by the names the reference looks up
+# (src/transformers_neuronx/hlo.py:485-501 -> activations.py) -> the kernels' codes (csrc/common.cuh).
+ACTIVATIONS = {None: 0, "none": 0, "relu": 1, "gelu_new": 2, "gelu_new_legacy": 2, "gelu_pytorch_tanh": 2,
+               "silu": 3, "swish": 3, "sigmoid": 4, "gelu": 5}
 
 
-def _is_bf16(t: torch.Tensor) -> int:
-    return 1 if t.dtype == torch.bfloat16 else 0
+def activation_code(name) -> int:
+    if name not in ACTIVATIONS:
+        raise KernelError(f"activation {name!r} is not built into the products' epilogues; "
+                          f"available: {sorted(k for k in ACTIVATIONS if k)}")
+    return ACTIVATIONS[name]
+
+
+def _is_h16(t: torch.Tensor) -> int:
+    return 1 if t.dtype in _H16 else 0
+
+
+def _lib(name: str, *tensors):
+    """The library `name` in the flavour of the 16-bit type among `tensors` (they must agree)."""
+    kinds = {t.dtype for t in tensors if t is not None and t.dtype in _H16}
+    if len(kinds) > 1:
+        raise KernelError(f"{name}: bfloat16 and float16 tensors in one call")
+    return _build.load(name, next(iter(kinds)) if kinds else None)
 
 
 def _rows_2d(t: torch.Tensor, name: str):
@@ -102,7 +123,7 @@ def _rows_2d(t: torch.Tensor, name: str):
 # ---------------------------------------------------------------------------------------------
 def embed(tok_table, pre, ids, pos_table, positions, pos_offset, out_f32, out_act):
     """out[n] = (tok_table[ids[n]] or pre[n]) + pos_table[positions[n] + pos_offset]."""
-    lib = _build.load("embedding")
+    lib = _lib("embedding", tok_table, pos_table, out_act)
     N = ids.shape[0]
     _need(ids, "ids", torch.int32, 1)
     ref = out_f32 if out_f32 is not None else out_act
@@ -112,7 +133,7 @@ def embed(tok_table, pre, ids, pos_table, positions, pos_offset, out_f32, out_ac
         _need(tok_table, "tok_table", _FLOATS, 2)
         if tok_table.shape[1] != H:
             raise KernelError("tok_table width differs from the output width")
-        table_bf16 = _is_bf16(tok_table)
+        table_bf16 = _is_h16(tok_table)
     else:
         _need(pre, "pre", torch.float32, 2)
     if pos_table is not None:
@@ -120,7 +141,7 @@ def embed(tok_table, pre, ids, pos_table, positions, pos_offset, out_f32, out_ac
         _need(positions, "positions", torch.int32, 1)
         if tok_table is not None and pos_table.dtype != tok_table.dtype:
             raise KernelError("token and position tables must have one dtype")
-        table_bf16 = _is_bf16(pos_table)
+        table_bf16 = _is_h16(pos_table)
         if pos_table.shape[1] != H:
             raise KernelError("pos_table width differs from the output width")
     if out_f32 is not None:
@@ -128,7 +149,7 @@ def embed(tok_table, pre, ids, pos_table, positions, pos_offset, out_f32, out_ac
     act_bf16 = 0
     if out_act is not None:
         _need(out_act, "out_act", _FLOATS, 2)
-        act_bf16 = _is_bf16(out_act)
+        act_bf16 = _is_h16(out_act)
     _check(lib.tnx_embed(_p(tok_table), _p(pre), _p(ids), _p(pos_table), _p(positions), c_int(pos_offset),
                          _p(out_f32), _p(out_act), c_int(N), c_int(H), c_int(table_bf16), c_int(act_bf16),
                          _stream()), "embed")
@@ -145,17 +166,17 @@ def patch_tokens(tokens, src, sampled):
 
 
 def gather_rows(table, ids, out):
-    lib = _build.load("embedding")
+    lib = _lib("embedding", table, out)
     _need(table, "table", _FLOATS, 2)
     _need(ids, "ids", torch.int32, 1)
     _need(out, "out", _FLOATS, 2)
     _check(lib.tnx_gather_rows(_p(table), _p(ids), _p(out), c_int(ids.shape[0]), c_int(table.shape[1]),
-                               c_int(_is_bf16(table)), c_int(_is_bf16(out)), _stream()), "gather_rows")
+                               c_int(_is_h16(table)), c_int(_is_h16(out)), _stream()), "gather_rows")
 
 
 def layer_norm(x, gamma, beta, eps, out_f32=None, out_act=None, rows=None):
     """Rows of the 32-bit x normalised; `rows` (int32) picks input rows."""
-    lib = _build.load("layernorm")
+    lib = _lib("layernorm", out_act)
     _need(x, "x", torch.float32, 2)
     H = x.shape[1]
     n_rows = rows.shape[0] if rows is not None else x.shape[0]
@@ -173,23 +194,25 @@ def layer_norm(x, gamma, beta, eps, out_f32=None, out_act=None, rows=None):
             if t.shape[0] < n_rows or t.shape[1] != H:
                 raise KernelError(f"{nm} has shape {tuple(t.shape)}, needs [{n_rows}, {H}]")
     if out_act is not None:
-        act_bf16 = _is_bf16(out_act)
+        act_bf16 = _is_h16(out_act)
     _check(lib.tnx_layer_norm(_p(x), _p(rows), _p(gamma), _p(beta), c_float(eps), _p(out_f32), _p(out_act),
                               c_int(n_rows), c_int(H), c_int(act_bf16), _stream()), "layer_norm")
 
 
 def pick_rows(x, rows, out_f32=None, out_act=None):
-    lib = _build.load("layernorm")
+    lib = _lib("layernorm", out_act)
     _need(x, "x", torch.float32, 2)
     n_rows = rows.shape[0] if rows is not None else x.shape[0]
-    act_bf16 = _is_bf16(out_act) if out_act is not None else 0
+    act_bf16 = _is_h16(out_act) if out_act is not None else 0
     _check(lib.tnx_pick_rows(_p(x), _p(rows), _p(out_f32), _p(out_act), c_int(n_rows), c_int(x.shape[1]),
                              c_int(act_bf16), _stream()), "pick_rows")
 
 
-def gemm_simt(a, w, out, bias=None, residual=None, relu=False):
-    """out = epilogue(a @ w^T) on CUDA cores with 32-bit FMA; a [M, K], w [N, K], out [M, N]."""
-    lib = _build.load("gemm_simt")
+def gemm_simt(a, w, out, bias=None, residual=None, activation=None):
+    """out = epilogue(a @ w^T) on CUDA cores with 32-bit FMA; a [M, K], w [N, K], out [M, N]; each of
+    them 32-bit or 16-bit (a 16-bit matrix is widened exactly as it is loaded)."""
+    lib = _lib("gemm_simt", a, w, out)
+    act = activation_code(activation)
     _need(a, "a", _FLOATS, None, contiguous=False)
     _need(w, "w", _FLOATS, None, contiguous=False)
     _need(out, "out", _FLOATS, None, contiguous=False)
@@ -207,14 +230,14 @@ def gemm_simt(a, w, out, bias=None, residual=None, relu=False):
         if tuple(residual.shape) != (M, N) or _rows_2d(residual, "residual")[2] != ldc or out.dtype != torch.float32:
             raise KernelError("residual must be float32 with the shape and row stride of a float32 out")
     _check(lib.tnx_gemm_simt(_p(a), _p(w), _p(bias), _p(residual), _p(out), c_int(M), c_int(N), c_int(K),
-                             c_int(lda), c_int(ldw), c_int(ldc), c_int(1 if relu else 0), c_int(_is_bf16(a)),
-                             c_int(_is_bf16(w)), c_int(_is_bf16(out)), _stream()), "gemm_simt")
+                             c_int(lda), c_int(ldw), c_int(ldc), c_int(act), c_int(_is_h16(a)),
+                             c_int(_is_h16(w)), c_int(_is_h16(out)), _stream()), "gemm_simt")
 
 
 def kv_append(k_src, v_src, slot_mapping, cache, page_size):
     """k_src, v_src: [N, n_kv_heads * head_dim] views (rows contiguous, one row stride);
     cache: [pages, 2, n_kv_heads, page_size, head_dim]."""
-    lib = _build.load("kv_cache")
+    lib = _lib("kv_cache", cache, k_src, v_src)
     _need(cache, "cache", _FLOATS, 5)
     _need(slot_mapping, "slot_mapping", torch.int32, 1)
     N, width, stride = _rows_2d(k_src, "k_src")
@@ -224,12 +247,12 @@ def kv_append(k_src, v_src, slot_mapping, cache, page_size):
     if two != 2 or ps != page_size or n_kv * d != width:
         raise KernelError(f"cache shape {tuple(cache.shape)} does not fit rows of width {width}")
     _check(lib.tnx_kv_append(_p(k_src), _p(v_src), c_int(stride), _p(slot_mapping), _p(cache), c_int(N),
-                             c_int(n_kv), c_int(d), c_int(ps), c_int(_is_bf16(cache)), _stream()), "kv_append")
+                             c_int(n_kv), c_int(d), c_int(ps), c_int(_is_h16(cache)), _stream()), "kv_append")
 
 
 def attention_simt(q, cache, block_tables, token_request, positions, out, n_heads, scale, window=0):
     """q: [N, n_heads * head_dim] view; out likewise; cache as in kv_append."""
-    lib = _build.load("attention_simt")
+    lib = _lib("attention_simt", cache, q, out)
     _need(cache, "cache", _FLOATS, 5)
     N, width, q_stride = _rows_2d(q, "q")
     No, wo, out_stride = _rows_2d(out, "out")
@@ -242,7 +265,7 @@ def attention_simt(q, cache, block_tables, token_request, positions, out, n_head
     _check(lib.tnx_attention_simt(_p(q), c_int(q_stride), _p(cache), _p(block_tables), c_int(block_tables.stride(0)),
                                   _p(token_request), _p(positions), _p(out), c_int(out_stride), c_int(N),
                                   c_int(n_heads), c_int(n_kv), c_int(d), c_int(ps), c_int(window or 0),
-                                  c_float(scale), c_int(_is_bf16(cache)), _stream()), "attention_simt")
+                                  c_float(scale), c_int(_is_h16(cache)), _stream()), "attention_simt")
 
 
 def sample(logits, out, temperature=None, top_k=None, top_p=None, seeds=None, counters=None, suppress_id=-1,
@@ -265,6 +288,40 @@ def sample(logits, out, temperature=None, top_k=None, top_p=None, seeds=None, co
     _check(lib.tnx_sample(_p(logits), c_int(ld), c_int(R), c_int(V), _p(temperature), _p(top_k), _p(top_p),
                           _p(min_keep), c_int(1 if deterministic else 0), _p(seeds), _p(counters),
                           c_int(suppress_id), _p(out), _stream()), "sample")
+
+
+def sample_packed(logits, packed, with_top_p, out, err_word=None):
+    """sample() with every row's parameters packed, 16 int32 words a row (csrc/sampling.cu):
+    temperature, top_k, top_p, min_keep, seed (2), counter (2), flags, up to four suppressed ids.
+    err_word: a device int32 whose value is written to out[rows] (out then needs rows + 1 entries)."""
+    lib = _build.load("sampling")
+    _need(logits, "logits", torch.float32, None, contiguous=False)
+    R, V, ld = _rows_2d(logits, "logits")
+    _need(out, "out", torch.int32, 1)
+    _need(packed, "packed", torch.int32, None)
+    words = lib.tnx_sample_row_words()
+    if packed.numel() < R * words:
+        raise KernelError(f"packed holds {packed.numel()} words, {R} rows need {R * words}")
+    if out.shape[0] < R + (1 if err_word is not None else 0):
+        raise KernelError("out is too short for the rows (and the error word)")
+    if err_word is not None:
+        _need(err_word, "err_word", torch.int32, 1)
+    _check(lib.tnx_sample_packed(_p(logits), c_int(ld), c_int(R), c_int(V), _p(packed), c_int(1 if with_top_p else 0),
+                                 _p(err_word), _p(out), _stream()), "sample")
+
+
+def error_word(device) -> torch.Tensor:
+    """The device word that kernels with bounded waits set when a wait ran out (0: none did)."""
+    return _state(device)["err"]
+
+
+def raise_if_error_code(code: int, where: str = "") -> None:
+    """Raises for a value of the error word that was read along with a step's results."""
+    if code:
+        for st in _dev_state.values():
+            st["err"].zero_()
+        raise KernelError(f"a bounded wait ran out inside a kernel{where} (where: {code}); its results, and "
+                          "everything computed from them, are invalid")
 
 
 # ---------------------------------------------------------------------------------------------
@@ -307,13 +364,19 @@ def raise_on_device_error(device=None):
                               "its results are invalid")
 
 
-def has_gemm_tc() -> bool:
-    return True
+def selftest_wait_runs_out(device, code: int = 99, limit_ns: int = 1_000_000) -> None:
+    """Launches a kernel whose bounded wait (about a millisecond) runs out by design and records
+    `code` in the device's error word: what raise_on_device_error() and the engine's per-step check
+    then report.  For tests of the error path; nothing hangs, the wait ends by itself."""
+    lib = _build.load("gemm_tc")
+    st = _state(torch.device(device))
+    _check(lib.tnx_selftest_wait_runs_out(_p(st["err"]), c_int(code), ctypes.c_longlong(limit_ns), _stream()),
+           "selftest_wait_runs_out")
 
 
 def gemm_tc_supported(a, w, out) -> bool:
     """Size rules of the TMA descriptors: row pitches multiples of 16 bytes, 16-byte aligned bases."""
-    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+    if a.dtype not in _H16 or w.dtype != a.dtype or (out.dtype in _H16 and out.dtype != a.dtype):
         return False
     K = a.shape[1]
     if K % 8 or a.stride(0) % 8 or w.stride(0) % 8 or a.data_ptr() % 16 or w.data_ptr() % 16:
@@ -321,12 +384,13 @@ def gemm_tc_supported(a, w, out) -> bool:
     return out.data_ptr() % 16 == 0
 
 
-def gemv(a, w, out, bias=None, residual=None, relu=False):
+def gemv(a, w, out, bias=None, residual=None, activation=None):
     """out = epilogue(a @ w^T) for one to four tokens, the weights streamed through the multiply-add
-    units (bfloat16 operands, 32-bit sums).  gemm_tc() picks it by itself for one token."""
-    lib = _build.load("gemv")
-    _need(a, "a", torch.bfloat16, None, contiguous=False)
-    _need(w, "w", torch.bfloat16, None, contiguous=False)
+    units (16-bit operands, 32-bit sums).  gemm_tc() picks it by itself for one token."""
+    lib = _lib("gemv", a, w, out)
+    act = activation_code(activation)
+    _need(a, "a", _H16, None, contiguous=False)
+    _need(w, "w", _H16, None, contiguous=False)
     _need(out, "out", _FLOATS, None, contiguous=False)
     M, K, lda = _rows_2d(a, "a")
     N, Kw, ldw = _rows_2d(w, "w")
@@ -344,19 +408,20 @@ def gemv(a, w, out, bias=None, residual=None, relu=False):
         if tuple(residual.shape) != (M, N) or _rows_2d(residual, "residual")[2] != ldc or out.dtype != torch.float32:
             raise KernelError("residual must be float32 with the shape and row stride of a float32 out")
     _check(lib.tnx_gemv(_p(a), _p(w), _p(bias), _p(residual), _p(out), c_int(M), c_int(N), c_int(K),
-                        c_int(lda), c_int(ldw), c_int(ldc), c_int(1 if relu else 0), c_int(_is_bf16(out)),
+                        c_int(lda), c_int(ldw), c_int(ldc), c_int(act), c_int(_is_h16(out)),
                         _stream()), "gemv")
 
 
-def gemm_tc(a, w, out, bias=None, residual=None, relu=False, splits=None, few_tokens_kernel=True, cluster=False):
-    """out = epilogue(a @ w^T), bfloat16 operands, 32-bit accumulation: on the tcgen05 tensor cores,
+def gemm_tc(a, w, out, bias=None, residual=None, activation=None, splits=None, few_tokens_kernel=True, cluster=False):
+    """out = epilogue(a @ w^T), 16-bit operands (both bfloat16 or both float16), 32-bit accumulation: on the tcgen05 tensor cores,
     or (one token, unless few_tokens_kernel is False or splits is given) as a stream of the
     weights through the multiply-add units.  `splits` forces a split of K for up to 128 tokens (a test
     hook): partial tiles added by the CTA that finishes last, or (cluster=True, at most 8 splits) by
     the CTAs of a cluster through their shared memory, which is what the kernel's own plan uses."""
-    lib = _build.load("gemm_tc")
-    _need(a, "a", torch.bfloat16, None, contiguous=False)
-    _need(w, "w", torch.bfloat16, None, contiguous=False)
+    lib = _lib("gemm_tc", a, w, out)
+    act = activation_code(activation)
+    _need(a, "a", _H16, None, contiguous=False)
+    _need(w, "w", _H16, None, contiguous=False)
     _need(out, "out", _FLOATS, None, contiguous=False)
     M, K, lda = _rows_2d(a, "a")
     N, Kw, ldw = _rows_2d(w, "w")
@@ -375,10 +440,10 @@ def gemm_tc(a, w, out, bias=None, residual=None, relu=False, splits=None, few_to
         if tuple(residual.shape) != (M, N) or _rows_2d(residual, "residual")[2] != ldc or out.dtype != torch.float32:
             raise KernelError("residual must be float32 with the shape and row stride of a float32 out")
     if few_tokens_kernel and splits is None and M == 1:    # with two tokens and more the tensor-core kernel is as fast (measured)
-        gv = _build.load("gemv")
+        gv = _lib("gemv", a, w, out)
         if gv.tnx_gemv_supported(c_int(M), c_int(N), c_int(K)):
             _check(gv.tnx_gemv(_p(a), _p(w), _p(bias), _p(residual), _p(out), c_int(M), c_int(N), c_int(K),
-                               c_int(lda), c_int(ldw), c_int(ldc), c_int(1 if relu else 0), c_int(_is_bf16(out)),
+                               c_int(lda), c_int(ldw), c_int(ldc), c_int(act), c_int(_is_h16(out)),
                                _stream()), "gemv")
             return
     st = _state(a.device)
@@ -409,22 +474,22 @@ def gemm_tc(a, w, out, bias=None, residual=None, relu=False, splits=None, few_to
         scratch = _grow(st, "scratch", need, torch.float32, a.device, 1 << 22)
         _grow(st, "counters", ncnt.value, torch.int32, a.device, 1024, zero=True)
     _check(lib.tnx_gemm_tc(_p(a), _p(w), _p(bias), _p(residual), _p(out), c_int(M), c_int(N), c_int(K),
-                           c_int(lda), c_int(ldw), c_int(ldc), c_int(1 if relu else 0), c_int(_is_bf16(out)),
+                           c_int(lda), c_int(ldw), c_int(ldc), c_int(act), c_int(_is_h16(out)),
                            n_splits, _p(scratch), _p(st["counters"]), _p(st["err"]), _stream()), "gemm_tc")
 
 
 def attention_decode(q, cache, block_tables, token_request, positions, out, n_heads, scale, window=0, rows=None,
                      n_rows=None, max_kv_len=None, n_splits=None, new_kv=None):
-    """One query token per row over the paged bfloat16 cache.  `rows` (int32) names the rows of q
+    """One query token per row over the paged 16-bit cache.  `rows` (int32) names the rows of q
     that are decode tokens (None: all); max_kv_len bounds their contexts (for the split plan).
     new_kv = (k, v), [rows of q, kv_heads * head_dim] bfloat16: the keys and values of the rows' own
     tokens, which the kernel then writes into their pages itself (no kv_append before it)."""
-    lib = _build.load("attention_decode")
-    _need(cache, "cache", torch.bfloat16, 5)
+    lib = _lib("attention_decode", cache, q, out)
+    _need(cache, "cache", _H16, 5)
     N, width, q_stride = _rows_2d(q, "q")
     No, wo, out_stride = _rows_2d(out, "out")
     _, _, n_kv, ps, d = cache.shape
-    if width != n_heads * d or (No, wo) != (N, width) or q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+    if width != n_heads * d or (No, wo) != (N, width) or q.dtype != cache.dtype or out.dtype != cache.dtype:
         raise KernelError("q/out do not fit the cache's head size or dtype")
     _need(block_tables, "block_tables", torch.int32, 2)
     _need(token_request, "token_request", torch.int32, 1)
@@ -457,7 +522,7 @@ def attention_decode(q, cache, block_tables, token_request, positions, out, n_he
     if new_kv is not None:
         k_new, v_new = new_kv
         for t, nm in ((k_new, "k"), (v_new, "v")):
-            _need(t, nm, torch.bfloat16, None, contiguous=False)
+            _need(t, nm, cache.dtype, None, contiguous=False)
             if _rows_2d(t, nm)[:2] != (N, n_kv * d):
                 raise KernelError(f"new {nm} must be [{N}, {n_kv * d}]")
         kv_stride = k_new.stride(0)
@@ -477,12 +542,12 @@ ATTN_PREFILL_TILE = 128      # query rows of one work item of the prefill attent
 def attention_prefill(q, cache, block_tables, tile_req, tile_q0, q_start, q_len, ctx_len, out, n_heads, scale,
                       window=0, n_items=None):
     """Causal attention of prompt portions: work items (request, first row of an ATTN_PREFILL_TILE-row tile)."""
-    lib = _build.load("attention_prefill")
-    _need(cache, "cache", torch.bfloat16, 5)
+    lib = _lib("attention_prefill", cache, q, out)
+    _need(cache, "cache", _H16, 5)
     N, width, q_stride = _rows_2d(q, "q")
     No, wo, out_stride = _rows_2d(out, "out")
     _, _, n_kv, ps, d = cache.shape
-    if width != n_heads * d or (No, wo) != (N, width) or q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+    if width != n_heads * d or (No, wo) != (N, width) or q.dtype != cache.dtype or out.dtype != cache.dtype:
         raise KernelError("q/out do not fit the cache's head size or dtype")
     for t, nm in ((block_tables, "block_tables"), (tile_req, "tile_req"), (tile_q0, "tile_q0"), (q_start, "q_start"),
                   (q_len, "q_len"), (ctx_len, "ctx_len")):
@@ -496,7 +561,7 @@ def attention_prefill(q, cache, block_tables, tile_req, tile_q0, q_start, q_len,
 
 def attention_prefill_tc_supported(q, cache, out) -> bool:
     """The tcgen05 prefill kernel takes head sizes 64 and 128, pages of 16 and 16-byte aligned rows."""
-    return (cache.dtype == torch.bfloat16 and cache.shape[4] in (64, 128) and cache.shape[3] == 16 and q.stride(0) % 8 == 0 and
+    return (cache.dtype in _H16 and q.dtype == cache.dtype and out.dtype == cache.dtype and cache.shape[4] in (64, 128) and cache.shape[3] == 16 and q.stride(0) % 8 == 0 and
             out.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0 and
             cache.shape[0] * 2 * cache.shape[2] * 16 < 2 ** 31)
 
@@ -505,13 +570,13 @@ def attention_prefill_tc(q, cache, block_tables, tile_req, tile_q0, q_start, q_l
                          window=0, n_items=None):
     """attention_prefill on the tcgen05 tensor cores (head sizes 64 and 128).  The cache must hold finite
     numbers in every row, written or not (CacheStorage allocates it zeroed)."""
-    lib = _build.load("attention_prefill_tc")
-    _need(cache, "cache", torch.bfloat16, 5)
+    lib = _lib("attention_prefill_tc", cache, q, out)
+    _need(cache, "cache", _H16, 5)
     N, width, q_stride = _rows_2d(q, "q")
     No, wo, out_stride = _rows_2d(out, "out")
     n_pages, _, n_kv, ps, d = cache.shape
     if not attention_prefill_tc_supported(q, cache, out) or width != n_heads * d or (No, wo) != (N, width):
-        raise KernelError("attention_prefill_tc takes bfloat16, head size 64 or 128, pages of 16, 16-byte aligned rows")
+        raise KernelError("attention_prefill_tc takes a 16-bit type, head size 64 or 128, pages of 16, 16-byte aligned rows")
     for t, nm in ((block_tables, "block_tables"), (tile_req, "tile_req"), (tile_q0, "tile_q0"), (q_start, "q_start"),
                   (q_len, "q_len"), (ctx_len, "ctx_len")):
         _need(t, nm, torch.int32, 2 if nm == "block_tables" else 1)
@@ -524,7 +589,7 @@ def attention_prefill_tc(q, cache, block_tables, tile_req, tile_q0, q_start, q_l
                                         c_float(scale), _p(st["err"]), _stream()), "attention_prefill_tc")
 
 
-def _attention_bf16(ctx, group, q, cache, out, n_heads, scale, window, new_kv):
+def _attention_h16(ctx, group, q, cache, out, n_heads, scale, window, new_kv):
     if cache.shape[3] != 16 or q.stride(0) % 8 or q.data_ptr() % 16:
         return False
     bt = ctx.block_tables[group]
@@ -547,17 +612,17 @@ def _attention_bf16(ctx, group, q, cache, out, n_heads, scale, window, new_kv):
     return True
 
 
-_attention_impls["bf16"] = _attention_bf16
+_attention_impls["h16"] = _attention_h16
 
 
 def attention(ctx, group, q, cache, out, n_heads, scale, window=0, new_kv=None):
     """Attention of this step's queries over the cache of the running schedule entry.  32-bit
-    caches, and head sizes or windows that the bfloat16 kernels do not take, run on the CUDA-core
-    kernel; bfloat16 runs the prefill kernel for requests with several rows and the split
+    caches, and head sizes or windows that the 16-bit kernels do not take, run on the CUDA-core
+    kernel; a 16-bit cache runs the prefill kernel for requests with several rows and the split
     decode kernel for requests with one.  new_kv = (k, v, slot_mapping): the keys and values of
     this step's tokens, not yet in the cache; they are appended here, by kv_append or (a step of
-    decode tokens only, bfloat16) by the decode kernel itself."""
-    impl = _attention_impls.get("bf16") if cache.dtype == torch.bfloat16 else None
+    decode tokens only, 16-bit) by the decode kernel itself."""
+    impl = _attention_impls.get("h16") if cache.dtype in _H16 else None
     if impl is not None and impl(ctx, group, q, cache, out, n_heads, scale, window, new_kv):
         return
     if new_kv is not None:

@@ -65,4 +65,4 @@ def build_spec(cfg: OPTConfig) -> ModelSpec:
 
 
 register_architecture(Architecture(name="OPTForCausalLM", model_type="opt", config_class=OPTConfig,
-                                   build_spec=build_spec, random_tensors=None))
+                                   build_spec=build_spec))

@@ -1,9 +1,9 @@
 """opt_demo: the reference's command line (src/transformers_neuronx/gpt_demo.py:31-150,
 opt/demo.py:19-29) for this engine.
 
-    opt_demo [--amp f32|bf16] save <folder> --random --config cfg.json [--seed N]
-    opt_demo [--amp f32|bf16] [--model_name <folder>] save <folder>         (re-save a local checkpoint)
-    opt_demo [--amp f32|bf16] run <folder> [--batch_size 4] [--n_positions 128] [--print_latency]
+    opt_demo [--amp f32|f16|bf16] save <folder> --random --config cfg.json [--seed N]
+    opt_demo [--amp f32|f16|bf16] [--model_name <folder>] save <folder>         (re-save a local checkpoint)
+    opt_demo [--amp f32|f16|bf16] run <folder> [--batch_size 4] [--n_positions 128] [--print_latency]
              [--top_k 50] [--temperature 1.0] [--top_p 1.0] [--prompt_ids 2,100,200]
 
 `save` casts attention, fc1, fc2 and embedding matrices to --amp and keeps LayerNorm tensors in
@@ -25,8 +25,7 @@ import time
 
 import torch
 
-from ..config import OPTConfig, canonical_dtype
-from ..models import opt as opt_arch
+from ..config import config_from_dict, load_config
 from ..models.decoder import DecoderModel
 from ..weights import load_tensors, save_safetensors, write_model_folder
 from .model import OPTForSampling
@@ -36,7 +35,7 @@ PROMPT_TEXT = "Hello, I'm a language model,"
 
 def _parser():
     ap = argparse.ArgumentParser(prog="opt_demo")
-    ap.add_argument("--amp", default="f32", choices=["f32", "f16", "bf16"], help="f16 is served as bf16")
+    ap.add_argument("--amp", default="f32", choices=["f32", "f16", "bf16"])
     ap.add_argument("--model_name", default=None, help="local folder of a pretrained model (for save)")
     sub = ap.add_subparsers(dest="which", required=True)
     sp = sub.add_parser("save")
@@ -62,21 +61,21 @@ def _parser():
 
 
 def save(args):
-    dtype = torch.float32 if args.amp == "f32" else torch.bfloat16
+    dtype = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[args.amp]
     if args.random:
         assert args.config, "Please provide the config.json like: --config=./config.json"
         assert os.path.exists(args.config), f"File {args.config} does not exist."
         with open(args.config) as fp:
-            cfg = OPTConfig.from_dict(json.load(fp))
-        specs = DecoderModel(opt_arch.build_spec(cfg)).tensor_specs()
+            arch, cfg = config_from_dict(json.load(fp))
+        specs = DecoderModel(arch.build_spec(cfg)).tensor_specs()
         write_model_folder(args.save, cfg, specs, args.seed, matrix_dtype=dtype)
     else:
         src = args.model_name
         if not src or not os.path.isdir(src):
             raise SystemExit("save without --random needs --model_name <local folder>; a model cannot be "
                              "fetched by name without a network")
-        cfg = OPTConfig.from_pretrained(src)
-        specs = DecoderModel(opt_arch.build_spec(cfg)).tensor_specs()
+        arch, cfg = load_config(src)
+        specs = DecoderModel(arch.build_spec(cfg)).tensor_specs()
         tensors = load_tensors(src, specs)
         out = {}
         for s in specs:

@@ -8,16 +8,15 @@ from __future__ import annotations
 import argparse
 import json
 
-from ..config import OPTConfig
-from ..models import opt as opt_arch
+from ..config import config_from_dict
 from ..models.decoder import DecoderModel
 from ..weights import write_model_folder
 
 
 def gen_random_pretrained(config_path: str, save: str, seed: int = 0):
     with open(config_path) as fp:
-        cfg = OPTConfig.from_dict(json.load(fp))
-    specs = DecoderModel(opt_arch.build_spec(cfg)).tensor_specs()
+        arch, cfg = config_from_dict(json.load(fp))      # the model class is chosen by config.json
+    specs = DecoderModel(arch.build_spec(cfg)).tensor_specs()
     write_model_folder(save, cfg, specs, seed)
     return cfg
 

@@ -26,6 +26,7 @@ import torch
 
 from ..config import EngineConfig, GenerationConfig, NeuronConfig, OPTConfig, canonical_dtype, load_config
 from ..engine import LLMEngine, SamplingParams, StepEntry, load_model
+from ..kernels import ops
 
 
 class OPTForSampling:
@@ -40,12 +41,8 @@ class OPTForSampling:
         self.neuron_config = neuron_config or NeuronConfig()
         if kwargs:
             raise KeyError(f"unknown argument(s): {sorted(kwargs)}")
-        if amp is None:
-            amp = "bf16" if str(config.torch_dtype).replace("torch.", "") in ("float16", "bfloat16") else "f32"
-        if str(amp).replace("torch.", "") in ("f16", "fp16", "float16", "half"):
-            warnings.warn("amp='f16' is served as bfloat16: this engine's 16-bit type (same size and speed, "
-                          "8 bits of mantissa instead of 11)")
-            amp = "bf16"
+        if amp is None:                  # the checkpoint's own type (opt/model.py:38-41, dtypes.py:29-35)
+            amp = {"float16": "f16", "bfloat16": "bf16"}.get(str(config.torch_dtype).replace("torch.", ""), "f32")
         self.amp = amp
         self.dtype = canonical_dtype(amp)
         max_bucket = max(n_positions) if isinstance(n_positions, (list, tuple)) else n_positions
@@ -230,6 +227,7 @@ class OPTForSampling:
             # logits of every position [batch, tokens, vocab] (base.py:716-717); left padding holds zeros
             entries = [StepEntry(rid, t, list(range(len(t)))) for rid, t in zip(self._rows, toks)]
             flat = runner.step(entries).to("cpu", torch.float32)
+            ops.raise_on_device_error()
             out = torch.zeros(B, T, flat.shape[1])
             row = 0
             for b, t in enumerate(toks):
@@ -237,7 +235,9 @@ class OPTForSampling:
                 row += len(t)
             return out
         entries = [StepEntry(rid, t, [len(t) - 1]) for rid, t in zip(self._rows, toks)]
-        return runner.step(entries).to("cpu", torch.float32)
+        logits = runner.step(entries).to("cpu", torch.float32)
+        ops.raise_on_device_error()           # a bounded wait that ran out inside a kernel: the logits are invalid
+        return logits
 
     __call__ = forward
 

@@ -44,6 +44,7 @@ class StepContext:
         self.state_slots = None               # [R] slot of each request (state of fixed size)
         self.block_tables: List[torch.Tensor] = []   # per paged group: [R, blocks]
         self.slot_mapping: List[torch.Tensor] = []   # per paged group: [N] page * page_size + row
+        self.extra = None                     # the caller's own section of the step's buffer (engine/step.py)
         self.host = None                      # the same numbers as Python lists (engine/step.py: HostBatch)
         self.storage = None                   # cache/storage.py: CacheStorage
         self.cache_id = -1                    # set by the model before each mixer runs
@@ -134,3 +135,29 @@ def to_device(t: torch.Tensor, device, dtype=None) -> torch.Tensor:
     if dtype is not None and t.dtype != dtype:
         t = t.to(dtype)
     return t.contiguous().to(device, non_blocking=False)
+
+
+_H16 = (torch.bfloat16, torch.float16)
+_rounded = {"count": 0, "example": None}
+
+
+def weight_to_device(t: torch.Tensor, device, act_dtype, name: str = "") -> torch.Tensor:
+    """A matrix or table goes to the device in the type it is stored in: a 32-bit tensor stays
+    32-bit (it runs on the 32-bit kernels whatever the engine's type), and the 32-bit engine reads
+    a 16-bit tensor of either kind as it is (its kernels widen each element exactly).  Only a
+    16-bit engine that meets the other 16-bit type rounds: once, on the device, and
+    rounding_report() says how many tensors lost bits that way."""
+    d = t.contiguous().to(device, non_blocking=False)
+    if d.dtype in _H16 and act_dtype in _H16 and d.dtype != act_dtype:
+        _rounded["count"] += 1
+        _rounded["example"] = _rounded["example"] or f"{name or 'a tensor'} ({d.dtype} -> {act_dtype})"
+        d = d.to(act_dtype)
+    return d
+
+
+def rounding_report(reset: bool = True):
+    """(number of tensors rounded from one 16-bit type to the other since the last report, one example)."""
+    out = (_rounded["count"], _rounded["example"])
+    if reset:
+        _rounded["count"], _rounded["example"] = 0, None
+    return out

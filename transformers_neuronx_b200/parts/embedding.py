@@ -12,7 +12,7 @@ import torch
 
 from ..kernels import ops
 from ..weights.loader import TensorSpec
-from .base import Part, to_device
+from .base import Part, to_device, weight_to_device
 from .linear import Linear, linear_forward
 from .registry import build_part
 from .spec import EmbeddingSpec, HeadSpec
@@ -43,7 +43,7 @@ class Embedding(Part):
         return out
 
     def load(self, tensors, device, act_dtype):
-        self.table = to_device(tensors[self.spec.table], device)
+        self.table = weight_to_device(tensors[self.spec.table], device, act_dtype, self.spec.table)
         for p in (self.project_in, self.position):
             if p is not None:
                 p.load(tensors, device, act_dtype)
@@ -104,7 +104,7 @@ class Head(Part):
         if shared is not None and s.tied_to in shared and src is tensors.get(s.tied_to):
             self.weight = shared[s.tied_to]
         else:
-            self.weight = to_device(src, device)
+            self.weight = weight_to_device(src, device, act_dtype, s.weight)
         for p in (self.final_norm, self.project_out):
             if p is not None:
                 p.load(tensors, device, act_dtype)

@@ -3,12 +3,11 @@
 (hlo.py:485-501).  The activation and the residual add run in the epilogues of the two products."""
 from __future__ import annotations
 
+from ..kernels.ops import activation_code
 from .base import FeedForward
 from .linear import Linear
 from .registry import register_feed_forward
 from .spec import DenseFeedForwardSpec
-
-_FUSED_ACTIVATIONS = ("relu",)
 
 
 class DenseFeedForward(FeedForward):
@@ -17,8 +16,7 @@ class DenseFeedForward(FeedForward):
 
     def __init__(self, spec: DenseFeedForwardSpec):
         self.spec = spec
-        if spec.activation not in _FUSED_ACTIVATIONS:
-            raise ValueError(f"activation {spec.activation!r} is not built; available: {_FUSED_ACTIVATIONS}")
+        activation_code(spec.activation)          # raises on a name the epilogues do not know
         self.fc1, self.fc2 = Linear(spec.fc1), Linear(spec.fc2)
 
     def tensor_specs(self):
@@ -33,7 +31,7 @@ class DenseFeedForward(FeedForward):
 
     def forward(self, ctx, h, residual):
         a = ctx.scratch(h.shape[0], self.spec.fc1.out_features)
-        self.fc1.forward(h, a, relu=True)
+        self.fc1.forward(h, a, activation=self.spec.activation)
         self.fc2.forward(a, residual, residual=residual)
 
 

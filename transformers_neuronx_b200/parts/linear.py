@@ -1,10 +1,10 @@
 """y = x W^T (+ b), with the epilogues the decoder needs (ReLU; adding into the 32-bit residual
-stream).  W keeps the checkpoint's [out, in] orientation and its stored type: bfloat16 stays
-bfloat16 and a matrix stored in 32-bit stays 32-bit (it then runs on the 32-bit kernel).  The
-bias is applied in 32-bit.
+stream), and the activation that the configuration names.  W keeps the checkpoint's [out, in]
+orientation and its stored type (parts/base.py: weight_to_device): a matrix stored in 32-bit stays
+32-bit (it then runs on the 32-bit kernel).  The bias is applied in 32-bit.
 
-Kernel choice: bfloat16 activations with a bfloat16 matrix go to the tcgen05 tensor-core kernel
-when its size rules hold (the row length in bytes a multiple of 16, for its TMA descriptors);
+Kernel choice: 16-bit activations with a matrix of the same 16-bit type go to the tcgen05 tensor-core
+kernel when its size rules hold (the row length in bytes a multiple of 16, for its TMA descriptors);
 everything else goes to the CUDA-core kernel with 32-bit FMA accumulation.
 """
 from __future__ import annotations
@@ -15,7 +15,7 @@ import torch
 
 from ..kernels import ops
 from ..weights.loader import TensorSpec
-from .base import Part, to_device
+from .base import Part, to_device, weight_to_device
 from .spec import LinearSpec
 
 
@@ -40,7 +40,7 @@ class Linear(Part):
         return out
 
     def load(self, tensors: Dict[str, torch.Tensor], device, act_dtype) -> None:
-        self.set_weight(to_device(tensors[self.spec.weight], device),
+        self.set_weight(weight_to_device(tensors[self.spec.weight], device, act_dtype, self.spec.weight),
                         to_device(tensors[self.spec.bias], device, torch.float32) if self.spec.bias else None)
 
     def set_weight(self, weight: torch.Tensor, bias: Optional[torch.Tensor]) -> None:
@@ -53,16 +53,16 @@ class Linear(Part):
         return n
 
     def forward(self, a: torch.Tensor, out: torch.Tensor, residual: Optional[torch.Tensor] = None,
-                relu: bool = False) -> torch.Tensor:
-        linear_forward(a, self.weight, self.bias, out, residual, relu)
+                activation: Optional[str] = None) -> torch.Tensor:
+        linear_forward(a, self.weight, self.bias, out, residual, activation)
         return out
 
 
-def linear_forward(a, weight, bias, out, residual=None, relu=False):
+def linear_forward(a, weight, bias, out, residual=None, activation=None):
     if ops.gemm_tc_supported(a, weight, out):
-        ops.gemm_tc(a, weight, out, bias=bias, residual=residual, relu=relu)
+        ops.gemm_tc(a, weight, out, bias=bias, residual=residual, activation=activation)
     else:
-        ops.gemm_simt(a, weight, out, bias=bias, residual=residual, relu=relu)
+        ops.gemm_simt(a, weight, out, bias=bias, residual=residual, activation=activation)
 
 
 def fuse_linears(parts: List[Linear], device) -> Linear:

@@ -4,7 +4,7 @@ src/transformers_neuronx/opt/model.py:232-244).  'none': nothing."""
 from __future__ import annotations
 
 from ..weights.loader import TensorSpec
-from .base import PositionEncoding, to_device
+from .base import PositionEncoding, weight_to_device
 from .registry import register_position
 from .spec import PositionSpec
 
@@ -21,7 +21,7 @@ class LearnedPositions(PositionEncoding):
         return [TensorSpec(self.spec.table, (self.spec.rows, self.spec.dim), "table")]
 
     def load(self, tensors, device, act_dtype):
-        self.table = to_device(tensors[self.spec.table], device)
+        self.table = weight_to_device(tensors[self.spec.table], device, act_dtype, self.spec.table)
 
     def parameter_bytes(self):
         return self.table.numel() * self.table.element_size()

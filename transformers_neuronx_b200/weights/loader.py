@@ -7,8 +7,10 @@ through a skeleton of modules (src/transformers_neuronx/module.py:129-279, opt/m
 retries without the ``model.`` prefix (module.py:161-176) and ties lm_head to embed_tokens when
 the file has no lm_head.weight (module.py:142-159).
 
-Dtype policy: bfloat16 stays bfloat16; float16 becomes bfloat16 (this engine's 16-bit type);
-a tensor stored in 32-bit stays 32-bit; integer tables become int32.
+Dtype policy: a tensor keeps the type it is stored in (bfloat16, float16 or 32-bit; the reference's
+three amp types, src/transformers_neuronx/dtypes.py:18-35); integer tables become int32.  What a
+part does with a 16-bit tensor of another kind than the engine's is the part's business
+(parts/base.py: weight_to_device): the 32-bit path widens it exactly.
 """
 from __future__ import annotations
 
@@ -50,10 +52,8 @@ class WeightError(ValueError):
 
 
 def _convert(t: torch.Tensor, name: str, other: List[str]) -> torch.Tensor:
-    if t.dtype == torch.bfloat16 or t.dtype == torch.float32 or t.dtype == torch.int32:
+    if t.dtype in (torch.bfloat16, torch.float16, torch.float32, torch.int32):
         return t
-    if t.dtype == torch.float16:
-        return t.to(torch.bfloat16)
     if t.dtype == torch.float64:
         return t.to(torch.float32)
     if t.dtype in (torch.int64, torch.int16, torch.int8, torch.uint8):

@@ -100,7 +100,7 @@ def save_safetensors(tensors: Dict[str, torch.Tensor], path: str, metadata=None)
         fp.write(struct.pack("<Q", len(blob)))
         fp.write(blob)
         for name in order:
-            t = tensors[name].detach().contiguous().cpu()
+            t = tensors[name].detach().contiguous().cpu().reshape(-1)     # flat: a 0-dimensional tensor has bytes too
             if t.numel():
                 fp.write(t.view(torch.uint8).numpy().tobytes() if t.dtype != torch.bool
                          else t.to(torch.uint8).numpy().tobytes())
