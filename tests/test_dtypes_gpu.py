@@ -8,7 +8,7 @@ import warnings
 import pytest
 import torch
 
-from helpers import TOLERANCE, TinyModel, compare_trace, run_trace_inprocess, storage_for
+from helpers import TOLERANCE, TinyModel, check_greedy, compare_trace, run_trace_inprocess, storage_for
 
 pytestmark = pytest.mark.gpu
 
@@ -97,16 +97,7 @@ def test_float16_through_the_entry_point():
     prompts = [tiny.random_ids(150, seed=s) for s in (1, 2)]
     out = model.sample(torch.tensor(prompts), sequence_length=170, top_k=1)
     for row, prompt in zip(out.tolist(), prompts):
-        seq, compared = list(prompt), 0
-        for t in row[150:]:
-            lg = tiny.plain_logits(seq)[-1]
-            lg[tiny.cfg.eos_token_id] = -float("inf")             # sample() never draws the end-of-sequence token
-            top = torch.topk(lg, 2).values
-            if t != int(lg.argmax()):
-                assert float(top[0] - top[1]) / float(lg[lg > -1e30].abs().max()) <= 2 * TOLERANCE["float16"], compared
-                break
-            seq.append(t); compared += 1
-        assert compared >= 1
+        check_greedy(tiny, "float16", prompt, row[150:], suppress=(tiny.cfg.eos_token_id,))   # sample() never draws that id
     lg = model.forward(torch.tensor(prompts))
     for b in range(2):
         want = tiny.plain_logits(prompts[b])[-1]

@@ -340,7 +340,7 @@ def test_kernel_profile(tiny):
     with kernel_profile() as prof:
         eng.generate([tiny.random_ids(20, seed=1)], 4, stop_on_eos=False)
     t = prof.totals()
-    assert {"embed", "layer_norm", "kv_append", "sample"} <= set(t)
+    assert {"embed", "layer_norm", "kv_append", "sample_packed"} <= set(t)
     assert ("gemm_tc" in t) or ("gemm_simt" in t)
     assert all(ms >= 0 and n > 0 for ms, n in t.values()) and "share" in prof.report()
     from transformers_neuronx_b200.kernels import ops

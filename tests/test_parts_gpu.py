@@ -50,8 +50,9 @@ def test_linear_norm_feed_forward_alone(dtype, tol):
     ff.forward(ctx, h, res)
     want = x.cpu() + P.feed_forward(h.float().cpu(), tf, "", "relu")
     assert rel_err(res, want.to(DEV)) <= tol
-    with pytest.raises(ValueError, match="not built"):
-        build_part("feed_forward", DenseFeedForwardSpec("dense", LinearSpec(H, F, "a", None), LinearSpec(F, H, "b", None), "swish"))
+    from transformers_neuronx_b200.kernels.ops import KernelError
+    with pytest.raises(KernelError, match="not built"):
+        build_part("feed_forward", DenseFeedForwardSpec("dense", LinearSpec(H, F, "a", None), LinearSpec(F, H, "b", None), "solu"))
     with pytest.raises(KeyError, match="registered"):
         build_part("norm", NormSpec("rms_norm_of_tomorrow", H, 1e-5))
 

@@ -49,13 +49,14 @@ def _run(model, prompts):
     p0, p1, p2 = prompts
     outs, where = [], []
     n0 = len(p0) - 3
-    outs.append(runner.step([StepEntry(0, p0[:260], [0, 259]), StepEntry(2, p2[:-4], [])]))
+    # (a step's logits are copied at once: a captured step hands out the same buffer at every replay)
+    outs.append(runner.step([StepEntry(0, p0[:260], [0, 259]), StepEntry(2, p2[:-4], [])]).clone())
     where += [(0, 0), (0, 259)]
     outs.append(runner.step([StepEntry(0, p0[260:n0], [n0 - 261]), StepEntry(1, p1[:-3], [len(p1) - 4]),
-                             StepEntry(2, [p2[-4]], [0])]))
+                             StepEntry(2, [p2[-4]], [0])]).clone())
     where += [(0, n0 - 1), (1, len(p1) - 4), (2, len(p2) - 4)]
     for k in (3, 2, 1):
-        outs.append(runner.step([StepEntry(i, [p[-k]], [0]) for i, p in enumerate(prompts)]))
+        outs.append(runner.step([StepEntry(i, [p[-k]], [0]) for i, p in enumerate(prompts)]).clone())
         where += [(i, len(p) - k) for i, p in enumerate(prompts)]
     return torch.cat([o.float() for o in outs]), where
 

@@ -474,7 +474,8 @@ class StepRunner:
     @torch.no_grad()
     def step(self, entries: Sequence[StepEntry], sampled: Optional[torch.Tensor] = None, extra=None) -> torch.Tensor:
         """Runs one step; returns the 32-bit logits [wanted, vocab] (a device tensor) in the order
-        of the entries and of their `want`.  `sampled` (int32, device): ids sampled in the step
+        of the entries and of their `want`; the tensor is the caller's until the next step (a captured
+        step writes its logits into the same buffer at every replay).  `sampled` (int32, device): ids sampled in the step
         before, for entries with `from_device`.  `extra` (int32 numpy array of at most EXTRA_WORDS
         words per entry): travels to the device in the step's one copy; `self.extra_dev` is its
         device copy afterwards (the engine sends the sampling parameters this way)."""
