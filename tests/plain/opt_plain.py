@@ -1,14 +1,15 @@
 """Plain, slow implementation of the OPT decoder used as the oracle of every test.
 
-It rests on the formulas of aws-neuron/transformers-neuronx alone: that project
-states the model only as an HLO graph for the Neuron compiler (its
-``OPTDecoderLayer`` in ``src/transformers_neuronx/opt/model.py:247-257`` has no
-forward method), so its model code can neither be imported nor compiled on a
-CPU here and no golden logits of it exist.  What of it does run on the CPU (the
-checkpoint writer's tensor names and shapes, the top-k / top-p filter) is pinned
-by tests/golden/ and tests/test_golden.py.  Each function below cites the
-place of its formula, by the file's path within that project
-(``T/`` = ``src/transformers_neuronx/``).
+Each function below is written from a formula of aws-neuron/transformers-neuronx and cites its
+place, by the file's path within that project (``T/`` = ``src/transformers_neuronx/``).  That
+project states the model only as Python that builds an HLO graph for the Neuron compiler (its
+``OPTDecoderLayer`` in ``T/opt/model.py:247-257`` has no forward method), so its model cannot be
+compiled or run as it is here.  Its graph-building code, however, is ordinary Python:
+tests/golden/reference_graph_eager.py runs the reference's own layer, attention, LayerNorm and head
+functions operation by operation on the CPU, and tests/test_golden.py compares this file with the
+logits that came out (a left-padded batch at every prompt position and three decode steps; 2e-5).
+What else of the reference runs on the CPU (the checkpoint writer's tensor names and shapes, the
+top-k / top-p filter) is pinned by the other files of tests/golden/.
 
 Whole sequences, no cache, one function for each part, plain torch on the CPU in
 32-bit (or 64-bit) floats.  It shares no code with the engine: it reads a

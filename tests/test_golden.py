@@ -56,3 +56,36 @@ def test_sampling_kernel_draws_only_what_the_reference_keeps():
             assert drawn <= kept, (c["top_k"], c["top_p"], b, sorted(drawn - kept))
             if len(kept) <= 12:
                 assert drawn == kept                      # every kept token is reachable
+
+
+def test_plain_implementation_computes_what_the_references_own_graph_computes():
+    """tests/golden/opt_reference_logits.json holds logits that the reference's OWN layer code
+    produced (opt/model.py:272-524 with layers/attention.py, layers/transformer.py and hlo.py, run
+    operation by operation on the CPU by tests/golden/reference_graph_eager.py): a left-padded batch of
+    two prompts at every position, then three decode steps through its split prior/active softmax and
+    its cache update.  The plain implementation, given each row without its padding, must agree at
+    every real position: this pins its formulas (LayerNorm, the order of bias and scale, masks, the
+    position offset, the head) to the reference's code rather than to a reading of it."""
+    import sys
+    sys.path.insert(0, GOLDEN)
+    from reference_graph_eager import golden_tokens, golden_weights
+    with open(os.path.join(GOLDEN, "opt_reference_logits.json")) as fp:
+        g = json.load(fp)
+    assert g["tokens"] == golden_tokens(g["config"])
+    w = golden_weights(g["config"])
+    prefill, decode = torch.tensor(g["prefill_logits"]), torch.tensor(g["decode_logits"])
+    T0 = prefill.shape[1]
+    worst = 0.0
+    for b, start in enumerate(g["start_ids"]):
+        ids = g["tokens"][b][start:]
+        mine = P.forward_logits(ids, w, g["config"])
+        theirs = torch.cat([prefill[b, start:], decode[b]])
+        assert mine.shape == theirs.shape
+        err = float((mine - theirs).abs().max() / theirs.abs().max())
+        worst = max(worst, err)
+        assert err <= 2e-5, f"row {b}: the plain implementation and the reference's graph differ by {err:.2e}"
+    # the golden can fail: the same weights without the position offset of 2 are far off
+    w2 = dict(w)
+    w2["model.decoder.embed_positions.weight"] = torch.roll(w["model.decoder.embed_positions.weight"], 1, 0)
+    off = P.forward_logits(g["tokens"][0], w2, g["config"])
+    assert float((off - torch.cat([prefill[0], decode[0]])).abs().max()) > 1e-2
