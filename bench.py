@@ -8,7 +8,12 @@ Prints ONE JSON line.  `value` is decoded tokens per second at batch 8 with the 
 2,048, timed on the device over exactly K decode steps; `e2e` is the same through the Python entry
 point's engine loop (host token ids in through pinned memory, sampled ids out, every step);
 `prefill` is one 2,048-token prompt; `roofline` is the decode step's bytes (every weight once plus
-the live requests' cache) over its time; `points` are decode at batch 1 and 64.
+the live requests' cache) over its time.  `points` holds decode at batch 1 and 64 with their
+roofline fractions, decode at batch 8 with the context ending at 1,024, 1,536 and 2,048 (the metric
+is "1,024-token prompts decoded to 2,048"), the percentiles of the step time over 256 consecutive
+decode steps (the reference reports p0/50/90/95/99/100 of its latencies,
+src/transformers_neuronx/generation_demo.py:157-163), and the two further workloads of the baseline:
+OPT-30B sizes decoding at batch 16, and OPT-13B sizes serving 32 requests with a 512-token budget.
 """
 from __future__ import annotations
 
@@ -27,7 +32,7 @@ sys.path.insert(0, ROOT)
 OPT_6_7B = dict(vocab_size=50272, hidden_size=4096, num_hidden_layers=32, num_attention_heads=32, ffn_dim=16384,
                 max_position_embeddings=2048, word_embed_proj_dim=4096, do_layer_norm_before=True, enable_bias=True,
                 layer_norm_elementwise_affine=True, activation_function="relu", init_std=0.02,
-                architectures=["OPTForCausalLM"], model_type="opt", torch_dtype="bfloat16")
+                architectures=["OPTForCausalLM"], model_type="opt", torch_dtype="float16")
 OPT_13B = dict(OPT_6_7B, hidden_size=5120, num_hidden_layers=40, num_attention_heads=40, ffn_dim=20480, word_embed_proj_dim=5120)
 OPT_30B = dict(OPT_6_7B, hidden_size=7168, num_hidden_layers=48, num_attention_heads=56, ffn_dim=28672, word_embed_proj_dim=7168)
 CONTEXT = 2048
@@ -81,8 +86,13 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def build(n_layers, dtype="bfloat16", base=None):
+DTYPE = "float16"        # OPT's own 16-bit type (the baseline's configurations say fp16); --dtype changes it
+SHORT = {"float16": "fp16", "bfloat16": "bf16"}
+
+
+def build(n_layers, dtype=None, base=None):
     import torch
+    dtype = dtype or DTYPE
     from transformers_neuronx_b200.config import OPTConfig
     from transformers_neuronx_b200.engine import build_model
     from transformers_neuronx_b200.models import opt as opt_arch
@@ -101,7 +111,7 @@ def build(n_layers, dtype="bfloat16", base=None):
         elif s.kind == "norm_bias":
             tensors[s.name] = t
         else:
-            tensors[s.name] = t.to(torch.bfloat16)
+            tensors[s.name] = t.to(getattr(torch, dtype))
     tensors["lm_head.weight"] = tensors["model.decoder.embed_tokens.weight"]
     model = build_model(spec, tensors, dtype, verbose=False)
     return model, cfg
@@ -124,13 +134,15 @@ def prefill_flops(cfg, T):
     return L * per_layer + 2 * V * H
 
 
-def time_decode(model, cfg, batch, steps, warmup, use_engine=False):
-    """K decode steps at `batch`, the context ending at CONTEXT.  Returns (ms_per_step, launches, h2d, d2h)."""
+def time_decode(model, cfg, batch, steps, warmup, use_engine=False, end=None, per_step=None):
+    """K decode steps at `batch`, the context ending at `end` (default CONTEXT).  Returns
+    (ms_per_step, launches, h2d, d2h); per_step (a list) receives every timed step's own time in ms."""
     import torch
     from transformers_neuronx_b200.engine import StepEntry, StepRunner
     from transformers_neuronx_b200.kernels import ops
     total = steps + warmup
-    ctx0 = CONTEXT - total
+    end = end or CONTEXT
+    ctx0 = end - total
     pages = batch * (CONTEXT // 16)
     runner = StepRunner(model, 16, pages, max(batch, 1), CONTEXT, use_cuda_graphs=True)
     g = torch.Generator().manual_seed(1)
@@ -157,13 +169,20 @@ def time_decode(model, cfg, batch, steps, warmup, use_engine=False):
     torch.cuda.synchronize()
     n0 = ops.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)] if per_step is not None else None
     t0 = time.perf_counter()
     e0.record()
     for i in range(warmup, total):
+        if marks:
+            marks[i - warmup].record()
         one(i)
+    if marks:
+        marks[steps].record()
     e1.record()
     torch.cuda.synchronize()
     wall = (time.perf_counter() - t0) * 1e3
+    if marks:
+        per_step.extend(marks[i].elapsed_time(marks[i + 1]) for i in range(steps))
     launches = ops.launch_count() - n0
     ops.raise_on_device_error()
     ms = e0.elapsed_time(e1) / steps
@@ -188,7 +207,7 @@ def time_e2e(model, cfg, batch, steps, warmup):
     from transformers_neuronx_b200.engine import LLMEngine
     total = steps + warmup
     prompt_len = CONTEXT - total - 1
-    eng = LLMEngine(model, EngineConfig(dtype="bfloat16", max_num_seqs=batch, max_batch_tokens=batch * prompt_len,
+    eng = LLMEngine(model, EngineConfig(dtype=DTYPE, max_num_seqs=batch, max_batch_tokens=batch * prompt_len,
                                         max_tokens=batch * CONTEXT, max_model_len=CONTEXT))   # all prompts in one step
     g = torch.Generator().manual_seed(3)
     for b in range(batch):
@@ -235,35 +254,36 @@ def time_prefill(model, cfg, steps, warmup):
     return sorted(times)[len(times) // 2]
 
 
-def extra_workload(name, steps, warmup):
-    """Two further workloads, each printed as one JSON line of its own:
-    decode30b: OPT-30B sizes, batch 16, context ending at 2,048, greedy;
-    mixed13b:  OPT-13B sizes, 32 requests with prompts of 64..1,536 tokens, a budget of 512 tokens a
-               step (one prompt portion beside the decode tokens of the others), 256 new tokens each at
-               temperature 0.7, through LLMEngine.generate (tokens per second of wall clock, prefill
-               included; the same workload has run once before as warm-up)."""
+def workload_decode30b(steps, warmup):
+    """OPT-30B sizes, batch 16, context ending at 2,048, greedy."""
     import torch
-    if name == "decode30b":
-        model, cfg = build(OPT_30B["num_hidden_layers"], base=OPT_30B)
-        ms, launches, _, _ = time_decode(model, cfg, 16, steps, warmup)
-        nbytes = decode_bytes(model, cfg, 16, CONTEXT - steps / 2)
-        hbm, _, src = peaks()
-        print(json.dumps({"workload": name, "value": round(16 / (ms / 1e3), 1), "unit": "tokens/s", "ms_per_step": round(ms, 3),
-                          "batch": 16, "context": CONTEXT, "layers": cfg.num_hidden_layers,
-                          "roofline_frac": round(nbytes / (ms / 1e3) / 1e9 / hbm, 4), "peaks": src}))
-        return 0
+    model, cfg = build(OPT_30B["num_hidden_layers"], base=OPT_30B)
+    ms, _, _, _ = time_decode(model, cfg, 16, steps, warmup)
+    nbytes = decode_bytes(model, cfg, 16, CONTEXT - steps / 2)
+    hbm, _, _ = peaks()
+    out = {"tokens_per_s": round(16 / (ms / 1e3), 1), "ms_per_step": round(ms, 3), "batch": 16, "context": CONTEXT,
+           "layers": cfg.num_hidden_layers, "roofline_frac": round(nbytes / (ms / 1e3) / 1e9 / hbm, 4)}
+    del model
+    torch.cuda.empty_cache()
+    return out
+
+
+def workload_mixed13b():
+    """OPT-13B sizes, 32 requests with prompts of 64..1,536 tokens, a budget of 512 tokens a step (one
+    prompt portion beside the decode tokens of the others), 256 new tokens each at temperature 0.7,
+    through LLMEngine.generate: new tokens per second of wall clock, prefill included; the same
+    workload has run once before as warm-up (kernels loaded, every graph captured)."""
+    import torch
     from transformers_neuronx_b200.config import EngineConfig
     from transformers_neuronx_b200.engine import LLMEngine, SamplingParams
     model, cfg = build(OPT_13B["num_hidden_layers"], base=OPT_13B)
     g = torch.Generator().manual_seed(4)
     lens = torch.randint(64, 1537, (32,), generator=g).tolist()
     prompts = [torch.randint(3, cfg.vocab_size, (n,), generator=g).tolist() for n in lens]
-    # a step's token budget is 512: the decode tokens of the running requests and one prompt portion
-    eng = LLMEngine(model, EngineConfig(dtype="bfloat16", max_num_seqs=32, max_batch_tokens=512,
+    eng = LLMEngine(model, EngineConfig(dtype=DTYPE, max_num_seqs=32, max_batch_tokens=512,
                                         max_tokens=32 * 1792, max_model_len=CONTEXT))
     params = [SamplingParams(temperature=0.7, seed=i) for i in range(32)]
-    for _ in range(max(1, min(warmup, 1))):                               # warm-up: the whole workload once
-        eng.generate(prompts, 256, params, stop_on_eos=False)             # (kernels loaded, every graph captured)
+    eng.generate(prompts, 256, params, stop_on_eos=False)
     torch.cuda.synchronize()
     steps0, pre0 = eng.stats["steps"], eng.stats["preemptions"]
     t0 = time.perf_counter()
@@ -271,11 +291,25 @@ def extra_workload(name, steps, warmup):
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
     n_new = sum(len(o) for o in out)
-    print(json.dumps({"workload": name, "value": round(n_new / dt, 1), "unit": "new tokens/s (wall clock, prefill included)",
-                      "seconds": round(dt, 3), "requests": 32, "prompt_tokens": sum(lens), "new_tokens": n_new,
-                      "steps": eng.stats["steps"] - steps0, "preemptions": eng.stats["preemptions"] - pre0,
-                      "token_budget": 512, "layers": cfg.num_hidden_layers}))
+    res = {"new_tokens_per_s": round(n_new / dt, 1), "seconds": round(dt, 3), "requests": 32, "prompt_tokens": sum(lens),
+           "new_tokens": n_new, "steps": eng.stats["steps"] - steps0, "preemptions": eng.stats["preemptions"] - pre0,
+           "token_budget": 512, "layers": cfg.num_hidden_layers}
+    del eng, model
+    torch.cuda.empty_cache()
+    return res
+
+
+def extra_workload(name, steps, warmup):
+    """One of the further workloads alone, printed as one JSON line of its own."""
+    res = workload_decode30b(steps, warmup) if name == "decode30b" else workload_mixed13b()
+    print(json.dumps(dict({"workload": name}, **res)))
     return 0
+
+
+def percentiles(xs):
+    xs = sorted(xs)
+    pick = lambda q: xs[min(len(xs) - 1, int(round(q / 100 * (len(xs) - 1))))]
+    return {f"p{q}": round(pick(q), 4) for q in (0, 50, 90, 95, 99, 100)}
 
 
 def reference_arm():
@@ -293,7 +327,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=OPT_6_7B["num_hidden_layers"])
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--skip-points", action="store_true", help="leave out everything under `points`")
+    ap.add_argument("--skip-large", action="store_true", help="leave out the OPT-13B and OPT-30B workloads")
+    ap.add_argument("--dtype", default="float16", choices=["float16", "bfloat16"],
+                    help="the serving type (float16 is what OPT checkpoints are stored in)")
     ap.add_argument("--workload", default=None, choices=["decode30b", "mixed13b"],
                     help="run one of the further workloads instead of the default line")
     ap.add_argument("--only", default=None, choices=["decode", "prefill"],
@@ -305,6 +342,8 @@ def main():
         print("bench.py: this engine runs on one GPU; --gpus must be 1")
         return 2
     a.warmup = max(a.warmup, 3)
+    global DTYPE
+    DTYPE = a.dtype
     if a.workload:
         return extra_workload(a.workload, a.steps, a.warmup)
     import torch
@@ -336,11 +375,30 @@ def main():
         for b in (1, 64):
             m, _, _, _ = time_decode(model, cfg, b, a.steps, a.warmup)
             points[f"decode_b{b}"] = round(b / (m / 1e3), 1)
+            points[f"decode_b{b}_frac"] = round(decode_bytes(model, cfg, b, ctx_mean) / (m / 1e3) / 1e9 / hbm_gbs, 4)
+        # the metric is "1,024-token prompts decoded to 2,048": the same batch with the context ending earlier
+        for end in (1024, 1536, 2048):
+            m, _, _, _ = time_decode(model, cfg, a.batch, a.steps, a.warmup, end=end)
+            points[f"decode_b{a.batch}_ctx{end}"] = round(a.batch / (m / 1e3), 1)
+        # every step's own time over 256 consecutive decode steps (contexts 1,792 .. 2,048)
+        per_step = []
+        time_decode(model, cfg, a.batch, 256, a.warmup, per_step=per_step)
+        for k, v in percentiles(per_step).items():
+            points[f"step_ms_{k}"] = v
+    del model
+    torch.cuda.empty_cache()
+    if not a.skip_points and not a.skip_large and a.layers == OPT_6_7B["num_hidden_layers"]:
+        r30 = workload_decode30b(a.steps, a.warmup)
+        points["opt30b_decode_b16"] = r30["tokens_per_s"]
+        points["opt30b_decode_b16_frac"] = r30["roofline_frac"]
+        r13 = workload_mixed13b()
+        points["opt13b_mixed_new_tokens_per_s"] = r13["new_tokens_per_s"]
+        points["opt13b_mixed_steps"] = r13["steps"]
     out = {
         "metric": "decode tokens/s (OPT-6.7B sizes, batch 8, context 2048, 1 B200)",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup,
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic (random weights N(0,0.02), uniform token ids, synthetic cache contents)",
+        "dtype": SHORT[DTYPE], "data": "synthetic (random weights N(0,0.02), uniform token ids, synthetic cache contents)",
         "config": {"model": "OPT-6.7B sizes", "layers": L, "layers_of_model": OPT_6_7B["num_hidden_layers"],
                    "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "head_dim": cfg.head_dim,
                    "ffn_dim": cfg.ffn_dim, "vocab": cfg.vocab_size, "max_positions": cfg.max_position_embeddings,

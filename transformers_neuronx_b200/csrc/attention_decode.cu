@@ -409,9 +409,24 @@ TNX_EXPORT int tnx_attention_decode_noalloc(const void* q, int q_stride, const v
                                             int n_splits, int pages_per_split, cudaStream_t stream) {
     g_noalloc_msg[0] = 0;
     if (n_rows <= 0) return 0;
-    if (n_splits < 1 || n_heads <= 0 || head_dim <= 0) {
-        snprintf(g_noalloc_msg, sizeof g_noalloc_msg, "n_splits, n_heads and head_dim must be positive");
+    // Every refusal leaves its reason, and nothing is queued on the stream before the arguments are
+    // known to be good (the checks are the kernel's own, made here first).
+    if (n_splits < 1 || pages_per_split < 1) {
+        snprintf(g_noalloc_msg, sizeof g_noalloc_msg, "n_splits %d and pages_per_split %d must be positive", n_splits, pages_per_split);
         return TNX_ERR_BAD_ARG;
+    }
+    if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads) {
+        snprintf(g_noalloc_msg, sizeof g_noalloc_msg, "n_heads %d must be a positive multiple of n_kv_heads %d", n_heads, n_kv_heads);
+        return TNX_ERR_BAD_ARG;
+    }
+    if (page_size != PAGE || head_dim % 16 || head_dim < 16 || head_dim > 256) {
+        snprintf(g_noalloc_msg, sizeof g_noalloc_msg, "sizes refused: page_size must be 16 (got %d) and head_dim a multiple of "
+                 "16 from 16 to 256 (got %d)", page_size, head_dim);
+        return TNX_ERR_UNSUPPORTED;
+    }
+    if (q_stride % 8 || (((uintptr_t)q | (uintptr_t)cache) & 15)) {
+        snprintf(g_noalloc_msg, sizeof g_noalloc_msg, "q and cache must be 16-byte aligned and q's row pitch a multiple of 8 elements");
+        return TNX_ERR_UNSUPPORTED;
     }
     const long long floats = tnx_attention_decode_scratch_floats(n_rows, n_heads, head_dim, n_splits);
     const long long counters = (long long)n_rows * n_heads;
@@ -425,7 +440,10 @@ TNX_EXPORT int tnx_attention_decode_noalloc(const void* q, int q_stride, const v
     }
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return (int)e;
+    if (e != cudaSuccess) {
+        snprintf(g_noalloc_msg, sizeof g_noalloc_msg, "cudaGetDevice failed with CUDA error %d", (int)e);
+        return (int)e;
+    }
     if (dev < 0 || dev >= MAX_DEVICES) {
         snprintf(g_noalloc_msg, sizeof g_noalloc_msg, "device index %d is beyond the %d this library tracks", dev, MAX_DEVICES);
         return TNX_ERR_UNSUPPORTED;
@@ -440,13 +458,15 @@ TNX_EXPORT int tnx_attention_decode_noalloc(const void* q, int q_stride, const v
     if (n_splits > 1) {
         // The arrays keep what the last call left; the counters must start at zero.
         e = cudaMemsetAsync(ctrs, 0, (size_t)counters * sizeof(int), stream);
-        if (e != cudaSuccess) return (int)e;
+        if (e != cudaSuccess) {
+            snprintf(g_noalloc_msg, sizeof g_noalloc_msg, "clearing the counters failed with CUDA error %d", (int)e);
+            return (int)e;
+        }
     }
     const int r = tnx_attention_decode(q, q_stride, cache, block_tables, bt_stride, rows, token_request, positions, out,
                                        out_stride, n_rows, n_heads, n_kv_heads, head_dim, page_size, window, scale,
                                        n_splits, pages_per_split, partials, ctrs, stream);
-    if (r == TNX_ERR_UNSUPPORTED)
-        snprintf(g_noalloc_msg, sizeof g_noalloc_msg, "sizes refused: page_size must be 16, head_dim a multiple of 16 "
-                 "up to 256, q rows 16-byte aligned");
+    if (r != 0)
+        snprintf(g_noalloc_msg, sizeof g_noalloc_msg, "the kernel's launch was refused with code %d", r);
     return r;
 }

@@ -16,8 +16,12 @@
 // Limits and rules:
 //   * n_rows * n_heads * n_splits * (head_dim + 2) <= TNX_NOALLOC_MAX_FLOATS and
 //     n_rows * n_heads <= TNX_NOALLOC_MAX_COUNTERS when n_splits > 1; beyond that the call returns
-//     -2 and tnx_attention_decode_noalloc_last_error() says which size was too large.  With
-//     n_splits == 1 no scratch is used and only the kernel's own size rules apply.
+//     -2.  With n_splits == 1 no scratch is used and only the kernel's own size rules apply.  Every
+//     refusal (a size, an alignment, a count that is not positive) leaves its reason in
+//     tnx_attention_decode_noalloc_last_error(), and a refused call queues nothing on the stream.
+//   * n_splits * pages_per_split pages must cover the longest context among the rows: the kernel
+//     reads positions on the device and cannot refuse a plan that is too short; keys beyond the
+//     plan would be left out.
 //   * Every GPU that loads the library holds the arrays (about 4.1 MB) until the process exits.
 //   * The first call on a device looks up the arrays' device addresses (cudaGetSymbolAddress, with
 //     that device current).  Make that first call before any stream capture.
