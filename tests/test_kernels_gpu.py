@@ -269,6 +269,21 @@ class PagedCase:
         self.cache = self.cache.to(DEV)
         self.N = row
 
+    def release_behind(self, window):
+        """What the cache manager does behind a sliding window: pages that no query of a request can
+        read any more (all their keys lie before the first query's window) leave the block table
+        (-1) and their contents are gone (poisoned here, as if another request had taken them)."""
+        bt = self.bt.cpu().clone()
+        gone = []
+        for r, (c, ql) in enumerate(self.lens):
+            first_needed = max(0, c - window + 1) // 16            # the first query sits at position c
+            for b in range(first_needed):
+                gone.append(int(bt[r, b])); bt[r, b] = -1
+        if gone:
+            self.cache[torch.tensor(gone, device=self.cache.device)] = float("nan") if self.dtype != torch.float32 else 7e4
+        self.bt = bt.to(self.bt.device)
+        return len(gone)
+
     def want(self, scale, window):
         outs = []
         for (c, ql), q, k, v in zip(self.lens, self.q, self.k, self.v):
@@ -565,3 +580,46 @@ def test_attention_prefill_tc_more_pages_than_fit_in_shared_memory(d):
                                case.ctx_len, out, n_heads, scale, 0)
     ops().raise_on_device_error()
     assert rel_err(out, case.want(scale, None)) <= 1.5e-2
+
+
+
+@pytest.mark.parametrize("d", [128, 64, 48])
+def test_attention_kernels_with_pages_released_behind_the_window(d):
+    """Behind a sliding window the cache manager gives pages back while a request runs: their block
+    table entries are -1 and their contents belong to someone else.  Every attention kernel must
+    leave them alone: the tcgen05 prefill kernel (which copies whole tiles of four pages and must
+    not wait for bytes of pages it does not copy), the mma.sync prefill kernel, the decode kernel
+    and the 32-bit kernel."""
+    window, n_heads = 45, 2
+    lens = [(200, 130), (100, 1), (64, 70), (333, 1), (50, 3), (16, 40), (47, 1)]
+    scale = 1.0 / math.sqrt(d)
+    o = ops()
+    for kind in ("prefill_tc", "prefill", "decode", "simt"):
+        if kind == "prefill_tc" and d not in (64, 128):
+            continue
+        # (the tcgen05 kernel multiplies unwritten rows of pages that it does hold by zero: those must be finite)
+        case = PagedCase(lens, n_heads, n_heads, d, torch.bfloat16, seed=31 + d,
+                         **({"poison": 3.0e4} if kind == "prefill_tc" else {}))
+        assert case.release_behind(window) >= 20
+        want = case.want(scale, window)
+        out = torch.zeros(case.N, n_heads * d, dtype=torch.bfloat16, device=DEV)
+        multi = torch.ones(case.N, dtype=torch.bool, device=DEV)
+        multi[case.decode_rows.long()] = False
+        if kind == "prefill_tc":
+            o.attention_prefill_tc(case.q_flat, case.cache, case.bt, case.tile_req, case.tile_q0, case.q_start, case.q_len,
+                                   case.ctx_len, out, n_heads, scale, window)
+            rows = multi
+        elif kind == "prefill":
+            o.attention_prefill(case.q_flat, case.cache, case.bt, case.tile_req, case.tile_q0, case.q_start, case.q_len,
+                                case.ctx_len, out, n_heads, scale, window)
+            rows = multi
+        elif kind == "decode":
+            o.attention_decode(case.q_flat, case.cache, case.bt, case.tok_req, case.positions, out, n_heads, scale, window,
+                               rows=case.decode_rows, max_kv_len=400)
+            rows = ~multi
+        else:
+            o.attention_simt(case.q_flat, case.cache, case.bt, case.tok_req, case.positions, out, n_heads, scale, window)
+            rows = torch.ones_like(multi)
+        o.raise_on_device_error()
+        assert torch.isfinite(out.float()).all(), kind
+        assert rel_err(out[rows], want[rows]) <= 1.5e-2, kind

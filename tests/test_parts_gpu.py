@@ -11,6 +11,7 @@ from helpers import TinyModel
 from plain import opt_plain as P
 
 pytestmark = pytest.mark.gpu
+TOL16 = {"bfloat16": 2e-2, "float16": 2.5e-3}
 DEV = "cuda:0"
 
 
@@ -359,3 +360,143 @@ def test_schedule_may_share_a_cache():
     bad = dataclasses.replace(spec, schedule=(ScheduleEntry(0, 0), ScheduleEntry(1, 0)))
     with pytest.raises(ValueError, match="different needs"):
         DecoderModel(bad).cache_needs()
+
+
+@pytest.mark.parametrize("dtype,d", [("bfloat16", 64), ("float16", 128), ("bfloat16", 48)])
+def test_windowed_attention_in_16_bit_with_portions_after_a_release(dtype, d):
+    """A sliding window in the 16-bit engine: head sizes 64 and 128 take the tcgen05 prefill kernel,
+    48 the mma.sync one.  The request is fed in portions, so later portions start after the cache
+    manager has given back the pages behind the window (their block-table entries are -1, and the
+    pages are filled with another request's numbers meanwhile)."""
+    from transformers_neuronx_b200.engine import StepEntry, StepRunner, build_model
+    from transformers_neuronx_b200.parts.spec import (AttentionSpec, DenseFeedForwardSpec, EmbeddingSpec, HeadSpec, LayerSpec,
+                                                      LinearSpec, ModelSpec, NormSpec, PositionSpec, ScheduleEntry)
+    heads, window, V = 2, 40, 211
+    H, F = heads * d, 96
+    g = torch.Generator().manual_seed(17)
+    tdt = torch.bfloat16 if dtype == "bfloat16" else torch.float16
+    rn = lambda *s: (torch.randn(*s, generator=g) / math.sqrt(s[-1])).to(tdt)
+    t = {"emb": torch.randn(V, H, generator=g).to(tdt), "fc1.w": rn(F, H), "fc2.w": rn(H, F)}
+    for n in "qkvo":
+        t[f"att.{n}"] = rn(H, H)
+    t["head"] = t["emb"]
+    norm = lambda: NormSpec("layer_norm", H, 1e-5)
+    att = AttentionSpec("attention", H, heads, heads, d, 1 / math.sqrt(d), q=LinearSpec(H, H, "att.q"), k=LinearSpec(H, H, "att.k"),
+                        v=LinearSpec(H, H, "att.v"), out=LinearSpec(H, H, "att.o"), window=window)
+    ff = DenseFeedForwardSpec("dense", LinearSpec(H, F, "fc1.w"), LinearSpec(F, H, "fc2.w"), "relu")
+    spec = ModelSpec(H, V, 512, EmbeddingSpec("emb", V, H, None, PositionSpec("none")),
+                     (LayerSpec("pre_norm", norm(), att, norm(), ff),), (ScheduleEntry(0, 0),),
+                     HeadSpec("head", V, H, tied_to="emb", final_norm=norm()))
+    model = build_model(spec, t, dtype, verbose=False)
+
+    def plain(ids):
+        w = {k: v.float() for k, v in t.items()}
+        x = w["emb"][torch.tensor(ids)]
+        T = len(ids)
+        h = P.layer_norm(x, None, None)
+        q, k, v = ((h @ w[f"att.{n}"].t()).view(T, heads, d).transpose(0, 1) for n in "qkv")
+        p = P.masked_softmax(P.attention_scores(q, k, d), P.causal_mask(T, T, 0, window)[None])
+        x = x + P.attention_context(p, v).transpose(0, 1).reshape(T, H) @ w["att.o"].t()
+        x = x + torch.relu(P.layer_norm(x, None, None) @ w["fc1.w"].t()) @ w["fc2.w"].t()
+        return P.layer_norm(x, None, None) @ w["emb"].t()
+
+    runner = StepRunner(model, 16, 9, 2, 512, use_cuda_graphs=True)      # nine pages: far fewer than the 300 tokens need
+    ids = torch.randint(0, V, (300,), generator=g).tolist()
+    other = torch.randint(0, V, (60,), generator=g).tolist()
+    want, want_other = plain(ids), plain(other)
+    runner.add_request("w")
+    got, pos = [], 0
+    for step, n in enumerate([70, 50, 33, 2, 1, 1, 47, 1, 64, 17, 1, 1, 12]):
+        entries = [StepEntry("w", ids[pos:pos + n], list(range(n)))]
+        if step == 3:                                          # another request takes (and dirties) the pages given back
+            runner.add_request("x")
+            entries.append(StepEntry("x", other, [len(other) - 1]))
+        lg = runner.step(entries).float().cpu()
+        got.append(lg[:n]); pos += n
+        if step == 3:
+            assert rel_err(lg[n], want_other[-1]) <= TOL16[dtype]
+            runner.finish("x")
+        assert -1 in runner.cache.block_table("w") or pos < 2 * window
+    assert pos == 300
+    assert rel_err(torch.cat(got), want) <= TOL16[dtype]
+    runner.finish("w")
+    runner.cache.check()
+    from transformers_neuronx_b200.kernels import ops
+    ops.raise_on_device_error()
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+@pytest.mark.parametrize("where", [15, 16, 127, 255, 256])
+def test_a_planted_key_is_found_through_portions_and_captured_decode_steps(dtype, where):
+    """With random weights attention is close to uniform over hundreds of keys, and a key dropped at
+    the edge of a page, a tile, a split or a context bucket moves the logits far less than the
+    16-bit tolerance.  Here the weights are made so that one query token (Q) puts nearly all its
+    weight on one key token (M): M sits at `where` (the last row of a page, the first of the next, a
+    tile's edge, the edge of the 256-token context bucket), the prompt goes in as two portions, and
+    the decode steps that follow (eager, captured, replayed, across the bucket change) feed Q again
+    and again.  Every logit is compared with the plain implementation, which would be far off if the
+    key were lost: that is asserted too."""
+    from transformers_neuronx_b200.engine import StepEntry, StepRunner, build_model
+    from transformers_neuronx_b200.parts.spec import (AttentionSpec, DenseFeedForwardSpec, EmbeddingSpec, HeadSpec, LayerSpec,
+                                                      LinearSpec, ModelSpec, NormSpec, PositionSpec, ScheduleEntry)
+    heads, d, V, F = 2, 64, 157, 96
+    H = heads * d
+    M, Q = 5, 6
+    g = torch.Generator().manual_seed(23)
+    tdt = torch.bfloat16 if dtype == "bfloat16" else torch.float16
+    emb = torch.randn(V, H, generator=g) * 0.3
+    emb[M, 0] += 5.0
+    emb[Q, 1] += 5.0
+    wq, wk = torch.randn(H, H, generator=g) / math.sqrt(H), torch.randn(H, H, generator=g) / math.sqrt(H)
+    wq[0, 1] += 4.0                      # head 0, dim 0 of the query reads the Q direction ...
+    wk[0, 0] += 4.0                      # ... and of the key the M direction
+    rn = lambda *s_: (torch.randn(*s_, generator=g) / math.sqrt(s_[-1]))
+    t = {"emb": emb, "att.q": wq, "att.k": wk, "att.v": rn(H, H), "att.o": rn(H, H), "fc1.w": rn(F, H), "fc2.w": rn(H, F)}
+    t = {k: v.to(tdt) for k, v in t.items()}
+    t["head"] = t["emb"]
+    norm = lambda: NormSpec("layer_norm", H, 1e-5)
+    att = AttentionSpec("attention", H, heads, heads, d, 1 / math.sqrt(d), q=LinearSpec(H, H, "att.q"), k=LinearSpec(H, H, "att.k"),
+                        v=LinearSpec(H, H, "att.v"), out=LinearSpec(H, H, "att.o"))
+    ff = DenseFeedForwardSpec("dense", LinearSpec(H, F, "fc1.w"), LinearSpec(F, H, "fc2.w"), "relu")
+    spec = ModelSpec(H, V, 512, EmbeddingSpec("emb", V, H, None, PositionSpec("none")),
+                     (LayerSpec("pre_norm", norm(), att, norm(), ff),), (ScheduleEntry(0, 0),),
+                     HeadSpec("head", V, H, tied_to="emb", final_norm=norm()))
+    model = build_model(spec, t, dtype, verbose=False)
+
+    def plain(ids):
+        w = {k: v.float() for k, v in t.items()}
+        x = w["emb"][torch.tensor(ids)]
+        T = len(ids)
+        h = P.layer_norm(x, None, None)
+        q, k, v = ((h @ w[f"att.{n}"].t()).view(T, heads, d).transpose(0, 1) for n in "qkv")
+        p = P.masked_softmax(P.attention_scores(q, k, d), P.causal_mask(T, T, 0, None)[None])
+        x = x + P.attention_context(p, v).transpose(0, 1).reshape(T, H) @ w["att.o"].t()
+        x = x + torch.relu(P.layer_norm(x, None, None) @ w["fc1.w"].t()) @ w["fc2.w"].t()
+        return P.layer_norm(x, None, None) @ w["emb"].t(), p
+
+    ids = torch.randint(7, V, (275,), generator=g).tolist()
+    ids[where] = M
+    q_places = [249] + list(range(251, 275, 3))                  # the last prompt token and every third decode token
+    for i in q_places:
+        ids[i] = Q
+    want, probs = plain(ids)
+    assert all(float(probs[0, i, where]) > 0.9 for i in q_places if i > where), "the plant must dominate head 0"
+    lost = list(ids); lost[where] = 9
+    gone, _ = plain(lost)
+    assert min(rel_err(gone[i], want[i]) for i in q_places if i > where) > 0.1, "losing the key must show"
+
+    runner = StepRunner(model, 16, 20, 1, 512, use_cuda_graphs=True)
+    runner.add_request("r")
+    got = [runner.step([StepEntry("r", ids[:100], [99])]).float().cpu(),
+           runner.step([StepEntry("r", ids[100:250], [149])]).float().cpu()]
+    for i in range(250, 275):
+        got.append(runner.step([StepEntry("r", [ids[i]], [0])]).float().cpu())
+    got = torch.cat(got)
+    places = [99, 249] + list(range(250, 275))
+    assert len(runner.captured_steps()) >= 2, "decode steps below and beyond 256 tokens of context are graphs of their own"
+    for row, i in enumerate(places):
+        assert rel_err(got[row], want[i]) <= TOL16[dtype], (i, rel_err(got[row], want[i]))
+        if i in q_places:
+            assert int(got[row].argmax()) == int(want[i].argmax()), i
+    from transformers_neuronx_b200.kernels import ops
+    ops.raise_on_device_error()

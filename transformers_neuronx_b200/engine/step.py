@@ -12,6 +12,7 @@ device once, run the model.
 from __future__ import annotations
 
 import gc
+import warnings
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence
 
@@ -63,6 +64,13 @@ class StepRunner:
         self.last_h2d_bytes = 0
         # decode-only steps can be replayed as CUDA graphs, one per (batch bucket, context bucket)
         self.use_cuda_graphs = bool(use_cuda_graphs) and getattr(model, "graph_safe", True)
+        # Parts that do not declare themselves graph_safe keep the whole model out of CUDA graphs: say so
+        # once, by name, instead of losing the graphs silently.
+        self.graph_blockers = sorted({type(p).__name__ for p in getattr(model, "all_parts", lambda: [])()
+                                      if not getattr(p, "graph_safe", False)})
+        if use_cuda_graphs and self.graph_blockers:
+            warnings.warn("steps of this model are not captured in CUDA graphs: " + ", ".join(self.graph_blockers) +
+                          " do(es) not declare graph_safe (parts/base.py)")
         self.max_graph_batch = max_graph_batch
         self.max_graphs = max_graphs              # shapes kept as graphs (each holds its buffers)
         self._graphs = {}
