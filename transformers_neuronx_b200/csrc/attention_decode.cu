@@ -5,7 +5,7 @@
 //   s_j = scale * <q, k_j>  (32-bit),  out = sum_j exp(s_j - max) v_j / sum_j exp(s_j - max)
 //
 // Grid (heads, rows, splits): a CTA takes one (row, head) and one contiguous range of pages; its
-// four warps take pages of the range in turn and keep an online softmax each (half a page at a
+// four, eight or sixteen warps take pages of the range in turn and keep an online softmax each (half a page at a
 // time, the next half's loads in flight meanwhile).  A lane owns eight
 // consecutive dims of the head (one 16-byte load per key) of some of the keys of a page, so a page
 // of 16 keys x head_dim is read with fully used 16-byte loads.  The warps' states are merged in
@@ -21,7 +21,6 @@
 
 namespace {
 
-constexpr int WARPS = 4;
 constexpr int PAGE = 16;
 
 struct DecodeParams {
@@ -45,7 +44,7 @@ struct DecodeParams {
 };
 
 // LPK lanes share one key (each 8 dims); KPL = 32 / LPK keys are read per warp-wide load.
-template <int LPK>
+template <int LPK, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_decode_kernel(const DecodeParams p) {
     constexpr int KPL = 32 / LPK;
@@ -324,7 +323,7 @@ TNX_EXPORT int tnx_attention_decode_append(const void* q, int q_stride, void* ca
                                            void* out, int out_stride, int n_rows, int n_heads, int n_kv_heads, int head_dim,
                                            int page_size, int window, float scale, int n_splits, int pages_per_split,
                                            float* scratch, int* counters, const void* k_new, const void* v_new,
-                                           int kv_stride, cudaStream_t stream) {
+                                           int kv_stride, int warps, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (page_size != PAGE || head_dim % 16 || head_dim < 16 || head_dim > 256 || n_kv_heads <= 0 ||
         n_heads % n_kv_heads || q_stride % 8 || ((uintptr_t)q & 15) || ((uintptr_t)cache & 15))
@@ -342,12 +341,31 @@ TNX_EXPORT int tnx_attention_decode_append(const void* q, int q_stride, void* ca
     p.k_new = (const h16*)k_new; p.v_new = (const h16*)v_new; p.kv_stride = kv_stride; p.cache_w = (h16*)cache;
     dim3 grid(n_heads, n_rows, n_splits);
     const int chunks = head_dim / 8;
-    const dim3 block(WARPS * 32);
-    if (chunks <= 2) return tnx_launch_pdl(attention_decode_kernel<2>, grid, block, 0, stream, p);
-    if (chunks <= 4) return tnx_launch_pdl(attention_decode_kernel<4>, grid, block, 0, stream, p);
-    if (chunks <= 8) return tnx_launch_pdl(attention_decode_kernel<8>, grid, block, 0, stream, p);
-    if (chunks <= 16) return tnx_launch_pdl(attention_decode_kernel<16>, grid, block, 0, stream, p);
-    return tnx_launch_pdl(attention_decode_kernel<32>, grid, block, 0, stream, p);
+    // Eight (or sixteen) warps a block where that puts every (row, head) on the GPU at once with few
+    // or no splits (batch 8 of 32 heads: 256 blocks of eight warps and no merge through scratch memory
+    // at all: 49 us against 53 with four warps and two splits); four warps otherwise.  The caller's plan
+    // says which.
+    if (warps != 4 && warps != 8 && warps != 16) return TNX_ERR_BAD_ARG;
+    if (warps == 16 && chunks > 16) return TNX_ERR_UNSUPPORTED;      // sixteen warps of the widest heads would spill
+    const dim3 block(warps * 32);
+    if (warps == 16) {
+        if (chunks <= 2) return tnx_launch_pdl(attention_decode_kernel<2, 16>, grid, block, 0, stream, p);
+        if (chunks <= 4) return tnx_launch_pdl(attention_decode_kernel<4, 16>, grid, block, 0, stream, p);
+        if (chunks <= 8) return tnx_launch_pdl(attention_decode_kernel<8, 16>, grid, block, 0, stream, p);
+        return tnx_launch_pdl(attention_decode_kernel<16, 16>, grid, block, 0, stream, p);
+    }
+    if (warps == 8) {
+        if (chunks <= 2) return tnx_launch_pdl(attention_decode_kernel<2, 8>, grid, block, 0, stream, p);
+        if (chunks <= 4) return tnx_launch_pdl(attention_decode_kernel<4, 8>, grid, block, 0, stream, p);
+        if (chunks <= 8) return tnx_launch_pdl(attention_decode_kernel<8, 8>, grid, block, 0, stream, p);
+        if (chunks <= 16) return tnx_launch_pdl(attention_decode_kernel<16, 8>, grid, block, 0, stream, p);
+        return tnx_launch_pdl(attention_decode_kernel<32, 8>, grid, block, 0, stream, p);
+    }
+    if (chunks <= 2) return tnx_launch_pdl(attention_decode_kernel<2, 4>, grid, block, 0, stream, p);
+    if (chunks <= 4) return tnx_launch_pdl(attention_decode_kernel<4, 4>, grid, block, 0, stream, p);
+    if (chunks <= 8) return tnx_launch_pdl(attention_decode_kernel<8, 4>, grid, block, 0, stream, p);
+    if (chunks <= 16) return tnx_launch_pdl(attention_decode_kernel<16, 4>, grid, block, 0, stream, p);
+    return tnx_launch_pdl(attention_decode_kernel<32, 4>, grid, block, 0, stream, p);
 }
 
 TNX_EXPORT int tnx_attention_decode(const void* q, int q_stride, const void* cache, const int* block_tables,
@@ -357,7 +375,7 @@ TNX_EXPORT int tnx_attention_decode(const void* q, int q_stride, const void* cac
                                     float* scratch, int* counters, cudaStream_t stream) {
     return tnx_attention_decode_append(q, q_stride, const_cast<void*>(cache), block_tables, bt_stride, rows, token_request,
                                        positions, out, out_stride, n_rows, n_heads, n_kv_heads, head_dim, page_size, window,
-                                       scale, n_splits, pages_per_split, scratch, counters, nullptr, nullptr, 0, stream);
+                                       scale, n_splits, pages_per_split, scratch, counters, nullptr, nullptr, 0, 4, stream);
 }
 
 // ---------------------------------------------------------------------------------------------------

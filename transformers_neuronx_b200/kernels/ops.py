@@ -479,11 +479,12 @@ def gemm_tc(a, w, out, bias=None, residual=None, activation=None, splits=None, f
 
 
 def attention_decode(q, cache, block_tables, token_request, positions, out, n_heads, scale, window=0, rows=None,
-                     n_rows=None, max_kv_len=None, n_splits=None, new_kv=None):
+                     n_rows=None, max_kv_len=None, n_splits=None, new_kv=None, warps=None):
     """One query token per row over the paged 16-bit cache.  `rows` (int32) names the rows of q
     that are decode tokens (None: all); max_kv_len bounds their contexts (for the split plan).
     new_kv = (k, v), [rows of q, kv_heads * head_dim] bfloat16: the keys and values of the rows' own
-    tokens, which the kernel then writes into their pages itself (no kv_append before it)."""
+    tokens, which the kernel then writes into their pages itself (no kv_append before it).
+    n_splits (with warps, 4 or 8 a block) forces a plan: a test hook."""
     lib = _lib("attention_decode", cache, q, out)
     _need(cache, "cache", _H16, 5)
     N, width, q_stride = _rows_2d(q, "q")
@@ -499,16 +500,29 @@ def attention_decode(q, cache, block_tables, token_request, positions, out, n_he
     R = int(n_rows) if n_rows is not None else (rows.shape[0] if rows is not None else N)
     st = _state(q.device)
     max_pages = max(1, -(-(int(max_kv_len) if max_kv_len is not None else block_tables.shape[1] * ps) // ps))
+    forced_warps, warps = warps, 4
     if n_splits is None:
-        # Splits in powers of two, as many as keep all CTAs on the GPU at once (four of them fit on an
-        # SM) with at least eight pages each; every split gets a multiple of four pages, one round of
-        # the CTA's four warps.  (Measured at 1 to 64 rows: other counts leave warps or SMs idle.)
-        n_splits = 1
-        while n_splits < 32 and R * n_heads * n_splits * 2 <= 4 * st["sms"] and n_splits * 2 <= max_pages // 8:
-            n_splits *= 2
+        # Measured at 1 to 64 rows of 32 heads (contexts of 2,040): the fastest plan has about two blocks
+        # of eight warps per SM with as few splits as that takes (8, 4, 2, 1 splits at 1, 2, 4, 8 rows:
+        # 13.4 / 18.6 / 30.6 / 49.3 us, where four warps took 14.7 / 19.2 / 30.5 / 53.0); with more
+        # (row, head) pairs than that, four warps and no split while four blocks per SM hold them all
+        # (16 rows: 91.5 us), eight warps beyond (64 rows: 324 us).  A split has at least eight pages and
+        # a whole number of rounds of the block's warps.
+        pairs = R * n_heads
+        if st["sms"] < 2 * pairs <= 2 * st["sms"] and d <= 128:
+            warps, n_splits = 16, 1        # one block of sixteen warps per SM and no split: 4 rows 28.9 us (eight warps, two splits: 30.8)
+        elif pairs <= 2 * st["sms"]:
+            warps, n_splits = 8, 1
+            while n_splits < 32 and pairs * n_splits * 2 <= 2 * st["sms"] and n_splits * 2 <= max_pages // 8:
+                n_splits *= 2
+        elif pairs <= 4 * st["sms"]:
+            warps, n_splits = 4, 1
+        else:
+            warps, n_splits = 8, 1
         pps = -(-max_pages // n_splits)
-        pps = -(-pps // 4) * 4
-    else:
+        pps = -(-pps // warps) * warps
+    else:                                                  # a test's own plan (warps: 4, 8 or 16 a block)
+        warps = int(forced_warps or 4)
         n_splits = max(1, min(int(n_splits), max_pages))
         pps = -(-max_pages // n_splits)
     n_splits = -(-max_pages // pps)
@@ -533,7 +547,7 @@ def attention_decode(q, cache, block_tables, token_request, positions, out, n_he
         _p(rows), _p(token_request), _p(positions), _p(out), c_int(out_stride), c_int(R),
         c_int(n_heads), c_int(n_kv), c_int(d), c_int(ps), c_int(window or 0), c_float(scale),
         c_int(n_splits), c_int(pps), _p(scratch), _p(st.get("att_counters")), _p(k_new), _p(v_new), c_int(kv_stride),
-        _stream()), "attention_decode")
+        c_int(warps), _stream()), "attention_decode")
 
 
 ATTN_PREFILL_TILE = 128      # query rows of one work item of the prefill attention kernel
