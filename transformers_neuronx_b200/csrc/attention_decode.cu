@@ -57,25 +57,31 @@ attention_decode_kernel(const DecodeParams p) {
 
     const int h = blockIdx.x, ri = blockIdx.y, split = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // The loads a block needs before its first page are a chain (row -> request -> block table -> page);
+    // what does not depend on the link before it is asked for at once.
     const int row = p.rows ? p.rows[ri] : ri;
     if (row < 0) return;                                        // a padded entry of the row list of a captured step
     const int req = p.token_request[row];
-    if (req < 0) return;                                        // a padded row of a captured batch
     const int pos = p.positions[row];
-    const int kv_len = pos + 1;
-    const int first_key = (p.window > 0 && kv_len > p.window) ? kv_len - p.window : 0;
     const int d = p.head_dim;
-    const int kvh = h / (p.n_heads / p.n_kv_heads);
     const int sub = lane % LPK;                                  // which 8 dims
     const int kgrp = lane / LPK;                                 // which key of a load
     const bool dim_ok = sub * 8 < d;
+    const uint4 q_raw = dim_ok ? *(const uint4*)(p.q + (size_t)row * p.q_stride + (size_t)h * d + sub * 8) : make_uint4(0, 0, 0, 0);
+    if (req < 0) return;                                        // a padded row of a captured batch
+    const int kv_len = pos + 1;
+    const int first_key = (p.window > 0 && kv_len > p.window) ? kv_len - p.window : 0;
+    const int kvh = h / (p.n_heads / p.n_kv_heads);
     const int* bt = p.block_tables + (size_t)req * p.bt_stride;
 
     float q[8];
     {
-        const h16* qrow = p.q + (size_t)row * p.q_stride + (size_t)h * d + sub * 8;
+        const h16x2* qq = (const h16x2*)&q_raw;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) q[i] = dim_ok ? h16_to_float(qrow[i]) * p.scale : 0.f;
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = h16x2_to_float2(qq[i]);
+            q[2 * i] = f.x * p.scale; q[2 * i + 1] = f.y * p.scale;
+        }
     }
     float m = -INFINITY, l = 0.f, acc[8];
 #pragma unroll
@@ -90,18 +96,6 @@ attention_decode_kernel(const DecodeParams p) {
     // value come from k_new / v_new.
     const bool own_here = p.k_new != nullptr && (pos / PAGE) / p.pages_per_split == split;    // one answer for the CTA
     const int cached_len = p.k_new != nullptr ? pos : kv_len;
-    if (own_here) {
-        // for later steps: CTAs of heads that share a key/value head write the same bytes
-        const int page = bt[pos / PAGE];
-        const int pieces = d / 8;
-        for (int i = threadIdx.x; i < 2 * pieces; i += WARPS * 32) {
-            const int which = i / pieces, piece = i - which * pieces;
-            const h16* src = (which ? p.v_new : p.k_new) + (size_t)row * p.kv_stride + (size_t)kvh * d;
-            h16* dst = p.cache_w + (((size_t)page * 2 + which) * p.n_kv_heads + kvh) * head_block + (size_t)(pos % PAGE) * d;
-            ((uint4*)dst)[piece] = ((const uint4*)src)[piece];
-        }
-    }
-
     // The warp's pages (page_lo + warp, + WARPS, ...) are taken in chunks of CH warp-wide loads of
     // keys and as many of values: half a page, or a whole one where a page is a single load.  The
     // loads of the next chunk are issued before the current one is used, so that the warp always
@@ -180,6 +174,19 @@ attention_decode_kernel(const DecodeParams p) {
             consume(t, k0, v0);
             if (t + 2 < n_chunks) issue(t + 2, k0, v0);
             if (t + 1 < n_chunks) consume(t + 1, k1, v1);
+        }
+    }
+    if (own_here) {
+        // The token's own key and value go into their page for later steps (CTAs of heads that share a
+        // key/value head write the same bytes).  This comes after the pages have been streamed, so that
+        // its loads do not stand between the block's start and its first page.
+        const int page = bt[pos / PAGE];
+        const int pieces = d / 8;
+        for (int i = threadIdx.x; i < 2 * pieces; i += WARPS * 32) {
+            const int which = i / pieces, piece = i - which * pieces;
+            const h16* src = (which ? p.v_new : p.k_new) + (size_t)row * p.kv_stride + (size_t)kvh * d;
+            h16* dst = p.cache_w + (((size_t)page * 2 + which) * p.n_kv_heads + kvh) * head_block + (size_t)(pos % PAGE) * d;
+            ((uint4*)dst)[piece] = ((const uint4*)src)[piece];
         }
     }
     if (own_here && warp == 0) {
