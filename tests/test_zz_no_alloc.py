@@ -70,7 +70,7 @@ def test_matches_the_allocating_entry_point_twice_in_a_row(n_splits):
 
 
 def test_a_row_list_with_a_padded_entry():
-    """Rows named by a list, one entry of which is -1 (the padding of a captured batch): only the
+    """Rows named by a list, one entry of which is -1 (the padding of a batch of fixed size): only the
     named rows are written."""
     lib = _lib()
     scale = 1.0 / math.sqrt(64)

@@ -24,10 +24,9 @@
 //     plan would be left out.
 //   * Every GPU that loads the library holds the arrays (about 4.1 MB) until the process exits.
 //   * The first call on a device looks up the arrays' device addresses (cudaGetSymbolAddress, with
-//     that device current).  Make that first call before any stream capture.
-//   * All calls share the arrays: two calls that overlap on the GPU (different streams, or the same
-//     call replayed concurrently) race on them.  Calls on one stream are safe; the counters are
-//     cleared at the start of every call.
+//     that device current).
+//   * All calls share the arrays: two calls that overlap on the GPU (on different streams) race on
+//     them.  Calls on one stream are safe; the counters are cleared at the start of every call.
 //   * Arguments are those of tnx_attention_decode without the scratch and counter pointers.
 #pragma once
 #include <cuda_runtime.h>
