@@ -173,6 +173,83 @@ def test_gemm_tc_split_k_in_clusters(M, N, K, splits):
     assert torch.equal(out1, out3)
 
 
+@pytest.mark.parametrize("M,N,K", [(300, 1000, 7168), (129, 520, 1160), (640, 2100, 4104), (257, 9000, 512)])
+def test_gemm_tc_every_many_token_kernel(M, N, K):
+    """Each kernel that the plan for more than 128 tokens can choose, imposed in turn on sizes that fill
+    no tile: the same product, bias, activation and residual from all of them."""
+    o = ops()
+    g = torch.Generator(device="cpu").manual_seed(M + N)
+    a = torch.randn(M, K, generator=g).bfloat16().to(DEV)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).bfloat16().to(DEV)
+    bias = torch.randn(N, generator=g).to(DEV)
+    res0 = torch.randn(M, N, generator=g).to(DEV)
+    want = a.float() @ w.float().t() + bias
+    ran = []
+    try:
+        for plan in o.GEMM_PLANS:
+            o.gemm_tc_force_plan(plan)
+            out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+            try:
+                o.gemm_tc(a, w, out, bias=bias, activation="relu")
+            except o.KernelError:
+                continue                                    # the sizes do not allow this plan
+            res = res0.clone()
+            o.gemm_tc(a, w, res, bias=bias, residual=res)
+            o.raise_on_device_error()
+            assert rel_err(out, torch.relu(want)) <= 5e-3, plan
+            assert rel_err(res, want + res0) <= 2e-5, plan
+            ran.append(plan)
+    finally:
+        o.gemm_tc_force_plan(None)
+    assert {"tiles_128", "pairs", "persistent"} <= set(ran), ran
+
+
+def test_gemm_tc_plan_is_near_the_best_kernel():
+    """The estimates that choose a kernel for more than 128 tokens were fitted on some layer sizes; here
+    they are held against the fastest of all kernels at others (the 30B model's K of 7,168 and 28,672,
+    a vocabulary-sized N), every call on cold caches."""
+    o = ops()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
+
+    def timed(a, w, out, reps=5):
+        ts = []
+        for _ in range(reps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            o.gemm_tc(a, w, out)
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return sorted(ts)[len(ts) // 2]
+
+    worst = []
+    try:
+        for (M, N, K) in [(384, 21504, 7168), (512, 21504, 7168), (1024, 7168, 7168), (192, 28672, 7168),
+                          (640, 28672, 7168), (256, 7168, 28672), (1280, 7168, 28672), (384, 50272, 4096)]:
+            a = torch.randn(M, K, device=DEV).bfloat16()
+            w = (torch.randn(N, K, device=DEV) * 0.02).bfloat16()
+            out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+            o.gemm_tc_force_plan(None)
+            o.gemm_tc(a, w, out)
+            chosen = timed(a, w, out)
+            best = {}
+            for plan in o.GEMM_PLANS:
+                o.gemm_tc_force_plan(plan)
+                try:
+                    o.gemm_tc(a, w, out)
+                except o.KernelError:
+                    continue
+                best[plan] = timed(a, w, out)
+            o.raise_on_device_error()
+            name = min(best, key=best.get)
+            worst.append((chosen / best[name], (M, N, K), name))
+    finally:
+        o.gemm_tc_force_plan(None)
+    ratio, shape, name = max(worst)
+    assert ratio <= 1.2, f"{shape}: the chosen kernel takes {ratio:.2f} times as long as {name}"
+
+
 def test_gemm_tc_finds_a_planted_column():
     """One large entry far along K and in the last rows of the last tile: a kernel that drops the
     tail of K, a tile edge or a swizzled chunk misses it."""

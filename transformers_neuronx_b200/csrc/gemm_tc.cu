@@ -1111,10 +1111,32 @@ static int few_tokens_max() { return FEW_TOKENS_MAX; }
 TNX_EXPORT int tnx_gemm_tc_few_tokens() { return few_tokens_max(); }
 
 struct ManyTokensPlan { int kind; int pairs; int sk_tiles; int sk_pairs; int splits; };   // kind 0: 128 x 128 tiles, 1: CTA pairs, 2: persistent, 3: 128 x 256 tiles with K split in clusters
+// A plan imposed from outside (-1: the estimates below choose).  0: 128 x 128 tiles; 1: CTA pairs, whole
+// tiles; 2: persistent 128 x 256 tiles; 4: CTA pairs with the last wave shared out by K blocks; 31, 32,
+// 34, 38: 128 x 256 tiles with K split 1, 2, 4, 8 ways in clusters.  It exists so that a test can time
+// every kernel that could run a product and hold the estimates' choice against the best of them.
+static int g_forced_plan = -1;
+TNX_EXPORT void tnx_gemm_tc_force_plan(int plan) { g_forced_plan = plan; }
+
 static ManyTokensPlan plan_many_tokens(int M, int N, int K, int sms) {
     ManyTokensPlan r{2, 0, 0, 0, 1};
     const int kb = (K + BLOCK_K - 1) / BLOCK_K;
     const int tiles_m = (M + TILE_P - 1) / TILE_P;
+    if (g_forced_plan >= 0) {
+        const int G = sms / 2, n_tiles = ((M + 255) / 256) * ((N + 255) / 256), rest = n_tiles % G;
+        const int sk_pairs = rest * 4 < G ? rest * 4 : G;
+        const int tiles_p = tiles_m * ((N + 255) / 256);
+        r.kind = -1;                                                // refused unless the sizes allow the plan
+        if (g_forced_plan == 0 || g_forced_plan == 2) r.kind = g_forced_plan;
+        else if (g_forced_plan == 1) { r.kind = 1; r.pairs = n_tiles < G ? n_tiles : G; }
+        else if (g_forced_plan == 4 && rest > 0 && (long long)rest * kb >= 4LL * sk_pairs) {
+            r.kind = 1; r.pairs = G; r.sk_tiles = rest; r.sk_pairs = sk_pairs;
+        } else if (g_forced_plan > 30 && g_forced_plan <= 30 + MAX_CLUSTER) {
+            const int sp = g_forced_plan - 30;
+            if ((sp & (sp - 1)) == 0 && tiles_p * sp <= sms && (sp == 1 || sp * 4 <= kb)) { r.kind = 3; r.splits = sp; }
+        }
+        return r;
+    }
     // Estimated times in microseconds, from measurements at 256..2,048 tokens: a K block of a
     // 256 x 256 pair tile takes 0.45 us, of a 128 x 128 single tile 0.38 us; start and drain 8 / 6 us.
     const float t_single = (float)((tiles_m * ((N + 127) / 128) + sms - 1) / sms) * kb * 0.38f + 6.f;
@@ -1131,14 +1153,18 @@ static ManyTokensPlan plan_many_tokens(int M, int N, int K, int sms) {
     // A margin of 1.3 on these costs; every pair must get at least four K blocks.
     int sk_pairs = rest * 4 < G ? rest * 4 : G;
     float t_share = 1e30f;
-    // Measured at 384..1,536 tokens on the layer products of the 6.7B and 13B sizes: sharing out pays where
-    // every shared tile is cut into exactly four runs (a pair then holds part of one tile only: 6-44 %
-    // faster), and with a long K (256 blocks and more) after a wave of whole tiles, or without one down to
-    // 1.6 pairs per tile (8-38 %); elsewhere, with runs that straddle two tiles, it lost 6-34 % against whole
-    // tiles in one more wave.
+    // Measured at 129..2,048 tokens over the layer products of the 6.7B, 13B and 30B sizes and a
+    // vocabulary-sized N: sharing out pays where every shared tile is cut into exactly four runs (a pair
+    // then holds part of one tile only: 5-32 % faster behind a whole wave, and without one when K is long).
+    // With runs that straddle two tiles it pays while the last wave holds at most 0.55 tiles per pair and
+    // K is 256 blocks or more (10-35 %; up to 0.75 tiles per pair behind a whole wave), or 100 blocks or
+    // more behind a whole wave, 80 behind two (3-16 %); with a fuller last wave or a shorter K it lost
+    // 5-40 % against whole tiles in one more wave.
     const bool four_runs = rest * 4 <= G;
-    const bool long_k = kb >= 256 && (full > 0 || sk_pairs * 10 >= rest * 16);
-    if (rest > 0 && (long long)rest * kb >= 4LL * sk_pairs && (four_runs || long_k)) {
+    const bool sparse_rest = rest * 100 <= G * 55;
+    const bool long_k = kb >= 256 && (full > 0 ? rest * 100 <= G * 75 : sparse_rest);
+    const bool behind_waves = sparse_rest && ((full >= 1 && kb >= 100) || (full >= 2 && kb >= 80));
+    if (rest > 0 && (long long)rest * kb >= 4LL * sk_pairs && (four_runs || long_k || behind_waves)) {
         const float reduce = ((float)sk_pairs / rest + 1.f) * 2.8f;
         const float exposed = full > 0 ? (reduce > t_tile ? reduce - t_tile : 0.f) : reduce;
         t_share = ((float)full + (float)rest / sk_pairs) * t_tile + 8.f + 1.3f * ((sk_pairs + rest) * 0.1f + exposed);
@@ -1160,7 +1186,8 @@ static ManyTokensPlan plan_many_tokens(int M, int N, int K, int sms) {
             if (sp >= 4) { r.kind = 3; r.splits = sp; return r; }
         }
         const bool single = tiles_p * 4 < sms * 3;
-        const float t_here = single ? t_single : (float)((tiles_p + sms - 1) / sms) * kb * 0.45f + 8.f;
+        // In as many waves the persistent kernel is 5-8 % slower than the pairs (measured), so it must win outright.
+        const float t_here = single ? t_single : (float)((tiles_p + sms - 1) / sms) * kb * 0.45f * 1.05f + 8.f;
         if (t_here <= t_pair && t_here <= t_share) { r.kind = single ? 0 : 2; return r; }
     } else {
         // 256 tokens and more: where the 128 x 256 tiles fit the GPU in one wave they can split K 1, 2, 4 or
@@ -1175,9 +1202,14 @@ static ManyTokensPlan plan_many_tokens(int M, int N, int K, int sms) {
             const float t = (float)((kb + sp - 1) / sp) * 0.45f + 8.f + (sp > 1 ? 2.f + (float)sp : 0.f);
             if (t < t_split) { t_split = t; best_sp = sp; }
         }
-        const float t_other = fminf(t_single, fminf(t_pair, t_share));
+        // The persistent kernel's 128 x 256 tiles waste less of a last token tile than the pairs' 256 rows
+        // (320 tokens: three tiles of 128 against two of 256): where that saves a wave it is 15-25 % faster
+        // (measured at 320, 384 and 640 tokens), in as many waves 3-7 % slower.
+        const float t_persistent = (float)((tiles_p + sms - 1) / sms) * kb * 0.45f * 1.05f + 8.f;
+        const float t_other = fminf(fminf(t_single, t_persistent), fminf(t_pair, t_share));
         if (best_sp > 0 && t_split * 1.1f < t_other) { r.kind = 3; r.splits = best_sp; return r; }
-        if (t_single <= t_pair && t_single <= t_share) { r.kind = 0; return r; }
+        if (t_single <= t_pair && t_single <= t_share && t_single <= t_persistent) { r.kind = 0; return r; }
+        if (t_persistent < t_pair && t_persistent < t_share) { r.kind = 2; return r; }
     }
     r.kind = 1;
     if (t_share < t_pair) { r.pairs = G; r.sk_tiles = rest; r.sk_pairs = sk_pairs; }
@@ -1238,6 +1270,7 @@ TNX_EXPORT int tnx_gemm_tc(const void* A, const void* W, const float* bias, cons
         }
         const int tiles_m = (M + TILE_P - 1) / TILE_P, tiles_n = (N + PBN - 1) / PBN;
         ManyTokensPlan mt = plan_many_tokens(M, N, K, sms);
+        if (mt.kind < 0) return TNX_ERR_UNSUPPORTED;
         if (mt.kind == 0) {
             if (!make_map(&mq, W, N, K, ldw, 128)) return TNX_ERR_UNSUPPORTED;
             dim3 grid((M + TILE_P - 1) / TILE_P, (N + 127) / 128, 1);

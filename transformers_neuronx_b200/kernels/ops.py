@@ -478,6 +478,19 @@ def gemm_tc(a, w, out, bias=None, residual=None, activation=None, splits=None, f
                            n_splits, _p(scratch), _p(st["counters"]), _p(st["err"]), _stream()), "gemm_tc")
 
 
+GEMM_PLANS = {"tiles_128": 0, "pairs": 1, "persistent": 2, "pairs_shared": 4,
+              "split_1": 31, "split_2": 32, "split_4": 34, "split_8": 38}
+
+
+def gemm_tc_force_plan(plan=None, dtype=torch.bfloat16) -> None:
+    """Imposes one kernel on every tensor-core product of more than 128 tokens (None: the library's
+    own estimates choose again).  A product whose sizes do not allow the plan is refused.  For the
+    test that times every candidate against the estimates' choice; not for serving."""
+    lib = _build.load("gemm_tc", dtype)
+    lib.tnx_gemm_tc_force_plan(c_int(-1 if plan is None else GEMM_PLANS[plan]))
+    _gemm_plans.clear()
+
+
 def attention_decode(q, cache, block_tables, token_request, positions, out, n_heads, scale, window=0, rows=None,
                      n_rows=None, max_kv_len=None, n_splits=None, new_kv=None, warps=None):
     """One query token per row over the paged 16-bit cache.  `rows` (int32) names the rows of q
