@@ -149,6 +149,62 @@ def test_sharded_index(tmp_path):
     assert torch.equal(out["model.a.bias"], b["model.a.bias"])
 
 
+def test_the_reference_s_torch_saved_layouts(tmp_path):
+    """The folders that the reference itself writes and reads besides safetensors
+    (src/transformers_neuronx/module.py:30-50 writer, :434-460 reader): a directory pytorch_model.bin/
+    with one torch-saved tensor per file and key_to_filename.json, one pytorch_model.bin state dict,
+    and shards with pytorch_model.bin.index.json.  The files are laid out here as that writer lays them
+    out ('p<index>.<key>'); the model's tensors come back the same from each, the tied head included."""
+    m = TinyModel("B", seed=4)
+    specs = DecoderModel(opt_arch.build_spec(m.cfg)).tensor_specs()
+    want = load_tensors(m.folder, specs)
+    stored = {k: v for k, v in m.plain_tensors.items()}
+    config = open(os.path.join(m.folder, "config.json")).read()
+
+    def check(folder):
+        got = load_tensors(str(folder), specs)
+        assert sorted(got) == sorted(want)
+        for k in want:
+            assert got[k].dtype == want[k].dtype and torch.equal(got[k], want[k]), k
+        assert got["lm_head.weight"] is got["model.decoder.embed_tokens.weight"]
+
+    split = tmp_path / "split"
+    (split / "pytorch_model.bin").mkdir(parents=True)
+    (split / "config.json").write_text(config)
+    names = {k: f"p{i}.{k}" for i, k in enumerate(stored)}
+    (split / "pytorch_model.bin" / "key_to_filename.json").write_text(json.dumps(names, indent=2))
+    for k, t in stored.items():
+        torch.save(t, str(split / "pytorch_model.bin" / names[k]))
+    check(split)
+
+    single = tmp_path / "single"
+    single.mkdir()
+    (single / "config.json").write_text(config)
+    torch.save(stored, str(single / "pytorch_model.bin"))
+    check(single)
+
+    shards = tmp_path / "shards"
+    shards.mkdir()
+    (shards / "config.json").write_text(config)
+    keys = list(stored)
+    parts = {"pytorch_model-00001-of-00002.bin": keys[: len(keys) // 2], "pytorch_model-00002-of-00002.bin": keys[len(keys) // 2:]}
+    for fn, ks in parts.items():
+        torch.save({k: stored[k] for k in ks}, str(shards / fn))
+    (shards / "pytorch_model.bin.index.json").write_text(json.dumps(
+        {"metadata": {}, "weight_map": {k: fn for fn, ks in parts.items() for k in ks}}))
+    check(shards)
+
+    # one error that lists everything, as for safetensors
+    os.remove(str(split / "pytorch_model.bin" / names[keys[3]]))
+    del names[keys[3]]
+    names["stray.weight"] = "p999.stray.weight"
+    torch.save(torch.zeros(2), str(split / "pytorch_model.bin" / "p999.stray.weight"))
+    (split / "pytorch_model.bin" / "key_to_filename.json").write_text(json.dumps(names))
+    with pytest.raises(WeightError) as ei:
+        load_tensors(str(split), specs)
+    assert keys[3] in ei.value.missing and "stray.weight" in ei.value.unexpected
+
+
 def test_compiled_kernels_can_be_kept_in_a_folder(tmp_path):
     """export_libraries / import_libraries (model.save / model.load): libraries carry the digest of
     their source in their names; a file of another version or of another origin is not taken."""

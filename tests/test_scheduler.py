@@ -84,6 +84,36 @@ def test_finish_frees_everything():
     assert s.running == [] and all(r.finished for r in done)
 
 
+def test_max_time_ends_a_request_after_a_token():
+    """The reference's MaxTimeCriteria (stopping_criteria.py:15-33) is asked after every token whether the
+    time is up: a request whose time has passed still gets the token of the step that was running."""
+    cache, s = make(num_pages=16)
+    a = Request("a", [1, 2, 3], 50, max_time=10.0)
+    b = Request("b", [1, 2, 3], 50)
+    s.add(a); s.add(b)
+    t0 = a.started
+    plan = s.schedule()
+    for it in plan.items:
+        cache.append(it.request.rid, it.count)
+    assert s.commit(plan, {"a": 7, "b": 7}, now=t0 + 1.0) == []
+    plan = s.schedule()
+    for it in plan.items:
+        cache.append(it.request.rid, it.count)
+    done = s.commit(plan, {"a": 7, "b": 7}, now=t0 + 11.0)
+    assert [r.rid for r in done] == ["a"] and a.finish_reason == "time" and a.output == [7, 7]
+    assert not b.finished and cache.slots.num_free == 3
+    cache.check()
+
+
+def test_finish_reasons():
+    cache, s = make(num_pages=16)
+    a, b = Request("a", [1, 2, 3], 2, eos_token_id=2), Request("b", [1, 2, 3], 9, eos_token_id=2)
+    s.add(a); s.add(b)
+    run_step(cache, s)
+    run_step(cache, s, next_token=lambda r: 2 if r.rid == "b" else 7)
+    assert (a.finish_reason, b.finish_reason) == ("length", "eos")
+
+
 def test_eos_ignored_when_asked():
     cache, s = make()
     s.add(Request("a", [1, 2, 3], 4, stop_on_eos=False, eos_token_id=2))

@@ -44,12 +44,14 @@ class LLMEngine:
         self.stats = {"steps": 0, "tokens_run": 0, "tokens_sampled": 0, "preemptions": 0}
 
     def add_request(self, prompt: Sequence[int], max_new_tokens: int, params: Optional[SamplingParams] = None,
-                    rid: Optional[Hashable] = None, stop_on_eos: bool = True, eos_token_id=None) -> Hashable:
+                    rid: Optional[Hashable] = None, stop_on_eos: bool = True, eos_token_id=None,
+                    max_time: Optional[float] = None) -> Hashable:
         rid = next(self._ids) if rid is None else rid
         if rid in self.requests and not self.requests[rid].finished:
             raise ValueError(f"request {rid!r} is still running")
         req = Request(rid, [int(t) for t in prompt], int(max_new_tokens), params or SamplingParams(),
-                      stop_on_eos=stop_on_eos, eos_token_id=self.eos_token_id if eos_token_id is None else eos_token_id)
+                      stop_on_eos=stop_on_eos, eos_token_id=self.eos_token_id if eos_token_id is None else eos_token_id,
+                      max_time=max_time)
         if req.params.suppress_eos and len(req.eos_ids()) > MAX_SUPPRESSED:
             raise ValueError(f"request {rid!r}: suppress_eos takes at most {MAX_SUPPRESSED} end-of-sequence ids, "
                              f"got {len(req.eos_ids())}")
@@ -162,6 +164,7 @@ class LLMEngine:
                 if req.stop_on_eos and req.is_eos(tok):
                     del req.output[place + 1:]
                     del req._all[len(req.prompt) + place + 1:]
+                    req.finish_reason = "eos"
                     if not req.finished:
                         req.finished = True
                         if req in self.scheduler.running:

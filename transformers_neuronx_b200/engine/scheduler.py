@@ -14,13 +14,16 @@ and continuous batching is left to an external server (base.py:492-587).  The de
   preempt the most recently admitted running request: everything it holds is given back and it
   returns to the head of the waiting queue with the tokens it has so far, to be computed again
   later.  Prompt portions are simply cut to the pages that are free (or wait).
-* finish: the requested number of new tokens is reached, or the end-of-sequence token was
-  produced and the request stops on it; its pages and slot are given back at once.
+* finish: the requested number of new tokens is reached, the end-of-sequence token was
+  produced and the request stops on it, or the request's ``max_time`` has passed (checked after a
+  token, stopping_criteria.py:15-33); its pages and slot are given back at once, and
+  ``finish_reason`` says which.
 
 The scheduler only decides; it takes pages through the cache manager when the step is prepared.
 """
 from __future__ import annotations
 
+import time
 from collections import deque
 from dataclasses import dataclass, field
 from typing import Deque, Dict, Hashable, List, Optional
@@ -47,7 +50,10 @@ class Request:
     params: SamplingParams = field(default_factory=SamplingParams)
     stop_on_eos: bool = True
     eos_token_id: Optional[object] = None      # one id, or several (any of them ends the request)
+    max_time: Optional[float] = None           # seconds after `started` beyond which no further token is asked for
+    started: float = field(default_factory=time.monotonic)
     # progress
+    finish_reason: Optional[str] = None        # "length", "eos" or "time" once finished
     output: List[int] = field(default_factory=list)
     computed: int = 0               # tokens of prompt+output whose keys/values are in the cache
     finished: bool = False
@@ -249,10 +255,14 @@ class Scheduler:
         return plan
 
     # ---- after the step ------------------------------------------------------------------------------
-    def commit(self, plan: StepPlan, sampled: Dict[Hashable, int]) -> List[Request]:
+    def commit(self, plan: StepPlan, sampled: Dict[Hashable, int], now: Optional[float] = None) -> List[Request]:
         """Records the step's progress and the sampled tokens; returns the requests that finished
-        (their pages and slots are already given back)."""
+        (their pages and slots are already given back).  A request with `max_time` ends with the
+        first token sampled after that many seconds, as the reference's MaxTimeCriteria ends a
+        generation (src/transformers_neuronx/stopping_criteria.py:15-33): the check comes after a
+        token, so at least one is produced."""
         done = []
+        now = time.monotonic() if now is None else now
         for it in plan.items:
             req = it.request
             req.computed = it.start + it.count
@@ -261,8 +271,10 @@ class Scheduler:
             tok = int(sampled[req.rid])
             req.append_output(tok)
             hit_eos = req.stop_on_eos and req.is_eos(tok)
-            if len(req.output) >= req.max_new_tokens or hit_eos:
+            timed_out = req.max_time is not None and now - req.started > req.max_time
+            if len(req.output) >= req.max_new_tokens or hit_eos or timed_out:
                 req.finished = True
+                req.finish_reason = "eos" if hit_eos else ("length" if len(req.output) >= req.max_new_tokens else "time")
                 self.running.remove(req)
                 self.cache.free_request(req.rid)
                 done.append(req)

@@ -19,7 +19,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
-from .safetensors_io import open_model_files
+from .model_files import open_model_files
 
 
 @dataclass(frozen=True)

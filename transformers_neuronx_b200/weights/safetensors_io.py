@@ -105,18 +105,3 @@ def save_safetensors(tensors: Dict[str, torch.Tensor], path: str, metadata=None)
                 fp.write(t.view(torch.uint8).numpy().tobytes() if t.dtype != torch.bool
                          else t.to(torch.uint8).numpy().tobytes())
     os.replace(tmp, path)
-
-
-def open_model_files(folder: str):
-    """The safetensors file(s) of a model folder: model.safetensors, or the shards named by
-    model.safetensors.index.json (the reference reads both, module.py:199-216, :434-460)."""
-    single = os.path.join(folder, "model.safetensors")
-    index = os.path.join(folder, "model.safetensors.index.json")
-    if os.path.isfile(single):
-        return [SafetensorsFile(single)]
-    if os.path.isfile(index):
-        with open(index) as fp:
-            names = sorted(set(json.load(fp)["weight_map"].values()))
-        return [SafetensorsFile(os.path.join(folder, n)) for n in names]
-    raise FileNotFoundError(
-        f"no model.safetensors or model.safetensors.index.json in {folder!r}")
