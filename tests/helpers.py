@@ -43,7 +43,13 @@ CONFIG_E = dict(vocab_size=1501, hidden_size=192, num_hidden_layers=2, num_atten
                 max_position_embeddings=420, word_embed_proj_dim=96, do_layer_norm_before=False, enable_bias=True,
                 layer_norm_elementwise_affine=True, layer_norm_eps=1e-5, activation_function="relu", init_std=0.03,
                 architectures=["OPTForCausalLM"], model_type="opt")
-CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C, "D": CONFIG_D, "E": CONFIG_E}
+# Head size 80 (OPT-2.7B's: 2,560 / 32): the tcgen05 attention kernel's layout of 128 with a partly filled
+# second slice; the decode kernel's lanes that own no dims.
+CONFIG_F = dict(vocab_size=777, hidden_size=240, num_hidden_layers=2, num_attention_heads=3, ffn_dim=328,
+                max_position_embeddings=400, word_embed_proj_dim=240, do_layer_norm_before=True, enable_bias=True,
+                layer_norm_elementwise_affine=True, layer_norm_eps=1e-5, activation_function="relu", init_std=0.03,
+                architectures=["OPTForCausalLM"], model_type="opt")
+CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C, "D": CONFIG_D, "E": CONFIG_E, "F": CONFIG_F}
 
 # Largest allowed |engine - plain| as a fraction of the largest |plain logit| of the compared rows.
 # float32: both sides compute in 32-bit and differ by the order of additions only.

@@ -368,7 +368,8 @@ class PagedCase:
         return torch.cat(outs).to(DEV)
 
 
-ATT_SHAPES = [(4, 4, 16), (3, 3, 32), (6, 2, 48), (8, 8, 64), (5, 1, 80), (4, 2, 128), (2, 2, 256)]
+ATT_SHAPES = [(4, 4, 16), (3, 3, 32), (6, 2, 48), (8, 8, 64), (5, 1, 80), (4, 4, 96), (3, 3, 112), (4, 2, 128), (2, 1, 160),
+              (2, 2, 192), (2, 2, 256)]
 
 
 @pytest.mark.parametrize("n_heads,n_kv,d", ATT_SHAPES)
@@ -400,7 +401,8 @@ def test_attention_decode(n_heads, n_kv, d, window, n_splits, warps):
         assert rel_err(out, case.want(scale, window)) <= 1e-2
 
 
-@pytest.mark.parametrize("n_heads,n_kv,d", [(4, 4, 128), (6, 2, 64), (3, 1, 80), (2, 2, 256)])
+@pytest.mark.parametrize("n_heads,n_kv,d", [(4, 4, 128), (6, 2, 64), (3, 1, 80), (2, 2, 256), (2, 2, 48), (4, 2, 96), (2, 1, 160),
+                                            (2, 2, 192), (3, 3, 112)])
 @pytest.mark.parametrize("n_splits,warps", [(1, 4), (3, 4), (1, 8), (3, 8), (None, None)])
 def test_attention_decode_appends_the_new_token(n_heads, n_kv, d, n_splits, warps):
     """The decode kernel writes the token's own key and value into its page and reads them back: the
@@ -628,9 +630,10 @@ def test_sampling_large_vocabulary_top_k():
 
 @pytest.mark.parametrize("n_heads,n_kv", [(4, 2), (3, 3), (8, 1)])
 @pytest.mark.parametrize("window", [None, 45, 200])
-@pytest.mark.parametrize("d", [128, 64])
+@pytest.mark.parametrize("d", [128, 64, 80, 96, 112])
 def test_attention_prefill_tc(n_heads, n_kv, window, d):
-    """The tcgen05 prefill kernel (head sizes 128 and 64).  Unwritten rows of pages hold a large finite
+    """The tcgen05 prefill kernel (head sizes 64 to 128 in steps of 16; those between use the layout of 128
+    with a partly filled second slice).  Unwritten rows of pages hold a large finite
     number: they are loaded with their page and must be weighted by exactly zero."""
     lens = [(0, 2), (0, 64), (0, 129), (30, 7), (64, 130), (15, 17), (200, 300), (5, 1), (1000, 260)]
     case = PagedCase(lens, n_heads, n_kv, d, torch.bfloat16, seed=77, poison=3.0e4)
@@ -648,7 +651,7 @@ def test_attention_prefill_tc(n_heads, n_kv, window, d):
     assert float(out[~keep].float().abs().max()) == 0.0
 
 
-@pytest.mark.parametrize("d", [128, 64])
+@pytest.mark.parametrize("d", [128, 64, 80])
 def test_attention_prefill_tc_more_pages_than_fit_in_shared_memory(d):
     """A context of more than 2,048 keys: the page numbers beyond the first 128 are read from global memory."""
     n_heads = 2
@@ -662,7 +665,7 @@ def test_attention_prefill_tc_more_pages_than_fit_in_shared_memory(d):
 
 
 
-@pytest.mark.parametrize("d", [128, 64, 48])
+@pytest.mark.parametrize("d", [128, 64, 48, 96])
 def test_attention_kernels_with_pages_released_behind_the_window(d):
     """Behind a sliding window the cache manager gives pages back while a request runs: their block
     table entries are -1 and their contents belong to someone else.  Every attention kernel must
@@ -674,7 +677,7 @@ def test_attention_kernels_with_pages_released_behind_the_window(d):
     scale = 1.0 / math.sqrt(d)
     o = ops()
     for kind in ("prefill_tc", "prefill", "decode", "simt"):
-        if kind == "prefill_tc" and d not in (64, 128):
+        if kind == "prefill_tc" and d not in (64, 80, 96, 112, 128):
             continue
         # (the tcgen05 kernel multiplies unwritten rows of pages that it does hold by zero: those must be finite)
         case = PagedCase(lens, n_heads, n_heads, d, torch.bfloat16, seed=31 + d,

@@ -164,6 +164,17 @@ def test_head_size_64(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+def test_head_size_80(dtype):
+    """Configuration F: head size 80, which is neither of the tcgen05 attention kernel's native sizes
+    (it runs in the layout of 128 with the columns beyond 80 left out of the products)."""
+    tiny = _model("F", dtype, 29)
+    reqs = {f"f{i}": tiny.random_ids(n, seed=700 + i) for i, n in enumerate([390, 130, 257, 66, 200])}
+    steps, peak = mixed_steps(reqs, chunk_sizes=(130, 2, 64, 17, 150), decode_tail=9, max_live=3)
+    res = run_trace_inprocess(tiny.folder, dtype, steps, peak)
+    compare_trace(tiny, reqs, steps, res, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_decode_steps_where_not_every_request_wants_logits(dtype):
     """Single-token steps (replayed as CUDA graphs) in which some entries ask for nothing."""
     tiny = _model("A", dtype, 17)

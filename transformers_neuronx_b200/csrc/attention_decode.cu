@@ -43,14 +43,19 @@ struct DecodeParams {
     h16* cache_w;
 };
 
-// LPK lanes share one key (each 8 dims); KPL = 32 / LPK keys are read per warp-wide load.
-template <int LPK, int WARPS>
+// LPK lanes share one key; each of them owns E pieces of 8 dims of the head (piece e * LPK + its place
+// among the LPK lanes, so that one warp-wide 16-byte load reads LPK * 16 consecutive bytes of every
+// key).  KPL = 32 / LPK keys are read per warp-wide load.  E = 1 serves the head sizes whose number of
+// 8-dim pieces is a power of two (and, with idle lanes, any other); E = 3 gives head sizes like 96
+// (4 x 3 pieces) a layout without idle lanes.
+template <int LPK, int E, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_decode_kernel(const DecodeParams p) {
     constexpr int KPL = 32 / LPK;
-    constexpr int LOADS = PAGE / KPL;          // warp-wide loads per page (LPK = 32: 16, LPK = 2: 1)
+    constexpr int GROUPS = PAGE / KPL;         // key groups (of KPL keys) per page
+    constexpr int LOADS = GROUPS * E;          // warp-wide loads per page and tensor (LPK = 32: 16, LPK = 2, E = 1: 1)
     __shared__ float sm_m[WARPS], sm_l[WARPS];
-    __shared__ float sm_acc[WARPS][LPK * 8];
+    __shared__ float sm_acc[WARPS][LPK * E * 8];
     __shared__ int last_flag;
     pdl_launch_dependents();
     pdl_wait();
@@ -64,28 +69,34 @@ attention_decode_kernel(const DecodeParams p) {
     const int req = p.token_request[row];
     const int pos = p.positions[row];
     const int d = p.head_dim;
-    const int sub = lane % LPK;                                  // which 8 dims
+    const int sub = lane % LPK;                                  // which 8 dims (of each of its E pieces)
     const int kgrp = lane / LPK;                                 // which key of a load
-    const bool dim_ok = sub * 8 < d;
-    const uint4 q_raw = dim_ok ? *(const uint4*)(p.q + (size_t)row * p.q_stride + (size_t)h * d + sub * 8) : make_uint4(0, 0, 0, 0);
+    const bool dim_ok = E > 1 || sub * 8 < d;                    // with E > 1 the head size is exactly LPK * E * 8
+    uint4 q_raw[E];
+#pragma unroll
+    for (int e = 0; e < E; ++e)
+        q_raw[e] = dim_ok ? *(const uint4*)(p.q + (size_t)row * p.q_stride + (size_t)h * d + (e * LPK + sub) * 8) : make_uint4(0, 0, 0, 0);
     if (req < 0) return;                                        // a padded row of a captured batch
     const int kv_len = pos + 1;
     const int first_key = (p.window > 0 && kv_len > p.window) ? kv_len - p.window : 0;
     const int kvh = h / (p.n_heads / p.n_kv_heads);
     const int* bt = p.block_tables + (size_t)req * p.bt_stride;
 
-    float q[8];
-    {
-        const h16x2* qq = (const h16x2*)&q_raw;
+    float q[E][8];
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+        const h16x2* qq = (const h16x2*)&q_raw[e];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const float2 f = h16x2_to_float2(qq[i]);
-            q[2 * i] = f.x * p.scale; q[2 * i + 1] = f.y * p.scale;
+            q[e][2 * i] = f.x * p.scale; q[e][2 * i + 1] = f.y * p.scale;
         }
     }
-    float m = -INFINITY, l = 0.f, acc[8];
+    float m = -INFINITY, l = 0.f, acc[E][8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    for (int e = 0; e < E; ++e)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[e][i] = 0.f;
 
     const int n_pages = (kv_len + PAGE - 1) / PAGE;
     const int page_lo = max(split * p.pages_per_split, first_key / PAGE);
@@ -96,12 +107,14 @@ attention_decode_kernel(const DecodeParams p) {
     // value come from k_new / v_new.
     const bool own_here = p.k_new != nullptr && (pos / PAGE) / p.pages_per_split == split;    // one answer for the CTA
     const int cached_len = p.k_new != nullptr ? pos : kv_len;
-    // The warp's pages (page_lo + warp, + WARPS, ...) are taken in chunks of CH warp-wide loads of
-    // keys and as many of values: half a page, or a whole one where a page is a single load.  The
-    // loads of the next chunk are issued before the current one is used, so that the warp always
-    // has loads in flight; each chunk does its own step of the online softmax.
-    constexpr int CH = LOADS >= 2 ? LOADS / 2 : 1;           // loads per chunk
-    constexpr int CPP = LOADS / CH;                          // chunks per page
+    // The warp's pages (page_lo + warp, + WARPS, ...) are taken in chunks of CG key groups, i.e. CH = CG * E
+    // warp-wide loads of keys and as many of values: half a page of the widest heads, a whole page
+    // up to head size 64, one key group where a lane owns several pieces.  The loads of the next
+    // chunk are issued before the current one is used, so that the warp always has loads in flight
+    // (the same number of bytes whatever the head size); each chunk does its own step of the online softmax.
+    constexpr int CG = E > 1 ? 1 : (GROUPS >= 8 ? GROUPS / 2 : GROUPS);   // key groups per chunk
+    constexpr int CH = CG * E;                                // loads per chunk
+    constexpr int CPP = GROUPS / CG;                          // chunks per page
     const int my_pages = page_hi > page_lo + warp ? (page_hi - page_lo - warp + WARPS - 1) / WARPS : 0;
     const int n_chunks = my_pages * CPP;
     auto issue = [&](int t, uint4 (&kb)[CH], uint4 (&vb)[CH]) {
@@ -109,38 +122,47 @@ attention_decode_kernel(const DecodeParams p) {
         const int page = bt[pg];
         const h16* kbase = p.cache + (((size_t)page * 2 + 0) * p.n_kv_heads + kvh) * head_block;
         const h16* vbase = p.cache + (((size_t)page * 2 + 1) * p.n_kv_heads + kvh) * head_block;
-        const int i0 = (t % CPP) * CH;
+        const int g0 = (t % CPP) * CG;
 #pragma unroll
-        for (int i = 0; i < CH; ++i) {
-            const int key = (i0 + i) * KPL + kgrp;
-            kb[i] = dim_ok ? __ldg((const uint4*)(kbase + (size_t)key * d + sub * 8)) : make_uint4(0, 0, 0, 0);
-        }
+        for (int g = 0; g < CG; ++g)
 #pragma unroll
-        for (int i = 0; i < CH; ++i) {
-            const int key = (i0 + i) * KPL + kgrp;
-            vb[i] = dim_ok ? __ldg((const uint4*)(vbase + (size_t)key * d + sub * 8)) : make_uint4(0, 0, 0, 0);
-        }
+            for (int e = 0; e < E; ++e) {
+                const int key = (g0 + g) * KPL + kgrp;
+                kb[g * E + e] = dim_ok ? __ldg((const uint4*)(kbase + (size_t)key * d + (e * LPK + sub) * 8)) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+        for (int g = 0; g < CG; ++g)
+#pragma unroll
+            for (int e = 0; e < E; ++e) {
+                const int key = (g0 + g) * KPL + kgrp;
+                vb[g * E + e] = dim_ok ? __ldg((const uint4*)(vbase + (size_t)key * d + (e * LPK + sub) * 8)) : make_uint4(0, 0, 0, 0);
+            }
     };
     auto consume = [&](int t, uint4 (&kb)[CH], uint4 (&vb)[CH]) {
         const int pg = page_lo + warp + (t / CPP) * WARPS;
-        const int i0 = (t % CPP) * CH;
-        float s[CH];
+        const int g0 = (t % CPP) * CG;
+        float s[CG];
         float chunk_max = -INFINITY;
 #pragma unroll
-        for (int i = 0; i < CH; ++i) {
-            const h16x2* kk = (const h16x2*)&kb[i];
+        for (int g = 0; g < CG; ++g) {
             float dot = 0.f;
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const float2 f = h16x2_to_float2(kk[u]);
-                dot = fmaf(q[2 * u], f.x, dot);
-                dot = fmaf(q[2 * u + 1], f.y, dot);
+            for (int e = 0; e < E; ++e) {                        // one chain of multiply-adds per piece, not one for all
+                const h16x2* kk = (const h16x2*)&kb[g * E + e];
+                float de = 0.f;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const float2 f = h16x2_to_float2(kk[u]);
+                    de = fmaf(q[e][2 * u], f.x, de);
+                    de = fmaf(q[e][2 * u + 1], f.y, de);
+                }
+                dot += de;
             }
 #pragma unroll
             for (int o = LPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-            const int j = pg * PAGE + (i0 + i) * KPL + kgrp;
-            s[i] = (j >= first_key && j < cached_len) ? dot : -INFINITY;
-            chunk_max = fmaxf(chunk_max, s[i]);
+            const int j = pg * PAGE + (g0 + g) * KPL + kgrp;
+            s[g] = (j >= first_key && j < cached_len) ? dot : -INFINITY;
+            chunk_max = fmaxf(chunk_max, s[g]);
         }
 #pragma unroll
         for (int o = 16; o >= LPK; o >>= 1) chunk_max = fmaxf(chunk_max, __shfl_xor_sync(0xffffffffu, chunk_max, o));
@@ -149,20 +171,25 @@ attention_decode_kernel(const DecodeParams p) {
         const float corr = (m == -INFINITY) ? 0.f : __expf(m - m_new);
         l *= corr;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] *= corr;
+        for (int e = 0; e < E; ++e)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[e][i] *= corr;
         m = m_new;
 #pragma unroll
-        for (int i = 0; i < CH; ++i) {
-            const bool live = s[i] != -INFINITY;
-            const float pj = live ? __expf(s[i] - m) : 0.f;
+        for (int g = 0; g < CG; ++g) {
+            const bool live = s[g] != -INFINITY;
+            const float pj = live ? __expf(s[g] - m) : 0.f;
             l += pj;
-            if (!live) vb[i] = make_uint4(0, 0, 0, 0);            // rows never written may hold anything, NaN included
-            const h16x2* vv = (const h16x2*)&vb[i];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const float2 f = h16x2_to_float2(vv[u]);
-                acc[2 * u] = fmaf(pj, f.x, acc[2 * u]);
-                acc[2 * u + 1] = fmaf(pj, f.y, acc[2 * u + 1]);
+            for (int e = 0; e < E; ++e) {
+                if (!live) vb[g * E + e] = make_uint4(0, 0, 0, 0);   // rows never written may hold anything, NaN included
+                const h16x2* vv = (const h16x2*)&vb[g * E + e];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const float2 f = h16x2_to_float2(vv[u]);
+                    acc[e][2 * u] = fmaf(pj, f.x, acc[e][2 * u]);
+                    acc[e][2 * u + 1] = fmaf(pj, f.y, acc[e][2 * u + 1]);
+                }
             }
         }
     };
@@ -191,17 +218,24 @@ attention_decode_kernel(const DecodeParams p) {
     }
     if (own_here && warp == 0) {
         // the token's own key and value, as one more key of warp 0 (the lanes of key group 0)
-        const h16* ksrc = p.k_new + (size_t)row * p.kv_stride + (size_t)kvh * d + sub * 8;
-        const h16* vsrc = p.v_new + (size_t)row * p.kv_stride + (size_t)kvh * d + sub * 8;
-        const uint4 kown = dim_ok ? *(const uint4*)ksrc : make_uint4(0, 0, 0, 0);
-        const uint4 vown = dim_ok ? *(const uint4*)vsrc : make_uint4(0, 0, 0, 0);
-        const h16x2* kk = (const h16x2*)&kown;
+        const h16* ksrc = p.k_new + (size_t)row * p.kv_stride + (size_t)kvh * d;
+        const h16* vsrc = p.v_new + (size_t)row * p.kv_stride + (size_t)kvh * d;
+        uint4 kown[E], vown[E];
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+            kown[e] = dim_ok ? *(const uint4*)(ksrc + (e * LPK + sub) * 8) : make_uint4(0, 0, 0, 0);
+            vown[e] = dim_ok ? *(const uint4*)(vsrc + (e * LPK + sub) * 8) : make_uint4(0, 0, 0, 0);
+        }
         float dot = 0.f;
 #pragma unroll
-        for (int t = 0; t < 4; ++t) {
-            const float2 f = h16x2_to_float2(kk[t]);
-            dot = fmaf(q[2 * t], f.x, dot);
-            dot = fmaf(q[2 * t + 1], f.y, dot);
+        for (int e = 0; e < E; ++e) {
+            const h16x2* kk = (const h16x2*)&kown[e];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                const float2 f = h16x2_to_float2(kk[t]);
+                dot = fmaf(q[e][2 * t], f.x, dot);
+                dot = fmaf(q[e][2 * t + 1], f.y, dot);
+            }
         }
 #pragma unroll
         for (int o = LPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
@@ -210,17 +244,22 @@ attention_decode_kernel(const DecodeParams p) {
         const float corr = (m == -INFINITY) ? 0.f : __expf(m - m_new);
         l *= corr;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] *= corr;
+        for (int e = 0; e < E; ++e)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[e][i] *= corr;
         m = m_new;
         if (kgrp == 0) {
             const float pj = __expf(s_own - m);
             l += pj;
-            const h16x2* vv = (const h16x2*)&vown;
 #pragma unroll
-            for (int t = 0; t < 4; ++t) {
-                const float2 f = h16x2_to_float2(vv[t]);
-                acc[2 * t] = fmaf(pj, f.x, acc[2 * t]);
-                acc[2 * t + 1] = fmaf(pj, f.y, acc[2 * t + 1]);
+            for (int e = 0; e < E; ++e) {
+                const h16x2* vv = (const h16x2*)&vown[e];
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    const float2 f = h16x2_to_float2(vv[t]);
+                    acc[e][2 * t] = fmaf(pj, f.x, acc[e][2 * t]);
+                    acc[e][2 * t + 1] = fmaf(pj, f.y, acc[e][2 * t + 1]);
+                }
             }
         }
     }
@@ -229,11 +268,15 @@ attention_decode_kernel(const DecodeParams p) {
     for (int o = 16; o >= LPK; o >>= 1) {
         l += __shfl_xor_sync(0xffffffffu, l, o);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], o);
+        for (int e = 0; e < E; ++e)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[e][i] += __shfl_xor_sync(0xffffffffu, acc[e][i], o);
     }
     if (lane < LPK) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) sm_acc[warp][lane * 8 + i] = acc[i];
+        for (int e = 0; e < E; ++e)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) sm_acc[warp][(e * LPK + lane) * 8 + i] = acc[e][i];
     }
     if (lane == 0) { sm_m[warp] = m; sm_l[warp] = l; }
     __syncthreads();
@@ -316,6 +359,17 @@ attention_decode_kernel(const DecodeParams p) {
     }
 }
 
+// Launches the kernel for LPK lanes a key and E pieces a lane with 4, 8 or 16 warps a block (16 only for
+// E = 1 and at most 16 lanes a key, where the registers allow it; 8 otherwise).
+template <int LPK, int E>
+int launch_decode(int warps, dim3 grid, cudaStream_t stream, const DecodeParams& p) {
+    if constexpr (E == 1 && LPK <= 16) {
+        if (warps == 16) return tnx_launch_pdl(attention_decode_kernel<LPK, E, 16>, grid, dim3(16 * 32), 0, stream, p);
+    }
+    if (warps >= 8) return tnx_launch_pdl(attention_decode_kernel<LPK, E, 8>, grid, dim3(8 * 32), 0, stream, p);
+    return tnx_launch_pdl(attention_decode_kernel<LPK, E, 4>, grid, dim3(4 * 32), 0, stream, p);
+}
+
 }  // namespace
 
 // Scratch floats and counters needed for n_rows decode rows with n_splits splits.
@@ -354,25 +408,21 @@ TNX_EXPORT int tnx_attention_decode_append(const void* q, int q_stride, void* ca
     // says which.
     if (warps != 4 && warps != 8 && warps != 16) return TNX_ERR_BAD_ARG;
     if (warps == 16 && chunks > 16) return TNX_ERR_UNSUPPORTED;      // sixteen warps of the widest heads would spill
-    const dim3 block(warps * 32);
-    if (warps == 16) {
-        if (chunks <= 2) return tnx_launch_pdl(attention_decode_kernel<2, 16>, grid, block, 0, stream, p);
-        if (chunks <= 4) return tnx_launch_pdl(attention_decode_kernel<4, 16>, grid, block, 0, stream, p);
-        if (chunks <= 8) return tnx_launch_pdl(attention_decode_kernel<8, 16>, grid, block, 0, stream, p);
-        return tnx_launch_pdl(attention_decode_kernel<16, 16>, grid, block, 0, stream, p);
+    // Pieces of 8 dims per head: a power of two -> that many lanes a key; 3 times a power of two (head
+    // sizes 48, 96, 192) -> a lane owns 3 pieces (96: 6.4 against 5.3 TB/s at batch 64); anything else ->
+    // the next power of two with idle lanes.  (5 pieces a lane for head sizes 80 and 160 was measured: 210
+    // registers, one block an SM, and no faster than the idle lanes: 4.6 TB/s both.)
+    switch (chunks) {
+        case 2: return launch_decode<2, 1>(warps, grid, stream, p);
+        case 3: case 4: return launch_decode<4, 1>(warps, grid, stream, p);
+        case 6: return launch_decode<2, 3>(warps, grid, stream, p);
+        case 5: case 7: case 8: return launch_decode<8, 1>(warps, grid, stream, p);
+        case 12: return launch_decode<4, 3>(warps, grid, stream, p);
+        case 24: return launch_decode<8, 3>(warps, grid, stream, p);
+        default: break;
     }
-    if (warps == 8) {
-        if (chunks <= 2) return tnx_launch_pdl(attention_decode_kernel<2, 8>, grid, block, 0, stream, p);
-        if (chunks <= 4) return tnx_launch_pdl(attention_decode_kernel<4, 8>, grid, block, 0, stream, p);
-        if (chunks <= 8) return tnx_launch_pdl(attention_decode_kernel<8, 8>, grid, block, 0, stream, p);
-        if (chunks <= 16) return tnx_launch_pdl(attention_decode_kernel<16, 8>, grid, block, 0, stream, p);
-        return tnx_launch_pdl(attention_decode_kernel<32, 8>, grid, block, 0, stream, p);
-    }
-    if (chunks <= 2) return tnx_launch_pdl(attention_decode_kernel<2, 4>, grid, block, 0, stream, p);
-    if (chunks <= 4) return tnx_launch_pdl(attention_decode_kernel<4, 4>, grid, block, 0, stream, p);
-    if (chunks <= 8) return tnx_launch_pdl(attention_decode_kernel<8, 4>, grid, block, 0, stream, p);
-    if (chunks <= 16) return tnx_launch_pdl(attention_decode_kernel<16, 4>, grid, block, 0, stream, p);
-    return tnx_launch_pdl(attention_decode_kernel<32, 4>, grid, block, 0, stream, p);
+    if (chunks <= 16) return launch_decode<16, 1>(warps, grid, stream, p);
+    return launch_decode<32, 1>(warps, grid, stream, p);
 }
 
 TNX_EXPORT int tnx_attention_decode(const void* q, int q_stride, const void* cache, const int* block_tables,

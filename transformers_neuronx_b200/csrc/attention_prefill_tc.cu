@@ -1,6 +1,6 @@
-// Causal attention of prompt portions over the paged bfloat16 cache on the 5th-generation tensor
-// cores (tcgen05), for head size 128.  Same work items and the same result as attention_prefill.cu;
-// this kernel is the fast one.
+// Causal attention of prompt portions over the paged 16-bit cache on the 5th-generation tensor
+// cores (tcgen05), for head sizes 64, 80, 96, 112 and 128 (described for 128).  Same work items and the
+// same result as attention_prefill.cu; this kernel is the fast one.
 //
 // Work item = (request, tile of 128 of its query rows, head); keys in tiles of 64 (four pages).
 //   S = Q K^T   : tcgen05.mma M=128 (queries) N=64 (keys) K=128 (head), Q and K from shared memory
@@ -31,14 +31,17 @@ constexpr int BQ = 128, BKV = 64, PAGE = 16;
 constexpr int ATOM_Q = BQ * 128;             // bytes of one 64-column slice of the Q tile (16 KB)
 constexpr int ATOM_KV = BKV * 128;           // bytes of one 64-column slice of a K or V tile (8 KB)
 constexpr int MAX_PAGES_SMEM = 128;          // page numbers kept in shared memory (2,048 keys); beyond: read from global
-// Head size D (64 or 128), KS stages of K tiles and VS of V tiles.  Everything lives in dynamic
+// Head size D (64..128 in steps of 16), KS stages of K tiles and VS of V tiles.  A head size between 64
+// and 128 uses the layout of 128: its second 64-column slice is partly filled (the TMA box of a K or V
+// tile reaches beyond the tensor's last column there and is filled with zeros; that of Q reaches into
+// the next head's columns), and the MMAs stop at the head's own columns.  Everything lives in dynamic
 // shared memory, the tiles first: with no static shared memory the dynamic part starts at the
 // CTA's shared window, which is 1024-byte aligned as the swizzled tiles need (checked at run time).
 // D = 128: Q 32 KB + (2 + 3) x 16 KB, so that two CTAs fit on an SM to the byte; D = 64: Q 16 KB +
 // (3 + 4) x 8 KB, stages enough to cover the time a tile takes to arrive.
 template <int D, int KS, int VS>
 struct Layout {
-    static constexpr int SLICES = D / 64;                        // 64-column slices of a row
+    static constexpr int SLICES = (D + 63) / 64;                 // 64-column slices of a row (the last may be partly used)
     static constexpr int Q_BYTES = SLICES * ATOM_Q, KV_BYTES = SLICES * ATOM_KV;
     static constexpr int TILE_BYTES = Q_BYTES + (KS + VS) * KV_BYTES;
     static constexpr int SMEM_BYTES = TILE_BYTES + 256 + MAX_PAGES_SMEM * 4;
@@ -378,6 +381,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 if (r < rows) {
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
+                        if (c + 8 * q >= D) break;                // the last 32 columns of a head size like 80 are partly beyond it
                         uint4 u;
                         h16x2 h0 = floats_to_h16x2(__uint_as_float(o[8 * q]) * inv, __uint_as_float(o[8 * q + 1]) * inv);
                         h16x2 h1 = floats_to_h16x2(__uint_as_float(o[8 * q + 2]) * inv, __uint_as_float(o[8 * q + 3]) * inv);
@@ -416,7 +420,7 @@ int launch_tc(const CUtensorMap& mq, const CUtensorMap& mkv, const TcPrefillPara
 
 }  // namespace
 
-// Same arguments as tnx_attention_prefill plus the error word; head_dim must be 64 or 128 and
+// Same arguments as tnx_attention_prefill plus the error word; head_dim must be 64, 80, 96, 112 or 128 and
 // n_rows_q is the number of rows of the q / out buffers (for the TMA descriptor).
 TNX_EXPORT int tnx_attention_prefill_tc(const void* q, int q_stride, int n_rows_q, const void* cache, long long cache_rows,
                                         const int* block_tables, int bt_stride, const int* tile_req, const int* tile_q0,
@@ -424,7 +428,7 @@ TNX_EXPORT int tnx_attention_prefill_tc(const void* q, int q_stride, int n_rows_
                                         int out_stride, int n_items, int n_heads, int n_kv_heads, int head_dim,
                                         int page_size, int window, float scale, int* err_word, cudaStream_t stream) {
     if (n_items <= 0) return 0;
-    if ((head_dim != 64 && head_dim != 128) || page_size != PAGE || n_kv_heads <= 0 || n_heads % n_kv_heads || q_stride % 8 ||
+    if (head_dim < 64 || head_dim > 128 || head_dim % 16 || page_size != PAGE || n_kv_heads <= 0 || n_heads % n_kv_heads || q_stride % 8 ||
         out_stride % 8 || ((uintptr_t)q & 15) || ((uintptr_t)cache & 15) || ((uintptr_t)out & 15) ||
         cache_rows > 0x7fffffffLL || !err_word)
         return TNX_ERR_UNSUPPORTED;
@@ -436,6 +440,11 @@ TNX_EXPORT int tnx_attention_prefill_tc(const void* q, int q_stride, int n_rows_
     p.q_start = q_start; p.q_len = q_len; p.ctx_len = ctx_len; p.out = (h16*)out; p.out_stride = out_stride;
     p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.window = window; p.scale_log2 = scale * 1.4426950408889634f;
     p.err = err_word;
-    if (head_dim == 128) return launch_tc<128, 2, 3>(mq, mkv, p, n_heads, n_items, stream);
-    return launch_tc<64, 3, 4>(mq, mkv, p, n_heads, n_items, stream);
+    switch (head_dim) {
+        case 128: return launch_tc<128, 2, 3>(mq, mkv, p, n_heads, n_items, stream);
+        case 112: return launch_tc<112, 2, 3>(mq, mkv, p, n_heads, n_items, stream);
+        case 96: return launch_tc<96, 2, 3>(mq, mkv, p, n_heads, n_items, stream);
+        case 80: return launch_tc<80, 2, 3>(mq, mkv, p, n_heads, n_items, stream);
+        default: return launch_tc<64, 3, 4>(mq, mkv, p, n_heads, n_items, stream);
+    }
 }

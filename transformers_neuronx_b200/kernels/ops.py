@@ -587,15 +587,15 @@ def attention_prefill(q, cache, block_tables, tile_req, tile_q0, q_start, q_len,
 
 
 def attention_prefill_tc_supported(q, cache, out) -> bool:
-    """The tcgen05 prefill kernel takes head sizes 64 and 128, pages of 16 and 16-byte aligned rows."""
-    return (cache.dtype in _H16 and q.dtype == cache.dtype and out.dtype == cache.dtype and cache.shape[4] in (64, 128) and cache.shape[3] == 16 and q.stride(0) % 8 == 0 and
+    """The tcgen05 prefill kernel takes head sizes 64, 80, 96, 112 and 128, pages of 16 and 16-byte aligned rows."""
+    return (cache.dtype in _H16 and q.dtype == cache.dtype and out.dtype == cache.dtype and cache.shape[4] in (64, 80, 96, 112, 128) and cache.shape[3] == 16 and q.stride(0) % 8 == 0 and
             out.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0 and
             cache.shape[0] * 2 * cache.shape[2] * 16 < 2 ** 31)
 
 
 def attention_prefill_tc(q, cache, block_tables, tile_req, tile_q0, q_start, q_len, ctx_len, out, n_heads, scale,
                          window=0, n_items=None):
-    """attention_prefill on the tcgen05 tensor cores (head sizes 64 and 128).  The cache must hold finite
+    """attention_prefill on the tcgen05 tensor cores (head sizes 64 to 128 in steps of 16).  The cache must hold finite
     numbers in every row, written or not (CacheStorage allocates it zeroed)."""
     lib = _lib("attention_prefill_tc", cache, q, out)
     _need(cache, "cache", _H16, 5)
@@ -603,7 +603,7 @@ def attention_prefill_tc(q, cache, block_tables, tile_req, tile_q0, q_start, q_l
     No, wo, out_stride = _rows_2d(out, "out")
     n_pages, _, n_kv, ps, d = cache.shape
     if not attention_prefill_tc_supported(q, cache, out) or width != n_heads * d or (No, wo) != (N, width):
-        raise KernelError("attention_prefill_tc takes a 16-bit type, head size 64 or 128, pages of 16, 16-byte aligned rows")
+        raise KernelError("attention_prefill_tc takes a 16-bit type, head sizes 64 to 128 in steps of 16, pages of 16, 16-byte aligned rows")
     for t, nm in ((block_tables, "block_tables"), (tile_req, "tile_req"), (tile_q0, "tile_q0"), (q_start, "q_start"),
                   (q_len, "q_len"), (ctx_len, "ctx_len")):
         _need(t, nm, torch.int32, 2 if nm == "block_tables" else 1)
