@@ -385,7 +385,7 @@ def test_attention_simt(n_heads, n_kv, d, dtype, window):
 
 @pytest.mark.parametrize("n_heads,n_kv,d", ATT_SHAPES)
 @pytest.mark.parametrize("window", [None, 50])
-@pytest.mark.parametrize("n_splits,warps", [(None, None), (1, 4), (3, 4), (7, 4), (1, 8), (2, 8), (5, 8), (1, 16), (3, 16)])
+@pytest.mark.parametrize("n_splits,warps", [(None, None), (1, 4), (3, 4), (7, 4), (1, 8), (2, 8), (5, 8), (1, 16), (3, 16), (20, 8), (44, 4)])
 def test_attention_decode(n_heads, n_kv, d, window, n_splits, warps):
     lens = [(0, 1), (15, 1), (16, 1), (17, 1), (255, 1), (256, 1), (700, 1), (63, 1)]
     case = PagedCase(lens, n_heads, n_kv, d, torch.bfloat16, seed=d + 1)

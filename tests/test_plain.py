@@ -120,3 +120,22 @@ def test_greedy_generate():
     m = TinyModel("A", seed=4)
     out = P.greedy_generate(m.random_ids(6, seed=1), 5, m.tensors, m.cfg.to_dict())
     assert len(out) == 5 and all(0 <= t < m.cfg.vocab_size for t in out)
+
+
+def test_decode_attention_plan_keeps_its_rules():
+    """The plan of the decode attention kernel (blocks of 4, 8 or 16 warps, splits of the context) for
+    every number of (row, head) pairs, head size and context: a split keeps at least eight pages, sixteen
+    warps only serve heads of up to 128 dims, and the whole GPU is used once there is work for it."""
+    from transformers_neuronx_b200.kernels.ops import decode_attention_plan
+    for sms in (148, 132, 80):
+        for head_dim in (64, 128, 256):
+            for max_pages in (1, 7, 8, 31, 63, 128, 512):
+                for pairs in list(range(1, 700, 7)) + [1024, 4096, 70000]:
+                    warps, splits = decode_attention_plan(pairs, sms, head_dim, max_pages)
+                    assert warps in (4, 8, 16) and 1 <= splits <= 32
+                    assert warps < 16 or head_dim <= 128
+                    assert splits == 1 or max_pages // splits >= 8, (pairs, max_pages, splits)
+                    assert pairs * splits <= 4 * sms or splits == 1 or pairs * 10 <= sms * 27
+                    if max_pages >= 64 and pairs * 4 <= sms * 3:
+                        assert pairs * splits * 2 > sms or splits == min(32, max_pages // 8), \
+                            "few pairs and a long context: the splits fill the GPU as far as eight pages each allow"

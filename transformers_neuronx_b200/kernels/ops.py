@@ -491,6 +491,45 @@ def gemm_tc_force_plan(plan=None, dtype=torch.bfloat16) -> None:
     _gemm_plans.clear()
 
 
+def decode_attention_plan(pairs: int, sms: int, head_dim: int, max_pages: int):
+    """(warps a block, splits of the context) for `pairs` (row, head) pairs of decode attention.
+
+    An SM holds sixteen warps of this kernel: four blocks of four, two of eight or one of sixteen.
+    Measured at 1 to 64 rows of 32, 40 and 56 heads of 128 dims over contexts of 2,040 (every plan
+    against the one chosen here), the fastest plan keeps all blocks on the GPU at once where it can and
+    gives the SMs equal numbers of them:
+      * few pairs: blocks of eight warps, as many splits as fill two blocks per SM (1 / 2 rows of 32
+        heads: 13 / 18 us);
+      * about one pair per SM (0.75 to 1): one block of sixteen warps each and no split (4 rows: 28 us,
+        eight warps and two splits 30);
+      * up to a third of four blocks per SM: four warps and three splits (6 rows: 39 us; eight warps and
+        no split, which leaves the SMs one or two blocks each, 47);
+      * up to two pairs per SM: eight warps, no split (8 rows: 49 us);
+      * up to 2.7 pairs per SM: four warps and three splits again (12 rows: 73 us; without splits the SMs
+        hold two or three blocks each, 80);
+      * up to four pairs per SM: four warps, no split (16 rows: 91 us); beyond: eight warps (64 rows: 321 us).
+    A split keeps at least eight pages, and contexts of fewer than 48 pages are not split in three (at
+    500 tokens the plans without splits were 7-12 % faster there, and from a quarter of a pair per SM
+    one block of sixteen warps was: 9 against 12 us at 3 rows)."""
+    most = max(1, max_pages // 8)
+    wide = 16 if head_dim <= 128 else 8
+    if pairs * 4 <= sms * 3:
+        if most <= 4 and pairs * 4 >= sms:
+            return wide, 1
+        return 8, max(1, min(most, 32, (2 * sms) // max(1, pairs)))
+    if pairs <= sms:
+        return wide, 1
+    if pairs * 3 <= 4 * sms and most >= 6:
+        return 4, 3
+    if pairs <= 2 * sms:
+        return 8, 1
+    if pairs * 10 <= sms * 27 and most >= 6:
+        return 4, 3
+    if pairs <= 4 * sms:
+        return 4, 1
+    return 8, 1
+
+
 def attention_decode(q, cache, block_tables, token_request, positions, out, n_heads, scale, window=0, rows=None,
                      n_rows=None, max_kv_len=None, n_splits=None, new_kv=None, warps=None):
     """One query token per row over the paged 16-bit cache.  `rows` (int32) names the rows of q
@@ -515,23 +554,7 @@ def attention_decode(q, cache, block_tables, token_request, positions, out, n_he
     max_pages = max(1, -(-(int(max_kv_len) if max_kv_len is not None else block_tables.shape[1] * ps) // ps))
     forced_warps, warps = warps, 4
     if n_splits is None:
-        # Measured at 1 to 64 rows of 32 heads (contexts of 2,040): the fastest plan has about two blocks
-        # of eight warps per SM with as few splits as that takes (8, 4, 2, 1 splits at 1, 2, 4, 8 rows:
-        # 13.4 / 18.6 / 30.6 / 49.3 us, where four warps took 14.7 / 19.2 / 30.5 / 53.0); with more
-        # (row, head) pairs than that, four warps and no split while four blocks per SM hold them all
-        # (16 rows: 91.5 us), eight warps beyond (64 rows: 324 us).  A split has at least eight pages and
-        # a whole number of rounds of the block's warps.
-        pairs = R * n_heads
-        if st["sms"] < 2 * pairs <= 2 * st["sms"] and d <= 128:
-            warps, n_splits = 16, 1        # one block of sixteen warps per SM and no split: 4 rows 28.9 us (eight warps, two splits: 30.8)
-        elif pairs <= 2 * st["sms"]:
-            warps, n_splits = 8, 1
-            while n_splits < 32 and pairs * n_splits * 2 <= 2 * st["sms"] and n_splits * 2 <= max_pages // 8:
-                n_splits *= 2
-        elif pairs <= 4 * st["sms"]:
-            warps, n_splits = 4, 1
-        else:
-            warps, n_splits = 8, 1
+        warps, n_splits = decode_attention_plan(R * n_heads, st["sms"], d, max_pages)
         pps = -(-max_pages // n_splits)
         pps = -(-pps // warps) * warps
     else:                                                  # a test's own plan (warps: 4, 8 or 16 a block)
