@@ -600,6 +600,45 @@ def test_sampling_with_a_fixed_uniform_number_matches_the_reference_choice(V):
         assert margin <= 2e-6 or int(out2[i]) == want
 
 
+@pytest.mark.parametrize("V", [5, 37, 4099, 50272])
+def test_sampling_does_not_depend_on_the_blocks_a_row(V):
+    """A row is shared out over 1, 2, 4 or 8 thread blocks of a cluster (few rows: more blocks each); all
+    sums are integers and added up across the cluster, so every way draws the same tokens: greedy with a
+    tie across slices, temperature, top-k, top-p with a least number of tokens, the fixed draw, suppressed ids."""
+    o = ops()
+    g = torch.Generator().manual_seed(V)
+    n = 24
+    logits = (torch.randn(n, V, generator=g) * 2.5)
+    logits[1, 0] = logits[1, V - 1] = 50.0                    # a tie between the first block's slice and the last's
+    logits[2] = float("-inf")                                 # nothing to draw from: token 0
+    temps = [0.0, 0.0, 1.0, 1.0, 0.7, 1.3, 0.9, 2.0] * 3
+    ks = [0, 0, 0, 0, 5, 0, 12, 3] * 3
+    ps = [1.0, 1.0, 1.0, 1.0, 1.0, 0.8, 0.6, 0.3] * 3
+    ms = [1, 1, 1, 1, 1, 1, 2, 4] * 3
+    dev = logits.to(DEV)
+    results = {}
+    try:
+        for blocks in (1, 2, 4, 8):
+            o.sample_force_blocks_per_row(blocks)
+            for det in (False, True):
+                out = torch.full((n,), -7, dtype=torch.int32, device=DEV)
+                o.sample(dev, out, temperature=torch.tensor(temps, device=DEV), top_k=torch.tensor(ks, dtype=torch.int32, device=DEV),
+                         top_p=torch.tensor(ps, device=DEV), min_keep=torch.tensor(ms, dtype=torch.int32, device=DEV),
+                         seeds=torch.arange(n, dtype=torch.int64, device=DEV) + 3,
+                         counters=torch.arange(n, dtype=torch.int64, device=DEV) * 5, deterministic=det, suppress_id=min(3, V - 1))
+                results[(blocks, det)] = out.cpu().tolist()
+            out = torch.full((n,), -7, dtype=torch.int32, device=DEV)
+            o.sample(dev, out, temperature=torch.tensor(temps, device=DEV))          # the variant without top-p
+            results[(blocks, "plain")] = out.cpu().tolist()
+    finally:
+        o.sample_force_blocks_per_row(None)
+    for kind in (False, True, "plain"):
+        for blocks in (2, 4, 8):
+            assert results[(blocks, kind)] == results[(1, kind)], (blocks, kind)
+        assert all(0 <= t < V for t in results[(1, kind)])
+    assert results[(1, False)][1] == 0 and results[(1, False)][2] == 0
+
+
 def test_sampling_top_p_keeps_at_least_min_tokens():
     V, n = 41, 20000
     row = torch.randn(V, generator=torch.Generator().manual_seed(13)) * 3

@@ -1,4 +1,8 @@
-// Next-token choice from 32-bit logits, one thread block per row.
+// Next-token choice from 32-bit logits, one cluster of thread blocks per row (1, 2, 4 or 8 blocks, as
+// many as keep all rows on the GPU at once: a row of 50,272 logits is walked up to fifteen times, and
+// with few rows one block per row would leave most of the GPU idle).  A block owns a contiguous
+// slice of the row; histograms and sums are added up across the cluster through distributed shared
+// memory, and since all of them are integers the result does not depend on the cluster's size.
 //
 //   temperature <= 0 : argmax, the lowest index winning a tie.
 //   temperature  > 0 : s_i = logit_i / temperature (the suppressed id, if any, at -inf);
@@ -47,8 +51,10 @@ __device__ __forceinline__ void philox4x32_10(uint32_t c0, uint32_t c1, uint32_t
 
 // exp(s - mx) as a 2^-40 fixed-point integer.  The product with 2^40 is exact in 32-bit (a change of
 // the exponent), so this is the value a 64-bit computation would truncate to as well.
+// A score that is NaN, or -inf where every score is, has no mass (the conversion of a NaN is not zero).
 __device__ __forceinline__ unsigned long long mass_of(float s, float mx) {
-    return __float2ull_rz(expf(s - mx) * 1099511627776.0f);
+    const float e = expf(s - mx);
+    return e == e ? __float2ull_rz(e * 1099511627776.0f) : 0ull;
 }
 
 struct ArgMax { float v; int i; };
@@ -73,6 +79,21 @@ struct SampleArgs {
     int n_rows;                      //   travels to the host with the sampled ids)
 };
 
+__device__ __forceinline__ uint32_t cluster_map(const void* smem_ptr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"((uint32_t)__cvta_generic_to_shared(smem_ptr)), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ unsigned long long cluster_ld_u64(uint32_t addr) {
+    unsigned long long v;
+    asm volatile("ld.shared::cluster.u64 %0, [%1];" : "=l"(v) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// Grid (blocks a row, rows), clusters of (blocks a row, 1).
 template <bool TOP_P>
 __global__ void __launch_bounds__(THREADS)
 sample_kernel(const float* __restrict__ logits, int ld, int V, const SampleArgs a, int* __restrict__ out) {
@@ -83,15 +104,31 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const SampleArgs 
     __shared__ ArgMax ascratch[32];
     __shared__ unsigned int chist[256];
     __shared__ unsigned long long mhist[256];
+    // What a block hands to the others of its cluster: two buffers used in turn, so that a block may fill
+    // the next one while a slower block still reads the last (one cluster barrier per exchange).
+    __shared__ unsigned long long xbuf[2][256];
     __shared__ unsigned int sh_prefix, sh_remaining;
     __shared__ unsigned long long sh_above, sh_total;
-    __shared__ int sh_owner;
     pdl_launch_dependents();
     pdl_wait();
 
-    const int r = blockIdx.x, tid = threadIdx.x;
+    const int r = blockIdx.y, tid = threadIdx.x;
+    const int CS = gridDim.x, rank = blockIdx.x;
+    const int slice = (V + CS - 1) / CS;
+    const int v_lo = min(V, rank * slice), v_hi = min(V, v_lo + slice);          // this block's tokens
+    int xp = 0;                                                  // exchanges so far (the same in every block)
     const float* row = logits + (size_t)r * ld;
-    if (a.err_word && r == 0 && tid == 0) out[a.n_rows] = *a.err_word;
+    if (a.err_word && r == 0 && rank == 0 && tid == 0) out[a.n_rows] = *a.err_word;
+    // After xbuf[xp & 1][0 .. n) has been written by every block: the values of all blocks, combined by `op`,
+    // in every thread that asks (index i < n).
+    auto exchange_ready = [&]() { __syncthreads(); if (CS > 1) cluster_sync_all(); };
+    auto gather_sum = [&](int i) -> unsigned long long {
+        unsigned long long t = 0;
+        for (int rk = 0; rk < CS; ++rk) t += cluster_ld_u64(cluster_map(&xbuf[xp & 1][i], (uint32_t)rk));
+        return t;
+    };
+    // No block may leave while another may still read its shared memory.
+    auto leave = [&]() { if (CS > 1) cluster_sync_all(); };
     float T, P;
     int k, n_min, deterministic, sup0, sup1 = -1, sup2 = -1, sup3 = -1;
     unsigned long long seed, ctr;
@@ -116,7 +153,7 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const SampleArgs 
 
     if (!(T > 0.f)) {
         ArgMax best{-INFINITY, 0x7fffffff};
-        for (int i = tid; i < V; i += THREADS) best = better(best, ArgMax{SUPPRESSED(i) ? -INFINITY : row[i], i});
+        for (int i = v_lo + tid; i < v_hi; i += THREADS) best = better(best, ArgMax{SUPPRESSED(i) ? -INFINITY : row[i], i});
         for (int o = 16; o > 0; o >>= 1) {
             ArgMax other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
             best = better(best, other);
@@ -129,15 +166,31 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const SampleArgs 
                 ArgMax other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
                 best = better(best, other);
             }
-            if (tid == 0) out[r] = best.i == 0x7fffffff ? 0 : best.i;
+            if (tid == 0) xbuf[0][0] = ((unsigned long long)__float_as_uint(best.v) << 32) | (unsigned)best.i;
         }
+        exchange_ready();
+        if (rank == 0 && tid == 0) {
+            for (int rk = 1; rk < CS; ++rk) {
+                const unsigned long long o = cluster_ld_u64(cluster_map(&xbuf[0][0], (uint32_t)rk));
+                best = better(best, ArgMax{__uint_as_float((unsigned)(o >> 32)), (int)(unsigned)o});
+            }
+            out[r] = best.i == 0x7fffffff ? 0 : best.i;
+        }
+        leave();
         return;
     }
 
 #define SCORE(i) (SUPPRESSED(i) ? -INFINITY : row[(i)] / T)
     float mx = -INFINITY;
-    for (int i = tid; i < V; i += THREADS) mx = fmaxf(mx, SCORE(i));
+    for (int i = v_lo + tid; i < v_hi; i += THREADS) mx = fmaxf(mx, SCORE(i));
     mx = block_max(mx, fscratch);
+    if (CS > 1) {
+        if (tid == 0) xbuf[xp & 1][0] = __float_as_uint(mx);
+        exchange_ready();
+        for (int rk = 0; rk < CS; ++rk)
+            mx = fmaxf(mx, __uint_as_float((unsigned)cluster_ld_u64(cluster_map(&xbuf[xp & 1][0], (uint32_t)rk))));
+        ++xp;
+    }
 
     // The key of the k-th largest score, by radix selection on the keys' four bytes (1 <= k < V).
     auto kth_largest_key = [&](int k) -> uint32_t {
@@ -148,11 +201,18 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const SampleArgs 
             if (tid < 256) chist[tid] = 0;
             __syncthreads();
             const uint32_t prefix = sh_prefix;
-            for (int i = tid; i < V; i += THREADS) {
+            for (int i = v_lo + tid; i < v_hi; i += THREADS) {
                 const uint32_t key = ordered_key(SCORE(i));
                 if ((key & mask) == prefix) atomicAdd(&chist[(key >> shift) & 255u], 1u);
             }
             __syncthreads();
+            if (CS > 1) {                                          // the counts of the whole row
+                if (tid < 256) xbuf[xp & 1][tid] = chist[tid];
+                exchange_ready();
+                if (tid < 256) chist[tid] = (unsigned)gather_sum(tid);
+                ++xp;
+                __syncthreads();
+            }
             if (tid < 32) {
                 // The highest digit b with count(digits >= b) >= remaining (0 if none): lane l looks at
                 // digits 8 l .. 8 l + 7, the counts of the lanes above it come from a suffix sum.
@@ -201,7 +261,7 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const SampleArgs 
             __syncthreads();
             const uint32_t prefix = sh_prefix;
             unsigned long long* mine64 = warp_hist64 + (tid >> 5) % GROUPS * 256;
-            for (int i = tid; i < V; i += THREADS) {
+            for (int i = v_lo + tid; i < v_hi; i += THREADS) {
                 const float s = SCORE(i);
                 const uint32_t key = ordered_key(s);
                 if (key >= floor_key && (key & mask) == prefix) atomicAdd(&mine64[(key >> shift) & 255u], mass_of(s, mx));
@@ -211,6 +271,12 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const SampleArgs 
                 unsigned long long c = 0;
                 for (int w = 0; w < GROUPS; ++w) c += warp_hist64[w * 256 + tid];
                 mhist[tid] = c;
+                if (CS > 1) xbuf[xp & 1][tid] = c;
+            }
+            if (CS > 1) {                                          // the masses of the whole row
+                exchange_ready();
+                if (tid < 256) mhist[tid] = gather_sum(tid);
+                ++xp;
             }
             __syncthreads();
             if (tid < 32) {
@@ -252,7 +318,7 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const SampleArgs 
     // The mass of all tokens with keys >= floor_key.
     auto mass_from = [&](uint32_t floor_key) -> unsigned long long {
         unsigned long long local = 0;
-        for (int i = tid; i < V; i += THREADS) {
+        for (int i = v_lo + tid; i < v_hi; i += THREADS) {
             const float s = SCORE(i);
             if (ordered_key(s) >= floor_key) local += mass_of(s, mx);
         }
@@ -263,7 +329,12 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const SampleArgs 
         for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
         if ((tid & 31) == 0) atomicAdd(&sh_total, local);
         __syncthreads();
-        return sh_total;
+        if (CS == 1) return sh_total;
+        if (tid == 0) xbuf[xp & 1][0] = sh_total;
+        exchange_ready();
+        const unsigned long long all = gather_sum(0);
+        ++xp;
+        return all;
     };
 
     // ---- top-k: the key of the k-th largest score (0 keeps everything) ----------------------
@@ -286,10 +357,10 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const SampleArgs 
     // likely down, the first at which the summed probability reaches one half; the lowest index of a tie
     if (TOP_P && deterministic) {
         const unsigned long long total = mass_from(thr);
-        if (total == 0) { if (tid == 0) out[r] = 0; return; }
+        if (total == 0) { if (rank == 0 && tid == 0) out[r] = 0; leave(); return; }
         const uint32_t key = lowest_key_within_mass((total + 1) / 2, thr);
         int first = 0x7fffffff;
-        for (int i = tid; i < V; i += THREADS)
+        for (int i = v_lo + tid; i < v_hi; i += THREADS)
             if (ordered_key(SCORE(i)) == key) { first = i; break; }
         for (int o = 16; o > 0; o >>= 1) first = min(first, __shfl_xor_sync(0xffffffffu, first, o));
         __syncthreads();
@@ -298,19 +369,27 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const SampleArgs 
         if (tid < 32) {
             first = ascratch[tid].i;
             for (int o = 16; o > 0; o >>= 1) first = min(first, __shfl_xor_sync(0xffffffffu, first, o));
-            if (tid == 0) out[r] = first == 0x7fffffff ? 0 : first;
+            if (tid == 0) xbuf[xp & 1][0] = (unsigned)first;
         }
+        exchange_ready();
+        if (rank == 0 && tid == 0) {
+            for (int rk = 1; rk < CS; ++rk) first = min(first, (int)(unsigned)cluster_ld_u64(cluster_map(&xbuf[xp & 1][0], (uint32_t)rk)));
+            out[r] = first == 0x7fffffff ? 0 : first;
+        }
+        leave();
         return;
     }
 
     // ---- inverse CDF in index order over the kept tokens --------------------------------------
-    const int chunk = (V + THREADS - 1) / THREADS;
-    const int lo = tid * chunk, hi = min(V, lo + chunk);
+    // A thread owns a contiguous run of its block's slice, so that thread and block order is index order.
+    const int chunk = (v_hi - v_lo + THREADS - 1) / THREADS;
+    const int lo = min(v_hi, v_lo + tid * chunk), hi = min(v_hi, lo + chunk);
     unsigned long long local = 0;
     for (int i = lo; i < hi; ++i) {
         const float s = SCORE(i);
         if (ordered_key(s) >= thr) local += mass_of(s, mx);
     }
+    __syncthreads();                                  // the histogram copies are done with: `sums` lies over them
     sums[tid] = local;
     __syncthreads();
     if (tid < 32) {                                   // exclusive scan of 1024 partial sums
@@ -324,17 +403,25 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const SampleArgs 
         }
         const unsigned long long excl = incl - run;
         for (int j = 0; j < 32; ++j) sums[base + j] += excl;
-        if (tid == 31) sh_total = incl;
+        if (tid == 31) { sh_total = incl; xbuf[xp & 1][0] = incl; }
     }
-    if (tid == 0) sh_owner = -1;
-    __syncthreads();
-    const unsigned long long total = sh_total;
+    exchange_ready();
+    unsigned long long before = 0, total = 0;         // the mass of the blocks before this one, and of the row
+    if (CS > 1) {
+        for (int rk = 0; rk < CS; ++rk) {
+            const unsigned long long t = cluster_ld_u64(cluster_map(&xbuf[xp & 1][0], (uint32_t)rk));
+            if (rk < rank) before += t;
+            total += t;
+        }
+    } else {
+        total = sh_total;
+    }
     uint32_t rnd[4];
     philox4x32_10((uint32_t)ctr, (uint32_t)(ctr >> 32), 0u, 0u, (uint32_t)seed, (uint32_t)(seed >> 32), rnd);
     // target = floor(total * u), u = rnd / 2^32 in [0, 1)
     const unsigned long long target = __umul64hi(total, (unsigned long long)rnd[0] << 32);
-    const unsigned long long mine = sums[tid];
-    if (local > 0 && target >= mine && target < mine + local) {
+    const unsigned long long mine = before + sums[tid];
+    if (local > 0 && target >= mine && target < mine + local) {       // exactly one thread of the cluster, if total > 0
         unsigned long long run = mine;
         int pick = lo;
         for (int i = lo; i < hi; ++i) {
@@ -346,15 +433,37 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const SampleArgs 
             }
         }
         out[r] = pick;
-        sh_owner = tid;
     }
-    __syncthreads();
-    if (tid == 0 && sh_owner < 0) {                   // total == 0: every score was -inf or NaN
-        out[r] = 0;
-    }
+    if (total == 0 && rank == 0 && tid == 0) out[r] = 0;               // every score was -inf or NaN
+    leave();
 #undef SCORE
 #undef SUPPRESSED
 }
+// Blocks a row: 8, 4 or 2 while all rows' blocks fit the GPU at once and a block keeps at least 2,048
+// tokens of the row (measured at 8 rows of 50,272 logits: one block a row took 12 us for the argmax and
+// 209 us with temperature and top-p).
+int g_forced_blocks = 0;                   // a test's own number of blocks a row (0: the rule below)
+int blocks_per_row(int n_rows, int V) {
+    if (g_forced_blocks > 0) return g_forced_blocks;
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 1;
+    }
+    // (Clusters of 8 and 4 find room on half of the SMs only: 16 rows took 107 us with 8 blocks each, 82 with 4.)
+    for (int c = 8; c > 1; c >>= 1)
+        if ((long long)n_rows * c * (c > 2 ? 2 : 1) <= sms && V >= c * 2048) return c;
+    return 1;
+}
+
+int launch_sample(bool with_top_p, int n_rows, int V, cudaStream_t stream, const float* logits, int ld, const SampleArgs& a, int* out) {
+    const int c = blocks_per_row(n_rows, V);
+    if (with_top_p)
+        return tnx_launch_cluster(0, dim3(c), sample_kernel<true>, dim3(c, n_rows), dim3(THREADS), 0, stream, logits, ld, V, a, out);
+    return tnx_launch_cluster(0, dim3(c), sample_kernel<false>, dim3(c, n_rows), dim3(THREADS), 0, stream, logits, ld, V, a, out);
+}
+
 }  // namespace
 
 // min_keep (per row, may be null: 1): top-p never keeps fewer tokens than this.  deterministic: the
@@ -366,9 +475,7 @@ TNX_EXPORT int tnx_sample(const float* logits, int ld, int n_rows, int V, const 
     if (n_rows <= 0) return 0;
     if (V <= 0 || ld < V) return TNX_ERR_BAD_ARG;
     SampleArgs a = {temperature, top_k, top_p, min_keep, seeds, counters, deterministic, suppress_id, nullptr, nullptr, n_rows};
-    if (top_p || deterministic)
-        return tnx_launch_pdl(sample_kernel<true>, dim3(n_rows), dim3(THREADS), 0, stream, logits, ld, V, a, out);
-    return tnx_launch_pdl(sample_kernel<false>, dim3(n_rows), dim3(THREADS), 0, stream, logits, ld, V, a, out);
+    return launch_sample(top_p || deterministic, n_rows, V, stream, logits, ld, a, out);
 }
 
 // The same with every row's parameters packed (ROW_WORDS 32-bit words a row, see above).  with_top_p: 0
@@ -379,9 +486,15 @@ TNX_EXPORT int tnx_sample_packed(const float* logits, int ld, int n_rows, int V,
     if (n_rows <= 0) return 0;
     if (V <= 0 || ld < V || !packed) return TNX_ERR_BAD_ARG;
     SampleArgs a = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0, -1, packed, err_word, n_rows};
-    if (with_top_p)
-        return tnx_launch_pdl(sample_kernel<true>, dim3(n_rows), dim3(THREADS), 0, stream, logits, ld, V, a, out);
-    return tnx_launch_pdl(sample_kernel<false>, dim3(n_rows), dim3(THREADS), 0, stream, logits, ld, V, a, out);
+    return launch_sample(with_top_p != 0, n_rows, V, stream, logits, ld, a, out);
 }
 
 TNX_EXPORT int tnx_sample_row_words() { return ROW_WORDS; }
+
+// For tests: 1, 2, 4 or 8 blocks a row whatever the sizes (0: the library's own rule again).  The drawn
+// tokens must not depend on it.
+TNX_EXPORT int tnx_sample_force_blocks_per_row(int blocks) {
+    if (blocks != 0 && blocks != 1 && blocks != 2 && blocks != 4 && blocks != 8) return TNX_ERR_BAD_ARG;
+    g_forced_blocks = blocks;
+    return 0;
+}

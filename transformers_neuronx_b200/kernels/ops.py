@@ -310,6 +310,12 @@ def sample_packed(logits, packed, with_top_p, out, err_word=None):
                                  _p(err_word), _p(out), _stream()), "sample")
 
 
+def sample_force_blocks_per_row(blocks=None) -> None:
+    """The sampling kernel with 1, 2, 4 or 8 thread blocks a row whatever the sizes (None: its own rule
+    again).  For the test that draws the same tokens with each; not for serving."""
+    _check(_build.load("sampling").tnx_sample_force_blocks_per_row(c_int(int(blocks or 0))), "sample_force_blocks_per_row")
+
+
 def error_word(device) -> torch.Tensor:
     """The device word that kernels with bounded waits set when a wait ran out (0: none did)."""
     return _state(device)["err"]
