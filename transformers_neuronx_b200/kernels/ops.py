@@ -514,7 +514,7 @@ def decode_attention_plan(pairs: int, sms: int, head_dim: int, max_pages: int):
       * up to 2.7 pairs per SM: four warps and three splits again (12 rows: 73 us; without splits the SMs
         hold two or three blocks each, 80);
       * up to four pairs per SM: four warps, no split (16 rows: 91 us); beyond: eight warps (64 rows: 321 us).
-    A split keeps at least eight pages, and contexts of fewer than 48 pages are not split in three (at
+    (kernels/microbench.py attention-plans repeats the sweep.)  A split keeps at least eight pages, and contexts of fewer than 48 pages are not split in three (at
     500 tokens the plans without splits were 7-12 % faster there, and from a quarter of a pair per SM
     one block of sixteen warps was: 9 against 12 us at 3 rows)."""
     most = max(1, max_pages // 8)
