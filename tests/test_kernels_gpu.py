@@ -123,6 +123,37 @@ def test_gemv_few_tokens(M, N, K):
         assert torch.equal(again, out)
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 4099, 4096), (1, 520, 328), (2, 300, 10920), (1, 96, 16384), (4, 64, 640)])
+@pytest.mark.parametrize("affine", [True, False])
+def test_gemv_with_the_layer_norm_inside(M, N, K, affine):
+    """The few-token product that normalizes its own input rows: the same numbers as the LayerNorm kernel
+    followed by the product (the normalized rows rounded to bfloat16 in both), against 32-bit torch."""
+    o = ops()
+    g = torch.Generator(device="cpu").manual_seed(M + N + K)
+    x = (torch.randn(M, K + 4, generator=g) * 3 + 0.5).to(DEV)[:, :K]           # a row pitch of its own
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).bfloat16().to(DEV)
+    gamma = (1 + 0.1 * torch.randn(K, generator=g)).to(DEV) if affine else None
+    beta = (0.1 * torch.randn(K, generator=g)).to(DEV) if affine else None
+    bias = torch.randn(N, generator=g).to(DEV)
+    eps = 1e-5
+    h = torch.nn.functional.layer_norm(x.float(), (K,), gamma, beta, eps)
+    want = h.bfloat16().float() @ w.float().t() + bias
+    assert o.gemv_layer_norm_supported(x[:1], w, torch.empty(1, N, dtype=torch.bfloat16, device=DEV))
+    outb = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    o.gemv_layer_norm(x, gamma, beta, eps, w, outb, bias=bias, activation="relu")
+    assert rel_err(outb, torch.relu(want)) <= 5e-3
+    res0 = torch.randn(M, N, generator=g).to(DEV)
+    res = res0.clone()
+    o.gemv_layer_norm(x, gamma, beta, eps, w, res, bias=bias, residual=res)
+    # the two-kernel way, with the engine's own LayerNorm kernel
+    hk = torch.empty(M, K, dtype=torch.bfloat16, device=DEV)
+    o.layer_norm(x.contiguous(), gamma, beta, eps, out_act=hk)
+    two = res0.clone()
+    o.gemv(hk, w, two, bias=bias, residual=two)
+    assert rel_err(res, want + res0) <= 3e-3          # a normalized value next to a rounding boundary may round the other way
+    assert rel_err(res, two) <= 3e-3
+
+
 @pytest.mark.parametrize("M,N,K,splits", [(8, 256, 4096, 4), (64, 130, 1024, 16), (1, 128, 512, 2), (20, 300, 1160, 3),
                                           (100, 300, 2048, 4), (128, 256, 4096, 16)])
 def test_gemm_tc_split_k(M, N, K, splits):

@@ -12,9 +12,17 @@
 // depends only on K, never on M or on the other tokens, so a token's result is the same alone and
 // beside others.  The weights are read before the kernel ahead has finished (they are never
 // written by a kernel); the activations after.
+//
+// The activations can also be given as rows of the 32-bit residual stream with a LayerNorm to apply
+// (tnx_gemv_ln): every block then normalizes the rows itself as it fills its shared memory (three
+// walks over a row that lies in the second-level cache: mean, variance of the formula, the affine),
+// and the LayerNorm kernel, its launch and the trip of its output through memory are not needed.
+// With one token that is 2 us a product, a twentieth of the step.
 #include "common.cuh"
 
 namespace {
+
+struct LnArgs { const float* x; int ldx; const float* gamma; const float* beta; float eps; };
 
 
 __device__ __forceinline__ uint4 load_stream(const uint4* p) { return __ldcs(p); }
@@ -37,9 +45,10 @@ template <int M, int R, int THREADS>
 __global__ void __launch_bounds__(THREADS)
 gemv_kernel(const h16* __restrict__ A, int lda, const h16* __restrict__ W, int ldw,
             const float* __restrict__ bias, const float* residual, void* C, int ldc,
-            int act, int c_is_h16, int N, int K) {
+            int act, int c_is_h16, int N, int K, const LnArgs ln) {
     extern __shared__ uint4 xs[];                         // [M][K / 8] pieces of the activations
     __shared__ float red[THREADS / 32][R * M];
+    __shared__ float lnred[32];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int K8 = K >> 3;
     // This block's rows: an equal share of the N rows (to within one row), taken R at a time; the
@@ -59,9 +68,55 @@ gemv_kernel(const h16* __restrict__ A, int lda, const h16* __restrict__ W, int l
     uint4 cur[R];
     if (row_begin < row_end && tid < K8) fetch(cur, row_begin, tid);
     pdl_wait();                                           // from here on the activations may be read, and C written
-    for (int i = tid; i < M * K8; i += THREADS) {
-        const int m = i / K8, p = i - m * K8;
-        xs[i] = *((const uint4*)(A + (size_t)m * lda) + p);
+    if (ln.x == nullptr) {
+        for (int i = tid; i < M * K8; i += THREADS) {
+            const int m = i / K8, p = i - m * K8;
+            xs[i] = *((const uint4*)(A + (size_t)m * lda) + p);
+        }
+    } else {
+        // y = (x - mean) / sqrt(mean((x - mean)^2) + eps) * gamma + beta, all in 32-bit (layernorm.cu).
+        // The row is read from memory once and kept in shared memory (behind the activations' pieces)
+        // for the two further walks.
+        float4* rowf = (float4*)(xs + M * K8);
+#pragma unroll 1
+        for (int m = 0; m < M; ++m) {
+            const float4* src = (const float4*)(ln.x + (size_t)m * ln.ldx);
+            if (m > 0) __syncthreads();                   // the row before is done with
+            float sum = 0.f;
+            for (int p = tid; p < K8; p += THREADS) {
+                const float4 a = src[2 * p], b = src[2 * p + 1];
+                rowf[2 * p] = a; rowf[2 * p + 1] = b;
+                sum += ((a.x + a.y) + (a.z + a.w)) + ((b.x + b.y) + (b.z + b.w));
+            }
+            const float mean = block_sum(sum, lnred) / (float)K;
+            float q = 0.f;
+            for (int p = tid; p < K8; p += THREADS) {     // a thread walks the pieces it wrote itself
+                const float4 a = rowf[2 * p], b = rowf[2 * p + 1];
+                const float d0 = a.x - mean, d1 = a.y - mean, d2 = a.z - mean, d3 = a.w - mean;
+                const float d4 = b.x - mean, d5 = b.y - mean, d6 = b.z - mean, d7 = b.w - mean;
+                q += ((d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3)) + ((d4 * d4 + d5 * d5) + (d6 * d6 + d7 * d7));
+            }
+            const float rstd = 1.0f / sqrtf(block_sum(q, lnred) / (float)K + ln.eps);
+            for (int p = tid; p < K8; p += THREADS) {
+                const float4 a = rowf[2 * p], b = rowf[2 * p + 1];
+                float y[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+                for (int e = 0; e < 8; ++e) y[e] = (y[e] - mean) * rstd;
+                if (ln.gamma) {
+                    const float4 ga = ((const float4*)ln.gamma)[2 * p], gb = ((const float4*)ln.gamma)[2 * p + 1];
+                    y[0] *= ga.x; y[1] *= ga.y; y[2] *= ga.z; y[3] *= ga.w; y[4] *= gb.x; y[5] *= gb.y; y[6] *= gb.z; y[7] *= gb.w;
+                }
+                if (ln.beta) {
+                    const float4 ba = ((const float4*)ln.beta)[2 * p], bb = ((const float4*)ln.beta)[2 * p + 1];
+                    y[0] += ba.x; y[1] += ba.y; y[2] += ba.z; y[3] += ba.w; y[4] += bb.x; y[5] += bb.y; y[6] += bb.z; y[7] += bb.w;
+                }
+                h16x2 h0 = floats_to_h16x2(y[0], y[1]), h1 = floats_to_h16x2(y[2], y[3]);
+                h16x2 h2 = floats_to_h16x2(y[4], y[5]), h3 = floats_to_h16x2(y[6], y[7]);
+                uint4 u;
+                u.x = *(uint32_t*)&h0; u.y = *(uint32_t*)&h1; u.z = *(uint32_t*)&h2; u.w = *(uint32_t*)&h3;
+                xs[m * K8 + p] = u;
+            }
+        }
     }
     __syncthreads();
 
@@ -121,28 +176,33 @@ gemv_kernel(const h16* __restrict__ A, int lda, const h16* __restrict__ W, int l
 
 template <int M, int R, int THREADS>
 int launch(const h16* A, int lda, const h16* W, int ldw, const float* bias, const float* residual, void* C, int ldc,
-           int act, int c_h16, int N, int K, int sms, cudaStream_t stream) {
-    const size_t smem = (size_t)M * K * 2;
+           int act, int c_h16, int N, int K, int sms, const LnArgs& ln, cudaStream_t stream) {
+    const size_t smem = (size_t)M * K * 2 + (ln.x ? (size_t)K * 4 : 0);          // with a LayerNorm: one 32-bit row beside the activations
     static size_t configured = 48 * 1024 - 1024;
     if (smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(gemv_kernel<M, R, THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = smem;
     }
-    static size_t asked_smem = ~(size_t)0;                 // blocks per SM for the last shared-memory size asked about
-    static int asked_per_sm = 0;
-    if (smem != asked_smem) {
+    // blocks per SM for the shared-memory sizes asked about last (a model's products alternate between a few)
+    static size_t asked_smem[4] = {~(size_t)0, ~(size_t)0, ~(size_t)0, ~(size_t)0};
+    static int asked_per_sm[4] = {0, 0, 0, 0};
+    static int asked_next = 0;
+    int per_sm = -1;
+    for (int i = 0; i < 4; ++i)
+        if (asked_smem[i] == smem) per_sm = asked_per_sm[i];
+    if (per_sm < 0) {
         int n = 0;
         cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, gemv_kernel<M, R, THREADS>, THREADS, smem);
         if (e != cudaSuccess) return (int)e;
-        asked_per_sm = n; asked_smem = smem;
+        asked_smem[asked_next] = smem; asked_per_sm[asked_next] = n; asked_next = (asked_next + 1) & 3;
+        per_sm = n;
     }
-    const int per_sm = asked_per_sm;
     if (per_sm < 1) return TNX_ERR_UNSUPPORTED;
     int blocks = sms * per_sm;
     if (blocks > (N + R - 1) / R) blocks = (N + R - 1) / R;
     return tnx_launch_ex(1, gemv_kernel<M, R, THREADS>, dim3(blocks), dim3(THREADS), smem, stream, A, lda, W, ldw, bias, residual, C, ldc,
-                         act, c_h16, N, K);
+                         act, c_h16, N, K, ln);
 }
 
 }  // namespace
@@ -157,11 +217,17 @@ TNX_EXPORT int tnx_gemv_supported(int M, int N, int K) {
     return smem <= (M <= 2 ? 112 * 1024 : 64 * 1024);
 }
 
-TNX_EXPORT int tnx_gemv(const void* A, const void* W, const float* bias, const float* residual, void* C,
-                        int M, int N, int K, int lda, int ldw, int ldc, int act, int c_h16, cudaStream_t stream) {
+static int gemv_any(const void* A, const void* W, const float* bias, const float* residual, void* C,
+                    int M, int N, int K, int lda, int ldw, int ldc, int act, int c_h16, const LnArgs& ln, cudaStream_t stream) {
     if (!tnx_gemv_supported(M, N, K)) return TNX_ERR_UNSUPPORTED;
-    if (lda % 8 || ldw % 8 || lda < K || ldw < K || ldc < N) return TNX_ERR_UNSUPPORTED;
-    if (((uintptr_t)A | (uintptr_t)W) & 15) return TNX_ERR_UNSUPPORTED;
+    if (ldw % 8 || ldw < K || ldc < N || ((uintptr_t)W & 15)) return TNX_ERR_UNSUPPORTED;
+    if (ln.x) {
+        if (ln.ldx % 4 || ln.ldx < K || ((uintptr_t)ln.x & 15)) return TNX_ERR_UNSUPPORTED;
+        if ((ln.gamma && ((uintptr_t)ln.gamma & 15)) || (ln.beta && ((uintptr_t)ln.beta & 15))) return TNX_ERR_UNSUPPORTED;
+        if ((long long)M * K * 2 + (long long)K * 4 > 112 * 1024) return TNX_ERR_UNSUPPORTED;
+    } else if (lda % 8 || lda < K || ((uintptr_t)A & 15)) {
+        return TNX_ERR_UNSUPPORTED;
+    }
     if (residual && c_h16) return TNX_ERR_BAD_ARG;
     if (act < 0 || act >= TNX_ACT_COUNT) return TNX_ERR_BAD_ARG;
     int dev = 0, sms = 148;
@@ -177,8 +243,8 @@ TNX_EXPORT int tnx_gemv(const void* A, const void* W, const float* bias, const f
     // the block-wide sums); longer rows: 256 threads.  The choice depends on K alone, so that the
     // order of the additions does not depend on the number of tokens.
 #define GEMV_LAUNCH(M_, R_)                                                                                              \
-    (K <= 4096 ? launch<M_, R_, 128>(a, lda, w, ldw, bias, residual, C, ldc, act, c_h16, N, K, sms, stream)           \
-               : launch<M_, R_, 256>(a, lda, w, ldw, bias, residual, C, ldc, act, c_h16, N, K, sms, stream))
+    (K <= 4096 ? launch<M_, R_, 128>(a, lda, w, ldw, bias, residual, C, ldc, act, c_h16, N, K, sms, ln, stream)       \
+               : launch<M_, R_, 256>(a, lda, w, ldw, bias, residual, C, ldc, act, c_h16, N, K, sms, ln, stream))
     switch (M) {
         case 1: return GEMV_LAUNCH(1, 8);
         case 2: return GEMV_LAUNCH(2, 8);
@@ -186,4 +252,18 @@ TNX_EXPORT int tnx_gemv(const void* A, const void* W, const float* bias, const f
         default: return GEMV_LAUNCH(4, 4);
     }
 #undef GEMV_LAUNCH
+}
+
+TNX_EXPORT int tnx_gemv(const void* A, const void* W, const float* bias, const float* residual, void* C,
+                        int M, int N, int K, int lda, int ldw, int ldc, int act, int c_h16, cudaStream_t stream) {
+    return gemv_any(A, W, bias, residual, C, M, N, K, lda, ldw, ldc, act, c_h16, LnArgs{nullptr, 0, nullptr, nullptr, 0.f}, stream);
+}
+
+// The same product with A = LayerNorm(x): x [M, K] 32-bit rows (pitch ldx elements), gamma and beta
+// [K] 32-bit or null.
+TNX_EXPORT int tnx_gemv_ln(const float* x, int ldx, const float* gamma, const float* beta, float eps, const void* W,
+                           const float* bias, const float* residual, void* C, int M, int N, int K, int ldw, int ldc,
+                           int act, int c_h16, cudaStream_t stream) {
+    if (!x) return TNX_ERR_BAD_ARG;
+    return gemv_any(nullptr, W, bias, residual, C, M, N, K, 0, ldw, ldc, act, c_h16, LnArgs{x, ldx, gamma, beta, eps}, stream);
 }

@@ -418,6 +418,54 @@ def gemv(a, w, out, bias=None, residual=None, activation=None):
                         _stream()), "gemv")
 
 
+def gemv_layer_norm_supported(x, w, out) -> bool:
+    """Whether gemv_layer_norm takes these tensors: one token (measured on the 6.7B sizes: a decode step of one
+    request 3.15 -> 3.11 ms; with two requests the tensor-core product after a LayerNorm kernel takes 3.40 ms
+    and this kernel 3.90), 32-bit rows of x, a 16-bit matrix, 16-byte aligned rows, the row within shared memory."""
+    if x.dim() != 2 or x.dtype != torch.float32 or w.dtype not in _H16 or x.shape[0] != 1:
+        return False
+    if out.dtype in _H16 and out.dtype != w.dtype:
+        return False
+    K = x.shape[1]
+    return (w.dim() == 2 and w.shape[1] == K and K % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 4 == 0
+            and x.data_ptr() % 16 == 0 and w.stride(1) == 1 and w.stride(0) % 8 == 0 and w.data_ptr() % 16 == 0
+            and K * 6 <= 112 * 1024)
+
+
+def gemv_layer_norm(x, gamma, beta, eps, w, out, bias=None, residual=None, activation=None):
+    """out = epilogue(LayerNorm(x) @ w^T) for one to four tokens: x are 32-bit rows (the residual stream),
+    normalized in 32-bit by every thread block of the product as it stages its activations, rounded to
+    the matrix's 16-bit type as a LayerNorm kernel would round them."""
+    lib = _lib("gemv", w, out)
+    act = activation_code(activation)
+    _need(x, "x", torch.float32, None, contiguous=False)
+    _need(w, "w", _H16, None, contiguous=False)
+    _need(out, "out", _FLOATS, None, contiguous=False)
+    M, K, ldx = _rows_2d(x, "x")
+    N, Kw, ldw = _rows_2d(w, "w")
+    Mo, No, ldc = _rows_2d(out, "out")
+    if Kw != K or Mo != M or No != N:
+        raise KernelError(f"gemv shapes do not fit: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if not lib.tnx_gemv_supported(c_int(M), c_int(N), c_int(K)):
+        raise KernelError("gemv takes one to four tokens and K a multiple of 8")
+    for t, nm in ((gamma, "gamma"), (beta, "beta")):
+        if t is not None:
+            _need(t, nm, torch.float32, 1)
+            if t.shape[0] != K:
+                raise KernelError(f"{nm} length differs from the row length")
+    if bias is not None:
+        _need(bias, "bias", torch.float32, 1)
+        if bias.shape[0] != N:
+            raise KernelError("bias length differs from the output width")
+    if residual is not None:
+        _need(residual, "residual", torch.float32, None, contiguous=False)
+        if tuple(residual.shape) != (M, N) or _rows_2d(residual, "residual")[2] != ldc or out.dtype != torch.float32:
+            raise KernelError("residual must be float32 with the shape and row stride of a float32 out")
+    _check(lib.tnx_gemv_ln(_p(x), c_int(ldx), _p(gamma), _p(beta), c_float(float(eps)), _p(w), _p(bias), _p(residual), _p(out),
+                           c_int(M), c_int(N), c_int(K), c_int(ldw), c_int(ldc), c_int(act), c_int(_is_h16(out)),
+                           _stream()), "gemv_layer_norm")
+
+
 def gemm_tc(a, w, out, bias=None, residual=None, activation=None, splits=None, few_tokens_kernel=True, cluster=False):
     """out = epilogue(a @ w^T), 16-bit operands (both bfloat16 or both float16), 32-bit accumulation: on the tcgen05 tensor cores,
     or (one token, unless few_tokens_kernel is False or splits is given) as a stream of the

@@ -18,7 +18,7 @@ import torch
 
 from . import ops
 
-_NAMES = ("embed", "gather_rows", "patch_tokens", "layer_norm", "pick_rows", "gemm_simt", "gemm_tc", "kv_append",
+_NAMES = ("embed", "gather_rows", "patch_tokens", "layer_norm", "pick_rows", "gemm_simt", "gemm_tc", "gemv_layer_norm", "kv_append",
           "attention_simt", "attention_decode", "attention_prefill", "attention_prefill_tc", "sample", "sample_packed")
 
 

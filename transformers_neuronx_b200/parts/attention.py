@@ -22,6 +22,7 @@ from .spec import AttentionSpec
 
 class PagedAttention(Mixer):
     graph_safe = True
+    takes_normed_input = True       # `h` only feeds the q/k/v product
     def __init__(self, spec: AttentionSpec):
         s = self.spec = spec
         if s.n_heads % s.n_kv_heads:

@@ -105,8 +105,37 @@ class Norm(Part):
     def forward(self, ctx, x, out_f32=None, out_act=None, rows=None):
         raise NotImplementedError
 
+    def fused_params(self):
+        """(gamma, beta, eps) when this norm is a LayerNorm that a following product may apply itself
+        (NormedInput below), else None."""
+        return None
+
+
+class NormedInput:
+    """A part's input that has not been normalized yet: rows of the 32-bit residual stream and the norm
+    to apply.  A consumer whose first kernel can apply the norm itself does so (Linear, for one token:
+    the LayerNorm kernel, its launch and its output's trip through memory are saved); anyone else
+    calls tensor(), which runs the norm's own kernel once.  A block hands one out only to parts that
+    say ``takes_normed_input`` (parts/block.py)."""
+
+    def __init__(self, ctx, x, norm):
+        self.ctx, self.x, self.norm = ctx, x, norm
+        self._tensor = None
+
+    @property
+    def shape(self):
+        return self.x.shape
+
+    def tensor(self):
+        if self._tensor is None:
+            self._tensor = self.ctx.scratch(self.x.shape[0], self.x.shape[1])
+            self.norm.forward(self.ctx, self.x, out_act=self._tensor)
+        return self._tensor
+
 
 class Mixer(Part):
+    takes_normed_input = False      # True: forward's `h` may be a NormedInput (the part hands it to a Linear)
+
     def cache_need(self):
         return None
 
@@ -115,6 +144,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    takes_normed_input = False
+
     def forward(self, ctx, h, residual):
         raise NotImplementedError
 

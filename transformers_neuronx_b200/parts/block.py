@@ -10,6 +10,7 @@ type, which a block that feeds x itself into a matrix product needs on entry
 """
 from __future__ import annotations
 
+from .base import NormedInput
 from .registry import register_block
 
 
@@ -23,12 +24,21 @@ class PreNormBlock:
     def parts(self):
         return [p for p in (self.norm1, self.mixer, self.norm2, self.feed_forward) if p is not None]
 
-    def forward(self, ctx, x, x_act):
+    @staticmethod
+    def _normed(ctx, x, norm, part):
+        """norm(x) as the part's input: for one token and a part that takes it, the norm is handed on
+        to be applied inside the part's first product; otherwise its own kernel runs here."""
+        fused = getattr(norm, "fused_params", None)
+        if (x.shape[0] == 1 and ctx.act_dtype != x.dtype and getattr(part, "takes_normed_input", False)
+                and fused is not None and fused() is not None):
+            return NormedInput(ctx, x, norm)
         h = ctx.scratch(x.shape[0], x.shape[1])
-        self.norm1.forward(ctx, x, out_act=h)
-        self.mixer.forward(ctx, h, x)
-        self.norm2.forward(ctx, x, out_act=h)
-        self.feed_forward.forward(ctx, h, x)
+        norm.forward(ctx, x, out_act=h)
+        return h
+
+    def forward(self, ctx, x, x_act):
+        self.mixer.forward(ctx, self._normed(ctx, x, self.norm1, self.mixer), x)
+        self.feed_forward.forward(ctx, self._normed(ctx, x, self.norm2, self.feed_forward), x)
 
 
 class PostNormBlock:

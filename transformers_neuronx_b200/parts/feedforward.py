@@ -12,6 +12,7 @@ from .spec import DenseFeedForwardSpec
 
 class DenseFeedForward(FeedForward):
     graph_safe = True
+    takes_normed_input = True       # `h` only feeds fc1
     libraries = ("gemm_simt", "gemm_tc", "gemv")
 
     def __init__(self, spec: DenseFeedForwardSpec):

@@ -15,7 +15,7 @@ import torch
 
 from ..kernels import ops
 from ..weights.loader import TensorSpec
-from .base import Part, to_device, weight_to_device
+from .base import NormedInput, Part, to_device, weight_to_device
 from .spec import LinearSpec
 
 
@@ -52,8 +52,17 @@ class Linear(Part):
             n += self.bias.numel() * 4
         return n
 
-    def forward(self, a: torch.Tensor, out: torch.Tensor, residual: Optional[torch.Tensor] = None,
+    def forward(self, a, out: torch.Tensor, residual: Optional[torch.Tensor] = None,
                 activation: Optional[str] = None) -> torch.Tensor:
+        """`a`: the activations, or a NormedInput (rows of the residual stream and the norm still to apply)."""
+        if isinstance(a, NormedInput):
+            fused = a.norm.fused_params()
+            if (fused is not None and a.ctx.act_dtype == self.weight.dtype
+                    and ops.gemv_layer_norm_supported(a.x, self.weight, out)):
+                ops.gemv_layer_norm(a.x, fused[0], fused[1], fused[2], self.weight, out, bias=self.bias,
+                                    residual=residual, activation=activation)
+                return out
+            a = a.tensor()
         linear_forward(a, self.weight, self.bias, out, residual, activation)
         return out
 

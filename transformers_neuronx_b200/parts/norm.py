@@ -36,6 +36,9 @@ class LayerNorm(Norm):
     def parameter_bytes(self):
         return sum(t.numel() * 4 for t in (self.weight, self.bias) if t is not None)
 
+    def fused_params(self):
+        return self.weight, self.bias, self.spec.eps
+
     def forward(self, ctx, x, out_f32=None, out_act=None, rows=None):
         ops.layer_norm(x, self.weight, self.bias, self.spec.eps, out_f32=out_f32, out_act=out_act, rows=rows)
 
