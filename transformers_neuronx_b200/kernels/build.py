@@ -162,9 +162,23 @@ def build(name: str, verbose: bool = True) -> str:
                 os.remove(tmp)
             raise KernelBuildError(f"nvcc failed on {src}:\n{log}")
         os.replace(tmp, out)
+        _drop_older_builds(out)
         if verbose:
             _say(f"built {os.path.basename(out)} in {time.time() - t0:.1f} s")
         return out
+
+
+def _drop_older_builds(current: str) -> None:
+    """Removes the binaries of earlier versions of the same source and flavour (a process that has one
+    loaded keeps its mapping).  Best effort: a folder that is not ours to write is left as it is."""
+    folder, keep = os.path.dirname(current), os.path.basename(current)
+    stem = keep.rsplit(".", 2)[0]                      # "gemm_tc" or "gemm_tc.f16"
+    try:
+        for f in os.listdir(folder):
+            if f != keep and f.endswith(".so") and f.rsplit(".", 2)[0] == stem and len(f.rsplit(".", 2)) == 3:
+                os.remove(os.path.join(folder, f))
+    except OSError:
+        pass
 
 
 def export_libraries(names: Iterable[str], directory: str) -> List[str]:
