@@ -93,7 +93,7 @@ __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-// Grid (blocks a row, rows), clusters of (blocks a row, 1).
+// Grid (rows, blocks a row), clusters of (1, blocks a row): the rows on the axis that has no limit worth the name.
 template <bool TOP_P>
 __global__ void __launch_bounds__(THREADS)
 sample_kernel(const float* __restrict__ logits, int ld, int V, const SampleArgs a, int* __restrict__ out) {
@@ -112,8 +112,8 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const SampleArgs 
     pdl_launch_dependents();
     pdl_wait();
 
-    const int r = blockIdx.y, tid = threadIdx.x;
-    const int CS = gridDim.x, rank = blockIdx.x;
+    const int r = blockIdx.x, tid = threadIdx.x;
+    const int CS = gridDim.y, rank = blockIdx.y;
     const int slice = (V + CS - 1) / CS;
     const int v_lo = min(V, rank * slice), v_hi = min(V, v_lo + slice);          // this block's tokens
     int xp = 0;                                                  // exchanges so far (the same in every block)
@@ -460,8 +460,8 @@ int blocks_per_row(int n_rows, int V) {
 int launch_sample(bool with_top_p, int n_rows, int V, cudaStream_t stream, const float* logits, int ld, const SampleArgs& a, int* out) {
     const int c = blocks_per_row(n_rows, V);
     if (with_top_p)
-        return tnx_launch_cluster(0, dim3(c), sample_kernel<true>, dim3(c, n_rows), dim3(THREADS), 0, stream, logits, ld, V, a, out);
-    return tnx_launch_cluster(0, dim3(c), sample_kernel<false>, dim3(c, n_rows), dim3(THREADS), 0, stream, logits, ld, V, a, out);
+        return tnx_launch_cluster(0, dim3(1, c), sample_kernel<true>, dim3(n_rows, c), dim3(THREADS), 0, stream, logits, ld, V, a, out);
+    return tnx_launch_cluster(0, dim3(1, c), sample_kernel<false>, dim3(n_rows, c), dim3(THREADS), 0, stream, logits, ld, V, a, out);
 }
 
 }  // namespace
