@@ -135,3 +135,56 @@ def test_random_orders(seed):
         m.free_request(rid)
     assert all(f == 12 for f in m.free_pages()) and m.slots.num_free == 4
     assert any(p.reuse_count > 0 for p in m.pools)
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_reorder_moves_pages_and_names_the_copies(seed):
+    """Beam search's reorder: request i goes on from what request sources[i] holds.  Pages change hands
+    without a copy for the first request that names a source; the others get the pages of requests that
+    nobody goes on from, with the copies to make.  No page is lost or held twice, sources and
+    destinations of copies are disjoint, and after 'copying' every request's pages hold its source's data."""
+    rng = random.Random(seed)
+    cm = CacheManager(group_needs({0: PagedKVNeed(2, 16), 1: PagedKVNeed(2, 16, window=40)}), 16, 200, 8)
+    n = rng.randint(2, 6)
+    rids = [f"b{i}" for i in range(n)]
+    length = rng.randint(1, 150)
+    for r in rids:
+        cm.add_request(r)
+        cm.append(r, length)
+        cm.release_behind_window(r)
+    other = "bystander"
+    cm.add_request(other); cm.append(other, 33)
+    content = {}                      # (group, page) -> whose data it holds
+    for i, r in enumerate(rids):
+        for g in range(2):
+            for p in cm.block_table(r, g):
+                if p >= 0:
+                    content[(g, p)] = i
+    bystander_pages = [list(cm.block_table(other, g)) for g in range(2)]
+    for _ in range(4):
+        sources = [rng.randrange(n) for _ in range(n)]
+        want = {i: None for i in range(n)}
+        before = {i: content[(0, next(p for p in cm.block_table(rids[i], 0) if p >= 0))] for i in range(n)}
+        copies, slot_copies = cm.reorder(rids, sources)
+        cm.check()
+        for g in range(2):
+            srcs, dsts = {s for s, _ in copies[g]}, {d for _, d in copies[g]}
+            assert not (srcs & dsts), "a page is both read and written"
+            assert len(dsts) == len(copies[g]), "a page is written twice"
+            for s, d in copies[g]:
+                content[(g, d)] = content[(g, s)]
+        for i, r in enumerate(rids):
+            for g in range(2):
+                held = [p for p in cm.block_table(r, g) if p >= 0]
+                assert held, "the last block is always held"
+                assert {content[(g, p)] for p in held} == {before[sources[i]]}, "the request holds its source's data"
+        assert sorted(slot_copies) == sorted((cm.slot(rids[s]), cm.slot(rids[i])) for i, s in enumerate(sources) if s != i)
+        assert [list(cm.block_table(other, g)) for g in range(2)] == bystander_pages
+    free_before = cm.free_pages()
+    with pytest.raises(ValueError, match="same number"):
+        cm.append(rids[0], 1)
+        cm.reorder(rids, list(range(n)))
+    for r in rids + [other]:
+        cm.free_request(r)
+    cm.check()
+    assert cm.free_pages() == [200, 200]

@@ -303,9 +303,104 @@ def test_generate_adapter_with_left_padded_rows(tiny):
     assert torch.equal(sampled, adapter.generate(ids, attention_mask=mask, max_new_tokens=6, do_sample=True, top_k=5,
                                                  temperature=0.8, seed=3))
     with pytest.raises(NotImplementedError):
-        adapter.generate(ids, num_beams=4)
+        adapter.generate(ids, num_beams=4, do_sample=True)
     with pytest.raises(TypeError):
         adapter.generate(ids, logits_processor=[])
+
+
+def test_reorder_cache_lets_a_row_go_on_from_another(tiny):
+    """The cache side of beam search: after reorder_cache(ids) row i holds what row ids[i] held; a row that
+    two rows go on from is copied, the others' pages only change hands.  The next token's logits are those
+    of the source's prompt, whatever is done twice in a row."""
+    from transformers_neuronx_b200.opt.model import OPTForSampling
+    model = OPTForSampling.from_pretrained(tiny.folder, batch_size=5, amp="f32", n_positions=64).to_neuron()
+    prompts = [tiny.random_ids(21, seed=70 + i) for i in range(5)]
+    model(torch.tensor(prompts), None, None)
+    cache = model.engine.runner.cache
+    held = [list(cache.block_table(f"row{i}")) for i in range(5)]
+    history = [list(p) for p in prompts]
+    for step, ids in enumerate(([2, 2, 0, 4, 2], [1, 0, 3, 3, 3], [0, 1, 2, 3, 4])):
+        model.reorder_cache(ids)
+        cache.check()
+        history = [list(history[i]) for i in ids]
+        nxt = [7 + step, 8, 9, 10, 11 + step]
+        lg = model(torch.tensor(nxt)[:, None], torch.tensor([21 + step]), None)
+        for i in range(5):
+            history[i].append(nxt[i])
+            want = tiny.plain_logits(history[i])[-1]
+            assert float((lg[i] - want).abs().max()) / float(want.abs().max()) <= TOLERANCE["float32"], (step, i)
+    assert sorted(p for t in held for p in t) == sorted(p for i in range(5) for p in cache.block_table(f"row{i}")[:len(held[0])])
+    with pytest.raises(ValueError):
+        model.reorder_cache([0, 1])
+
+
+def _plain_beam_search(tiny, prompt, nb, n_new, eos, length_penalty=1.0, early_stopping=False):
+    """Beam search restated over whole sequences: every step the plain implementation reads each running
+    sequence from its first token (no cache, nothing reordered)."""
+    running = [(0.0, [])]
+    ended = []
+    for step in range(n_new):
+        cands = []
+        for score, toks in running:
+            logp = torch.log_softmax(tiny.plain_logits(list(prompt) + toks)[-1].float(), -1)
+            top = torch.topk(logp, min(2 * nb, logp.numel()))
+            cands += [(score + float(v), toks, int(t)) for v, t in zip(top.values, top.indices)]
+        cands.sort(key=lambda c: -c[0])
+        cands = cands[:2 * nb]
+        nxt = []
+        for rank, (v, toks, t) in enumerate(cands):
+            if t in eos:
+                if rank < nb:
+                    ended.append((v / (len(toks) + 1) ** length_penalty, toks + [t]))
+                continue
+            nxt.append((v, toks + [t]))
+            if len(nxt) == nb:
+                break
+        running = nxt
+        if len(ended) >= nb:
+            ended = sorted(ended, key=lambda h: -h[0])[:nb]
+            best = max((r[0] for r in running), default=float("-inf")) / (step + 1) ** length_penalty
+            if early_stopping or not running or best <= ended[-1][0]:
+                return max(ended, key=lambda h: h[0])[1]
+        if not running:
+            break
+    cands = ended + [(v / len(t) ** length_penalty, t) for v, t in running if t]
+    return max(cands, key=lambda h: h[0])[1]
+
+
+@pytest.mark.parametrize("nb,lp,early", [(3, 1.0, False), (4, 0.6, True), (2, 1.5, False)])
+def test_beam_search_through_the_adapter(tiny, nb, lp, early):
+    """generate(num_beams=...) against a beam search over the plain implementation's logits: left-padded
+    prompts of different lengths, an eos id that ends some beams early, length penalty and early stopping."""
+    from transformers_neuronx_b200.generation_utils import HuggingFaceGenerationModelAdapter
+    from transformers_neuronx_b200.opt.model import OPTForSampling
+    model = OPTForSampling.from_pretrained(tiny.folder, batch_size=2 * nb, amp="f32", n_positions=40).to_neuron()
+    adapter = HuggingFaceGenerationModelAdapter(model.config, model)
+    prompts = [tiny.random_ids(n, seed=90 + n) for n in (6, 11)]
+    pad = tiny.cfg.pad_token_id
+    ids = torch.tensor([[pad] * (11 - len(p)) + p for p in prompts])
+    mask = torch.tensor([[0] * (11 - len(p)) + [1] * len(p) for p in prompts])
+    n_new = 9
+    free = _plain_beam_search(tiny, prompts[0], nb, n_new, set(), lp, early)
+    eos = free[4]                                            # a token that the best beam of prompt 0 reaches
+    out = adapter.generate(ids, attention_mask=mask, num_beams=nb, max_new_tokens=n_new, eos_token_id=eos,
+                           pad_token_id=pad, length_penalty=lp, early_stopping=early)
+    assert torch.equal(out[:, :11], ids)
+    longest = 0
+    for b in range(2):
+        want = _plain_beam_search(tiny, prompts[b], nb, n_new, {eos}, lp, early)
+        got = out[b, 11:].tolist()
+        assert got[:len(want)] == want, (b, got, want)
+        assert all(t == pad for t in got[len(want):])
+        longest = max(longest, len(want))
+    assert out.shape[1] == 11 + longest
+    model.engine.runner.cache.check()
+    assert model.engine.runner.cache.live_requests() == []
+    # without an eos id every beam runs to the limit and the most likely one is returned
+    out2 = adapter.generate(ids, attention_mask=mask, num_beams=nb, max_new_tokens=n_new, length_penalty=lp)
+    assert out2[0, 11:].tolist() == _plain_beam_search(tiny, prompts[0], nb, n_new, set(), lp, False)
+    with pytest.raises(ValueError, match="batch_size"):
+        adapter.generate(ids, num_beams=nb + 1, max_new_tokens=2)
 
 
 def test_all_logits_of_a_prompt_and_kept_kernels(tiny, tmp_path):

@@ -275,6 +275,34 @@ def test_toy_parts_are_registered_built_and_stepped():
     runner.finish("c")
 
 
+def test_reorder_carries_state_of_fixed_size_and_windowed_pages():
+    """StepRunner.reorder on the toy model: a request goes on from another one's recurrent state (slots'
+    rows, which may be read and written by the same reorder: a swap) and from its attention pages behind a
+    window (some of them released already)."""
+    from transformers_neuronx_b200.engine import StepEntry, StepRunner
+    model, t, spec = _toy_model("float32")
+    runner = StepRunner(model, 16, 24, 4, 256)
+    g = torch.Generator().manual_seed(9)
+    rids = ["a", "b", "c", "d"]
+    hist = {r: torch.randint(0, 97, (45,), generator=g).tolist() for r in rids}
+    for r in rids:
+        runner.add_request(r)
+    runner.step([StepEntry(r, hist[r], []) for r in rids])
+    for sources in ([1, 0, 0, 3], [2, 2, 2, 2], [3, 0, 1, 2]):
+        runner.reorder(rids, sources)
+        runner.cache.check()
+        hist = {r: list(hist[rids[s]]) for r, s in zip(rids, sources)}
+        nxt = torch.randint(0, 97, (4,), generator=g).tolist()
+        logits = runner.step([StepEntry(r, [nxt[i]], [0]) for i, r in enumerate(rids)]).cpu()
+        for i, r in enumerate(rids):
+            hist[r].append(nxt[i])
+            assert rel_err(logits[i], _toy_plain(hist[r], t)[-1]) <= 5e-5, (sources, r)
+    for r in rids:
+        runner.finish(r)
+    runner.cache.check()
+    assert runner.cache.free_pages() == [24]
+
+
 def test_toy_feed_forward_with_routing():
     """A feed-forward that routes each token to one of three experts (router logits in 32-bit, top-1),
     defined here, registered and stepped in portions beside the framework's attention."""

@@ -64,6 +64,16 @@ class PagePool:
             self._owner[p] = None
             self._free.append(p)
 
+    def transfer(self, pages, owner: Hashable, new_owner: Hashable) -> None:
+        """Held pages change hands (a request continues from what another one holds)."""
+        if new_owner is None:
+            raise ValueError("a page needs an owner")
+        for p in pages:
+            if not (0 <= p < self.num_pages) or self._owner[p] != owner:
+                raise ValueError(f"page {p} is not held by {owner!r}")
+        for p in pages:
+            self._owner[p] = new_owner
+
     def owner_of(self, page: int):
         return self._owner[page]
 

@@ -203,6 +203,50 @@ class CacheManager:
             pool.free([p for p in table if p >= 0], rid)
         self.slots.give_back(r.slot, rid)
 
+    def reorder(self, rids: Sequence[Hashable], sources: Sequence[int]):
+        """Request rids[i] goes on from what rids[sources[i]] holds now: what beam search asks of a cache
+        after every step (the reference gathers whole cache lines by these indices,
+        src/transformers_neuronx/decoder.py:2303-2320).  All named requests hold the same number of tokens.
+
+        No page is allocated or freed: the first request to name a source takes over that source's pages
+        as they are; every further one takes the pages of a request that nobody continues from, and
+        those pages must be overwritten with the source's.  Returns (per paged group the list of
+        (source page, destination page) to copy, the list of (source slot, destination slot) of state of
+        fixed size to copy); the caller copies on the device before the next step."""
+        n = len(rids)
+        if len(sources) != n or len(set(rids)) != n or any(not (0 <= s < n) for s in sources):
+            raise ValueError("reorder needs one source index (into the list of requests) per request")
+        reqs = [self._req[r] for r in rids]
+        if len({r.length for r in reqs}) > 1:
+            raise ValueError("the requests of a reorder must hold the same number of tokens")
+        old = [r.tables for r in reqs]
+        first_claim, extra = {}, []
+        for i, s in enumerate(sources):
+            if s in first_claim:
+                extra.append(i)
+            else:
+                first_claim[s] = i
+        orphans = [u for u in range(n) if u not in first_claim]          # as many as there are further claims
+        takes = {i: s for s, i in first_claim.items()}                    # destination -> whose tables it takes
+        takes.update(dict(zip(extra, orphans)))
+        copies = [[] for _ in self.paged_groups]
+        for i, u in zip(extra, orphans):
+            for g in range(len(self.paged_groups)):
+                for ps, pd in zip(old[sources[i]][g], old[u][g]):
+                    if (ps < 0) != (pd < 0):
+                        raise AssertionError("requests of equal length differ in the blocks they still hold")
+                    if ps >= 0:
+                        copies[g].append((ps, pd))
+        for i, j in takes.items():
+            if i != j:
+                for pool, table in zip(self.pools, old[j]):
+                    pool.transfer([p for p in table if p >= 0], rids[j], rids[i])
+        new_tables = {i: old[j] for i, j in takes.items()}
+        for i, r in enumerate(reqs):
+            r.tables = new_tables[i]
+        slot_copies = [(reqs[s].slot, reqs[i].slot) for i, s in enumerate(sources) if s != i]
+        return copies, slot_copies
+
     def slot_of_position(self, rid, pos: int, group: int = 0) -> int:
         """Physical row (page * page_size + offset) of a position in a paged group."""
         page = self._req[rid].tables[group][pos // self.page_size]

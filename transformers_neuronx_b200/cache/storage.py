@@ -46,6 +46,22 @@ class CacheStorage:
         for t in self._cleared:
             t[slot].zero_()
 
+    def copy(self, page_copies, slot_copies, device) -> None:
+        """Carries out what CacheManager.reorder returned: pages of every paged cache of a group and the
+        slots' rows of every state tensor are copied on the device (pages: sources and destinations are disjoint)."""
+        from ..kernels import ops
+        for cid, t in self._tensors.items():
+            g = self._group[cid]
+            if g >= 0:
+                if page_copies[g]:
+                    ops.copy_rows(t, torch.tensor(page_copies[g], dtype=torch.int32, device=device))
+            elif slot_copies:
+                # slots stay with their requests, so a slot may be source and destination at once:
+                # read all sources first
+                src = torch.tensor([s for s, _ in slot_copies], dtype=torch.long, device=device)
+                dst = torch.tensor([d for _, d in slot_copies], dtype=torch.long, device=device)
+                t[dst] = t[src].clone()
+
     def bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self._tensors.values())
 

@@ -48,3 +48,32 @@ TNX_EXPORT int tnx_kv_append(const void* k_src, const void* v_src, int src_strid
     return wide ? KV_LAUNCH(float, 4) : KV_LAUNCH(float, 1);
 #undef KV_LAUNCH
 }
+
+// Whole rows of a tensor copied within it: row dst[i] takes the bytes of row src[i] (pages of a cache,
+// or slots of a state tensor, when a request goes on from what another one holds: beam search).  No
+// row may be both a source and a destination.  pairs: [n_pairs][2] (source, destination).
+__global__ void copy_rows_kernel(uint8_t* __restrict__ base, const int* __restrict__ pairs, long long row_bytes) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int src = pairs[2 * blockIdx.x], dst = pairs[2 * blockIdx.x + 1];
+    if (src < 0 || dst < 0 || src == dst) return;
+    const uint8_t* s = base + (size_t)src * row_bytes;
+    uint8_t* d = base + (size_t)dst * row_bytes;
+    const long long chunk = (row_bytes + gridDim.y - 1) / gridDim.y;
+    const long long lo = (long long)blockIdx.y * chunk, hi = lo + chunk < row_bytes ? lo + chunk : row_bytes;
+    if ((((uintptr_t)s | (uintptr_t)d | (uintptr_t)chunk) & 15) == 0) {
+        for (long long o = lo + 16LL * threadIdx.x; o + 16 <= hi; o += 16LL * blockDim.x) *(uint4*)(d + o) = *(const uint4*)(s + o);
+        for (long long o = lo + ((hi - lo) & ~15LL) + threadIdx.x; o < hi; o += blockDim.x) d[o] = s[o];
+    } else {
+        for (long long o = lo + threadIdx.x; o < hi; o += blockDim.x) d[o] = s[o];
+    }
+}
+
+TNX_EXPORT int tnx_copy_rows(void* base, const int* pairs, int n_pairs, long long row_bytes, cudaStream_t stream) {
+    if (n_pairs <= 0 || row_bytes <= 0) return 0;
+    if (!base || !pairs) return TNX_ERR_BAD_ARG;
+    long long parts = (row_bytes + 16383) / 16384;                // 16 KB a block
+    if (parts > 1024) parts = 1024;
+    return tnx_launch_pdl(copy_rows_kernel, dim3(n_pairs, (unsigned)parts), dim3(256), 0, stream, (uint8_t*)base, pairs, row_bytes);
+}
+

@@ -93,6 +93,17 @@ class StepRunner:
         for g in range(self.n_groups):
             self._table_arrays.pop((rid, g), None)
 
+    def reorder(self, rids: Sequence, sources: Sequence[int]) -> None:
+        """Request rids[i] goes on from what rids[sources[i]] holds now (beam search).  The requests hold
+        equally many tokens; pages change hands where they can and are copied where two requests go on
+        from the same one."""
+        if all(s == i for i, s in enumerate(sources)):
+            return
+        page_copies, slot_copies = self.cache.reorder(list(rids), [int(s) for s in sources])
+        self.storage.copy(page_copies, slot_copies, self.device)
+        for rid in rids:
+            self.forget(rid)
+
     def pages_needed(self, entries: Sequence[StepEntry]) -> List[int]:
         tot = [0] * self.n_groups
         for e in entries:

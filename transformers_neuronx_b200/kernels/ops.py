@@ -250,6 +250,19 @@ def kv_append(k_src, v_src, slot_mapping, cache, page_size):
                              c_int(n_kv), c_int(d), c_int(ps), c_int(_is_h16(cache)), _stream()), "kv_append")
 
 
+def copy_rows(tensor, pairs):
+    """Rows (first axis) of a contiguous tensor copied within it: for each (source, destination) of the
+    int32 tensor `pairs` [n, 2], row destination takes the contents of row source.  No row may be both."""
+    lib = _build.load("kv_cache")
+    if not tensor.is_cuda or not tensor.is_contiguous() or tensor.dim() < 1:
+        raise KernelError("copy_rows needs a contiguous tensor on the GPU")
+    _need(pairs, "pairs", torch.int32, 2)
+    if pairs.shape[1] != 2:
+        raise KernelError("pairs must be [n, 2]")
+    row_bytes = tensor[0].numel() * tensor.element_size() if tensor.shape[0] else 0
+    _check(lib.tnx_copy_rows(_p(tensor), _p(pairs), c_int(pairs.shape[0]), ctypes.c_longlong(row_bytes), _stream()), "copy_rows")
+
+
 def attention_simt(q, cache, block_tables, token_request, positions, out, n_heads, scale, window=0):
     """q: [N, n_heads * head_dim] view; out likewise; cache as in kv_append."""
     lib = _lib("attention_simt", cache, q, out)

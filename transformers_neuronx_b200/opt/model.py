@@ -241,6 +241,28 @@ class OPTForSampling:
 
     __call__ = forward
 
+    def reorder_cache(self, reorder_ids) -> None:
+        """Row i of the running batch goes on from what row reorder_ids[i] holds: the cache side of beam
+        search (src/transformers_neuronx/base.py:153-154, decoder.py:2303-2320, which gather whole cache
+        lines).  Here the rows' pages change hands, and only a row that a second beam also goes on from
+        is copied.  Rows may only go on from rows that hold as many tokens (the beams of one prompt)."""
+        self._ready()
+        ids = [int(i) for i in torch.as_tensor(reorder_ids).flatten().tolist()]
+        if len(ids) != len(self._rows):
+            raise ValueError(f"reorder_cache got {len(ids)} indices for {len(self._rows)} rows")
+        runner = self.engine.runner
+        by_length = {}
+        for i, rid in enumerate(self._rows):
+            by_length.setdefault(runner.cache.length(rid), []).append(i)
+        for length, members in by_length.items():
+            local = {i: j for j, i in enumerate(members)}
+            if any(ids[i] not in local for i in members):
+                raise ValueError("a row can only go on from a row that holds as many tokens")
+            runner.reorder([self._rows[i] for i in members], [local[ids[i]] for i in members])
+
+    def setup_reorder_cache(self) -> None:
+        """The reference compiles its reorder kernel on request (base.py:156-160); nothing to prepare here."""
+
 
 class OPTForGreedySearch(OPTForSampling):
     """Greedy search with the choice made on the device (opt/model.py:534-570)."""
