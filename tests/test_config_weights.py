@@ -268,3 +268,20 @@ def test_files_agree_with_the_safetensors_package_in_both_directions(tmp_path):
             seen[k] = fl.tensor(k).clone()
         fl.close()
     assert sorted(seen) == names and all(torch.equal(seen[k], t[k]) for k in names)
+
+
+def test_entry_point_small_parity_methods(tmp_path):
+    """is_compiled() and update_generation_config(), which the reference's base class offers
+    (src/transformers_neuronx/base.py:143-151, :761-762), work without a GPU."""
+    from transformers_neuronx_b200 import GenerationConfig
+    from transformers_neuronx_b200.kernels import build as kb
+    from transformers_neuronx_b200.opt.model import OPTForSampling
+    m = OPTForSampling.from_pretrained(TinyModel("A", seed=2).folder, batch_size=2, amp="bf16", n_positions=32)
+    have = all(os.path.isfile(kb.library_path(n)) for n in ("gemm_tc", "gemv", "layernorm", "embedding", "kv_cache",
+                                                              "attention_decode", "attention_prefill", "attention_prefill_tc",
+                                                              "gemm_simt", "attention_simt"))
+    assert m.is_compiled() == have
+    m.update_generation_config(GenerationConfig(do_sample=True, top_k=7))
+    assert m.neuron_config.on_device_generation.top_k == 7
+    with pytest.raises(TypeError):
+        m.update_generation_config({"top_k": 3})

@@ -94,6 +94,26 @@ class OPTForSampling:
         from ..kernels import build as kbuild
         kbuild.import_libraries(directory)
 
+    def is_compiled(self) -> bool:
+        """Whether every kernel library this model needs is built already (base.py:143-151 asks the same of
+        its compiled kernels)."""
+        from ..kernels import build as kbuild
+        from ..models.decoder import DecoderModel
+        import torch as _torch
+        act = {"float32": _torch.float32, "bfloat16": _torch.bfloat16, "float16": _torch.float16}[self.dtype]
+        if self.model is not None:
+            libs = self.model.libraries(self.model.act_dtype)
+        else:
+            arch, cfg = load_config(self.folder)
+            libs = DecoderModel(arch.build_spec(cfg)).libraries(act)
+        return all(os.path.isfile(kbuild.library_path(n)) for n in kbuild.with_flavour(libs, act))
+
+    def update_generation_config(self, generation_config: GenerationConfig) -> None:
+        """Replaces the on-device generation settings; the next sample() call uses them (base.py:761-762)."""
+        if not isinstance(generation_config, GenerationConfig):
+            raise TypeError("generation_config must be a GenerationConfig of this package")
+        self.neuron_config.on_device_generation = generation_config
+
     def _ready(self):
         if self.engine is None:
             self.to_neuron()
