@@ -276,7 +276,8 @@ def test_entry_point_small_parity_methods(tmp_path):
     from transformers_neuronx_b200 import GenerationConfig
     from transformers_neuronx_b200.kernels import build as kb
     from transformers_neuronx_b200.opt.model import OPTForSampling
-    m = OPTForSampling.from_pretrained(TinyModel("A", seed=2).folder, batch_size=2, amp="bf16", n_positions=32)
+    tiny = TinyModel("A", seed=2)
+    m = OPTForSampling.from_pretrained(tiny.folder, batch_size=2, amp="bf16", n_positions=32)
     have = all(os.path.isfile(kb.library_path(n)) for n in ("gemm_tc", "gemv", "layernorm", "embedding", "kv_cache",
                                                               "attention_decode", "attention_prefill", "attention_prefill_tc",
                                                               "gemm_simt", "attention_simt"))
