@@ -442,6 +442,20 @@ def test_kernel_profile(tiny):
     assert ops.embed.__name__ == "embed"                      # the wrappers are gone
 
 
+def test_profile_of_the_entry_point(tiny, tmp_path):
+    """model.profile(dir), under the reference's name: a report per kernel family, written to the folder."""
+    from transformers_neuronx_b200.opt.model import OPTForSampling
+    model = OPTForSampling.from_pretrained(tiny.folder, batch_size=2, amp="bf16", n_positions=48).to_neuron()
+    assert model.is_compiled()
+    report = model.profile(str(tmp_path / "prof"))
+    assert open(tmp_path / "prof" / "kernel_profile.txt").read() == report
+    for word in ("layer_norm", "embed", "share", "decode steps"):
+        assert word in report
+    assert model.engine.runner.cache.live_requests() == []
+    out = model.sample(torch.tensor([tiny.random_ids(5, seed=3)] * 2), sequence_length=12, top_k=1)      # still usable
+    assert out.shape == (2, 12)
+
+
 def test_command_line_save_and_run(tmp_path):
     cfg = tmp_path / "cfg.json"
     import json

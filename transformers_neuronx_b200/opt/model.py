@@ -108,6 +108,35 @@ class OPTForSampling:
             libs = DecoderModel(arch.build_spec(cfg)).libraries(act)
         return all(os.path.isfile(kbuild.library_path(n)) for n in kbuild.with_flavour(libs, act))
 
+    def profile(self, profile_dir: str, ntff_count_limit=None) -> str:
+        """Where the time of a prompt step and a few decode steps goes, kernel family by kernel family
+        (CUDA events around every kernel call, graphs off meanwhile), written to
+        `profile_dir`/kernel_profile.txt and returned.  The reference runs each compiled kernel under the
+        Neuron profiler here (base.py:754-759); `ntff_count_limit` is its option and has no meaning here."""
+        from ..kernels.profile import kernel_profile
+        self._ready()
+        self.reset()
+        runner = self.engine.runner
+        n_prompt = max(1, min(64, self.n_positions // 2))
+        n_decode = max(0, min(8, self.n_positions - n_prompt - 1))
+        ids = [[self.config.bos_token_id] + [3 + (7 * i + b) % (self.config.vocab_size - 3) for i in range(1, n_prompt)]
+               for b in range(self.batch_size)]
+        graphs, runner.use_cuda_graphs = runner.use_cuda_graphs, False
+        try:
+            with kernel_profile() as prof:
+                self.forward(torch.tensor(ids))
+                for t in range(n_decode):
+                    self.forward(torch.full((self.batch_size, 1), 5, dtype=torch.long), torch.tensor([n_prompt + t]))
+            report = (f"{self.batch_size} rows: one step of {n_prompt}-token prompts and {n_decode} decode steps, "
+                      f"{self.dtype}\n" + prof.report() + "\n")
+        finally:
+            runner.use_cuda_graphs = graphs
+            self.reset()
+        os.makedirs(profile_dir, exist_ok=True)
+        with open(os.path.join(profile_dir, "kernel_profile.txt"), "w") as fp:
+            fp.write(report)
+        return report
+
     def update_generation_config(self, generation_config: GenerationConfig) -> None:
         """Replaces the on-device generation settings; the next sample() call uses them (base.py:761-762)."""
         if not isinstance(generation_config, GenerationConfig):
