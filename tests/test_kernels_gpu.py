@@ -553,6 +553,25 @@ def test_kv_append(dt):
     assert int((cache != 0).sum()) <= 2 * N * n_kv * d
 
 
+@pytest.mark.parametrize("shape,dtype", [((9, 2, 3, 16, 48), torch.bfloat16), ((7, 33), torch.float32), ((5, 2, 2, 16, 128), torch.float16),
+                                         ((6, 1000003), torch.uint8)])
+def test_copy_rows(shape, dtype):
+    """Rows copied within a tensor (pages of a cache, slots of a state tensor): sources and destinations
+    disjoint, pairs with a -1 or with equal ends skipped, everything else untouched."""
+    g = torch.Generator().manual_seed(len(shape))
+    t = (torch.randn(*shape, generator=g) * 50).to(dtype).to(DEV) if dtype != torch.uint8 else \
+        torch.randint(0, 255, shape, dtype=torch.uint8, generator=g).to(DEV)
+    before = t.clone()
+    pairs = torch.tensor([[0, 3], [1, 4], [1, 2], [-1, 0], [0, -1]], dtype=torch.int32, device=DEV)
+    ops().copy_rows(t, pairs)
+    want = before.clone()
+    for s, d in ((0, 3), (1, 4), (1, 2)):
+        want[d] = before[s]
+    assert torch.equal(t, want)
+    with pytest.raises(ops().KernelError):
+        ops().copy_rows(t.transpose(0, 1) if t.dim() > 1 else t[::2], pairs)
+
+
 def test_sampling_greedy_and_ties():
     logits = torch.randn(9, 50272, generator=torch.Generator().manual_seed(3)).to(DEV)
     logits[2, 777] = logits[2, 40000] = 99.0                  # a tie: the lowest index wins
