@@ -174,6 +174,49 @@ def test_head_size_80(dtype):
     compare_trace(tiny, reqs, steps, res, dtype)
 
 
+def _random_trace(rng, tiny, n_req, max_live):
+    """Requests of random lengths cut at random: single tokens, portions of 2 to 200 tokens, requests left out
+    of a step, random wanted rows, at most max_live alive; the pool is sized for the peak, so pages come back."""
+    maxlen = tiny.cfg.max_position_embeddings
+    reqs = {f"q{i}": tiny.random_ids(rng.randint(1, maxlen), seed=rng.randrange(10 ** 6)) for i in range(n_req)}
+    waiting, live, steps, peak = list(reqs), {}, [], 0
+    while waiting or live:
+        while waiting and len(live) < max_live and (not live or rng.random() < 0.7):
+            live[waiting.pop(0)] = 0
+        entries, end = [], []
+        for rid in list(live):
+            if len(live) > 1 and rng.random() < 0.2:
+                continue
+            ids, p = reqs[rid], live[rid]
+            n = 1 if rng.random() < 0.45 else rng.choice([1, 2, 3, 5, 15, 16, 17, 31, 33, 64, 65, 127, 129, 200])
+            n = min(n, len(ids) - p)
+            want = sorted(set(rng.sample(range(n), min(n, rng.choice([0, 1, 1, 2, 3])))) | ({n - 1} if rng.random() < 0.7 else set()))
+            entries.append({"id": rid, "tokens": ids[p:p + n], "want": want})
+            live[rid] = p + n
+            if live[rid] == len(ids):
+                end.append(rid)
+        if not entries:
+            continue
+        peak = max(peak, live_tokens_rounded([live[r] for r in live]))
+        steps.append({"step": len(steps), "entries": entries, "end": end})
+        for rid in end:
+            del live[rid]
+    return reqs, steps, peak
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_traces(seed):
+    """Random cuts and interleavings of random requests, one configuration per seed, in all three types."""
+    import random
+    rng = random.Random(1000 + seed)
+    name = "ABCDEF"[seed]
+    models = {dt: _model(name, dt, 31 + seed) for dt in DTYPES}
+    reqs, steps, peak = _random_trace(rng, models["float32"], rng.randint(3, 6), rng.randint(1, 4))
+    for dt in DTYPES:
+        res = run_trace_inprocess(models[dt].folder, dt, steps, peak)
+        compare_trace(models[dt], reqs, steps, res, dt)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_decode_steps_where_not_every_request_wants_logits(dtype):
     """Single-token steps (replayed as CUDA graphs) in which some entries ask for nothing."""
