@@ -139,6 +139,39 @@ def test_launching_ahead_changes_no_token(tiny):
         assert cut == want and -1 not in cut
 
 
+@pytest.mark.parametrize("seed", range(4))
+def test_a_tight_engine_generates_what_a_roomy_one_does(seed):
+    """Random requests through two engines in 32-bit: one with room for everything, whole prompts and no
+    graphs; one with few pages and slots, a small token budget, CUDA graphs and steps launched ahead, so that
+    prompts are cut, requests wait and some are preempted and computed again.  The tokens are the same
+    (greedy, and sampled with temperature, top-k and top-p: a draw depends on seed and counter alone)."""
+    import random
+    from transformers_neuronx_b200.config import EngineConfig
+    from transformers_neuronx_b200.engine import LLMEngine, SamplingParams, load_model
+    rng = random.Random(500 + seed)
+    tiny = TinyModel("ABDF"[seed], seed=rng.randrange(50))
+    maxlen = tiny.cfg.max_position_embeddings
+    n = rng.randint(3, 8)
+    prompts = [tiny.random_ids(rng.randint(1, maxlen // 2), seed=rng.randrange(10 ** 6)) for _ in range(n)]
+    news = [rng.randint(1, min(40, maxlen - len(p))) for p in prompts]
+    sample = seed % 2 == 1
+    params = [SamplingParams(temperature=0.8, top_k=rng.choice([0, 20]), top_p=rng.choice([1.0, 0.9]), seed=i) if sample else None
+              for i in range(n)]
+    model, cfg = load_model(tiny.folder, "float32", verbose=False)
+    roomy = LLMEngine(model, EngineConfig(dtype="float32", max_num_seqs=16, max_batch_tokens=4096, async_scheduling=False,
+                                          use_cuda_graphs=False), eos_token_id=cfg.eos_token_id)
+    want = roomy.generate(prompts, news, params, stop_on_eos=True)
+    most = max(-(-(len(p) + m) // 16) for p, m in zip(prompts, news))
+    pages = most + rng.randint(0, most)
+    tight = LLMEngine(model, EngineConfig(dtype="float32", max_num_seqs=rng.randint(1, 4), max_batch_tokens=rng.choice([8, 24, 100]),
+                                          num_pages=pages, async_scheduling=True, use_cuda_graphs=True),
+                      eos_token_id=cfg.eos_token_id)
+    got = tight.generate(prompts, news, params, stop_on_eos=True)
+    assert got == want
+    assert tight.runner.cache.free_pages() == [pages]
+    tight.runner.cache.check()
+
+
 def test_temperature_sampling_is_seeded(tiny):
     from transformers_neuronx_b200.engine import SamplingParams
     eng = _engine(tiny, "bfloat16", max_num_seqs=4)
