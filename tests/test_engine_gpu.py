@@ -436,6 +436,53 @@ def test_beam_search_through_the_adapter(tiny, nb, lp, early):
         adapter.generate(ids, num_beams=nb + 1, max_new_tokens=2)
 
 
+def test_forward_with_sequence_ids_as_a_serving_loop_drives_it(tiny):
+    """NeuronConfig(continuous_batching=...): forward(input_ids, cache_ids, seq_ids) as the reference takes it from
+    a serving loop outside the model (base.py:492-587): prompts for some cache lines (right-padded rows, 2-D
+    positions), single tokens for any lines in any order, a line begun anew, a further portion of a prompt."""
+    from transformers_neuronx_b200 import ContinuousBatchingConfig, NeuronConfig
+    from transformers_neuronx_b200.opt.model import OPTForSampling
+    nc = NeuronConfig(continuous_batching=ContinuousBatchingConfig(batch_size_for_shared_caches=3))
+    model = OPTForSampling.from_pretrained(tiny.folder, batch_size=1, amp="f32", n_positions=64, neuron_config=nc).to_neuron()
+    tol = TOLERANCE["float32"]
+
+    def close(got, ids):
+        want = tiny.plain_logits(ids)[-1]
+        assert float((got - want).abs().max()) / float(want.abs().max()) <= tol
+
+    seqs = {2: tiny.random_ids(9, seed=1)}
+    lg = model(torch.tensor([seqs[2]]), torch.arange(9)[None], torch.tensor([2]))
+    close(lg[0], seqs[2])
+    seqs[0], seqs[1] = tiny.random_ids(12, seed=2), tiny.random_ids(5, seed=3)
+    ids = torch.tensor([seqs[0], seqs[1] + [0] * 7])
+    pos = torch.tensor([list(range(12)), list(range(5)) + [0] * 7])
+    lg = model(ids, pos, torch.tensor([0, 1]))
+    close(lg[0], seqs[0]); close(lg[1], seqs[1])
+    for step in range(3):                                    # single tokens, the lines in another order every time
+        order = [[1, 2, 0], [2, 0, 1], [0, 1, 2]][step]
+        toks = [7 + step + s for s in order]
+        lg = model(torch.tensor(toks)[:, None], torch.tensor([[len(seqs[s])] for s in order]), torch.tensor(order))
+        for i, s in enumerate(order):
+            seqs[s] = seqs[s] + [toks[i]]
+            close(lg[i], seqs[s])
+    seqs[1] = tiny.random_ids(6, seed=4)                     # line 1 begins anew; what it held is given back
+    lg = model(torch.tensor([seqs[1]]), torch.arange(6)[None], torch.tensor([1]))
+    close(lg[0], seqs[1])
+    more = tiny.random_ids(4, seed=5)                        # a further portion of line 2, beside nothing else
+    lg = model(torch.tensor([more]), torch.arange(len(seqs[2]), len(seqs[2]) + 4)[None], torch.tensor([2]))
+    seqs[2] = seqs[2] + more
+    close(lg[0], seqs[2])
+    lg = model(torch.tensor([[9], [10]]), torch.tensor([[len(seqs[1])], [len(seqs[2])]]), torch.tensor([1, 2]))
+    close(lg[0], seqs[1] + [9]); close(lg[1], seqs[2] + [10])
+    with pytest.raises(ValueError, match="holds"):
+        model(torch.tensor([[3]]), torch.tensor([[40]]), torch.tensor([0]))
+    with pytest.raises(ValueError, match="sequence id"):
+        model(torch.tensor([[3]]), torch.tensor([[0]]), torch.tensor([3]))
+    model.engine.runner.cache.check()
+    model.reset()
+    assert model.engine.runner.cache.live_requests() == []
+
+
 def test_all_logits_of_a_prompt_and_kept_kernels(tiny, tmp_path):
     from transformers_neuronx_b200 import NeuronConfig
     from transformers_neuronx_b200.opt.model import OPTForSampling

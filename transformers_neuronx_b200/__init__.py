@@ -4,4 +4,4 @@ sampling, and hand-written CUDA kernels.  Capabilities follow aws-neuron/transfo
 support; the design does not."""
 __version__ = "0.1.0"
 
-from .config.generation_config import GenerationConfig, NeuronConfig      # as `from transformers_neuronx import ...`
+from .config.generation_config import ContinuousBatchingConfig, GenerationConfig, NeuronConfig      # as `from transformers_neuronx import ...`

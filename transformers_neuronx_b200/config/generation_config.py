@@ -105,9 +105,34 @@ class GenerationConfig:
         return "GenerationConfig(" + ", ".join(f"{k}={v!r}" for k, v in self.__dict__.items()) + ")"
 
 
+class ContinuousBatchingConfig:
+    """The reference's settings for a batch whose rows are sequences that come and go
+    (config.py:73-103): `max_num_seqs` (or its older name `batch_size_for_shared_caches`) cache lines that
+    forward() addresses by sequence id.  Block size and number of blocks are the engine's own business here."""
+
+    def __init__(self, **kwargs):
+        n = kwargs.pop("max_num_seqs", None)
+        if n is None:
+            n = kwargs.pop("batch_size_for_shared_caches", None)
+        else:
+            kwargs.pop("batch_size_for_shared_caches", None)
+        if n is None or int(n) < 1:
+            raise ValueError("ContinuousBatchingConfig needs max_num_seqs (or batch_size_for_shared_caches) >= 1")
+        self.max_num_seqs = int(n)
+        self.max_model_len = kwargs.pop("max_model_len", None)
+        self.optimized_paged_attention = bool(kwargs.pop("optimized_paged_attention", False))
+        self.enable_chunked_prefill = bool(kwargs.pop("enable_chunked_prefill", False))
+        if kwargs:
+            raise TypeError(f"unexpected key word arguments: {sorted(kwargs)}")
+
+    @property
+    def batch_size_for_shared_caches(self) -> int:
+        return self.max_num_seqs
+
+
 class NeuronConfig:
-    """The reference's bag of options (config.py:160-330).  `on_device_generation` and
-    `output_all_logits` have a meaning here; `on_device_embedding`, `fuse_qkv` and
+    """The reference's bag of options (config.py:160-330).  `on_device_generation`,
+    `output_all_logits` and `continuous_batching` have a meaning here; `on_device_embedding`, `fuse_qkv` and
     `padding_side='left'` name what this engine does anyway.  Anything else set to a value of its own is kept in
     `ignored` and reported once."""
 
@@ -115,10 +140,13 @@ class NeuronConfig:
                  "attention_layout", "collectives_layout", "cache_layout", "compilation_worker_count"}
 
     def __init__(self, *, on_device_generation: Optional[GenerationConfig] = None, output_all_logits: bool = False,
-                 **options):
+                 continuous_batching: Optional[ContinuousBatchingConfig] = None, **options):
         if on_device_generation is not None and not isinstance(on_device_generation, GenerationConfig):
             raise TypeError("on_device_generation must be a GenerationConfig")
+        if continuous_batching is not None and not isinstance(continuous_batching, ContinuousBatchingConfig):
+            raise TypeError("continuous_batching must be a ContinuousBatchingConfig")
         self.on_device_generation = on_device_generation
+        self.continuous_batching = continuous_batching        # forward() then takes sequence ids as start_ids
         self.output_all_logits = bool(output_all_logits)      # forward() of a prompt returns every position's logits
         self.ignored = {k: v for k, v in options.items()
                         if k not in self._AS_BUILT and v not in (None, False)}

@@ -52,10 +52,13 @@ class OPTForSampling:
         self.folder = folder
         self.config = config
         self.batch_size = max(batch_size) if isinstance(batch_size, (list, tuple)) else int(batch_size)
+        if self.neuron_config.continuous_batching is not None:      # as many cache lines as sequences may be alive
+            self.batch_size = max(self.batch_size, self.neuron_config.continuous_batching.max_num_seqs)
         self.n_positions = int(max_bucket)
         self.engine: Optional[LLMEngine] = None
         self.model = None
         self._rows: List[str] = []
+        self._seqs = set()              # sequence ids alive under continuous batching
 
     # ---- loading ------------------------------------------------------------------------------------
     @classmethod
@@ -245,10 +248,11 @@ class OPTForSampling:
     # ---- the static-batch forward of the reference ---------------------------------------------------------
     def reset(self):
         if self.engine is not None:
-            for rid in self._rows:
+            for rid in self._rows + [("seq", s) for s in self._seqs]:
                 if rid in self.engine.runner.cache:
                     self.engine.runner.finish(rid)
         self._rows = []
+        self._seqs = set()
 
     def forward(self, input_ids, cache_ids=None, start_ids=None):
         """cache_ids None: the rows are whole prompts (a new batch).  Otherwise input_ids holds the
@@ -258,6 +262,8 @@ class OPTForSampling:
         input_ids = torch.as_tensor(input_ids)
         B, T = input_ids.shape
         runner = self.engine.runner
+        if self.neuron_config.continuous_batching is not None and start_ids is not None and cache_ids is not None:
+            return self._forward_sequences(input_ids, torch.as_tensor(cache_ids), torch.as_tensor(start_ids))
         starts = [0] * B if start_ids is None else [int(s) for s in torch.as_tensor(start_ids).tolist()]
         if cache_ids is None:
             self.reset()
@@ -289,6 +295,44 @@ class OPTForSampling:
         return logits
 
     __call__ = forward
+
+    def _forward_sequences(self, input_ids, cache_ids, seq_ids):
+        """forward() under NeuronConfig(continuous_batching=...), as a serving loop outside the model drives
+        the reference (base.py:492-587, :613-639): row i belongs to sequence seq_ids[i], which owns a cache
+        line; cache_ids [rows, tokens] holds the positions of the row's tokens, a shorter row padded on the
+        right with zeros.  A row that starts at position 0 begins its sequence anew (what the line held is
+        given back); any other row goes on where its sequence ends, with one token or with a further
+        portion.  Rows of different kinds may share a call.  Returns the logits [rows, vocab] of each row's
+        last token, 32-bit, on the host."""
+        runner = self.engine.runner
+        B, T = input_ids.shape
+        cache_ids = cache_ids.reshape(B, -1)
+        if cache_ids.shape[1] != T or seq_ids.numel() != B:
+            raise ValueError("cache_ids must be [rows, tokens] like input_ids, with one sequence id per row")
+        lines = self.neuron_config.continuous_batching.max_num_seqs
+        entries, seen = [], set()
+        for b in range(B):
+            sid = int(seq_ids.flatten()[b])
+            if not 0 <= sid < lines or sid in seen:
+                raise ValueError(f"row {b}: sequence id {sid} (ids are 0..{lines - 1}, each at most once a call)")
+            seen.add(sid)
+            rid = ("seq", sid)
+            pos = cache_ids[b].tolist()
+            count = 1 if T == 1 else max(pos) - pos[0] + 1
+            if pos[:count] != list(range(pos[0], pos[0] + count)):
+                raise ValueError(f"row {b}: positions {pos[:count]} are not consecutive")
+            if pos[0] == 0:
+                if rid in runner.cache:
+                    runner.finish(rid)
+                runner.add_request(rid)
+                self._seqs.add(sid)
+            elif rid not in runner.cache or runner.cache.length(rid) != pos[0]:
+                have = runner.cache.length(rid) if rid in runner.cache else 0
+                raise ValueError(f"row {b}: sequence {sid} holds {have} tokens; cache_ids says {pos[0]}")
+            entries.append(StepEntry(rid, input_ids[b, :count].tolist(), [count - 1]))
+        logits = runner.step(entries).to("cpu", torch.float32)
+        ops.raise_on_device_error()
+        return logits
 
     def reorder_cache(self, reorder_ids) -> None:
         """Row i of the running batch goes on from what row reorder_ids[i] holds: the cache side of beam
