@@ -481,6 +481,13 @@ def test_forward_with_sequence_ids_as_a_serving_loop_drives_it(tiny):
     model.engine.runner.cache.check()
     model.reset()
     assert model.engine.runner.cache.live_requests() == []
+    # cast_logits_dtype (base.py:641-647): the type the logits are handed out in
+    nc16 = NeuronConfig(cast_logits_dtype="bfloat16")
+    m16 = OPTForSampling.from_pretrained(tiny.folder, batch_size=1, amp="f32", n_positions=32, neuron_config=nc16).to_neuron()
+    lg = m16(torch.tensor([seqs[0][:8]]))
+    assert lg.dtype == torch.bfloat16
+    want = tiny.plain_logits(seqs[0][:8])[-1]
+    assert float((lg[0].float() - want).abs().max()) / float(want.abs().max()) <= 1e-2
 
 
 def test_all_logits_of_a_prompt_and_kept_kernels(tiny, tmp_path):

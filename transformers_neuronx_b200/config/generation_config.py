@@ -132,21 +132,26 @@ class ContinuousBatchingConfig:
 
 class NeuronConfig:
     """The reference's bag of options (config.py:160-330).  `on_device_generation`,
-    `output_all_logits` and `continuous_batching` have a meaning here; `on_device_embedding`, `fuse_qkv` and
+    `output_all_logits`, `continuous_batching` and `cast_logits_dtype` have a meaning here; `on_device_embedding`, `fuse_qkv` and
     `padding_side='left'` name what this engine does anyway.  Anything else set to a value of its own is kept in
     `ignored` and reported once."""
 
-    _AS_BUILT = {"on_device_embedding", "fuse_qkv", "fuse_mlp", "cast_logits_dtype", "padding_side",
+    _AS_BUILT = {"on_device_embedding", "fuse_qkv", "fuse_mlp", "padding_side",
                  "attention_layout", "collectives_layout", "cache_layout", "compilation_worker_count"}
 
     def __init__(self, *, on_device_generation: Optional[GenerationConfig] = None, output_all_logits: bool = False,
-                 continuous_batching: Optional[ContinuousBatchingConfig] = None, **options):
+                 continuous_batching: Optional[ContinuousBatchingConfig] = None, cast_logits_dtype: str = "float32",
+                 **options):
         if on_device_generation is not None and not isinstance(on_device_generation, GenerationConfig):
             raise TypeError("on_device_generation must be a GenerationConfig")
         if continuous_batching is not None and not isinstance(continuous_batching, ContinuousBatchingConfig):
             raise TypeError("continuous_batching must be a ContinuousBatchingConfig")
+        if cast_logits_dtype not in ("float32", "float16", "bfloat16"):      # config.py:247-250
+            raise ValueError(f"The `cast_logits_dtype={cast_logits_dtype}` argument must be one of "
+                             "['float32', 'float16', 'bfloat16']")
         self.on_device_generation = on_device_generation
         self.continuous_batching = continuous_batching        # forward() then takes sequence ids as start_ids
+        self.cast_logits_dtype = cast_logits_dtype            # the type forward() hands its logits out in (base.py:641-647)
         self.output_all_logits = bool(output_all_logits)      # forward() of a prompt returns every position's logits
         self.ignored = {k: v for k, v in options.items()
                         if k not in self._AS_BUILT and v not in (None, False)}

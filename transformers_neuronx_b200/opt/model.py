@@ -288,11 +288,15 @@ class OPTForSampling:
             for b, t in enumerate(toks):
                 out[b, T - len(t):] = flat[row:row + len(t)]
                 row += len(t)
-            return out
+            return self._cast_logits(out)
         entries = [StepEntry(rid, t, [len(t) - 1]) for rid, t in zip(self._rows, toks)]
         logits = runner.step(entries).to("cpu", torch.float32)
         ops.raise_on_device_error()           # a bounded wait that ran out inside a kernel: the logits are invalid
-        return logits
+        return self._cast_logits(logits)
+
+    def _cast_logits(self, logits):
+        """The logits in NeuronConfig.cast_logits_dtype (32-bit unless asked otherwise; base.py:641-647)."""
+        return logits.to(getattr(torch, self.neuron_config.cast_logits_dtype))
 
     __call__ = forward
 
@@ -332,7 +336,7 @@ class OPTForSampling:
             entries.append(StepEntry(rid, input_ids[b, :count].tolist(), [count - 1]))
         logits = runner.step(entries).to("cpu", torch.float32)
         ops.raise_on_device_error()
-        return logits
+        return self._cast_logits(logits)
 
     def reorder_cache(self, reorder_ids) -> None:
         """Row i of the running batch goes on from what row reorder_ids[i] holds: the cache side of beam
