@@ -286,3 +286,16 @@ def test_entry_point_small_parity_methods(tmp_path):
     assert m.neuron_config.on_device_generation.top_k == 7
     with pytest.raises(TypeError):
         m.update_generation_config({"top_k": 3})
+
+
+def test_auto_class_picks_the_entry_point_by_config(tmp_path):
+    """NeuronAutoModelForCausalLM.from_pretrained (modeling_auto.py:5-47): the folder's model_type chooses the class."""
+    from transformers_neuronx_b200 import NeuronAutoModelForCausalLM, OPTForSampling
+    tiny = TinyModel("B", seed=3)
+    m = NeuronAutoModelForCausalLM.from_pretrained(tiny.folder, batch_size=2, amp="f32", n_positions=32)
+    assert isinstance(m, OPTForSampling) and m.batch_size == 2 and m.config == tiny.cfg
+    (tmp_path / "config.json").write_text(json.dumps({"architectures": ["NobodyForCausalLM"], "model_type": "nobody"}))
+    with pytest.raises(Exception, match="nobody|Nobody"):
+        NeuronAutoModelForCausalLM.from_pretrained(str(tmp_path))
+    with pytest.raises(FileNotFoundError):
+        NeuronAutoModelForCausalLM.from_pretrained("facebook/opt-125m")

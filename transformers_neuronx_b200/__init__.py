@@ -5,3 +5,15 @@ support; the design does not."""
 __version__ = "0.1.0"
 
 from .config.generation_config import ContinuousBatchingConfig, GenerationConfig, NeuronConfig      # as `from transformers_neuronx import ...`
+
+_LAZY = {"OPTForSampling": ".opt.model", "OPTForGreedySearch": ".opt.model",
+         "NeuronAutoModelForCausalLM": ".modeling_auto", "HuggingFaceGenerationModelAdapter": ".generation_utils"}
+
+
+def __getattr__(name):
+    """The entry-point classes under the package's own name, as `from transformers_neuronx import OPTForSampling`
+    (src/transformers_neuronx/__init__.py); imported when first asked for."""
+    if name in _LAZY:
+        import importlib
+        return getattr(importlib.import_module(_LAZY[name], __name__), name)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
