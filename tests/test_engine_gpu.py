@@ -490,6 +490,34 @@ def test_forward_with_sequence_ids_as_a_serving_loop_drives_it(tiny):
     assert float((lg[0].float() - want).abs().max()) / float(want.abs().max()) <= 1e-2
 
 
+def test_validate_against_a_reference_model(tiny):
+    """testing.validate (the reference's testing/validation.py:23-101) with the plain implementation standing in
+    for the CPU model, on the left-padded batches of testing.data."""
+    from transformers_neuronx_b200.opt.model import OPTForSampling
+    from transformers_neuronx_b200.testing import batch_all_lengths, batch_full_lengths, batch_varying_lengths, validate
+
+    class PlainModel:
+        def generate(self, input_ids, attention_mask, max_new_tokens, **_):
+            rows = []
+            for ids, mask in zip(input_ids.tolist(), attention_mask.tolist()):
+                start = mask.index(1)
+                toks, _ = _plain_greedy_with_margin(tiny, ids[start:], max_new_tokens)
+                rows.append(ids + toks)
+            return torch.tensor(rows)
+
+    V = tiny.cfg.vocab_size
+    ids, mask, starts = batch_all_lengths(V, 6, seed=1)
+    assert mask.tolist()[2] == [0, 0, 1, 1, 1, 1] and starts.tolist() == list(range(6)) and int(ids[3, 2]) == 0
+    for inputs in (batch_varying_lengths(V, 4, 9, seed=2), batch_full_lengths(V, 3, 5, seed=3), (ids, mask, starts)):
+        rows = inputs[0].shape[0]
+        model = OPTForSampling.from_pretrained(tiny.folder, batch_size=rows, amp="f32", n_positions=32)
+        validate(PlainModel(), model, tiny.cfg, inputs, sequence_length=inputs[0].shape[1] + 6, verbose=False)
+    wrong = PlainModel()
+    wrong.generate = lambda **kw: PlainModel().generate(**kw) + 1
+    with pytest.raises(AssertionError, match="differs"):
+        validate(wrong, model, tiny.cfg, inputs, sequence_length=inputs[0].shape[1] + 6, verbose=False)
+
+
 def test_all_logits_of_a_prompt_and_kept_kernels(tiny, tmp_path):
     from transformers_neuronx_b200 import NeuronConfig
     from transformers_neuronx_b200.opt.model import OPTForSampling
