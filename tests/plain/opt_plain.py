@@ -198,11 +198,15 @@ def decoder_layer(x: torch.Tensor, w: Dict[str, torch.Tensor], i: int, cfg: dict
     act = cfg.get("activation_function", "relu")
     ln1 = (w.get(p + "self_attn_layer_norm.weight"), w.get(p + "self_attn_layer_norm.bias"))
     ln2 = (w.get(p + "final_layer_norm.weight"), w.get(p + "final_layer_norm.bias"))
+    # Not a key of OPT's config.json: the reference takes a sliding window from NeuronConfig.sparse_attn
+    # (T/opt/model.py:395-415; T/sparse_attn_utils.py:140-150: a row attends to itself and window_size before).
+    window = cfg.get("sliding_window_size")
+    window = None if window is None else window + 1
     if cfg.get("do_layer_norm_before", True):
-        x = x + multi_head_attention(layer_norm(x, *ln1, eps), w, p + "self_attn.", heads)
+        x = x + multi_head_attention(layer_norm(x, *ln1, eps), w, p + "self_attn.", heads, window=window)
         x = x + feed_forward(layer_norm(x, *ln2, eps), w, p, act)
     else:
-        x = layer_norm(x + multi_head_attention(x, w, p + "self_attn.", heads), *ln1, eps)
+        x = layer_norm(x + multi_head_attention(x, w, p + "self_attn.", heads, window=window), *ln1, eps)
         x = layer_norm(x + feed_forward(x, w, p, act), *ln2, eps)
     return x
 

@@ -518,6 +518,42 @@ def test_validate_against_a_reference_model(tiny):
         validate(wrong, model, tiny.cfg, inputs, sequence_length=inputs[0].shape[1] + 6, verbose=False)
 
 
+@pytest.mark.parametrize("amp", ["f32", "bf16"])
+def test_sliding_window_through_neuron_config(tiny, amp):
+    """NeuronConfig(sparse_attn=SparseAttnConfig('window', causal=True, SlidingWindowAttnConfig(W))): every layer
+    attends to the token itself and the W before it (sparse_attn_utils.py:140-150), in prompts, in portions and when
+    decoding; pages behind the window go back to the pool while the sequence runs."""
+    from transformers_neuronx_b200 import NeuronConfig, SlidingWindowAttnConfig, SparseAttnConfig
+    from transformers_neuronx_b200.opt.model import OPTForSampling
+    W = 19
+    nc = NeuronConfig(sparse_attn=SparseAttnConfig("window", causal=True, sparse_attn_config=SlidingWindowAttnConfig(W)))
+    n_pos = min(100, tiny.cfg.max_position_embeddings)
+    model = OPTForSampling.from_pretrained(tiny.folder, batch_size=2, amp=amp, n_positions=n_pos, neuron_config=nc).to_neuron()
+    cfg = dict(tiny.cfg.to_dict(), sliding_window_size=W)
+    dtype = {"f32": "float32", "bf16": "bfloat16"}[amp]
+    prompts = [tiny.random_ids(60, seed=5), tiny.random_ids(60, seed=6)]
+    lg = model(torch.tensor(prompts))
+    seqs = [list(p) for p in prompts]
+    for step in range(12):
+        for b in range(2):
+            want = P.forward_logits(seqs[b], tiny.plain_tensors, cfg)[-1]
+            assert float((lg[b] - want).abs().max()) / float(want.abs().max()) <= TOLERANCE[dtype], (step, b)
+            full = tiny.plain_logits(seqs[b])[-1]
+            if step == 0:
+                assert float((want - full).abs().max()) / float(full.abs().max()) > 1e-3, \
+                    "the window must matter for this check to mean anything"
+        nxt = [int(lg[b].argmax()) for b in range(2)]
+        for b in range(2):
+            seqs[b].append(nxt[b])
+        lg = model(torch.tensor(nxt)[:, None], torch.tensor([60 + step]))
+    held = [p for p in model.engine.runner.cache.block_table("row0") if p >= 0]
+    assert len(held) <= -(-(W + 1) // 16) + 1 < -(-72 // 16), "pages behind the window were given back"
+    with pytest.raises(NotImplementedError):
+        SparseAttnConfig("blk_sparse")
+    with pytest.raises(NotImplementedError):
+        SparseAttnConfig("window", causal=False, sparse_attn_config=SlidingWindowAttnConfig(8))
+
+
 def test_all_logits_of_a_prompt_and_kept_kernels(tiny, tmp_path):
     from transformers_neuronx_b200 import NeuronConfig
     from transformers_neuronx_b200.opt.model import OPTForSampling
@@ -586,3 +622,13 @@ def test_command_line_save_and_run(tmp_path):
                         "--print_latency"], capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stderr[-1500:]
     assert "generated_sequence=" in r.stdout and "Latency:" in r.stdout
+    # the reference's sliding-window options (gpt_demo.py:57-65, :107-123): tokens differ from the full attention's
+    # once the window is shorter than the sequence
+    full = r.stdout[r.stdout.index("generated_sequence="):]
+    r = subprocess.run([sys.executable, demo, "--amp", "bf16", "run", str(folder), "--batch_size", "2", "--n_positions", "24",
+                        "--sparse_attn", "window", "--window_size", "3"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-1500:]
+    assert "generated_sequence=" in r.stdout and r.stdout[r.stdout.index("generated_sequence="):] != full
+    r = subprocess.run([sys.executable, demo, "run", str(folder), "--sparse_attn", "blk_sparse"], capture_output=True, text=True,
+                       timeout=600)
+    assert r.returncode != 0 and "not implemented" in r.stderr.lower()

@@ -4,7 +4,8 @@ sampling, and hand-written CUDA kernels.  Capabilities follow aws-neuron/transfo
 support; the design does not."""
 __version__ = "0.1.0"
 
-from .config.generation_config import ContinuousBatchingConfig, GenerationConfig, NeuronConfig      # as `from transformers_neuronx import ...`
+from .config.generation_config import (BlkSparseAttnConfig, ContinuousBatchingConfig, GenerationConfig, NeuronConfig,
+                                       SlidingWindowAttnConfig, SparseAttnConfig)      # as `from transformers_neuronx import ...`
 
 _LAZY = {"OPTForSampling": ".opt.model", "OPTForGreedySearch": ".opt.model",
          "NeuronAutoModelForCausalLM": ".modeling_auto", "HuggingFaceGenerationModelAdapter": ".generation_utils"}

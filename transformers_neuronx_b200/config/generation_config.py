@@ -105,6 +105,53 @@ class GenerationConfig:
         return "GenerationConfig(" + ", ".join(f"{k}={v!r}" for k, v in self.__dict__.items()) + ")"
 
 
+class SlidingWindowAttnConfig:
+    """(sparse_attn_utils.py:80-83)"""
+
+    def __init__(self, window_size: int = 128):
+        if int(window_size) < 1:
+            raise ValueError("window_size must be at least 1")
+        self.window_size = int(window_size)
+
+
+class BlkSparseAttnConfig:
+    """(sparse_attn_utils.py:72-78) kept so that a configuration written for the reference is understood; the
+    engine's attention kernels have no block-sparse mask and SparseAttnConfig refuses it."""
+
+    def __init__(self, blk_size: int = 128, num_global_blks: int = 0, num_local_blks: int = 1, num_random_blks: int = 0):
+        self.blk_size, self.num_global_blks = blk_size, num_global_blks
+        self.num_local_blks, self.num_random_blks = num_local_blks, num_random_blks
+
+
+class SparseAttnConfig:
+    """Attention over part of the earlier tokens (sparse_attn_utils.py:86-160).  The engine builds the causal
+    sliding window: a token attends to itself and to the `window_size` tokens before it, in prompts
+    (create_sliding_window_mask, :140-150) and when decoding (the reference then slices the last window_size
+    cached positions, opt/model.py:470-482).  Pages that have fallen out of every later token's window go
+    back to the pool.  Block-sparse and caller-supplied masks, and the window that looks both ways, are refused."""
+
+    def __init__(self, attn_type: str = "blk_sparse", causal: bool = False, sparse_attn_config=None,
+                 same_mask_per_layer: bool = True, sparse_mask_dict=None):
+        if attn_type not in ("blk_sparse", "window", "custom"):
+            raise ValueError("Supported attention types are: ['blk_sparse', 'window', 'custom']")
+        if attn_type != "window":
+            raise NotImplementedError(f"sparse attention of type {attn_type!r} is not built: the attention kernels mask by "
+                                      "position (causal, sliding window), not by an arbitrary mask")
+        if not isinstance(sparse_attn_config, SlidingWindowAttnConfig):
+            raise ValueError("Must provide a valid sliding window attention config!")
+        if not causal:
+            raise NotImplementedError("a window that looks both ways has no meaning for a decoder that generates; "
+                                      "pass causal=True")
+        self.attn_type, self.causal, self.sparse_attn_config = attn_type, True, sparse_attn_config
+        self.same_mask_per_layer = bool(same_mask_per_layer)
+        self.skip_masking_decode = True
+
+    @property
+    def keys_attended(self) -> int:
+        """The token itself and window_size before it."""
+        return self.sparse_attn_config.window_size + 1
+
+
 class ContinuousBatchingConfig:
     """The reference's settings for a batch whose rows are sequences that come and go
     (config.py:73-103): `max_num_seqs` (or its older name `batch_size_for_shared_caches`) cache lines that
@@ -132,7 +179,8 @@ class ContinuousBatchingConfig:
 
 class NeuronConfig:
     """The reference's bag of options (config.py:160-330).  `on_device_generation`,
-    `output_all_logits`, `continuous_batching` and `cast_logits_dtype` have a meaning here; `on_device_embedding`, `fuse_qkv` and
+    `output_all_logits`, `continuous_batching`, `cast_logits_dtype` and `sparse_attn` (sliding window) have a
+    meaning here; `on_device_embedding`, `fuse_qkv` and
     `padding_side='left'` name what this engine does anyway.  Anything else set to a value of its own is kept in
     `ignored` and reported once."""
 
@@ -141,7 +189,7 @@ class NeuronConfig:
 
     def __init__(self, *, on_device_generation: Optional[GenerationConfig] = None, output_all_logits: bool = False,
                  continuous_batching: Optional[ContinuousBatchingConfig] = None, cast_logits_dtype: str = "float32",
-                 **options):
+                 sparse_attn: Optional[SparseAttnConfig] = None, **options):
         if on_device_generation is not None and not isinstance(on_device_generation, GenerationConfig):
             raise TypeError("on_device_generation must be a GenerationConfig")
         if continuous_batching is not None and not isinstance(continuous_batching, ContinuousBatchingConfig):
@@ -152,6 +200,9 @@ class NeuronConfig:
         self.on_device_generation = on_device_generation
         self.continuous_batching = continuous_batching        # forward() then takes sequence ids as start_ids
         self.cast_logits_dtype = cast_logits_dtype            # the type forward() hands its logits out in (base.py:641-647)
+        if sparse_attn is not None and not isinstance(sparse_attn, SparseAttnConfig):
+            raise TypeError("sparse_attn must be a SparseAttnConfig")
+        self.sparse_attn = sparse_attn                        # a causal sliding window for every attention layer
         self.output_all_logits = bool(output_all_logits)      # forward() of a prompt returns every position's logits
         self.ignored = {k: v for k, v in options.items()
                         if k not in self._AS_BUILT and v not in (None, False)}

@@ -46,10 +46,14 @@ def build_model(spec, tensors, dtype: str, device="cuda:0", verbose=True) -> Dec
     return model
 
 
-def load_model(folder: str, dtype: str = "bfloat16", device="cuda:0", verbose=True):
-    """Returns (model, typed config).  The model class is chosen by config.json."""
+def load_model(folder: str, dtype: str = "bfloat16", device="cuda:0", verbose=True, spec_hook=None):
+    """Returns (model, typed config).  The model class is chosen by config.json.  `spec_hook`, when given,
+    takes the architecture's ModelSpec and returns the one to build (a run-time option that changes a part's
+    parameters, such as a sliding window for every attention layer)."""
     arch, cfg = load_config(folder)
     spec = arch.build_spec(cfg)
+    if spec_hook is not None:
+        spec = spec_hook(spec)
     probe = DecoderModel(spec)                       # host-only: lists the tensors the model reads
     t0 = time.time()
     tensors = load_tensors(folder, probe.tensor_specs())

@@ -5,13 +5,14 @@ opt/demo.py:19-29) for this engine.
     opt_demo [--amp f32|f16|bf16] [--model_name <folder>] save <folder>         (re-save a local checkpoint)
     opt_demo [--amp f32|f16|bf16] run <folder> [--batch_size 4] [--n_positions 128] [--print_latency]
              [--top_k 50] [--temperature 1.0] [--top_p 1.0] [--prompt_ids 2,100,200]
+             [--sparse_attn window --window_size 128]
 
 `save` casts attention, fc1, fc2 and embedding matrices to --amp and keeps LayerNorm tensors in
 32-bit, as the reference's amp_callback does (opt/demo.py:23-29).  `run` seeds with 15213, repeats
 one prompt batch_size times and samples to n_positions (gpt_demo.py:100-150).  With tokenizer files
 in the folder and the `transformers` tokenizer classes importable the prompt is the reference's
 "Hello, I'm a language model,"; otherwise token ids go in and out.  Options of the reference that
-only mean something on Neuron hardware (--tp_degree, --unroll, --quantize, --sparse_attn ...) are
+only mean something on Neuron hardware (--tp_degree, --unroll, --quantize, the block-sparse numbers ...) are
 accepted and ignored.
 """
 from __future__ import annotations
@@ -52,11 +53,13 @@ def _parser():
     rp.add_argument("--temperature", type=float, default=1.0)
     rp.add_argument("--top_p", type=float, default=1.0)
     rp.add_argument("--prompt_ids", type=str, default=None, help="comma-separated token ids of the prompt")
-    for name in ("--tp_degree", "--unroll", "--context_length_estimate", "--window_size", "--blk_size",
+    rp.add_argument("--sparse_attn", type=str, default=None, choices=[None, "blk_sparse", "custom", "window"],
+                    help="'window': sliding-window attention (the other patterns are not built)")
+    rp.add_argument("--window_size", type=int, default=128, help="Window size for sliding-window attention.")
+    for name in ("--tp_degree", "--unroll", "--context_length_estimate", "--blk_size",
                  "--num_global_blks", "--num_local_blks", "--num_random_blks"):
         rp.add_argument(name, type=int, default=None, help=argparse.SUPPRESS)
     rp.add_argument("--quantize", action="store_true", help=argparse.SUPPRESS)
-    rp.add_argument("--sparse_attn", type=str, default=None, help=argparse.SUPPRESS)
     return ap
 
 
@@ -101,8 +104,15 @@ def _tokenizer(folder):
 def run(args):
     torch.manual_seed(15213)
     print("running OPTForSampling.from_pretrained")
+    neuron_config = None
+    if args.sparse_attn:                                    # gpt_demo.py:107-123
+        if args.sparse_attn != "window":
+            raise NotImplementedError("Interface for other attention patterns not implemented yet!")
+        from ..config import NeuronConfig, SlidingWindowAttnConfig, SparseAttnConfig
+        neuron_config = NeuronConfig(sparse_attn=SparseAttnConfig(
+            attn_type="window", causal=True, sparse_attn_config=SlidingWindowAttnConfig(window_size=args.window_size)))
     model = OPTForSampling.from_pretrained(args.load, batch_size=args.batch_size, amp=args.amp,
-                                           n_positions=args.n_positions)
+                                           n_positions=args.n_positions, neuron_config=neuron_config)
     print("running model.to_neuron")
     model.to_neuron()
     tok = _tokenizer(args.load)

@@ -75,7 +75,7 @@ class OPTForSampling:
         """Weights to the GPU, kernels compiled, cache made.  Kept under the reference's name."""
         if self.engine is not None:
             return self
-        self.model, _ = load_model(self.folder, self.dtype)
+        self.model, _ = load_model(self.folder, self.dtype, spec_hook=self._spec_hook())
         ec = EngineConfig(dtype=self.dtype, max_num_seqs=max(self.batch_size, 1), max_model_len=self.n_positions,
                           max_tokens=self.batch_size * (-(-self.n_positions // 16) * 16),
                           max_batch_tokens=max(2048, self.batch_size))
@@ -83,6 +83,19 @@ class OPTForSampling:
         return self
 
     to_gpu = to_neuron
+
+    def _spec_hook(self):
+        """NeuronConfig(sparse_attn=...) of the sliding-window kind: every attention layer gets the window."""
+        sa = self.neuron_config.sparse_attn
+        if sa is None:
+            return None
+        import dataclasses
+
+        def with_window(spec):
+            layers = tuple(dataclasses.replace(l, mixer=dataclasses.replace(l.mixer, window=sa.keys_attended))
+                           if hasattr(l.mixer, "window") else l for l in spec.layers)
+            return dataclasses.replace(spec, layers=layers)
+        return with_window
 
     # ---- compiled kernels kept between processes (base.py:110-190: save / load of compiled artifacts) ----
     def save(self, directory: str) -> None:
