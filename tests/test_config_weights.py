@@ -11,7 +11,7 @@ from transformers_neuronx_b200.config import (ConfigError, EngineConfig, OPTConf
 from transformers_neuronx_b200.models import opt as opt_arch
 from transformers_neuronx_b200.models.decoder import DecoderModel
 from transformers_neuronx_b200.weights import (TensorSpec, WeightError, load_tensors, match_tensors,
-                                               random_tensors, save_safetensors, SafetensorsFile)
+                                               save_safetensors, SafetensorsFile)
 
 
 def test_config_reads_its_keys():

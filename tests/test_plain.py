@@ -1,6 +1,5 @@
 """The plain implementation checked against itself and against torch's own primitives, so that
 the oracle of all other tests is not trusted blindly."""
-import math
 
 import pytest
 import torch

@@ -1,7 +1,6 @@
 """Trace replay against the plain implementation, in 32-bit and in bfloat16: each request alone and
 whole; most of it in one step and the last 32 tokens one by one; in portions of changing size down
 to two tokens; and mixed, up to four live requests with so few pages that they are used again."""
-import json
 import os
 import subprocess
 import sys

@@ -5,7 +5,7 @@ import random
 import pytest
 
 from transformers_neuronx_b200.cache import CacheManager, PagedKVNeed, group_needs
-from transformers_neuronx_b200.engine.scheduler import Request, SamplingParams, Scheduler
+from transformers_neuronx_b200.engine.scheduler import Request, Scheduler
 
 
 def make(num_pages=8, slots=4, budget=32, max_len=128, portion=None):

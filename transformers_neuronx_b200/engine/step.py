@@ -14,7 +14,7 @@ from __future__ import annotations
 import gc
 import warnings
 from dataclasses import dataclass, field
-from typing import Dict, Hashable, List, Optional, Sequence
+from typing import Hashable, List, Optional, Sequence
 
 import numpy as np
 import torch

@@ -21,7 +21,6 @@ import argparse
 import json
 import math
 import os
-import sys
 import time
 
 import torch

@@ -10,8 +10,6 @@ attention kernels then read keys and values from the pages alone, whatever the c
 """
 from __future__ import annotations
 
-import torch
-
 from ..cache.manager import PagedKVNeed
 from ..kernels import ops
 from .base import Mixer

@@ -18,7 +18,7 @@ state of fixed size per request, or nothing.  No part knows which model it is in
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Sequence
+from typing import Dict, List, Sequence
 
 import torch
 

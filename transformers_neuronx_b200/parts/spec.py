@@ -8,8 +8,8 @@ name a layer twice, or give two entries the same cache so that one layer reads w
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
-from typing import Any, List, Optional, Tuple
+from dataclasses import dataclass
+from typing import Any, Optional, Tuple
 
 
 @dataclass(frozen=True)
