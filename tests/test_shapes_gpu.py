@@ -1,5 +1,5 @@
-"""The kernels at the sizes of real OPT models (6.7B, 13B, 30B layer shapes, one layer each, random
-weights).  The 32-bit engine against the plain implementation (restated on the GPU, and checked
+"""The kernels at the sizes of the real OPT models (the layer shapes of 6.7B, 13B, 30B and 66B, one layer
+each, and of 125M, 350M, 1.3B and 2.7B, two layers each; random weights).  The 32-bit engine against the plain implementation (restated on the GPU, and checked
 against the CPU original on a short sequence) at 2e-5: a long portion, a mixed step of a portion
 beside decode tokens, and decode steps; then the bfloat16 and float16 engines against the same
 32-bit numbers, through the CTA-pair product, the swapped product with split-K, the split decode
@@ -15,6 +15,15 @@ SHAPES = {
     "6.7b": dict(hidden_size=4096, num_attention_heads=32, ffn_dim=16384),
     "13b": dict(hidden_size=5120, num_attention_heads=40, ffn_dim=20480),
     "30b": dict(hidden_size=7168, num_attention_heads=56, ffn_dim=28672),
+    "66b": dict(hidden_size=9216, num_attention_heads=72, ffn_dim=36864),
+}
+# The small members of the family, two layers each, against the plain implementation itself on the CPU: head
+# sizes 64 and 80, and the one model with post-norm blocks and a projected embedding (350M).
+SMALL_SHAPES = {
+    "125m": dict(hidden_size=768, num_attention_heads=12, ffn_dim=3072),
+    "350m": dict(hidden_size=1024, num_attention_heads=16, ffn_dim=4096, word_embed_proj_dim=512, do_layer_norm_before=False),
+    "1.3b": dict(hidden_size=2048, num_attention_heads=32, ffn_dim=8192),
+    "2.7b": dict(hidden_size=2560, num_attention_heads=32, ffn_dim=10240),
 }
 
 
@@ -23,8 +32,9 @@ def _build(shape, dtype, tensors=None, stored=torch.bfloat16):
     from transformers_neuronx_b200.engine import build_model
     from transformers_neuronx_b200.models import opt as opt_arch
     from transformers_neuronx_b200.models.decoder import DecoderModel
-    cfg = OPTConfig.from_dict(dict(SHAPES[shape], vocab_size=50272, num_hidden_layers=1, max_position_embeddings=2048,
-                                   init_std=0.02))
+    sizes = SHAPES[shape] if shape in SHAPES else dict(SMALL_SHAPES[shape], num_hidden_layers=2)
+    cfg = OPTConfig.from_dict(dict(dict(vocab_size=50272, num_hidden_layers=1, max_position_embeddings=2048, init_std=0.02),
+                                   **sizes))
     spec = opt_arch.build_spec(cfg)
     if tensors is None:
         g = torch.Generator(device="cuda:0").manual_seed(7)
@@ -98,3 +108,34 @@ def test_layer_sizes_of_the_large_models(shape):
         ops.raise_on_device_error()
     finally:
         torch.backends.cuda.matmul.allow_tf32 = tf32
+
+
+@pytest.mark.parametrize("shape", list(SMALL_SHAPES))
+def test_layer_sizes_of_the_small_models(shape):
+    """125M, 350M, 1.3B and 2.7B layer sizes (two layers, the real vocabulary): every wanted row of a long portion, a
+    mixed step and three decode steps against the plain implementation on the CPU, in all three types."""
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(3, 50272, (n,), generator=g).tolist() for n in (300, 41, 77)]
+    m32, cfg, tensors = _build(shape, "float32")
+    cpu = {k: v.cpu() for k, v in tensors.items()}
+    plain = [opt_plain.forward_logits(p, cpu, cfg.to_dict()) for p in prompts]
+    got32, where = _run(m32, prompts)
+    want = torch.stack([plain[r][pos] for r, pos in where])
+    del m32
+    for dtype in ("float32", "bfloat16", "float16"):
+        if dtype == "float32":
+            got = got32
+        else:
+            t16 = tensors if dtype == "bfloat16" else {k: (v.to(torch.float16) if v.dtype == torch.bfloat16 else v)
+                                                         for k, v in tensors.items()}
+            if dtype == "float16":
+                t16["lm_head.weight"] = t16["model.decoder.embed_tokens.weight"]
+            m16, _, _ = _build(shape, dtype, t16)
+            got, _ = _run(m16, prompts)
+            del m16
+        for row, (r, pos) in enumerate(where):
+            e = rel_error(got[row], want[row])
+            assert e <= TOLERANCE[dtype], f"{shape} {dtype}: request {r} position {pos}: {e:.3e}"
+    from transformers_neuronx_b200.kernels import ops
+    ops.raise_on_device_error()
+
