@@ -34,6 +34,16 @@ OPT_6_7B = dict(vocab_size=50272, hidden_size=4096, num_hidden_layers=32, num_at
                 architectures=["OPTForCausalLM"], model_type="opt", torch_dtype="float16")
 OPT_13B = dict(OPT_6_7B, hidden_size=5120, num_hidden_layers=40, num_attention_heads=40, ffn_dim=20480, word_embed_proj_dim=5120)
 OPT_30B = dict(OPT_6_7B, hidden_size=7168, num_hidden_layers=48, num_attention_heads=56, ffn_dim=28672, word_embed_proj_dim=7168)
+# the other published sizes of the family (facebook/opt-* config.json values): layers, width, heads, ffn, embedding width
+OPT_FAMILY = {
+    "125m": dict(OPT_6_7B, hidden_size=768, num_hidden_layers=12, num_attention_heads=12, ffn_dim=3072, word_embed_proj_dim=768),
+    "350m": dict(OPT_6_7B, hidden_size=1024, num_hidden_layers=24, num_attention_heads=16, ffn_dim=4096, word_embed_proj_dim=512,
+                 do_layer_norm_before=False),
+    "1.3b": dict(OPT_6_7B, hidden_size=2048, num_hidden_layers=24, num_attention_heads=32, ffn_dim=8192, word_embed_proj_dim=2048),
+    "2.7b": dict(OPT_6_7B, hidden_size=2560, num_hidden_layers=32, num_attention_heads=32, ffn_dim=10240, word_embed_proj_dim=2560),
+    "6.7b": OPT_6_7B, "13b": OPT_13B, "30b": OPT_30B,
+    "66b": dict(OPT_6_7B, hidden_size=9216, num_hidden_layers=64, num_attention_heads=72, ffn_dim=36864, word_embed_proj_dim=9216),
+}
 CONTEXT = 2048
 PREFILL_TOKENS = 2048
 
@@ -122,7 +132,7 @@ def decode_bytes(model, cfg, batch, ctx):
     H, L = cfg.hidden_size, cfg.num_hidden_layers
     w = model.parameter_bytes()
     pos_table = (cfg.max_position_embeddings + 2) * H * 2
-    w = w - pos_table + batch * H * 2 * 2
+    w = w - pos_table + batch * (H + cfg.word_embed_proj_dim) * 2
     kv = batch * ctx * 2 * H * 2 * L
     return w + kv
 
@@ -298,9 +308,45 @@ def workload_mixed13b():
     return res
 
 
-def extra_workload(name, steps, warmup):
+def workload_family(steps, warmup, sizes=None):
+    """Every published size of the family at its full depth: decode at batch 8 (66B: batch 4, so that
+    weights and cache fit one GPU) with the context ending at 2,048, batch 1, and a 2,048-token prefill,
+    each with its fraction of the measured peak.  The two smallest models' weights are about the size of
+    the L2 cache, so their "hbm" fractions say how far the step is from launch-bound, not from DRAM."""
+    import torch
+    hbm, tflops, _ = peaks()
+    rows = {}
+    for name in sizes or list(OPT_FAMILY):
+        base = OPT_FAMILY[name]
+        try:
+            model, cfg = build(base["num_hidden_layers"], base=base)
+        except torch.OutOfMemoryError as e:
+            rows[name] = {"does_not_fit": str(e).split(".")[0]}
+            torch.cuda.empty_cache()
+            continue
+        batch = 4 if name == "66b" else 8
+        row = {"layers": cfg.num_hidden_layers, "hidden": cfg.hidden_size, "head_dim": cfg.head_dim,
+               "weights_gb": round(model.parameter_bytes() / 1e9, 2)}
+        for b in (batch, 1):
+            ms, launches, _, _ = time_decode(model, cfg, b, steps, warmup)
+            nbytes = decode_bytes(model, cfg, b, CONTEXT - steps / 2)
+            row[f"decode_b{b}"] = {"tokens_per_s": round(b / (ms / 1e3), 1), "ms_per_step": round(ms, 3),
+                                   "frac_hbm": round(nbytes / (ms / 1e3) / 1e9 / hbm, 4), "launches_per_step": launches // steps}
+        pf = time_prefill(model, cfg, 3, 3)
+        row["prefill_2048"] = {"ms": round(pf, 3), "tokens_per_s": round(PREFILL_TOKENS / (pf / 1e3), 1),
+                               "frac_flops": round(prefill_flops(cfg, PREFILL_TOKENS) / (pf / 1e3) / (tflops * 1e12), 4)}
+        rows[name] = row
+        del model
+        torch.cuda.empty_cache()
+    return rows
+
+
+def extra_workload(name, steps, warmup, sizes=None):
     """One of the further workloads alone, printed as one JSON line of its own."""
-    res = workload_decode30b(steps, warmup) if name == "decode30b" else workload_mixed13b()
+    if name == "family":
+        res = workload_family(steps, warmup, sizes)
+    else:
+        res = workload_decode30b(steps, warmup) if name == "decode30b" else workload_mixed13b()
     print(json.dumps(dict({"workload": name}, **res)))
     return 0
 
@@ -330,8 +376,9 @@ def main():
     ap.add_argument("--skip-large", action="store_true", help="leave out the OPT-13B and OPT-30B workloads")
     ap.add_argument("--dtype", default="float16", choices=["float16", "bfloat16"],
                     help="the serving type (float16 is what OPT checkpoints are stored in)")
-    ap.add_argument("--workload", default=None, choices=["decode30b", "mixed13b"],
+    ap.add_argument("--workload", default=None, choices=["decode30b", "mixed13b", "family"],
                     help="run one of the further workloads instead of the default line")
+    ap.add_argument("--sizes", default=None, help="for --workload family: comma-separated sizes (default: all of 125m .. 66b)")
     ap.add_argument("--only", default=None, choices=["decode", "prefill"],
                     help="run just this part and print its time (for profiling a small case)")
     a = ap.parse_args()
@@ -344,7 +391,7 @@ def main():
     global DTYPE
     DTYPE = a.dtype
     if a.workload:
-        return extra_workload(a.workload, a.steps, a.warmup)
+        return extra_workload(a.workload, a.steps, a.warmup, a.sizes.split(",") if a.sizes else None)
     import torch
     hbm_gbs, tflops, peak_src = peaks()
     model, cfg = build(a.layers)
