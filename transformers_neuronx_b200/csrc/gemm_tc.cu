@@ -177,6 +177,165 @@ __device__ __forceinline__ void store_tile_row(const Params& p, int lane_row, in
     }
 }
 
+// The sum over a cluster's partial tiles for this CTA's band of rows, fetched from the S CTAs' shared memory
+// (16-byte loads, in split order; bias, activation, residual; 16- or 8-byte stores).  A thread keeps four
+// neighbouring features and walks over the band's tokens, two at a time with all their loads asked for before
+// the first sum (a round trip to another SM's shared memory takes about a microsecond); what depends on the
+// features only is computed once.
+template <int BN, bool SWAP, int S>
+__device__ __forceinline__ void cluster_reduce_items(const Params& p, uint32_t part_addr, int tile_p, int tile_q) {
+    constexpr int NR = TILE_P / S;                                   // rows of this CTA's band
+    constexpr int GROUPS = SWAP ? NR / 4 : BN / 4;                   // groups of four features
+    constexpr int T_STEP = NUM_THREADS / GROUPS, U = 2;
+    static_assert(NUM_THREADS % GROUPS == 0, "threads per feature group");
+    const int my_rank = (int)cluster_ctarank();
+    const int row_lo = NR * my_rank;
+    const int g = threadIdx.x % GROUPS, t0 = threadIdx.x / GROUPS;
+    const int n = SWAP ? tile_p * TILE_P + row_lo + 4 * g : tile_q * BN + 4 * g;          // first feature
+    const int n_lim = SWAP ? p.rows_p : p.rows_q;
+    if (n >= n_lim) return;
+    const bool whole = n + 3 < n_lim;
+    float b[4] = {0.f, 0.f, 0.f, 0.f};
+    if (p.bias) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) if (n + e < n_lim) b[e] = __ldg(p.bias + n + e);
+    }
+    // token t of the band: its index m and the byte offset of this thread's four values in a partial tile
+    const int m0 = SWAP ? tile_q * BN : tile_p * TILE_P + row_lo;
+    const int tokens = min(SWAP ? BN : NR, (SWAP ? p.rows_q : p.rows_p) - m0);
+    const uint32_t base = part_addr + (uint32_t)((SWAP ? row_lo + 4 * g : row_lo * (BN + 4) + 4 * g) * 4);
+    constexpr uint32_t T_BYTES = (SWAP ? TILE_P : BN + 4) * 4;
+    uint32_t src[S];
+#pragma unroll
+    for (int s = 0; s < S; ++s) src[s] = s == my_rank ? base : map_to_cta(base, (uint32_t)s);
+    for (int t = t0; t < tokens; t += T_STEP * U) {
+        float4 f[U][S], res[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int tt = t + u * T_STEP;
+            res[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (tt < tokens && p.residual) {
+                const float* rp = p.residual + (size_t)(m0 + tt) * p.ldc + n;
+                if (whole) res[u] = __ldcg((const float4*)rp);
+                else { res[u].x = rp[0]; if (n + 1 < n_lim) res[u].y = rp[1]; if (n + 2 < n_lim) res[u].z = rp[2]; }
+            }
+#pragma unroll
+            for (int s = 0; s < S; ++s) {
+                const uint32_t a = src[s] + (uint32_t)tt * T_BYTES;
+                if (tt >= tokens) {
+                    f[u][s] = make_float4(0.f, 0.f, 0.f, 0.f);
+                } else if (s == my_rank) {                    // this CTA's own partial tile: a plain shared-memory load
+                    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                 : "=f"(f[u][s].x), "=f"(f[u][s].y), "=f"(f[u][s].z), "=f"(f[u][s].w) : "r"(a) : "memory");
+                } else {
+                    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                 : "=f"(f[u][s].x), "=f"(f[u][s].y), "=f"(f[u][s].z), "=f"(f[u][s].w) : "r"(a) : "memory");
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int tt = t + u * T_STEP;
+            if (tt >= tokens) continue;
+            float v[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int s = 0; s < S; ++s) { v[0] += f[u][s].x; v[1] += f[u][s].y; v[2] += f[u][s].z; v[3] += f[u][s].w; }      // split order
+            const float rr[4] = {res[u].x, res[u].y, res[u].z, res[u].w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v[e] = apply_activation(v[e] + b[e], p.act) + rr[e];
+            const size_t o = (size_t)(m0 + tt) * p.ldc + n;
+            if (whole) {
+                if (p.c_is_h16) {
+                    h16x2 h0 = floats_to_h16x2(v[0], v[1]), h1 = floats_to_h16x2(v[2], v[3]);
+                    uint2 w; w.x = *(uint32_t*)&h0; w.y = *(uint32_t*)&h1;
+                    *(uint2*)((h16*)p.C + o) = w;
+                } else {
+                    *(float4*)((float*)p.C + o) = make_float4(v[0], v[1], v[2], v[3]);
+                }
+            } else {
+                for (int e = 0; e < 4 && n + e < n_lim; ++e) {
+                    if (p.c_is_h16) ((h16*)p.C)[o + e] = float_to_h16(v[e]);
+                    else ((float*)p.C)[o + e] = v[e];
+                }
+            }
+        }
+    }
+}
+
+// The same sum when the partial tiles' bands have been sent to their owners (swapped form): this CTA's own band
+// lies in its staging area, the S - 1 others' in the receive area, all [col][row of the band]; plain shared loads.
+template <int BN, int S>
+__device__ __forceinline__ void cluster_sum_received(const Params& p, const float* staged, const float* recv, int r, int tile_p, int tile_q) {
+    // A thread keeps its four features and walks over the tokens: everything that depends on the features
+    // only (bias, bounds, the addresses' fixed parts) is computed once.
+    constexpr int NR = TILE_P / S, GROUPS = NR / 4, COL_STEP = NUM_THREADS / GROUPS;
+    static_assert(NUM_THREADS % GROUPS == 0, "threads per band row group");
+    const int rg = threadIdx.x % GROUPS, col0 = threadIdx.x / GROUPS;
+    const int n = tile_p * TILE_P + r * NR + 4 * rg;                       // first feature
+    if (n >= p.rows_p) return;
+    const bool whole = n + 3 < p.rows_p;
+    float b[4] = {0.f, 0.f, 0.f, 0.f};
+    if (p.bias) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) if (n + e < p.rows_p) b[e] = __ldg(p.bias + n + e);
+    }
+    const float* src[S];
+#pragma unroll
+    for (int s = 0; s < S; ++s) src[s] = (s == r ? staged + (size_t)r * BN * NR : recv + (size_t)(s < r ? s : s - 1) * BN * NR) + 4 * rg;
+    const int m0 = tile_q * BN;
+    const int cols = min(BN, p.rows_q - m0);                               // tokens that exist
+    constexpr int U = 2;
+    for (int col = col0; col < cols; col += COL_STEP * U) {
+        float4 res[U];
+        float v[U][4];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int c = col + u * COL_STEP;
+            res[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (c < cols && p.residual) {
+                const float* rp = p.residual + (size_t)(m0 + c) * p.ldc + n;
+                if (whole) res[u] = __ldcg((const float4*)rp);
+                else { res[u].x = rp[0]; if (n + 1 < p.rows_p) res[u].y = rp[1]; if (n + 2 < p.rows_p) res[u].z = rp[2]; }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int c = col + u * COL_STEP;
+            v[u][0] = v[u][1] = v[u][2] = v[u][3] = 0.f;
+            if (c < cols) {
+#pragma unroll
+                for (int s = 0; s < S; ++s) {                              // split order
+                    const float4 f = *(const float4*)(src[s] + c * NR);
+                    v[u][0] += f.x; v[u][1] += f.y; v[u][2] += f.z; v[u][3] += f.w;
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int c = col + u * COL_STEP;
+            if (c >= cols) continue;
+            const float rr[4] = {res[u].x, res[u].y, res[u].z, res[u].w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v[u][e] = apply_activation(v[u][e] + b[e], p.act) + rr[e];
+            const size_t o = (size_t)(m0 + c) * p.ldc + n;
+            if (whole) {
+                if (p.c_is_h16) {
+                    h16x2 h0 = floats_to_h16x2(v[u][0], v[u][1]), h1 = floats_to_h16x2(v[u][2], v[u][3]);
+                    uint2 w; w.x = *(uint32_t*)&h0; w.y = *(uint32_t*)&h1;
+                    *(uint2*)((h16*)p.C + o) = w;
+                } else {
+                    *(float4*)((float*)p.C + o) = make_float4(v[u][0], v[u][1], v[u][2], v[u][3]);
+                }
+            } else {
+                for (int e = 0; e < 4 && n + e < p.rows_p; ++e) {
+                    if (p.c_is_h16) ((h16*)p.C)[o + e] = float_to_h16(v[u][e]);
+                    else ((float*)p.C)[o + e] = v[u][e];
+                }
+            }
+        }
+    }
+}
+
 template <int BN, int STAGES, bool SWAP>
 __global__ void __launch_bounds__(NUM_THREADS, SWAP ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, const Params p) {
@@ -188,12 +347,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], tmem_full_bar;
+    __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], tmem_full_bar, recv_bar;
     __shared__ uint32_t tmem_base_smem;
     __shared__ int last_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile_p = blockIdx.x, tile_q = blockIdx.y, split = blockIdx.z;
+    // Split K summed in a cluster, swapped form, 2, 4 or 8 splits: every CTA sends the bands of its partial tile
+    // to their owners (one bulk copy from shared memory to shared memory each) and adds up what it receives
+    // with plain shared-memory loads.  The staging area (a tile) and the receive area (S - 1 bands of it) must
+    // fit the stages; where they do not (128 tokens with 4 or 8 splits), or the addresses do not allow 16-byte
+    // accesses, the owners fetch the bands from the other CTAs' shared memory instead.
+    constexpr int TILE_BYTES = BN * TILE_P * 4;
+    const bool sum_by_push = SWAP && p.cluster_reduce && (p.splits == 2 || p.splits == 4 || p.splits == 8) &&
+                             TILE_BYTES * (2 * p.splits - 1) <= STAGES * STAGE_BYTES * p.splits && p.ldc % 4 == 0 &&
+                             !(((uintptr_t)p.C | (uintptr_t)p.residual | (uintptr_t)p.bias) & 15);
     const int num_kb_total = (p.K + BLOCK_K - 1) / BLOCK_K;
     const int kb_begin = split * p.kb_per_split;
     const int kb_end = min(num_kb_total, kb_begin + p.kb_per_split);
@@ -222,6 +390,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
         mbar_init(&tmem_full_bar, 1);
+        mbar_init(&recv_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_p) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_q) : "memory");
@@ -292,7 +461,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                     for (int j = 0; j < 32; ++j) v[j] = (j < LD_COLS && num_kb > 0) ? __uint_as_float(r[j]) : 0.f;
                     store_tile_row<BN, SWAP>(p, lane_row, tile_q * BN + c, v, LD_COLS);
                 }
-            } else if (p.cluster_reduce) {
+            } else if (p.cluster_reduce && !sum_by_push) {
                 // 32-bit partial tile -> this CTA's shared memory, [col 0..BN)[row 0..127], over the
                 // first stages (every load into them has been consumed by now)
                 // (swapped: [col][row], the lanes of a warp write consecutive floats; otherwise [row][col]
@@ -314,7 +483,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                                                                   : make_float4(0.f, 0.f, 0.f, 0.f);
                     }
                 }
-            } else {
+            } else if (!p.cluster_reduce) {
                 // 32-bit partial tile -> scratch: [split][tile][col 0..BN)[row 0..127]: the 32 lanes
                 // of a warp write 32 consecutive floats
                 const size_t tiles = (size_t)gridDim.x * gridDim.y;
@@ -335,7 +504,51 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     }
 
     // ---- split-K within a cluster: every CTA adds a band of rows over all partial tiles ----------
-    if (p.splits > 1 && p.cluster_reduce) {
+    if (p.splits > 1 && p.cluster_reduce && sum_by_push) {
+        const int S = p.splits, r = (int)cluster_ctarank();
+        const int nr = TILE_P / S;
+        const uint32_t band_bytes = (uint32_t)(BN * nr * 4);
+        float* const recv = (float*)(smem + TILE_BYTES);
+        if (warp >= 2) {
+            // the partial tile -> the staging area, [band][col][row of the band]: a band is one run of bytes
+            const int quad = warp & 3, rr = quad * 32 + lane;
+            float* part = (float*)smem + (rr / nr) * BN * nr + rr % nr;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += LD_COLS) {
+                uint32_t v[32];
+                if (ok) {
+                    const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c;
+                    if (LD_COLS == 32) tmem_ld32(taddr, v); else tmem_ld16(taddr, v);
+                    tmem_ld_wait();
+                }
+#pragma unroll
+                for (int j = 0; j < LD_COLS; ++j) part[(c + j) * nr] = (ok && num_kb > 0) ? __uint_as_float(v[j]) : 0.f;    // defined even if a wait ran out
+            }
+            fence_proxy_async_smem();                     // the staged tile is read by bulk copies
+        }
+        if (threadIdx.x == 0) mbar_expect_tx(&recv_bar, (uint32_t)(S - 1) * band_bytes);
+        tc_fence_before();
+        cluster_sync();                                   // every CTA's tile is staged, its stages idle, its barrier armed
+        if ((int)threadIdx.x < S && (int)threadIdx.x != r) {
+            const int t = (int)threadIdx.x;               // the owner of band t gets it, as contributor r
+            const uint32_t src = smem_u32(smem) + (uint32_t)t * band_bytes;
+            const uint32_t dst = map_to_cta(smem_u32(recv) + (uint32_t)(r < t ? r : r - 1) * band_bytes, (uint32_t)t);
+            const uint32_t bar = map_to_cta(smem_u32(&recv_bar), (uint32_t)t);
+            asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"(dst), "r"(src), "r"(band_bytes), "r"(bar) : "memory");
+        }
+        const bool got = mbar_wait(&recv_bar, 0, p.err, 4);
+        __syncwarp();
+        // What the others sent here has arrived, so they may let go of it: a CTA leaves when all have said so.
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        if (got) {
+            if (S == 2) cluster_sum_received<BN, 2>(p, (const float*)smem, recv, r, tile_p, tile_q);
+            else if (S == 4) cluster_sum_received<BN, 4>(p, (const float*)smem, recv, r, tile_p, tile_q);
+            else cluster_sum_received<BN, 8>(p, (const float*)smem, recv, r, tile_p, tile_q);
+        }
+        __syncwarp();
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    } else if (p.splits > 1 && p.cluster_reduce) {
         if (warp >= 2 && !ok) {                           // a wait ran out: the partial tile must still be defined
             const int rr = (warp & 3) * 32 + lane;
             float* part = (float*)smem + (SWAP ? rr : rr * (BN + 4));
@@ -350,60 +563,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         // loads from the other SMs' shared memory, 16- or 8-byte stores), else one by one.
         const bool vec = (S == 2 || S == 4 || S == 8) && p.ldc % 4 == 0 && !(((uintptr_t)p.C | (uintptr_t)p.residual | (uintptr_t)p.bias) & 15);
         if (vec) {
-            constexpr int LD = SWAP ? TILE_P : BN + 4;        // floats between consecutive columns (swapped) or rows
-            const int n_items = SWAP ? (n_rows / 4) * BN : n_rows * (BN / 4);
-            for (int item = threadIdx.x; item < n_items; item += NUM_THREADS) {
-                int row, col;                                 // of the first of the four elements
-                if (SWAP) { col = item / (n_rows / 4); row = row_lo + 4 * (item - col * (n_rows / 4)); }
-                else { row = row_lo + item / (BN / 4); col = 4 * (item - (item / (BN / 4)) * (BN / 4)); }
-                const int n = SWAP ? tile_p * TILE_P + row : tile_q * BN + col;      // first feature
-                const int m = SWAP ? tile_q * BN + col : tile_p * TILE_P + row;      // token
-                const int n_lim = SWAP ? p.rows_p : p.rows_q, m_lim = SWAP ? p.rows_q : p.rows_p;
-                if (m >= m_lim || n >= n_lim) continue;
-                const size_t o = (size_t)m * p.ldc + n;
-                const bool whole = n + 3 < n_lim;
-                float4 res = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (p.residual) {
-                    if (whole) res = __ldcg((const float4*)(p.residual + o));
-                    else { res.x = p.residual[o]; if (n + 1 < n_lim) res.y = p.residual[o + 1]; if (n + 2 < n_lim) res.z = p.residual[o + 2]; }
-                }
-                const uint32_t a = part_addr + (uint32_t)((SWAP ? col * LD + row : row * LD + col) * 4);
-                float4 f[MAX_CLUSTER];
-#pragma unroll
-                for (int s = 0; s < MAX_CLUSTER; ++s) {
-                    if (s < S) {
-                        asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
-                                     : "=f"(f[s].x), "=f"(f[s].y), "=f"(f[s].z), "=f"(f[s].w) : "r"(map_to_cta(a, (uint32_t)s)) : "memory");
-                    } else {
-                        f[s] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    }
-                }
-                float v[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                for (int s = 0; s < MAX_CLUSTER; ++s)
-                    if (s < S) { v[0] += f[s].x; v[1] += f[s].y; v[2] += f[s].z; v[3] += f[s].w; }      // split order
-                const float rr[4] = {res.x, res.y, res.z, res.w};
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    if (p.bias && n + e < n_lim) v[e] += __ldg(p.bias + n + e);
-                    v[e] = apply_activation(v[e], p.act);
-                    v[e] += rr[e];
-                }
-                if (whole) {
-                    if (p.c_is_h16) {
-                        h16x2 h0 = floats_to_h16x2(v[0], v[1]), h1 = floats_to_h16x2(v[2], v[3]);
-                        uint2 u; u.x = *(uint32_t*)&h0; u.y = *(uint32_t*)&h1;
-                        *(uint2*)((h16*)p.C + o) = u;
-                    } else {
-                        *(float4*)((float*)p.C + o) = make_float4(v[0], v[1], v[2], v[3]);
-                    }
-                } else {
-                    for (int e = 0; e < 4 && n + e < n_lim; ++e) {
-                        if (p.c_is_h16) ((h16*)p.C)[o + e] = float_to_h16(v[e]);
-                        else ((float*)p.C)[o + e] = v[e];
-                    }
-                }
-            }
+            if (S == 2) cluster_reduce_items<BN, SWAP, 2>(p, part_addr, tile_p, tile_q);
+            else if (S == 4) cluster_reduce_items<BN, SWAP, 4>(p, part_addr, tile_p, tile_q);
+            else cluster_reduce_items<BN, SWAP, 8>(p, part_addr, tile_p, tile_q);
         } else
         for (int item = threadIdx.x; item < n_rows * BN; item += NUM_THREADS) {
             // consecutive threads: consecutive features, which lie side by side in the output
