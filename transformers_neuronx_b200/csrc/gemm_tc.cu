@@ -1400,8 +1400,15 @@ TNX_EXPORT int tnx_gemm_tc_plan(int M, int N, int K, int n_sms, int* splits, lon
     // 64 tokens: a second round of CTAs, or a cluster of 3, costs more than a coarser split.)
     const int tiles = (N + TILE_P - 1) / TILE_P;
     const int kb = (K + BLOCK_K - 1) / BLOCK_K;
+    // Clusters of 4 and 8 do not fill the last places (the CTAs of a cluster lie in one GPC): measured at 8 tokens,
+    // 72 and 74 tiles split 4 ways (288 and 296 CTAs for 296 places) took 38 and 21 us where a split of 2 takes 31
+    // and 16, while 56 tiles split 4 ways (224) and 32 tiles split 8 ways (256) are the fastest of their kind and
+    // 148 tiles split 2 ways (296) still beat no split.  So clusters of 4 and 8 may take nine places in ten.
     int s = MAX_CLUSTER;
-    while (s > 1 && (tiles * s > 2 * n_sms || s * 4 > kb)) s >>= 1;
+    for (; s > 1; s >>= 1) {
+        if (s * 4 > kb) continue;
+        if (s == 2 ? tiles * s <= 2 * n_sms : tiles * s * 10 <= 2 * n_sms * 9) break;
+    }
     *splits = s;
     return 0;
 }
