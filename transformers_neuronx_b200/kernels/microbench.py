@@ -4,6 +4,8 @@
     python -m transformers_neuronx_b200.kernels.microbench attention-sizes
     python -m transformers_neuronx_b200.kernels.microbench attention-plans [--context 2040]
     python -m transformers_neuronx_b200.kernels.microbench gemm-plans [--models 30b,13b,6.7b,head]
+    python -m transformers_neuronx_b200.kernels.microbench gemm-tokens [--models 6.7b] [--tokens 8,16,...]
+    python -m transformers_neuronx_b200.kernels.microbench gemm-splits [--models 1.3b,...,66b] [--tokens 8]
 
 Every number is a CUDA-event time on one GPU: kernels that read more than the second-level cache
 holds between two calls are replayed back to back from one CUDA graph over several copies of their
@@ -221,6 +223,54 @@ def gemm_plans(models=("30b", "13b", "6.7b", "head")) -> None:
           f"more than 10 % behind in {sum(r > 1.1 for r in ratios)} of {len(ratios)}")
 
 
+FEW_TOKEN_SHAPES = {     # the four products of a layer: (N, K, adds into the 32-bit residual stream)
+    name: [(3 * h, h, False), (h, h, True), (4 * h, h, False), (h, 4 * h, True)]
+    for name, h in (("1.3b", 2048), ("2.7b", 2560), ("6.7b", 4096), ("13b", 5120), ("30b", 7168), ("66b", 9216))
+}
+
+
+def _rotating_product_time(M, N, K, with_res, dtype, **kw) -> float:
+    """Microseconds of one product whose weights come from memory: 16 calls over as many copies of the
+    matrix as exceed the second-level cache several times, replayed back to back from one CUDA graph."""
+    copies = max(2, int(600e6 // (N * K * 2)) + 1)
+    ws = [(torch.randn(N, K, device=DEV) * 0.02).to(dtype) for _ in range(copies)]
+    a = torch.randn(M, K, device=DEV).to(dtype)
+    bias = torch.randn(N, device=DEV)
+    out = torch.zeros(M, N, device=DEV, dtype=torch.float32 if with_res else dtype)
+    res = out if with_res else None
+    return _graph_time(lambda i: ops.gemm_tc(a, ws[i % copies], out, bias=bias, residual=res, **kw), 16)
+
+
+def gemm_tokens(models=("6.7b",), tokens=(1, 2, 4, 8, 16, 32, 64, 96, 128, 160, 192, 256, 384, 512), dtype=torch.float16) -> None:
+    """A layer's products by the number of tokens: time and the rate at which the weights stream."""
+    for name in models:
+        for (N, K, with_res) in FEW_TOKEN_SHAPES[name]:
+            row = {"sizes": name, "N": N, "K": K}
+            for M in tokens:
+                us = _rotating_product_time(M, N, K, with_res, dtype)
+                row[f"M{M}"] = [round(us, 1), round(N * K * 2 / us / 1e6, 2)]          # us, TB/s of weights
+            ops.raise_on_device_error()
+            print(json.dumps(row), flush=True)
+
+
+def gemm_splits(models=("1.3b", "2.7b", "6.7b", "13b", "30b", "66b"), tokens=8, dtype=torch.float16) -> None:
+    """The few-token product with K split 1, 2, 4 and 8 ways in clusters beside the library's own choice
+    (gemm_tc.cu: tnx_gemm_tc_plan), at the layer sizes of the family."""
+    ratios = []
+    for name in models:
+        for (N, K, with_res) in FEW_TOKEN_SHAPES[name]:
+            times = {"own choice": _rotating_product_time(tokens, N, K, with_res, dtype, few_tokens_kernel=False)}
+            for sp in (1, 2, 4, 8):
+                if sp * 4 <= -(-K // 64):
+                    times[f"split_{sp}"] = _rotating_product_time(tokens, N, K, with_res, dtype, splits=sp, cluster=True)
+            ops.raise_on_device_error()
+            best = min((v, k) for k, v in times.items() if k != "own choice")
+            ratios.append(times["own choice"] / best[0])
+            print(json.dumps(dict(sizes=name, N=N, K=K, M=tokens, ratio_to_best=round(ratios[-1], 3), best=best[1],
+                                  us={k: round(v, 1) for k, v in times.items()})), flush=True)
+    print(f"own choice / best split: mean {statistics.mean(ratios):.3f}, worst {max(ratios):.3f}")
+
+
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     sub = ap.add_subparsers(dest="what", required=True)
@@ -228,6 +278,12 @@ def main(argv=None) -> None:
     sub.add_parser("attention-sizes")
     sub.add_parser("attention-plans").add_argument("--context", type=int, default=2040)
     sub.add_parser("gemm-plans").add_argument("--models", default="30b,13b,6.7b,head")
+    gt = sub.add_parser("gemm-tokens")
+    gt.add_argument("--models", default="6.7b")
+    gt.add_argument("--tokens", default="1,2,4,8,16,32,64,96,128,160,192,256,384,512")
+    gs = sub.add_parser("gemm-splits")
+    gs.add_argument("--models", default="1.3b,2.7b,6.7b,13b,30b,66b")
+    gs.add_argument("--tokens", type=int, default=8)
     args = ap.parse_args(argv)
     if not torch.cuda.is_available():
         raise SystemExit("these timings need a GPU")
@@ -237,6 +293,10 @@ def main(argv=None) -> None:
         attention_sizes()
     elif args.what == "attention-plans":
         attention_plans(args.context)
+    elif args.what == "gemm-tokens":
+        gemm_tokens(tuple(args.models.split(",")), tuple(int(t) for t in args.tokens.split(",")))
+    elif args.what == "gemm-splits":
+        gemm_splits(tuple(args.models.split(",")), args.tokens)
     else:
         gemm_plans(tuple(args.models.split(",")))
 
