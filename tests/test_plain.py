@@ -135,6 +135,20 @@ def test_decode_attention_plan_keeps_its_rules():
                     assert warps < 16 or head_dim <= 128
                     assert splits == 1 or max_pages // splits >= 8, (pairs, max_pages, splits)
                     assert pairs * splits <= 4 * sms or splits == 1 or pairs * 10 <= sms * 27
+                    if pairs > 4 * sms:
+                        assert splits == 1, "more pairs than blocks fit at once: no split"
                     if max_pages >= 64 and pairs * 4 <= sms * 3:
                         assert pairs * splits * 2 > sms or splits == min(32, max_pages // 8), \
                             "few pairs and a long context: the splits fill the GPU as far as eight pages each allow"
+
+
+def test_decode_attention_plan_beyond_the_blocks_the_gpu_holds():
+    """More (row, head) pairs than blocks fit at once: many short contexts take blocks of four warps (a block's
+    own cost counts), and where four-warp blocks would leave most of their last round empty, eight-warp blocks
+    run (measured: 8,192 pairs over 256 tokens 176 against 208 us; 1,280 pairs over 1,024 tokens 123 against 115 us)."""
+    from transformers_neuronx_b200.kernels.ops import decode_attention_plan
+    assert decode_attention_plan(8192, 148, 128, 16) == (4, 1)
+    assert decode_attention_plan(4096, 148, 128, 8) == (4, 1)
+    assert decode_attention_plan(1280, 148, 128, 64) == (8, 1)          # 2.2 rounds of 592 blocks against 4.3 of 296
+    assert decode_attention_plan(608, 148, 128, 128) == (8, 1)          # one block more than a round of 592
+    assert decode_attention_plan(896, 148, 128, 64) == (4, 1)           # 1.5 rounds against 3.03

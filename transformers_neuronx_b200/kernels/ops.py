@@ -574,7 +574,9 @@ def decode_attention_plan(pairs: int, sms: int, head_dim: int, max_pages: int):
       * up to two pairs per SM: eight warps, no split (8 rows: 49 us);
       * up to 2.7 pairs per SM: four warps and three splits again (12 rows: 73 us; without splits the SMs
         hold two or three blocks each, 80);
-      * up to four pairs per SM: four warps, no split (16 rows: 91 us); beyond: eight warps (64 rows: 321 us).
+      * up to four pairs per SM: four warps, no split (16 rows: 91 us); beyond: four or eight warps, whichever
+        an estimate of rounds x (streaming + cost of a block) makes the faster (64 rows: eight warps, 321 us;
+        256 rows over 256 tokens: four warps, 176 against 208 us).
     (kernels/microbench.py attention-plans repeats the sweep.)  A split keeps at least eight pages, and contexts of fewer than 48 pages are not split in three (at
     500 tokens the plans without splits were 7-12 % faster there, and from a quarter of a pair per SM
     one block of sixteen warps was: 9 against 12 us at 3 rows)."""
@@ -594,7 +596,14 @@ def decode_attention_plan(pairs: int, sms: int, head_dim: int, max_pages: int):
         return 4, 3
     if pairs <= 4 * sms:
         return 4, 1
-    return 8, 1
+    # More pairs than the GPU holds blocks: blocks of four warps (four an SM) or of eight (two an SM) follow
+    # one another.  A block costs 0.9 / 1.6 us beside its pages' streaming (8,192 pairs over 256 tokens: 176
+    # against 208 us), and the last round of blocks is as long as a full one (1,280 pairs over 1,024 tokens:
+    # 123 us in three rounds of four-warp blocks, 115 us in five of eight-warp ones).
+    page_us = 16 * head_dim * 4 / 6.5e6                      # one page of keys and values at 6.5 TB/s
+    t4 = -(-pairs // (4 * sms)) * (4 * sms * max_pages * page_us + 0.9)
+    t8 = -(-pairs // (2 * sms)) * (2 * sms * max_pages * page_us + 1.6)
+    return (4, 1) if t4 < t8 else (8, 1)
 
 
 def attention_decode(q, cache, block_tables, token_request, positions, out, n_heads, scale, window=0, rows=None,
