@@ -143,16 +143,17 @@ def prefill_flops(cfg, T):
     return L * per_layer + 2 * V * H
 
 
-def time_decode(model, cfg, batch, steps, warmup, use_engine=False, end=None, per_step=None):
+def time_decode(model, cfg, batch, steps, warmup, use_engine=False, end=None, per_step=None, tight_pool=False):
     """K decode steps at `batch`, the context ending at `end` (default CONTEXT).  Returns
-    (ms_per_step, launches, h2d, d2h); per_step (a list) receives every timed step's own time in ms."""
+    (ms_per_step, launches, h2d, d2h); per_step (a list) receives every timed step's own time in ms.
+    tight_pool: pages for contexts of `end` only (large batches of short contexts), not of CONTEXT."""
     import torch
     from transformers_neuronx_b200.engine import StepEntry, StepRunner
     from transformers_neuronx_b200.kernels import ops
     total = steps + warmup
     end = end or CONTEXT
     ctx0 = end - total
-    pages = batch * (CONTEXT // 16)
+    pages = batch * ((end + 15) // 16 + 1 if tight_pool else CONTEXT // 16)
     runner = StepRunner(model, 16, pages, max(batch, 1), CONTEXT, use_cuda_graphs=True)
     g = torch.Generator().manual_seed(1)
     for b in range(batch):                                  # the cache as 2,048 - (W + K) earlier tokens left it:
@@ -341,10 +342,33 @@ def workload_family(steps, warmup, sizes=None):
     return rows
 
 
+def workload_sweep(steps, warmup):
+    """The decode step over batch x context at the default layer sizes: ms a step and the fraction of the
+    measured HBM copy rate, for every pair whose cache fits."""
+    import torch
+    hbm, _, _ = peaks()
+    model, cfg = build(OPT_6_7B["num_hidden_layers"])
+    rows = {}
+    for end in (256, 512, 1024, 2048):
+        row = {}
+        for batch in (1, 8, 16, 32, 64, 128, 256):
+            if batch * end > 144 * 2048:
+                continue
+            ms, _, _, _ = time_decode(model, cfg, batch, steps, warmup, end=end, tight_pool=True)
+            nbytes = decode_bytes(model, cfg, batch, end - steps / 2)
+            row[f"b{batch}"] = [round(ms, 3), round(nbytes / (ms / 1e3) / 1e9 / hbm, 3)]
+        rows[f"ctx{end}"] = row
+    del model
+    torch.cuda.empty_cache()
+    return rows
+
+
 def extra_workload(name, steps, warmup, sizes=None):
     """One of the further workloads alone, printed as one JSON line of its own."""
     if name == "family":
         res = workload_family(steps, warmup, sizes)
+    elif name == "sweep":
+        res = workload_sweep(steps, warmup)
     else:
         res = workload_decode30b(steps, warmup) if name == "decode30b" else workload_mixed13b()
     print(json.dumps(dict({"workload": name}, **res)))
@@ -376,7 +400,7 @@ def main():
     ap.add_argument("--skip-large", action="store_true", help="leave out the OPT-13B and OPT-30B workloads")
     ap.add_argument("--dtype", default="float16", choices=["float16", "bfloat16"],
                     help="the serving type (float16 is what OPT checkpoints are stored in)")
-    ap.add_argument("--workload", default=None, choices=["decode30b", "mixed13b", "family"],
+    ap.add_argument("--workload", default=None, choices=["decode30b", "mixed13b", "family", "sweep"],
                     help="run one of the further workloads instead of the default line")
     ap.add_argument("--sizes", default=None, help="for --workload family: comma-separated sizes (default: all of 125m .. 66b)")
     ap.add_argument("--only", default=None, choices=["decode", "prefill"],
