@@ -174,9 +174,13 @@ def test_gemm_tc_split_k(M, N, K, splits):
 
 @pytest.mark.parametrize("M,N,K,splits", [(8, 256, 4096, 4), (64, 130, 1024, 8), (2, 128, 512, 2), (20, 300, 1160, 3),
                                           (16, 4096, 4096, 8), (33, 520, 2048, 5), (64, 1000, 4104, 7), (5, 96, 640, 8),
-                                          (100, 520, 2048, 4), (128, 4096, 4096, 2), (70, 130, 1160, 3), (97, 1000, 8200, 8)])
+                                          (100, 520, 2048, 4), (128, 4096, 4096, 2), (70, 130, 1160, 3), (97, 1000, 8200, 8),
+                                          (24, 512, 2048, 4), (48, 1024, 4096, 8), (64, 256, 1024, 2), (120, 384, 512, 2)])
 def test_gemm_tc_split_k_in_clusters(M, N, K, splits):
-    """K split over the CTAs of a cluster, partial tiles added through distributed shared memory."""
+    """K split over the CTAs of a cluster, partial tiles added through distributed shared memory: the bands sent
+    to their owners by bulk copies (2, 4 or 8 splits, aligned output, tile and bands fit the stages: every tile
+    width is among the cases), fetched by the owners with 16-byte loads (128 tokens with 4 or 8 splits) or one by
+    one (other splits, or an output whose rows are not 16-byte aligned)."""
     o = ops()
     g = torch.Generator(device="cpu").manual_seed(splits + M)
     a = torch.randn(M, K, generator=g).bfloat16().to(DEV)
