@@ -2,7 +2,7 @@
 
     python -m transformers_neuronx_b200.kernels.microbench sampling
     python -m transformers_neuronx_b200.kernels.microbench attention-sizes
-    python -m transformers_neuronx_b200.kernels.microbench attention-plans [--context 2040]
+    python -m transformers_neuronx_b200.kernels.microbench attention-plans [--context 2040] [--rows 1,2,...] [--heads 32,40,56]
     python -m transformers_neuronx_b200.kernels.microbench gemm-plans [--models 30b,13b,6.7b,head]
     python -m transformers_neuronx_b200.kernels.microbench gemm-tokens [--models 6.7b] [--tokens 8,16,...]
     python -m transformers_neuronx_b200.kernels.microbench gemm-splits [--models 1.3b,...,66b] [--tokens 8]
@@ -144,18 +144,19 @@ def attention_sizes() -> None:
             del case
 
 
-def attention_plans(context: int = 2040) -> None:
+def attention_plans(context: int = 2040, rows=(1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64), heads=(32, 40, 56)) -> None:
     """Every plan of the decode attention kernel (4, 8, 16 warps a block; 1 to 16 splits) against
-    ops.decode_attention_plan's choice, 1 to 64 rows of 32, 40 and 56 heads of 128 dims."""
+    ops.decode_attention_plan's choice, 1 to 64 rows of 32, 40 and 56 heads of 128 dims (or the rows and heads given:
+    --rows 32,64,128,256 --heads 32 --context 256 is the many-short-contexts case)."""
     ratios = []
-    for H in (32, 40, 56):
-        for R in (1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64):
+    for H in heads:
+        for R in rows:
             case = _DecodeCase(R, H, H, 128, context)
             own = case.time()
             plans = {}
             for w in (4, 8, 16):
                 for S in (1, 2, 3, 4, 6, 8, 12, 16):
-                    if R * H * S <= 4096 and S * 8 <= -(-context // 16) * 2:
+                    if (S == 1 or R * H * S <= 4096) and S * 8 <= -(-context // 16) * 2:
                         plans[f"w{w}s{S}"] = round(case.time(n_splits=S, warps=w), 1)
             best = sorted(plans.items(), key=lambda kv: kv[1])[:3]
             ratios.append(own / best[0][1])
@@ -276,7 +277,10 @@ def main(argv=None) -> None:
     sub = ap.add_subparsers(dest="what", required=True)
     sub.add_parser("sampling").add_argument("--vocab", type=int, default=50272)
     sub.add_parser("attention-sizes")
-    sub.add_parser("attention-plans").add_argument("--context", type=int, default=2040)
+    apl = sub.add_parser("attention-plans")
+    apl.add_argument("--context", type=int, default=2040)
+    apl.add_argument("--rows", default="1,2,3,4,6,8,12,16,24,32,48,64")
+    apl.add_argument("--heads", default="32,40,56")
     sub.add_parser("gemm-plans").add_argument("--models", default="30b,13b,6.7b,head")
     gt = sub.add_parser("gemm-tokens")
     gt.add_argument("--models", default="6.7b")
@@ -292,7 +296,7 @@ def main(argv=None) -> None:
     elif args.what == "attention-sizes":
         attention_sizes()
     elif args.what == "attention-plans":
-        attention_plans(args.context)
+        attention_plans(args.context, tuple(int(r) for r in args.rows.split(",")), tuple(int(h) for h in args.heads.split(",")))
     elif args.what == "gemm-tokens":
         gemm_tokens(tuple(args.models.split(",")), tuple(int(t) for t in args.tokens.split(",")))
     elif args.what == "gemm-splits":
