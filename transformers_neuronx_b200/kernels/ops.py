@@ -597,12 +597,12 @@ def decode_attention_plan(pairs: int, sms: int, head_dim: int, max_pages: int):
     if pairs <= 4 * sms:
         return 4, 1
     # More pairs than the GPU holds blocks: blocks of four warps (four an SM) or of eight (two an SM) follow
-    # one another.  A block costs 0.9 / 1.6 us beside its pages' streaming (8,192 pairs over 256 tokens: 176
+    # one another.  A block costs 0.6 / 2.2 us beside its pages' streaming (8,192 pairs over 256 tokens: 176
     # against 208 us), and the last round of blocks is as long as a full one (1,280 pairs over 1,024 tokens:
-    # 123 us in three rounds of four-warp blocks, 115 us in five of eight-warp ones).
+    # 123 us in three rounds of four-warp blocks, 115 us in five of eight-warp ones; over 256 tokens 37 against 41).
     page_us = 16 * head_dim * 4 / 6.5e6                      # one page of keys and values at 6.5 TB/s
-    t4 = -(-pairs // (4 * sms)) * (4 * sms * max_pages * page_us + 0.9)
-    t8 = -(-pairs // (2 * sms)) * (2 * sms * max_pages * page_us + 1.6)
+    t4 = -(-pairs // (4 * sms)) * (4 * sms * max_pages * page_us + 0.6)
+    t8 = -(-pairs // (2 * sms)) * (2 * sms * max_pages * page_us + 2.2)
     return (4, 1) if t4 < t8 else (8, 1)
 
 
