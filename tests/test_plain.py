@@ -144,11 +144,11 @@ def test_decode_attention_plan_keeps_its_rules():
 
 def test_decode_attention_plan_beyond_the_blocks_the_gpu_holds():
     """More (row, head) pairs than blocks fit at once: many short contexts take blocks of four warps (a block's
-    own cost counts), and where four-warp blocks would leave most of their last round empty, eight-warp blocks
+    own cost counts), and where four-warp blocks would leave most of their last wave empty, eight-warp blocks
     run (measured: 8,192 pairs over 256 tokens 176 against 208 us; 1,280 pairs over 1,024 tokens 123 against 115 us)."""
     from transformers_neuronx_b200.kernels.ops import decode_attention_plan
     assert decode_attention_plan(8192, 148, 128, 16) == (4, 1)
     assert decode_attention_plan(4096, 148, 128, 8) == (4, 1)
-    assert decode_attention_plan(1280, 148, 128, 64) == (8, 1)          # 2.2 rounds of 592 blocks against 4.3 of 296
-    assert decode_attention_plan(608, 148, 128, 128) == (8, 1)          # one block more than a round of 592
-    assert decode_attention_plan(896, 148, 128, 64) == (4, 1)           # 1.5 rounds against 3.03
+    assert decode_attention_plan(1280, 148, 128, 64) == (8, 1)          # 2.2 waves of 592 blocks against 4.3 of 296
+    assert decode_attention_plan(608, 148, 128, 128) == (8, 1)          # one block more than a wave of 592
+    assert decode_attention_plan(896, 148, 128, 64) == (4, 1)           # 1.5 waves against 3.03

@@ -575,7 +575,7 @@ def decode_attention_plan(pairs: int, sms: int, head_dim: int, max_pages: int):
       * up to 2.7 pairs per SM: four warps and three splits again (12 rows: 73 us; without splits the SMs
         hold two or three blocks each, 80);
       * up to four pairs per SM: four warps, no split (16 rows: 91 us); beyond: four or eight warps, whichever
-        an estimate of rounds x (streaming + cost of a block) makes the faster (64 rows: eight warps, 321 us;
+        an estimate of waves x (streaming + cost of a block) makes the faster (64 rows: eight warps, 321 us;
         256 rows over 256 tokens: four warps, 176 against 208 us).
     (kernels/microbench.py attention-plans repeats the sweep.)  A split keeps at least eight pages, and contexts of fewer than 48 pages are not split in three (at
     500 tokens the plans without splits were 7-12 % faster there, and from a quarter of a pair per SM
@@ -598,8 +598,8 @@ def decode_attention_plan(pairs: int, sms: int, head_dim: int, max_pages: int):
         return 4, 1
     # More pairs than the GPU holds blocks: blocks of four warps (four an SM) or of eight (two an SM) follow
     # one another.  A block costs 0.6 / 2.2 us beside its pages' streaming (8,192 pairs over 256 tokens: 176
-    # against 208 us), and the last round of blocks is as long as a full one (1,280 pairs over 1,024 tokens:
-    # 123 us in three rounds of four-warp blocks, 115 us in five of eight-warp ones; over 256 tokens 37 against 41).
+    # against 208 us), and the last wave of blocks is as long as a full one (1,280 pairs over 1,024 tokens:
+    # 123 us in three waves of four-warp blocks, 115 us in five of eight-warp ones; over 256 tokens 37 against 41).
     page_us = 16 * head_dim * 4 / 6.5e6                      # one page of keys and values at 6.5 TB/s
     t4 = -(-pairs // (4 * sms)) * (4 * sms * max_pages * page_us + 0.6)
     t8 = -(-pairs // (2 * sms)) * (2 * sms * max_pages * page_us + 2.2)
