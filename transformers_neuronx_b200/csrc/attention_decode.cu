@@ -364,10 +364,10 @@ attention_decode_kernel(const DecodeParams p) {
 template <int LPK, int E>
 int launch_decode(int warps, dim3 grid, cudaStream_t stream, const DecodeParams& p) {
     if constexpr (E == 1 && LPK <= 16) {
-        if (warps == 16) return tnx_launch_pdl(attention_decode_kernel<LPK, E, 16>, grid, dim3(16 * 32), 0, stream, p);
+        if (warps == 16) return tnx_launch_in_order(attention_decode_kernel<LPK, E, 16>, grid, dim3(16 * 32), 0, stream, p);
     }
-    if (warps >= 8) return tnx_launch_pdl(attention_decode_kernel<LPK, E, 8>, grid, dim3(8 * 32), 0, stream, p);
-    return tnx_launch_pdl(attention_decode_kernel<LPK, E, 4>, grid, dim3(4 * 32), 0, stream, p);
+    if (warps >= 8) return tnx_launch_in_order(attention_decode_kernel<LPK, E, 8>, grid, dim3(8 * 32), 0, stream, p);
+    return tnx_launch_in_order(attention_decode_kernel<LPK, E, 4>, grid, dim3(4 * 32), 0, stream, p);
 }
 
 }  // namespace

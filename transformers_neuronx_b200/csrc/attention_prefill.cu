@@ -271,7 +271,7 @@ int launch(const PrefillParams& p, int n_items, cudaStream_t stream) {
         configured = true;
     }
     dim3 grid(p.n_heads, n_items);        // heads vary fastest: CTAs start in the order of the work items
-    return tnx_launch_pdl(attention_prefill_kernel<HEAD>, grid, dim3(WARPS * 32), smem, stream, p);
+    return tnx_launch_in_order(attention_prefill_kernel<HEAD>, grid, dim3(WARPS * 32), smem, stream, p);
 }
 
 }  // namespace

@@ -415,7 +415,7 @@ int launch_tc(const CUtensorMap& mq, const CUtensorMap& mkv, const TcPrefillPara
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    return tnx_launch_pdl(attention_prefill_tc_kernel<D, KS, VS>, dim3(n_heads, n_items), dim3(THREADS), smem, stream, mq, mkv, p);   // heads vary fastest
+    return tnx_launch_in_order(attention_prefill_tc_kernel<D, KS, VS>, dim3(n_heads, n_items), dim3(THREADS), smem, stream, mq, mkv, p);   // heads vary fastest
 }
 
 }  // namespace

@@ -98,11 +98,11 @@ TNX_EXPORT int tnx_attention_simt(const void* q, int q_stride, const void* cache
     const int blocks = (int)((pairs + warps - 1) / warps);
     const size_t smem = (size_t)warps * head_dim * sizeof(float);
     if (is_h16)
-        return tnx_launch_pdl(attention_simt_kernel<h16>, dim3(blocks), dim3(warps * 32), smem, stream,
+        return tnx_launch_in_order(attention_simt_kernel<h16>, dim3(blocks), dim3(warps * 32), smem, stream,
                               (const h16*)q, q_stride, (const h16*)cache, block_tables, bt_stride, token_request,
                               positions, (h16*)out, out_stride, n_tokens, n_heads, n_kv_heads, head_dim, page_size,
                               window, scale);
-    return tnx_launch_pdl(attention_simt_kernel<float>, dim3(blocks), dim3(warps * 32), smem, stream,
+    return tnx_launch_in_order(attention_simt_kernel<float>, dim3(blocks), dim3(warps * 32), smem, stream,
                           (const float*)q, q_stride, (const float*)cache, block_tables, bt_stride, token_request,
                           positions, (float*)out, out_stride, n_tokens, n_heads, n_kv_heads, head_dim, page_size,
                           window, scale);

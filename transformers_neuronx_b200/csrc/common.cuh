@@ -50,18 +50,20 @@ TNX_EXPORT int tnx_h16_is_float16() {
 #endif
 }
 
-// Programmatic dependent launch.  Every kernel of the engine is launched with the attribute that
-// lets it start while the kernel before it in the stream is still running.  The rules each kernel
-// keeps: it calls pdl_launch_dependents() at its start (the next kernel may begin its own set-up
-// and prefetch data that no kernel writes, i.e. weights), and it calls pdl_wait() before it reads
-// anything a preceding kernel wrote and before it writes anything at all.  pdl_wait() returns when
-// the preceding kernel has completed and its writes are visible; since every kernel waits before
-// it finishes, completion is transitive along the stream.
+// Programmatic dependent launch.  The matrix products and LayerNorm are launched with the attribute that
+// lets a kernel start while the kernel before it in the stream is still running (tnx_launch_ex with
+// early = 1); the other kernels are launched in stream order (tnx_launch_in_order).  The rules every kernel
+// keeps, so that either launch is right for it: it calls pdl_launch_dependents() at its start (the next kernel
+// may begin its own set-up and prefetch data that no kernel writes, i.e. weights), and it calls pdl_wait()
+// before it reads anything a preceding kernel wrote and before it writes anything at all.  pdl_wait() returns
+// when the preceding kernel has completed and its writes are visible; since every kernel waits before
+// it finishes, completion is transitive along the stream.  (In a kernel launched in stream order the wait
+// returns at once; its call of pdl_launch_dependents() still lets a following kernel with the attribute in.)
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // early != 0: the kernel may start before the kernel ahead of it has finished (it must keep the
-// rules above).  early == 0: an ordinary launch; the calls above are then no-ops.
+// rules above).  early == 0: an ordinary launch, after the kernel ahead of it.
 template <typename... KArgs, typename... Args>
 static inline int tnx_launch_ex(int early, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
                                 cudaStream_t stream, Args... args) {
@@ -92,7 +94,7 @@ static inline int tnx_launch_cluster(int early, dim3 cluster, void (*kernel)(KAr
     return 0;
 }
 template <typename... KArgs, typename... Args>
-static inline int tnx_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+static inline int tnx_launch_in_order(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                                  Args... args) {
     return tnx_launch_ex(0, kernel, grid, block, smem, stream, args...);
 }

@@ -48,7 +48,7 @@ __global__ void patch_tokens_kernel(int* __restrict__ tokens, const int* __restr
 
 TNX_EXPORT int tnx_patch_tokens(int* tokens, const int* src, const int* sampled, int n, cudaStream_t stream) {
     if (n <= 0) return 0;
-    return tnx_launch_pdl(patch_tokens_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, tokens, src, sampled, n);
+    return tnx_launch_in_order(patch_tokens_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, tokens, src, sampled, n);
 }
 
 // table_h16 / act_h16: 1 when the tables / the activation output are bfloat16, 0 for float.
@@ -59,7 +59,7 @@ TNX_EXPORT int tnx_embed(const void* tok_table, const float* pre, const int* ids
     if (H <= 0 || (!tok_table && !pre)) return TNX_ERR_BAD_ARG;
     const int threads = H >= 1024 ? 256 : 128;
 #define LAUNCH(TT, TA)                                                                                        \
-    tnx_launch_pdl(embed_kernel<TT, TA>, dim3(N), dim3(threads), 0, stream, (const TT*)tok_table, pre, ids,   \
+    tnx_launch_in_order(embed_kernel<TT, TA>, dim3(N), dim3(threads), 0, stream, (const TT*)tok_table, pre, ids,   \
                    (const TT*)pos_table, positions, pos_offset, out_f32, (TA*)out_act, H)
     if (table_h16 && act_h16) return LAUNCH(h16, h16);
     if (table_h16 && !act_h16) return LAUNCH(h16, float);
@@ -73,8 +73,8 @@ TNX_EXPORT int tnx_gather_rows(const void* table, const int* ids, void* out, int
     if (N <= 0) return 0;
     if (E <= 0) return TNX_ERR_BAD_ARG;
     const int threads = E >= 1024 ? 256 : 128;
-    if (table_h16 && act_h16) return tnx_launch_pdl(gather_rows_kernel<h16, h16>, dim3(N), dim3(threads), 0, stream, (const h16*)table, ids, (h16*)out, E);
-    if (table_h16) return tnx_launch_pdl(gather_rows_kernel<h16, float>, dim3(N), dim3(threads), 0, stream, (const h16*)table, ids, (float*)out, E);
-    if (act_h16) return tnx_launch_pdl(gather_rows_kernel<float, h16>, dim3(N), dim3(threads), 0, stream, (const float*)table, ids, (h16*)out, E);
-    return tnx_launch_pdl(gather_rows_kernel<float, float>, dim3(N), dim3(threads), 0, stream, (const float*)table, ids, (float*)out, E);
+    if (table_h16 && act_h16) return tnx_launch_in_order(gather_rows_kernel<h16, h16>, dim3(N), dim3(threads), 0, stream, (const h16*)table, ids, (h16*)out, E);
+    if (table_h16) return tnx_launch_in_order(gather_rows_kernel<h16, float>, dim3(N), dim3(threads), 0, stream, (const h16*)table, ids, (float*)out, E);
+    if (act_h16) return tnx_launch_in_order(gather_rows_kernel<float, h16>, dim3(N), dim3(threads), 0, stream, (const float*)table, ids, (h16*)out, E);
+    return tnx_launch_in_order(gather_rows_kernel<float, float>, dim3(N), dim3(threads), 0, stream, (const float*)table, ids, (float*)out, E);
 }

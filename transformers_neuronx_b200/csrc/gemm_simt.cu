@@ -75,7 +75,7 @@ template <typename TA, typename TW, typename TO>
 int launch(const void* A, const void* W, const float* bias, const float* residual, void* C, int M,
            int N, int K, int lda, int ldw, int ldc, int act, cudaStream_t stream) {
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-    return tnx_launch_pdl(gemm_simt_kernel<TA, TW, TO>, grid, dim3(256), 0, stream, (const TA*)A, (const TW*)W, bias,
+    return tnx_launch_in_order(gemm_simt_kernel<TA, TW, TO>, grid, dim3(256), 0, stream, (const TA*)A, (const TW*)W, bias,
                           residual, (TO*)C, M, N, K, lda, ldw, ldc, act);
 }
 

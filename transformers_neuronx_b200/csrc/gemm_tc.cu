@@ -1522,6 +1522,6 @@ __global__ void wait_runs_out_kernel(int* err, int code, unsigned long long limi
 
 TNX_EXPORT int tnx_selftest_wait_runs_out(int* err, int code, long long limit_ns, cudaStream_t stream) {
     if (!err || limit_ns <= 0 || limit_ns > 100000000ll) return TNX_ERR_BAD_ARG;      // 0.1 s at most
-    return tnx_launch_pdl(wait_runs_out_kernel, dim3(1), dim3(32), 0, stream, err, code, (unsigned long long)limit_ns);
+    return tnx_launch_in_order(wait_runs_out_kernel, dim3(1), dim3(32), 0, stream, err, code, (unsigned long long)limit_ns);
 }
 

@@ -42,7 +42,7 @@ TNX_EXPORT int tnx_kv_append(const void* k_src, const void* v_src, int src_strid
     const int work = 2 * n_kv_heads * head_dim / (wide ? vec : 1);
     const dim3 grid(N), block(work >= 256 ? 256 : (work >= 128 ? 128 : 64));
 #define KV_LAUNCH(T, V)                                                                                          \
-    tnx_launch_pdl(kv_append_kernel<T, V>, grid, block, 0, stream, (const T*)k_src, (const T*)v_src, src_stride, \
+    tnx_launch_in_order(kv_append_kernel<T, V>, grid, block, 0, stream, (const T*)k_src, (const T*)v_src, src_stride, \
                    slot_mapping, (T*)cache, n_kv_heads, head_dim, page_size)
     if (is_h16) return wide ? KV_LAUNCH(h16, 8) : KV_LAUNCH(h16, 1);
     return wide ? KV_LAUNCH(float, 4) : KV_LAUNCH(float, 1);
@@ -74,6 +74,6 @@ TNX_EXPORT int tnx_copy_rows(void* base, const int* pairs, int n_pairs, long lon
     if (!base || !pairs) return TNX_ERR_BAD_ARG;
     long long parts = (row_bytes + 16383) / 16384;                // 16 KB a block
     if (parts > 1024) parts = 1024;
-    return tnx_launch_pdl(copy_rows_kernel, dim3(n_pairs, (unsigned)parts), dim3(256), 0, stream, (uint8_t*)base, pairs, row_bytes);
+    return tnx_launch_in_order(copy_rows_kernel, dim3(n_pairs, (unsigned)parts), dim3(256), 0, stream, (uint8_t*)base, pairs, row_bytes);
 }
 

@@ -137,10 +137,10 @@ TNX_EXPORT int tnx_layer_norm(const float* x, const int* rows, const float* gamm
     const size_t smem = (size_t)H * sizeof(float);
     if (act_h16) {
         if (smem + 1024 > 48 * 1024) cudaFuncSetAttribute(layer_norm_kernel<h16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        return tnx_launch_pdl(layer_norm_kernel<h16>, dim3(n_rows), dim3(threads), smem, stream, x, rows, gamma, beta, eps, out_f32, (h16*)out_act, H);
+        return tnx_launch_in_order(layer_norm_kernel<h16>, dim3(n_rows), dim3(threads), smem, stream, x, rows, gamma, beta, eps, out_f32, (h16*)out_act, H);
     } else {
         if (smem + 1024 > 48 * 1024) cudaFuncSetAttribute(layer_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        return tnx_launch_pdl(layer_norm_kernel<float>, dim3(n_rows), dim3(threads), smem, stream, x, rows, gamma, beta, eps, out_f32, (float*)out_act, H);
+        return tnx_launch_in_order(layer_norm_kernel<float>, dim3(n_rows), dim3(threads), smem, stream, x, rows, gamma, beta, eps, out_f32, (float*)out_act, H);
     }
 }
 
@@ -148,6 +148,6 @@ TNX_EXPORT int tnx_pick_rows(const float* x, const int* rows, float* out_f32, vo
                              int n_rows, int H, int act_h16, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     const int threads = H >= 1024 ? 256 : 128;
-    if (act_h16) return tnx_launch_pdl(pick_rows_kernel<h16>, dim3(n_rows), dim3(threads), 0, stream, x, rows, out_f32, (h16*)out_act, H);
-    return tnx_launch_pdl(pick_rows_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, rows, out_f32, (float*)out_act, H);
+    if (act_h16) return tnx_launch_in_order(pick_rows_kernel<h16>, dim3(n_rows), dim3(threads), 0, stream, x, rows, out_f32, (h16*)out_act, H);
+    return tnx_launch_in_order(pick_rows_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, rows, out_f32, (float*)out_act, H);
 }
