@@ -44,16 +44,29 @@ __global__ void layer_norm_kernel(const float* __restrict__ x, const int* __rest
 // is there for rows of 5,120, which 8 loads per thread served a seventh slower).
 // Launched so that it may start while the kernel ahead still runs: it waits for that kernel's
 // results before its first load (measured: 1 % of a decode step).
-template <typename TA, int NV>
+template <typename TA, int NV, bool EARLY>
 __global__ void layer_norm_reg_kernel(const float* __restrict__ x, const int* __restrict__ rows,
                                       const float* __restrict__ gamma, const float* __restrict__ beta,
                                       float eps, float* __restrict__ out_f32, TA* __restrict__ out_act, int H) {
     __shared__ float scratch[32];
     pdl_launch_dependents();
-    pdl_wait();
     const int r = blockIdx.x;
-    const float4* src = (const float4*)(x + (size_t)(rows ? rows[r] : r) * H);
     const int n4 = H / 4;
+    // The scale and the shift are weights: no kernel writes them.  EARLY (few rows, where the kernel is a chain of
+    // round trips): they are fetched before the wait for the preceding kernel and are not a second round trip to
+    // the second-level cache behind the statistics.  With many rows they are read where they are used, which
+    // keeps the registers few and the blocks an SM many.
+    float4 g[EARLY ? NV : 1], b[EARLY ? NV : 1];
+    if (EARLY) {
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int c = threadIdx.x + i * blockDim.x;
+            g[i] = (gamma && c < n4) ? __ldg((const float4*)gamma + c) : make_float4(1.f, 1.f, 1.f, 1.f);
+            b[i] = (beta && c < n4) ? __ldg((const float4*)beta + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    pdl_wait();
+    const float4* src = (const float4*)(x + (size_t)(rows ? rows[r] : r) * H);
     float4 v[NV];
     float s = 0.f;
 #pragma unroll
@@ -79,8 +92,13 @@ __global__ void layer_norm_reg_kernel(const float* __restrict__ x, const int* __
         const int c = threadIdx.x + i * blockDim.x;
         if (c >= n4) continue;
         float4 y = make_float4((v[i].x - mean) * rstd, (v[i].y - mean) * rstd, (v[i].z - mean) * rstd, (v[i].w - mean) * rstd);
-        if (gamma) { const float4 g = ((const float4*)gamma)[c]; y.x *= g.x; y.y *= g.y; y.z *= g.z; y.w *= g.w; }
-        if (beta) { const float4 b = ((const float4*)beta)[c]; y.x += b.x; y.y += b.y; y.z += b.z; y.w += b.w; }
+        if (EARLY) {
+            if (gamma) { y.x *= g[i].x; y.y *= g[i].y; y.z *= g[i].z; y.w *= g[i].w; }
+            if (beta) { y.x += b[i].x; y.y += b[i].y; y.z += b[i].z; y.w += b[i].w; }
+        } else {
+            if (gamma) { const float4 gg = ((const float4*)gamma)[c]; y.x *= gg.x; y.y *= gg.y; y.z *= gg.z; y.w *= gg.w; }
+            if (beta) { const float4 bb = ((const float4*)beta)[c]; y.x += bb.x; y.y += bb.y; y.z += bb.z; y.w += bb.w; }
+        }
         if (out_f32) ((float4*)(out_f32 + (size_t)r * H))[c] = y;
         if (out_act) {
             TA* dst = out_act + (size_t)r * H + 4 * c;
@@ -123,9 +141,12 @@ TNX_EXPORT int tnx_layer_norm(const float* x, const int* rows, const float* gamm
         const int n4 = H / 4;
         const int threads = n4 >= 1024 ? 256 : (n4 >= 256 ? 128 : 64);
         const int nv = (n4 + threads - 1) / threads;
+        const bool early = n_rows <= 64;
 #define LN_LAUNCH(TA, NV)                                                                                      \
-    tnx_launch_ex(1, layer_norm_reg_kernel<TA, NV>, dim3(n_rows), dim3(threads), 0, stream, x, rows, gamma, beta, \
-                   eps, out_f32, (TA*)out_act, H)
+    (early ? tnx_launch_ex(1, layer_norm_reg_kernel<TA, NV, true>, dim3(n_rows), dim3(threads), 0, stream, x, rows, gamma, beta, \
+                           eps, out_f32, (TA*)out_act, H)                                                       \
+           : tnx_launch_ex(1, layer_norm_reg_kernel<TA, NV, false>, dim3(n_rows), dim3(threads), 0, stream, x, rows, gamma, beta, \
+                           eps, out_f32, (TA*)out_act, H))
 #define LN_PICK(TA)                                                                        \
     (nv <= 1 ? LN_LAUNCH(TA, 1) : nv <= 2 ? LN_LAUNCH(TA, 2) : nv <= 4 ? LN_LAUNCH(TA, 4) : nv <= 5 ? LN_LAUNCH(TA, 5) : LN_LAUNCH(TA, 8))
         if (act_h16) return LN_PICK(h16);
