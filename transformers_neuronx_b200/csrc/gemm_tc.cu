@@ -264,8 +264,19 @@ __device__ __forceinline__ void cluster_reduce_items(const Params& p, uint32_t p
 
 // The same sum when the partial tiles' bands have been sent to their owners (swapped form): this CTA's own band
 // lies in its staging area, the S - 1 others' in the receive area, all [col][row of the band]; plain shared loads.
+// What a thread of the sum over received bands needs from memory and can ask for long before the sum: the bias of
+// its four features (before the wait for the preceding kernel: no kernel writes it) and, where its tokens are at most
+// two, their residual values (right after that wait).  They then stand in registers through the main loop instead
+// of costing a round trip to the second-level cache in the product's tail.
+struct EarlyOperands {
+    float bias[4];
+    float4 res[2];
+    bool have;                   // the residual values are in res (else the sum reads them itself)
+};
+
 template <int BN, int S>
-__device__ __forceinline__ void cluster_sum_received(const Params& p, const float* staged, const float* recv, int r, int tile_p, int tile_q) {
+__device__ __forceinline__ void cluster_sum_received(const Params& p, const float* staged, const float* recv, int r, int tile_p, int tile_q,
+                                                     const EarlyOperands& early) {
     // A thread keeps its four features and walks over the tokens: everything that depends on the features
     // only (bias, bounds, the addresses' fixed parts) is computed once.
     constexpr int NR = TILE_P / S, GROUPS = NR / 4, COL_STEP = NUM_THREADS / GROUPS;
@@ -274,11 +285,7 @@ __device__ __forceinline__ void cluster_sum_received(const Params& p, const floa
     const int n = tile_p * TILE_P + r * NR + 4 * rg;                       // first feature
     if (n >= p.rows_p) return;
     const bool whole = n + 3 < p.rows_p;
-    float b[4] = {0.f, 0.f, 0.f, 0.f};
-    if (p.bias) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) if (n + e < p.rows_p) b[e] = __ldg(p.bias + n + e);
-    }
+    const float b[4] = {early.bias[0], early.bias[1], early.bias[2], early.bias[3]};
     const float* src[S];
 #pragma unroll
     for (int s = 0; s < S; ++s) src[s] = (s == r ? staged + (size_t)r * BN * NR : recv + (size_t)(s < r ? s : s - 1) * BN * NR) + 4 * rg;
@@ -292,7 +299,9 @@ __device__ __forceinline__ void cluster_sum_received(const Params& p, const floa
         for (int u = 0; u < U; ++u) {
             const int c = col + u * COL_STEP;
             res[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (c < cols && p.residual) {
+            if (early.have) {
+                res[u] = early.res[u];                                     // this thread's only tokens: col0 and col0 + COL_STEP
+            } else if (c < cols && p.residual) {
                 const float* rp = p.residual + (size_t)(m0 + c) * p.ldc + n;
                 if (whole) res[u] = __ldcg((const float4*)rp);
                 else { res[u].x = rp[0]; if (n + 1 < p.rows_p) res[u].y = rp[1]; if (n + 2 < p.rows_p) res[u].z = rp[2]; }
@@ -400,7 +409,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         tmem_alloc(&tmem_base_smem, TMEM_COLS);
         tmem_relinquish();
     }
+    // (the indices are those of cluster_sum_received)
+    EarlyOperands early;
+    early.have = false;
+    early.bias[0] = early.bias[1] = early.bias[2] = early.bias[3] = 0.f;
+    early.res[0] = early.res[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    const int e_groups = TILE_P / 4 / (sum_by_push ? p.splits : 1);
+    const int e_n = tile_p * TILE_P + (sum_by_push ? (int)cluster_ctarank() * (TILE_P / p.splits) : 0) + 4 * ((int)threadIdx.x % e_groups);
+    if (sum_by_push && p.bias) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) if (e_n + e < p.rows_p) early.bias[e] = __ldg(p.bias + e_n + e);
+    }
     pdl_wait();                       // from here on the preceding kernel's results may be read, and ours written
+    if (sum_by_push) {
+        const int col_step = NUM_THREADS / e_groups, col0 = (int)threadIdx.x / e_groups;
+        const int cols = min(BN, p.rows_q - tile_q * BN);
+        early.have = cols <= 2 * col_step;
+        if (early.have && p.residual && e_n < p.rows_p) {
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int c = col0 + u * col_step;
+                if (c < cols) {
+                    const float* rp = p.residual + (size_t)(tile_q * BN + c) * p.ldc + e_n;
+                    if (e_n + 3 < p.rows_p) early.res[u] = __ldcg((const float4*)rp);
+                    else { early.res[u].x = rp[0]; if (e_n + 1 < p.rows_p) early.res[u].y = rp[1]; if (e_n + 2 < p.rows_p) early.res[u].z = rp[2]; }
+                }
+            }
+        }
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -542,9 +578,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         // What the others sent here has arrived, so they may let go of it: a CTA leaves when all have said so.
         asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
         if (got) {
-            if (S == 2) cluster_sum_received<BN, 2>(p, (const float*)smem, recv, r, tile_p, tile_q);
-            else if (S == 4) cluster_sum_received<BN, 4>(p, (const float*)smem, recv, r, tile_p, tile_q);
-            else cluster_sum_received<BN, 8>(p, (const float*)smem, recv, r, tile_p, tile_q);
+            if (S == 2) cluster_sum_received<BN, 2>(p, (const float*)smem, recv, r, tile_p, tile_q, early);
+            else if (S == 4) cluster_sum_received<BN, 4>(p, (const float*)smem, recv, r, tile_p, tile_q, early);
+            else cluster_sum_received<BN, 8>(p, (const float*)smem, recv, r, tile_p, tile_q, early);
         }
         __syncwarp();
         asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
