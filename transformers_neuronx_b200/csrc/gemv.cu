@@ -78,6 +78,19 @@ gemv_kernel(const h16* __restrict__ A, int lda, const h16* __restrict__ W, int l
         // The row is read from memory once and kept in shared memory (behind the activations' pieces)
         // for the two further walks.
         float4* rowf = (float4*)(xs + M * K8);
+        // The scale and the shift of this thread's first EARLY pieces are asked for together with the row, so that
+        // they are not one more round trip to the second-level cache behind the statistics.
+        constexpr int EARLY = 4;
+        float4 ga[EARLY][2], be[EARLY][2];
+#pragma unroll
+        for (int i = 0; i < EARLY; ++i) {
+            const int p = tid + i * THREADS;
+            const bool in = p < K8;
+            ga[i][0] = (ln.gamma && in) ? __ldg((const float4*)ln.gamma + 2 * p) : make_float4(1.f, 1.f, 1.f, 1.f);
+            ga[i][1] = (ln.gamma && in) ? __ldg((const float4*)ln.gamma + 2 * p + 1) : make_float4(1.f, 1.f, 1.f, 1.f);
+            be[i][0] = (ln.beta && in) ? __ldg((const float4*)ln.beta + 2 * p) : make_float4(0.f, 0.f, 0.f, 0.f);
+            be[i][1] = (ln.beta && in) ? __ldg((const float4*)ln.beta + 2 * p + 1) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
 #pragma unroll 1
         for (int m = 0; m < M; ++m) {
             const float4* src = (const float4*)(ln.x + (size_t)m * ln.ldx);
@@ -97,24 +110,28 @@ gemv_kernel(const h16* __restrict__ A, int lda, const h16* __restrict__ W, int l
                 q += ((d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3)) + ((d4 * d4 + d5 * d5) + (d6 * d6 + d7 * d7));
             }
             const float rstd = 1.0f / sqrtf(block_sum(q, lnred) / (float)K + ln.eps);
-            for (int p = tid; p < K8; p += THREADS) {
+            auto finish_piece = [&](int p, const float4& g0, const float4& g1, const float4& b0, const float4& b1) {
                 const float4 a = rowf[2 * p], b = rowf[2 * p + 1];
                 float y[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
 #pragma unroll
                 for (int e = 0; e < 8; ++e) y[e] = (y[e] - mean) * rstd;
-                if (ln.gamma) {
-                    const float4 ga = ((const float4*)ln.gamma)[2 * p], gb = ((const float4*)ln.gamma)[2 * p + 1];
-                    y[0] *= ga.x; y[1] *= ga.y; y[2] *= ga.z; y[3] *= ga.w; y[4] *= gb.x; y[5] *= gb.y; y[6] *= gb.z; y[7] *= gb.w;
-                }
-                if (ln.beta) {
-                    const float4 ba = ((const float4*)ln.beta)[2 * p], bb = ((const float4*)ln.beta)[2 * p + 1];
-                    y[0] += ba.x; y[1] += ba.y; y[2] += ba.z; y[3] += ba.w; y[4] += bb.x; y[5] += bb.y; y[6] += bb.z; y[7] += bb.w;
-                }
+                y[0] = y[0] * g0.x + b0.x; y[1] = y[1] * g0.y + b0.y; y[2] = y[2] * g0.z + b0.z; y[3] = y[3] * g0.w + b0.w;
+                y[4] = y[4] * g1.x + b1.x; y[5] = y[5] * g1.y + b1.y; y[6] = y[6] * g1.z + b1.z; y[7] = y[7] * g1.w + b1.w;
                 h16x2 h0 = floats_to_h16x2(y[0], y[1]), h1 = floats_to_h16x2(y[2], y[3]);
                 h16x2 h2 = floats_to_h16x2(y[4], y[5]), h3 = floats_to_h16x2(y[6], y[7]);
                 uint4 u;
                 u.x = *(uint32_t*)&h0; u.y = *(uint32_t*)&h1; u.z = *(uint32_t*)&h2; u.w = *(uint32_t*)&h3;
                 xs[m * K8 + p] = u;
+            };
+#pragma unroll
+            for (int i = 0; i < EARLY; ++i) {
+                const int p = tid + i * THREADS;
+                if (p < K8) finish_piece(p, ga[i][0], ga[i][1], be[i][0], be[i][1]);
+            }
+            for (int p = tid + EARLY * THREADS; p < K8; p += THREADS) {       // rows longer than the early pieces cover
+                const float4 one = make_float4(1.f, 1.f, 1.f, 1.f), zero = make_float4(0.f, 0.f, 0.f, 0.f);
+                finish_piece(p, ln.gamma ? ((const float4*)ln.gamma)[2 * p] : one, ln.gamma ? ((const float4*)ln.gamma)[2 * p + 1] : one,
+                             ln.beta ? ((const float4*)ln.beta)[2 * p] : zero, ln.beta ? ((const float4*)ln.beta)[2 * p + 1] : zero);
             }
         }
     }
@@ -126,6 +143,17 @@ gemv_kernel(const h16* __restrict__ A, int lda, const h16* __restrict__ W, int l
         for (int r = 0; r < R; ++r)
 #pragma unroll
             for (int m = 0; m < M; ++m) acc[r][m] = 0.f;
+        // What the threads that finish the rows need from memory is asked for before the walk over K, not after it
+        // (where the whole block would wait for the round trip).
+        float early_bias = 0.f, early_res = 0.f;
+        if (tid < R * M) {
+            const int r = tid / M, m = tid - r * M;
+            const int n = row0 + r;
+            if (n < row_end) {
+                if (bias) early_bias = __ldg(bias + n);
+                if (residual) early_res = residual[(size_t)m * ldc + n];
+            }
+        }
         for (int p = tid; p < K8; p += THREADS) {
             uint4 nxt[R];
             const int pn = p + THREADS;
@@ -162,10 +190,10 @@ gemv_kernel(const h16* __restrict__ A, int lda, const h16* __restrict__ W, int l
                 float v = 0.f;
 #pragma unroll
                 for (int w = 0; w < THREADS / 32; ++w) v += red[w][tid];
-                if (bias) v += bias[n];
+                v += early_bias;
                 v = apply_activation(v, act);
                 const size_t o = (size_t)m * ldc + n;
-                if (residual) v += residual[o];
+                v += early_res;
                 if (c_is_h16) ((h16*)C)[o] = float_to_h16(v);
                 else ((float*)C)[o] = v;
             }
