@@ -520,6 +520,38 @@ def test_layer_norm(rows, H, affine):
     assert rel_err(xin, P.layer_norm(x.cpu(), None if w is None else w.cpu(), None if b is None else b.cpu(), 1e-5).to(DEV)) <= 1e-5
 
 
+@pytest.mark.parametrize("H", [768, 4096, 5120])
+def test_layer_norm_of_few_rows_and_of_many_is_the_same(H):
+    """Up to 64 rows the kernel fetches the scale and the shift before it waits for the kernel ahead of it, beyond
+    it reads them where it uses them: a row's result is the same bits either way (a decode row and a row of a
+    prompt portion), also when the kernel ahead of it is one of the engine's own that lets it in early."""
+    o = ops()
+    g = torch.Generator().manual_seed(H)
+    x = (torch.randn(200, H, generator=g) * 2 + 0.5).to(DEV)
+    w, b = torch.randn(H, generator=g).to(DEV), torch.randn(H, generator=g).to(DEV)
+    many = torch.empty(200, H, dtype=torch.bfloat16, device=DEV)
+    o.layer_norm(x, w, b, 1e-5, out_act=many)
+    for rows in (1, 8, 64):
+        few = torch.empty(rows, H, dtype=torch.bfloat16, device=DEV)
+        o.layer_norm(x[:rows], w, b, 1e-5, out_act=few)
+        assert torch.equal(few, many[:rows])
+    # behind a product of the engine (which lets the next kernel start early) that writes the rows it normalises
+    a = torch.randn(8, 256, generator=g).bfloat16().to(DEV)
+    wt = (torch.randn(H, 256, generator=g) / 16).bfloat16().to(DEV)
+    y = torch.zeros(8, H, device=DEV)
+    outs = []
+    for _ in range(3):
+        y.zero_()
+        o.gemm_tc(a, wt, y)
+        z = torch.empty(8, H, dtype=torch.bfloat16, device=DEV)
+        o.layer_norm(y, w, b, 1e-5, out_act=z)
+        outs.append(z)
+    o.raise_on_device_error()
+    want = P.layer_norm((a.float() @ wt.float().t()).cpu(), w.cpu(), b.cpu(), 1e-5).to(DEV)
+    assert rel_err(outs[0], want) <= 5e-3
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[1], outs[2])
+
+
 @pytest.mark.parametrize("tdt", [torch.float32, torch.bfloat16])
 def test_embedding(tdt):
     V, H, Pn, off = 301, 72, 50, 2
