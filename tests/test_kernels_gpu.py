@@ -522,16 +522,16 @@ def test_layer_norm(rows, H, affine):
 
 @pytest.mark.parametrize("H", [768, 4096, 5120])
 def test_layer_norm_of_few_rows_and_of_many_is_the_same(H):
-    """Up to 64 rows the kernel fetches the scale and the shift before it waits for the kernel ahead of it, beyond
+    """Up to 256 rows the kernel fetches the scale and the shift before it waits for the kernel ahead of it, beyond
     it reads them where it uses them: a row's result is the same bits either way (a decode row and a row of a
     prompt portion), also when the kernel ahead of it is one of the engine's own that lets it in early."""
     o = ops()
     g = torch.Generator().manual_seed(H)
-    x = (torch.randn(200, H, generator=g) * 2 + 0.5).to(DEV)
+    x = (torch.randn(600, H, generator=g) * 2 + 0.5).to(DEV)
     w, b = torch.randn(H, generator=g).to(DEV), torch.randn(H, generator=g).to(DEV)
-    many = torch.empty(200, H, dtype=torch.bfloat16, device=DEV)
+    many = torch.empty(600, H, dtype=torch.bfloat16, device=DEV)
     o.layer_norm(x, w, b, 1e-5, out_act=many)
-    for rows in (1, 8, 64):
+    for rows in (1, 8, 64, 256):
         few = torch.empty(rows, H, dtype=torch.bfloat16, device=DEV)
         o.layer_norm(x[:rows], w, b, 1e-5, out_act=few)
         assert torch.equal(few, many[:rows])

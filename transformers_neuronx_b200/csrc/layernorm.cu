@@ -141,7 +141,7 @@ TNX_EXPORT int tnx_layer_norm(const float* x, const int* rows, const float* gamm
         const int n4 = H / 4;
         const int threads = n4 >= 1024 ? 256 : (n4 >= 256 ? 128 : 64);
         const int nv = (n4 + threads - 1) / threads;
-        const bool early = n_rows <= 64;
+        const bool early = n_rows <= 256;
 #define LN_LAUNCH(TA, NV)                                                                                      \
     (early ? tnx_launch_ex(1, layer_norm_reg_kernel<TA, NV, true>, dim3(n_rows), dim3(threads), 0, stream, x, rows, gamma, beta, \
                            eps, out_f32, (TA*)out_act, H)                                                       \
